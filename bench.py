@@ -1,0 +1,354 @@
+#!/usr/bin/env python
+"""Benchmark of the decode hot path: Llama-2-7B architecture, Q4_K weights (Q6_K logits matrix), batch 1,
+fp16 KV cache, 512-token prompt, greedy decoding (BASELINE configs[2]).  Synthetic seeded weights generated on
+the GPU stand in for a checkpoint.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--gemv]
+
+One step = one decoded token.  Prints ONE JSON line (rank 0).  `value` is tokens/s with everything resident in
+HBM (device-side greedy loop, CUDA events); `e2e` is the same metric through the per-token public call with the
+token id going host->device and the logits + greedy token coming back to pinned host memory every step.
+With N > 1 the path does not shard at this model size (replicas only): every rank decodes its own sequence.
+`--impl reference` times the reference's CPU operator path (CPU oracle port, all host threads) on a bounded
+sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+PROMPT_LEN = 512
+WORKLOAD = "llama2-7b-arch q4_k (q6_k logits) bs1 decode, 512-token prompt, fp16 KV (BASELINE configs[2])"
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs, burst copy)"
+    return 6650.0, "fallback (6.65 TB/s earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples during the timed region."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.p = None
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                       "-i", str(gpu_index)], stdout=self.f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.p = None
+
+    def stop(self):
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except Exception:
+            self.p.kill()
+        self.f.flush()
+        rows = [r.strip().split(", ") for r in open(self.f.name) if r.strip()]
+        os.unlink(self.f.name)
+        sm, mx, reasons, power = [], [], set(), []
+        for r in rows:
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2])); power.append(float(r[3]))
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                    if val.strip().lower().startswith("active"):
+                        reasons.add(name)
+            except Exception:
+                continue
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "power_w_max": float(max(power)),
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def build_model(backend, seed=0):
+    """Llama-2-7B-architecture model with device-generated weights; layer 0 and the logits matrix keep their raw
+    GGUF blocks so the CPU baseline can run on exactly the same bytes."""
+    from slai_b200 import synth
+    from slai_b200.models import LLAMA2_7B, Llama2
+    from slai_b200.ops import GpuQuantMatrix, GpuVector
+    cfg = LLAMA2_7B
+    m = Llama2(backend, cfg)
+    sid = seed * 1_000_003
+    raw = {}
+    mats = {}
+    for l in range(cfg.n_layers):
+        for i, (name, (r, c)) in enumerate(cfg.matrix_shapes().items()):
+            qm = GpuQuantMatrix.synthetic(backend, synth.FMT_Q4_K, r, c, sid + 100 * l + i + 1, 0.02, keep_raw=(l == 0))
+            m.set_matrix(name, l, qm)
+            mats[(name, l)] = qm
+            if l == 0:
+                raw[name] = qm
+        ones = np.ones(cfg.dim, dtype=np.float32)
+        m.set_f32("attn_norm", l, ones)
+        m.set_f32("ffn_norm", l, ones)
+    emb = GpuVector(backend, cfg.vocab_size * cfg.dim)
+    backend.check(backend.lib.slai_synth_normal_f32(backend.h, C.c_void_p(emb.ptr), emb.n, sid + 7_000_001, 0.02))
+    m.set_f32("token_embd", -1, emb)
+    del emb
+    m.set_f32("out_norm", -1, np.ones(cfg.dim, dtype=np.float32))
+    out = GpuQuantMatrix.synthetic(backend, synth.FMT_Q6_K, cfg.vocab_size, cfg.dim, sid + 7_000_002, 0.02, keep_raw=True)
+    m.set_matrix("output", -1, out)
+    raw["output"] = out
+    return cfg, m, mats, raw
+
+
+def time_dominant_kernel(backend, ctx, cfg, mats, rounds=8):
+    """Average duration of the dominant kernel (the dequant-GEMV, here on the 11008x4096 Q4_K gate matrices of
+    all 32 layers in turn: 813 MB, larger than L2), CUDA events on the launching stream."""
+    from slai_b200 import synth
+    x = backend.vector(np.random.default_rng(0).standard_normal(cfg.dim).astype(np.float32))
+    out = backend.zeros(cfg.hidden_dim)
+    gates = [mats[("w_gate", l)] for l in range(cfg.n_layers)]
+    for g in gates[:4]:
+        ctx.matmul_quant_assign(out, g, x)
+    backend.synchronize()
+    backend.timer_start()
+    for _ in range(rounds):
+        for g in gates:
+            ctx.matmul_quant_assign(out, g, x)
+    ms = backend.timer_stop()
+    n = rounds * len(gates)
+    per = ms / n * 1e-3
+    algo = synth.gemv_bytes(synth.FMT_Q4_K, cfg.hidden_dim, cfg.dim)
+    return algo, per, n
+
+
+def gemv_microbench(backend, ctx, peak):
+    """BASELINE configs[1]: quantised GEMV on the four Llama-2-7B shapes x four formats, rotating over enough
+    distinct weight copies that the working set exceeds L2."""
+    from slai_b200 import synth
+    from slai_b200.ops import GpuQuantMatrix
+    res = []
+    for (M, K) in ((4096, 4096), (11008, 4096), (4096, 11008), (32000, 4096)):
+        for fmt in (synth.FMT_Q8_0, synth.FMT_Q4_K, synth.FMT_Q5_K, synth.FMT_Q6_K):
+            algo = synth.gemv_bytes(fmt, M, K)
+            ncopies = max(2, int(np.ceil(200e6 / algo)) + 1)
+            mats = [GpuQuantMatrix.synthetic(backend, fmt, M, K, 1000 + i, 0.02) for i in range(ncopies)]
+            x = backend.vector(np.random.default_rng(1).standard_normal(K).astype(np.float32))
+            out = backend.zeros(M)
+            for m_ in mats[:3]:
+                ctx.matmul_quant_assign(out, m_, x)
+            backend.synchronize()
+            reps = max(1, 60 // ncopies)
+            backend.timer_start()
+            for _ in range(reps):
+                for m_ in mats:
+                    ctx.matmul_quant_assign(out, m_, x)
+            ms = backend.timer_stop()
+            per = ms * 1e-3 / (reps * ncopies)
+            res.append({"M": M, "K": K, "fmt": synth.FMT_NAMES[fmt], "us": round(per * 1e6, 2), "GBs": round(algo / per / 1e9, 1),
+                        "frac": round(algo / per / 1e9 / peak, 3)})
+            del mats
+    return res
+
+
+def cpu_layer_times(cfg, raw, pos, nthreads, reps=2):
+    """The reference's CPU path on layer 0 and the logits matrix of the benchmark model: weights dequantised to
+    f32 at load (models/llama2/cpu.rs:200-219), dense f32 gemv per matrix (:370-376), attention over `pos`+1
+    positions.  Returns (seconds per layer, seconds for the logits gemv)."""
+    from oracle import oracle as O
+    from slai_b200 import synth
+    shapes = cfg.matrix_shapes()
+    W = {}
+    for name, (r, c) in shapes.items():
+        W[name] = O.dequantize(synth.FMT_Q4_K, raw[name].raw.to_numpy()).reshape(r, c)
+    Wout = O.dequantize(synth.FMT_Q6_K, raw["output"].raw.to_numpy()).reshape(cfg.vocab_size, cfg.dim)
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal(cfg.dim).astype(np.float32)
+    ones = np.ones(cfg.dim, np.float32)
+    kc = rng.standard_normal((pos + 1, cfg.kv_dim)).astype(np.float32)
+    vc = rng.standard_normal((pos + 1, cfg.kv_dim)).astype(np.float32)
+    best_layer, best_out = 1e9, 1e9
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        xb = O.rms_norm(x, ones, cfg.rms_norm_eps)
+        q = O.gemv_f32(W["wq"], xb, nthreads)
+        k = O.gemv_f32(W["wk"], xb, nthreads)
+        v = O.gemv_f32(W["wv"], xb, nthreads)
+        q, k = O.rope(q, k, cfg.head_size, cfg.kv_dim, pos)
+        kc[pos], vc[pos] = k, v
+        att, _ = O.attention(q, kc, vc, seq_len=pos + 1, kv_dim=cfg.kv_dim, kv_mul=1, n_heads=cfg.n_q_heads, head_size=cfg.head_size, pos=pos)
+        x2 = x + O.gemv_f32(W["wo"], att, nthreads)
+        xb = O.rms_norm(x2, ones, cfg.rms_norm_eps)
+        hb = O.silu_gate(O.gemv_f32(W["w_gate"], xb, nthreads), O.gemv_f32(W["w_up"], xb, nthreads))
+        x2 = x2 + O.gemv_f32(W["w_down"], hb, nthreads)
+        t1 = time.perf_counter()
+        logits = O.gemv_f32(Wout, O.rms_norm(x2, ones, cfg.rms_norm_eps), nthreads)
+        t2 = time.perf_counter()
+        best_layer, best_out = min(best_layer, t1 - t0), min(best_out, t2 - t1)
+    return best_layer, best_out
+
+
+def run_reference(args, rank, world):
+    """Reference arm: the reference's CPU implementation of the path (the oracle port; the Rust reference cannot be
+    built here) with all host threads, on a bounded sample per step: one full layer + the logits GEMV of the same
+    model, extrapolated to 32 layers."""
+    if rank != 0:
+        return
+    from slai_b200.ops import Backend
+    backend = Backend(0)
+    cfg, m, mats, raw = build_model(backend)
+    nthreads = os.cpu_count() or 1
+    pos = PROMPT_LEN
+    times = []
+    for i in range(args.warmup + args.steps):
+        tl, to = cpu_layer_times(cfg, raw, pos + i, nthreads, reps=1)
+        if i >= args.warmup:
+            times.append(cfg.n_layers * tl + to)
+    ms = 1e3 * float(np.mean(times))
+    val = 1e3 / ms
+    line = {"impl": "reference", "metric": "decode tok/s bs1 (Llama-2-7B Q4_K)", "value": val, "unit": "tok/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "prompt_len": PROMPT_LEN},
+            "cpu_baseline": {"value": val, "unit": "tok/s", "cores": nthreads, "kind": "port",
+                             "sample": "per step: one full layer (7 dense f32 gemvs on dequantised weights, attention over the "
+                                       "prompt) + the logits gemv on the host, layer time x32"},
+            "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--gemv", action="store_true", help="also run the 16-case quantised GEMV microbenchmark")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local))
+
+    from slai_b200 import synth
+    from slai_b200.ops import Backend, LlmContext
+    backend = Backend(local)
+    ctx = LlmContext(backend)
+    peak, peak_src = measured_peaks()
+    cfg, m, mats, raw = build_model(backend, seed=rank)
+    K, W = args.steps, args.warmup
+    assert PROMPT_LEN + W + K + W + K < cfg.seq_len
+
+    rng = np.random.default_rng(42 + rank)
+    prompt = rng.integers(0, cfg.vocab_size, size=PROMPT_LEN).astype(np.int32)
+    m.prefill(prompt[:-1], 0)
+    pos = PROMPT_LEN - 1
+    tok = int(prompt[-1])
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        backend.synchronize()
+
+    # ---- device-resident decode: W warm-up tokens, then K timed tokens ----
+    warm = m.generate(tok, pos, W)
+    tok, pos = int(warm[-1]), pos + W
+    sampler = ClockSampler(local)
+    barrier()
+    backend.timer_start()
+    toks = m.generate(tok, pos, K)
+    ms = backend.timer_stop()
+    barrier()
+    clocks = sampler.stop()
+    pos_first, pos_last = pos, pos + K - 1
+    tok, pos = int(toks[-1]), pos + K
+
+    # ---- end to end through the per-token call: token id H2D, logits + greedy id D2H (pinned), every step ----
+    pinned = C.c_void_p()
+    backend.check(backend.lib.slai_malloc_host(backend.h, cfg.vocab_size * 4, C.byref(pinned)))
+    for _ in range(W):
+        tok = m.decode_into(tok, pos, pinned.value)
+        pos += 1
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        tok = m.decode_into(tok, pos, pinned.value)
+        pos += 1
+    backend.synchronize()
+    e2e_s = time.perf_counter() - t0
+    barrier()
+
+    if dist is not None:
+        import torch
+        t = torch.tensor([ms, e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_s = float(t[0]), float(t[1])
+
+    if rank == 0:
+        value = world * K / (ms * 1e-3)
+        e2e = world * K / e2e_s
+        wbytes = cfg.weight_bytes_per_token(synth.FMT_Q4_K, synth.FMT_Q6_K)
+        kv_mean = float(np.mean([cfg.kv_bytes_at(p) for p in range(pos_first, pos_last + 1)]))
+        small = (2 * cfg.n_layers + 1) * cfg.dim * 4 + cfg.dim * 4
+        token_bytes = wbytes + kv_mean + small
+        algo, per, nl = time_dominant_kernel(backend, ctx, cfg, mats)
+        line = {
+            "metric": "decode tok/s bs1 (Llama-2-7B Q4_K)", "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "prompt_len": PROMPT_LEN, "decode_positions": [pos_first, pos_last],
+                       "parallelism": "single GPU" if world == 1 else f"replicas x{world} (path does not shard at this model size)",
+                       "l2": "every token streams 3.75 GB of weights, far larger than the 126 MB L2 (no flush needed)"},
+            "clocks": clocks,
+            "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 16, "d2h_bytes_per_step": cfg.vocab_size * 4 + 4},
+            "gpu_launches": m.launches_per_token() * K,
+            "launches_per_token": m.launches_per_token(),
+            "token_roofline": {"bytes_per_token": token_bytes, "roofline_tok_s": peak * 1e9 / token_bytes,
+                               "frac": (value / world) / (peak * 1e9 / token_bytes), "peak_source": peak_src},
+            "roofline": {"bound": "hbm", "kernel": "gemv_kernel<Q4K> 11008x4096 (all 32 gate matrices in turn, 813 MB > L2)",
+                         "achieved": algo / per / 1e9, "peak": peak, "unit": "GB/s", "frac": algo / per / 1e9 / peak,
+                         "traffic": None, "launches_timed": nl, "us_per_launch": per * 1e6, "peak_source": peak_src},
+        }
+        if args.gemv:
+            line["gemv_microbench"] = gemv_microbench(backend, ctx, peak)
+        if world == 1 and not args.no_cpu:
+            nthreads = os.cpu_count() or 1
+            tl, to = cpu_layer_times(cfg, raw, PROMPT_LEN, nthreads, reps=2)
+            tl1, to1 = cpu_layer_times(cfg, raw, PROMPT_LEN, 1, reps=1)
+            line["cpu_baseline"] = {"value": 1.0 / (cfg.n_layers * tl + to), "unit": "tok/s", "cores": nthreads, "kind": "port",
+                                    "single_thread_value": 1.0 / (cfg.n_layers * tl1 + to1),
+                                    "sample": "one full layer (f32-dequantised weights, 7 dense gemvs, attention over 513 positions) "
+                                              "+ the logits gemv of the same model on the host; token time = 32 x layer + logits"}
+        print(json.dumps(line), flush=True)
+    backend.lib.slai_free_host(backend.h, pinned)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

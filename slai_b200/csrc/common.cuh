@@ -1,0 +1,169 @@
+// Shared declarations of the slai_b200 CUDA library (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string>
+#include <vector>
+#include <unordered_map>
+
+#include "../../include/slai_b200.h"
+
+#define SLAI_API extern "C" __attribute__((visibility("default")))
+
+struct RopeTable {
+    int head_size;
+    float base;
+    float* d_theta;  // head_size/2 inverse frequencies, computed on the host with libm powf
+};
+
+struct slai_ctx {
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    std::string last_error;
+    bool use_pdl = true;            // programmatic dependent launch between decode kernels
+    void* d_scratch = nullptr;      // attention split partials etc.
+    size_t scratch_bytes = 0;
+    std::vector<RopeTable> rope_tables;
+    unsigned int* d_counters = nullptr;  // tickets for "last block finishes" reductions (zeroed)
+};
+
+int slai_set_error(slai_ctx* ctx, int code, const char* fmt, ...);
+
+#define SLAI_CHECK_CUDA(ctx, expr)                                                                 \
+    do {                                                                                           \
+        cudaError_t _e = (expr);                                                                   \
+        if (_e != cudaSuccess)                                                                     \
+            return slai_set_error((ctx), SLAI_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,            \
+                                  cudaGetErrorString(_e), __FILE__, __LINE__);                     \
+    } while (0)
+
+#define SLAI_REQUIRE(ctx, cond, code, ...)                                                         \
+    do {                                                                                           \
+        if (!(cond)) return slai_set_error((ctx), (code), __VA_ARGS__);                            \
+    } while (0)
+
+// ------------------------------------------------------------------------------------------------
+// Quantized matrix as stored on the device.
+//   Q4_K / Q5_K : the GGUF bytes, unchanged (144 / 176-byte super-blocks, rows 16-byte aligned).
+//   Q8_0        : per row  [K int8 quants][K/32 f16 scales][pad to 16 bytes]
+//   Q6_K        : per row  [nb*128 ql][nb*64 qh][nb*16 int8 scales][nb f16 d][pad to 16 bytes]
+//   F32         : dense row-major.
+// Rows are padded with zero rows up to a multiple of 16 so kernels may read whole 16-row tiles.
+// ------------------------------------------------------------------------------------------------
+struct slai_qmatrix {
+    slai_ctx* ctx = nullptr;
+    int fmt = 0;
+    int64_t nrows = 0, ncols = 0;
+    int64_t nrows_padded = 0;
+    int64_t row_stride = 0;  // bytes between rows in `data`
+    uint8_t* data = nullptr;
+    size_t bytes = 0;
+    bool owns = true;
+};
+
+static inline int fmt_block_elems(int fmt) {
+    switch (fmt) {
+        case SLAI_FMT_F32: return 1;
+        case SLAI_FMT_Q8_0: return 32;
+        case SLAI_FMT_Q4_K:
+        case SLAI_FMT_Q5_K:
+        case SLAI_FMT_Q6_K: return 256;
+    }
+    return 0;
+}
+static inline int fmt_block_bytes(int fmt) {
+    switch (fmt) {
+        case SLAI_FMT_F32: return 4;
+        case SLAI_FMT_Q8_0: return 34;
+        case SLAI_FMT_Q4_K: return 144;
+        case SLAI_FMT_Q5_K: return 176;
+        case SLAI_FMT_Q6_K: return 210;
+    }
+    return 0;
+}
+static inline int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
+
+// ------------------------------------------------------------------------------------------------
+// GEMV launch description (gemv.cu).  One launch covers up to three matrices that share the input
+// vector (q/k/v or gate/up); the rows of all segments form one virtual row space tiled by 16.
+// ------------------------------------------------------------------------------------------------
+enum GemvPrologue { PRO_NONE = 0, PRO_RMS = 1, PRO_LN = 2 };
+enum GemvEpilogue {
+    EPI_STORE = 0,     // out[r] = acc (+bias)
+    EPI_RESID = 1,     // out[r] = resid[r] + acc (+bias)       (out may alias resid)
+    EPI_SILU = 2,      // segments 0/1 = gate/up: out[r] = up * gate / (1 + exp(-gate))
+    EPI_GELU = 3,      // out[r] = gelu(acc + bias)
+    EPI_QKV = 4        // segments q,k,v: optional bias, optional adjacent-pair RoPE on q,k; q -> out f32,
+                       // k,v -> KV cache at position *d_pos
+};
+
+struct GemvSeg {
+    const uint8_t* w = nullptr;   // device data of the matrix (first row of the segment)
+    int64_t row_stride = 0;
+    int rows = 0;                 // logical rows
+    int tile0 = 0;                // first 16-row tile of this segment in the virtual tile space (set by gemv_launch)
+    const float* bias = nullptr;  // per row of the segment, may be null
+    int out_off = 0;              // index in `out` of the segment's row 0
+    int role = 0;                 // EPI_QKV: 0 = q (to `out`), 1 = k, 2 = v (to the caches)
+};
+
+struct GemvLaunch {
+    int fmt = 0;
+    int K = 0;
+    int nseg = 1;
+    GemvSeg seg[3];
+    const float* v = nullptr;  // input vector (K floats)
+    float* out = nullptr;
+    int pro = PRO_NONE;
+    const float* norm_w = nullptr;  // RMS weight or LN gamma
+    const float* norm_b = nullptr;  // LN beta
+    float eps = 0.f;
+    int epi = EPI_STORE;
+    const float* resid = nullptr;
+    // EPI_QKV
+    int rope = 0;                  // 1: rotate adjacent pairs of q and k
+    const float* rope_theta = nullptr;  // head_size/2 inverse frequencies
+    int head_size = 0;
+    const int* d_pos = nullptr;    // device scalar: position (RoPE angle and KV slot)
+    void* kcache = nullptr;        // layer base of the K cache
+    void* vcache = nullptr;
+    int kv_dtype = SLAI_KV_F16;
+    int64_t kv_pos_stride = 0;     // elements between positions
+    int64_t kv_head_stride = 0;    // elements between heads
+    bool pdl = false;              // launch with programmatic stream serialization
+};
+
+int gemv_launch(slai_ctx* ctx, const GemvLaunch& L);
+
+// attention.cu
+struct AttnLaunch {
+    const float* q;
+    const void* kcache;
+    const void* vcache;
+    int kv_dtype;
+    int64_t pos_stride, head_stride;  // in elements
+    int n_heads, kv_mul, head_size;
+    const int* d_pos;   // device scalar position (attends to 0..=pos)
+    int max_pos;        // upper bound of *d_pos (sizes the split)
+    float* out;         // n_heads*head_size
+    bool pdl;
+    void* scratch;      // split partials; NULL = the context's scratch (grown on demand, not graph-safe)
+    size_t scratch_bytes;
+};
+size_t attention_scratch_bytes(slai_ctx* ctx, int n_heads, int kv_mul, int head_size, int max_pos);
+int attention_launch(slai_ctx* ctx, const AttnLaunch& A);
+int ensure_scratch(slai_ctx* ctx, size_t bytes);
+const float* rope_table(slai_ctx* ctx, int head_size, float base);
+
+// ops.cu helpers used by the models
+int launch_embed_f32(slai_ctx* ctx, float* x, const float* table, int dim, const int* d_token, const float* wpe,
+                     const int* d_pos, bool pdl);
+int launch_embed_q8(slai_ctx* ctx, float* x, const slai_qmatrix* wte, const int* d_token, const float* wpe,
+                    const int* d_pos, bool pdl);
+int launch_argmax(slai_ctx* ctx, const float* v, int64_t n, int32_t* d_out, bool pdl);
+int launch_advance(slai_ctx* ctx, int* d_token, int* d_pos, const int32_t* d_next, int32_t* d_history, bool pdl);

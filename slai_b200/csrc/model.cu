@@ -1,0 +1,697 @@
+// Per-token decode of the Llama-2 family (Llama2::launch, crates/slai/src/models/llama2/transformer.rs:316-381;
+// caller ChatLlama2::forward_logits, crates/slai-chat/src/chat_llama2.rs:163-240) and of GPT-2
+// (gpt2::cpu::Transformer::forward, crates/slai/src/models/gpt2/cpu.rs:225-383).
+//
+// The reference records ~16 dispatches per layer and synchronises + reads back all logits per token.
+// Here a layer is five kernels (norm+QKV+RoPE+KV-append, attention, O+residual, norm+gate/up+SiLU,
+// down+residual), chained with programmatic dependent launch and captured once into a CUDA graph that is
+// replayed per token; token id and position live in device scalars, and greedy decoding / prompt
+// processing advance them on the device so the host only launches graphs.
+#include "common.cuh"
+
+namespace {
+
+struct Scalars {  // device ints: [0] token, [1] pos, [2] step, [3] next
+    int* d = nullptr;
+};
+
+enum GraphKind { G_DECODE = 0, G_GENERATE = 1, G_FORCED = 2, G_COUNT = 3 };
+
+struct GraphSet {
+    cudaGraphExec_t exec[G_COUNT] = {nullptr, nullptr, nullptr};
+    bool warmed[G_COUNT] = {false, false, false};  // first token of a kind runs eagerly (sets kernel attributes)
+    bool use_graph = true;
+};
+
+int copy_f32(slai_ctx* ctx, float** dst, const float* src, int64_t n, bool from_device) {
+    if (*dst) {
+        cudaStreamSynchronize(ctx->stream);
+        cudaFree(*dst);
+        *dst = nullptr;
+    }
+    SLAI_CHECK_CUDA(ctx, cudaMalloc(dst, (size_t)n * 4 + 16));
+    SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(*dst, src, (size_t)n * 4, from_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice,
+                                         ctx->stream));
+    SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return SLAI_OK;
+}
+
+void destroy_graphs(GraphSet& g) {
+    for (int i = 0; i < G_COUNT; i++)
+        if (g.exec[i]) {
+            cudaGraphExecDestroy(g.exec[i]);
+            g.exec[i] = nullptr;
+        }
+    for (int i = 0; i < G_COUNT; i++) g.warmed[i] = false;
+}
+
+GemvSeg seg_of(const slai_qmatrix* m, int row0, int rows, const float* bias, int out_off, int role) {
+    GemvSeg s;
+    s.w = m->data + (size_t)row0 * m->row_stride;
+    s.row_stride = m->row_stride;
+    s.rows = rows;
+    s.bias = bias;
+    s.out_off = out_off;
+    s.role = role;
+    return s;
+}
+
+}  // namespace
+
+// =================================================================================================
+// Llama
+// =================================================================================================
+struct LlamaLayer {
+    const slai_qmatrix *wq = nullptr, *wk = nullptr, *wv = nullptr, *wo = nullptr, *wgate = nullptr, *wup = nullptr,
+                       *wdown = nullptr;
+    float *attn_norm = nullptr, *ffn_norm = nullptr, *bq = nullptr, *bk = nullptr, *bv = nullptr;
+};
+
+struct slai_llama {
+    slai_ctx* ctx = nullptr;
+    slai_llama_config cfg;
+    int kv_dim = 0, head_size = 0, kv_mul = 0;
+    std::vector<LlamaLayer> layers;
+    const slai_qmatrix* output = nullptr;
+    const slai_qmatrix* embd_q = nullptr;
+    slai_qmatrix embd_as_matrix;  // non-owning F32 view of the f32 embedding table (tied output)
+    float* token_embd = nullptr;  // [vocab][dim] f32
+    float* out_norm = nullptr;
+    float *x = nullptr, *xb = nullptr, *q = nullptr, *hb = nullptr, *hb2 = nullptr, *logits = nullptr;
+    void *kcache = nullptr, *vcache = nullptr;
+    size_t kv_layer_elems = 0;
+    Scalars sc;
+    int32_t* d_history = nullptr;  // generated / forced token ids
+    int history_cap = 0;
+    void* attn_scratch = nullptr;
+    size_t attn_scratch_bytes = 0;
+    const float* rope_theta = nullptr;
+    GraphSet graphs;
+    int launches = 0;
+};
+
+static int llama_record(slai_llama* m, int kind) {
+    slai_ctx* ctx = m->ctx;
+    const slai_llama_config& c = m->cfg;
+    const bool pdl = ctx->use_pdl;
+    int n = 0;
+    int* d_token = m->sc.d;
+    int* d_pos = m->sc.d + 1;
+    int rc;
+    SLAI_REQUIRE(ctx, m->out_norm && (m->token_embd || m->embd_q), SLAI_ERR_INVALID_ARG, "llama: embedding / output norm not set");
+    if (m->embd_q) rc = launch_embed_q8(ctx, m->x, m->embd_q, d_token, nullptr, nullptr, false);
+    else rc = launch_embed_f32(ctx, m->x, m->token_embd, c.dim, d_token, nullptr, nullptr, false);
+    if (rc) return rc;
+    n++;
+    const size_t esz = c.kv_dtype == SLAI_KV_F16 ? 2 : 4;
+    for (int l = 0; l < c.n_layers; l++) {
+        const LlamaLayer& w = m->layers[l];
+        SLAI_REQUIRE(ctx, w.wq && w.wk && w.wv && w.wo && w.wgate && w.wup && w.wdown && w.attn_norm && w.ffn_norm,
+                     SLAI_ERR_INVALID_ARG, "llama: layer %d has unset weights", l);
+        void* kc = (char*)m->kcache + (size_t)l * m->kv_layer_elems * esz;
+        void* vc = (char*)m->vcache + (size_t)l * m->kv_layer_elems * esz;
+        // 1. xb = rmsnorm(x); q = Wq xb; k,v -> cache[pos]; RoPE(q,k)          transformer.rs:327-347
+        const bool fuse_rope = c.rope_variant == 0;
+        auto qkv_launch = [&](int nseg, const GemvSeg* segs, int fmt) {
+            GemvLaunch L;
+            L.fmt = fmt; L.K = c.dim; L.nseg = nseg;
+            for (int i = 0; i < nseg; i++) L.seg[i] = segs[i];
+            L.v = m->x; L.out = m->q; L.pro = PRO_RMS; L.norm_w = w.attn_norm; L.eps = c.rms_norm_eps;
+            L.epi = EPI_QKV; L.rope = fuse_rope ? 1 : 0; L.rope_theta = m->rope_theta; L.head_size = m->head_size;
+            L.d_pos = d_pos; L.kcache = kc; L.vcache = vc; L.kv_dtype = c.kv_dtype;
+            L.kv_pos_stride = m->head_size; L.kv_head_stride = (int64_t)c.seq_len * m->head_size;
+            L.pdl = pdl;
+            n++;
+            return gemv_launch(ctx, L);
+        };
+        SLAI_REQUIRE(ctx, fuse_rope, SLAI_ERR_INVALID_ARG, "llama: the NeoX RoPE variant is served by slai_rope, not by the fused decode path");
+        GemvSeg sq = seg_of(w.wq, 0, c.dim, w.bq, 0, 0), sk = seg_of(w.wk, 0, m->kv_dim, w.bk, 0, 1),
+                sv = seg_of(w.wv, 0, m->kv_dim, w.bv, 0, 2);
+        if (w.wq->fmt == w.wk->fmt && w.wk->fmt == w.wv->fmt) {
+            GemvSeg s3[3] = {sq, sk, sv};
+            if ((rc = qkv_launch(3, s3, w.wq->fmt))) return rc;
+        } else {
+            if ((rc = qkv_launch(1, &sq, w.wq->fmt))) return rc;
+            if ((rc = qkv_launch(1, &sk, w.wk->fmt))) return rc;
+            if ((rc = qkv_launch(1, &sv, w.wv->fmt))) return rc;
+        }
+        // 2. xb = attention(q, cache)                                           transformer.rs:350,383-400
+        {
+            AttnLaunch A;
+            A.q = m->q; A.kcache = kc; A.vcache = vc; A.kv_dtype = c.kv_dtype;
+            A.pos_stride = m->head_size; A.head_stride = (int64_t)c.seq_len * m->head_size;
+            A.n_heads = c.n_q_heads; A.kv_mul = m->kv_mul; A.head_size = m->head_size;
+            A.d_pos = d_pos; A.max_pos = c.seq_len - 1; A.out = m->xb; A.pdl = pdl;
+            A.scratch = m->attn_scratch; A.scratch_bytes = m->attn_scratch_bytes;
+            if ((rc = attention_launch(ctx, A))) return rc;
+            n++;
+        }
+        // 3. x += Wo xb                                                         transformer.rs:352-355
+        {
+            GemvLaunch L;
+            L.fmt = w.wo->fmt; L.K = c.dim; L.nseg = 1; L.seg[0] = seg_of(w.wo, 0, c.dim, nullptr, 0, 0);
+            L.v = m->xb; L.out = m->x; L.resid = m->x; L.epi = EPI_RESID; L.pdl = pdl;
+            if ((rc = gemv_launch(ctx, L))) return rc;
+            n++;
+        }
+        // 4. xb = rmsnorm(x); hb = silu(Wgate xb) * (Wup xb)                    transformer.rs:356-361
+        if (w.wgate->fmt == w.wup->fmt) {
+            GemvLaunch L;
+            L.fmt = w.wgate->fmt; L.K = c.dim; L.nseg = 2;
+            L.seg[0] = seg_of(w.wgate, 0, c.hidden_dim, nullptr, 0, 0);
+            L.seg[1] = seg_of(w.wup, 0, c.hidden_dim, nullptr, 0, 0);
+            L.v = m->x; L.out = m->hb; L.pro = PRO_RMS; L.norm_w = w.ffn_norm; L.eps = c.rms_norm_eps; L.epi = EPI_SILU;
+            L.pdl = pdl;
+            if ((rc = gemv_launch(ctx, L))) return rc;
+            n++;
+        } else {
+            for (int i = 0; i < 2; i++) {
+                const slai_qmatrix* wm = i == 0 ? w.wgate : w.wup;
+                GemvLaunch L;
+                L.fmt = wm->fmt; L.K = c.dim; L.nseg = 1; L.seg[0] = seg_of(wm, 0, c.hidden_dim, nullptr, 0, 0);
+                L.v = m->x; L.out = i == 0 ? m->hb : m->hb2; L.pro = PRO_RMS; L.norm_w = w.ffn_norm; L.eps = c.rms_norm_eps;
+                L.epi = EPI_STORE; L.pdl = pdl;
+                if ((rc = gemv_launch(ctx, L))) return rc;
+                n++;
+            }
+            if ((rc = slai_silu_gate(ctx, m->hb, m->hb2, c.hidden_dim))) return rc;
+            n++;
+        }
+        // 5. x += Wdown hb                                                      transformer.rs:362-365
+        {
+            GemvLaunch L;
+            L.fmt = w.wdown->fmt; L.K = c.hidden_dim; L.nseg = 1; L.seg[0] = seg_of(w.wdown, 0, c.dim, nullptr, 0, 0);
+            L.v = m->hb; L.out = m->x; L.resid = m->x; L.epi = EPI_RESID; L.pdl = pdl;
+            if ((rc = gemv_launch(ctx, L))) return rc;
+            n++;
+        }
+    }
+    // logits = Wout rmsnorm(x)                                                  transformer.rs:368-375
+    const slai_qmatrix* wout = m->output ? m->output : (m->embd_q ? m->embd_q : &m->embd_as_matrix);
+    if (wout->fmt == SLAI_FMT_F32) {
+        if ((rc = slai_rms_norm(ctx, m->xb, m->x, m->out_norm, c.dim, c.rms_norm_eps))) return rc;
+        n++;
+        GemvLaunch L;
+        L.fmt = SLAI_FMT_F32; L.K = c.dim; L.nseg = 1; L.seg[0] = seg_of(wout, 0, c.vocab_size, nullptr, 0, 0);
+        L.v = m->xb; L.out = m->logits; L.pdl = false;
+        if ((rc = gemv_launch(ctx, L))) return rc;
+        n++;
+    } else {
+        GemvLaunch L;
+        L.fmt = wout->fmt; L.K = c.dim; L.nseg = 1; L.seg[0] = seg_of(wout, 0, c.vocab_size, nullptr, 0, 0);
+        L.v = m->x; L.out = m->logits; L.pro = PRO_RMS; L.norm_w = m->out_norm; L.eps = c.rms_norm_eps; L.epi = EPI_STORE;
+        L.pdl = pdl;
+        if ((rc = gemv_launch(ctx, L))) return rc;
+        n++;
+    }
+    if ((rc = launch_argmax(ctx, m->logits, c.vocab_size, m->sc.d + 3, pdl))) return rc;
+    n++;
+    if (kind == G_GENERATE) {
+        if ((rc = launch_advance(ctx, d_token, d_pos, m->sc.d + 3, m->d_history, pdl))) return rc;
+        n++;
+    } else if (kind == G_FORCED) {
+        // next token comes from the prompt: history[] holds tokens[1..]; advance copies history[step]
+        if ((rc = launch_advance(ctx, d_token, d_pos, nullptr, m->d_history, pdl))) return rc;
+        n++;
+    }
+    m->launches = n;
+    return SLAI_OK;
+}
+
+template <class M, class RecordFn>
+static int run_graph(M* m, int kind, RecordFn record) {
+    slai_ctx* ctx = m->ctx;
+    if (!m->graphs.use_graph) return record(m, kind);
+    if (!m->graphs.warmed[kind]) {
+        m->graphs.warmed[kind] = true;
+        return record(m, kind);
+    }
+    if (!m->graphs.exec[kind]) {
+        cudaGraph_t graph = nullptr;
+        SLAI_CHECK_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+        int rc = record(m, kind);
+        cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+        if (rc) {
+            if (graph) cudaGraphDestroy(graph);
+            return rc;
+        }
+        SLAI_CHECK_CUDA(ctx, e);
+        e = cudaGraphInstantiate(&m->graphs.exec[kind], graph, 0);
+        cudaGraphDestroy(graph);
+        SLAI_CHECK_CUDA(ctx, e);
+    }
+    SLAI_CHECK_CUDA(ctx, cudaGraphLaunch(m->graphs.exec[kind], ctx->stream));
+    return SLAI_OK;
+}
+
+SLAI_API int slai_llama_create(slai_ctx* ctx, const slai_llama_config* cfg, slai_llama** out) {
+    if (!ctx || !cfg || !out) return SLAI_ERR_INVALID_ARG;
+    *out = nullptr;
+    const slai_llama_config& c = *cfg;
+    SLAI_REQUIRE(ctx, c.dim > 0 && c.hidden_dim > 0 && c.n_layers > 0 && c.n_q_heads > 0 && c.n_kv_heads > 0 && c.vocab_size > 0 &&
+                          c.seq_len > 0, SLAI_ERR_INVALID_ARG, "llama: non-positive dimension");
+    SLAI_REQUIRE(ctx, c.dim % c.n_q_heads == 0 && c.n_q_heads % c.n_kv_heads == 0, SLAI_ERR_SHAPE, "llama: head counts do not divide");
+    SLAI_REQUIRE(ctx, (c.dim / c.n_q_heads) % 2 == 0, SLAI_ERR_SHAPE, "llama: odd head size");
+    SLAI_REQUIRE(ctx, c.kv_dtype == SLAI_KV_F16 || c.kv_dtype == SLAI_KV_F32, SLAI_ERR_INVALID_ARG, "llama: unknown kv_dtype");
+    slai_llama* m = new slai_llama();
+    m->ctx = ctx;
+    m->cfg = c;
+    // derived sizes: Llama2Config::derived_configs (models/llama2/cpu.rs:111-143)
+    m->head_size = c.dim / c.n_q_heads;
+    m->kv_dim = c.dim * c.n_kv_heads / c.n_q_heads;
+    m->kv_mul = c.n_q_heads / c.n_kv_heads;
+    m->layers.resize(c.n_layers);
+    const size_t esz = c.kv_dtype == SLAI_KV_F16 ? 2 : 4;
+    m->kv_layer_elems = (size_t)c.seq_len * m->kv_dim;
+    const char* ng = getenv("SLAI_NO_GRAPH");
+    m->graphs.use_graph = !(ng && ng[0] == '1');
+    m->history_cap = c.seq_len + 8;
+    m->attn_scratch_bytes = attention_scratch_bytes(ctx, c.n_q_heads, m->kv_mul, m->head_size, c.seq_len - 1);
+    bool ok = cudaMalloc(&m->x, (size_t)c.dim * 4) == cudaSuccess && cudaMalloc(&m->xb, (size_t)c.dim * 4) == cudaSuccess &&
+              cudaMalloc(&m->q, (size_t)c.dim * 4) == cudaSuccess && cudaMalloc(&m->hb, (size_t)c.hidden_dim * 4) == cudaSuccess &&
+              cudaMalloc(&m->hb2, (size_t)c.hidden_dim * 4) == cudaSuccess &&
+              cudaMalloc(&m->logits, (size_t)c.vocab_size * 4) == cudaSuccess &&
+              cudaMalloc(&m->kcache, m->kv_layer_elems * c.n_layers * esz) == cudaSuccess &&
+              cudaMalloc(&m->vcache, m->kv_layer_elems * c.n_layers * esz) == cudaSuccess &&
+              cudaMalloc(&m->sc.d, 64) == cudaSuccess && cudaMalloc(&m->d_history, (size_t)m->history_cap * 4) == cudaSuccess &&
+              cudaMalloc(&m->attn_scratch, m->attn_scratch_bytes) == cudaSuccess;
+    if (ok) {
+        ok = cudaMemsetAsync(m->kcache, 0, m->kv_layer_elems * c.n_layers * esz, ctx->stream) == cudaSuccess &&
+             cudaMemsetAsync(m->vcache, 0, m->kv_layer_elems * c.n_layers * esz, ctx->stream) == cudaSuccess &&
+             cudaMemsetAsync(m->sc.d, 0, 64, ctx->stream) == cudaSuccess &&
+             cudaMemsetAsync(m->d_history, 0, (size_t)m->history_cap * 4, ctx->stream) == cudaSuccess;
+    }
+    m->rope_theta = rope_table(ctx, m->head_size, c.rope_base_freq);
+    if (!ok || !m->rope_theta) {
+        cudaGetLastError();
+        slai_llama_destroy(m);
+        return slai_set_error(ctx, SLAI_ERR_OOM, "llama: cannot allocate the model state");
+    }
+    *out = m;
+    return SLAI_OK;
+}
+
+SLAI_API int slai_llama_destroy(slai_llama* m) {
+    if (!m) return SLAI_OK;
+    cudaStreamSynchronize(m->ctx->stream);
+    destroy_graphs(m->graphs);
+    for (auto& l : m->layers) {
+        cudaFree(l.attn_norm); cudaFree(l.ffn_norm); cudaFree(l.bq); cudaFree(l.bk); cudaFree(l.bv);
+    }
+    cudaFree(m->token_embd); cudaFree(m->out_norm);
+    cudaFree(m->x); cudaFree(m->xb); cudaFree(m->q); cudaFree(m->hb); cudaFree(m->hb2); cudaFree(m->logits);
+    cudaFree(m->kcache); cudaFree(m->vcache); cudaFree(m->sc.d); cudaFree(m->d_history); cudaFree(m->attn_scratch);
+    delete m;
+    return SLAI_OK;
+}
+
+SLAI_API int slai_llama_set_matrix(slai_llama* m, int id, int layer, const slai_qmatrix* w) {
+    if (!m || !w) return SLAI_ERR_INVALID_ARG;
+    slai_ctx* ctx = m->ctx;
+    const slai_llama_config& c = m->cfg;
+    destroy_graphs(m->graphs);
+    auto shape_is = [&](int64_t r, int64_t k) { return w->nrows == r && w->ncols == k; };
+    if (id == SLAI_W_OUTPUT) {
+        SLAI_REQUIRE(ctx, shape_is(c.vocab_size, c.dim), SLAI_ERR_SHAPE, "llama: output matrix must be vocab x dim");
+        m->output = w;
+        return SLAI_OK;
+    }
+    if (id == SLAI_W_TOKEN_EMBD) {
+        SLAI_REQUIRE(ctx, shape_is(c.vocab_size, c.dim), SLAI_ERR_SHAPE, "llama: token_embd must be vocab x dim");
+        m->embd_q = w;
+        return SLAI_OK;
+    }
+    SLAI_REQUIRE(ctx, layer >= 0 && layer < c.n_layers, SLAI_ERR_INVALID_ARG, "llama: layer %d out of range", layer);
+    LlamaLayer& l = m->layers[layer];
+    switch (id) {
+        case SLAI_W_Q: SLAI_REQUIRE(ctx, shape_is(c.dim, c.dim), SLAI_ERR_SHAPE, "llama: attn_q must be dim x dim"); l.wq = w; break;
+        case SLAI_W_K: SLAI_REQUIRE(ctx, shape_is(m->kv_dim, c.dim), SLAI_ERR_SHAPE, "llama: attn_k must be kv_dim x dim"); l.wk = w; break;
+        case SLAI_W_V: SLAI_REQUIRE(ctx, shape_is(m->kv_dim, c.dim), SLAI_ERR_SHAPE, "llama: attn_v must be kv_dim x dim"); l.wv = w; break;
+        case SLAI_W_O: SLAI_REQUIRE(ctx, shape_is(c.dim, c.dim), SLAI_ERR_SHAPE, "llama: attn_output must be dim x dim"); l.wo = w; break;
+        case SLAI_W_GATE: SLAI_REQUIRE(ctx, shape_is(c.hidden_dim, c.dim), SLAI_ERR_SHAPE, "llama: ffn_gate must be hidden x dim"); l.wgate = w; break;
+        case SLAI_W_UP: SLAI_REQUIRE(ctx, shape_is(c.hidden_dim, c.dim), SLAI_ERR_SHAPE, "llama: ffn_up must be hidden x dim"); l.wup = w; break;
+        case SLAI_W_DOWN: SLAI_REQUIRE(ctx, shape_is(c.dim, c.hidden_dim), SLAI_ERR_SHAPE, "llama: ffn_down must be dim x hidden"); l.wdown = w; break;
+        default: return slai_set_error(ctx, SLAI_ERR_INVALID_ARG, "llama: weight id %d is not a matrix", id);
+    }
+    return SLAI_OK;
+}
+
+static int llama_set_f32_impl(slai_llama* m, int id, int layer, const float* data, int64_t n, bool dev) {
+    if (!m || !data) return SLAI_ERR_INVALID_ARG;
+    slai_ctx* ctx = m->ctx;
+    const slai_llama_config& c = m->cfg;
+    destroy_graphs(m->graphs);
+    if (id == SLAI_W_TOKEN_EMBD) {
+        SLAI_REQUIRE(ctx, n == (int64_t)c.vocab_size * c.dim, SLAI_ERR_SHAPE, "llama: token_embd needs vocab*dim floats");
+        int rc = copy_f32(ctx, &m->token_embd, data, n, dev);
+        if (rc) return rc;
+        m->embd_as_matrix.ctx = ctx; m->embd_as_matrix.fmt = SLAI_FMT_F32; m->embd_as_matrix.nrows = c.vocab_size;
+        m->embd_as_matrix.ncols = c.dim; m->embd_as_matrix.row_stride = (int64_t)c.dim * 4;
+        m->embd_as_matrix.data = (uint8_t*)m->token_embd; m->embd_as_matrix.owns = false;
+        return SLAI_OK;
+    }
+    if (id == SLAI_W_OUT_NORM) {
+        SLAI_REQUIRE(ctx, n == c.dim, SLAI_ERR_SHAPE, "llama: output_norm needs dim floats");
+        return copy_f32(ctx, &m->out_norm, data, n, dev);
+    }
+    SLAI_REQUIRE(ctx, layer >= 0 && layer < c.n_layers, SLAI_ERR_INVALID_ARG, "llama: layer %d out of range", layer);
+    LlamaLayer& l = m->layers[layer];
+    float** dst = nullptr;
+    int64_t want = c.dim;
+    switch (id) {
+        case SLAI_W_ATTN_NORM: dst = &l.attn_norm; break;
+        case SLAI_W_FFN_NORM: dst = &l.ffn_norm; break;
+        case SLAI_W_BQ: dst = &l.bq; break;
+        case SLAI_W_BK: dst = &l.bk; want = m->kv_dim; break;
+        case SLAI_W_BV: dst = &l.bv; want = m->kv_dim; break;
+        default: return slai_set_error(ctx, SLAI_ERR_INVALID_ARG, "llama: weight id %d is not an f32 vector", id);
+    }
+    SLAI_REQUIRE(ctx, n == want, SLAI_ERR_SHAPE, "llama: weight %d needs %lld floats, got %lld", id, (long long)want, (long long)n);
+    return copy_f32(ctx, dst, data, n, dev);
+}
+SLAI_API int slai_llama_set_f32(slai_llama* m, int id, int layer, const float* h_data, int64_t n) {
+    return llama_set_f32_impl(m, id, layer, h_data, n, false);
+}
+SLAI_API int slai_llama_set_f32_device(slai_llama* m, int id, int layer, const float* d_data, int64_t n) {
+    return llama_set_f32_impl(m, id, layer, d_data, n, true);
+}
+
+template <class M>
+static int set_scalars(M* m, int token, int pos, int step) {
+    const int h[4] = {token, pos, step, 0};
+    SLAI_CHECK_CUDA(m->ctx, cudaMemcpyAsync(m->sc.d, h, sizeof(h), cudaMemcpyHostToDevice, m->ctx->stream));
+    return SLAI_OK;
+}
+
+template <class M, class RecordFn>
+static int decode_impl(M* m, RecordFn record, int vocab, int seq_len, int32_t token, int32_t pos, float* h_logits,
+                       int32_t* next_token) {
+    slai_ctx* ctx = m->ctx;
+    SLAI_REQUIRE(ctx, token >= 0 && token < vocab, SLAI_ERR_INVALID_ARG, "decode: token %d out of range", token);
+    SLAI_REQUIRE(ctx, pos >= 0 && pos < seq_len, SLAI_ERR_INVALID_ARG, "decode: pos %d out of range", pos);
+    int rc = set_scalars(m, token, pos, 0);
+    if (rc) return rc;
+    if ((rc = run_graph(m, G_DECODE, record))) return rc;
+    if (h_logits) SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(h_logits, m->logits, (size_t)vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (next_token) SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(next_token, m->sc.d + 3, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (h_logits || next_token) SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return SLAI_OK;
+}
+
+template <class M, class RecordFn>
+static int generate_impl(M* m, RecordFn record, int vocab, int seq_len, int32_t token, int32_t pos, int32_t n, int32_t* h_tokens) {
+    slai_ctx* ctx = m->ctx;
+    SLAI_REQUIRE(ctx, token >= 0 && token < vocab, SLAI_ERR_INVALID_ARG, "generate: token %d out of range", token);
+    SLAI_REQUIRE(ctx, n > 0 && pos >= 0 && pos + n <= seq_len && n <= m->history_cap, SLAI_ERR_INVALID_ARG,
+                 "generate: positions %d..%d exceed the context", pos, pos + n);
+    int rc = set_scalars(m, token, pos, 0);
+    if (rc) return rc;
+    for (int i = 0; i < n; i++)
+        if ((rc = run_graph(m, G_GENERATE, record))) return rc;
+    if (h_tokens) SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(h_tokens, m->d_history, (size_t)n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return SLAI_OK;
+}
+
+template <class M, class RecordFn>
+static int prefill_impl(M* m, RecordFn record, int vocab, int seq_len, const int32_t* h_tokens, int32_t n, int32_t pos0,
+                        float* h_last_logits) {
+    slai_ctx* ctx = m->ctx;
+    SLAI_REQUIRE(ctx, h_tokens && n > 0 && pos0 >= 0 && pos0 + n <= seq_len && n < m->history_cap, SLAI_ERR_INVALID_ARG,
+                 "prefill: positions %d..%d exceed the context", pos0, pos0 + n);
+    for (int i = 0; i < n; i++)
+        SLAI_REQUIRE(ctx, h_tokens[i] >= 0 && h_tokens[i] < vocab, SLAI_ERR_INVALID_ARG, "prefill: token %d out of range", h_tokens[i]);
+    // history[step] = the token to feed after step `step` (tokens[1..]; the entry after the last is unused)
+    std::vector<int32_t> next(n, 0);
+    for (int i = 0; i + 1 < n; i++) next[i] = h_tokens[i + 1];
+    SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(m->d_history, next.data(), (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream));
+    int rc = set_scalars(m, h_tokens[0], pos0, 0);
+    if (rc) return rc;
+    SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // `next` leaves scope
+    for (int i = 0; i < n; i++)
+        if ((rc = run_graph(m, G_FORCED, record))) return rc;
+    if (h_last_logits) SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(h_last_logits, m->logits, (size_t)vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return SLAI_OK;
+}
+
+SLAI_API int slai_llama_decode(slai_llama* m, int32_t token, int32_t pos, float* h_logits, int32_t* next_token) {
+    if (!m) return SLAI_ERR_INVALID_ARG;
+    return decode_impl(m, llama_record, m->cfg.vocab_size, m->cfg.seq_len, token, pos, h_logits, next_token);
+}
+SLAI_API int slai_llama_generate(slai_llama* m, int32_t token, int32_t pos, int32_t n, int32_t* h_tokens) {
+    if (!m) return SLAI_ERR_INVALID_ARG;
+    return generate_impl(m, llama_record, m->cfg.vocab_size, m->cfg.seq_len, token, pos, n, h_tokens);
+}
+SLAI_API int slai_llama_prefill(slai_llama* m, const int32_t* h_tokens, int32_t n, int32_t pos0, float* h_last_logits) {
+    if (!m) return SLAI_ERR_INVALID_ARG;
+    return prefill_impl(m, llama_record, m->cfg.vocab_size, m->cfg.seq_len, h_tokens, n, pos0, h_last_logits);
+}
+SLAI_API int slai_llama_read_state(slai_llama* m, int which, float* h_out, int64_t n) {
+    if (!m || !h_out) return SLAI_ERR_INVALID_ARG;
+    const float* src = nullptr;
+    int64_t cap = 0;
+    switch (which) {
+        case 0: src = m->x; cap = m->cfg.dim; break;
+        case 1: src = m->xb; cap = m->cfg.dim; break;
+        case 2: src = m->q; cap = m->cfg.dim; break;
+        case 3: src = m->hb; cap = m->cfg.hidden_dim; break;
+        case 4: src = m->logits; cap = m->cfg.vocab_size; break;
+        default: return slai_set_error(m->ctx, SLAI_ERR_INVALID_ARG, "read_state: unknown vector %d", which);
+    }
+    SLAI_REQUIRE(m->ctx, n > 0 && n <= cap, SLAI_ERR_SHAPE, "read_state: n=%lld exceeds %lld", (long long)n, (long long)cap);
+    return slai_read_buffer(m->ctx, h_out, src, (size_t)n * 4);
+}
+SLAI_API int slai_llama_launches_per_token(const slai_llama* m) { return m ? m->launches : 0; }
+
+// =================================================================================================
+// GPT-2
+// =================================================================================================
+struct Gpt2Layer {
+    const slai_qmatrix *w_qkv = nullptr, *w_proj = nullptr, *w_fc = nullptr, *w_fcproj = nullptr;
+    float *ln1_g = nullptr, *ln1_b = nullptr, *b_qkv = nullptr, *b_proj = nullptr, *ln2_g = nullptr, *ln2_b = nullptr, *b_fc = nullptr,
+          *b_fcproj = nullptr;
+};
+struct slai_gpt2 {
+    slai_ctx* ctx = nullptr;
+    slai_gpt2_config cfg;
+    int head_size = 0;
+    std::vector<Gpt2Layer> layers;
+    const slai_qmatrix* wte = nullptr;  // token embedding and tied lm_head (models/gpt2/cpu.rs:197)
+    float *wpe = nullptr, *lnf_g = nullptr, *lnf_b = nullptr;
+    float *x = nullptr, *xb = nullptr, *q = nullptr, *ff = nullptr, *logits = nullptr;
+    void *kcache = nullptr, *vcache = nullptr;
+    size_t kv_layer_elems = 0;
+    Scalars sc;
+    int32_t* d_history = nullptr;
+    int history_cap = 0;
+    void* attn_scratch = nullptr;
+    size_t attn_scratch_bytes = 0;
+    GraphSet graphs;
+    int launches = 0;
+};
+
+static int gpt2_record(slai_gpt2* m, int kind) {
+    slai_ctx* ctx = m->ctx;
+    const slai_gpt2_config& c = m->cfg;
+    const bool pdl = ctx->use_pdl;
+    const int E = c.n_embd;
+    int n = 0, rc;
+    int* d_token = m->sc.d;
+    int* d_pos = m->sc.d + 1;
+    SLAI_REQUIRE(ctx, m->wte && m->wpe && m->lnf_g && m->lnf_b, SLAI_ERR_INVALID_ARG, "gpt2: embeddings / final norm not set");
+    // x = wte[:,tok] + wpe[:,pos]                                              gpt2/cpu.rs:227-228
+    if ((rc = launch_embed_q8(ctx, m->x, m->wte, d_token, m->wpe, d_pos, false))) return rc;
+    n++;
+    const size_t esz = c.kv_dtype == SLAI_KV_F16 ? 2 : 4;
+    for (int l = 0; l < c.n_layer; l++) {
+        const Gpt2Layer& w = m->layers[l];
+        SLAI_REQUIRE(ctx, w.w_qkv && w.w_proj && w.w_fc && w.w_fcproj && w.ln1_g && w.ln1_b && w.ln2_g && w.ln2_b && w.b_qkv &&
+                              w.b_proj && w.b_fc && w.b_fcproj, SLAI_ERR_INVALID_ARG, "gpt2: layer %d has unset weights", l);
+        void* kc = (char*)m->kcache + (size_t)l * m->kv_layer_elems * esz;
+        void* vc = (char*)m->vcache + (size_t)l * m->kv_layer_elems * esz;
+        {   // LayerNorm*g+b; qkv = W x + b; split into q / cache                gpt2/cpu.rs:235-270
+            GemvLaunch L;
+            L.fmt = w.w_qkv->fmt; L.K = E; L.nseg = 3;
+            L.seg[0] = seg_of(w.w_qkv, 0, E, w.b_qkv, 0, 0);
+            L.seg[1] = seg_of(w.w_qkv, E, E, w.b_qkv + E, 0, 1);
+            L.seg[2] = seg_of(w.w_qkv, 2 * E, E, w.b_qkv + 2 * E, 0, 2);
+            L.v = m->x; L.out = m->q; L.pro = PRO_LN; L.norm_w = w.ln1_g; L.norm_b = w.ln1_b; L.eps = c.layernorm_eps;
+            L.epi = EPI_QKV; L.rope = 0; L.head_size = m->head_size; L.d_pos = d_pos; L.kcache = kc; L.vcache = vc;
+            L.kv_dtype = c.kv_dtype; L.kv_pos_stride = m->head_size; L.kv_head_stride = (int64_t)c.n_seq * m->head_size;
+            L.pdl = pdl;
+            if ((rc = gemv_launch(ctx, L))) return rc;
+            n++;
+        }
+        {   // attention with kv_mul = 1                                        gpt2/cpu.rs:272-290
+            AttnLaunch A;
+            A.q = m->q; A.kcache = kc; A.vcache = vc; A.kv_dtype = c.kv_dtype;
+            A.pos_stride = m->head_size; A.head_stride = (int64_t)c.n_seq * m->head_size;
+            A.n_heads = c.n_head; A.kv_mul = 1; A.head_size = m->head_size; A.d_pos = d_pos; A.max_pos = c.n_seq - 1;
+            A.out = m->xb; A.pdl = pdl; A.scratch = m->attn_scratch; A.scratch_bytes = m->attn_scratch_bytes;
+            if ((rc = attention_launch(ctx, A))) return rc;
+            n++;
+        }
+        {   // x += W_proj xb + b                                               gpt2/cpu.rs:302-312
+            GemvLaunch L;
+            L.fmt = w.w_proj->fmt; L.K = E; L.nseg = 1; L.seg[0] = seg_of(w.w_proj, 0, E, w.b_proj, 0, 0);
+            L.v = m->xb; L.out = m->x; L.resid = m->x; L.epi = EPI_RESID; L.pdl = pdl;
+            if ((rc = gemv_launch(ctx, L))) return rc;
+            n++;
+        }
+        {   // ff = gelu(W_fc (LayerNorm(x)*g+b) + b)                            gpt2/cpu.rs:318-343
+            GemvLaunch L;
+            L.fmt = w.w_fc->fmt; L.K = E; L.nseg = 1; L.seg[0] = seg_of(w.w_fc, 0, c.ff_len, w.b_fc, 0, 0);
+            L.v = m->x; L.out = m->ff; L.pro = PRO_LN; L.norm_w = w.ln2_g; L.norm_b = w.ln2_b; L.eps = c.layernorm_eps;
+            L.epi = EPI_GELU; L.pdl = pdl;
+            if ((rc = gemv_launch(ctx, L))) return rc;
+            n++;
+        }
+        {   // x += W_proj2 ff + b                                              gpt2/cpu.rs:353-360
+            GemvLaunch L;
+            L.fmt = w.w_fcproj->fmt; L.K = c.ff_len; L.nseg = 1; L.seg[0] = seg_of(w.w_fcproj, 0, E, w.b_fcproj, 0, 0);
+            L.v = m->ff; L.out = m->x; L.resid = m->x; L.epi = EPI_RESID; L.pdl = pdl;
+            if ((rc = gemv_launch(ctx, L))) return rc;
+            n++;
+        }
+    }
+    {   // logits = wte (LayerNorm(x)*g+b)                                      gpt2/cpu.rs:366-379
+        GemvLaunch L;
+        L.fmt = m->wte->fmt; L.K = E; L.nseg = 1; L.seg[0] = seg_of(m->wte, 0, c.n_vocab, nullptr, 0, 0);
+        L.v = m->x; L.out = m->logits; L.pro = PRO_LN; L.norm_w = m->lnf_g; L.norm_b = m->lnf_b; L.eps = c.layernorm_eps;
+        L.epi = EPI_STORE; L.pdl = pdl;
+        if ((rc = gemv_launch(ctx, L))) return rc;
+        n++;
+    }
+    if ((rc = launch_argmax(ctx, m->logits, c.n_vocab, m->sc.d + 3, pdl))) return rc;
+    n++;
+    if (kind == G_GENERATE) {
+        if ((rc = launch_advance(ctx, d_token, d_pos, m->sc.d + 3, m->d_history, pdl))) return rc;
+        n++;
+    } else if (kind == G_FORCED) {
+        if ((rc = launch_advance(ctx, d_token, d_pos, nullptr, m->d_history, pdl))) return rc;
+        n++;
+    }
+    m->launches = n;
+    return SLAI_OK;
+}
+
+SLAI_API int slai_gpt2_create(slai_ctx* ctx, const slai_gpt2_config* cfg, slai_gpt2** out) {
+    if (!ctx || !cfg || !out) return SLAI_ERR_INVALID_ARG;
+    *out = nullptr;
+    const slai_gpt2_config& c = *cfg;
+    SLAI_REQUIRE(ctx, c.n_vocab > 0 && c.n_seq > 0 && c.n_embd > 0 && c.n_head > 0 && c.n_layer > 0 && c.ff_len > 0, SLAI_ERR_INVALID_ARG,
+                 "gpt2: non-positive dimension");
+    SLAI_REQUIRE(ctx, c.n_embd % c.n_head == 0 && (c.n_embd / c.n_head) % 2 == 0, SLAI_ERR_SHAPE, "gpt2: bad head size");
+    SLAI_REQUIRE(ctx, c.kv_dtype == SLAI_KV_F16 || c.kv_dtype == SLAI_KV_F32, SLAI_ERR_INVALID_ARG, "gpt2: unknown kv_dtype");
+    slai_gpt2* m = new slai_gpt2();
+    m->ctx = ctx;
+    m->cfg = c;
+    m->head_size = c.n_embd / c.n_head;
+    m->layers.resize(c.n_layer);
+    const size_t esz = c.kv_dtype == SLAI_KV_F16 ? 2 : 4;
+    m->kv_layer_elems = (size_t)c.n_seq * c.n_embd;
+    const char* ng = getenv("SLAI_NO_GRAPH");
+    m->graphs.use_graph = !(ng && ng[0] == '1');
+    m->history_cap = c.n_seq + 8;
+    m->attn_scratch_bytes = attention_scratch_bytes(ctx, c.n_head, 1, m->head_size, c.n_seq - 1);
+    bool ok = cudaMalloc(&m->x, (size_t)c.n_embd * 4) == cudaSuccess && cudaMalloc(&m->xb, (size_t)c.n_embd * 4) == cudaSuccess &&
+              cudaMalloc(&m->q, (size_t)c.n_embd * 4) == cudaSuccess && cudaMalloc(&m->ff, (size_t)c.ff_len * 4) == cudaSuccess &&
+              cudaMalloc(&m->logits, (size_t)c.n_vocab * 4) == cudaSuccess &&
+              cudaMalloc(&m->kcache, m->kv_layer_elems * c.n_layer * esz) == cudaSuccess &&
+              cudaMalloc(&m->vcache, m->kv_layer_elems * c.n_layer * esz) == cudaSuccess && cudaMalloc(&m->sc.d, 64) == cudaSuccess &&
+              cudaMalloc(&m->d_history, (size_t)m->history_cap * 4) == cudaSuccess &&
+              cudaMalloc(&m->attn_scratch, m->attn_scratch_bytes) == cudaSuccess;
+    if (ok)
+        ok = cudaMemsetAsync(m->kcache, 0, m->kv_layer_elems * c.n_layer * esz, ctx->stream) == cudaSuccess &&
+             cudaMemsetAsync(m->vcache, 0, m->kv_layer_elems * c.n_layer * esz, ctx->stream) == cudaSuccess &&
+             cudaMemsetAsync(m->sc.d, 0, 64, ctx->stream) == cudaSuccess &&
+             cudaMemsetAsync(m->d_history, 0, (size_t)m->history_cap * 4, ctx->stream) == cudaSuccess;
+    if (!ok) {
+        cudaGetLastError();
+        slai_gpt2_destroy(m);
+        return slai_set_error(ctx, SLAI_ERR_OOM, "gpt2: cannot allocate the model state");
+    }
+    *out = m;
+    return SLAI_OK;
+}
+
+SLAI_API int slai_gpt2_destroy(slai_gpt2* m) {
+    if (!m) return SLAI_OK;
+    cudaStreamSynchronize(m->ctx->stream);
+    destroy_graphs(m->graphs);
+    for (auto& l : m->layers) {
+        cudaFree(l.ln1_g); cudaFree(l.ln1_b); cudaFree(l.b_qkv); cudaFree(l.b_proj); cudaFree(l.ln2_g); cudaFree(l.ln2_b);
+        cudaFree(l.b_fc); cudaFree(l.b_fcproj);
+    }
+    cudaFree(m->wpe); cudaFree(m->lnf_g); cudaFree(m->lnf_b);
+    cudaFree(m->x); cudaFree(m->xb); cudaFree(m->q); cudaFree(m->ff); cudaFree(m->logits);
+    cudaFree(m->kcache); cudaFree(m->vcache); cudaFree(m->sc.d); cudaFree(m->d_history); cudaFree(m->attn_scratch);
+    delete m;
+    return SLAI_OK;
+}
+
+SLAI_API int slai_gpt2_set_matrix(slai_gpt2* m, int id, int layer, const slai_qmatrix* w) {
+    if (!m || !w) return SLAI_ERR_INVALID_ARG;
+    slai_ctx* ctx = m->ctx;
+    const slai_gpt2_config& c = m->cfg;
+    destroy_graphs(m->graphs);
+    auto shape_is = [&](int64_t r, int64_t k) { return w->nrows == r && w->ncols == k; };
+    if (id == SLAI_G_WTE) {
+        SLAI_REQUIRE(ctx, shape_is(c.n_vocab, c.n_embd), SLAI_ERR_SHAPE, "gpt2: wte must be n_vocab x n_embd");
+        m->wte = w;
+        return SLAI_OK;
+    }
+    SLAI_REQUIRE(ctx, layer >= 0 && layer < c.n_layer, SLAI_ERR_INVALID_ARG, "gpt2: layer %d out of range", layer);
+    Gpt2Layer& l = m->layers[layer];
+    switch (id) {
+        case SLAI_G_W_QKV: SLAI_REQUIRE(ctx, shape_is(3 * c.n_embd, c.n_embd), SLAI_ERR_SHAPE, "gpt2: attn_qkv must be 3E x E"); l.w_qkv = w; break;
+        case SLAI_G_W_PROJ: SLAI_REQUIRE(ctx, shape_is(c.n_embd, c.n_embd), SLAI_ERR_SHAPE, "gpt2: attn_output must be E x E"); l.w_proj = w; break;
+        case SLAI_G_W_FC: SLAI_REQUIRE(ctx, shape_is(c.ff_len, c.n_embd), SLAI_ERR_SHAPE, "gpt2: ffn_up must be ff x E"); l.w_fc = w; break;
+        case SLAI_G_W_FCPROJ: SLAI_REQUIRE(ctx, shape_is(c.n_embd, c.ff_len), SLAI_ERR_SHAPE, "gpt2: ffn_down must be E x ff"); l.w_fcproj = w; break;
+        default: return slai_set_error(ctx, SLAI_ERR_INVALID_ARG, "gpt2: weight id %d is not a matrix", id);
+    }
+    return SLAI_OK;
+}
+
+SLAI_API int slai_gpt2_set_f32(slai_gpt2* m, int id, int layer, const float* h_data, int64_t n) {
+    if (!m || !h_data) return SLAI_ERR_INVALID_ARG;
+    slai_ctx* ctx = m->ctx;
+    const slai_gpt2_config& c = m->cfg;
+    destroy_graphs(m->graphs);
+    float** dst = nullptr;
+    int64_t want = c.n_embd;
+    if (id == SLAI_G_WPE) { dst = &m->wpe; want = (int64_t)c.n_seq * c.n_embd; }
+    else if (id == SLAI_G_LNF_G) dst = &m->lnf_g;
+    else if (id == SLAI_G_LNF_B) dst = &m->lnf_b;
+    else {
+        SLAI_REQUIRE(ctx, layer >= 0 && layer < c.n_layer, SLAI_ERR_INVALID_ARG, "gpt2: layer %d out of range", layer);
+        Gpt2Layer& l = m->layers[layer];
+        switch (id) {
+            case SLAI_G_LN1_G: dst = &l.ln1_g; break;
+            case SLAI_G_LN1_B: dst = &l.ln1_b; break;
+            case SLAI_G_B_QKV: dst = &l.b_qkv; want = 3 * (int64_t)c.n_embd; break;
+            case SLAI_G_B_PROJ: dst = &l.b_proj; break;
+            case SLAI_G_LN2_G: dst = &l.ln2_g; break;
+            case SLAI_G_LN2_B: dst = &l.ln2_b; break;
+            case SLAI_G_B_FC: dst = &l.b_fc; want = c.ff_len; break;
+            case SLAI_G_B_FCPROJ: dst = &l.b_fcproj; break;
+            default: return slai_set_error(ctx, SLAI_ERR_INVALID_ARG, "gpt2: weight id %d is not an f32 vector", id);
+        }
+    }
+    SLAI_REQUIRE(ctx, n == want, SLAI_ERR_SHAPE, "gpt2: weight %d needs %lld floats, got %lld", id, (long long)want, (long long)n);
+    return copy_f32(ctx, dst, h_data, n, false);
+}
+
+SLAI_API int slai_gpt2_decode(slai_gpt2* m, int32_t token, int32_t pos, float* h_logits, int32_t* next_token) {
+    if (!m) return SLAI_ERR_INVALID_ARG;
+    return decode_impl(m, gpt2_record, m->cfg.n_vocab, m->cfg.n_seq, token, pos, h_logits, next_token);
+}
+SLAI_API int slai_gpt2_generate(slai_gpt2* m, int32_t token, int32_t pos, int32_t n, int32_t* h_tokens) {
+    if (!m) return SLAI_ERR_INVALID_ARG;
+    return generate_impl(m, gpt2_record, m->cfg.n_vocab, m->cfg.n_seq, token, pos, n, h_tokens);
+}
+SLAI_API int slai_gpt2_prefill(slai_gpt2* m, const int32_t* h_tokens, int32_t n, int32_t pos0, float* h_last_logits) {
+    if (!m) return SLAI_ERR_INVALID_ARG;
+    return prefill_impl(m, gpt2_record, m->cfg.n_vocab, m->cfg.n_seq, h_tokens, n, pos0, h_last_logits);
+}

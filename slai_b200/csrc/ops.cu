@@ -1,0 +1,891 @@
+// Context, buffers, quantized-matrix upload / bit-exact dequantisation, the small decode operators and
+// the synthetic-weight generator of the slai_b200 C ABI.
+#include <stdarg.h>
+#include <math.h>
+#include <stdlib.h>
+
+#include "common.cuh"
+#include "gemv_frag.cuh"
+#include "layout.cuh"
+
+int slai_set_error(slai_ctx* ctx, int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    if (ctx) ctx->last_error = buf;
+    return code;
+}
+
+static thread_local std::string g_noctx_error;
+
+// ------------------------------------------------------------------------------------------------
+// context
+// ------------------------------------------------------------------------------------------------
+SLAI_API int slai_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+SLAI_API int slai_ctx_create(int device, slai_ctx** out) {
+    if (!out) return SLAI_ERR_INVALID_ARG;
+    *out = nullptr;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0) {
+        cudaGetLastError();
+        g_noctx_error = "no CUDA device available (this library has no CPU fallback)";
+        return SLAI_ERR_CUDA;
+    }
+    if (device < 0 || device >= n) return SLAI_ERR_INVALID_ARG;
+    slai_ctx* ctx = new slai_ctx();
+    ctx->device = device;
+    if (cudaSetDevice(device) != cudaSuccess) { delete ctx; return SLAI_ERR_CUDA; }
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) { delete ctx; return SLAI_ERR_CUDA; }
+    if (prop.major != 10) {
+        g_noctx_error = "slai_b200 is built for sm_100a only";
+        delete ctx;
+        return SLAI_ERR_CUDA;
+    }
+    ctx->sm_count = prop.multiProcessorCount;
+    if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreate(&ctx->ev0) != cudaSuccess || cudaEventCreate(&ctx->ev1) != cudaSuccess ||
+        cudaMalloc(&ctx->d_counters, 4096 * sizeof(unsigned int)) != cudaSuccess ||
+        cudaMemset(ctx->d_counters, 0, 4096 * sizeof(unsigned int)) != cudaSuccess) {
+        delete ctx;
+        return SLAI_ERR_CUDA;
+    }
+    const char* pdl = getenv("SLAI_NO_PDL");
+    ctx->use_pdl = !(pdl && pdl[0] == '1');
+    *out = ctx;
+    return SLAI_OK;
+}
+
+SLAI_API int slai_ctx_destroy(slai_ctx* ctx) {
+    if (!ctx) return SLAI_OK;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    for (auto& t : ctx->rope_tables) cudaFree(t.d_theta);
+    if (ctx->d_scratch) cudaFree(ctx->d_scratch);
+    if (ctx->d_counters) cudaFree(ctx->d_counters);
+    cudaEventDestroy(ctx->ev0);
+    cudaEventDestroy(ctx->ev1);
+    cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return SLAI_OK;
+}
+
+SLAI_API int slai_ctx_sync(slai_ctx* ctx) {
+    if (!ctx) return SLAI_ERR_INVALID_ARG;
+    SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return SLAI_OK;
+}
+SLAI_API const char* slai_last_error_string(slai_ctx* ctx) { return ctx ? ctx->last_error.c_str() : g_noctx_error.c_str(); }
+SLAI_API void* slai_ctx_stream(slai_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+SLAI_API int slai_ctx_device_info(slai_ctx* ctx, char* name, int name_len, int* sm_count) {
+    if (!ctx) return SLAI_ERR_INVALID_ARG;
+    cudaDeviceProp prop;
+    SLAI_CHECK_CUDA(ctx, cudaGetDeviceProperties(&prop, ctx->device));
+    if (name && name_len > 0) snprintf(name, name_len, "%s", prop.name);
+    if (sm_count) *sm_count = prop.multiProcessorCount;
+    return SLAI_OK;
+}
+
+SLAI_API int slai_malloc(slai_ctx* ctx, size_t bytes, void** d_out) {
+    if (!ctx || !d_out) return SLAI_ERR_INVALID_ARG;
+    cudaError_t e = cudaMalloc(d_out, bytes ? bytes : 16);
+    if (e == cudaErrorMemoryAllocation) {
+        cudaGetLastError();
+        return slai_set_error(ctx, SLAI_ERR_OOM, "out of device memory allocating %zu bytes", bytes);
+    }
+    SLAI_CHECK_CUDA(ctx, e);
+    return SLAI_OK;
+}
+SLAI_API int slai_free(slai_ctx* ctx, void* d_ptr) {
+    if (!ctx) return SLAI_ERR_INVALID_ARG;
+    SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    SLAI_CHECK_CUDA(ctx, cudaFree(d_ptr));
+    return SLAI_OK;
+}
+SLAI_API int slai_memset(slai_ctx* ctx, void* d_ptr, int value, size_t bytes) {
+    if (!ctx) return SLAI_ERR_INVALID_ARG;
+    SLAI_CHECK_CUDA(ctx, cudaMemsetAsync(d_ptr, value, bytes, ctx->stream));
+    return SLAI_OK;
+}
+SLAI_API int slai_write_buffer(slai_ctx* ctx, void* d_dst, const void* h_src, size_t bytes) {
+    if (!ctx) return SLAI_ERR_INVALID_ARG;
+    SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(d_dst, h_src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    return SLAI_OK;
+}
+SLAI_API int slai_read_buffer(slai_ctx* ctx, void* h_dst, const void* d_src, size_t bytes) {
+    if (!ctx) return SLAI_ERR_INVALID_ARG;
+    SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(h_dst, d_src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return SLAI_OK;
+}
+SLAI_API int slai_malloc_host(slai_ctx* ctx, size_t bytes, void** h_out) {
+    if (!ctx || !h_out) return SLAI_ERR_INVALID_ARG;
+    SLAI_CHECK_CUDA(ctx, cudaMallocHost(h_out, bytes ? bytes : 16));
+    return SLAI_OK;
+}
+SLAI_API int slai_free_host(slai_ctx* ctx, void* h_ptr) {
+    if (!ctx) return SLAI_ERR_INVALID_ARG;
+    SLAI_CHECK_CUDA(ctx, cudaFreeHost(h_ptr));
+    return SLAI_OK;
+}
+SLAI_API int slai_timer_start(slai_ctx* ctx) {
+    if (!ctx) return SLAI_ERR_INVALID_ARG;
+    SLAI_CHECK_CUDA(ctx, cudaEventRecord(ctx->ev0, ctx->stream));
+    return SLAI_OK;
+}
+SLAI_API int slai_timer_stop(slai_ctx* ctx, float* ms) {
+    if (!ctx || !ms) return SLAI_ERR_INVALID_ARG;
+    SLAI_CHECK_CUDA(ctx, cudaEventRecord(ctx->ev1, ctx->stream));
+    SLAI_CHECK_CUDA(ctx, cudaEventSynchronize(ctx->ev1));
+    SLAI_CHECK_CUDA(ctx, cudaEventElapsedTime(ms, ctx->ev0, ctx->ev1));
+    return SLAI_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// quantized matrices
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+__global__ void repack_kernel(int fmt, const uint8_t* __restrict__ raw, uint8_t* __restrict__ dst, long long nrows,
+                              long long nbk, long long K, int bb, long long row_stride) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= nrows * nbk) return;
+    const long long r = i / nbk, b = i % nbk;
+    layout::repack_block(fmt, raw + (size_t)i * bb, dst + (size_t)r * row_stride, b, K);
+}
+
+__device__ __forceinline__ float dev_h2f(unsigned int bits) { return __half2float(__ushort_as_half((unsigned short)bits)); }
+
+// One dequantised element, with the reference's rounding sequence (no FMA contraction):
+//   Q8_0: q * scale                         quantization.rs:38-41
+//   Q4_K/Q5_K: (d*sc)*q - (dmin*m)          quantization.rs:357-371, 288-307
+//   Q6_K: (d*scale)*q                       quantization.rs:233-236
+__device__ float dequant_elem(int fmt, const uint8_t* row, long long K, long long k) {
+    if (fmt == SLAI_FMT_Q8_0) {
+        const int q = (int)(signed char)row[k];
+        const unsigned int sb = row[K + 2 * (k >> 5)] | (row[K + 2 * (k >> 5) + 1] << 8);
+        return __fmul_rn((float)q, dev_h2f(sb));
+    }
+    const long long blk = k >> 8;
+    const int e = (int)(k & 255);
+    if (fmt == SLAI_FMT_Q4_K || fmt == SLAI_FMT_Q5_K) {
+        const int bb = fmt == SLAI_FMT_Q4_K ? 144 : 176;
+        const uint8_t* b = row + blk * bb;
+        const float d = dev_h2f(b[0] | (b[1] << 8)), mn = dev_h2f(b[2] | (b[3] << 8));
+        const int G = e >> 6, half = (e >> 5) & 1, l = e & 31;
+        const uint8_t* qs = b + (fmt == SLAI_FMT_Q4_K ? 16 : 48);
+        int q = half ? (qs[32 * G + l] >> 4) : (qs[32 * G + l] & 0xF);
+        if (fmt == SLAI_FMT_Q5_K) q += ((b[16 + l] >> (2 * G + half)) & 1) ? 16 : 0;
+        const uint32_t s0 = b[4] | (b[5] << 8) | (b[6] << 16) | ((uint32_t)b[7] << 24);
+        const uint32_t s1 = b[8] | (b[9] << 8) | (b[10] << 16) | ((uint32_t)b[11] << 24);
+        const uint32_t s2 = b[12] | (b[13] << 8) | (b[14] << 16) | ((uint32_t)b[15] << 24);
+        uint32_t sc, m;
+        frag::scale_min_k4(2 * G + half, s0, s1, s2, sc, m);
+        const float d1 = __fmul_rn(d, (float)sc), m1 = __fmul_rn(mn, (float)m);
+        return __fsub_rn(__fmul_rn(d1, (float)q), m1);
+    }
+    // Q6_K planes
+    const long long nb = K >> 8;
+    const int h = e >> 7, r = e & 127, quarter = r >> 5, l = r & 31;
+    const uint8_t qlb = row[blk * 128 + 64 * h + l + 32 * (quarter & 1)];
+    const int nib = quarter >= 2 ? (qlb >> 4) : (qlb & 0xF);
+    const uint8_t qhb = row[nb * 128 + blk * 64 + 32 * h + l];
+    const int q = (nib | (((qhb >> (2 * quarter)) & 3) << 4)) - 32;
+    const int sc = (int)(signed char)row[nb * 192 + blk * 16 + 8 * h + (l >> 4) + 2 * quarter];
+    const float d = dev_h2f(row[nb * 208 + 2 * blk] | (row[nb * 208 + 2 * blk + 1] << 8));
+    return __fmul_rn(__fmul_rn(d, (float)sc), (float)q);
+}
+
+__global__ void dequant_kernel(int fmt, const uint8_t* __restrict__ data, long long row_stride, long long row0,
+                               long long nrows, long long K, float* __restrict__ out) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= nrows * K) return;
+    const long long r = i / K, k = i % K;
+    const uint8_t* row = data + (size_t)(row0 + r) * row_stride;
+    out[i] = fmt == SLAI_FMT_F32 ? reinterpret_cast<const float*>(row)[k] : dequant_elem(fmt, row, K, k);
+}
+
+}  // namespace
+
+static int qmatrix_alloc(slai_ctx* ctx, int fmt, int64_t nrows, int64_t ncols, size_t nbytes, slai_qmatrix** out) {
+    SLAI_REQUIRE(ctx, out, SLAI_ERR_INVALID_ARG, "qmatrix: null output");
+    *out = nullptr;
+    const int be = fmt_block_elems(fmt), bb = fmt_block_bytes(fmt);
+    SLAI_REQUIRE(ctx, be > 0, SLAI_ERR_UNSUPPORTED_FORMAT,
+                 "qmatrix: GGML type %d is not supported (supported: F32, Q8_0, Q4_K, Q5_K, Q6_K)", fmt);
+    SLAI_REQUIRE(ctx, nrows > 0 && ncols > 0 && ncols % be == 0, SLAI_ERR_SHAPE,
+                 "qmatrix: %lld x %lld is not a whole number of %d-element blocks per row", (long long)nrows,
+                 (long long)ncols, be);
+    SLAI_REQUIRE(ctx, fmt == SLAI_FMT_F32 || ncols % 4 == 0, SLAI_ERR_SHAPE, "qmatrix: ncols must be a multiple of 4");
+    SLAI_REQUIRE(ctx, nbytes == (size_t)nrows * (ncols / be) * bb, SLAI_ERR_SHAPE,
+                 "qmatrix: expected %zu bytes of blocks, got %zu", (size_t)nrows * (ncols / be) * bb, nbytes);
+    slai_qmatrix* m = new slai_qmatrix();
+    m->ctx = ctx; m->fmt = fmt; m->nrows = nrows; m->ncols = ncols;
+    m->nrows_padded = round_up(nrows, 16) + 16;  // segments of a fused matrix may start at any row
+    m->row_stride = layout::row_stride(fmt, ncols);
+    m->bytes = (size_t)m->nrows_padded * m->row_stride + 256;  // slack: partial Q8_0 steps never read past it
+    cudaError_t e = cudaMalloc(&m->data, m->bytes);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        delete m;
+        return slai_set_error(ctx, SLAI_ERR_OOM, "qmatrix: cannot allocate %zu bytes", m->bytes);
+    }
+    *out = m;
+    return SLAI_OK;
+}
+
+SLAI_API int slai_qmatrix_create_from_device(slai_ctx* ctx, int fmt, int64_t nrows, int64_t ncols, const void* d_blocks,
+                                             size_t nbytes, slai_qmatrix** out) {
+    if (!ctx) return SLAI_ERR_INVALID_ARG;
+    int rc = qmatrix_alloc(ctx, fmt, nrows, ncols, nbytes, out);
+    if (rc) return rc;
+    slai_qmatrix* m = *out;
+    const int be = fmt_block_elems(fmt), bb = fmt_block_bytes(fmt);
+    const long long nbk = ncols / be;
+    SLAI_CHECK_CUDA(ctx, cudaMemsetAsync(m->data, 0, m->bytes, ctx->stream));
+    if (fmt == SLAI_FMT_Q8_0 || fmt == SLAI_FMT_Q6_K) {
+        const long long total = nrows * nbk;
+        repack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(fmt, (const uint8_t*)d_blocks, m->data, nrows,
+                                                                               nbk, ncols, bb, m->row_stride);
+        SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    } else {
+        SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(m->data, d_blocks, nbytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    }
+    return SLAI_OK;
+}
+
+SLAI_API int slai_qmatrix_create(slai_ctx* ctx, int fmt, int64_t nrows, int64_t ncols, const void* h_blocks, size_t nbytes,
+                                 slai_qmatrix** out) {
+    if (!ctx) return SLAI_ERR_INVALID_ARG;
+    SLAI_REQUIRE(ctx, h_blocks, SLAI_ERR_INVALID_ARG, "qmatrix: null block pointer");
+    if (fmt == SLAI_FMT_Q8_0 || fmt == SLAI_FMT_Q6_K) {
+        void* tmp = nullptr;
+        cudaError_t e = cudaMalloc(&tmp, nbytes ? nbytes : 16);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            return slai_set_error(ctx, SLAI_ERR_OOM, "qmatrix: cannot allocate %zu bytes of staging", nbytes);
+        }
+        int rc = SLAI_OK;
+        if (cudaMemcpyAsync(tmp, h_blocks, nbytes, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess)
+            rc = slai_set_error(ctx, SLAI_ERR_CUDA, "qmatrix: upload failed");
+        if (!rc) rc = slai_qmatrix_create_from_device(ctx, fmt, nrows, ncols, tmp, nbytes, out);
+        cudaStreamSynchronize(ctx->stream);
+        cudaFree(tmp);
+        return rc;
+    }
+    int rc = qmatrix_alloc(ctx, fmt, nrows, ncols, nbytes, out);
+    if (rc) return rc;
+    slai_qmatrix* m = *out;
+    SLAI_CHECK_CUDA(ctx, cudaMemsetAsync(m->data, 0, m->bytes, ctx->stream));
+    SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(m->data, h_blocks, nbytes, cudaMemcpyHostToDevice, ctx->stream));
+    SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return SLAI_OK;
+}
+
+SLAI_API int slai_qmatrix_destroy(slai_qmatrix* m) {
+    if (!m) return SLAI_OK;
+    if (m->owns && m->data) {
+        cudaStreamSynchronize(m->ctx->stream);
+        cudaFree(m->data);
+    }
+    delete m;
+    return SLAI_OK;
+}
+SLAI_API int slai_qmatrix_shape(const slai_qmatrix* m, int* fmt, int64_t* nrows, int64_t* ncols) {
+    if (!m) return SLAI_ERR_INVALID_ARG;
+    if (fmt) *fmt = m->fmt;
+    if (nrows) *nrows = m->nrows;
+    if (ncols) *ncols = m->ncols;
+    return SLAI_OK;
+}
+SLAI_API size_t slai_qmatrix_device_bytes(const slai_qmatrix* m) { return m ? m->bytes : 0; }
+
+SLAI_API int slai_qmatrix_dequantize(slai_ctx* ctx, const slai_qmatrix* m, float* d_out) {
+    if (!ctx || !m || !d_out) return SLAI_ERR_INVALID_ARG;
+    const long long total = m->nrows * m->ncols;
+    dequant_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(m->fmt, m->data, m->row_stride, 0, m->nrows,
+                                                                            m->ncols, d_out);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    return SLAI_OK;
+}
+SLAI_API int slai_qmatrix_dequantize_row(slai_ctx* ctx, const slai_qmatrix* m, int64_t row, float* d_out) {
+    if (!ctx || !m || !d_out) return SLAI_ERR_INVALID_ARG;
+    SLAI_REQUIRE(ctx, row >= 0 && row < m->nrows, SLAI_ERR_INVALID_ARG, "dequantize_row: row %lld out of range", (long long)row);
+    dequant_kernel<<<(unsigned)((m->ncols + 255) / 256), 256, 0, ctx->stream>>>(m->fmt, m->data, m->row_stride, row, 1,
+                                                                               m->ncols, d_out);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    return SLAI_OK;
+}
+
+SLAI_API int slai_gemv_quant(slai_ctx* ctx, float* d_out, const slai_qmatrix* w, const float* d_v, int n_batch) {
+    if (!ctx || !w || !d_out || !d_v) return SLAI_ERR_INVALID_ARG;
+    SLAI_REQUIRE(ctx, n_batch >= 1 && n_batch <= 8, SLAI_ERR_INVALID_ARG, "gemv: n_batch=%d must be in 1..8", n_batch);
+    for (int b = 0; b < n_batch; b++) {
+        GemvLaunch L;
+        L.fmt = w->fmt;
+        L.K = (int)w->ncols;
+        L.nseg = 1;
+        L.seg[0] = GemvSeg{w->data, w->row_stride, (int)w->nrows, 0};
+        L.v = d_v + (size_t)b * w->ncols;
+        L.out = d_out + (size_t)b * w->nrows;
+        int rc = gemv_launch(ctx, L);
+        if (rc) return rc;
+    }
+    return SLAI_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// small operators
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+constexpr int NT = 256;
+
+__device__ __forceinline__ float blk_sum(float x, float* sh) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = x;
+    __syncthreads();
+    float t = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); w++) t += sh[w];
+    return t;
+}
+__device__ __forceinline__ float blk_max(float x, float* sh) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, o));
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = x;
+    __syncthreads();
+    float t = -INFINITY;
+    for (int w = 0; w < (int)(blockDim.x >> 5); w++) t = fmaxf(t, sh[w]);
+    return t;
+}
+
+__global__ void rms_norm_kernel(float* out, const float* x, const float* w, long long n, float eps) {
+    __shared__ float sh[32];
+    float ss = 0.f;
+    for (long long i = threadIdx.x; i < n; i += blockDim.x) ss += x[i] * x[i];
+    ss = blk_sum(ss, sh);
+    const float rms = 1.0f / sqrtf(ss / (float)n + eps);
+    for (long long i = threadIdx.x; i < n; i += blockDim.x) out[i] = (x[i] * rms) * w[i];
+}
+
+__global__ void layernorm_kernel(float* out, const float* x, long long n, float eps, const float* gamma, const float* beta) {
+    __shared__ float sh[32];
+    float s = 0.f;
+    for (long long i = threadIdx.x; i < n; i += blockDim.x) s += x[i];
+    const float mean = blk_sum(s, sh) / (float)n;
+    float ss = 0.f;
+    for (long long i = threadIdx.x; i < n; i += blockDim.x) {
+        const float d = x[i] - mean;
+        ss += d * d;
+    }
+    const float var = blk_sum(ss, sh) / (float)n;
+    const float scale = 1.0f / sqrtf(var + eps);
+    for (long long i = threadIdx.x; i < n; i += blockDim.x) {
+        float y = (x[i] - mean) * scale;
+        if (gamma) y *= gamma[i];
+        if (beta) y += beta[i];
+        out[i] = y;
+    }
+}
+
+__global__ void softmax_cols_kernel(float* m, long long nrows, long long col_stride) {
+    __shared__ float sh[32];
+    float* col = m + (size_t)blockIdx.x * col_stride;
+    float mx = -INFINITY;
+    for (long long i = threadIdx.x; i < nrows; i += blockDim.x) mx = fmaxf(mx, col[i]);
+    mx = blk_max(mx, sh);
+    float s = 0.f;
+    for (long long i = threadIdx.x; i < nrows; i += blockDim.x) {
+        const float e = expf(col[i] - mx);
+        col[i] = e;
+        s += e;
+    }
+    s = blk_sum(s, sh);
+    for (long long i = threadIdx.x; i < nrows; i += blockDim.x) col[i] = col[i] / s;
+}
+
+__global__ void silu_gate_kernel(float* h1, const float* h2, long long n) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        const float x = h1[i];
+        h1[i] = h2[i] * (x / (1.0f + expf(-x)));
+    }
+}
+
+__device__ float unary_eval(int op, float x, float a0, float a1) {
+    switch (op) {
+        case 0: return fabsf(x);
+        case 1: return isnan(x) ? x : copysignf(1.0f, x);
+        case 2: return -x;
+        case 3: return x > 0.f ? 1.f : 0.f;
+        case 4: return x > 0.f ? x : expf(x) - 1.0f;
+        case 5: {
+            const float A = 0.044715f, S = 0.7978846f;
+            return 0.5f * x * (1.0f + tanhf(S * x * (1.0f + A * x * x)));
+        }
+        case 6: return x * (1.0f / (1.0f + expf(-1.702f * x)));
+        case 7: return x / (1.0f + expf(-x));
+        case 8: return tanhf(x);
+        case 9: return sinf(x);
+        case 10: return cosf(x);
+        case 11: return fmaxf(x, 0.f);
+        case 12: return 1.0f / (1.0f + expf(-x));
+        case 13: return fminf(1.0f, fmaxf(0.0f, (x + 3.0f) / 6.0f));
+        case 14: return x * x;
+        case 15: return sqrtf(x);
+        case 16: return logf(x);
+        case 17: return fmaxf(x, 0.f) + fminf(x, 0.f) * a0;
+        case 18: return fminf(fmaxf(x, a0), a1);
+        case 19: return x * a0;
+        case 20: return x + a0;
+    }
+    return NAN;
+}
+__global__ void unary_kernel(int op, float* dst, const float* src, long long n, float a0, float a1) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        dst[i] = unary_eval(op, src[i], a0, a1);
+}
+
+// mode 0: a += b, 1: a *= b, 2: a = b
+__global__ void binary_kernel(int mode, float* a, const float* b, long long n) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) a[i] = mode == 0 ? a[i] + b[i] : mode == 1 ? a[i] * b[i] : b[i];
+}
+
+__global__ void rope_kernel(int neox, float* q, long long q_len, float* k, int head_size, int kv_dim, int pos,
+                            const float* theta) {
+    const long long pair = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long i = 2 * pair;
+    if (i >= q_len) return;
+    const int hd = (int)(i % head_size);
+    const float ang = (float)pos * theta[hd >> 1];
+    float sn, cs;
+    sincosf(ang, &sn, &cs);
+    long long i0, i1;
+    if (!neox) {
+        i0 = i;
+        i1 = i + 1;
+    } else {
+        const long long head = i / head_size;
+        i0 = pair + head * head_size / 2;
+        i1 = i0 + head_size / 2;
+    }
+    const float q0 = q[i0], q1 = q[i1];
+    q[i0] = cs * q0 - sn * q1;
+    q[i1] = sn * q0 + cs * q1;
+    if (i < kv_dim) {
+        const float k0 = k[i0], k1 = k[i1];
+        k[i0] = cs * k0 - sn * k1;
+        k[i1] = sn * k0 + cs * k1;
+    }
+}
+
+template <typename T>
+__global__ void kv_append_kernel(T* kc, T* vc, const float* k, const float* v, int kv_dim, long long off) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < kv_dim) {
+        kc[off + i] = (T)k[i];
+        vc[off + i] = (T)v[i];
+    }
+}
+template <>
+__global__ void kv_append_kernel<__half>(__half* kc, __half* vc, const float* k, const float* v, int kv_dim, long long off) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < kv_dim) {
+        kc[off + i] = __float2half_rn(k[i]);
+        vc[off + i] = __float2half_rn(v[i]);
+    }
+}
+
+// first maximal index (nalgebra `imax`): ties resolve to the smaller index
+__global__ void argmax_kernel(const float* v, long long n, int* out) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (long long i = threadIdx.x; i < n; i += blockDim.x) {
+        const float x = v[i];
+        if (x > best || (x == best && (int)i < bi)) {
+            best = x;
+            bi = (int)i;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ob > best || (ob == best && oi < bi)) {
+            best = ob;
+            bi = oi;
+        }
+    }
+    if ((threadIdx.x & 31) == 0) {
+        sv[threadIdx.x >> 5] = best;
+        si[threadIdx.x >> 5] = bi;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); w++)
+            if (sv[w] > best || (sv[w] == best && si[w] < bi)) {
+                best = sv[w];
+                bi = si[w];
+            }
+        *out = bi == 0x7fffffff ? 0 : bi;
+    }
+}
+
+__global__ void embed_f32_kernel(float* x, const float* table, int dim, const int* d_token, const float* wpe, const int* d_pos) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= dim) return;
+    float y = table[(size_t)(*d_token) * dim + i];
+    if (wpe) y += wpe[(size_t)(*d_pos) * dim + i];
+    x[i] = y;
+}
+__global__ void embed_q_kernel(float* x, int fmt, const uint8_t* data, long long row_stride, int dim, const int* d_token,
+                               const float* wpe, const int* d_pos) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= dim) return;
+    const uint8_t* row = data + (size_t)(*d_token) * row_stride;
+    float y = fmt == SLAI_FMT_F32 ? reinterpret_cast<const float*>(row)[i] : dequant_elem(fmt, row, dim, i);
+    if (wpe) y += wpe[(size_t)(*d_pos) * dim + i];
+    x[i] = y;
+}
+// Advance the device-side loop state without a host round trip: pos <- pos + 1, step <- step + 1 and
+//   greedy (d_next != NULL): token <- *d_next, history[step] <- *d_next
+//   forced (d_next == NULL): token <- history[step]   (prompt processing)
+__global__ void advance_kernel(int* d_token, int* d_pos, const int* d_next, int* d_history, int* d_step) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int step = *d_step;
+    int nx;
+    if (d_next) {
+        nx = *d_next;
+        d_history[step] = nx;
+    } else {
+        nx = d_history[step];
+    }
+    *d_token = nx;
+    *d_pos = *d_pos + 1;
+    *d_step = step + 1;
+}
+
+template <typename... Args>
+int launch_pdl(slai_ctx* ctx, void (*kern)(Args...), dim3 grid, dim3 block, bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl ? 1 : 0;
+    SLAI_CHECK_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, args...));
+    return SLAI_OK;
+}
+
+}  // namespace
+
+SLAI_API int slai_rms_norm(slai_ctx* ctx, float* d_out, const float* d_x, const float* d_w, int64_t n, float eps) {
+    if (!ctx || !d_out || !d_x || !d_w || n <= 0) return SLAI_ERR_INVALID_ARG;
+    rms_norm_kernel<<<1, 1024, 0, ctx->stream>>>(d_out, d_x, d_w, n, eps);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    return SLAI_OK;
+}
+SLAI_API int slai_layernorm(slai_ctx* ctx, float* d_out, const float* d_x, int64_t n, float eps, const float* d_gamma,
+                            const float* d_beta) {
+    if (!ctx || !d_out || !d_x || n <= 0) return SLAI_ERR_INVALID_ARG;
+    layernorm_kernel<<<1, 1024, 0, ctx->stream>>>(d_out, d_x, n, eps, d_gamma, d_beta);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    return SLAI_OK;
+}
+SLAI_API int slai_softmax_cols(slai_ctx* ctx, float* d_m, int64_t nrows, int64_t ncols, int64_t col_stride) {
+    if (!ctx || !d_m || nrows <= 0 || ncols <= 0) return SLAI_ERR_INVALID_ARG;
+    SLAI_REQUIRE(ctx, col_stride >= nrows, SLAI_ERR_SHAPE, "softmax: col_stride < nrows");
+    softmax_cols_kernel<<<(unsigned)ncols, NT, 0, ctx->stream>>>(d_m, nrows, col_stride);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    return SLAI_OK;
+}
+SLAI_API int slai_silu_gate(slai_ctx* ctx, float* d_h1, const float* d_h2, int64_t n) {
+    if (!ctx || !d_h1 || !d_h2 || n <= 0) return SLAI_ERR_INVALID_ARG;
+    silu_gate_kernel<<<(unsigned)((n + NT - 1) / NT), NT, 0, ctx->stream>>>(d_h1, d_h2, n);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    return SLAI_OK;
+}
+SLAI_API int slai_unary(slai_ctx* ctx, int op, float* d_dst, const float* d_src, int64_t n, const float args4[4]) {
+    if (!ctx || !d_dst || !d_src || n <= 0) return SLAI_ERR_INVALID_ARG;
+    SLAI_REQUIRE(ctx, op >= 0 && op <= 20, SLAI_ERR_INVALID_ARG, "unary: unknown op %d", op);
+    const float a0 = args4 ? args4[0] : 0.f, a1 = args4 ? args4[1] : 0.f;
+    long long blocks = (n + NT - 1) / NT;
+    if (blocks > 65535) blocks = 65535;  // launch_capped: grid-stride above the cap (ops/unary.rs:222)
+    unary_kernel<<<(unsigned)blocks, NT, 0, ctx->stream>>>(op, d_dst, d_src, n, a0, a1);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    return SLAI_OK;
+}
+static int binary(slai_ctx* ctx, int mode, float* a, const float* b, int64_t n) {
+    if (!ctx || !a || !b || n <= 0) return SLAI_ERR_INVALID_ARG;
+    binary_kernel<<<(unsigned)((n + NT - 1) / NT), NT, 0, ctx->stream>>>(mode, a, b, n);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    return SLAI_OK;
+}
+SLAI_API int slai_add_assign(slai_ctx* ctx, float* d_a, const float* d_b, int64_t n) { return binary(ctx, 0, d_a, d_b, n); }
+SLAI_API int slai_mul_assign(slai_ctx* ctx, float* d_a, const float* d_b, int64_t n) { return binary(ctx, 1, d_a, d_b, n); }
+SLAI_API int slai_copy(slai_ctx* ctx, float* d_dst, const float* d_src, int64_t n) { return binary(ctx, 2, d_dst, d_src, n); }
+
+const float* rope_table(slai_ctx* ctx, int head_size, float base) {
+    for (auto& t : ctx->rope_tables)
+        if (t.head_size == head_size && t.base == base) return t.d_theta;
+    // theta_i = base^(-(2i)/head_size), evaluated with the host libm like the CPU twin
+    // (models/llama2/cpu.rs:468: `10000.0_f32.powf(-head_dim / head_size as f32)`).
+    std::vector<float> th(head_size / 2);
+    for (int i = 0; i < head_size / 2; i++) th[i] = powf(base, -(float)(2 * i) / (float)head_size);
+    RopeTable t;
+    t.head_size = head_size;
+    t.base = base;
+    t.d_theta = nullptr;
+    if (cudaMalloc(&t.d_theta, sizeof(float) * (head_size / 2 + 4)) != cudaSuccess) return nullptr;
+    if (cudaMemcpy(t.d_theta, th.data(), sizeof(float) * (head_size / 2), cudaMemcpyHostToDevice) != cudaSuccess) return nullptr;
+    ctx->rope_tables.push_back(t);
+    return t.d_theta;
+}
+
+SLAI_API int slai_rope(slai_ctx* ctx, int variant, float* d_q, int64_t q_len, float* d_k, int head_size, int kv_dim, int pos,
+                       float base_freq) {
+    if (!ctx || !d_q || !d_k) return SLAI_ERR_INVALID_ARG;
+    // the reference asserts even lengths and len(q) >= len(k) (ops/rope.rs:58-63)
+    SLAI_REQUIRE(ctx, q_len > 0 && q_len % 2 == 0 && kv_dim % 2 == 0 && kv_dim <= q_len, SLAI_ERR_SHAPE,
+                 "rope: q_len=%lld and kv_dim=%d must be even with kv_dim <= q_len", (long long)q_len, kv_dim);
+    SLAI_REQUIRE(ctx, head_size > 0 && head_size % 2 == 0 && q_len % head_size == 0, SLAI_ERR_SHAPE,
+                 "rope: head_size=%d must be even and divide q_len", head_size);
+    SLAI_REQUIRE(ctx, variant == 0 || variant == 1, SLAI_ERR_INVALID_ARG, "rope: unknown variant %d", variant);
+    const float* th = rope_table(ctx, head_size, base_freq);
+    SLAI_REQUIRE(ctx, th, SLAI_ERR_CUDA, "rope: cannot build the frequency table");
+    const long long pairs = q_len / 2;
+    rope_kernel<<<(unsigned)((pairs + NT - 1) / NT), NT, 0, ctx->stream>>>(variant, d_q, q_len, d_k, head_size, kv_dim, pos, th);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    return SLAI_OK;
+}
+
+SLAI_API int slai_kv_append(slai_ctx* ctx, void* d_key_cache, void* d_value_cache, int kv_dtype, const float* d_k,
+                            const float* d_v, int kv_dim, int pos) {
+    if (!ctx || !d_key_cache || !d_value_cache || !d_k || !d_v || kv_dim <= 0 || pos < 0) return SLAI_ERR_INVALID_ARG;
+    const long long off = (long long)pos * kv_dim;
+    const unsigned blocks = (kv_dim + NT - 1) / NT;
+    if (kv_dtype == SLAI_KV_F16)
+        kv_append_kernel<__half><<<blocks, NT, 0, ctx->stream>>>((__half*)d_key_cache, (__half*)d_value_cache, d_k, d_v, kv_dim, off);
+    else if (kv_dtype == SLAI_KV_F32)
+        kv_append_kernel<float><<<blocks, NT, 0, ctx->stream>>>((float*)d_key_cache, (float*)d_value_cache, d_k, d_v, kv_dim, off);
+    else
+        return slai_set_error(ctx, SLAI_ERR_INVALID_ARG, "kv_append: unknown cache type %d", kv_dtype);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    return SLAI_OK;
+}
+
+SLAI_API int slai_attention(slai_ctx* ctx, const slai_attn_params* p, const float* d_q, const void* d_key_cache,
+                            const void* d_value_cache, int kv_dtype, float* d_xb) {
+    if (!ctx || !p || !d_q || !d_key_cache || !d_value_cache || !d_xb) return SLAI_ERR_INVALID_ARG;
+    SLAI_REQUIRE(ctx, p->pos < p->seq_len, SLAI_ERR_SHAPE, "attention: pos=%u >= seq_len=%u", p->pos, p->seq_len);
+    SLAI_REQUIRE(ctx, p->kv_mul > 0 && p->n_heads % p->kv_mul == 0 && p->kv_dim == p->n_heads / p->kv_mul * p->head_size,
+                 SLAI_ERR_SHAPE, "attention: inconsistent head counts");
+    SLAI_REQUIRE(ctx, kv_dtype == SLAI_KV_F16 || kv_dtype == SLAI_KV_F32, SLAI_ERR_INVALID_ARG, "attention: unknown cache type");
+    // position scalar on the device (the kernels read it from memory so that CUDA graphs can be replayed)
+    int* d_pos = reinterpret_cast<int*>(ctx->d_counters + 2048);
+    const int pos = (int)p->pos;
+    SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(d_pos, &pos, sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
+    AttnLaunch A;
+    A.q = d_q; A.kcache = d_key_cache; A.vcache = d_value_cache; A.kv_dtype = kv_dtype;
+    A.pos_stride = p->kv_dim; A.head_stride = p->head_size;
+    A.n_heads = (int)p->n_heads; A.kv_mul = (int)p->kv_mul; A.head_size = (int)p->head_size;
+    A.d_pos = d_pos; A.max_pos = pos; A.out = d_xb; A.pdl = false; A.scratch = nullptr; A.scratch_bytes = 0;
+    return attention_launch(ctx, A);
+}
+
+SLAI_API int slai_argmax(slai_ctx* ctx, const float* d_v, int64_t n, int32_t* d_index_out) {
+    if (!ctx || !d_v || !d_index_out || n <= 0) return SLAI_ERR_INVALID_ARG;
+    return launch_argmax(ctx, d_v, n, d_index_out, false);
+}
+
+int launch_argmax(slai_ctx* ctx, const float* v, int64_t n, int32_t* d_out, bool pdl) {
+    return launch_pdl(ctx, argmax_kernel, dim3(1), dim3(1024), pdl, v, (long long)n, (int*)d_out);
+}
+int launch_embed_f32(slai_ctx* ctx, float* x, const float* table, int dim, const int* d_token, const float* wpe,
+                     const int* d_pos, bool pdl) {
+    return launch_pdl(ctx, embed_f32_kernel, dim3((dim + NT - 1) / NT), dim3(NT), pdl, x, table, dim, d_token, wpe, d_pos);
+}
+int launch_embed_q8(slai_ctx* ctx, float* x, const slai_qmatrix* wte, const int* d_token, const float* wpe,
+                    const int* d_pos, bool pdl) {
+    const int dim = (int)wte->ncols;
+    return launch_pdl(ctx, embed_q_kernel, dim3((dim + NT - 1) / NT), dim3(NT), pdl, x, wte->fmt, (const uint8_t*)wte->data,
+                      (long long)wte->row_stride, dim, d_token, wpe, d_pos);
+}
+int launch_advance(slai_ctx* ctx, int* d_token, int* d_pos, const int32_t* d_next, int32_t* d_history, bool pdl) {
+    // d_history[-1] is not used; the step counter lives right after the position scalar (see models)
+    return launch_pdl(ctx, advance_kernel, dim3(1), dim3(1), pdl, d_token, d_pos, (const int*)d_next, (int*)d_history,
+                      d_pos + 1);
+}
+
+// ------------------------------------------------------------------------------------------------
+// synthetic weights
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+__device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+// standard normal from a counter: Box-Muller on two 24-bit uniforms
+__device__ __forceinline__ float normal_at(uint64_t seed, uint64_t idx) {
+    const uint64_t h = splitmix64(seed ^ splitmix64(idx));
+    const float u1 = ((float)((h >> 40) & 0xFFFFFF) + 1.0f) * (1.0f / 16777217.0f);
+    const float u2 = (float)((h >> 8) & 0xFFFFFF) * (1.0f / 16777216.0f);
+    return sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2);
+}
+__device__ __forceinline__ unsigned short f2h_bits(float x) { return __half_as_ushort(__float2half_rn(x)); }
+__device__ __forceinline__ float sdiv(float a, float b) { return b != 0.f ? a / b : 0.f; }
+
+__global__ void synth_normal_kernel(float* out, long long n, uint64_t seed, float std) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = normal_at(seed, (uint64_t)i) * std;
+}
+
+// one thread per block of 32 (Q8_0) or 256 (K-quants) values; simple min/max quantisers that always
+// yield valid blocks (the reference has no quantiser; quality is irrelevant to parity)
+__global__ void synth_blocks_kernel(int fmt, uint8_t* out, long long nblocks, uint64_t seed, float std) {
+    const long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= nblocks) return;
+    if (fmt == SLAI_FMT_Q8_0) {
+        float x[32];
+        float amax = 0.f;
+        for (int i = 0; i < 32; i++) {
+            x[i] = normal_at(seed, (uint64_t)b * 32 + i) * std;
+            amax = fmaxf(amax, fabsf(x[i]));
+        }
+        const unsigned short sb = f2h_bits(amax / 127.0f);
+        const float sv = __half2float(__ushort_as_half(sb));
+        uint8_t* o = out + b * 34;
+        o[0] = sb & 0xFF;
+        o[1] = sb >> 8;
+        for (int i = 0; i < 32; i++) {
+            int q = (int)rintf(sdiv(x[i], sv));
+            q = max(-127, min(127, q));
+            o[2 + i] = (uint8_t)(signed char)q;
+        }
+        return;
+    }
+    float x[256];
+    for (int i = 0; i < 256; i++) x[i] = normal_at(seed, (uint64_t)b * 256 + i) * std;
+    if (fmt == SLAI_FMT_Q4_K || fmt == SLAI_FMT_Q5_K) {
+        const int levels = fmt == SLAI_FMT_Q4_K ? 15 : 31;
+        float s[8], o8[8], smax = 0.f, omax = 0.f;
+        for (int j = 0; j < 8; j++) {
+            float lo = 0.f, hi = -INFINITY;
+            for (int i = 0; i < 32; i++) {
+                lo = fminf(lo, x[32 * j + i]);
+                hi = fmaxf(hi, x[32 * j + i]);
+            }
+            hi = fmaxf(hi, lo);
+            s[j] = (hi - lo) / (float)levels;
+            o8[j] = -lo;
+            smax = fmaxf(smax, s[j]);
+            omax = fmaxf(omax, o8[j]);
+        }
+        const unsigned short db = f2h_bits(smax / 63.0f), mb = f2h_bits(omax / 63.0f);
+        const float dv = __half2float(__ushort_as_half(db)), mv = __half2float(__ushort_as_half(mb));
+        uint8_t sc[8], mn[8];
+        for (int j = 0; j < 8; j++) {
+            sc[j] = (uint8_t)max(0, min(63, (int)rintf(sdiv(s[j], dv))));
+            mn[j] = (uint8_t)max(0, min(63, (int)rintf(sdiv(o8[j], mv))));
+        }
+        const int bb = fmt == SLAI_FMT_Q4_K ? 144 : 176;
+        uint8_t* o = out + b * bb;
+        o[0] = db & 0xFF; o[1] = db >> 8; o[2] = mb & 0xFF; o[3] = mb >> 8;
+        for (int j = 0; j < 4; j++) {
+            o[4 + j] = sc[j] | ((sc[j + 4] >> 4) << 6);
+            o[8 + j] = mn[j] | ((mn[j + 4] >> 4) << 6);
+            o[12 + j] = (sc[j + 4] & 0xF) | ((mn[j + 4] & 0xF) << 4);
+        }
+        uint8_t* qh = o + 16;
+        uint8_t* qs = o + (fmt == SLAI_FMT_Q4_K ? 16 : 48);
+        if (fmt == SLAI_FMT_Q5_K)
+            for (int i = 0; i < 32; i++) qh[i] = 0;
+        for (int G = 0; G < 4; G++)
+            for (int l = 0; l < 32; l++) {
+                int q2[2];
+                for (int hf = 0; hf < 2; hf++) {
+                    const int j = 2 * G + hf;
+                    const float eff = dv * (float)sc[j], off = mv * (float)mn[j];
+                    q2[hf] = max(0, min(levels, (int)rintf(sdiv(x[64 * G + 32 * hf + l] + off, eff))));
+                }
+                qs[32 * G + l] = (uint8_t)((q2[0] & 0xF) | ((q2[1] & 0xF) << 4));
+                if (fmt == SLAI_FMT_Q5_K) qh[l] |= (uint8_t)((((q2[0] >> 4) & 1) << (2 * G)) | (((q2[1] >> 4) & 1) << (2 * G + 1)));
+            }
+        return;
+    }
+    // Q6_K
+    float s[16], smax = 0.f;
+    for (int j = 0; j < 16; j++) {
+        float amax = 0.f;
+        for (int i = 0; i < 16; i++) amax = fmaxf(amax, fabsf(x[16 * j + i]));
+        s[j] = amax / 32.0f;
+        smax = fmaxf(smax, s[j]);
+    }
+    const unsigned short db = f2h_bits(smax / 127.0f);
+    const float dv = __half2float(__ushort_as_half(db));
+    uint8_t* o = out + b * 210;
+    int sc[16];
+    for (int j = 0; j < 16; j++) {
+        sc[j] = max(-128, min(127, (int)rintf(sdiv(s[j], dv))));
+        o[192 + j] = (uint8_t)(signed char)sc[j];
+    }
+    o[208] = db & 0xFF;
+    o[209] = db >> 8;
+    for (int h = 0; h < 2; h++)
+        for (int l = 0; l < 32; l++) {
+            int q[4];
+            for (int c = 0; c < 4; c++) {
+                const int e = 128 * h + 32 * c + l;
+                const float eff = dv * (float)sc[e >> 4];
+                q[c] = max(-32, min(31, (int)rintf(sdiv(x[e], eff)))) + 32;
+            }
+            o[64 * h + l] = (uint8_t)((q[0] & 0xF) | ((q[2] & 0xF) << 4));
+            o[64 * h + 32 + l] = (uint8_t)((q[1] & 0xF) | ((q[3] & 0xF) << 4));
+            o[128 + 32 * h + l] = (uint8_t)((q[0] >> 4) | ((q[1] >> 4) << 2) | ((q[2] >> 4) << 4) | ((q[3] >> 4) << 6));
+        }
+}
+
+}  // namespace
+
+SLAI_API int slai_synth_blocks(slai_ctx* ctx, int fmt, int64_t nrows, int64_t ncols, uint64_t seed, float std, void* d_blocks) {
+    if (!ctx || !d_blocks) return SLAI_ERR_INVALID_ARG;
+    const int be = fmt_block_elems(fmt);
+    SLAI_REQUIRE(ctx, be > 1, SLAI_ERR_UNSUPPORTED_FORMAT, "synth: format %d has no generator", fmt);
+    SLAI_REQUIRE(ctx, nrows > 0 && ncols > 0 && ncols % be == 0, SLAI_ERR_SHAPE, "synth: bad shape");
+    const long long nblocks = nrows * (ncols / be);
+    synth_blocks_kernel<<<(unsigned)((nblocks + 127) / 128), 128, 0, ctx->stream>>>(fmt, (uint8_t*)d_blocks, nblocks, seed, std);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    return SLAI_OK;
+}
+SLAI_API int slai_synth_normal_f32(slai_ctx* ctx, float* d_out, int64_t n, uint64_t seed, float std) {
+    if (!ctx || !d_out || n <= 0) return SLAI_ERR_INVALID_ARG;
+    synth_normal_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(d_out, n, seed, std);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    return SLAI_OK;
+}

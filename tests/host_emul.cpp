@@ -1,0 +1,144 @@
+// CPU emulation of one warp of the dequant-GEMV kernel: 32 host threads play the lanes, the MMA and the
+// shared-memory loads are emulated (slai_b200/csrc/gemv_formats.cuh), everything else is the kernel's own
+// source.  Usage: host_emul <fmt> <K> <blocks.bin (16 rows, GGUF order)> <v.bin (K f32)>  -> prints 16 floats.
+// Compiled for the host only; it never touches a GPU.
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+#include <pthread.h>
+#include <cuda_fp16.h>
+
+#include "../slai_b200/csrc/gemv_formats.cuh"
+#include "../slai_b200/csrc/layout.cuh"
+
+namespace hostemu {
+thread_local int lane;
+thread_local Warp* warp;
+}  // namespace hostemu
+
+using namespace gemvfmt;
+
+struct Job {
+    int fmt, K, nsteps;
+    const uint8_t* rows;  // repacked device-layout rows
+    int64_t stride;
+    Smem S;
+    hostemu::Warp* W;
+    float acc[32][2];
+};
+
+template <class F>
+static void lane_body(Job* J, int lane) {
+    LaneCtx L;
+    L.lane = lane; L.g = lane >> 2; L.t = lane & 3;
+    for (int i = 0; i < 8; i++) { L.bp[i] = 0; L.bs[i] = 0; }
+    F::init(L, J->S);
+    L.bs[7] = F::aux(J->K);
+    const uint8_t* rowA = J->rows + (size_t)L.g * J->stride;
+    const uint8_t* rowB = rowA + 8 * J->stride;
+    float a = 0.f, b = 0.f;
+    typename F::Regs R;
+    for (int s = 0; s < J->nsteps; s++) {
+        F::load(R, rowA, rowB, s, L);
+        F::compute(R, s, L, J->S, a, b);
+    }
+    J->acc[lane][0] = a;
+    J->acc[lane][1] = b;
+}
+
+struct ThreadArg { Job* J; int lane; };
+static void* thread_main(void* p) {
+    ThreadArg* A = (ThreadArg*)p;
+    hostemu::lane = A->lane;
+    hostemu::warp = A->J->W;
+    switch (A->J->fmt) {
+        case 12: lane_body<Q4K>(A->J, A->lane); break;
+        case 13: lane_body<Q5K>(A->J, A->lane); break;
+        case 14: lane_body<Q6K>(A->J, A->lane); break;
+        case 8: lane_body<Q80>(A->J, A->lane); break;
+    }
+    return nullptr;
+}
+
+static std::vector<uint8_t> read_file(const char* path) {
+    FILE* f = fopen(path, "rb");
+    if (!f) { perror(path); exit(2); }
+    fseek(f, 0, SEEK_END);
+    long n = ftell(f);
+    fseek(f, 0, SEEK_SET);
+    std::vector<uint8_t> d(n);
+    if (fread(d.data(), 1, n, f) != (size_t)n) exit(2);
+    fclose(f);
+    return d;
+}
+
+int main(int argc, char** argv) {
+    if (argc < 5) return 2;
+    const int fmt = atoi(argv[1]), K = atoi(argv[2]);
+    std::vector<uint8_t> raw = read_file(argv[3]);
+    std::vector<uint8_t> vb = read_file(argv[4]);
+    const float* v = (const float*)vb.data();
+    const int be = fmt == 8 ? 32 : 256, bb = fmt == 8 ? 34 : fmt == 12 ? 144 : fmt == 13 ? 176 : 210;
+    const int nbk = K / be;
+    if ((int)raw.size() != 16 * nbk * bb || (int)vb.size() != 4 * K) { fprintf(stderr, "size mismatch\n"); return 2; }
+
+    // device layout
+    const int64_t stride = layout::row_stride(fmt, K);
+    std::vector<uint8_t> rows(16 * stride + 64, 0);
+    for (int r = 0; r < 16; r++)
+        for (int b = 0; b < nbk; b++)
+            layout::repack_block(fmt, raw.data() + ((size_t)r * nbk + b) * bb, rows.data() + r * stride, b, K);
+
+    // staging (mirrors stage_vector in gemv.cu with PRO_NONE)
+    const int Kp = (K + 255) & ~255;
+    std::vector<unsigned char> smem(4 * Kp + 32 + (Kp / 32) * 4 + 64, 0);
+    float mx = 0.f;
+    for (int k = 0; k < K; k++) mx = fmaxf(mx, fabsf(v[k]));
+    float scale = 1.f;
+    if (mx > 0.f) { int e; frexpf(mx, &e); if (e < -100) e = -100; scale = ldexpf(1.0f, 14 - e); }
+    __half* hi = (__half*)smem.data();
+    __half* lo = hi + Kp;
+    float* sv = (float*)(smem.data() + 4 * Kp + 32);
+    for (int k = 0; k < Kp; k++) {
+        const float x = k < K ? v[k] * scale : 0.f;
+        const __half h = __float2half_rn(x);
+        hi[frag::perm4(k)] = h;
+        lo[frag::perm4(k)] = __float2half_rn(x - __half2float(h));
+    }
+    for (int j = 0; j < Kp / 32; j++) {
+        float s = 0.f;  // same association as the kernel: ((x0+x1)+(x2+x3)) then a xor-tree over 8 lanes
+        float part[8];
+        for (int q = 0; q < 8; q++) {
+            float x[4];
+            for (int i = 0; i < 4; i++) { int k = 32 * j + 4 * q + i; x[i] = k < K ? v[k] * scale : 0.f; }
+            part[q] = (x[0] + x[1]) + (x[2] + x[3]);
+        }
+        for (int o = 1; o < 8; o <<= 1) { float n[8]; for (int q = 0; q < 8; q++) n[q] = part[q] + part[q ^ o]; memcpy(part, n, sizeof n); }
+        s = part[0];
+        sv[j] = s;
+    }
+
+    hostemu::Warp W;
+    pthread_barrier_init(&W.bar, nullptr, 32);
+    W.smem = smem.data();
+    Job J;
+    J.fmt = fmt; J.K = K; J.rows = rows.data(); J.stride = stride; J.W = &W;
+    J.nsteps = (fmt == 12 || fmt == 13) ? K / 256 : (K + 127) / 128;
+    J.S.hi = 0; J.S.lo = 2 * Kp; J.S.zero = 4 * Kp; J.S.sv = 4 * Kp + 32; J.S.red = nullptr; J.S.stat = nullptr;
+    pthread_t th[32];
+    ThreadArg args[32];
+    for (int l = 0; l < 32; l++) { args[l] = {&J, l}; pthread_create(&th[l], nullptr, thread_main, &args[l]); }
+    for (int l = 0; l < 32; l++) pthread_join(th[l], nullptr);
+    for (int r = 0; r < 16; r++) {
+        const int g = r & 7, which = r >> 3;
+        float s = 0.f;
+        // xor-1 then xor-2 shuffle reduction as in the kernel
+        float a0 = J.acc[g * 4 + 0][which] + J.acc[g * 4 + 1][which];
+        float a1 = J.acc[g * 4 + 2][which] + J.acc[g * 4 + 3][which];
+        s = a0 + a1;
+        printf("%.9g\n", s / scale);
+    }
+    return 0;
+}

@@ -1,0 +1,307 @@
+"""GPU parity tests of the operator kernels, through the C ABI, against the CPU oracle on the same seeded inputs.
+Tolerances: dequantised weights bit-exact; GEMV / attention <= 1e-3 relative L2 (f32 accumulation); the small
+operators at the tolerances of the reference's own tests (1e-4 ... 1e-7, crates/slai/src/ops/*.rs)."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from slai_b200 import synth, _lib
+from slai_b200._lib import SlaiError
+from slai_b200.ops import (BatchedMultiqueryAttentionParams, GpuQuantMatrix, GpuVector, RoPEVariant, UnaryOp)
+from helpers import bits, rel_l2
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+FMTS = [synth.FMT_Q8_0, synth.FMT_Q4_K, synth.FMT_Q5_K, synth.FMT_Q6_K]
+GEMV_TOL = 1e-3
+
+
+def test_device_is_b200(backend):
+    name, sms = backend.device_info()
+    assert sms > 0 and "NVIDIA" in name
+
+
+# ---- dequantisation: bit-exact ------------------------------------------------------------------------
+@pytest.mark.parametrize("fmt", FMTS)
+def test_dequantize_recipes_bit_exact(backend, fmt):
+    g = np.load(os.path.join(GOLD, "block_recipes.npz"))
+    name = synth.FMT_NAMES[fmt]
+    blocks = g[f"{name}_blocks"]
+    nb = blocks.shape[0]
+    be = synth.BLOCK_ELEMS[fmt]
+    for rows in (1, 2, nb // 2 if fmt == synth.FMT_Q8_0 else 4):
+        m = GpuQuantMatrix(backend, fmt, rows, nb // rows * be, blocks)
+        got = m.dequantize().reshape(-1)
+        assert np.array_equal(bits(got), bits(g[f"{name}_values"]))
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("shape", [(1, 256), (5, 512), (33, 2816), (16, 4096)])
+def test_dequantize_bit_exact(backend, fmt, shape):
+    M, K = shape
+    rng = np.random.default_rng(M * K + fmt)
+    for blocks in (synth.quantize(fmt, synth.normal_matrix(M + K, M, K)), synth.random_blocks(fmt, M, K, rng)):
+        m = GpuQuantMatrix(backend, fmt, M, K, blocks)
+        ref = O.dequantize(fmt, blocks)
+        assert np.array_equal(bits(m.dequantize().reshape(-1)), bits(ref))
+        r = M // 2
+        assert np.array_equal(bits(m.dequantize_row(r)), bits(ref.reshape(M, K)[r]))
+
+
+def test_q8_0_odd_block_counts_stay_quantized(backend):
+    """K = 288 (9 blocks) and K = 1600 (25 pairs): the reference dequantises / truncates these; here they are exact."""
+    for M, K in ((288, 288), (48, 1600), (7, 32)):
+        blocks = synth.quantize(synth.FMT_Q8_0, synth.normal_matrix(K, M, K))
+        m = GpuQuantMatrix(backend, synth.FMT_Q8_0, M, K, blocks)
+        assert np.array_equal(bits(m.dequantize().reshape(-1)), bits(O.dequantize(synth.FMT_Q8_0, blocks)))
+
+
+# ---- GEMV ---------------------------------------------------------------------------------------------
+def run_gemv(backend, ctx, fmt, M, K, blocks, v):
+    m = GpuQuantMatrix(backend, fmt, M, K, blocks)
+    dv = backend.vector(v)
+    out = backend.zeros(M)
+    ctx.matmul_quant_assign(out, m, dv)
+    return out.to_numpy()
+
+
+GEMV_SHAPES = [(16, 256), (5, 512), (17, 768), (288, 2816), (1000, 4096), (4096, 4096), (512, 11008), (11008, 4096)]
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("shape", GEMV_SHAPES)
+def test_gemv_parity(backend, ctx, fmt, shape):
+    M, K = shape
+    rng = np.random.default_rng(M + 31 * K + fmt)
+    blocks = synth.quantize(fmt, synth.normal_matrix(M * 7 + K, M, K))
+    v = rng.standard_normal(K).astype(np.float32)
+    got = run_gemv(backend, ctx, fmt, M, K, blocks, v)
+    ref = O.gemv_quant(fmt, blocks, v, M, K, nthreads=8)
+    assert rel_l2(got, ref) < GEMV_TOL
+    ref64 = O.dequantize(fmt, blocks).reshape(M, K).astype(np.float64) @ v.astype(np.float64)
+    assert rel_l2(got, ref64) < 1e-5  # far inside the budget: the f16 split keeps ~22 bits of the activations
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_gemv_random_bit_patterns(backend, ctx, fmt):
+    """Blocks of random bits (every scale / quant code occurs), the input style of the reference benchmark."""
+    M, K = 300, 2048
+    rng = np.random.default_rng(99 + fmt)
+    blocks = synth.random_blocks(fmt, M, K, rng)
+    v = rng.standard_normal(K).astype(np.float32)
+    got = run_gemv(backend, ctx, fmt, M, K, blocks, v)
+    ref64 = O.dequantize(fmt, blocks).reshape(M, K).astype(np.float64) @ v.astype(np.float64)
+    assert rel_l2(got, ref64) < 1e-5
+
+
+@pytest.mark.parametrize("M,K", [(288, 288), (768, 288), (288, 768), (1031, 1600), (1600, 6400), (9, 32)])
+def test_gemv_q8_0_ragged_shapes(backend, ctx, M, K):
+    rng = np.random.default_rng(M + K)
+    blocks = synth.quantize(synth.FMT_Q8_0, synth.normal_matrix(M + K, M, K))
+    v = rng.standard_normal(K).astype(np.float32)
+    got = run_gemv(backend, ctx, synth.FMT_Q8_0, M, K, blocks, v)
+    assert rel_l2(got, O.gemv_quant(synth.FMT_Q8_0, blocks, v, M, K, nthreads=4)) < GEMV_TOL
+
+
+@pytest.mark.parametrize("scale", [1e-30, 1e-6, 1.0, 1e4, 1e30])
+def test_gemv_activation_range(backend, ctx, scale):
+    """The f16 hi/lo split is preceded by a power-of-two scaling of the vector: tiny and huge activations work."""
+    M, K, fmt = 64, 1024, synth.FMT_Q4_K
+    rng = np.random.default_rng(5)
+    blocks = synth.quantize(fmt, synth.normal_matrix(3, M, K))
+    v = (rng.standard_normal(K) * scale).astype(np.float32)
+    got = run_gemv(backend, ctx, fmt, M, K, blocks, v)
+    ref64 = O.dequantize(fmt, blocks).reshape(M, K).astype(np.float64) @ v.astype(np.float64)
+    assert rel_l2(got, ref64) < 1e-5
+    z = run_gemv(backend, ctx, fmt, M, K, blocks, np.zeros(K, np.float32))
+    assert np.all(z == 0)
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_gemv_full_size_device_blocks(backend, ctx, fmt):
+    """BASELINE config 2's largest shape (32000 x 4096) with blocks generated on the device; the same bytes are
+    read back for the oracle.  Also checks linearity W(a x + y) = a W x + W y, a size-independent property."""
+    M, K = 32000, 4096
+    m = GpuQuantMatrix.synthetic(backend, fmt, M, K, seed=1234 + fmt, std=0.02, keep_raw=True)
+    blocks = m.raw.to_numpy()
+    w = O.dequantize(fmt, blocks[: 64 * (K // synth.BLOCK_ELEMS[fmt]) * synth.BLOCK_BYTES[fmt]]).reshape(64, K)
+    assert np.isfinite(w).all() and 0.015 < w.std() < 0.025
+    rng = np.random.default_rng(fmt)
+    x, y = rng.standard_normal(K).astype(np.float32), rng.standard_normal(K).astype(np.float32)
+    dx, dy, dz = backend.vector(x), backend.vector(y), backend.vector(np.float32(2.5) * x + y)
+    ox, oy, oz = backend.zeros(M), backend.zeros(M), backend.zeros(M)
+    ctx.matmul_quant_assign(ox, m, dx)
+    ctx.matmul_quant_assign(oy, m, dy)
+    ctx.matmul_quant_assign(oz, m, dz)
+    gx, gy, gz = ox.to_numpy(), oy.to_numpy(), oz.to_numpy()
+    assert rel_l2(gx, O.gemv_quant(fmt, blocks, x, M, K, nthreads=8)) < GEMV_TOL
+    assert rel_l2(gz, 2.5 * gx.astype(np.float64) + gy) < 1e-5
+
+
+def test_gemv_batch(backend, ctx):
+    M, K, fmt, nb = 96, 512, synth.FMT_Q5_K, 3
+    rng = np.random.default_rng(1)
+    blocks = synth.quantize(fmt, synth.normal_matrix(8, M, K))
+    v = rng.standard_normal((nb, K)).astype(np.float32)
+    m = GpuQuantMatrix(backend, fmt, M, K, blocks)
+    out = backend.zeros(nb * M)
+    ctx.matmul_quant_assign(out, m, backend.vector(v), n_batch=nb)
+    got = out.to_numpy().reshape(nb, M)
+    for b in range(nb):
+        assert rel_l2(got[b], O.gemv_quant(fmt, blocks, v[b], M, K)) < GEMV_TOL
+
+
+def test_gemv_f32_matrix(backend, ctx):
+    M, K = 100, 288
+    rng = np.random.default_rng(2)
+    w = rng.standard_normal((M, K)).astype(np.float32)
+    v = rng.standard_normal(K).astype(np.float32)
+    got = run_gemv(backend, ctx, synth.FMT_F32, M, K, w.view(np.uint8), v)
+    assert rel_l2(got, O.gemv_f32(w, v)) < 1e-5
+
+
+def test_errors(backend, ctx):
+    with pytest.raises(SlaiError) as e:  # legacy formats are listed in the enum but have no kernel
+        GpuQuantMatrix(backend, _lib.FMT_Q4_0, 4, 64, np.zeros(4 * 2 * 18, np.uint8))
+    assert e.value.code == _lib.ERR_UNSUPPORTED_FORMAT
+    with pytest.raises(SlaiError) as e:
+        GpuQuantMatrix(backend, synth.FMT_Q4_K, 4, 300, np.zeros(4 * 144, np.uint8))
+    assert e.value.code == _lib.ERR_SHAPE
+    m = GpuQuantMatrix(backend, synth.FMT_Q4_K, 16, 256, synth.quantize(synth.FMT_Q4_K, synth.normal_matrix(1, 16, 256)))
+    with pytest.raises(SlaiError) as e:
+        ctx.matmul_quant_assign(backend.zeros(16), m, backend.zeros(255))
+    assert e.value.code == _lib.ERR_SHAPE
+    with pytest.raises(SlaiError) as e:  # odd length (the reference asserts, ops/rope.rs:58-63)
+        ctx.rope(RoPEVariant.Original, backend.zeros(33), backend.zeros(33), 32, 32, 1)
+    assert e.value.code == _lib.ERR_SHAPE
+    p = BatchedMultiqueryAttentionParams(seq_len=8, kv_dim=64, kv_mul=1, n_heads=2, head_size=32, pos=8)
+    with pytest.raises(SlaiError):
+        ctx.attention(p, backend.zeros(64), backend.zeros(8 * 64), backend.zeros(8 * 64), backend.zeros(64))
+
+
+# ---- small operators (sizes and tolerances of the reference's tests) ----------------------------------
+N = 1757
+
+
+def test_rms_norm(backend, ctx):
+    rng = np.random.default_rng(0)
+    a, w = rng.random(N, dtype=np.float32), rng.random(N, dtype=np.float32)
+    for eps in (1e-5, 1e-6):
+        out = backend.zeros(N)
+        ctx.rms_norm_assign(out, backend.vector(a), backend.vector(w), eps)
+        np.testing.assert_allclose(out.to_numpy(), O.rms_norm(a, w, eps), rtol=1e-4)  # ops/rms_norm.rs:166
+
+
+def test_layernorm(backend, ctx):
+    rng = np.random.default_rng(1)
+    a = rng.random(N, dtype=np.float32)
+    out = backend.zeros(N)
+    ctx.layernorm(out, backend.vector(a))
+    np.testing.assert_allclose(out.to_numpy(), O.layernorm(a), rtol=1e-5, atol=1e-5)  # ops/layernorm.rs:188
+    g, b = rng.random(N, dtype=np.float32), rng.random(N, dtype=np.float32)
+    ctx.layernorm(out, backend.vector(a), 1e-5, backend.vector(g), backend.vector(b))
+    np.testing.assert_allclose(out.to_numpy(), O.layernorm(a) * g + b, rtol=1e-5, atol=1e-5)
+
+
+def test_softmax(backend, ctx):
+    rng = np.random.default_rng(2)
+    a = rng.random((3, N), dtype=np.float32)
+    buf = backend.vector(a)
+    ctx.softmax_cols(buf, N, 3)
+    got = buf.to_numpy().reshape(3, N)
+    for c in range(3):
+        np.testing.assert_allclose(got[c], O.softmax(a[c]), rtol=1e-5, atol=1e-7)  # ops/softmax.rs:129
+
+
+def test_silu(backend, ctx):
+    rng = np.random.default_rng(3)
+    h1, h2 = (rng.random(N, dtype=np.float32) - 0.5) * 10, rng.random(N, dtype=np.float32)
+    buf = backend.vector(h1)
+    ctx.silu(buf, backend.vector(h2))
+    np.testing.assert_allclose(buf.to_numpy(), O.silu_gate(h1, h2), rtol=1e-5, atol=1e-6)  # ops/silu.rs:129
+
+
+@pytest.mark.parametrize("op", list(UnaryOp))
+def test_unary(backend, ctx, op):
+    rng = np.random.default_rng(int(op))
+    x = rng.random(N, dtype=np.float32)  # [0,1) like the reference test (ops/unary.rs:308-407)
+    if op not in (UnaryOp.Sqrt, UnaryOp.Log):
+        x = (x - 0.5) * 6
+    else:
+        x = x + 0.01
+    args = (0.1, 0.8, 0.0, 0.0) if op != UnaryOp.Clamp else (-0.5, 0.8, 0.0, 0.0)
+    src, dst = backend.vector(x), backend.zeros(N)
+    ctx.unary(op, dst, src, args)
+    ref = O.unary(int(op), x, args)
+    np.testing.assert_allclose(dst.to_numpy(), ref, rtol=1e-5, atol=1e-5)
+    ctx.unary(op, src, src, args)  # in place
+    np.testing.assert_allclose(src.to_numpy(), ref, rtol=1e-5, atol=1e-5)
+
+
+def test_binary_ops(backend, ctx):
+    rng = np.random.default_rng(4)
+    a, b = rng.random(N, dtype=np.float32), rng.random(N, dtype=np.float32)
+    da, db = backend.vector(a), backend.vector(b)
+    ctx.add_assign(da, db)
+    assert np.array_equal(da.to_numpy(), a + b)
+    ctx.mul_assign(da, db)
+    assert np.array_equal(da.to_numpy(), (a + b) * b)
+    ctx.copy(da, db)
+    assert np.array_equal(da.to_numpy(), b)
+    assert ctx.argmax(backend.vector(np.array([1, 7, 3, 7, 2], np.float32))) == 1
+    big = rng.random(50257, dtype=np.float32)
+    assert ctx.argmax(backend.vector(big)) == int(np.argmax(big))
+
+
+@pytest.mark.parametrize("variant", [RoPEVariant.Original, RoPEVariant.Neox])
+@pytest.mark.parametrize("pos", [0, 10, 4095])
+def test_rope(backend, ctx, variant, pos):
+    rng = np.random.default_rng(5)
+    hs, nq, nk = 128, 13, 9  # ops/rope.rs:144-228
+    q, k = rng.random(nq * hs, dtype=np.float32), rng.random(nq * hs, dtype=np.float32)
+    dq, dk = backend.vector(q), backend.vector(k)
+    ctx.rope(variant, dq, dk, hs, nk * hs, pos, 10000.0)
+    rq, rk = O.rope(q, k, hs, nk * hs, pos, 10000.0, neox=(variant == RoPEVariant.Neox))
+    np.testing.assert_allclose(dq.to_numpy(), rq, atol=1e-5)  # ops/rope.rs:225-227
+    np.testing.assert_allclose(dk.to_numpy(), rk, atol=1e-5)
+
+
+# ---- attention ----------------------------------------------------------------------------------------
+@pytest.mark.parametrize("kv_dtype", [_lib.KV_F32, _lib.KV_F16])
+@pytest.mark.parametrize("cfg", [(1024, 12, 1, 64, (0, 1, 7, 8, 100, 1023)),   # the reference's disabled test shape
+                                 (256, 6, 1, 48, (0, 33, 255)),                  # tiny Llama heads (48)
+                                 (4096, 32, 1, 128, (0, 640, 4095)),             # Llama-2-7B
+                                 (2048, 64, 8, 128, (5, 1500))])                 # Llama-2-70B GQA
+def test_attention_parity(backend, ctx, kv_dtype, cfg):
+    seq, nh, kvm, hs, positions = cfg
+    nkv = nh // kvm
+    kvd = nkv * hs
+    rng = np.random.default_rng(seq + nh)
+    kc = rng.standard_normal((seq, kvd)).astype(np.float32)
+    vc = rng.standard_normal((seq, kvd)).astype(np.float32)
+    if kv_dtype == _lib.KV_F16:
+        kc, vc = kc.astype(np.float16), vc.astype(np.float16)
+    dk, dv = backend.vector(kc, kc.dtype), backend.vector(vc, vc.dtype)
+    for pos in positions:
+        q = rng.standard_normal(nh * hs).astype(np.float32)
+        out = backend.zeros(nh * hs)
+        p = BatchedMultiqueryAttentionParams(seq_len=seq, kv_dim=kvd, kv_mul=kvm, n_heads=nh, head_size=hs, pos=pos)
+        ctx.attention(p, backend.vector(q), dk, dv, out, kv_dtype)
+        ref, _ = O.attention(q, kc.astype(np.float32), vc.astype(np.float32), seq_len=seq, kv_dim=kvd, kv_mul=kvm, n_heads=nh,
+                             head_size=hs, pos=pos)
+        assert rel_l2(out.to_numpy(), ref) < 1e-3, pos
+        assert rel_l2(out.to_numpy(), ref) < 2e-5, pos
+
+
+def test_kv_append(backend, ctx):
+    kvd, seq = 96, 8
+    rng = np.random.default_rng(6)
+    k, v = rng.standard_normal(kvd).astype(np.float32), rng.standard_normal(kvd).astype(np.float32)
+    for dt, npdt in ((_lib.KV_F32, np.float32), (_lib.KV_F16, np.float16)):
+        kc, vc = backend.zeros(seq * kvd, npdt), backend.zeros(seq * kvd, npdt)
+        ctx.kv_append(kc, vc, backend.vector(k), backend.vector(v), kvd, 3, dt)
+        a, b = kc.to_numpy().reshape(seq, kvd), vc.to_numpy().reshape(seq, kvd)
+        assert np.array_equal(a[3], k.astype(npdt)) and np.array_equal(b[3], v.astype(npdt))
+        assert not a[[0, 1, 2, 4, 5, 6, 7]].any()
