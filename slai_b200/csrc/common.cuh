@@ -48,19 +48,14 @@ int slai_set_error(slai_ctx* ctx, int code, const char* fmt, ...);
     } while (0)
 
 // ------------------------------------------------------------------------------------------------
-// Quantized matrix as stored on the device.
-//   Q4_K / Q5_K : the GGUF bytes, unchanged (144 / 176-byte super-blocks, rows 16-byte aligned).
-//   Q8_0        : per row  [K int8 quants][K/32 f16 scales][pad to 16 bytes]
-//   Q6_K        : per row  [nb*128 ql][nb*64 qh][nb*16 int8 scales][nb f16 d][pad to 16 bytes]
-//   F32         : dense row-major.
-// Rows are padded with zero rows up to a multiple of 16 so kernels may read whole 16-row tiles.
+// Quantized matrix as stored on the device: tile-major blocks of 16 rows x one K step (layout.cuh);
+// F32 matrices are dense row-major.  The last tile is padded with zero rows.
 // ------------------------------------------------------------------------------------------------
 struct slai_qmatrix {
     slai_ctx* ctx = nullptr;
     int fmt = 0;
     int64_t nrows = 0, ncols = 0;
-    int64_t nrows_padded = 0;
-    int64_t row_stride = 0;  // bytes between rows in `data`
+    int64_t tile_bytes = 0;  // bytes of one 16-row tile (F32: bytes of one row)
     uint8_t* data = nullptr;
     size_t bytes = 0;
     bool owns = true;
@@ -103,8 +98,8 @@ enum GemvEpilogue {
 };
 
 struct GemvSeg {
-    const uint8_t* w = nullptr;   // device data of the matrix (first row of the segment)
-    int64_t row_stride = 0;
+    const uint8_t* w = nullptr;   // first tile of the segment (tile-major data; F32: first row)
+    int64_t tile_bytes = 0;       // bytes of one 16-row tile
     int rows = 0;                 // logical rows
     int tile0 = 0;                // first 16-row tile of this segment in the virtual tile space (set by gemv_launch)
     const float* bias = nullptr;  // per row of the segment, may be null

@@ -4,34 +4,45 @@
 //   epilogue : store | residual add | SiLU gate (ops/silu.rs:50-58) | GELU (ops/unary.rs:81-85) |
 //              q/k/v split with RoPE (ops/rope.rs:88-125) and KV-cache append (transformer.rs:329-334)
 //
-// Kernel shape.  256 threads = 8 warps.  A work item is one 16-row tile; `KS` warps share an item and
-// split its K range by steps, so a block works on 8/KS items at a time.  Every lane streams 16-byte
-// chunks of packed quants straight from global memory (each row is read exactly once, 64 contiguous
-// bytes per row per load instruction, two steps in flight per warp), expands them to exact f16 pairs
-// and feeds mma.sync.m16n8k16 against the activation vector staged once per block in shared memory
-// (see gemv_frag.cuh).  Scales are applied to the per-sub-block sums in f32; the lanes of a row are
-// reduced by shuffles, the warps of an item through shared memory in a fixed order (deterministic).
+// Kernel shape.  One persistent block of 16 warps per SM.  The weights are stored tile-major (layout.cuh):
+// the packed data of 16 rows x one K step is one contiguous block.  A work item is one 16-row tile; `ks`
+// warps share an item and split its K range into contiguous runs of blocks.  Every warp owns a private ring
+// of shared-memory stages: one lane issues a bulk asynchronous copy (cp.async.bulk, completion counted on an
+// mbarrier) per block, always NSTAGE blocks ahead of the block being consumed and running on across item
+// boundaries, so the bytes in flight per SM are set by the ring size (100-180 KB), not by registers or
+// occupancy.  The consumer side expands the packed quants to exact f16 pairs and feeds mma.sync.m16n8k16
+// against the activation vector staged once per block of threads in shared memory (gemv_frag.cuh); scales are
+// applied to the per-sub-block sums in f32; the lanes of a row are reduced by shuffles, the warps of an item
+// through shared memory in a fixed order (deterministic).
 //
-// The first weight loads are issued before `griddepcontrol.wait`, so under programmatic dependent
-// launch they overlap the tail of the kernel that produces the activation vector.
+// The first NSTAGE copies are issued before `griddepcontrol.wait`, so under programmatic dependent launch
+// the weight stream starts while the kernel that produces the activation vector is still finishing.
+// Every mbarrier wait is bounded; on expiry the warp raises the context's error flag and stops waiting.
 #include "common.cuh"
 #include "gemv_frag.cuh"
 #include "gemv_formats.cuh"
+#include "layout.cuh"
 
 namespace {
 
 using namespace frag;
 using namespace gemvfmt;
 
-constexpr int THREADS = 256;
-constexpr int WARPS = 8;
+constexpr int THREADS = 512;
+constexpr int WARPS = 16;
+constexpr int MAX_STAGES = 8;
+constexpr int SMEM_LIMIT = 227 * 1024;
 
 struct GemvParams {
     GemvSeg seg[3];
     int nseg;
     int K;
-    int n_items;     // 16-row tiles (NMAT==2: tiles of seg[0])
-    int nsteps;      // K steps per row
+    int n_items;     // 16-row tiles (dual launch: tiles of seg[0])
+    int nsteps;      // tile-step blocks per tile
+    int ks;          // warps per item
+    int nstage;      // ring depth per warp
+    int step_bytes;  // bytes of a tile-step block
+    int stage_stride;
     const float* v;
     float* out;
     const float* norm_w;
@@ -46,11 +57,41 @@ struct GemvParams {
     void* vcache;
     int kv_f16;
     long long kv_pos_stride, kv_head_stride;
+    unsigned int* err_flag;
 };
 
-// ---------------------------------------------------------------------------------------------
-// Block-wide reductions used by the staging pass.
-// ---------------------------------------------------------------------------------------------
+// ---- mbarrier / bulk copy -------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t a, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(a), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t a, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(a), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t a, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(a), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: returns false (and raises the error flag) if the phase does not complete.
+__device__ __forceinline__ bool mbar_wait(uint32_t a, uint32_t parity, unsigned int* err_flag) {
+    for (int i = 0; i < (1 << 20); i++) {
+        if (mbar_try_wait(a, parity)) return true;
+        if (i > 1024) __nanosleep(64);
+    }
+    atomicExch(err_flag, 1u);
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t mbar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(mbar)
+                 : "memory");
+}
+
+// ---- block-wide reductions used by the staging pass -----------------------------------------
 __device__ __forceinline__ float warp_sum(float x) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
@@ -61,7 +102,6 @@ __device__ __forceinline__ float warp_max(float x) {
     for (int o = 16; o > 0; o >>= 1) x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, o));
     return x;
 }
-// returns (sum, max) over the block; `stat` is scratch of >= 2*WARPS floats
 __device__ __forceinline__ void block_sum_max(float& s, float& m, float* stat) {
     s = warp_sum(s);
     m = warp_max(m);
@@ -86,11 +126,11 @@ __device__ __forceinline__ void block_sum_max(float& s, float& m, float* stat) {
 // [2^13, 2^14), split into f16 hi + lo in the [0,2,1,3] order, and per-32 sums of the scaled values
 // (for the `- dmin*m * sum(v)` term of Q4_K / Q5_K).  Returns 1/scale.
 template <int PRO, bool NEED_SV>
-__device__ float stage_vector(const GemvParams& P, const Smem& S, int Kp) {
+__device__ float stage_vector(const GemvParams& P, const Smem& S, float* stat, int Kp) {
     const int K = P.K;
     const int tid = threadIdx.x;
     const float4* v4 = reinterpret_cast<const float4*>(P.v);
-    const int n4 = K >> 2;  // K is a multiple of 32
+    const int n4 = K >> 2;
     float mul = 1.f, sub = 0.f;
     float sum = 0.f, mx = 0.f;
     if (PRO == PRO_LN) {
@@ -98,7 +138,7 @@ __device__ float stage_vector(const GemvParams& P, const Smem& S, int Kp) {
             const float4 x = __ldg(v4 + i);
             sum += (x.x + x.y) + (x.z + x.w);
         }
-        block_sum_max(sum, mx, S.stat);
+        block_sum_max(sum, mx, stat);
         sub = sum / (float)K;
         sum = 0.f;
     }
@@ -108,35 +148,27 @@ __device__ float stage_vector(const GemvParams& P, const Smem& S, int Kp) {
         float4 x = __ldg(v4 + i);
         if (PRO == PRO_NONE) {
             mx = fmaxf(mx, fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w))));
-        } else if (PRO == PRO_RMS) {
-            const float4 w = __ldg(w4p + i);
-            sum += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
-            mx = fmaxf(mx, fmaxf(fmaxf(fabsf(x.x * w.x), fabsf(x.y * w.y)), fmaxf(fabsf(x.z * w.z), fabsf(x.w * w.w))));
         } else {
             const float4 w = __ldg(w4p + i);
-            x.x -= sub; x.y -= sub; x.z -= sub; x.w -= sub;
+            if (PRO == PRO_LN) { x.x -= sub; x.y -= sub; x.z -= sub; x.w -= sub; }
             sum += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
             mx = fmaxf(mx, fmaxf(fmaxf(fabsf(x.x * w.x), fabsf(x.y * w.y)), fmaxf(fabsf(x.z * w.z), fabsf(x.w * w.w))));
         }
     }
-    block_sum_max(sum, mx, S.stat);
-    if (PRO == PRO_RMS) {
+    block_sum_max(sum, mx, stat);
+    if (PRO != PRO_NONE) {
         mul = 1.0f / sqrtf(sum / (float)K + P.eps);
         mx *= mul;
-    } else if (PRO == PRO_LN) {
-        mul = 1.0f / sqrtf(sum / (float)K + P.eps);
-        mx *= mul;
-        if (P.norm_b) {
+        if (PRO == PRO_LN && P.norm_b) {
             float mb = 0.f, dummy = 0.f;
             for (int i = tid; i < n4; i += THREADS) {
                 const float4 b = __ldg(b4p + i);
                 mb = fmaxf(mb, fmaxf(fmaxf(fabsf(b.x), fabsf(b.y)), fmaxf(fabsf(b.z), fabsf(b.w))));
             }
-            block_sum_max(dummy, mb, S.stat);
+            block_sum_max(dummy, mb, stat);
             mx += mb;
         }
     }
-    // power-of-two scale: max|v| * scale in [2^13, 2^14)
     float scale = 1.f;
     if (mx > 0.f && mx < 3.0e38f) {
         int e;
@@ -146,6 +178,7 @@ __device__ float stage_vector(const GemvParams& P, const Smem& S, int Kp) {
     }
     __half* hi = reinterpret_cast<__half*>(__cvta_shared_to_generic(S.hi));
     __half* lo = reinterpret_cast<__half*>(__cvta_shared_to_generic(S.lo));
+    float* sv = reinterpret_cast<float*>(__cvta_shared_to_generic(S.sv));
     const int np4 = Kp >> 2;
     for (int i = tid; i < np4; i += THREADS) {
         float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -168,10 +201,9 @@ __device__ float stage_vector(const GemvParams& P, const Smem& S, int Kp) {
         const __half h0 = __float2half_rn(x.x), h1 = __float2half_rn(x.y), h2 = __float2half_rn(x.z), h3 = __float2half_rn(x.w);
         const __half l0 = __float2half_rn(x.x - __half2float(h0)), l1 = __float2half_rn(x.y - __half2float(h1));
         const __half l2 = __float2half_rn(x.z - __half2float(h2)), l3 = __float2half_rn(x.w - __half2float(h3));
-        // order [0,2,1,3]
         __half2* hp = reinterpret_cast<__half2*>(hi + 4 * i);
         __half2* lp = reinterpret_cast<__half2*>(lo + 4 * i);
-        hp[0] = __halves2half2(h0, h2);
+        hp[0] = __halves2half2(h0, h2);  // order [0,2,1,3]
         hp[1] = __halves2half2(h1, h3);
         lp[0] = __halves2half2(l0, l2);
         lp[1] = __halves2half2(l1, l3);
@@ -180,7 +212,7 @@ __device__ float stage_vector(const GemvParams& P, const Smem& S, int Kp) {
             s4 += __shfl_xor_sync(0xffffffffu, s4, 1);
             s4 += __shfl_xor_sync(0xffffffffu, s4, 2);
             s4 += __shfl_xor_sync(0xffffffffu, s4, 4);
-            if ((tid & 7) == 0) reinterpret_cast<float*>(__cvta_shared_to_generic(S.sv))[i >> 3] = s4;
+            if ((tid & 7) == 0) sv[i >> 3] = s4;
         }
     }
     if (tid < 8) reinterpret_cast<uint32_t*>(__cvta_shared_to_generic(S.zero))[tid] = 0u;
@@ -203,84 +235,102 @@ __device__ __forceinline__ int seg_of_tile(const GemvParams& P, int tile) {
 // ---------------------------------------------------------------------------------------------
 // The kernel.
 // ---------------------------------------------------------------------------------------------
-template <class F, int KS, int NMAT, int PRO, int EPI>
-__global__ void __launch_bounds__(THREADS, 2) gemv_kernel(const GemvParams P) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+template <class F, int NMAT, int PRO, int EPI>
+__global__ void __launch_bounds__(THREADS, 1) gemv_kernel(const GemvParams P) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     const int K = P.K;
     const int Kp = (K + 255) & ~255;
+    // [hi Kp f16][lo Kp f16][zero 32B][sv Kp/32 f32][red WARPS*32 f32][stat 64 f32][mbar WARPS*MAX_STAGES u64][ring]
     Smem S;
     S.hi = (uint32_t)__cvta_generic_to_shared(smem_raw);
     S.lo = S.hi + 2 * Kp;
     S.zero = S.lo + 2 * Kp;
     S.sv = S.zero + 32;
-    S.red = reinterpret_cast<float*>(smem_raw + 4 * Kp + 32) + (Kp >> 5);
-    S.stat = S.red + WARPS * 32;
+    float* red = reinterpret_cast<float*>(smem_raw + 4 * Kp + 32) + (Kp >> 5);
+    float* stat = red + WARPS * 32;
+    const uint32_t fixed = (uint32_t)(4 * Kp + 32 + (Kp >> 5) * 4 + WARPS * 32 * 4 + 64 * 4);
+    const uint32_t mbar_base = S.hi + fixed;
+    const uint32_t ring_base = (mbar_base + WARPS * MAX_STAGES * 8 + 127u) & ~127u;
 
+    const int warp = threadIdx.x >> 5;
     LaneCtx L;
     L.lane = threadIdx.x & 31;
     L.g = L.lane >> 2;
     L.t = L.lane & 3;
-    for (int i = 0; i < 8; i++) { L.bp[i] = 0; L.bs[i] = 0; }
+    for (int i = 0; i < 4; i++) { L.bp[i] = 0; L.bs[i] = 0; }
     F::init(L, S);
-    L.bs[7] = F::aux(K);
 
-    constexpr int GROUPS = WARPS / KS;
-    const int warp = threadIdx.x >> 5;
-    const int grp = warp / KS, wi = warp % KS;
-    const int item_stride = gridDim.x * GROUPS;
-    int item = blockIdx.x * GROUPS + grp;
-    const int nsteps = P.nsteps;
+    const int ks = P.ks, nstage = P.nstage, nsteps = P.nsteps;
+    const int groups = WARPS / ks;
+    const int grp = warp / ks, wi = warp % ks;
+    const int item_stride = gridDim.x * groups;
+    const int first_item = blockIdx.x * groups + grp;
+    const int s0 = (nsteps * wi) / ks, s1 = (nsteps * (wi + 1)) / ks;
+    const uint32_t my_mbar = mbar_base + warp * MAX_STAGES * 8;
+    const uint32_t my_ring = ring_base + warp * nstage * P.stage_stride;
 
-    typename F::Regs R0, R1;
-    const uint8_t *rowA = nullptr, *rowB = nullptr;
-    auto rows_of = [&](int it, int mat) {
-        int s = NMAT == 2 ? mat : seg_of_tile(P, it);
-        const int tile_in_seg = NMAT == 2 ? it : it - P.seg[s].tile0;
-        const uint8_t* base = P.seg[s].w + (size_t)(tile_in_seg * 16 + L.g) * P.seg[s].row_stride;
-        rowA = base;
-        rowB = base + 8 * P.seg[s].row_stride;
-    };
-    // First loads before waiting for the producer of `v`.
-    bool preloaded = false;
-    if (item < P.n_items && wi < nsteps) {
-        rows_of(item, 0);
-        F::load(R0, rowA, rowB, wi, L);
-        preloaded = true;
+    if (L.lane == 0) {
+        for (int s = 0; s < nstage; s++) mbar_init(my_mbar + 8 * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    __syncwarp();
+
+    // Producer cursor over this warp's sequence of blocks: for item, for mat, for step in [s0, s1).
+    int p_item = s1 > s0 ? first_item : P.n_items, p_mat = 0, p_step = s0, p_stage = 0;
+    auto issue = [&]() {
+        if (p_item < P.n_items) {
+            if (L.lane == 0) {
+                const int sidx = NMAT == 2 ? p_mat : seg_of_tile(P, p_item);
+                const GemvSeg& sg = P.seg[sidx];
+                const int tile = NMAT == 2 ? p_item : p_item - sg.tile0;
+                const uint8_t* src = sg.w + (size_t)tile * sg.tile_bytes + (size_t)p_step * P.step_bytes;
+                const uint32_t mb = my_mbar + 8 * p_stage;
+                mbar_expect_tx(mb, P.step_bytes);
+                bulk_g2s(my_ring + p_stage * P.stage_stride, src, P.step_bytes, mb);
+            }
+            if (++p_stage == nstage) p_stage = 0;
+            if (++p_step == s1) {
+                p_step = s0;
+                if (++p_mat == NMAT) {
+                    p_mat = 0;
+                    p_item += item_stride;
+                }
+            }
+        }
+    };
+    for (int s = 0; s < nstage; s++) issue();  // weights do not depend on the previous kernel
+
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const float inv_scale = stage_vector<PRO, F::NEED_SV>(P, S, Kp);
+    const float inv_scale = stage_vector<PRO, F::NEED_SV>(P, S, stat, Kp);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    for (; item < P.n_items; item += item_stride) {
+    int c_stage = 0;
+    uint32_t c_phase = 0;
+    bool alive = true;
+    for (int item = first_item; item < P.n_items; item += item_stride) {
         float acc[NMAT][2];
 #pragma unroll
         for (int mat = 0; mat < NMAT; mat++) {
             acc[mat][0] = 0.f;
             acc[mat][1] = 0.f;
-            rows_of(item, mat);
-            int s = wi;
-            if (s < nsteps) {
-                if (!preloaded) F::load(R0, rowA, rowB, s, L);
-                preloaded = false;
-                while (true) {
-                    if (s + KS < nsteps) F::load(R1, rowA, rowB, s + KS, L);
-                    F::compute(R0, s, L, S, acc[mat][0], acc[mat][1]);
-                    s += KS;
-                    if (s >= nsteps) break;
-                    if (s + KS < nsteps) F::load(R0, rowA, rowB, s + KS, L);
-                    F::compute(R1, s, L, S, acc[mat][0], acc[mat][1]);
-                    s += KS;
-                    if (s >= nsteps) break;
+            for (int s = s0; s < s1; s++) {
+                if (alive) alive = mbar_wait(my_mbar + 8 * c_stage, c_phase, P.err_flag);
+                if (alive) F::compute(my_ring + c_stage * P.stage_stride, s, L, S, acc[mat][0], acc[mat][1]);
+                __syncwarp();
+                if (L.lane == 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                if (alive) issue();  // refill the stage just consumed
+                if (++c_stage == nstage) {
+                    c_stage = 0;
+                    c_phase ^= 1;
                 }
             }
-            // reduce the four lanes that share a row
             acc[mat][0] += __shfl_xor_sync(0xffffffffu, acc[mat][0], 1);
             acc[mat][0] += __shfl_xor_sync(0xffffffffu, acc[mat][0], 2);
             acc[mat][1] += __shfl_xor_sync(0xffffffffu, acc[mat][1], 1);
             acc[mat][1] += __shfl_xor_sync(0xffffffffu, acc[mat][1], 2);
         }
-        // partials of this warp: red[warp][mat*16 + row]
-        float* my = S.red + warp * 32;
+        float* my = red + warp * 32;
         if (L.t == 0) {
 #pragma unroll
             for (int mat = 0; mat < NMAT; mat++) {
@@ -288,21 +338,16 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_kernel(const GemvParams P) {
                 my[mat * 16 + L.g + 8] = acc[mat][1];
             }
         }
-        if (KS == 1) {
-            __syncwarp();
-        } else if (KS == WARPS) {
-            __syncthreads();
-        } else {
-            asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(KS * 32) : "memory");
-        }
+        if (ks == 1) __syncwarp();
+        else if (ks == WARPS) __syncthreads();
+        else asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(ks * 32) : "memory");
         if (wi == 0 && L.lane < 16) {
             const int r = L.lane;
             float val[NMAT];
 #pragma unroll
             for (int mat = 0; mat < NMAT; mat++) {
                 float s = 0.f;
-#pragma unroll
-                for (int w = 0; w < KS; w++) s += S.red[(grp * KS + w) * 32 + mat * 16 + r];
+                for (int w = 0; w < ks; w++) s += red[(grp * ks + w) * 32 + mat * 16 + r];
                 val[mat] = s * inv_scale;
             }
             const int sidx = NMAT == 2 ? 0 : seg_of_tile(P, item);
@@ -347,35 +392,31 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_kernel(const GemvParams P) {
             }
         }
         // the partial buffer is reused by the next item of this group
-        if (KS == 1) {
-            __syncwarp();
-        } else if (KS == WARPS) {
-            __syncthreads();
-        } else {
-            asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(KS * 32) : "memory");
-        }
+        if (ks == 1) __syncwarp();
+        else if (ks == WARPS) __syncthreads();
+        else asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(ks * 32) : "memory");
     }
 }
 
 // Dense f32 matrix (GpuQuantMatrix::F32): one warp per row.
-__global__ void gemv_f32_kernel(float* out, const float* w, const float* v, int M, int K, long long row_stride_f) {
+__global__ void gemv_f32_kernel(float* out, const float* w, const float* v, int M, int K) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (row >= M) return;
-    const float* wr = w + (size_t)row * row_stride_f;
+    const float* wr = w + (size_t)row * K;
     float acc = 0.f;
     for (int k = lane; k < K; k += 32) acc = fmaf(wr[k], v[k], acc);
     acc = warp_sum(acc);
     if (lane == 0) out[row] = acc;
 }
 
-template <class F, int KS, int NMAT, int PRO, int EPI>
+template <class F, int NMAT, int PRO, int EPI>
 int launch_inst(slai_ctx* ctx, const GemvParams& P, int grid, size_t smem, bool pdl) {
-    auto kern = gemv_kernel<F, KS, NMAT, PRO, EPI>;
+    auto kern = gemv_kernel<F, NMAT, PRO, EPI>;
     static bool attr_done = false;  // per instantiation
     if (!attr_done) {
-        SLAI_CHECK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        SLAI_CHECK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT));
         attr_done = true;
     }
     cudaLaunchConfig_t cfg = {};
@@ -392,25 +433,10 @@ int launch_inst(slai_ctx* ctx, const GemvParams& P, int grid, size_t smem, bool 
     return SLAI_OK;
 }
 
-template <class F, int NMAT, int PRO, int EPI>
-int launch_ks(slai_ctx* ctx, const GemvParams& P, int ks, int grid_cap, size_t smem, bool pdl) {
-    auto grid_for = [&](int k) {
-        const int groups = WARPS / k;
-        int g = (P.n_items + groups - 1) / groups;
-        return g < grid_cap ? g : grid_cap;
-    };
-    switch (ks) {
-        case 1: return launch_inst<F, 1, NMAT, PRO, EPI>(ctx, P, grid_for(1), smem, pdl);
-        case 2: return launch_inst<F, 2, NMAT, PRO, EPI>(ctx, P, grid_for(2), smem, pdl);
-        case 4: return launch_inst<F, 4, NMAT, PRO, EPI>(ctx, P, grid_for(4), smem, pdl);
-        default: return launch_inst<F, 8, NMAT, PRO, EPI>(ctx, P, grid_for(8), smem, pdl);
-    }
-}
-
 template <class F>
-int launch_fmt(slai_ctx* ctx, const GemvParams& P, const GemvLaunch& L, int ks, int grid_cap, size_t smem) {
+int launch_fmt(slai_ctx* ctx, const GemvParams& P, const GemvLaunch& L, int grid, size_t smem) {
     const bool pdl = L.pdl;
-#define GO(NMAT, PRO, EPI) return launch_ks<F, NMAT, PRO, EPI>(ctx, P, ks, grid_cap, smem, pdl)
+#define GO(NMAT, PRO, EPI) return launch_inst<F, NMAT, PRO, EPI>(ctx, P, grid, smem, pdl)
     switch (L.epi) {
         case EPI_STORE:
             if (L.pro == PRO_NONE) GO(1, PRO_NONE, EPI_STORE);
@@ -454,8 +480,7 @@ int gemv_launch(slai_ctx* ctx, const GemvLaunch& L) {
         at[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = at;
         cfg.numAttrs = L.pdl ? 1 : 0;
-        SLAI_CHECK_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_f32_kernel, L.out, (const float*)L.seg[0].w, L.v, M, K,
-                                                (long long)(L.seg[0].row_stride / 4)));
+        SLAI_CHECK_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_f32_kernel, L.out, (const float*)L.seg[0].w, L.v, M, K));
         return SLAI_OK;
     }
     const int be = fmt_block_elems(L.fmt);
@@ -470,6 +495,7 @@ int gemv_launch(slai_ctx* ctx, const GemvLaunch& L) {
         P.seg[s] = L.seg[s];
         P.seg[s].tile0 = tiles;
         tiles += (L.seg[s].rows + 15) / 16;
+        SLAI_REQUIRE(ctx, ((uintptr_t)L.seg[s].w & 15) == 0, SLAI_ERR_INVALID_ARG, "gemv: matrix data must be 16-byte aligned");
     }
     const bool dual = (L.epi == EPI_SILU);
     if (dual) {
@@ -483,36 +509,58 @@ int gemv_launch(slai_ctx* ctx, const GemvLaunch& L) {
         SLAI_REQUIRE(ctx, !L.rope || L.rope_theta, SLAI_ERR_INVALID_ARG, "gemv: RoPE table missing");
     }
     P.K = K;
-    const int step = (L.fmt == SLAI_FMT_Q4_K || L.fmt == SLAI_FMT_Q5_K) ? 256 : 128;
-    P.nsteps = (K + step - 1) / step;
+    P.nsteps = (int)layout::num_steps(L.fmt, K);
+    P.step_bytes = layout::step_bytes(L.fmt);
+    P.stage_stride = (P.step_bytes + 127) & ~127;
     P.v = L.v; P.out = L.out; P.norm_w = L.norm_w; P.norm_b = L.norm_b; P.eps = L.eps;
     P.resid = L.resid; P.rope = L.rope; P.rope_theta = L.rope_theta; P.head_size = L.head_size;
     P.d_pos = L.d_pos; P.kcache = L.kcache; P.vcache = L.vcache; P.kv_f16 = (L.kv_dtype == SLAI_KV_F16);
     P.kv_pos_stride = L.kv_pos_stride; P.kv_head_stride = L.kv_head_stride;
+    P.err_flag = ctx->d_counters + 3000;
 
     const int Kp = (K + 255) & ~255;
-    const size_t smem = (size_t)4 * Kp + 32 + (size_t)(Kp / 32) * 4 + WARPS * 32 * 4 + 64 * 4;
-    SLAI_REQUIRE(ctx, smem <= 200 * 1024, SLAI_ERR_SHAPE, "gemv: K=%d needs %zu bytes of shared memory (max 204800)", K, smem);
-
-    // K split: enough warp-items to fill the machine, at least two steps per warp where possible.
-    static int ks_env = -1;
-    if (ks_env < 0) {
-        const char* e = getenv("SLAI_GEMV_KS");
+    const size_t fixed = (size_t)4 * Kp + 32 + (size_t)(Kp / 32) * 4 + WARPS * 32 * 4 + 64 * 4 + WARPS * MAX_STAGES * 8 + 128;
+    const size_t per_stage = (size_t)WARPS * P.stage_stride;
+    SLAI_REQUIRE(ctx, fixed + 2 * per_stage <= SMEM_LIMIT, SLAI_ERR_SHAPE, "gemv: K=%d does not fit in shared memory", K);
+    static int stage_env = -1, ks_env = -1;
+    if (stage_env < 0) {
+        const char* e = getenv("SLAI_GEMV_STAGES");
+        stage_env = e ? atoi(e) : 0;
+        e = getenv("SLAI_GEMV_KS");
         ks_env = e ? atoi(e) : 0;
     }
-    int ks = 8;
-    const double want = 1.5 * ctx->sm_count * 16.0 / (double)(P.n_items * (dual ? 2 : 1));
-    while (ks > 1 && ks > want) ks >>= 1;
-    while (ks > 1 && P.nsteps < ks) ks >>= 1;
-    if (ks_env == 1 || ks_env == 2 || ks_env == 4 || ks_env == 8) ks = ks_env;
-    const int ctas_per_sm = smem > 100 * 1024 ? 1 : 2;
-    const int grid_cap = ctx->sm_count * ctas_per_sm;
+    int nstage = (int)((SMEM_LIMIT - fixed) / per_stage);
+    if (nstage > 6) nstage = 6;
+    if (stage_env >= 2 && stage_env <= nstage) nstage = stage_env;
+    P.nstage = nstage;
+    const size_t smem = fixed + (size_t)nstage * per_stage;
+
+    // K split: minimise rounds x (blocks per warp-item + fixed cost of an item).
+    const int mats = dual ? 2 : 1;
+    int best_ks = 1;
+    double best_cost = 1e30;
+    for (int ks = 1; ks <= WARPS; ks *= 2) {
+        if (ks > 1 && ks > P.nsteps) break;
+        const long long slots = (long long)ctx->sm_count * (WARPS / ks);
+        const long long rounds = (P.n_items + slots - 1) / slots;
+        const double per_item = (double)((P.nsteps + ks - 1) / ks) * mats + 1.5 + 0.25 * ks;
+        const double cost = rounds * per_item;
+        if (cost < best_cost) {
+            best_cost = cost;
+            best_ks = ks;
+        }
+    }
+    if (ks_env == 1 || ks_env == 2 || ks_env == 4 || ks_env == 8 || ks_env == 16) best_ks = ks_env;
+    P.ks = best_ks;
+    const int groups = WARPS / best_ks;
+    int grid = (P.n_items + groups - 1) / groups;
+    if (grid > ctx->sm_count) grid = ctx->sm_count;
 
     switch (L.fmt) {
-        case SLAI_FMT_Q4_K: return launch_fmt<Q4K>(ctx, P, L, ks, grid_cap, smem);
-        case SLAI_FMT_Q5_K: return launch_fmt<Q5K>(ctx, P, L, ks, grid_cap, smem);
-        case SLAI_FMT_Q6_K: return launch_fmt<Q6K>(ctx, P, L, ks, grid_cap, smem);
-        case SLAI_FMT_Q8_0: return launch_fmt<Q80>(ctx, P, L, ks, grid_cap, smem);
+        case SLAI_FMT_Q4_K: return launch_fmt<Q4K>(ctx, P, L, grid, smem);
+        case SLAI_FMT_Q5_K: return launch_fmt<Q5K>(ctx, P, L, grid, smem);
+        case SLAI_FMT_Q6_K: return launch_fmt<Q6K>(ctx, P, L, grid, smem);
+        case SLAI_FMT_Q8_0: return launch_fmt<Q80>(ctx, P, L, grid, smem);
     }
     return slai_set_error(ctx, SLAI_ERR_UNSUPPORTED_FORMAT, "gemv: format %d has no kernel", L.fmt);
 }

@@ -1,6 +1,7 @@
-// Per-format step loaders and MMA bodies of the dequant-GEMV kernel (see gemv.cu for the kernel shape
-// and gemv_frag.cuh for the fragment mapping).  The functions are written against a small set of
-// primitives (16-byte global / shared loads, the m16n8k16 MMA) that have a device implementation in PTX
+// Per-format MMA bodies of the dequant-GEMV kernel (see gemv.cu for the kernel shape, layout.cuh for the
+// tile-step blocks they read from shared memory and gemv_frag.cuh for the fragment mapping).  The functions
+// are written against a small set of primitives (shared loads, the m16n8k16 MMA) that have a device
+// implementation in PTX
 // and a host implementation in which 32 CPU threads play the lanes of a warp, so the very same source is
 // exercised by the CPU test-suite (tests/host_emul.cpp) before it ever runs on a GPU.
 #pragma once
@@ -69,6 +70,17 @@ SLAI_HD float lds_f32(uint32_t addr) {
     return r;
 #endif
 }
+SLAI_HD uint32_t lds_u16(uint32_t addr) {
+#ifdef __CUDA_ARCH__
+    unsigned short r;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(r) : "r"(addr));
+    return r;
+#else
+    unsigned short r;
+    memcpy(&r, hostemu::warp->smem + addr, 2);
+    return r;
+#endif
+}
 SLAI_HD float h2f(uint32_t bits16) {
 #ifdef __CUDA_ARCH__
     return __half2float(__ushort_as_half((unsigned short)bits16));
@@ -129,30 +141,29 @@ using namespace frag;
 
 SLAI_HD uint32_t w4(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
 
-// Shared-memory layout (dynamic): [hi: Kp halves][lo: Kp halves][zero: 16 halves][sv: Kp/32 floats]
-// [red: WARPS * 32 floats][stat: 64 floats]
+// Shared-space byte addresses of the staged activation vector: f16 hi / lo arrays in [0,2,1,3] order, 32
+// bytes of zeros, and per-32-element sums of the scaled activations.
 struct Smem {
-    uint32_t hi, lo, zero, sv;  // shared-space byte addresses
-    float* red;
-    float* stat;
+    uint32_t hi, lo, zero, sv;
 };
 
-// ---------------------------------------------------------------------------------------------
-// Format traits: per-step register payload, loader and MMA body.
-// ---------------------------------------------------------------------------------------------
 struct LaneCtx {
     int lane, g, t;
-    // B-operand source addresses (shared space, bytes) and per-step strides
-    uint32_t bp[8];
-    uint32_t bs[8];
+    // B-operand source addresses (shared space, bytes) and their per-step strides
+    uint32_t bp[4];
+    uint32_t bs[4];
 };
 
+// Every format provides
+//   STEP      elements of K per tile-step block
+//   init      the lane's B-operand sources
+//   compute   one tile-step block at shared address `blk` (K step number `step`): accumulates rows g and g+8
 // ---- Q4_K ----------------------------------------------------------------------------------
 struct Q4K {
+    static constexpr int FMT = 12;
     static constexpr int STEP = 256;
+    static constexpr int QOFF = 256;  // start of the lane-ordered quant regions
     static constexpr bool NEED_SV = true;
-    SLAI_HD static uint32_t aux(int) { return 0u; }
-    struct Regs { uint4 hA, hB, qA[2], qB[2]; };
     SLAI_HD static void init(LaneCtx& L, const Smem& S) {
         for (int ci = 0; ci < 2; ci++)
             for (int slot = 0; slot < 2; slot++) {
@@ -162,31 +173,37 @@ struct Q4K {
                 L.bs[i] = b.off < 0 ? 0 : 2 * STEP;
             }
     }
-    SLAI_HD static void load(Regs& r, const uint8_t* rowA, const uint8_t* rowB, int step, const LaneCtx& L) {
-        const uint8_t* a = rowA + (size_t)step * 144;
-        const uint8_t* b = rowB + (size_t)step * 144;
-        r.hA = prim::ldg16(a);
-        r.hB = prim::ldg16(b);
-        r.qA[0] = prim::ldg16(a + 16 + 16 * L.t);
-        r.qB[0] = prim::ldg16(b + 16 + 16 * L.t);
-        r.qA[1] = prim::ldg16(a + 80 + 16 * L.t);
-        r.qB[1] = prim::ldg16(b + 80 + 16 * L.t);
-    }
-    SLAI_HD static void compute(const Regs& r, int step, const LaneCtx& L, const Smem& S, float& accA, float& accB) {
-        const float dA = prim::h2f(r.hA.x & 0xFFFF), mnA = prim::h2f(r.hA.x >> 16);
-        const float dB = prim::h2f(r.hB.x & 0xFFFF), mnB = prim::h2f(r.hB.x >> 16);
+    template <bool FIVE>
+    SLAI_HD static void compute_k(uint32_t blk, int step, const LaneCtx& L, const Smem& S, float& accA, float& accB) {
+        const uint4 hA = prim::lds16(blk + 16 * L.g), hB = prim::lds16(blk + 16 * (L.g + 8));
+        const float dA = prim::h2f(hA.x & 0xFFFF), mnA = prim::h2f(hA.x >> 16);
+        const float dB = prim::h2f(hB.x & 0xFFFF), mnB = prim::h2f(hB.x >> 16);
+        uint4 hqA = hA, hqB = hB;
+        if (FIVE) {
+            hqA = prim::lds16(blk + 256 + 32 * L.g + 16 * (L.t & 1));
+            hqB = prim::lds16(blk + 256 + 32 * (L.g + 8) + 16 * (L.t & 1));
+        }
+        const uint32_t q0 = blk + (FIVE ? 768 : 256) + 16 * L.lane;
 #pragma unroll
         for (int ci = 0; ci < 2; ci++) {
+            const uint4 qA = prim::lds16(q0 + (ci * 2) * 512), qB = prim::lds16(q0 + (ci * 2 + 1) * 512);
             const uint32_t p0 = L.bp[ci * 2] + step * L.bs[ci * 2], p1 = L.bp[ci * 2 + 1] + step * L.bs[ci * 2 + 1];
             const uint4 b0a = prim::lds16(p0), b0b = prim::lds16(p0 + 16), b1a = prim::lds16(p1), b1b = prim::lds16(p1 + 16);
+            const int sh = 2 * ((L.t >> 1) + 2 * ci);  // Q5_K: 2 * (64-element group index)
             float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int w = 0; w < 4; w++) {
+                const uint32_t hwA = FIVE ? (w4(hqA, w) >> sh) : 0u, hwB = FIVE ? (w4(hqB, w) >> sh) : 0u;
 #pragma unroll
                 for (int sel = 0; sel < 2; sel++) {
                     uint32_t a0, a1, a2, a3;
-                    q4_pair(w4(r.qA[ci], w), sel, a0, a2);
-                    q4_pair(w4(r.qB[ci], w), sel, a1, a3);
+                    if (FIVE) {
+                        q5_pair(w4(qA, w), hwA, sel, a0, a2);
+                        q5_pair(w4(qB, w), hwB, sel, a1, a3);
+                    } else {
+                        q4_pair(w4(qA, w), sel, a0, a2);
+                        q4_pair(w4(qB, w), sel, a1, a3);
+                    }
                     const int i = 2 * w + sel;
                     prim::mma16816(c, a0, a1, a2, a3, i < 4 ? w4(b0a, i) : w4(b0b, i - 4), i < 4 ? w4(b1a, i) : w4(b1b, i - 4));
                 }
@@ -194,137 +211,90 @@ struct Q4K {
             const int j = 4 * ci + L.t;
             const float sv = prim::lds_f32(S.sv + 4 * (step * 8 + j));
             uint32_t sc, m;
-            scale_min_k4(j, r.hA.y, r.hA.z, r.hA.w, sc, m);
+            scale_min_k4(j, hA.y, hA.z, hA.w, sc, m);
             accA = prim::fma(dA * (float)sc, c[0] + c[1], accA);
             accA = prim::fma(-(mnA * (float)m), sv, accA);
-            scale_min_k4(j, r.hB.y, r.hB.z, r.hB.w, sc, m);
+            scale_min_k4(j, hB.y, hB.z, hB.w, sc, m);
             accB = prim::fma(dB * (float)sc, c[2] + c[3], accB);
             accB = prim::fma(-(mnB * (float)m), sv, accB);
         }
+    }
+    SLAI_HD static void compute(uint32_t blk, int step, const LaneCtx& L, const Smem& S, float& accA, float& accB) {
+        compute_k<false>(blk, step, L, S, accA, accB);
     }
 };
 
 // ---- Q5_K ----------------------------------------------------------------------------------
 struct Q5K {
+    static constexpr int FMT = 13;
     static constexpr int STEP = 256;
     static constexpr bool NEED_SV = true;
-    SLAI_HD static uint32_t aux(int) { return 0u; }
-    struct Regs { uint4 hA, hB, hqA, hqB, qA[2], qB[2]; };
     SLAI_HD static void init(LaneCtx& L, const Smem& S) { Q4K::init(L, S); }
-    SLAI_HD static void load(Regs& r, const uint8_t* rowA, const uint8_t* rowB, int step, const LaneCtx& L) {
-        const uint8_t* a = rowA + (size_t)step * 176;
-        const uint8_t* b = rowB + (size_t)step * 176;
-        r.hA = prim::ldg16(a);
-        r.hB = prim::ldg16(b);
-        r.hqA = prim::ldg16(a + 16 + 16 * (L.t & 1));
-        r.hqB = prim::ldg16(b + 16 + 16 * (L.t & 1));
-        r.qA[0] = prim::ldg16(a + 48 + 16 * L.t);
-        r.qB[0] = prim::ldg16(b + 48 + 16 * L.t);
-        r.qA[1] = prim::ldg16(a + 112 + 16 * L.t);
-        r.qB[1] = prim::ldg16(b + 112 + 16 * L.t);
-    }
-    SLAI_HD static void compute(const Regs& r, int step, const LaneCtx& L, const Smem& S, float& accA, float& accB) {
-        const float dA = prim::h2f(r.hA.x & 0xFFFF), mnA = prim::h2f(r.hA.x >> 16);
-        const float dB = prim::h2f(r.hB.x & 0xFFFF), mnB = prim::h2f(r.hB.x >> 16);
-#pragma unroll
-        for (int ci = 0; ci < 2; ci++) {
-            const uint32_t p0 = L.bp[ci * 2] + step * L.bs[ci * 2], p1 = L.bp[ci * 2 + 1] + step * L.bs[ci * 2 + 1];
-            const uint4 b0a = prim::lds16(p0), b0b = prim::lds16(p0 + 16), b1a = prim::lds16(p1), b1b = prim::lds16(p1 + 16);
-            const int sh = 2 * ((L.t >> 1) + 2 * ci);  // 2 * (64-element group index)
-            float c[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int w = 0; w < 4; w++) {
-                const uint32_t hwA = w4(r.hqA, w) >> sh, hwB = w4(r.hqB, w) >> sh;
-#pragma unroll
-                for (int sel = 0; sel < 2; sel++) {
-                    uint32_t a0, a1, a2, a3;
-                    q5_pair(w4(r.qA[ci], w), hwA, sel, a0, a2);
-                    q5_pair(w4(r.qB[ci], w), hwB, sel, a1, a3);
-                    const int i = 2 * w + sel;
-                    prim::mma16816(c, a0, a1, a2, a3, i < 4 ? w4(b0a, i) : w4(b0b, i - 4), i < 4 ? w4(b1a, i) : w4(b1b, i - 4));
-                }
-            }
-            const int j = 4 * ci + L.t;
-            const float sv = prim::lds_f32(S.sv + 4 * (step * 8 + j));
-            uint32_t sc, m;
-            scale_min_k4(j, r.hA.y, r.hA.z, r.hA.w, sc, m);
-            accA = prim::fma(dA * (float)sc, c[0] + c[1], accA);
-            accA = prim::fma(-(mnA * (float)m), sv, accA);
-            scale_min_k4(j, r.hB.y, r.hB.z, r.hB.w, sc, m);
-            accB = prim::fma(dB * (float)sc, c[2] + c[3], accB);
-            accB = prim::fma(-(mnB * (float)m), sv, accB);
-        }
+    SLAI_HD static void compute(uint32_t blk, int step, const LaneCtx& L, const Smem& S, float& accA, float& accB) {
+        Q4K::compute_k<true>(blk, step, L, S, accA, accB);
     }
 };
 
-// ---- Q6_K (row planes: ql | qh | scales | d), one step = half a super-block (128 elements) ---
+// ---- Q6_K: two halves of 128 elements per block ----------------------------------------------
 struct Q6K {
-    static constexpr int STEP = 128;
+    static constexpr int FMT = 14;
+    static constexpr int STEP = 256;
     static constexpr bool NEED_SV = false;
-    SLAI_HD static uint32_t aux(int K) { return (uint32_t)(K >> 8); }  // super-blocks per row
-    struct Regs { uint4 qlA, qlB, qhA, qhB; uint32_t scA, scB, dA, dB; };
     SLAI_HD static void init(LaneCtx& L, const Smem& S) {
         for (int slot = 0; slot < 2; slot++) {
             const int off = bsel_q6(L.lane, slot);
             L.bp[slot * 2 + 0] = off < 0 ? S.zero : S.hi + 2 * off;
             L.bp[slot * 2 + 1] = off < 0 ? S.zero : S.lo + 2 * off;
-            L.bs[slot * 2 + 0] = L.bs[slot * 2 + 1] = off < 0 ? 0 : 2 * STEP;
+            L.bs[slot * 2 + 0] = L.bs[slot * 2 + 1] = off < 0 ? 0 : 2 * 128;  // per half
         }
     }
-    // nb = super-blocks per row (plane offsets depend on it); passed through L.bs[7]
-    SLAI_HD static void load(Regs& r, const uint8_t* rowA, const uint8_t* rowB, int step, const LaneCtx& L) {
-        const int nb = (int)L.bs[7];
-        const size_t oql = (size_t)step * 64 + 16 * L.t;                            // 64 ql bytes per half
-        const size_t oqh = (size_t)nb * 128 + (size_t)step * 32 + 16 * (L.t & 1);   // 32 qh bytes per half
-        const size_t osc = (size_t)nb * 192 + (size_t)step * 8 + 2 * L.t;           // 8 scales per half
-        const size_t od = (size_t)nb * 208 + (size_t)(step >> 1) * 2;
-        r.qlA = prim::ldg16(rowA + oql);
-        r.qlB = prim::ldg16(rowB + oql);
-        r.qhA = prim::ldg16(rowA + oqh);
-        r.qhB = prim::ldg16(rowB + oqh);
-        r.scA = prim::ldg2(rowA + osc);
-        r.scB = prim::ldg2(rowB + osc);
-        r.dA = prim::ldg2(rowA + od);
-        r.dB = prim::ldg2(rowB + od);
-    }
-    SLAI_HD static void compute(const Regs& r, int step, const LaneCtx& L, const Smem& S, float& accA, float& accB) {
-        const uint32_t p0h = L.bp[0] + step * L.bs[0], p0l = L.bp[1] + step * L.bs[1];
-        const uint32_t p1h = L.bp[2] + step * L.bs[2], p1l = L.bp[3] + step * L.bs[3];
+    SLAI_HD static void compute(uint32_t blk, int step, const LaneCtx& L, const Smem& S, float& accA, float& accB) {
+        const float dA = prim::h2f(prim::lds_u16(blk + 3328 + 2 * L.g)), dB = prim::h2f(prim::lds_u16(blk + 3328 + 2 * (L.g + 8)));
         const int sh = 2 * (L.t >> 1);
-        float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int hf = 0; hf < 2; hf++) {  // two groups of 4 MMAs: words 0-1, words 2-3
-            const uint4 b0h = prim::lds16(p0h + 16 * hf), b0l = prim::lds16(p0l + 16 * hf);
-            const uint4 b1h = prim::lds16(p1h + 16 * hf), b1l = prim::lds16(p1l + 16 * hf);
+        for (int h = 0; h < 2; h++) {
+            const int hstep = 2 * step + h;
+            const uint4 qlA = prim::lds16(blk + (h * 2) * 512 + 16 * L.lane), qlB = prim::lds16(blk + (h * 2 + 1) * 512 + 16 * L.lane);
+            const uint4 qhA = prim::lds16(blk + 2048 + h * 512 + 32 * L.g + 16 * (L.t & 1));
+            const uint4 qhB = prim::lds16(blk + 2048 + h * 512 + 32 * (L.g + 8) + 16 * (L.t & 1));
+            const uint32_t scA = prim::lds_u16(blk + 3072 + 16 * L.g + 8 * h + 2 * L.t);
+            const uint32_t scB = prim::lds_u16(blk + 3072 + 16 * (L.g + 8) + 8 * h + 2 * L.t);
+            const uint32_t p0h = L.bp[0] + hstep * L.bs[0], p0l = L.bp[1] + hstep * L.bs[1];
+            const uint32_t p1h = L.bp[2] + hstep * L.bs[2], p1l = L.bp[3] + hstep * L.bs[3];
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int ww = 0; ww < 2; ww++) {
-                const int w = 2 * hf + ww;
-                const uint32_t hwA = w4(r.qhA, w) >> sh, hwB = w4(r.qhB, w) >> sh;
+            for (int hf = 0; hf < 2; hf++) {  // two groups of 4 MMAs: words 0-1, words 2-3
+                const uint4 b0h = prim::lds16(p0h + 16 * hf), b0l = prim::lds16(p0l + 16 * hf);
+                const uint4 b1h = prim::lds16(p1h + 16 * hf), b1l = prim::lds16(p1l + 16 * hf);
 #pragma unroll
-                for (int sel = 0; sel < 2; sel++) {
-                    uint32_t a0, a1, a2, a3;
-                    q6_pair(w4(r.qlA, w), hwA, sel, a0, a2);
-                    q6_pair(w4(r.qlB, w), hwB, sel, a1, a3);
-                    const int i = 2 * ww + sel;
-                    prim::mma16816(c, a0, a1, a2, a3, w4(b0h, i), w4(b1h, i));
-                    prim::mma16816(c, a0, a1, a2, a3, w4(b0l, i), w4(b1l, i));
+                for (int ww = 0; ww < 2; ww++) {
+                    const int w = 2 * hf + ww;
+                    const uint32_t hwA = w4(qhA, w) >> sh, hwB = w4(qhB, w) >> sh;
+#pragma unroll
+                    for (int sel = 0; sel < 2; sel++) {
+                        uint32_t a0, a1, a2, a3;
+                        q6_pair(w4(qlA, w), hwA, sel, a0, a2);
+                        q6_pair(w4(qlB, w), hwB, sel, a1, a3);
+                        const int i = 2 * ww + sel;
+                        prim::mma16816(c, a0, a1, a2, a3, w4(b0h, i), w4(b1h, i));
+                        prim::mma16816(c, a0, a1, a2, a3, w4(b0l, i), w4(b1l, i));
+                    }
                 }
             }
+            // lane holds columns 2t, 2t+1 = sub-blocks 2t, 2t+1 of this half; scales are int8
+            const float s0A = (float)(int)(signed char)(scA & 0xFF), s1A = (float)(int)(signed char)(scA >> 8);
+            const float s0B = (float)(int)(signed char)(scB & 0xFF), s1B = (float)(int)(signed char)(scB >> 8);
+            accA = prim::fma(dA, prim::fma(s0A, c[0], s1A * c[1]), accA);
+            accB = prim::fma(dB, prim::fma(s0B, c[2], s1B * c[3]), accB);
         }
-        // lane holds columns 2t, 2t+1 = sub-blocks 2t, 2t+1 of this half; scales are int8
-        const float s0A = (float)(int)(signed char)(r.scA & 0xFF), s1A = (float)(int)(signed char)(r.scA >> 8);
-        const float s0B = (float)(int)(signed char)(r.scB & 0xFF), s1B = (float)(int)(signed char)(r.scB >> 8);
-        accA = prim::fma(prim::h2f(r.dA), prim::fma(s0A, c[0], s1A * c[1]), accA);
-        accB = prim::fma(prim::h2f(r.dB), prim::fma(s0B, c[2], s1B * c[3]), accB);
     }
 };
 
-// ---- Q8_0 (row planes: K int8 | K/32 f16 scales), one step = 128 elements (4 blocks) -------
+// ---- Q8_0: a block is 4 GGUF blocks (128 values) ---------------------------------------------
 struct Q80 {
+    static constexpr int FMT = 8;
     static constexpr int STEP = 128;
     static constexpr bool NEED_SV = false;
-    SLAI_HD static uint32_t aux(int K) { return (uint32_t)K; }
-    struct Regs { uint4 qA[2], qB[2]; uint32_t sA, sB; };
     SLAI_HD static void init(LaneCtx& L, const Smem& S) {
         for (int ci = 0; ci < 2; ci++) {
             const BSel b = bsel_q8(L.lane, ci);
@@ -332,39 +302,25 @@ struct Q80 {
             L.bs[ci] = b.off < 0 ? 0 : 2 * STEP;
         }
     }
-    // K passed through L.bs[7] (offset of the scale plane, and the bound for partial steps)
-    SLAI_HD static void load(Regs& r, const uint8_t* rowA, const uint8_t* rowB, int step, const LaneCtx& L) {
-        const int K = (int)L.bs[7];
-        const int e0 = step * 128 + 16 * L.t, e1 = e0 + 64;
-        const uint4 z = make_uint4(0x0, 0x0, 0x0, 0x0);
-        r.qA[0] = e0 < K ? prim::ldg16(rowA + e0) : z;
-        r.qB[0] = e0 < K ? prim::ldg16(rowB + e0) : z;
-        r.qA[1] = e1 < K ? prim::ldg16(rowA + e1) : z;
-        r.qB[1] = e1 < K ? prim::ldg16(rowB + e1) : z;
-        const int blk = step * 4 + L.t;
-        const bool ok = blk * 32 < K;
-        r.sA = ok ? prim::ldg2(rowA + K + 2 * blk) : 0;
-        r.sB = ok ? prim::ldg2(rowB + K + 2 * blk) : 0;
-    }
-    SLAI_HD static void compute(const Regs& r, int step, const LaneCtx& L, const Smem& S, float& accA, float& accB) {
+    SLAI_HD static void compute(uint32_t blk, int step, const LaneCtx& L, const Smem& S, float& accA, float& accB) {
+        const float sA = prim::h2f(prim::lds_u16(blk + 8 * L.g + 2 * L.t)), sB = prim::h2f(prim::lds_u16(blk + 8 * (L.g + 8) + 2 * L.t));
         float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int ci = 0; ci < 2; ci++) {
+            const uint4 qA = prim::lds16(blk + 128 + (ci * 2) * 512 + 16 * L.lane), qB = prim::lds16(blk + 128 + (ci * 2 + 1) * 512 + 16 * L.lane);
             const uint32_t p = L.bp[ci] + step * L.bs[ci];
             const uint4 ba = prim::lds16(p), bb = prim::lds16(p + 16);
 #pragma unroll
             for (int w = 0; w < 4; w++) {
                 uint32_t a0, a1, a2, a3;
-                q8_pair(w4(r.qA[ci], w), a0, a2);
-                q8_pair(w4(r.qB[ci], w), a1, a3);
-                prim::mma16816(c, a0, a1, a2, a3, w < 2 ? w4(ba, 2 * w) : w4(bb, 2 * w - 4),
-                         w < 2 ? w4(ba, 2 * w + 1) : w4(bb, 2 * w - 3));
+                q8_pair(w4(qA, w), a0, a2);
+                q8_pair(w4(qB, w), a1, a3);
+                prim::mma16816(c, a0, a1, a2, a3, w < 2 ? w4(ba, 2 * w) : w4(bb, 2 * w - 4), w < 2 ? w4(ba, 2 * w + 1) : w4(bb, 2 * w - 3));
             }
         }
-        accA = prim::fma(prim::h2f(r.sA), c[0] + c[1], accA);
-        accB = prim::fma(prim::h2f(r.sB), c[2] + c[3], accB);
+        accA = prim::fma(sA, c[0] + c[1], accA);
+        accB = prim::fma(sB, c[2] + c[3], accB);
     }
 };
-
 
 }  // namespace gemvfmt

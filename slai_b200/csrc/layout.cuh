@@ -1,4 +1,26 @@
-// Device layout of quantized matrices (see common.cuh) and the per-block repacking from GGUF order.
+// Device layout of quantized matrices, and the placement of GGUF blocks into it.
+//
+// A matrix is stored tile-major for streaming: rows are grouped into tiles of 16, the K dimension into
+// steps (256 elements; 128 for Q8_0), and the packed data of one (tile, step) is one contiguous,
+// 16-byte aligned "tile-step block":
+//
+//     data = [tile 0][tile 1]...      tile = [step 0][step 1]...      step = SB bytes (below)
+//
+// so the 16 rows x K-range handled by one warp is a single contiguous byte range that a bulk asynchronous
+// copy brings into shared memory, and inside a block the 16-byte chunks are ordered so that the 32 lanes
+// of a warp read consecutive chunks (no bank conflicts).  The byte count equals the GGUF file's (plus zero
+// padding of the last tile / last Q8_0 step).
+//
+//   lane = 4*g + t,  g = row & 7,  ab = row >> 3 (rows 0-7 feed MMA rows g, rows 8-15 feed rows g+8)
+//
+//   Q4_K  (2304 B): [hdr 16 x 16B: d,dmin,scales] [q(ci,ab): 32 lanes x 16B] for ci = 0,1 / ab = 0,1
+//                   lane (g,t) of q(ci,ab) holds qs bytes 16*(4ci+t) .. +15 of row g + 8ab
+//   Q5_K  (2816 B): [hdr 16 x 16B] [qh 16 x 32B] [q(ci,ab) as Q4_K]
+//   Q6_K  (3360 B): [ql(h,ab): 32 lanes x 16B, h = 0,1] [qh(h): 16 rows x 32B] [scales 16 x 16B] [d 16 x 2B]
+//                   lane (g,t) of ql(h,ab) holds ql bytes 64h + 16t .. +15 of row g + 8ab
+//   Q8_0  (2176 B): [scales 16 rows x 4 x f16] [q(ci,ab): 32 lanes x 16B]; a step is 4 blocks (128 values),
+//                   lane (g,t) of q(ci,ab) holds the int8 values 64ci + 16t .. +15 of the step
+//   F32           : dense row-major (no tiling).
 #pragma once
 #include <stdint.h>
 #include <string.h>
@@ -6,36 +28,61 @@
 
 namespace layout {
 
-SLAI_HD int64_t round16(int64_t x) { return (x + 15) & ~(int64_t)15; }
-
-// Bytes between consecutive rows of the device layout.
-SLAI_HD int64_t row_stride(int fmt, int64_t K) {
+SLAI_HD int step_elems(int fmt) { return fmt == 8 ? 128 : 256; }
+SLAI_HD int step_bytes(int fmt) {
     switch (fmt) {
-        case 0: return K * 4;                         // F32
-        case 8: return round16(K + K / 16);           // Q8_0: K int8 + K/32 f16
-        case 12: return K / 256 * 144;                // Q4_K (file layout)
-        case 13: return K / 256 * 176;                // Q5_K (file layout)
-        case 14: return round16(K / 256 * 210);       // Q6_K planes
+        case 8: return 2176;
+        case 12: return 2304;
+        case 13: return 2816;
+        case 14: return 3360;
     }
     return 0;
 }
+SLAI_HD int64_t num_steps(int fmt, int64_t K) { return (K + step_elems(fmt) - 1) / step_elems(fmt); }
+SLAI_HD int64_t num_tiles(int64_t rows) { return (rows + 15) / 16; }
+// Bytes of a matrix with `rows` rows (padded to whole tiles).
+SLAI_HD int64_t matrix_bytes(int fmt, int64_t rows, int64_t K) {
+    if (fmt == 0) return rows * K * 4;
+    return num_tiles(rows) * num_steps(fmt, K) * step_bytes(fmt);
+}
+SLAI_HD int64_t tile_bytes(int fmt, int64_t K) { return num_steps(fmt, K) * step_bytes(fmt); }
 
-// Copy GGUF block number `blk` of a row (raw bytes at `src`) to its place in the device row `dst`.
-SLAI_HD void repack_block(int fmt, const uint8_t* src, uint8_t* dst, int64_t blk, int64_t K) {
-    if (fmt == 8) {  // [f16 scale][32 x int8]  ->  quant plane, scale plane
-        for (int i = 0; i < 32; i++) dst[blk * 32 + i] = src[2 + i];
-        dst[K + 2 * blk] = src[0];
-        dst[K + 2 * blk + 1] = src[1];
-    } else if (fmt == 14) {  // [ql 128][qh 64][scales 16][d 2]  ->  four planes
-        const int64_t nb = K / 256;
-        for (int i = 0; i < 128; i++) dst[blk * 128 + i] = src[i];
-        for (int i = 0; i < 64; i++) dst[nb * 128 + blk * 64 + i] = src[128 + i];
-        for (int i = 0; i < 16; i++) dst[nb * 192 + blk * 16 + i] = src[192 + i];
-        dst[nb * 208 + blk * 2] = src[208];
-        dst[nb * 208 + blk * 2 + 1] = src[209];
-    } else {
-        const int bb = fmt == 12 ? 144 : fmt == 13 ? 176 : 4;
-        for (int i = 0; i < bb; i++) dst[blk * bb + i] = src[i];
+// Offset, inside a tile-step block, of byte `idx` of the packed quant array (qs / ql / int8 values of the
+// step) of row r.  The array is cut into 16-byte chunks c = idx/16; chunk c = 4*ci + t goes to lane 4g+t of
+// the lane-ordered region (ci, ab).
+SLAI_HD int qbyte_off(int region0, int r, int idx) {
+    const int c = idx >> 4, ci = c >> 2, t = c & 3, g = r & 7, ab = r >> 3;
+    return region0 + (ci * 2 + ab) * 512 + 16 * (4 * g + t) + (idx & 15);
+}
+
+// Copy GGUF block number `blk` of row `row` (raw bytes at `src`) to its place in the tile-major matrix.
+SLAI_HD void place_block(int fmt, const uint8_t* src, uint8_t* data, int64_t row, int64_t blk, int64_t K) {
+    const int64_t tile = row >> 4;
+    const int r = (int)(row & 15);
+    const int64_t ns = num_steps(fmt, K);
+    if (fmt == 8) {
+        const int64_t step = blk >> 2;
+        const int b = (int)(blk & 3);
+        uint8_t* d = data + (tile * ns + step) * 2176;
+        d[8 * r + 2 * b] = src[0];
+        d[8 * r + 2 * b + 1] = src[1];
+        for (int i = 0; i < 32; i++) d[qbyte_off(128, r, 32 * b + i)] = src[2 + i];
+        return;
+    }
+    uint8_t* d = data + (tile * ns + blk) * step_bytes(fmt);
+    if (fmt == 12) {
+        for (int i = 0; i < 16; i++) d[16 * r + i] = src[i];
+        for (int i = 0; i < 128; i++) d[qbyte_off(256, r, i)] = src[16 + i];
+    } else if (fmt == 13) {
+        for (int i = 0; i < 16; i++) d[16 * r + i] = src[i];
+        for (int i = 0; i < 32; i++) d[256 + 32 * r + i] = src[16 + i];
+        for (int i = 0; i < 128; i++) d[qbyte_off(768, r, i)] = src[48 + i];
+    } else if (fmt == 14) {
+        for (int i = 0; i < 128; i++) d[qbyte_off(0, r, i)] = src[i];  // chunk c = 4h + t, h = ql half
+        for (int i = 0; i < 64; i++) d[2048 + (i >> 5) * 512 + 32 * r + (i & 31)] = src[128 + i];
+        for (int i = 0; i < 16; i++) d[3072 + 16 * r + i] = src[192 + i];
+        d[3328 + 2 * r] = src[208];
+        d[3328 + 2 * r + 1] = src[209];
     }
 }
 

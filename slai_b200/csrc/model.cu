@@ -46,9 +46,9 @@ void destroy_graphs(GraphSet& g) {
 }
 
 GemvSeg seg_of(const slai_qmatrix* m, int row0, int rows, const float* bias, int out_off, int role) {
-    GemvSeg s;
-    s.w = m->data + (size_t)row0 * m->row_stride;
-    s.row_stride = m->row_stride;
+    GemvSeg s;  // row0 is a multiple of 16 (checked where fused matrices are attached)
+    s.w = m->fmt == SLAI_FMT_F32 ? m->data + (size_t)row0 * m->tile_bytes : m->data + (size_t)(row0 / 16) * m->tile_bytes;
+    s.tile_bytes = m->tile_bytes;
     s.rows = rows;
     s.bias = bias;
     s.out_off = out_off;
@@ -346,7 +346,7 @@ static int llama_set_f32_impl(slai_llama* m, int id, int layer, const float* dat
         int rc = copy_f32(ctx, &m->token_embd, data, n, dev);
         if (rc) return rc;
         m->embd_as_matrix.ctx = ctx; m->embd_as_matrix.fmt = SLAI_FMT_F32; m->embd_as_matrix.nrows = c.vocab_size;
-        m->embd_as_matrix.ncols = c.dim; m->embd_as_matrix.row_stride = (int64_t)c.dim * 4;
+        m->embd_as_matrix.ncols = c.dim; m->embd_as_matrix.tile_bytes = (int64_t)c.dim * 4;
         m->embd_as_matrix.data = (uint8_t*)m->token_embd; m->embd_as_matrix.owns = false;
         return SLAI_OK;
     }
@@ -645,7 +645,11 @@ SLAI_API int slai_gpt2_set_matrix(slai_gpt2* m, int id, int layer, const slai_qm
     SLAI_REQUIRE(ctx, layer >= 0 && layer < c.n_layer, SLAI_ERR_INVALID_ARG, "gpt2: layer %d out of range", layer);
     Gpt2Layer& l = m->layers[layer];
     switch (id) {
-        case SLAI_G_W_QKV: SLAI_REQUIRE(ctx, shape_is(3 * c.n_embd, c.n_embd), SLAI_ERR_SHAPE, "gpt2: attn_qkv must be 3E x E"); l.w_qkv = w; break;
+        case SLAI_G_W_QKV:
+            SLAI_REQUIRE(ctx, shape_is(3 * c.n_embd, c.n_embd), SLAI_ERR_SHAPE, "gpt2: attn_qkv must be 3E x E");
+            SLAI_REQUIRE(ctx, c.n_embd % 16 == 0, SLAI_ERR_SHAPE, "gpt2: n_embd must be a multiple of 16 (q/k/v rows start on tile boundaries)");
+            l.w_qkv = w;
+            break;
         case SLAI_G_W_PROJ: SLAI_REQUIRE(ctx, shape_is(c.n_embd, c.n_embd), SLAI_ERR_SHAPE, "gpt2: attn_output must be E x E"); l.w_proj = w; break;
         case SLAI_G_W_FC: SLAI_REQUIRE(ctx, shape_is(c.ff_len, c.n_embd), SLAI_ERR_SHAPE, "gpt2: ffn_up must be ff x E"); l.w_fc = w; break;
         case SLAI_G_W_FCPROJ: SLAI_REQUIRE(ctx, shape_is(c.n_embd, c.ff_len), SLAI_ERR_SHAPE, "gpt2: ffn_down must be E x ff"); l.w_fcproj = w; break;

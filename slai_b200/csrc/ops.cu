@@ -157,63 +157,64 @@ SLAI_API int slai_timer_stop(slai_ctx* ctx, float* ms) {
 // ------------------------------------------------------------------------------------------------
 namespace {
 
-__global__ void repack_kernel(int fmt, const uint8_t* __restrict__ raw, uint8_t* __restrict__ dst, long long nrows,
-                              long long nbk, long long K, int bb, long long row_stride) {
+__global__ void place_kernel(int fmt, const uint8_t* __restrict__ raw, uint8_t* __restrict__ dst, long long nrows, long long nbk,
+                             long long K, int bb) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= nrows * nbk) return;
-    const long long r = i / nbk, b = i % nbk;
-    layout::repack_block(fmt, raw + (size_t)i * bb, dst + (size_t)r * row_stride, b, K);
+    layout::place_block(fmt, raw + (size_t)i * bb, dst, i / nbk, i % nbk, K);
 }
 
 __device__ __forceinline__ float dev_h2f(unsigned int bits) { return __half2float(__ushort_as_half((unsigned short)bits)); }
 
-// One dequantised element, with the reference's rounding sequence (no FMA contraction):
+// One dequantised element, read from the tile-major layout, with the reference's rounding sequence (no FMA
+// contraction):
 //   Q8_0: q * scale                         quantization.rs:38-41
 //   Q4_K/Q5_K: (d*sc)*q - (dmin*m)          quantization.rs:357-371, 288-307
 //   Q6_K: (d*scale)*q                       quantization.rs:233-236
-__device__ float dequant_elem(int fmt, const uint8_t* row, long long K, long long k) {
+__device__ float dequant_elem(int fmt, const uint8_t* data, long long K, long long row, long long k) {
+    const long long ns = layout::num_steps(fmt, K);
+    const int r = (int)(row & 15);
     if (fmt == SLAI_FMT_Q8_0) {
-        const int q = (int)(signed char)row[k];
-        const unsigned int sb = row[K + 2 * (k >> 5)] | (row[K + 2 * (k >> 5) + 1] << 8);
+        const uint8_t* b = data + ((row >> 4) * ns + (k >> 7)) * 2176;
+        const int e = (int)(k & 127);
+        const int q = (int)(signed char)b[layout::qbyte_off(128, r, e)];
+        const unsigned int sb = b[8 * r + 2 * (e >> 5)] | (b[8 * r + 2 * (e >> 5) + 1] << 8);
         return __fmul_rn((float)q, dev_h2f(sb));
     }
-    const long long blk = k >> 8;
+    const uint8_t* b = data + ((row >> 4) * ns + (k >> 8)) * layout::step_bytes(fmt);
     const int e = (int)(k & 255);
     if (fmt == SLAI_FMT_Q4_K || fmt == SLAI_FMT_Q5_K) {
-        const int bb = fmt == SLAI_FMT_Q4_K ? 144 : 176;
-        const uint8_t* b = row + blk * bb;
-        const float d = dev_h2f(b[0] | (b[1] << 8)), mn = dev_h2f(b[2] | (b[3] << 8));
+        const uint8_t* h = b + 16 * r;
+        const float d = dev_h2f(h[0] | (h[1] << 8)), mn = dev_h2f(h[2] | (h[3] << 8));
         const int G = e >> 6, half = (e >> 5) & 1, l = e & 31;
-        const uint8_t* qs = b + (fmt == SLAI_FMT_Q4_K ? 16 : 48);
-        int q = half ? (qs[32 * G + l] >> 4) : (qs[32 * G + l] & 0xF);
-        if (fmt == SLAI_FMT_Q5_K) q += ((b[16 + l] >> (2 * G + half)) & 1) ? 16 : 0;
-        const uint32_t s0 = b[4] | (b[5] << 8) | (b[6] << 16) | ((uint32_t)b[7] << 24);
-        const uint32_t s1 = b[8] | (b[9] << 8) | (b[10] << 16) | ((uint32_t)b[11] << 24);
-        const uint32_t s2 = b[12] | (b[13] << 8) | (b[14] << 16) | ((uint32_t)b[15] << 24);
+        const uint8_t qb = b[layout::qbyte_off(fmt == SLAI_FMT_Q4_K ? 256 : 768, r, 32 * G + l)];
+        int q = half ? (qb >> 4) : (qb & 0xF);
+        if (fmt == SLAI_FMT_Q5_K) q += ((b[256 + 32 * r + l] >> (2 * G + half)) & 1) ? 16 : 0;
+        const uint32_t s0 = h[4] | (h[5] << 8) | (h[6] << 16) | ((uint32_t)h[7] << 24);
+        const uint32_t s1 = h[8] | (h[9] << 8) | (h[10] << 16) | ((uint32_t)h[11] << 24);
+        const uint32_t s2 = h[12] | (h[13] << 8) | (h[14] << 16) | ((uint32_t)h[15] << 24);
         uint32_t sc, m;
         frag::scale_min_k4(2 * G + half, s0, s1, s2, sc, m);
         const float d1 = __fmul_rn(d, (float)sc), m1 = __fmul_rn(mn, (float)m);
         return __fsub_rn(__fmul_rn(d1, (float)q), m1);
     }
-    // Q6_K planes
-    const long long nb = K >> 8;
-    const int h = e >> 7, r = e & 127, quarter = r >> 5, l = r & 31;
-    const uint8_t qlb = row[blk * 128 + 64 * h + l + 32 * (quarter & 1)];
+    // Q6_K
+    const int hf = e >> 7, rr = e & 127, quarter = rr >> 5, l = rr & 31;
+    const uint8_t qlb = b[layout::qbyte_off(0, r, 64 * hf + l + 32 * (quarter & 1))];
     const int nib = quarter >= 2 ? (qlb >> 4) : (qlb & 0xF);
-    const uint8_t qhb = row[nb * 128 + blk * 64 + 32 * h + l];
+    const uint8_t qhb = b[2048 + hf * 512 + 32 * r + l];
     const int q = (nib | (((qhb >> (2 * quarter)) & 3) << 4)) - 32;
-    const int sc = (int)(signed char)row[nb * 192 + blk * 16 + 8 * h + (l >> 4) + 2 * quarter];
-    const float d = dev_h2f(row[nb * 208 + 2 * blk] | (row[nb * 208 + 2 * blk + 1] << 8));
+    const int sc = (int)(signed char)b[3072 + 16 * r + 8 * hf + (l >> 4) + 2 * quarter];
+    const float d = dev_h2f(b[3328 + 2 * r] | (b[3328 + 2 * r + 1] << 8));
     return __fmul_rn(__fmul_rn(d, (float)sc), (float)q);
 }
 
-__global__ void dequant_kernel(int fmt, const uint8_t* __restrict__ data, long long row_stride, long long row0,
-                               long long nrows, long long K, float* __restrict__ out) {
+__global__ void dequant_kernel(int fmt, const uint8_t* __restrict__ data, long long row0, long long nrows, long long K,
+                               float* __restrict__ out) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= nrows * K) return;
-    const long long r = i / K, k = i % K;
-    const uint8_t* row = data + (size_t)(row0 + r) * row_stride;
-    out[i] = fmt == SLAI_FMT_F32 ? reinterpret_cast<const float*>(row)[k] : dequant_elem(fmt, row, K, k);
+    const long long r = row0 + i / K, k = i % K;
+    out[i] = fmt == SLAI_FMT_F32 ? reinterpret_cast<const float*>(data)[r * K + k] : dequant_elem(fmt, data, K, r, k);
 }
 
 }  // namespace
@@ -228,14 +229,14 @@ static int qmatrix_alloc(slai_ctx* ctx, int fmt, int64_t nrows, int64_t ncols, s
                  "qmatrix: %lld x %lld is not a whole number of %d-element blocks per row", (long long)nrows,
                  (long long)ncols, be);
     SLAI_REQUIRE(ctx, fmt == SLAI_FMT_F32 || ncols % 4 == 0, SLAI_ERR_SHAPE, "qmatrix: ncols must be a multiple of 4");
+    SLAI_REQUIRE(ctx, nrows < (1ll << 31) && ncols < (1ll << 31), SLAI_ERR_SHAPE, "qmatrix: dimension too large");
     SLAI_REQUIRE(ctx, nbytes == (size_t)nrows * (ncols / be) * bb, SLAI_ERR_SHAPE,
                  "qmatrix: expected %zu bytes of blocks, got %zu", (size_t)nrows * (ncols / be) * bb, nbytes);
     slai_qmatrix* m = new slai_qmatrix();
     m->ctx = ctx; m->fmt = fmt; m->nrows = nrows; m->ncols = ncols;
-    m->nrows_padded = round_up(nrows, 16) + 16;  // segments of a fused matrix may start at any row
-    m->row_stride = layout::row_stride(fmt, ncols);
-    m->bytes = (size_t)m->nrows_padded * m->row_stride + 256;  // slack: partial Q8_0 steps never read past it
-    cudaError_t e = cudaMalloc(&m->data, m->bytes);
+    m->tile_bytes = fmt == SLAI_FMT_F32 ? ncols * 4 : layout::tile_bytes(fmt, ncols);
+    m->bytes = (size_t)layout::matrix_bytes(fmt, nrows, ncols);
+    cudaError_t e = cudaMalloc(&m->data, m->bytes + 256);
     if (e != cudaSuccess) {
         cudaGetLastError();
         delete m;
@@ -253,14 +254,13 @@ SLAI_API int slai_qmatrix_create_from_device(slai_ctx* ctx, int fmt, int64_t nro
     slai_qmatrix* m = *out;
     const int be = fmt_block_elems(fmt), bb = fmt_block_bytes(fmt);
     const long long nbk = ncols / be;
-    SLAI_CHECK_CUDA(ctx, cudaMemsetAsync(m->data, 0, m->bytes, ctx->stream));
-    if (fmt == SLAI_FMT_Q8_0 || fmt == SLAI_FMT_Q6_K) {
-        const long long total = nrows * nbk;
-        repack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(fmt, (const uint8_t*)d_blocks, m->data, nrows,
-                                                                               nbk, ncols, bb, m->row_stride);
-        SLAI_CHECK_CUDA(ctx, cudaGetLastError());
-    } else {
+    if (fmt == SLAI_FMT_F32) {
         SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(m->data, d_blocks, nbytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    } else {
+        SLAI_CHECK_CUDA(ctx, cudaMemsetAsync(m->data, 0, m->bytes, ctx->stream));  // padding rows / steps are zero
+        const long long total = nrows * nbk;
+        place_kernel<<<(unsigned)((total + 127) / 128), 128, 0, ctx->stream>>>(fmt, (const uint8_t*)d_blocks, m->data, nrows, nbk, ncols, bb);
+        SLAI_CHECK_CUDA(ctx, cudaGetLastError());
     }
     return SLAI_OK;
 }
@@ -269,28 +269,19 @@ SLAI_API int slai_qmatrix_create(slai_ctx* ctx, int fmt, int64_t nrows, int64_t 
                                  slai_qmatrix** out) {
     if (!ctx) return SLAI_ERR_INVALID_ARG;
     SLAI_REQUIRE(ctx, h_blocks, SLAI_ERR_INVALID_ARG, "qmatrix: null block pointer");
-    if (fmt == SLAI_FMT_Q8_0 || fmt == SLAI_FMT_Q6_K) {
-        void* tmp = nullptr;
-        cudaError_t e = cudaMalloc(&tmp, nbytes ? nbytes : 16);
-        if (e != cudaSuccess) {
-            cudaGetLastError();
-            return slai_set_error(ctx, SLAI_ERR_OOM, "qmatrix: cannot allocate %zu bytes of staging", nbytes);
-        }
-        int rc = SLAI_OK;
-        if (cudaMemcpyAsync(tmp, h_blocks, nbytes, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess)
-            rc = slai_set_error(ctx, SLAI_ERR_CUDA, "qmatrix: upload failed");
-        if (!rc) rc = slai_qmatrix_create_from_device(ctx, fmt, nrows, ncols, tmp, nbytes, out);
-        cudaStreamSynchronize(ctx->stream);
-        cudaFree(tmp);
-        return rc;
+    void* tmp = nullptr;
+    cudaError_t e = cudaMalloc(&tmp, nbytes ? nbytes : 16);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return slai_set_error(ctx, SLAI_ERR_OOM, "qmatrix: cannot allocate %zu bytes of staging", nbytes);
     }
-    int rc = qmatrix_alloc(ctx, fmt, nrows, ncols, nbytes, out);
-    if (rc) return rc;
-    slai_qmatrix* m = *out;
-    SLAI_CHECK_CUDA(ctx, cudaMemsetAsync(m->data, 0, m->bytes, ctx->stream));
-    SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(m->data, h_blocks, nbytes, cudaMemcpyHostToDevice, ctx->stream));
-    SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    return SLAI_OK;
+    int rc = SLAI_OK;
+    if (cudaMemcpyAsync(tmp, h_blocks, nbytes, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess)
+        rc = slai_set_error(ctx, SLAI_ERR_CUDA, "qmatrix: upload failed");
+    if (!rc) rc = slai_qmatrix_create_from_device(ctx, fmt, nrows, ncols, tmp, nbytes, out);
+    cudaStreamSynchronize(ctx->stream);
+    cudaFree(tmp);
+    return rc;
 }
 
 SLAI_API int slai_qmatrix_destroy(slai_qmatrix* m) {
@@ -314,16 +305,14 @@ SLAI_API size_t slai_qmatrix_device_bytes(const slai_qmatrix* m) { return m ? m-
 SLAI_API int slai_qmatrix_dequantize(slai_ctx* ctx, const slai_qmatrix* m, float* d_out) {
     if (!ctx || !m || !d_out) return SLAI_ERR_INVALID_ARG;
     const long long total = m->nrows * m->ncols;
-    dequant_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(m->fmt, m->data, m->row_stride, 0, m->nrows,
-                                                                            m->ncols, d_out);
+    dequant_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(m->fmt, m->data, 0, m->nrows, m->ncols, d_out);
     SLAI_CHECK_CUDA(ctx, cudaGetLastError());
     return SLAI_OK;
 }
 SLAI_API int slai_qmatrix_dequantize_row(slai_ctx* ctx, const slai_qmatrix* m, int64_t row, float* d_out) {
     if (!ctx || !m || !d_out) return SLAI_ERR_INVALID_ARG;
     SLAI_REQUIRE(ctx, row >= 0 && row < m->nrows, SLAI_ERR_INVALID_ARG, "dequantize_row: row %lld out of range", (long long)row);
-    dequant_kernel<<<(unsigned)((m->ncols + 255) / 256), 256, 0, ctx->stream>>>(m->fmt, m->data, m->row_stride, row, 1,
-                                                                               m->ncols, d_out);
+    dequant_kernel<<<(unsigned)((m->ncols + 255) / 256), 256, 0, ctx->stream>>>(m->fmt, m->data, row, 1, m->ncols, d_out);
     SLAI_CHECK_CUDA(ctx, cudaGetLastError());
     return SLAI_OK;
 }
@@ -336,7 +325,9 @@ SLAI_API int slai_gemv_quant(slai_ctx* ctx, float* d_out, const slai_qmatrix* w,
         L.fmt = w->fmt;
         L.K = (int)w->ncols;
         L.nseg = 1;
-        L.seg[0] = GemvSeg{w->data, w->row_stride, (int)w->nrows, 0};
+        L.seg[0].w = w->data;
+        L.seg[0].tile_bytes = w->tile_bytes;
+        L.seg[0].rows = (int)w->nrows;
         L.v = d_v + (size_t)b * w->ncols;
         L.out = d_out + (size_t)b * w->nrows;
         int rc = gemv_launch(ctx, L);
@@ -557,13 +548,13 @@ __global__ void embed_f32_kernel(float* x, const float* table, int dim, const in
     if (wpe) y += wpe[(size_t)(*d_pos) * dim + i];
     x[i] = y;
 }
-__global__ void embed_q_kernel(float* x, int fmt, const uint8_t* data, long long row_stride, int dim, const int* d_token,
-                               const float* wpe, const int* d_pos) {
+__global__ void embed_q_kernel(float* x, int fmt, const uint8_t* data, int dim, const int* d_token, const float* wpe,
+                               const int* d_pos) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= dim) return;
-    const uint8_t* row = data + (size_t)(*d_token) * row_stride;
-    float y = fmt == SLAI_FMT_F32 ? reinterpret_cast<const float*>(row)[i] : dequant_elem(fmt, row, dim, i);
+    const long long row = *d_token;
+    float y = fmt == SLAI_FMT_F32 ? reinterpret_cast<const float*>(data)[row * dim + i] : dequant_elem(fmt, data, dim, row, i);
     if (wpe) y += wpe[(size_t)(*d_pos) * dim + i];
     x[i] = y;
 }
@@ -731,8 +722,8 @@ int launch_embed_f32(slai_ctx* ctx, float* x, const float* table, int dim, const
 int launch_embed_q8(slai_ctx* ctx, float* x, const slai_qmatrix* wte, const int* d_token, const float* wpe,
                     const int* d_pos, bool pdl) {
     const int dim = (int)wte->ncols;
-    return launch_pdl(ctx, embed_q_kernel, dim3((dim + NT - 1) / NT), dim3(NT), pdl, x, wte->fmt, (const uint8_t*)wte->data,
-                      (long long)wte->row_stride, dim, d_token, wpe, d_pos);
+    return launch_pdl(ctx, embed_q_kernel, dim3((dim + NT - 1) / NT), dim3(NT), pdl, x, wte->fmt, (const uint8_t*)wte->data, dim,
+                      d_token, wpe, d_pos);
 }
 int launch_advance(slai_ctx* ctx, int* d_token, int* d_pos, const int32_t* d_next, int32_t* d_history, bool pdl) {
     // d_history[-1] is not used; the step counter lives right after the position scalar (see models)

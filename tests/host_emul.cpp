@@ -22,8 +22,8 @@ using namespace gemvfmt;
 
 struct Job {
     int fmt, K, nsteps;
-    const uint8_t* rows;  // repacked device-layout rows
-    int64_t stride;
+    uint32_t tile0;  // shared-space address of the tile's first tile-step block
+    int step_bytes;
     Smem S;
     hostemu::Warp* W;
     float acc[32][2];
@@ -33,17 +33,10 @@ template <class F>
 static void lane_body(Job* J, int lane) {
     LaneCtx L;
     L.lane = lane; L.g = lane >> 2; L.t = lane & 3;
-    for (int i = 0; i < 8; i++) { L.bp[i] = 0; L.bs[i] = 0; }
+    for (int i = 0; i < 4; i++) { L.bp[i] = 0; L.bs[i] = 0; }
     F::init(L, J->S);
-    L.bs[7] = F::aux(J->K);
-    const uint8_t* rowA = J->rows + (size_t)L.g * J->stride;
-    const uint8_t* rowB = rowA + 8 * J->stride;
     float a = 0.f, b = 0.f;
-    typename F::Regs R;
-    for (int s = 0; s < J->nsteps; s++) {
-        F::load(R, rowA, rowB, s, L);
-        F::compute(R, s, L, J->S, a, b);
-    }
+    for (int s = 0; s < J->nsteps; s++) F::compute(J->tile0 + (uint32_t)s * J->step_bytes, s, L, J->S, a, b);
     J->acc[lane][0] = a;
     J->acc[lane][1] = b;
 }
@@ -84,16 +77,18 @@ int main(int argc, char** argv) {
     const int nbk = K / be;
     if ((int)raw.size() != 16 * nbk * bb || (int)vb.size() != 4 * K) { fprintf(stderr, "size mismatch\n"); return 2; }
 
-    // device layout
-    const int64_t stride = layout::row_stride(fmt, K);
-    std::vector<uint8_t> rows(16 * stride + 64, 0);
+    // device layout: one tile of 16 rows, tile-major (layout.cuh)
+    const int sbytes = layout::step_bytes(fmt);
+    const int nsteps = (int)layout::num_steps(fmt, K);
+    std::vector<uint8_t> tile((size_t)nsteps * sbytes, 0);
     for (int r = 0; r < 16; r++)
-        for (int b = 0; b < nbk; b++)
-            layout::repack_block(fmt, raw.data() + ((size_t)r * nbk + b) * bb, rows.data() + r * stride, b, K);
+        for (int b = 0; b < nbk; b++) layout::place_block(fmt, raw.data() + ((size_t)r * nbk + b) * bb, tile.data(), r, b, K);
 
     // staging (mirrors stage_vector in gemv.cu with PRO_NONE)
     const int Kp = (K + 255) & ~255;
-    std::vector<unsigned char> smem(4 * Kp + 32 + (Kp / 32) * 4 + 64, 0);
+    const size_t tile_off = (size_t)(4 * Kp + 32 + (Kp / 32) * 4 + 127) & ~(size_t)127;
+    std::vector<unsigned char> smem(tile_off + tile.size() + 64, 0);
+    memcpy(smem.data() + tile_off, tile.data(), tile.size());
     float mx = 0.f;
     for (int k = 0; k < K; k++) mx = fmaxf(mx, fabsf(v[k]));
     float scale = 1.f;
@@ -124,9 +119,9 @@ int main(int argc, char** argv) {
     pthread_barrier_init(&W.bar, nullptr, 32);
     W.smem = smem.data();
     Job J;
-    J.fmt = fmt; J.K = K; J.rows = rows.data(); J.stride = stride; J.W = &W;
-    J.nsteps = (fmt == 12 || fmt == 13) ? K / 256 : (K + 127) / 128;
-    J.S.hi = 0; J.S.lo = 2 * Kp; J.S.zero = 4 * Kp; J.S.sv = 4 * Kp + 32; J.S.red = nullptr; J.S.stat = nullptr;
+    J.fmt = fmt; J.K = K; J.W = &W;
+    J.nsteps = nsteps; J.tile0 = (uint32_t)tile_off; J.step_bytes = sbytes;
+    J.S.hi = 0; J.S.lo = 2 * Kp; J.S.zero = 4 * Kp; J.S.sv = 4 * Kp + 32;
     pthread_t th[32];
     ThreadArg args[32];
     for (int l = 0; l < 32; l++) { args[l] = {&J, l}; pthread_create(&th[l], nullptr, thread_main, &args[l]); }
