@@ -123,9 +123,9 @@ __device__ __forceinline__ void block_sum_max(float& s, float& m, float* stat) {
 }
 
 // Stage the activation vector: optional normalisation, power-of-two scaling so that max|v| lands in
-// [2^13, 2^14), split into f16 hi + lo in the [0,2,1,3] order, and per-32 sums of the scaled values
-// (for the `- dmin*m * sum(v)` term of Q4_K / Q5_K).  Returns 1/scale.
-template <int PRO, bool NEED_SV>
+// [2^25, 2^26), rounding to integers, split into four base-128 digit planes (gemv_frag.cuh), and per-sub-block
+// digit sums (for the `- dmin*m * sum(v)` term of Q4_K / Q5_K and the -32 offset of Q6_K).  Returns 1/scale.
+template <int PRO, int SV_GRAN>
 __device__ float stage_vector(const GemvParams& P, const Smem& S, float* stat, int Kp) {
     const int K = P.K;
     const int tid = threadIdx.x;
@@ -173,12 +173,11 @@ __device__ float stage_vector(const GemvParams& P, const Smem& S, float* stat, i
     if (mx > 0.f && mx < 3.0e38f) {
         int e;
         frexpf(mx, &e);  // mx = f * 2^e, f in [0.5, 1)
-        e = e < -100 ? -100 : e;
-        scale = ldexpf(1.0f, 14 - e);
+        e = e < -90 ? -90 : e;
+        scale = ldexpf(1.0f, 26 - e);
     }
-    __half* hi = reinterpret_cast<__half*>(__cvta_shared_to_generic(S.hi));
-    __half* lo = reinterpret_cast<__half*>(__cvta_shared_to_generic(S.lo));
-    float* sv = reinterpret_cast<float*>(__cvta_shared_to_generic(S.sv));
+    unsigned char* dig = reinterpret_cast<unsigned char*>(__cvta_shared_to_generic(S.dig));
+    int4* sv = reinterpret_cast<int4*>(__cvta_shared_to_generic(S.sv));
     const int np4 = Kp >> 2;
     for (int i = tid; i < np4; i += THREADS) {
         float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -196,26 +195,31 @@ __device__ float stage_vector(const GemvParams& P, const Smem& S, float* stat, i
                     x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
                 }
             }
-            x.x *= scale; x.y *= scale; x.z *= scale; x.w *= scale;
         }
-        const __half h0 = __float2half_rn(x.x), h1 = __float2half_rn(x.y), h2 = __float2half_rn(x.z), h3 = __float2half_rn(x.w);
-        const __half l0 = __float2half_rn(x.x - __half2float(h0)), l1 = __float2half_rn(x.y - __half2float(h1));
-        const __half l2 = __float2half_rn(x.z - __half2float(h2)), l3 = __float2half_rn(x.w - __half2float(h3));
-        __half2* hp = reinterpret_cast<__half2*>(hi + 4 * i);
-        __half2* lp = reinterpret_cast<__half2*>(lo + 4 * i);
-        hp[0] = __halves2half2(h0, h2);  // order [0,2,1,3]
-        hp[1] = __halves2half2(h1, h3);
-        lp[0] = __halves2half2(l0, l2);
-        lp[1] = __halves2half2(l1, l3);
-        if (NEED_SV) {
-            float s4 = (x.x + x.y) + (x.z + x.w);
-            s4 += __shfl_xor_sync(0xffffffffu, s4, 1);
-            s4 += __shfl_xor_sync(0xffffffffu, s4, 2);
-            s4 += __shfl_xor_sync(0xffffffffu, s4, 4);
-            if ((tid & 7) == 0) sv[i >> 3] = s4;
+        int d0[4], d1[4], d2[4], d3[4];
+        split_digits(__float2int_rn(x.x * scale), d0);
+        split_digits(__float2int_rn(x.y * scale), d1);
+        split_digits(__float2int_rn(x.z * scale), d2);
+        split_digits(__float2int_rn(x.w * scale), d3);
+        int s[4];
+#pragma unroll
+        for (int p = 0; p < 4; p++) {
+            const uint32_t word = (uint32_t)(d0[p] & 0xFF) | ((uint32_t)(d1[p] & 0xFF) << 8) | ((uint32_t)(d2[p] & 0xFF) << 16) |
+                                  ((uint32_t)(d3[p] & 0xFF) << 24);
+            *reinterpret_cast<uint32_t*>(dig + (size_t)p * S.plane + 4 * i) = word;
+            s[p] = (d0[p] + d1[p]) + (d2[p] + d3[p]);
+        }
+        if (SV_GRAN > 0) {
+#pragma unroll
+            for (int p = 0; p < 4; p++) {
+                s[p] += __shfl_xor_sync(0xffffffffu, s[p], 1);
+                s[p] += __shfl_xor_sync(0xffffffffu, s[p], 2);
+                if (SV_GRAN == 32) s[p] += __shfl_xor_sync(0xffffffffu, s[p], 4);
+            }
+            constexpr int LANES = SV_GRAN > 0 ? SV_GRAN / 4 : 1;  // float4 groups per sub-block
+            if ((tid & (LANES - 1)) == 0) sv[i / LANES] = make_int4(s[0], s[1], s[2], s[3]);
         }
     }
-    if (tid < 8) reinterpret_cast<uint32_t*>(__cvta_shared_to_generic(S.zero))[tid] = 0u;
     __syncthreads();
     return 1.0f / scale;
 }
@@ -240,25 +244,22 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_kernel(const GemvParams P) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int K = P.K;
     const int Kp = (K + 255) & ~255;
-    // [hi Kp f16][lo Kp f16][zero 32B][sv Kp/32 f32][red WARPS*32 f32][stat 64 f32][mbar WARPS*MAX_STAGES u64][ring]
+    // [digit planes 4*Kp s8][sv: Kp/SV_GRAN x 4 s32][red WARPS*32 f32][stat 64 f32][mbar WARPS*MAX_STAGES u64][ring]
+    constexpr int SV_BYTES_PER_256 = F::SV_GRAN > 0 ? 256 / F::SV_GRAN * 16 : 0;
+    const uint32_t sv_bytes = (uint32_t)(Kp >> 8) * SV_BYTES_PER_256;
     Smem S;
-    S.hi = (uint32_t)__cvta_generic_to_shared(smem_raw);
-    S.lo = S.hi + 2 * Kp;
-    S.zero = S.lo + 2 * Kp;
-    S.sv = S.zero + 32;
-    float* red = reinterpret_cast<float*>(smem_raw + 4 * Kp + 32) + (Kp >> 5);
+    S.dig = (uint32_t)__cvta_generic_to_shared(smem_raw);
+    S.plane = Kp;
+    S.sv = S.dig + 4 * Kp;
+    float* red = reinterpret_cast<float*>(smem_raw + 4 * Kp + sv_bytes);
     float* stat = red + WARPS * 32;
-    const uint32_t fixed = (uint32_t)(4 * Kp + 32 + (Kp >> 5) * 4 + WARPS * 32 * 4 + 64 * 4);
-    const uint32_t mbar_base = S.hi + fixed;
+    const uint32_t fixed = (uint32_t)(4 * Kp) + sv_bytes + WARPS * 32 * 4 + 64 * 4;
+    const uint32_t mbar_base = S.dig + fixed;
     const uint32_t ring_base = (mbar_base + WARPS * MAX_STAGES * 8 + 127u) & ~127u;
 
     const int warp = threadIdx.x >> 5;
     LaneCtx L;
-    L.lane = threadIdx.x & 31;
-    L.g = L.lane >> 2;
-    L.t = L.lane & 3;
-    for (int i = 0; i < 4; i++) { L.bp[i] = 0; L.bs[i] = 0; }
-    F::init(L, S);
+    lane_init(L, threadIdx.x & 31, S);
 
     const int ks = P.ks, nstage = P.nstage, nsteps = P.nsteps;
     const int groups = WARPS / ks;
@@ -302,7 +303,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_kernel(const GemvParams P) {
     for (int s = 0; s < nstage; s++) issue();  // weights do not depend on the previous kernel
 
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const float inv_scale = stage_vector<PRO, F::NEED_SV>(P, S, stat, Kp);
+    const float inv_scale = stage_vector<PRO, F::SV_GRAN>(P, S, stat, Kp);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     int c_stage = 0;
@@ -519,7 +520,9 @@ int gemv_launch(slai_ctx* ctx, const GemvLaunch& L) {
     P.err_flag = ctx->d_counters + 3000;
 
     const int Kp = (K + 255) & ~255;
-    const size_t fixed = (size_t)4 * Kp + 32 + (size_t)(Kp / 32) * 4 + WARPS * 32 * 4 + 64 * 4 + WARPS * MAX_STAGES * 8 + 128;
+    const int sv_gran = (L.fmt == SLAI_FMT_Q4_K || L.fmt == SLAI_FMT_Q5_K) ? 32 : L.fmt == SLAI_FMT_Q6_K ? 16 : 0;
+    const size_t sv_bytes = sv_gran ? (size_t)(Kp / sv_gran) * 16 : 0;
+    const size_t fixed = (size_t)4 * Kp + sv_bytes + WARPS * 32 * 4 + 64 * 4 + WARPS * MAX_STAGES * 8 + 128;
     const size_t per_stage = (size_t)WARPS * P.stage_stride;
     SLAI_REQUIRE(ctx, fixed + 2 * per_stage <= SMEM_LIMIT, SLAI_ERR_SHAPE, "gemv: K=%d does not fit in shared memory", K);
     static int stage_env = -1, ks_env = -1;

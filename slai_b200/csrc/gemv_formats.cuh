@@ -1,14 +1,14 @@
 // Per-format MMA bodies of the dequant-GEMV kernel (see gemv.cu for the kernel shape, layout.cuh for the
-// tile-step blocks they read from shared memory and gemv_frag.cuh for the fragment mapping).  The functions
-// are written against a small set of primitives (shared loads, the m16n8k16 MMA) that have a device
-// implementation in PTX
-// and a host implementation in which 32 CPU threads play the lanes of a warp, so the very same source is
-// exercised by the CPU test-suite (tests/host_emul.cpp) before it ever runs on a GPU.
+// tile-step blocks they read from shared memory and gemv_frag.cuh for the operand mapping).  The functions
+// are written against a small set of primitives (shared loads, the integer m16n8k32 MMA) that have a device
+// implementation in PTX and a host implementation in which 32 CPU threads play the lanes of a warp, so the
+// very same source is exercised by the CPU test-suite (tests/host_emul.cpp) before it ever runs on a GPU.
 #pragma once
 #include "gemv_frag.cuh"
 
 #ifndef __CUDA_ARCH__
 #include <pthread.h>
+#include <string.h>
 namespace hostemu {
 // One emulated warp: 32 host threads, a barrier, an exchange area for MMA operands, and a byte array that
 // stands for shared memory (shared-space addresses are offsets into it).
@@ -24,30 +24,6 @@ extern thread_local Warp* warp;
 
 namespace prim {
 
-SLAI_HD uint4 ldg16(const void* p) {
-#ifdef __CUDA_ARCH__
-    uint4 r;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
-                 : "l"(p));
-    return r;
-#else
-    uint4 r;
-    memcpy(&r, p, 16);
-    return r;
-#endif
-}
-SLAI_HD uint32_t ldg2(const void* p) {
-#ifdef __CUDA_ARCH__
-    unsigned short r;
-    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(r) : "l"(p));
-    return r;
-#else
-    unsigned short r;
-    memcpy(&r, p, 2);
-    return r;
-#endif
-}
 SLAI_HD uint4 lds16(uint32_t addr) {
 #ifdef __CUDA_ARCH__
     uint4 r;
@@ -59,14 +35,14 @@ SLAI_HD uint4 lds16(uint32_t addr) {
     return r;
 #endif
 }
-SLAI_HD float lds_f32(uint32_t addr) {
+SLAI_HD uint2 lds8(uint32_t addr) {
 #ifdef __CUDA_ARCH__
-    float r;
-    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(r) : "r"(addr));
+    uint2 r;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(r.x), "=r"(r.y) : "r"(addr));
     return r;
 #else
-    float r;
-    memcpy(&r, hostemu::warp->smem + addr, 4);
+    uint2 r;
+    memcpy(&r, hostemu::warp->smem + addr, 8);
     return r;
 #endif
 }
@@ -97,14 +73,14 @@ SLAI_HD float fma(float a, float b, float c) {
     return (float)((double)a * (double)b + (double)c);  // single rounding, like fmaf
 #endif
 }
-// D = A(16x16, row) * B(16x8, col) + D, f16 inputs, f32 accumulation.  Lane (g = lane/4, t = lane%4):
-//   a0 = A[g][2t..2t+1], a1 = A[g+8][2t..], a2 = A[g][2t+8..], a3 = A[g+8][2t+8..]
-//   b0 = B[2t..2t+1][g], b1 = B[2t+8..2t+9][g];  c0,c1 = D[g][2t..2t+1], c2,c3 = D[g+8][2t..2t+1]
-SLAI_HD void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+// D = A(16x32, row, s8) * B(32x8, col, s8) + D (s32).  Lane (g = lane/4, t = lane%4):
+//   a0 = A[g][4t..4t+3], a1 = A[g+8][4t..], a2 = A[g][16+4t..], a3 = A[g+8][16+4t..]   (4 x s8 per register)
+//   b0 = B[4t..4t+3][g], b1 = B[16+4t..][g];   c0,c1 = D[g][2t..2t+1], c2,c3 = D[g+8][2t..2t+1]
+SLAI_HD void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
 #ifdef __CUDA_ARCH__
     asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 #else
     hostemu::Warp* W = hostemu::warp;
@@ -113,21 +89,21 @@ SLAI_HD void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint
     W->b[lane][0] = b0; W->b[lane][1] = b1;
     pthread_barrier_wait(&W->bar);
     auto A = [&](int row, int k) {
-        const int l = (row & 7) * 4 + ((k & 7) >> 1);
-        const int reg = (row >= 8 ? 1 : 0) + (k >= 8 ? 2 : 0);
-        return h2f((W->a[l][reg] >> (16 * (k & 1))) & 0xFFFF);
+        const int l = (row & 7) * 4 + ((k & 15) >> 2);
+        const int reg = (row >= 8 ? 1 : 0) + (k >= 16 ? 2 : 0);
+        return (int)(signed char)((W->a[l][reg] >> (8 * (k & 3))) & 0xFF);
     };
     auto B = [&](int k, int n) {
-        const int l = n * 4 + ((k & 7) >> 1);
-        const int reg = k >= 8 ? 1 : 0;
-        return h2f((W->b[l][reg] >> (16 * (k & 1))) & 0xFFFF);
+        const int l = n * 4 + ((k & 15) >> 2);
+        const int reg = k >= 16 ? 1 : 0;
+        return (int)(signed char)((W->b[l][reg] >> (8 * (k & 3))) & 0xFF);
     };
     const int g = lane >> 2, t = lane & 3;
     for (int i = 0; i < 4; i++) {
         const int row = g + (i >= 2 ? 8 : 0), col = 2 * t + (i & 1);
-        double s = c[i];
-        for (int k = 0; k < 16; k++) s += (double)A(row, k) * (double)B(k, col);
-        c[i] = (float)s;
+        int s = c[i];
+        for (int k = 0; k < 32; k++) s += A(row, k) * B(k, col);
+        c[i] = s;
     }
     pthread_barrier_wait(&W->bar);
 #endif
@@ -139,154 +115,134 @@ namespace gemvfmt {
 
 using namespace frag;
 
-SLAI_HD uint32_t w4(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
-
-// Shared-space byte addresses of the staged activation vector: f16 hi / lo arrays in [0,2,1,3] order, 32
-// bytes of zeros, and per-32-element sums of the scaled activations.
+// Shared-space byte addresses of the staged activation vector: four planes of s8 digits (plane p at
+// dig + p*plane, element k at byte k) and per-sub-block digit sums (4 x s32 per sub-block of SV_GRAN elements).
 struct Smem {
-    uint32_t hi, lo, zero, sv;
+    uint32_t dig, plane, sv;
 };
 
 struct LaneCtx {
     int lane, g, t;
-    // B-operand source addresses (shared space, bytes) and their per-step strides
-    uint32_t bp[4];
-    uint32_t bs[4];
+    bool bact;        // this lane supplies non-zero B values (its column belongs to its own sub-block)
+    uint32_t bdig;    // digit plane of this lane's B column (g & 3)
+    float wd0, wd1;   // weights of the two digits whose sums this lane holds (digits 2(t&1), 2(t&1)+1)
 };
 
+SLAI_HD void lane_init(LaneCtx& L, int lane, const Smem& S) {
+    L.lane = lane;
+    L.g = lane >> 2;
+    L.t = lane & 3;
+    L.bact = (L.t >> 1) == (L.g >> 2);
+    L.bdig = S.dig + (L.g & 3) * S.plane;
+    L.wd0 = digit_weight(2 * (L.t & 1));
+    L.wd1 = digit_weight(2 * (L.t & 1) + 1);
+}
+
+SLAI_HD float combine(int p0, int p1, const LaneCtx& L) { return prim::fma((float)p1, L.wd1, (float)p0 * L.wd0); }
+
 // Every format provides
-//   STEP      elements of K per tile-step block
-//   init      the lane's B-operand sources
+//   STEP      elements of K per tile-step block          SV_GRAN  elements per digit-sum entry (0: none)
 //   compute   one tile-step block at shared address `blk` (K step number `step`): accumulates rows g and g+8
-// ---- Q4_K ----------------------------------------------------------------------------------
-struct Q4K {
-    static constexpr int FMT = 12;
+// ---- Q4_K / Q5_K ---------------------------------------------------------------------------
+template <bool FIVE>
+struct K45 {
+    static constexpr int FMT = FIVE ? 13 : 12;
     static constexpr int STEP = 256;
-    static constexpr int QOFF = 256;  // start of the lane-ordered quant regions
-    static constexpr bool NEED_SV = true;
-    SLAI_HD static void init(LaneCtx& L, const Smem& S) {
-        for (int ci = 0; ci < 2; ci++)
-            for (int slot = 0; slot < 2; slot++) {
-                const BSel b = bsel_k4(L.lane, ci, slot);
-                const int i = ci * 2 + slot;
-                L.bp[i] = b.off < 0 ? S.zero : (b.lo ? S.lo : S.hi) + 2 * b.off;
-                L.bs[i] = b.off < 0 ? 0 : 2 * STEP;
-            }
-    }
-    template <bool FIVE>
-    SLAI_HD static void compute_k(uint32_t blk, int step, const LaneCtx& L, const Smem& S, float& accA, float& accB) {
+    static constexpr int SV_GRAN = 32;
+    SLAI_HD static void compute(uint32_t blk, int step, const LaneCtx& L, const Smem& S, float& accA, float& accB) {
         const uint4 hA = prim::lds16(blk + 16 * L.g), hB = prim::lds16(blk + 16 * (L.g + 8));
-        const float dA = prim::h2f(hA.x & 0xFFFF), mnA = prim::h2f(hA.x >> 16);
-        const float dB = prim::h2f(hB.x & 0xFFFF), mnB = prim::h2f(hB.x >> 16);
         uint4 hqA = hA, hqB = hB;
         if (FIVE) {
             hqA = prim::lds16(blk + 256 + 32 * L.g + 16 * (L.t & 1));
             hqB = prim::lds16(blk + 256 + 32 * (L.g + 8) + 16 * (L.t & 1));
         }
         const uint32_t q0 = blk + (FIVE ? 768 : 256) + 16 * L.lane;
+        const int tsh = 16 * (L.t >> 1);  // this lane's sub-blocks are 2(t>>1)+nib (+4 for ci = 1)
+        const uint32_t yA = hA.y >> tsh, zA = hA.z >> tsh, wA = hA.w >> tsh;
+        const uint32_t yB = hB.y >> tsh, zB = hB.z >> tsh, wB = hB.w >> tsh;
+        int PA0 = 0, PA1 = 0, QA0 = 0, QA1 = 0, PB0 = 0, PB1 = 0, QB0 = 0, QB1 = 0;
 #pragma unroll
         for (int ci = 0; ci < 2; ci++) {
             const uint4 qA = prim::lds16(q0 + (ci * 2) * 512), qB = prim::lds16(q0 + (ci * 2 + 1) * 512);
-            const uint32_t p0 = L.bp[ci * 2] + step * L.bs[ci * 2], p1 = L.bp[ci * 2 + 1] + step * L.bs[ci * 2 + 1];
-            const uint4 b0a = prim::lds16(p0), b0b = prim::lds16(p0 + 16), b1a = prim::lds16(p1), b1b = prim::lds16(p1 + 16);
-            const int sh = 2 * ((L.t >> 1) + 2 * ci);  // Q5_K: 2 * (64-element group index)
-            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            const int hsh = 2 * ((L.t >> 1) + 2 * ci);  // Q5_K: 2 * (64-element group index)
+            const uint32_t hAx = hqA.x >> hsh, hAy = hqA.y >> hsh, hAz = hqA.z >> hsh, hAw = hqA.w >> hsh;
+            const uint32_t hBx = hqB.x >> hsh, hBy = hqB.y >> hsh, hBz = hqB.z >> hsh, hBw = hqB.w >> hsh;
 #pragma unroll
-            for (int w = 0; w < 4; w++) {
-                const uint32_t hwA = FIVE ? (w4(hqA, w) >> sh) : 0u, hwB = FIVE ? (w4(hqB, w) >> sh) : 0u;
-#pragma unroll
-                for (int sel = 0; sel < 2; sel++) {
-                    uint32_t a0, a1, a2, a3;
-                    if (FIVE) {
-                        q5_pair(w4(qA, w), hwA, sel, a0, a2);
-                        q5_pair(w4(qB, w), hwB, sel, a1, a3);
-                    } else {
-                        q4_pair(w4(qA, w), sel, a0, a2);
-                        q4_pair(w4(qB, w), sel, a1, a3);
-                    }
-                    const int i = 2 * w + sel;
-                    prim::mma16816(c, a0, a1, a2, a3, i < 4 ? w4(b0a, i) : w4(b0b, i - 4), i < 4 ? w4(b1a, i) : w4(b1b, i - 4));
+            for (int nib = 0; nib < 2; nib++) {
+                const int j = 4 * ci + 2 * (L.t >> 1) + nib;  // sub-block (of 32) inside the super-block
+                uint4 bv = make_uint4(0u, 0u, 0u, 0u);
+                if (L.bact) bv = prim::lds16(L.bdig + 256 * step + 32 * j + 16 * (L.t & 1));
+                int c[4] = {0, 0, 0, 0};
+                if (FIVE) {
+                    prim::mma_s8(c, q5_nibs(qA.x, hAx, nib), q5_nibs(qB.x, hBx, nib), q5_nibs(qA.y, hAy, nib), q5_nibs(qB.y, hBy, nib), bv.x, bv.y);
+                    prim::mma_s8(c, q5_nibs(qA.z, hAz, nib), q5_nibs(qB.z, hBz, nib), q5_nibs(qA.w, hAw, nib), q5_nibs(qB.w, hBw, nib), bv.z, bv.w);
+                } else {
+                    prim::mma_s8(c, q4_nibs(qA.x, nib), q4_nibs(qB.x, nib), q4_nibs(qA.y, nib), q4_nibs(qB.y, nib), bv.x, bv.y);
+                    prim::mma_s8(c, q4_nibs(qA.z, nib), q4_nibs(qB.z, nib), q4_nibs(qA.w, nib), q4_nibs(qB.w, nib), bv.z, bv.w);
                 }
+                const uint2 sv = prim::lds8(S.sv + 16 * (step * 8 + j) + 8 * (L.t & 1));
+                int scA, mA, scB, mB;
+                if (ci == 0) {
+                    scA = (yA >> (8 * nib)) & 63; mA = (zA >> (8 * nib)) & 63;
+                    scB = (yB >> (8 * nib)) & 63; mB = (zB >> (8 * nib)) & 63;
+                } else {
+                    scA = ((wA >> (8 * nib)) & 0xF) | (((yA >> (8 * nib + 6)) & 3) << 4);
+                    mA = ((wA >> (8 * nib + 4)) & 0xF) | (((zA >> (8 * nib + 6)) & 3) << 4);
+                    scB = ((wB >> (8 * nib)) & 0xF) | (((yB >> (8 * nib + 6)) & 3) << 4);
+                    mB = ((wB >> (8 * nib + 4)) & 0xF) | (((zB >> (8 * nib + 6)) & 3) << 4);
+                }
+                PA0 += scA * c[0]; PA1 += scA * c[1]; QA0 += mA * (int)sv.x; QA1 += mA * (int)sv.y;
+                PB0 += scB * c[2]; PB1 += scB * c[3]; QB0 += mB * (int)sv.x; QB1 += mB * (int)sv.y;
             }
-            const int j = 4 * ci + L.t;
-            const float sv = prim::lds_f32(S.sv + 4 * (step * 8 + j));
-            uint32_t sc, m;
-            scale_min_k4(j, hA.y, hA.z, hA.w, sc, m);
-            accA = prim::fma(dA * (float)sc, c[0] + c[1], accA);
-            accA = prim::fma(-(mnA * (float)m), sv, accA);
-            scale_min_k4(j, hB.y, hB.z, hB.w, sc, m);
-            accB = prim::fma(dB * (float)sc, c[2] + c[3], accB);
-            accB = prim::fma(-(mnB * (float)m), sv, accB);
         }
-    }
-    SLAI_HD static void compute(uint32_t blk, int step, const LaneCtx& L, const Smem& S, float& accA, float& accB) {
-        compute_k<false>(blk, step, L, S, accA, accB);
-    }
-};
-
-// ---- Q5_K ----------------------------------------------------------------------------------
-struct Q5K {
-    static constexpr int FMT = 13;
-    static constexpr int STEP = 256;
-    static constexpr bool NEED_SV = true;
-    SLAI_HD static void init(LaneCtx& L, const Smem& S) { Q4K::init(L, S); }
-    SLAI_HD static void compute(uint32_t blk, int step, const LaneCtx& L, const Smem& S, float& accA, float& accB) {
-        Q4K::compute_k<true>(blk, step, L, S, accA, accB);
+        const float dA = prim::h2f(hA.x & 0xFFFF), mnA = prim::h2f(hA.x >> 16);
+        const float dB = prim::h2f(hB.x & 0xFFFF), mnB = prim::h2f(hB.x >> 16);
+        accA = prim::fma(dA, combine(PA0, PA1, L), accA);
+        accA = prim::fma(-mnA, combine(QA0, QA1, L), accA);
+        accB = prim::fma(dB, combine(PB0, PB1, L), accB);
+        accB = prim::fma(-mnB, combine(QB0, QB1, L), accB);
     }
 };
+using Q4K = K45<false>;
+using Q5K = K45<true>;
 
-// ---- Q6_K: two halves of 128 elements per block ----------------------------------------------
+// ---- Q6_K ----------------------------------------------------------------------------------
 struct Q6K {
     static constexpr int FMT = 14;
     static constexpr int STEP = 256;
-    static constexpr bool NEED_SV = false;
-    SLAI_HD static void init(LaneCtx& L, const Smem& S) {
-        for (int slot = 0; slot < 2; slot++) {
-            const int off = bsel_q6(L.lane, slot);
-            L.bp[slot * 2 + 0] = off < 0 ? S.zero : S.hi + 2 * off;
-            L.bp[slot * 2 + 1] = off < 0 ? S.zero : S.lo + 2 * off;
-            L.bs[slot * 2 + 0] = L.bs[slot * 2 + 1] = off < 0 ? 0 : 2 * 128;  // per half
-        }
-    }
+    static constexpr int SV_GRAN = 16;
     SLAI_HD static void compute(uint32_t blk, int step, const LaneCtx& L, const Smem& S, float& accA, float& accB) {
-        const float dA = prim::h2f(prim::lds_u16(blk + 3328 + 2 * L.g)), dB = prim::h2f(prim::lds_u16(blk + 3328 + 2 * (L.g + 8)));
-        const int sh = 2 * (L.t >> 1);
+        int PA0 = 0, PA1 = 0, PB0 = 0, PB1 = 0;
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-            const int hstep = 2 * step + h;
-            const uint4 qlA = prim::lds16(blk + (h * 2) * 512 + 16 * L.lane), qlB = prim::lds16(blk + (h * 2 + 1) * 512 + 16 * L.lane);
-            const uint4 qhA = prim::lds16(blk + 2048 + h * 512 + 32 * L.g + 16 * (L.t & 1));
-            const uint4 qhB = prim::lds16(blk + 2048 + h * 512 + 32 * (L.g + 8) + 16 * (L.t & 1));
-            const uint32_t scA = prim::lds_u16(blk + 3072 + 16 * L.g + 8 * h + 2 * L.t);
-            const uint32_t scB = prim::lds_u16(blk + 3072 + 16 * (L.g + 8) + 8 * h + 2 * L.t);
-            const uint32_t p0h = L.bp[0] + hstep * L.bs[0], p0l = L.bp[1] + hstep * L.bs[1];
-            const uint32_t p1h = L.bp[2] + hstep * L.bs[2], p1l = L.bp[3] + hstep * L.bs[3];
-            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint2 qhA = prim::lds8(blk + 2048 + (h * 2) * 256 + 8 * L.lane), qhB = prim::lds8(blk + 2048 + (h * 2 + 1) * 256 + 8 * L.lane);
+            const uint2 scwA = prim::lds8(blk + 3072 + 16 * L.g + 8 * h), scwB = prim::lds8(blk + 3072 + 16 * (L.g + 8) + 8 * h);
 #pragma unroll
-            for (int hf = 0; hf < 2; hf++) {  // two groups of 4 MMAs: words 0-1, words 2-3
-                const uint4 b0h = prim::lds16(p0h + 16 * hf), b0l = prim::lds16(p0l + 16 * hf);
-                const uint4 b1h = prim::lds16(p1h + 16 * hf), b1l = prim::lds16(p1l + 16 * hf);
+            for (int pair = 0; pair < 2; pair++) {
+                const uint2 qlA = prim::lds8(blk + ((h * 2 + pair) * 2) * 256 + 8 * L.lane);
+                const uint2 qlB = prim::lds8(blk + ((h * 2 + pair) * 2 + 1) * 256 + 8 * L.lane);
 #pragma unroll
-                for (int ww = 0; ww < 2; ww++) {
-                    const int w = 2 * hf + ww;
-                    const uint32_t hwA = w4(qhA, w) >> sh, hwB = w4(qhB, w) >> sh;
-#pragma unroll
-                    for (int sel = 0; sel < 2; sel++) {
-                        uint32_t a0, a1, a2, a3;
-                        q6_pair(w4(qlA, w), hwA, sel, a0, a2);
-                        q6_pair(w4(qlB, w), hwB, sel, a1, a3);
-                        const int i = 2 * ww + sel;
-                        prim::mma16816(c, a0, a1, a2, a3, w4(b0h, i), w4(b1h, i));
-                        prim::mma16816(c, a0, a1, a2, a3, w4(b0l, i), w4(b1l, i));
-                    }
+                for (int nib = 0; nib < 2; nib++) {
+                    const int sh = 2 * pair + 4 * nib;
+                    const int j8 = 4 * nib + 2 * pair + (L.t >> 1);  // sub-block (of 16) inside the half
+                    const int j = 16 * step + 8 * h + j8;
+                    uint2 bv = make_uint2(0u, 0u);
+                    if (L.bact) bv = prim::lds8(L.bdig + 16 * j + 8 * (L.t & 1));
+                    int c[4] = {0, 0, 0, 0};
+                    prim::mma_s8(c, q6_nibs(qlA.x, qhA.x >> sh, nib), q6_nibs(qlB.x, qhB.x >> sh, nib), q6_nibs(qlA.y, qhA.y >> sh, nib),
+                                 q6_nibs(qlB.y, qhB.y >> sh, nib), bv.x, bv.y);
+                    const uint2 sv = prim::lds8(S.sv + 16 * j + 8 * (L.t & 1));
+                    // int8 scale of sub-block j8: byte j8 of the half's 8 scale bytes
+                    const uint32_t wsA = j8 < 4 ? scwA.x : scwA.y, wsB = j8 < 4 ? scwB.x : scwB.y;
+                    const int scA = (int)(signed char)((wsA >> (8 * (j8 & 3))) & 0xFF), scB = (int)(signed char)((wsB >> (8 * (j8 & 3))) & 0xFF);
+                    PA0 += scA * (c[0] - 32 * (int)sv.x); PA1 += scA * (c[1] - 32 * (int)sv.y);
+                    PB0 += scB * (c[2] - 32 * (int)sv.x); PB1 += scB * (c[3] - 32 * (int)sv.y);
                 }
             }
-            // lane holds columns 2t, 2t+1 = sub-blocks 2t, 2t+1 of this half; scales are int8
-            const float s0A = (float)(int)(signed char)(scA & 0xFF), s1A = (float)(int)(signed char)(scA >> 8);
-            const float s0B = (float)(int)(signed char)(scB & 0xFF), s1B = (float)(int)(signed char)(scB >> 8);
-            accA = prim::fma(dA, prim::fma(s0A, c[0], s1A * c[1]), accA);
-            accB = prim::fma(dB, prim::fma(s0B, c[2], s1B * c[3]), accB);
         }
+        const float dA = prim::h2f(prim::lds_u16(blk + 3328 + 2 * L.g)), dB = prim::h2f(prim::lds_u16(blk + 3328 + 2 * (L.g + 8)));
+        accA = prim::fma(dA, combine(PA0, PA1, L), accA);
+        accB = prim::fma(dB, combine(PB0, PB1, L), accB);
     }
 };
 
@@ -294,32 +250,21 @@ struct Q6K {
 struct Q80 {
     static constexpr int FMT = 8;
     static constexpr int STEP = 128;
-    static constexpr bool NEED_SV = false;
-    SLAI_HD static void init(LaneCtx& L, const Smem& S) {
-        for (int ci = 0; ci < 2; ci++) {
-            const BSel b = bsel_q8(L.lane, ci);
-            L.bp[ci] = b.off < 0 ? S.zero : (b.lo ? S.lo : S.hi) + 2 * b.off;
-            L.bs[ci] = b.off < 0 ? 0 : 2 * STEP;
-        }
-    }
+    static constexpr int SV_GRAN = 0;
     SLAI_HD static void compute(uint32_t blk, int step, const LaneCtx& L, const Smem& S, float& accA, float& accB) {
-        const float sA = prim::h2f(prim::lds_u16(blk + 8 * L.g + 2 * L.t)), sB = prim::h2f(prim::lds_u16(blk + 8 * (L.g + 8) + 2 * L.t));
-        float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int ci = 0; ci < 2; ci++) {
+            const int b = 2 * ci + (L.t >> 1);  // GGUF block inside the step
             const uint4 qA = prim::lds16(blk + 128 + (ci * 2) * 512 + 16 * L.lane), qB = prim::lds16(blk + 128 + (ci * 2 + 1) * 512 + 16 * L.lane);
-            const uint32_t p = L.bp[ci] + step * L.bs[ci];
-            const uint4 ba = prim::lds16(p), bb = prim::lds16(p + 16);
-#pragma unroll
-            for (int w = 0; w < 4; w++) {
-                uint32_t a0, a1, a2, a3;
-                q8_pair(w4(qA, w), a0, a2);
-                q8_pair(w4(qB, w), a1, a3);
-                prim::mma16816(c, a0, a1, a2, a3, w < 2 ? w4(ba, 2 * w) : w4(bb, 2 * w - 4), w < 2 ? w4(ba, 2 * w + 1) : w4(bb, 2 * w - 3));
-            }
+            uint4 bv = make_uint4(0u, 0u, 0u, 0u);
+            if (L.bact) bv = prim::lds16(L.bdig + 128 * step + 32 * b + 16 * (L.t & 1));
+            int c[4] = {0, 0, 0, 0};
+            prim::mma_s8(c, qA.x, qB.x, qA.y, qB.y, bv.x, bv.y);
+            prim::mma_s8(c, qA.z, qB.z, qA.w, qB.w, bv.z, bv.w);
+            const float sA = prim::h2f(prim::lds_u16(blk + 8 * L.g + 2 * b)), sB = prim::h2f(prim::lds_u16(blk + 8 * (L.g + 8) + 2 * b));
+            accA = prim::fma(sA, combine(c[0], c[1], L), accA);
+            accB = prim::fma(sB, combine(c[2], c[3], L), accB);
         }
-        accA = prim::fma(sA, c[0] + c[1], accA);
-        accB = prim::fma(sB, c[2] + c[3], accB);
     }
 };
 

@@ -16,8 +16,10 @@
 //   Q4_K  (2304 B): [hdr 16 x 16B: d,dmin,scales] [q(ci,ab): 32 lanes x 16B] for ci = 0,1 / ab = 0,1
 //                   lane (g,t) of q(ci,ab) holds qs bytes 16*(4ci+t) .. +15 of row g + 8ab
 //   Q5_K  (2816 B): [hdr 16 x 16B] [qh 16 x 32B] [q(ci,ab) as Q4_K]
-//   Q6_K  (3360 B): [ql(h,ab): 32 lanes x 16B, h = 0,1] [qh(h): 16 rows x 32B] [scales 16 x 16B] [d 16 x 2B]
-//                   lane (g,t) of ql(h,ab) holds ql bytes 64h + 16t .. +15 of row g + 8ab
+//   Q6_K  (3360 B): [ql(h,pair,ab): 32 lanes x 8B] [qh(h,ab): 32 lanes x 8B] [scales 16 x 16B] [d 16 x 2B]
+//                   lane (g,t) of ql(h,pair,ab) holds ql bytes 64h + 16(2 pair + t/2) + 8(t%2) .. +7 and lane
+//                   (g,t) of qh(h,ab) holds qh bytes 32h + 8t .. +7 of row g + 8ab: two lanes carry one
+//                   16-element sub-block, so an MMA sees two sub-blocks
 //   Q8_0  (2176 B): [scales 16 rows x 4 x f16] [q(ci,ab): 32 lanes x 16B]; a step is 4 blocks (128 values),
 //                   lane (g,t) of q(ci,ab) holds the int8 values 64ci + 16t .. +15 of the step
 //   F32           : dense row-major (no tiling).
@@ -55,6 +57,18 @@ SLAI_HD int qbyte_off(int region0, int r, int idx) {
     return region0 + (ci * 2 + ab) * 512 + 16 * (4 * g + t) + (idx & 15);
 }
 
+// Q6_K: offsets of ql byte idx (0..127) and qh byte idx (0..63) of row r.  The 64 ql bytes of half h are cut
+// into 8-byte pieces; piece (chunk c = idx/16 within the half, half-chunk) goes to lane 4g + 2(c&1) + piece of
+// region (h, pair = c/2, ab); the 32 qh bytes of half h go, 8 per lane, to lanes 4g + t of region (h, ab).
+SLAI_HD int q6_ql_off(int r, int idx) {
+    const int h = idx >> 6, i = idx & 63, c = i >> 4, pair = c >> 1, t = ((c & 1) << 1) | ((i >> 3) & 1), g = r & 7, ab = r >> 3;
+    return ((h * 2 + pair) * 2 + ab) * 256 + (4 * g + t) * 8 + (i & 7);
+}
+SLAI_HD int q6_qh_off(int r, int idx) {
+    const int h = idx >> 5, i = idx & 31, g = r & 7, ab = r >> 3;
+    return 2048 + (h * 2 + ab) * 256 + (4 * g + (i >> 3)) * 8 + (i & 7);
+}
+
 // Copy GGUF block number `blk` of row `row` (raw bytes at `src`) to its place in the tile-major matrix.
 SLAI_HD void place_block(int fmt, const uint8_t* src, uint8_t* data, int64_t row, int64_t blk, int64_t K) {
     const int64_t tile = row >> 4;
@@ -78,8 +92,8 @@ SLAI_HD void place_block(int fmt, const uint8_t* src, uint8_t* data, int64_t row
         for (int i = 0; i < 32; i++) d[256 + 32 * r + i] = src[16 + i];
         for (int i = 0; i < 128; i++) d[qbyte_off(768, r, i)] = src[48 + i];
     } else if (fmt == 14) {
-        for (int i = 0; i < 128; i++) d[qbyte_off(0, r, i)] = src[i];  // chunk c = 4h + t, h = ql half
-        for (int i = 0; i < 64; i++) d[2048 + (i >> 5) * 512 + 32 * r + (i & 31)] = src[128 + i];
+        for (int i = 0; i < 128; i++) d[q6_ql_off(r, i)] = src[i];
+        for (int i = 0; i < 64; i++) d[q6_qh_off(r, i)] = src[128 + i];
         for (int i = 0; i < 16; i++) d[3072 + 16 * r + i] = src[192 + i];
         d[3328 + 2 * r] = src[208];
         d[3328 + 2 * r + 1] = src[209];

@@ -200,9 +200,9 @@ __device__ float dequant_elem(int fmt, const uint8_t* data, long long K, long lo
     }
     // Q6_K
     const int hf = e >> 7, rr = e & 127, quarter = rr >> 5, l = rr & 31;
-    const uint8_t qlb = b[layout::qbyte_off(0, r, 64 * hf + l + 32 * (quarter & 1))];
+    const uint8_t qlb = b[layout::q6_ql_off(r, 64 * hf + l + 32 * (quarter & 1))];
     const int nib = quarter >= 2 ? (qlb >> 4) : (qlb & 0xF);
-    const uint8_t qhb = b[2048 + hf * 512 + 32 * r + l];
+    const uint8_t qhb = b[layout::q6_qh_off(r, 32 * hf + l)];
     const int q = (nib | (((qhb >> (2 * quarter)) & 3) << 4)) - 32;
     const int sc = (int)(signed char)b[3072 + 16 * r + 8 * hf + (l >> 4) + 2 * quarter];
     const float d = dev_h2f(b[3328 + 2 * r] | (b[3328 + 2 * r + 1] << 8));

@@ -32,9 +32,7 @@ struct Job {
 template <class F>
 static void lane_body(Job* J, int lane) {
     LaneCtx L;
-    L.lane = lane; L.g = lane >> 2; L.t = lane & 3;
-    for (int i = 0; i < 4; i++) { L.bp[i] = 0; L.bs[i] = 0; }
-    F::init(L, J->S);
+    lane_init(L, lane, J->S);
     float a = 0.f, b = 0.f;
     for (int s = 0; s < J->nsteps; s++) F::compute(J->tile0 + (uint32_t)s * J->step_bytes, s, L, J->S, a, b);
     J->acc[lane][0] = a;
@@ -84,35 +82,27 @@ int main(int argc, char** argv) {
     for (int r = 0; r < 16; r++)
         for (int b = 0; b < nbk; b++) layout::place_block(fmt, raw.data() + ((size_t)r * nbk + b) * bb, tile.data(), r, b, K);
 
-    // staging (mirrors stage_vector in gemv.cu with PRO_NONE)
+    // staging (mirrors stage_vector in gemv.cu with no prologue): power-of-two scale, integer rounding,
+    // four base-128 digit planes, per-sub-block digit sums
     const int Kp = (K + 255) & ~255;
-    const size_t tile_off = (size_t)(4 * Kp + 32 + (Kp / 32) * 4 + 127) & ~(size_t)127;
+    const int sv_gran = (fmt == 12 || fmt == 13) ? 32 : fmt == 14 ? 16 : 0;
+    const size_t sv_bytes = sv_gran ? (size_t)(Kp / sv_gran) * 16 : 0;
+    const size_t tile_off = (size_t)(4 * Kp + sv_bytes + 127) & ~(size_t)127;
     std::vector<unsigned char> smem(tile_off + tile.size() + 64, 0);
     memcpy(smem.data() + tile_off, tile.data(), tile.size());
     float mx = 0.f;
     for (int k = 0; k < K; k++) mx = fmaxf(mx, fabsf(v[k]));
     float scale = 1.f;
-    if (mx > 0.f) { int e; frexpf(mx, &e); if (e < -100) e = -100; scale = ldexpf(1.0f, 14 - e); }
-    __half* hi = (__half*)smem.data();
-    __half* lo = hi + Kp;
-    float* sv = (float*)(smem.data() + 4 * Kp + 32);
+    if (mx > 0.f) { int e; frexpf(mx, &e); if (e < -90) e = -90; scale = ldexpf(1.0f, 26 - e); }
+    int* sv = (int*)(smem.data() + 4 * Kp);
     for (int k = 0; k < Kp; k++) {
         const float x = k < K ? v[k] * scale : 0.f;
-        const __half h = __float2half_rn(x);
-        hi[frag::perm4(k)] = h;
-        lo[frag::perm4(k)] = __float2half_rn(x - __half2float(h));
-    }
-    for (int j = 0; j < Kp / 32; j++) {
-        float s = 0.f;  // same association as the kernel: ((x0+x1)+(x2+x3)) then a xor-tree over 8 lanes
-        float part[8];
-        for (int q = 0; q < 8; q++) {
-            float x[4];
-            for (int i = 0; i < 4; i++) { int k = 32 * j + 4 * q + i; x[i] = k < K ? v[k] * scale : 0.f; }
-            part[q] = (x[0] + x[1]) + (x[2] + x[3]);
+        int d[4];
+        frag::split_digits((int)nearbyintf(x), d);
+        for (int p = 0; p < 4; p++) {
+            smem[(size_t)p * Kp + k] = (unsigned char)(d[p] & 0xFF);
+            if (sv_gran) sv[(k / sv_gran) * 4 + p] += d[p];
         }
-        for (int o = 1; o < 8; o <<= 1) { float n[8]; for (int q = 0; q < 8; q++) n[q] = part[q] + part[q ^ o]; memcpy(part, n, sizeof n); }
-        s = part[0];
-        sv[j] = s;
     }
 
     hostemu::Warp W;
@@ -121,7 +111,7 @@ int main(int argc, char** argv) {
     Job J;
     J.fmt = fmt; J.K = K; J.W = &W;
     J.nsteps = nsteps; J.tile0 = (uint32_t)tile_off; J.step_bytes = sbytes;
-    J.S.hi = 0; J.S.lo = 2 * Kp; J.S.zero = 4 * Kp; J.S.sv = 4 * Kp + 32;
+    J.S.dig = 0; J.S.plane = Kp; J.S.sv = 4 * Kp;
     pthread_t th[32];
     ThreadArg args[32];
     for (int l = 0; l < 32; l++) { args[l] = {&J, l}; pthread_create(&th[l], nullptr, thread_main, &args[l]); }
