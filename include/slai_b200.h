@@ -160,6 +160,24 @@ typedef struct slai_attn_params {
  * (f32 or f16), head h at offset h*head_size.  The score buffer of the reference (`attn`) is internal. */
 int slai_attention(slai_ctx* ctx, const slai_attn_params* p, const float* d_q, const void* d_key_cache,
                    const void* d_value_cache, int kv_dtype, float* d_xb);
+/* ---- slai_attention for callers that may not allocate.  This entry point has no counterpart in the
+ * reference (whose scratch tensors always come from its backend's allocator).
+ * Same arguments and result as slai_attention, but the call reaches no allocator at all (no cudaMalloc /
+ * cudaFree, nothing that allocates behind the scenes): the split partials, the per-head tickets and the
+ * position scalar live in a device array that is part of the library image, SLAI_ATTENTION_STATIC_MAX_SCRATCH_BYTES
+ * (+ 4 KiB) per GPU that loads the library, held until the process exits.  It is meant for hosts that receive
+ * their device memory once and must stay off the driver allocator afterwards (an engine that partitions the GPU
+ * among its subsystems, a serving loop whose latency path may not synchronise on cudaMalloc / cudaFree).
+ *  - Shapes whose partials exceed the array are rejected with SLAI_ERR_SHAPE and a message naming both sizes;
+ *    use slai_attention for those.
+ *  - The first call on a device resolves the array's device address (cudaGetSymbolAddress) with that device made
+ *    current; make that first call before starting any stream capture.
+ *  - All calls share the one array and it keeps the last call's contents: each call re-zeroes the tickets it uses
+ *    and rewrites the position; two calls whose kernels overlap on the GPU (different contexts / streams on the
+ *    same device) race on it.  Calls on one context are ordered by its stream and are safe. */
+#define SLAI_ATTENTION_STATIC_MAX_SCRATCH_BYTES (4u << 20)
+int slai_attention_static(slai_ctx* ctx, const slai_attn_params* p, const float* d_q, const void* d_key_cache,
+                          const void* d_value_cache, int kv_dtype, float* d_xb);
 /* Writes the kv_dim-float vectors k and v into position `pos` of the caches (the reference lets the K/V
  * GEMVs write into `key_cache.column(pos)` directly, transformer.rs:329-334). */
 int slai_kv_append(slai_ctx* ctx, void* d_key_cache, void* d_value_cache, int kv_dtype, const float* d_k,

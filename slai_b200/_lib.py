@@ -87,6 +87,7 @@ SIGNATURES = {
     "slai_copy": (C.c_int, [_vp, _vp, _vp, _i64]),
     "slai_argmax": (C.c_int, [_vp, _vp, _i64, _vp]),
     "slai_attention": (C.c_int, [_vp, C.POINTER(AttnParams), _vp, _vp, _vp, C.c_int, _vp]),
+    "slai_attention_static": (C.c_int, [_vp, C.POINTER(AttnParams), _vp, _vp, _vp, C.c_int, _vp]),
     "slai_kv_append": (C.c_int, [_vp, _vp, _vp, C.c_int, _vp, _vp, C.c_int, C.c_int]),
     "slai_llama_create": (C.c_int, [_vp, C.POINTER(LlamaConfig), _pp]),
     "slai_llama_destroy": (C.c_int, [_vp]),

@@ -292,3 +292,85 @@ int attention_launch(slai_ctx* ctx, const AttnLaunch& A) {
     if (A.kv_mul <= 4) return f16 ? launch_t<__half, 4>(ctx, P, n_kv, smem, A.pdl) : launch_t<float, 4>(ctx, P, n_kv, smem, A.pdl);
     return f16 ? launch_t<__half, 8>(ctx, P, n_kv, smem, A.pdl) : launch_t<float, 8>(ctx, P, n_kv, smem, A.pdl);
 }
+
+// =================================================================================================
+// Attention without any allocation (slai_attention_static).
+//
+// Some hosts hand every component its device memory once, up front, and then forbid further calls into the
+// driver's allocator (a game or simulation engine embedding the model next to its own buffers, a serving
+// process whose latency path must never reach cudaMalloc / cudaFree because both synchronise the device and can
+// fail late).  `slai_attention` grows a per-context scratch buffer on demand, so such callers cannot use it.
+// This variant keeps the flash-decoding partials, the per-head tickets and the position scalar in one
+// file-scope device array of fixed size that every GPU loading the library holds until the process exits.
+//
+// The array's name is only a host-side handle: its device address is looked up once per device with
+// cudaGetSymbolAddress while that device is current, and the kernel is given that address.
+// =================================================================================================
+namespace {
+
+constexpr size_t STATIC_PART_BYTES = SLAI_ATTENTION_STATIC_MAX_SCRATCH_BYTES;  // split partials
+constexpr size_t STATIC_TICKET_BYTES = 4096;                                  // one ticket per KV head (<= 1024)
+constexpr int STATIC_MAX_DEVICES = 64;
+
+static __device__ __align__(256) unsigned char g_attn_static[STATIC_PART_BYTES + STATIC_TICKET_BYTES + 256];
+static unsigned char* g_attn_static_ptr[STATIC_MAX_DEVICES];  // device address of the array, per device
+
+__global__ void static_set_pos_kernel(int* dst, int pos) { *dst = pos; }
+
+}  // namespace
+
+SLAI_API int slai_attention_static(slai_ctx* ctx, const slai_attn_params* p, const float* d_q, const void* d_key_cache,
+                                   const void* d_value_cache, int kv_dtype, float* d_xb) {
+    if (!ctx || !p || !d_q || !d_key_cache || !d_value_cache || !d_xb) return SLAI_ERR_INVALID_ARG;
+    SLAI_REQUIRE(ctx, p->pos < p->seq_len, SLAI_ERR_SHAPE, "attention: pos=%u >= seq_len=%u", p->pos, p->seq_len);
+    SLAI_REQUIRE(ctx, p->kv_mul >= 1 && p->kv_mul <= 8 && p->n_heads % p->kv_mul == 0 &&
+                          p->kv_dim == p->n_heads / p->kv_mul * p->head_size,
+                 SLAI_ERR_SHAPE, "attention: inconsistent head counts");
+    SLAI_REQUIRE(ctx, p->head_size % 2 == 0 && p->head_size <= 64 * MAX_J, SLAI_ERR_SHAPE,
+                 "attention: head_size=%u must be even and <= %d", p->head_size, 64 * MAX_J);
+    SLAI_REQUIRE(ctx, kv_dtype == SLAI_KV_F16 || kv_dtype == SLAI_KV_F32, SLAI_ERR_INVALID_ARG, "attention: unknown cache type");
+    const int n_heads = (int)p->n_heads, kv_mul = (int)p->kv_mul, hs = (int)p->head_size, pos = (int)p->pos;
+    const int n_kv = n_heads / kv_mul;
+    SLAI_REQUIRE(ctx, n_kv <= 1024, SLAI_ERR_SHAPE, "attention: too many KV heads");
+    SLAI_REQUIRE(ctx, ctx->device >= 0 && ctx->device < STATIC_MAX_DEVICES, SLAI_ERR_INVALID_ARG, "attention: device index out of range");
+
+    const int n_splits = pick_splits(ctx, n_kv, pos + 1);
+    const int chunk_max = (pos + 1 + n_splits - 1) / n_splits;
+    const size_t po = (size_t)n_heads * n_splits * hs * 4;
+    const size_t need = attention_scratch_bytes(ctx, n_heads, kv_mul, hs, pos);
+    SLAI_REQUIRE(ctx, need <= STATIC_PART_BYTES, SLAI_ERR_SHAPE,
+                 "slai_attention_static: this shape needs %zu bytes of split scratch, the built-in array holds %zu "
+                 "(use slai_attention, which allocates)", need, STATIC_PART_BYTES);
+
+    // Set-up, once per device: resolve the array's device address with that device current.
+    SLAI_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (!g_attn_static_ptr[ctx->device]) {
+        void* sym = nullptr;
+        SLAI_CHECK_CUDA(ctx, cudaGetSymbolAddress(&sym, g_attn_static));
+        g_attn_static_ptr[ctx->device] = reinterpret_cast<unsigned char*>(sym);
+    }
+    unsigned char* base = g_attn_static_ptr[ctx->device];
+    unsigned int* tickets = reinterpret_cast<unsigned int*>(base + STATIC_PART_BYTES);
+    int* d_pos = reinterpret_cast<int*>(base + STATIC_PART_BYTES + STATIC_TICKET_BYTES);
+
+    // The array keeps whatever the last call left: the tickets must start at zero, the position is rewritten.
+    SLAI_CHECK_CUDA(ctx, cudaMemsetAsync(tickets, 0, (size_t)n_kv * sizeof(unsigned int), ctx->stream));
+    static_set_pos_kernel<<<1, 1, 0, ctx->stream>>>(d_pos, pos);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+
+    AttnParams P;
+    P.q = d_q; P.kc = d_key_cache; P.vc = d_value_cache;
+    P.pos_stride = p->kv_dim; P.head_stride = hs;
+    P.n_heads = n_heads; P.kv_mul = kv_mul; P.hs = hs;
+    P.d_pos = d_pos; P.n_splits = n_splits; P.chunk_max = chunk_max;
+    P.out = d_xb;
+    P.part_o = reinterpret_cast<float*>(base);
+    P.part_ml = reinterpret_cast<float*>(base + ((po + 255) & ~(size_t)255));
+    P.counters = tickets;
+    const size_t smem = (size_t)4 * (kv_mul * hs + kv_mul * chunk_max + ATT_WARPS * kv_mul * hs + 2 * kv_mul);
+    SLAI_REQUIRE(ctx, smem <= 160 * 1024, SLAI_ERR_SHAPE, "attention: shared memory %zu too large", smem);
+    const bool f16 = kv_dtype == SLAI_KV_F16;
+    if (kv_mul == 1) return f16 ? launch_t<__half, 1>(ctx, P, n_kv, smem, false) : launch_t<float, 1>(ctx, P, n_kv, smem, false);
+    if (kv_mul <= 4) return f16 ? launch_t<__half, 4>(ctx, P, n_kv, smem, false) : launch_t<float, 4>(ctx, P, n_kv, smem, false);
+    return f16 ? launch_t<__half, 8>(ctx, P, n_kv, smem, false) : launch_t<float, 8>(ctx, P, n_kv, smem, false);
+}
