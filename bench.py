@@ -238,8 +238,11 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--gemv", action="store_true", help="also run the 16-case quantised GEMV microbenchmark")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--prompt-len", type=int, default=512, help="prompt length (512 = the benchmark; smaller for profiling)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    global PROMPT_LEN
+    PROMPT_LEN = args.prompt_len
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

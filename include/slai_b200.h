@@ -87,10 +87,10 @@ int slai_timer_stop(slai_ctx* ctx, float* ms); /* records, waits, returns elapse
 
 /* ---- quantized matrices: GgufTensor::to_gpu_matrix (gguf.rs:133-194,357-366) ------------------------- */
 /* `h_blocks`: nrows rows of (ncols / block_elems) GGUF blocks, row-major, exactly the file's bytes.
- * Q8_0 and Q6_K rows are re-laid-out on upload into 16-byte aligned planes (same byte count, rows
- * padded to 16 bytes); Q4_K / Q5_K keep the file layout; F32 is kept dense.  Unlike the reference there
- * is no "dequantise when the block count is odd" fallback: every shape with ncols % block_elems == 0
- * stays quantized. */
+ * On upload the blocks are re-laid-out tile-major (16 rows x one K step per contiguous block, same byte
+ * count up to zero padding of the last tile) so that the kernels stream them with bulk copies; F32 is
+ * kept dense.  Unlike the reference there is no "dequantise when the block count is odd" fallback:
+ * every shape with ncols % block_elems == 0 stays quantized. */
 int slai_qmatrix_create(slai_ctx* ctx, int fmt, int64_t nrows, int64_t ncols, const void* h_blocks, size_t nbytes,
                         slai_qmatrix** out);
 /* Same, with the raw blocks already in device memory. */

@@ -10,10 +10,10 @@
 // of shared-memory stages: one lane issues a bulk asynchronous copy (cp.async.bulk, completion counted on an
 // mbarrier) per block, always NSTAGE blocks ahead of the block being consumed and running on across item
 // boundaries, so the bytes in flight per SM are set by the ring size (100-180 KB), not by registers or
-// occupancy.  The consumer side expands the packed quants to exact f16 pairs and feeds mma.sync.m16n8k16
-// against the activation vector staged once per block of threads in shared memory (gemv_frag.cuh); scales are
-// applied to the per-sub-block sums in f32; the lanes of a row are reduced by shuffles, the warps of an item
-// through shared memory in a fixed order (deterministic).
+// occupancy.  The consumer side feeds the packed quants, four per register, to the integer tensor-core MMA
+// (mma.sync.m16n8k32 s8) against base-128 digit planes of the activation vector, staged once per block of
+// threads in shared memory (gemv_frag.cuh); block scales are applied to the per-sub-block integer sums; the lanes
+// of a row are reduced by shuffles, the warps of an item through shared memory in a fixed order (deterministic).
 //
 // The first NSTAGE copies are issued before `griddepcontrol.wait`, so under programmatic dependent launch
 // the weight stream starts while the kernel that produces the activation vector is still finishing.
@@ -249,11 +249,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_kernel(const GemvParams P) {
     const uint32_t sv_bytes = (uint32_t)(Kp >> 8) * SV_BYTES_PER_256;
     Smem S;
     S.dig = (uint32_t)__cvta_generic_to_shared(smem_raw);
-    S.plane = Kp;
-    S.sv = S.dig + 4 * Kp;
-    float* red = reinterpret_cast<float*>(smem_raw + 4 * Kp + sv_bytes);
+    S.plane = Kp + 32;  // planes 32 bytes apart modulo 128: the four digit columns of a sub-block hit different banks
+    S.sv = S.dig + 4 * S.plane;
+    float* red = reinterpret_cast<float*>(smem_raw + 4 * S.plane + sv_bytes);
     float* stat = red + WARPS * 32;
-    const uint32_t fixed = (uint32_t)(4 * Kp) + sv_bytes + WARPS * 32 * 4 + 64 * 4;
+    const uint32_t fixed = (uint32_t)(4 * S.plane) + sv_bytes + WARPS * 32 * 4 + 64 * 4;
     const uint32_t mbar_base = S.dig + fixed;
     const uint32_t ring_base = (mbar_base + WARPS * MAX_STAGES * 8 + 127u) & ~127u;
 
@@ -522,7 +522,7 @@ int gemv_launch(slai_ctx* ctx, const GemvLaunch& L) {
     const int Kp = (K + 255) & ~255;
     const int sv_gran = (L.fmt == SLAI_FMT_Q4_K || L.fmt == SLAI_FMT_Q5_K) ? 32 : L.fmt == SLAI_FMT_Q6_K ? 16 : 0;
     const size_t sv_bytes = sv_gran ? (size_t)(Kp / sv_gran) * 16 : 0;
-    const size_t fixed = (size_t)4 * Kp + sv_bytes + WARPS * 32 * 4 + 64 * 4 + WARPS * MAX_STAGES * 8 + 128;
+    const size_t fixed = (size_t)4 * (Kp + 32) + sv_bytes + WARPS * 32 * 4 + 64 * 4 + WARPS * MAX_STAGES * 8 + 128;
     const size_t per_stage = (size_t)WARPS * P.stage_stride;
     SLAI_REQUIRE(ctx, fixed + 2 * per_stage <= SMEM_LIMIT, SLAI_ERR_SHAPE, "gemv: K=%d does not fit in shared memory", K);
     static int stage_env = -1, ks_env = -1;

@@ -35,6 +35,35 @@ SLAI_HD uint4 lds16(uint32_t addr) {
     return r;
 #endif
 }
+// Predicated loads: lanes with pred == false get zeros and do not touch shared memory (no branch).
+SLAI_HD uint4 lds16_if(bool pred, uint32_t addr) {
+#ifdef __CUDA_ARCH__
+    uint4 r;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %5, 0;\n\tmov.u32 %0, 0;\n\tmov.u32 %1, 0;\n\tmov.u32 %2, 0;\n\tmov.u32 %3, 0;\n\t"
+        "@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n\t}"
+        : "=&r"(r.x), "=&r"(r.y), "=&r"(r.z), "=&r"(r.w)
+        : "r"(addr), "r"((uint32_t)pred));
+    return r;
+#else
+    uint4 r = make_uint4(0u, 0u, 0u, 0u);
+    if (pred) memcpy(&r, hostemu::warp->smem + addr, 16);
+    return r;
+#endif
+}
+SLAI_HD uint2 lds8_if(bool pred, uint32_t addr) {
+#ifdef __CUDA_ARCH__
+    uint2 r;
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %3, 0;\n\tmov.u32 %0, 0;\n\tmov.u32 %1, 0;\n\t@p ld.shared.v2.u32 {%0,%1}, [%2];\n\t}"
+                 : "=&r"(r.x), "=&r"(r.y)
+                 : "r"(addr), "r"((uint32_t)pred));
+    return r;
+#else
+    uint2 r = make_uint2(0u, 0u);
+    if (pred) memcpy(&r, hostemu::warp->smem + addr, 8);
+    return r;
+#endif
+}
 SLAI_HD uint2 lds8(uint32_t addr) {
 #ifdef __CUDA_ARCH__
     uint2 r;
@@ -78,7 +107,7 @@ SLAI_HD float fma(float a, float b, float c) {
 //   b0 = B[4t..4t+3][g], b1 = B[16+4t..][g];   c0,c1 = D[g][2t..2t+1], c2,c3 = D[g+8][2t..2t+1]
 SLAI_HD void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
 #ifdef __CUDA_ARCH__
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -170,8 +199,7 @@ struct K45 {
 #pragma unroll
             for (int nib = 0; nib < 2; nib++) {
                 const int j = 4 * ci + 2 * (L.t >> 1) + nib;  // sub-block (of 32) inside the super-block
-                uint4 bv = make_uint4(0u, 0u, 0u, 0u);
-                if (L.bact) bv = prim::lds16(L.bdig + 256 * step + 32 * j + 16 * (L.t & 1));
+                const uint4 bv = prim::lds16_if(L.bact, L.bdig + 256 * step + 32 * j + 16 * (L.t & 1));
                 int c[4] = {0, 0, 0, 0};
                 if (FIVE) {
                     prim::mma_s8(c, q5_nibs(qA.x, hAx, nib), q5_nibs(qB.x, hBx, nib), q5_nibs(qA.y, hAy, nib), q5_nibs(qB.y, hBy, nib), bv.x, bv.y);
@@ -226,8 +254,7 @@ struct Q6K {
                     const int sh = 2 * pair + 4 * nib;
                     const int j8 = 4 * nib + 2 * pair + (L.t >> 1);  // sub-block (of 16) inside the half
                     const int j = 16 * step + 8 * h + j8;
-                    uint2 bv = make_uint2(0u, 0u);
-                    if (L.bact) bv = prim::lds8(L.bdig + 16 * j + 8 * (L.t & 1));
+                    const uint2 bv = prim::lds8_if(L.bact, L.bdig + 16 * j + 8 * (L.t & 1));
                     int c[4] = {0, 0, 0, 0};
                     prim::mma_s8(c, q6_nibs(qlA.x, qhA.x >> sh, nib), q6_nibs(qlB.x, qhB.x >> sh, nib), q6_nibs(qlA.y, qhA.y >> sh, nib),
                                  q6_nibs(qlB.y, qhB.y >> sh, nib), bv.x, bv.y);
@@ -256,8 +283,7 @@ struct Q80 {
         for (int ci = 0; ci < 2; ci++) {
             const int b = 2 * ci + (L.t >> 1);  // GGUF block inside the step
             const uint4 qA = prim::lds16(blk + 128 + (ci * 2) * 512 + 16 * L.lane), qB = prim::lds16(blk + 128 + (ci * 2 + 1) * 512 + 16 * L.lane);
-            uint4 bv = make_uint4(0u, 0u, 0u, 0u);
-            if (L.bact) bv = prim::lds16(L.bdig + 128 * step + 32 * b + 16 * (L.t & 1));
+            const uint4 bv = prim::lds16_if(L.bact, L.bdig + 128 * step + 32 * b + 16 * (L.t & 1));
             int c[4] = {0, 0, 0, 0};
             prim::mma_s8(c, qA.x, qB.x, qA.y, qB.y, bv.x, bv.y);
             prim::mma_s8(c, qA.z, qB.z, qA.w, qB.w, bv.z, bv.w);

@@ -87,20 +87,21 @@ int main(int argc, char** argv) {
     const int Kp = (K + 255) & ~255;
     const int sv_gran = (fmt == 12 || fmt == 13) ? 32 : fmt == 14 ? 16 : 0;
     const size_t sv_bytes = sv_gran ? (size_t)(Kp / sv_gran) * 16 : 0;
-    const size_t tile_off = (size_t)(4 * Kp + sv_bytes + 127) & ~(size_t)127;
+    const int plane = Kp + 32;
+    const size_t tile_off = (size_t)(4 * plane + sv_bytes + 127) & ~(size_t)127;
     std::vector<unsigned char> smem(tile_off + tile.size() + 64, 0);
     memcpy(smem.data() + tile_off, tile.data(), tile.size());
     float mx = 0.f;
     for (int k = 0; k < K; k++) mx = fmaxf(mx, fabsf(v[k]));
     float scale = 1.f;
     if (mx > 0.f) { int e; frexpf(mx, &e); if (e < -90) e = -90; scale = ldexpf(1.0f, 26 - e); }
-    int* sv = (int*)(smem.data() + 4 * Kp);
+    int* sv = (int*)(smem.data() + 4 * plane);
     for (int k = 0; k < Kp; k++) {
         const float x = k < K ? v[k] * scale : 0.f;
         int d[4];
         frag::split_digits((int)nearbyintf(x), d);
         for (int p = 0; p < 4; p++) {
-            smem[(size_t)p * Kp + k] = (unsigned char)(d[p] & 0xFF);
+            smem[(size_t)p * plane + k] = (unsigned char)(d[p] & 0xFF);
             if (sv_gran) sv[(k / sv_gran) * 4 + p] += d[p];
         }
     }
@@ -111,7 +112,7 @@ int main(int argc, char** argv) {
     Job J;
     J.fmt = fmt; J.K = K; J.W = &W;
     J.nsteps = nsteps; J.tile0 = (uint32_t)tile_off; J.step_bytes = sbytes;
-    J.S.dig = 0; J.S.plane = Kp; J.S.sv = 4 * Kp;
+    J.S.dig = 0; J.S.plane = plane; J.S.sv = 4 * plane;
     pthread_t th[32];
     ThreadArg args[32];
     for (int l = 0; l < 32; l++) { args[l] = {&J, l}; pthread_create(&th[l], nullptr, thread_main, &args[l]); }

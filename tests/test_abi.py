@@ -31,6 +31,12 @@ def test_every_declared_symbol_is_exported(lib):
     assert sorted(_lib.SIGNATURES) == names  # the Python binding covers exactly the header
 
 
+def test_rust_binding_source_covers_the_header():
+    rs = open(os.path.join(ROOT, "rust", "slai-b200-sys", "src", "lib.rs")).read()
+    missing = [n for n in header_functions() if f"pub fn {n}(" not in rs]
+    assert not missing, missing
+
+
 def test_header_cites_reference_interfaces():
     src = open(os.path.join(ROOT, "include", "slai_b200.h")).read()
     for cite in ("gemv_quant.rs:206-312", "rms_norm.rs:35-67", "rope.rs:45-85", "silu.rs:24-48", "softmax.rs:22-40",
