@@ -180,22 +180,30 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnParams P) {
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    // Merge the splits of this KV head (fixed order over splits).
+    // Merge the splits of this KV head (fixed order over splits).  The (max, sum) pairs of all splits are first
+    // brought into shared memory with independent loads, then every thread merges one output element.
+    float* ml_all = red_s;  // kv_mul * n_splits * 2 floats (n_splits <= 64 <= 2 * head_size fits the reduce buffer)
+    {
+        const float* src = P.part_ml + (size_t)kvh * kv_mul * P.n_splits * 2;
+        for (int i = tid; i < kv_mul * P.n_splits * 2; i += ATT_THREADS) ml_all[i] = __ldcg(src + i);
+    }
+    __syncthreads();
     for (int i = tid; i < kv_mul * hs; i += ATT_THREADS) {
         const int h = i / hs, d = i % hs;
         const int head = kvh * kv_mul + h;
-        const float* ml = P.part_ml + (size_t)head * P.n_splits * 2;
+        const float* ml = ml_all + h * P.n_splits * 2;
         float M = -INFINITY;
         for (int s = 0; s < P.n_splits; s++)
-            if (__ldcg(ml + 2 * s + 1) > 0.f) M = fmaxf(M, __ldcg(ml + 2 * s));
+            if (ml[2 * s + 1] > 0.f) M = fmaxf(M, ml[2 * s]);
+        const float* po = P.part_o + ((size_t)head * P.n_splits) * hs + d;
         float num = 0.f, den = 0.f;
+#pragma unroll 8
         for (int s = 0; s < P.n_splits; s++) {
-            const float l = __ldcg(ml + 2 * s + 1);
-            if (l > 0.f) {
-                const float w = expf(__ldcg(ml + 2 * s) - M);
-                num = fmaf(w, __ldcg(P.part_o + ((size_t)head * P.n_splits + s) * hs + d), num);
-                den = fmaf(w, l, den);
-            }
+            const float l = ml[2 * s + 1];
+            const float o = l > 0.f ? __ldcg(po + (size_t)s * hs) : 0.f;
+            const float w = l > 0.f ? expf(ml[2 * s] - M) : 0.f;
+            num = fmaf(w, o, num);
+            den = fmaf(w, l, den);
         }
         P.out[(size_t)head * hs + d] = num / den;
     }
@@ -243,6 +251,7 @@ static int pick_splits(slai_ctx* ctx, int n_kv, int n_max) {
     int n_splits = (2 * ctx->sm_count + n_kv - 1) / n_kv;
     if (n_splits > (n_max + 31) / 32) n_splits = (n_max + 31) / 32;
     if (n_splits < 1) n_splits = 1;
+    if (n_splits > 64) n_splits = 64;
     while ((n_max + n_splits - 1) / n_splits > 1024) n_splits++;
     return n_splits;
 }
@@ -287,6 +296,7 @@ int attention_launch(slai_ctx* ctx, const AttnLaunch& A) {
     P.counters = ctx->d_counters;
     const size_t smem = (size_t)4 * (A.kv_mul * A.head_size + A.kv_mul * chunk_max + ATT_WARPS * A.kv_mul * A.head_size + 2 * A.kv_mul);
     SLAI_REQUIRE(ctx, smem <= 160 * 1024, SLAI_ERR_SHAPE, "attention: shared memory %zu too large", smem);
+    SLAI_REQUIRE(ctx, n_splits <= 2 * P.hs, SLAI_ERR_SHAPE, "attention: context too long for head_size=%d", P.hs);
     const bool f16 = A.kv_dtype == SLAI_KV_F16;
     if (A.kv_mul == 1) return f16 ? launch_t<__half, 1>(ctx, P, n_kv, smem, A.pdl) : launch_t<float, 1>(ctx, P, n_kv, smem, A.pdl);
     if (A.kv_mul <= 4) return f16 ? launch_t<__half, 4>(ctx, P, n_kv, smem, A.pdl) : launch_t<float, 4>(ctx, P, n_kv, smem, A.pdl);
@@ -369,6 +379,7 @@ SLAI_API int slai_attention_static(slai_ctx* ctx, const slai_attn_params* p, con
     P.counters = tickets;
     const size_t smem = (size_t)4 * (kv_mul * hs + kv_mul * chunk_max + ATT_WARPS * kv_mul * hs + 2 * kv_mul);
     SLAI_REQUIRE(ctx, smem <= 160 * 1024, SLAI_ERR_SHAPE, "attention: shared memory %zu too large", smem);
+    SLAI_REQUIRE(ctx, n_splits <= 2 * P.hs, SLAI_ERR_SHAPE, "attention: context too long for head_size=%d", P.hs);
     const bool f16 = kv_dtype == SLAI_KV_F16;
     if (kv_mul == 1) return f16 ? launch_t<__half, 1>(ctx, P, n_kv, smem, false) : launch_t<float, 1>(ctx, P, n_kv, smem, false);
     if (kv_mul <= 4) return f16 ? launch_t<__half, 4>(ctx, P, n_kv, smem, false) : launch_t<float, 4>(ctx, P, n_kv, smem, false);

@@ -5,15 +5,19 @@
 //              q/k/v split with RoPE (ops/rope.rs:88-125) and KV-cache append (transformer.rs:329-334)
 //
 // Kernel shape.  One persistent block of 16 warps per SM.  The weights are stored tile-major (layout.cuh):
-// the packed data of 16 rows x one K step is one contiguous block.  A work item is one 16-row tile; `ks`
-// warps share an item and split its K range into contiguous runs of blocks.  Every warp owns a private ring
-// of shared-memory stages: one lane issues a bulk asynchronous copy (cp.async.bulk, completion counted on an
-// mbarrier) per block, always NSTAGE blocks ahead of the block being consumed and running on across item
-// boundaries, so the bytes in flight per SM are set by the ring size (100-180 KB), not by registers or
-// occupancy.  The consumer side feeds the packed quants, four per register, to the integer tensor-core MMA
+// the packed data of 16 rows x one K step is one contiguous block.  Work is divided in two levels so that
+// every SM and every warp gets the same amount (+-1 block) whatever the matrix shape: the 16-row tiles are
+// dealt out in contiguous, equal runs to the thread blocks; inside a block of threads the run's sequence of
+// (tile, matrix, K-step) units is cut into 16 equal contiguous pieces, one per warp.  A warp's piece may
+// cover the end of one tile and the start of the next; its partial row sums go to shared memory, and after
+// a barrier the 16 partials of every row are added in warp order (deterministic) and the epilogue runs.
+//
+// Data movement: every warp owns a private ring of shared-memory stages; one lane issues a bulk asynchronous
+// copy (cp.async.bulk, completion counted on an mbarrier) per block, always NSTAGE blocks ahead of the block
+// being consumed, so the bytes in flight per SM are set by the ring size (100-180 KB), not by registers or
+// occupancy.  Arithmetic: packed quants, four per register, go to the integer tensor-core MMA
 // (mma.sync.m16n8k32 s8) against base-128 digit planes of the activation vector, staged once per block of
-// threads in shared memory (gemv_frag.cuh); block scales are applied to the per-sub-block integer sums; the lanes
-// of a row are reduced by shuffles, the warps of an item through shared memory in a fixed order (deterministic).
+// threads in shared memory (gemv_frag.cuh); block scales are applied to the per-sub-block integer sums.
 //
 // The first NSTAGE copies are issued before `griddepcontrol.wait`, so under programmatic dependent launch
 // the weight stream starts while the kernel that produces the activation vector is still finishing.
@@ -31,7 +35,9 @@ using namespace gemvfmt;
 constexpr int THREADS = 512;
 constexpr int WARPS = 16;
 constexpr int MAX_STAGES = 8;
+constexpr int WAVE = 8;  // tiles whose partial sums are held in shared memory at a time
 constexpr int SMEM_LIMIT = 227 * 1024;
+constexpr int STAGE_REGS = 6;  // float4 per thread kept in registers between the staging passes (K <= 12288)
 
 struct GemvParams {
     GemvSeg seg[3];
@@ -39,7 +45,6 @@ struct GemvParams {
     int K;
     int n_items;     // 16-row tiles (dual launch: tiles of seg[0])
     int nsteps;      // tile-step blocks per tile
-    int ks;          // warps per item
     int nstage;      // ring depth per warp
     int step_bytes;  // bytes of a tile-step block
     int stage_stride;
@@ -122,49 +127,70 @@ __device__ __forceinline__ void block_sum_max(float& s, float& m, float* stat) {
     m = tm;
 }
 
+__device__ __forceinline__ float max4(const float4& x) { return fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w))); }
+
 // Stage the activation vector: optional normalisation, power-of-two scaling so that max|v| lands in
 // [2^25, 2^26), rounding to integers, split into four base-128 digit planes (gemv_frag.cuh), and per-sub-block
 // digit sums (for the `- dmin*m * sum(v)` term of Q4_K / Q5_K and the -32 offset of Q6_K).  Returns 1/scale.
-template <int PRO, int SV_GRAN>
-__device__ float stage_vector(const GemvParams& P, const Smem& S, float* stat, int Kp) {
+// The vector is read from global memory once and kept in registers between the passes when K <= 12288.
+template <int PRO, int SV_GRAN, bool CACHED>
+__device__ float stage_impl(const GemvParams& P, const Smem& S, float* stat, int Kp) {
     const int K = P.K;
     const int tid = threadIdx.x;
     const float4* v4 = reinterpret_cast<const float4*>(P.v);
-    const int n4 = K >> 2;
+    const float4* w4p = reinterpret_cast<const float4*>(P.norm_w);
+    const float4* b4p = reinterpret_cast<const float4*>(P.norm_b);
+    const int n4 = K >> 2, np4 = Kp >> 2;
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 xr[CACHED ? STAGE_REGS : 1];
+    if (CACHED) {
+#pragma unroll
+        for (int r = 0; r < STAGE_REGS; r++) {
+            const int i = tid + r * THREADS;
+            xr[r] = i < n4 ? __ldg(v4 + i) : zero4;
+        }
+    }
+    // element group of register slot r (CACHED) or of loop round r (not CACHED)
+#define SLAI_STAGE_LOOP(...)                                                            \
+    if (CACHED) {                                                                       \
+        _Pragma("unroll") for (int r = 0; r < STAGE_REGS; r++) {                        \
+            const int i = tid + r * THREADS;                                            \
+            float4 x = xr[r];                                                           \
+            __VA_ARGS__                                                                    \
+        }                                                                               \
+    } else {                                                                            \
+        for (int i = tid; i < np4; i += THREADS) {                                      \
+            float4 x = i < n4 ? __ldg(v4 + i) : zero4;                                  \
+            __VA_ARGS__                                                                    \
+        }                                                                               \
+    }
     float mul = 1.f, sub = 0.f;
     float sum = 0.f, mx = 0.f;
     if (PRO == PRO_LN) {
-        for (int i = tid; i < n4; i += THREADS) {
-            const float4 x = __ldg(v4 + i);
-            sum += (x.x + x.y) + (x.z + x.w);
-        }
+        SLAI_STAGE_LOOP({ sum += (x.x + x.y) + (x.z + x.w); })
         block_sum_max(sum, mx, stat);
         sub = sum / (float)K;
         sum = 0.f;
     }
-    const float4* w4p = reinterpret_cast<const float4*>(P.norm_w);
-    const float4* b4p = reinterpret_cast<const float4*>(P.norm_b);
-    for (int i = tid; i < n4; i += THREADS) {
-        float4 x = __ldg(v4 + i);
-        if (PRO == PRO_NONE) {
-            mx = fmaxf(mx, fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w))));
-        } else {
-            const float4 w = __ldg(w4p + i);
-            if (PRO == PRO_LN) { x.x -= sub; x.y -= sub; x.z -= sub; x.w -= sub; }
-            sum += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
-            mx = fmaxf(mx, fmaxf(fmaxf(fabsf(x.x * w.x), fabsf(x.y * w.y)), fmaxf(fabsf(x.z * w.z), fabsf(x.w * w.w))));
+    SLAI_STAGE_LOOP({
+        if (i < n4) {
+            if (PRO == PRO_NONE) {
+                mx = fmaxf(mx, max4(x));
+            } else {
+                const float4 w = __ldg(w4p + i);
+                if (PRO == PRO_LN) { x.x -= sub; x.y -= sub; x.z -= sub; x.w -= sub; }
+                sum += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+                mx = fmaxf(mx, max4(make_float4(x.x * w.x, x.y * w.y, x.z * w.z, x.w * w.w)));
+            }
         }
-    }
+    })
     block_sum_max(sum, mx, stat);
     if (PRO != PRO_NONE) {
         mul = 1.0f / sqrtf(sum / (float)K + P.eps);
         mx *= mul;
         if (PRO == PRO_LN && P.norm_b) {
             float mb = 0.f, dummy = 0.f;
-            for (int i = tid; i < n4; i += THREADS) {
-                const float4 b = __ldg(b4p + i);
-                mb = fmaxf(mb, fmaxf(fmaxf(fabsf(b.x), fabsf(b.y)), fmaxf(fabsf(b.z), fabsf(b.w))));
-            }
+            for (int i = tid; i < n4; i += THREADS) mb = fmaxf(mb, max4(__ldg(b4p + i)));
             block_sum_max(dummy, mb, stat);
             mx += mb;
         }
@@ -178,50 +204,54 @@ __device__ float stage_vector(const GemvParams& P, const Smem& S, float* stat, i
     }
     unsigned char* dig = reinterpret_cast<unsigned char*>(__cvta_shared_to_generic(S.dig));
     int4* sv = reinterpret_cast<int4*>(__cvta_shared_to_generic(S.sv));
-    const int np4 = Kp >> 2;
-    for (int i = tid; i < np4; i += THREADS) {
-        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (i < n4) {
-            x = __ldg(v4 + i);
-            if (PRO == PRO_RMS) {
-                const float4 w = __ldg(w4p + i);
-                x.x = (x.x * mul) * w.x; x.y = (x.y * mul) * w.y; x.z = (x.z * mul) * w.z; x.w = (x.w * mul) * w.w;
-            } else if (PRO == PRO_LN) {
-                const float4 w = __ldg(w4p + i);
-                x.x = ((x.x - sub) * mul) * w.x; x.y = ((x.y - sub) * mul) * w.y;
-                x.z = ((x.z - sub) * mul) * w.z; x.w = ((x.w - sub) * mul) * w.w;
-                if (P.norm_b) {
-                    const float4 b = __ldg(b4p + i);
-                    x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
+    SLAI_STAGE_LOOP({
+        if (i < np4) {  // np4 is a multiple of 64: whole warps take the branch together
+            if (i < n4) {
+                if (PRO == PRO_RMS) {
+                    const float4 w = __ldg(w4p + i);
+                    x.x = (x.x * mul) * w.x; x.y = (x.y * mul) * w.y; x.z = (x.z * mul) * w.z; x.w = (x.w * mul) * w.w;
+                } else if (PRO == PRO_LN) {
+                    const float4 w = __ldg(w4p + i);
+                    x.x = ((x.x - sub) * mul) * w.x; x.y = ((x.y - sub) * mul) * w.y;
+                    x.z = ((x.z - sub) * mul) * w.z; x.w = ((x.w - sub) * mul) * w.w;
+                    if (P.norm_b) {
+                        const float4 b = __ldg(b4p + i);
+                        x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
+                    }
                 }
             }
-        }
-        int d0[4], d1[4], d2[4], d3[4];
-        split_digits(__float2int_rn(x.x * scale), d0);
-        split_digits(__float2int_rn(x.y * scale), d1);
-        split_digits(__float2int_rn(x.z * scale), d2);
-        split_digits(__float2int_rn(x.w * scale), d3);
-        int s[4];
-#pragma unroll
-        for (int p = 0; p < 4; p++) {
-            const uint32_t word = (uint32_t)(d0[p] & 0xFF) | ((uint32_t)(d1[p] & 0xFF) << 8) | ((uint32_t)(d2[p] & 0xFF) << 16) |
-                                  ((uint32_t)(d3[p] & 0xFF) << 24);
-            *reinterpret_cast<uint32_t*>(dig + (size_t)p * S.plane + 4 * i) = word;
-            s[p] = (d0[p] + d1[p]) + (d2[p] + d3[p]);
-        }
-        if (SV_GRAN > 0) {
-#pragma unroll
-            for (int p = 0; p < 4; p++) {
-                s[p] += __shfl_xor_sync(0xffffffffu, s[p], 1);
-                s[p] += __shfl_xor_sync(0xffffffffu, s[p], 2);
-                if (SV_GRAN == 32) s[p] += __shfl_xor_sync(0xffffffffu, s[p], 4);
+            int d0[4], d1[4], d2[4], d3[4];
+            split_digits(__float2int_rn(x.x * scale), d0);
+            split_digits(__float2int_rn(x.y * scale), d1);
+            split_digits(__float2int_rn(x.z * scale), d2);
+            split_digits(__float2int_rn(x.w * scale), d3);
+            int s[4];
+            _Pragma("unroll") for (int p = 0; p < 4; p++) {
+                const uint32_t word = (uint32_t)(d0[p] & 0xFF) | ((uint32_t)(d1[p] & 0xFF) << 8) | ((uint32_t)(d2[p] & 0xFF) << 16) |
+                                      ((uint32_t)(d3[p] & 0xFF) << 24);
+                *reinterpret_cast<uint32_t*>(dig + (size_t)p * S.plane + 4 * i) = word;
+                s[p] = (d0[p] + d1[p]) + (d2[p] + d3[p]);
             }
-            constexpr int LANES = SV_GRAN > 0 ? SV_GRAN / 4 : 1;  // float4 groups per sub-block
-            if ((tid & (LANES - 1)) == 0) sv[i / LANES] = make_int4(s[0], s[1], s[2], s[3]);
+            if (SV_GRAN > 0) {
+                _Pragma("unroll") for (int p = 0; p < 4; p++) {
+                    s[p] += __shfl_xor_sync(0xffffffffu, s[p], 1);
+                    s[p] += __shfl_xor_sync(0xffffffffu, s[p], 2);
+                    if (SV_GRAN == 32) s[p] += __shfl_xor_sync(0xffffffffu, s[p], 4);
+                }
+                constexpr int LANES = SV_GRAN > 0 ? SV_GRAN / 4 : 1;  // float4 groups per sub-block
+                if ((tid & (LANES - 1)) == 0) sv[i / LANES] = make_int4(s[0], s[1], s[2], s[3]);
+            }
         }
-    }
+    })
+#undef SLAI_STAGE_LOOP
     __syncthreads();
     return 1.0f / scale;
+}
+
+template <int PRO, int SV_GRAN>
+__device__ float stage_vector(const GemvParams& P, const Smem& S, float* stat, int Kp) {
+    if ((Kp >> 2) <= STAGE_REGS * THREADS) return stage_impl<PRO, SV_GRAN, true>(P, S, stat, Kp);
+    return stage_impl<PRO, SV_GRAN, false>(P, S, stat, Kp);
 }
 
 __device__ __forceinline__ float gelu_ref(float x) {
@@ -244,29 +274,39 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_kernel(const GemvParams P) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int K = P.K;
     const int Kp = (K + 255) & ~255;
-    // [digit planes 4*Kp s8][sv: Kp/SV_GRAN x 4 s32][red WARPS*32 f32][stat 64 f32][mbar WARPS*MAX_STAGES u64][ring]
+    // [digit planes 4*(Kp+32) s8][sv: Kp/SV_GRAN x 4 s32][red WAVE*WARPS*NMAT*16 f32][stat 64 f32]
+    // [mbar WARPS*MAX_STAGES u64][ring]
     constexpr int SV_BYTES_PER_256 = F::SV_GRAN > 0 ? 256 / F::SV_GRAN * 16 : 0;
+    constexpr int RED_FLOATS = WAVE * WARPS * NMAT * 16;
     const uint32_t sv_bytes = (uint32_t)(Kp >> 8) * SV_BYTES_PER_256;
     Smem S;
     S.dig = (uint32_t)__cvta_generic_to_shared(smem_raw);
     S.plane = Kp + 32;  // planes 32 bytes apart modulo 128: the four digit columns of a sub-block hit different banks
     S.sv = S.dig + 4 * S.plane;
     float* red = reinterpret_cast<float*>(smem_raw + 4 * S.plane + sv_bytes);
-    float* stat = red + WARPS * 32;
-    const uint32_t fixed = (uint32_t)(4 * S.plane) + sv_bytes + WARPS * 32 * 4 + 64 * 4;
+    float* stat = red + RED_FLOATS;
+    const uint32_t fixed = (uint32_t)(4 * S.plane) + sv_bytes + RED_FLOATS * 4 + 64 * 4;
     const uint32_t mbar_base = S.dig + fixed;
     const uint32_t ring_base = (mbar_base + WARPS * MAX_STAGES * 8 + 127u) & ~127u;
 
-    const int warp = threadIdx.x >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5;
     LaneCtx L;
-    lane_init(L, threadIdx.x & 31, S);
+    lane_init(L, tid & 31, S);
 
-    const int ks = P.ks, nstage = P.nstage, nsteps = P.nsteps;
-    const int groups = WARPS / ks;
-    const int grp = warp / ks, wi = warp % ks;
-    const int item_stride = gridDim.x * groups;
-    const int first_item = blockIdx.x * groups + grp;
-    const int s0 = (nsteps * wi) / ks, s1 = (nsteps * (wi + 1)) / ks;
+    // Work of this block of threads: tiles [i0, i1); in waves of WAVE tiles the units (tile, matrix, step) are cut
+    // into WARPS contiguous pieces.
+    const int nstage = P.nstage, nsteps = P.nsteps;
+    const int upi = nsteps * NMAT;  // units per tile
+    const int i0 = (int)(((long long)P.n_items * blockIdx.x) / gridDim.x);
+    const int i1 = (int)(((long long)P.n_items * (blockIdx.x + 1)) / gridDim.x);
+    const int n_local = i1 - i0;
+    const int n_waves = (n_local + WAVE - 1) / WAVE;
+    auto wave_range = [&](int wv, int& u0, int& u1) {  // this warp's unit range inside wave wv
+        const int items = min(WAVE, n_local - wv * WAVE);
+        const int U = items * upi;
+        u0 = (U * warp) / WARPS;
+        u1 = (U * (warp + 1)) / WARPS;
+    };
     const uint32_t my_mbar = mbar_base + warp * MAX_STAGES * 8;
     const uint32_t my_ring = ring_base + warp * nstage * P.stage_stride;
 
@@ -277,31 +317,34 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_kernel(const GemvParams P) {
     }
     __syncwarp();
 
-    // Producer cursor over this warp's sequence of blocks: for item, for mat, for step in [s0, s1).
-    int p_item = s1 > s0 ? first_item : P.n_items, p_mat = 0, p_step = s0, p_stage = 0;
+    // Producer cursor: (wave, unit) in the same order the consumer walks.
+    int p_wave = 0, p_u = 0, p_u1 = 0, p_stage = 0;
+    if (n_waves > 0) wave_range(0, p_u, p_u1);
     auto issue = [&]() {
-        if (p_item < P.n_items) {
+        while (p_wave < n_waves && p_u >= p_u1) {  // skip empty ranges, move to the next wave
+            if (++p_wave < n_waves) wave_range(p_wave, p_u, p_u1);
+        }
+        if (p_wave < n_waves) {
             if (L.lane == 0) {
-                const int sidx = NMAT == 2 ? p_mat : seg_of_tile(P, p_item);
+                const int li = p_u / upi, rem = p_u - li * upi;
+                const int mat = NMAT == 2 ? rem / nsteps : 0;
+                const int step = rem - mat * nsteps;
+                const int item = i0 + p_wave * WAVE + li;
+                const int sidx = NMAT == 2 ? mat : seg_of_tile(P, item);
                 const GemvSeg& sg = P.seg[sidx];
-                const int tile = NMAT == 2 ? p_item : p_item - sg.tile0;
-                const uint8_t* src = sg.w + (size_t)tile * sg.tile_bytes + (size_t)p_step * P.step_bytes;
+                const int tile = NMAT == 2 ? item : item - sg.tile0;
+                const uint8_t* src = sg.w + (size_t)tile * sg.tile_bytes + (size_t)step * P.step_bytes;
                 const uint32_t mb = my_mbar + 8 * p_stage;
                 mbar_expect_tx(mb, P.step_bytes);
                 bulk_g2s(my_ring + p_stage * P.stage_stride, src, P.step_bytes, mb);
             }
             if (++p_stage == nstage) p_stage = 0;
-            if (++p_step == s1) {
-                p_step = s0;
-                if (++p_mat == NMAT) {
-                    p_mat = 0;
-                    p_item += item_stride;
-                }
-            }
+            p_u++;
         }
     };
     for (int s = 0; s < nstage; s++) issue();  // weights do not depend on the previous kernel
 
+    for (int i = tid; i < RED_FLOATS; i += THREADS) red[i] = 0.f;
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const float inv_scale = stage_vector<PRO, F::SV_GRAN>(P, S, stat, Kp);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -309,15 +352,20 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_kernel(const GemvParams P) {
     int c_stage = 0;
     uint32_t c_phase = 0;
     bool alive = true;
-    for (int item = first_item; item < P.n_items; item += item_stride) {
-        float acc[NMAT][2];
-#pragma unroll
-        for (int mat = 0; mat < NMAT; mat++) {
-            acc[mat][0] = 0.f;
-            acc[mat][1] = 0.f;
-            for (int s = s0; s < s1; s++) {
+    for (int wv = 0; wv < n_waves; wv++) {
+        int u0, u1;
+        wave_range(wv, u0, u1);
+        int u = u0;
+        while (u < u1) {
+            // one run of consecutive units inside the same (tile, matrix)
+            const int li = u / upi, rem = u - li * upi;
+            const int mat = NMAT == 2 ? rem / nsteps : 0;
+            int step = rem - mat * nsteps;
+            const int run_end = min(u1, u + (nsteps - step));
+            float accA = 0.f, accB = 0.f;
+            for (; u < run_end; u++, step++) {
                 if (alive) alive = mbar_wait(my_mbar + 8 * c_stage, c_phase, P.err_flag);
-                if (alive) F::compute(my_ring + c_stage * P.stage_stride, s, L, S, acc[mat][0], acc[mat][1]);
+                if (alive) F::compute(my_ring + c_stage * P.stage_stride, step, L, S, accA, accB);
                 __syncwarp();
                 if (L.lane == 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 if (alive) issue();  // refill the stage just consumed
@@ -326,29 +374,28 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_kernel(const GemvParams P) {
                     c_phase ^= 1;
                 }
             }
-            acc[mat][0] += __shfl_xor_sync(0xffffffffu, acc[mat][0], 1);
-            acc[mat][0] += __shfl_xor_sync(0xffffffffu, acc[mat][0], 2);
-            acc[mat][1] += __shfl_xor_sync(0xffffffffu, acc[mat][1], 1);
-            acc[mat][1] += __shfl_xor_sync(0xffffffffu, acc[mat][1], 2);
-        }
-        float* my = red + warp * 32;
-        if (L.t == 0) {
-#pragma unroll
-            for (int mat = 0; mat < NMAT; mat++) {
-                my[mat * 16 + L.g] = acc[mat][0];
-                my[mat * 16 + L.g + 8] = acc[mat][1];
+            accA += __shfl_xor_sync(0xffffffffu, accA, 1);
+            accA += __shfl_xor_sync(0xffffffffu, accA, 2);
+            accB += __shfl_xor_sync(0xffffffffu, accB, 1);
+            accB += __shfl_xor_sync(0xffffffffu, accB, 2);
+            if (L.t == 0) {  // a warp has at most one run per (tile, matrix): plain stores
+                float* dst = red + ((li * WARPS + warp) * NMAT + mat) * 16;
+                dst[L.g] = accA;
+                dst[L.g + 8] = accB;
             }
         }
-        if (ks == 1) __syncwarp();
-        else if (ks == WARPS) __syncthreads();
-        else asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(ks * 32) : "memory");
-        if (wi == 0 && L.lane < 16) {
-            const int r = L.lane;
+        __syncthreads();
+        // Epilogue of the wave: thread (li, r) adds the 16 partials of its row in warp order.
+        const int items = min(WAVE, n_local - wv * WAVE);
+        if (tid < items * 16) {
+            const int li = tid >> 4, r = tid & 15;
+            const int item = i0 + wv * WAVE + li;
             float val[NMAT];
 #pragma unroll
             for (int mat = 0; mat < NMAT; mat++) {
                 float s = 0.f;
-                for (int w = 0; w < ks; w++) s += red[(grp * ks + w) * 32 + mat * 16 + r];
+#pragma unroll
+                for (int w = 0; w < WARPS; w++) s += red[((li * WARPS + w) * NMAT + mat) * 16 + r];
                 val[mat] = s * inv_scale;
             }
             const int sidx = NMAT == 2 ? 0 : seg_of_tile(P, item);
@@ -371,8 +418,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_kernel(const GemvParams P) {
             } else if (EPI == EPI_QKV) {
                 float y = val[0] + bias;
                 const int pos = *P.d_pos;
+                // rows 2i, 2i+1 of a tile sit in neighbouring lanes of the same half-warp
+                const float other = __shfl_xor_sync(__activemask(), y, 1);
                 if (P.rope && sg.role < 2) {
-                    const float other = __shfl_xor_sync(0x0000ffffu, y, 1);
                     const int hd = (row_in_seg & ~1) % P.head_size;
                     const float ang = (float)pos * P.rope_theta[hd >> 1];
                     float sn, cs;
@@ -392,10 +440,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_kernel(const GemvParams P) {
                 }
             }
         }
-        // the partial buffer is reused by the next item of this group
-        if (ks == 1) __syncwarp();
-        else if (ks == WARPS) __syncthreads();
-        else asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(ks * 32) : "memory");
+        if (wv + 1 < n_waves) {  // the partial buffer is reused by the next wave
+            __syncthreads();
+            for (int i = tid; i < RED_FLOATS; i += THREADS) red[i] = 0.f;
+            __syncthreads();
+        }
     }
 }
 
@@ -435,9 +484,25 @@ int launch_inst(slai_ctx* ctx, const GemvParams& P, int grid, size_t smem, bool 
 }
 
 template <class F>
-int launch_fmt(slai_ctx* ctx, const GemvParams& P, const GemvLaunch& L, int grid, size_t smem) {
+int launch_fmt(slai_ctx* ctx, const GemvParams& P, const GemvLaunch& L, int grid, size_t smem_fixed, size_t per_stage) {
     const bool pdl = L.pdl;
-#define GO(NMAT, PRO, EPI) return launch_inst<F, NMAT, PRO, EPI>(ctx, P, grid, smem, pdl)
+    // the partial-sum buffer of the dual (gate/up) kernel is twice as large
+    const bool dual = L.epi == EPI_SILU;
+    const size_t red_bytes = (size_t)WAVE * WARPS * (dual ? 2 : 1) * 16 * 4;
+    const size_t fixed = smem_fixed + red_bytes;
+    GemvParams Q = P;
+    int nstage = (int)((SMEM_LIMIT - fixed) / per_stage);
+    if (nstage > 6) nstage = 6;
+    static int stage_env = -1;
+    if (stage_env < 0) {
+        const char* e = getenv("SLAI_GEMV_STAGES");
+        stage_env = e ? atoi(e) : 0;
+    }
+    if (stage_env >= 2 && stage_env <= nstage) nstage = stage_env;
+    SLAI_REQUIRE(ctx, nstage >= 2, SLAI_ERR_SHAPE, "gemv: K=%d does not fit in shared memory", P.K);
+    Q.nstage = nstage;
+    const size_t smem = fixed + (size_t)nstage * per_stage;
+#define GO(NMAT, PRO, EPI) return launch_inst<F, NMAT, PRO, EPI>(ctx, Q, grid, smem, pdl)
     switch (L.epi) {
         case EPI_STORE:
             if (L.pro == PRO_NONE) GO(1, PRO_NONE, EPI_STORE);
@@ -522,48 +587,16 @@ int gemv_launch(slai_ctx* ctx, const GemvLaunch& L) {
     const int Kp = (K + 255) & ~255;
     const int sv_gran = (L.fmt == SLAI_FMT_Q4_K || L.fmt == SLAI_FMT_Q5_K) ? 32 : L.fmt == SLAI_FMT_Q6_K ? 16 : 0;
     const size_t sv_bytes = sv_gran ? (size_t)(Kp / sv_gran) * 16 : 0;
-    const size_t fixed = (size_t)4 * (Kp + 32) + sv_bytes + WARPS * 32 * 4 + 64 * 4 + WARPS * MAX_STAGES * 8 + 128;
+    // everything except the partial-sum buffer and the ring
+    const size_t fixed = (size_t)4 * (Kp + 32) + sv_bytes + 64 * 4 + WARPS * MAX_STAGES * 8 + 128;
     const size_t per_stage = (size_t)WARPS * P.stage_stride;
-    SLAI_REQUIRE(ctx, fixed + 2 * per_stage <= SMEM_LIMIT, SLAI_ERR_SHAPE, "gemv: K=%d does not fit in shared memory", K);
-    static int stage_env = -1, ks_env = -1;
-    if (stage_env < 0) {
-        const char* e = getenv("SLAI_GEMV_STAGES");
-        stage_env = e ? atoi(e) : 0;
-        e = getenv("SLAI_GEMV_KS");
-        ks_env = e ? atoi(e) : 0;
-    }
-    int nstage = (int)((SMEM_LIMIT - fixed) / per_stage);
-    if (nstage > 6) nstage = 6;
-    if (stage_env >= 2 && stage_env <= nstage) nstage = stage_env;
-    P.nstage = nstage;
-    const size_t smem = fixed + (size_t)nstage * per_stage;
-
-    // K split: minimise rounds x (blocks per warp-item + fixed cost of an item).
-    const int mats = dual ? 2 : 1;
-    int best_ks = 1;
-    double best_cost = 1e30;
-    for (int ks = 1; ks <= WARPS; ks *= 2) {
-        if (ks > 1 && ks > P.nsteps) break;
-        const long long slots = (long long)ctx->sm_count * (WARPS / ks);
-        const long long rounds = (P.n_items + slots - 1) / slots;
-        const double per_item = (double)((P.nsteps + ks - 1) / ks) * mats + 1.5 + 0.25 * ks;
-        const double cost = rounds * per_item;
-        if (cost < best_cost) {
-            best_cost = cost;
-            best_ks = ks;
-        }
-    }
-    if (ks_env == 1 || ks_env == 2 || ks_env == 4 || ks_env == 8 || ks_env == 16) best_ks = ks_env;
-    P.ks = best_ks;
-    const int groups = WARPS / best_ks;
-    int grid = (P.n_items + groups - 1) / groups;
-    if (grid > ctx->sm_count) grid = ctx->sm_count;
+    int grid = P.n_items < ctx->sm_count ? P.n_items : ctx->sm_count;
 
     switch (L.fmt) {
-        case SLAI_FMT_Q4_K: return launch_fmt<Q4K>(ctx, P, L, grid, smem);
-        case SLAI_FMT_Q5_K: return launch_fmt<Q5K>(ctx, P, L, grid, smem);
-        case SLAI_FMT_Q6_K: return launch_fmt<Q6K>(ctx, P, L, grid, smem);
-        case SLAI_FMT_Q8_0: return launch_fmt<Q80>(ctx, P, L, grid, smem);
+        case SLAI_FMT_Q4_K: return launch_fmt<Q4K>(ctx, P, L, grid, fixed, per_stage);
+        case SLAI_FMT_Q5_K: return launch_fmt<Q5K>(ctx, P, L, grid, fixed, per_stage);
+        case SLAI_FMT_Q6_K: return launch_fmt<Q6K>(ctx, P, L, grid, fixed, per_stage);
+        case SLAI_FMT_Q8_0: return launch_fmt<Q80>(ctx, P, L, grid, fixed, per_stage);
     }
     return slai_set_error(ctx, SLAI_ERR_UNSUPPORTED_FORMAT, "gemv: format %d has no kernel", L.fmt);
 }
