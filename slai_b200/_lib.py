@@ -9,7 +9,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libslai_b200.so")
+LIB_PATH = os.environ.get("SLAI_B200_LIB") or os.path.join(_HERE, "libslai_b200.so")
 
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED_FORMAT, ERR_SHAPE, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT, ERR_OOM = range(8)
 STATUS_NAMES = ["OK", "INVALID_ARG", "UNSUPPORTED_FORMAT", "SHAPE", "CUDA", "NCCL", "TIMEOUT", "OOM"]

@@ -19,8 +19,6 @@
 // (mma.sync.m16n8k32 s8) against base-128 digit planes of the activation vector, staged once per block of
 // threads in shared memory (gemv_frag.cuh); block scales are applied to the per-sub-block integer sums.
 //
-// The first NSTAGE copies are issued before `griddepcontrol.wait`, so under programmatic dependent launch
-// the weight stream starts while the kernel that produces the activation vector is still finishing.
 // Every mbarrier wait is bounded; on expiry the warp raises the context's error flag and stops waiting.
 #include "common.cuh"
 #include "gemv_frag.cuh"
@@ -32,8 +30,11 @@ namespace {
 using namespace frag;
 using namespace gemvfmt;
 
-constexpr int THREADS = 512;
-constexpr int WARPS = 16;
+#ifndef SLAI_GEMV_WARPS
+#define SLAI_GEMV_WARPS 16
+#endif
+constexpr int WARPS = SLAI_GEMV_WARPS;
+constexpr int THREADS = 32 * WARPS;
 constexpr int MAX_STAGES = 8;
 constexpr int WAVE = 8;  // tiles whose partial sums are held in shared memory at a time
 constexpr int SMEM_LIMIT = 227 * 1024;
@@ -63,7 +64,22 @@ struct GemvParams {
     int kv_f16;
     long long kv_pos_stride, kv_head_stride;
     unsigned int* err_flag;
+#ifdef SLAI_TRACE
+    unsigned long long* trace;  // debug build only: per block of threads 8 x (globaltimer, clock64)
+#endif
 };
+
+#ifdef SLAI_TRACE
+#define SLAI_TRACE_POINT(k)                                                                     \
+    if (threadIdx.x == 0 && P.trace) {                                                           \
+        unsigned long long gt;                                                                   \
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));                                    \
+        P.trace[(blockIdx.x * 8 + (k)) * 2] = gt;                                                \
+        P.trace[(blockIdx.x * 8 + (k)) * 2 + 1] = (unsigned long long)clock64();                 \
+    }
+#else
+#define SLAI_TRACE_POINT(k)
+#endif
 
 // ---- mbarrier / bulk copy -------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t a, uint32_t count) {
@@ -133,8 +149,8 @@ __device__ __forceinline__ float max4(const float4& x) { return fmaxf(fmaxf(fabs
 // [2^25, 2^26), rounding to integers, split into four base-128 digit planes (gemv_frag.cuh), and per-sub-block
 // digit sums (for the `- dmin*m * sum(v)` term of Q4_K / Q5_K and the -32 offset of Q6_K).  Returns 1/scale.
 // The vector is read from global memory once and kept in registers between the passes when K <= 12288.
-template <int PRO, int SV_GRAN, bool CACHED>
-__device__ float stage_impl(const GemvParams& P, const Smem& S, float* stat, int Kp) {
+template <int PRO, int SV_GRAN, bool CACHED, class Hook>
+__device__ float stage_impl(const GemvParams& P, const Smem& S, float* stat, int Kp, Hook after_loads) {
     const int K = P.K;
     const int tid = threadIdx.x;
     const float4* v4 = reinterpret_cast<const float4*>(P.v);
@@ -150,6 +166,7 @@ __device__ float stage_impl(const GemvParams& P, const Smem& S, float* stat, int
             xr[r] = i < n4 ? __ldg(v4 + i) : zero4;
         }
     }
+    after_loads();  // the vector's loads are in flight ahead of whatever this issues
     // element group of register slot r (CACHED) or of loop round r (not CACHED)
 #define SLAI_STAGE_LOOP(...)                                                            \
     if (CACHED) {                                                                       \
@@ -248,10 +265,10 @@ __device__ float stage_impl(const GemvParams& P, const Smem& S, float* stat, int
     return 1.0f / scale;
 }
 
-template <int PRO, int SV_GRAN>
-__device__ float stage_vector(const GemvParams& P, const Smem& S, float* stat, int Kp) {
-    if ((Kp >> 2) <= STAGE_REGS * THREADS) return stage_impl<PRO, SV_GRAN, true>(P, S, stat, Kp);
-    return stage_impl<PRO, SV_GRAN, false>(P, S, stat, Kp);
+template <int PRO, int SV_GRAN, class Hook>
+__device__ float stage_vector(const GemvParams& P, const Smem& S, float* stat, int Kp, Hook after_loads) {
+    if ((Kp >> 2) <= STAGE_REGS * THREADS) return stage_impl<PRO, SV_GRAN, true>(P, S, stat, Kp, after_loads);
+    return stage_impl<PRO, SV_GRAN, false>(P, S, stat, Kp, after_loads);
 }
 
 __device__ __forceinline__ float gelu_ref(float x) {
@@ -290,6 +307,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_kernel(const GemvParams P) {
     const uint32_t ring_base = (mbar_base + WARPS * MAX_STAGES * 8 + 127u) & ~127u;
 
     const int tid = threadIdx.x, warp = tid >> 5;
+    SLAI_TRACE_POINT(0)
     LaneCtx L;
     lane_init(L, tid & 31, S);
 
@@ -317,37 +335,68 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_kernel(const GemvParams P) {
     }
     __syncwarp();
 
-    // Producer cursor: (wave, unit) in the same order the consumer walks.
-    int p_wave = 0, p_u = 0, p_u1 = 0, p_stage = 0;
-    if (n_waves > 0) wave_range(0, p_u, p_u1);
+    // Producer cursor: (wave, unit) in the same order the consumer walks; the source pointer is advanced
+    // incrementally (divisions only when a wave starts).
+    int p_wave = 0, p_u = 0, p_u1 = 0, p_stage = 0, p_li = 0, p_mat = 0, p_step = 0;
+    const uint8_t* p_ptr = nullptr;
+    auto p_base = [&](int li, int mat) -> const uint8_t* {
+        const int item = i0 + p_wave * WAVE + li;
+        const int sidx = NMAT == 2 ? mat : seg_of_tile(P, item);
+        const GemvSeg& sg = P.seg[sidx];
+        const int tile = NMAT == 2 ? item : item - sg.tile0;
+        return sg.w + (size_t)tile * sg.tile_bytes;
+    };
+    auto p_seek = [&]() {
+        if (p_u < p_u1) {
+            p_li = p_u / upi;
+            const int rem = p_u - p_li * upi;
+            p_mat = NMAT == 2 ? rem / nsteps : 0;
+            p_step = rem - p_mat * nsteps;
+            p_ptr = p_base(p_li, p_mat) + (size_t)p_step * P.step_bytes;
+        }
+    };
+    if (n_waves > 0) {
+        wave_range(0, p_u, p_u1);
+        p_seek();
+    }
     auto issue = [&]() {
         while (p_wave < n_waves && p_u >= p_u1) {  // skip empty ranges, move to the next wave
-            if (++p_wave < n_waves) wave_range(p_wave, p_u, p_u1);
+            if (++p_wave < n_waves) {
+                wave_range(p_wave, p_u, p_u1);
+                p_seek();
+            }
         }
         if (p_wave < n_waves) {
             if (L.lane == 0) {
-                const int li = p_u / upi, rem = p_u - li * upi;
-                const int mat = NMAT == 2 ? rem / nsteps : 0;
-                const int step = rem - mat * nsteps;
-                const int item = i0 + p_wave * WAVE + li;
-                const int sidx = NMAT == 2 ? mat : seg_of_tile(P, item);
-                const GemvSeg& sg = P.seg[sidx];
-                const int tile = NMAT == 2 ? item : item - sg.tile0;
-                const uint8_t* src = sg.w + (size_t)tile * sg.tile_bytes + (size_t)step * P.step_bytes;
                 const uint32_t mb = my_mbar + 8 * p_stage;
                 mbar_expect_tx(mb, P.step_bytes);
-                bulk_g2s(my_ring + p_stage * P.stage_stride, src, P.step_bytes, mb);
+                bulk_g2s(my_ring + p_stage * P.stage_stride, p_ptr, P.step_bytes, mb);
             }
             if (++p_stage == nstage) p_stage = 0;
-            p_u++;
+            p_ptr += P.step_bytes;
+            if (++p_u < p_u1 && ++p_step == nsteps) {  // next (tile, matrix)
+                p_step = 0;
+                if (NMAT == 2 && p_mat == 0) {
+                    p_mat = 1;
+                } else {
+                    p_mat = 0;
+                    p_li++;
+                }
+                p_ptr = p_base(p_li, p_mat);
+            }
         }
     };
-    for (int s = 0; s < nstage; s++) issue();  // weights do not depend on the previous kernel
 
     for (int i = tid; i < RED_FLOATS; i += THREADS) red[i] = 0.f;
+    SLAI_TRACE_POINT(1)
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const float inv_scale = stage_vector<PRO, F::SV_GRAN>(P, S, stat, Kp);
+    SLAI_TRACE_POINT(2)
+    // The activation vector's loads go out first; the ring fill follows them into the memory system.
+    const float inv_scale = stage_vector<PRO, F::SV_GRAN>(P, S, stat, Kp, [&]() {
+        for (int s = 0; s < nstage; s++) issue();
+    });
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    SLAI_TRACE_POINT(3)
 
     int c_stage = 0;
     uint32_t c_phase = 0;
@@ -365,10 +414,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_kernel(const GemvParams P) {
             float accA = 0.f, accB = 0.f;
             for (; u < run_end; u++, step++) {
                 if (alive) alive = mbar_wait(my_mbar + 8 * c_stage, c_phase, P.err_flag);
-                if (alive) F::compute(my_ring + c_stage * P.stage_stride, step, L, S, accA, accB);
+                F::compute(my_ring + c_stage * P.stage_stride, step, L, S, accA, accB);
                 __syncwarp();
                 if (L.lane == 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                if (alive) issue();  // refill the stage just consumed
+                issue();  // refill the stage just consumed
                 if (++c_stage == nstage) {
                     c_stage = 0;
                     c_phase ^= 1;
@@ -384,7 +433,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_kernel(const GemvParams P) {
                 dst[L.g + 8] = accB;
             }
         }
+        SLAI_TRACE_POINT(4)
         __syncthreads();
+        SLAI_TRACE_POINT(5)
         // Epilogue of the wave: thread (li, r) adds the 16 partials of its row in warp order.
         const int items = min(WAVE, n_local - wv * WAVE);
         if (tid < items * 16) {
@@ -440,6 +491,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_kernel(const GemvParams P) {
                 }
             }
         }
+        SLAI_TRACE_POINT(6)
         if (wv + 1 < n_waves) {  // the partial buffer is reused by the next wave
             __syncthreads();
             for (int i = tid; i < RED_FLOATS; i += THREADS) red[i] = 0.f;
@@ -583,6 +635,9 @@ int gemv_launch(slai_ctx* ctx, const GemvLaunch& L) {
     P.d_pos = L.d_pos; P.kcache = L.kcache; P.vcache = L.vcache; P.kv_f16 = (L.kv_dtype == SLAI_KV_F16);
     P.kv_pos_stride = L.kv_pos_stride; P.kv_head_stride = L.kv_head_stride;
     P.err_flag = ctx->d_counters + 3000;
+#ifdef SLAI_TRACE
+    P.trace = reinterpret_cast<unsigned long long*>(ctx->d_scratch);  // the debug driver sizes the scratch first
+#endif
 
     const int Kp = (K + 255) & ~255;
     const int sv_gran = (L.fmt == SLAI_FMT_Q4_K || L.fmt == SLAI_FMT_Q5_K) ? 32 : L.fmt == SLAI_FMT_Q6_K ? 16 : 0;

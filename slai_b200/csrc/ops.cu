@@ -880,3 +880,8 @@ SLAI_API int slai_synth_normal_f32(slai_ctx* ctx, float* d_out, int64_t n, uint6
     SLAI_CHECK_CUDA(ctx, cudaGetLastError());
     return SLAI_OK;
 }
+
+#ifdef SLAI_TRACE
+// debug build only (never part of the shipped library): device address of the context's scratch buffer
+SLAI_API void* slai_debug_scratch(slai_ctx* ctx) { return ctx ? ctx->d_scratch : nullptr; }
+#endif
