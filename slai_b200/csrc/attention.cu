@@ -215,6 +215,10 @@ int launch_t(slai_ctx* ctx, const AttnParams& P, int n_kv, size_t smem, bool pdl
     static bool attr_done = false;
     if (!attr_done) {
         SLAI_CHECK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        // Same shared-memory carve-out as the GEMV kernels it alternates with: no reconfiguration between launches.
+        const char* co = getenv("SLAI_ATTN_CARVEOUT");
+        if (!(co && co[0] == '0'))
+            SLAI_CHECK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         attr_done = true;
     }
     cudaLaunchConfig_t cfg = {};
