@@ -8,205 +8,18 @@
 // to finish a KV head merges the splits with the usual (max, sum) rescaling in a fixed order.
 // Cache element type is f16 or f32; strides are parameters so both the reference's position-major layout
 // and the models' head-major layout are served.
-#include "common.cuh"
+#include "attention.cuh"
+
+using namespace attn;
 
 namespace {
-
-constexpr int ATT_THREADS = 128;
-constexpr int ATT_WARPS = 4;
-constexpr int MAX_J = 4;  // head_size <= 256
-
-struct AttnParams {
-    const float* q;
-    const void* kc;
-    const void* vc;
-    long long pos_stride, head_stride;
-    int n_heads, kv_mul, hs;
-    const int* d_pos;
-    int n_splits, chunk_max;
-    float* out;
-    float* part_o;   // [n_heads][n_splits][hs]
-    float* part_ml;  // [n_heads][n_splits][2]
-    unsigned int* counters;  // [n_kv_heads]
-};
-
-template <typename T> struct Ld2;
-template <> struct Ld2<__half> {
-    __device__ static float2 ld(const __half* p) { return __half22float2(*reinterpret_cast<const __half2*>(p)); }
-};
-template <> struct Ld2<float> {
-    __device__ static float2 ld(const float* p) { return *reinterpret_cast<const float2*>(p); }
-};
 
 template <typename T, int MAXQ>
 __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnParams P) {
     extern __shared__ __align__(16) float sm[];
-    const int hs = P.hs, kv_mul = P.kv_mul;
-    float* q_s = sm;                                 // [kv_mul][hs]
-    float* sc_s = q_s + kv_mul * hs;                 // [kv_mul][chunk_max]
-    float* red_s = sc_s + kv_mul * P.chunk_max;      // [ATT_WARPS][kv_mul][hs]
-    float* ml_s = red_s + ATT_WARPS * kv_mul * hs;   // [kv_mul][2]
-    __shared__ int is_last;
-
-    const int kvh = blockIdx.x, split = blockIdx.y;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int n = *P.d_pos + 1;
-    const int chunk = (n + P.n_splits - 1) / P.n_splits;
-    const int t0 = split * chunk;
-    const int t1 = min(n, t0 + chunk);
-    const int cnt = max(0, t1 - t0);
-
-    for (int i = tid; i < kv_mul * hs; i += ATT_THREADS) q_s[i] = P.q[(size_t)kvh * kv_mul * hs + i];
-    __syncthreads();
+    attn_item<T, MAXQ>(P, blockIdx.x, blockIdx.y, threadIdx.x, sm, 0);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-
-    const T* kbase = reinterpret_cast<const T*>(P.kc) + (size_t)kvh * P.head_stride;
-    const T* vbase = reinterpret_cast<const T*>(P.vc) + (size_t)kvh * P.head_stride;
-    const float inv_sqrt = sqrtf((float)hs);
-
-    // Phase 1: scores.  Eight lanes per position, four positions per warp iteration.
-    {
-        const int sub = lane >> 3, l8 = lane & 7;
-        for (int i0 = warp * 4; i0 < cnt; i0 += ATT_WARPS * 4) {
-            const int i = i0 + sub;
-            float part[MAXQ];
-#pragma unroll
-            for (int h = 0; h < MAXQ; h++) part[h] = 0.f;
-            if (i < cnt) {
-                const T* kp = kbase + (size_t)(t0 + i) * P.pos_stride;
-                for (int e = l8; e < (hs >> 1); e += 8) {
-                    const float2 k2 = Ld2<T>::ld(kp + 2 * e);
-#pragma unroll
-                    for (int h = 0; h < MAXQ; h++)
-                        if (h < kv_mul) part[h] = fmaf(k2.y, q_s[h * hs + 2 * e + 1], fmaf(k2.x, q_s[h * hs + 2 * e], part[h]));
-                }
-            }
-#pragma unroll
-            for (int h = 0; h < MAXQ; h++) {
-                part[h] += __shfl_xor_sync(0xffffffffu, part[h], 1);
-                part[h] += __shfl_xor_sync(0xffffffffu, part[h], 2);
-                part[h] += __shfl_xor_sync(0xffffffffu, part[h], 4);
-            }
-            if (i < cnt && l8 == 0) {
-#pragma unroll
-                for (int h = 0; h < MAXQ; h++)
-                    if (h < kv_mul) sc_s[h * P.chunk_max + i] = part[h] / inv_sqrt;
-            }
-        }
-    }
-    __syncthreads();
-    // Phase 1b: local softmax numerators per query head.
-    for (int h = warp; h < kv_mul; h += ATT_WARPS) {
-        float m = -INFINITY;
-        for (int i = lane; i < cnt; i += 32) m = fmaxf(m, sc_s[h * P.chunk_max + i]);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        float l = 0.f;
-        for (int i = lane; i < cnt; i += 32) {
-            const float p = expf(sc_s[h * P.chunk_max + i] - m);
-            sc_s[h * P.chunk_max + i] = p;
-            l += p;
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
-        if (lane == 0) {
-            ml_s[2 * h] = m;
-            ml_s[2 * h + 1] = l;
-        }
-    }
-    __syncthreads();
-    // Phase 2: weighted sum of V.  A warp takes every ATT_WARPS-th position; a lane owns dims 64j+2*lane.
-    float acc[MAXQ][MAX_J][2];
-#pragma unroll
-    for (int h = 0; h < MAXQ; h++)
-#pragma unroll
-        for (int j = 0; j < MAX_J; j++) acc[h][j][0] = acc[h][j][1] = 0.f;
-    for (int i = warp; i < cnt; i += ATT_WARPS) {
-        const T* vp = vbase + (size_t)(t0 + i) * P.pos_stride;
-#pragma unroll
-        for (int j = 0; j < MAX_J; j++) {
-            const int d = 64 * j + 2 * lane;
-            if (d < hs) {
-                const float2 v2 = Ld2<T>::ld(vp + d);
-#pragma unroll
-                for (int h = 0; h < MAXQ; h++)
-                    if (h < kv_mul) {
-                        const float p = sc_s[h * P.chunk_max + i];
-                        acc[h][j][0] = fmaf(p, v2.x, acc[h][j][0]);
-                        acc[h][j][1] = fmaf(p, v2.y, acc[h][j][1]);
-                    }
-            }
-        }
-    }
-#pragma unroll
-    for (int h = 0; h < MAXQ; h++)
-        if (h < kv_mul)
-#pragma unroll
-            for (int j = 0; j < MAX_J; j++) {
-                const int d = 64 * j + 2 * lane;
-                if (d < hs) {
-                    red_s[(warp * kv_mul + h) * hs + d] = acc[h][j][0];
-                    red_s[(warp * kv_mul + h) * hs + d + 1] = acc[h][j][1];
-                }
-            }
-    __syncthreads();
-    for (int i = tid; i < kv_mul * hs; i += ATT_THREADS) {
-        const int h = i / hs, d = i % hs;
-        float o = 0.f;
-#pragma unroll
-        for (int w = 0; w < ATT_WARPS; w++) o += red_s[(w * kv_mul + h) * hs + d];
-        const int head = kvh * kv_mul + h;
-        if (P.n_splits == 1) {
-            P.out[(size_t)head * hs + d] = o / ml_s[2 * h + 1];
-        } else {
-            P.part_o[((size_t)head * P.n_splits + split) * hs + d] = o;
-        }
-    }
-    if (P.n_splits == 1) return;
-    if (tid < kv_mul) {
-        const int head = kvh * kv_mul + tid;
-        P.part_ml[((size_t)head * P.n_splits + split) * 2] = ml_s[2 * tid];
-        P.part_ml[((size_t)head * P.n_splits + split) * 2 + 1] = ml_s[2 * tid + 1];
-    }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        const unsigned int ticket = atomicAdd(&P.counters[kvh], 1u);
-        is_last = (ticket == (unsigned int)P.n_splits - 1);
-        if (is_last) P.counters[kvh] = 0;  // ready for the next launch
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    // Merge the splits of this KV head (fixed order over splits).  The (max, sum) pairs of all splits are first
-    // brought into shared memory with independent loads, then every thread merges one output element.
-    float* ml_all = red_s;  // kv_mul * n_splits * 2 floats (n_splits <= 64 <= 2 * head_size fits the reduce buffer)
-    {
-        const float* src = P.part_ml + (size_t)kvh * kv_mul * P.n_splits * 2;
-        for (int i = tid; i < kv_mul * P.n_splits * 2; i += ATT_THREADS) ml_all[i] = __ldcg(src + i);
-    }
-    __syncthreads();
-    for (int i = tid; i < kv_mul * hs; i += ATT_THREADS) {
-        const int h = i / hs, d = i % hs;
-        const int head = kvh * kv_mul + h;
-        const float* ml = ml_all + h * P.n_splits * 2;
-        float M = -INFINITY;
-        for (int s = 0; s < P.n_splits; s++)
-            if (ml[2 * s + 1] > 0.f) M = fmaxf(M, ml[2 * s]);
-        const float* po = P.part_o + ((size_t)head * P.n_splits) * hs + d;
-        float num = 0.f, den = 0.f;
-#pragma unroll 8
-        for (int s = 0; s < P.n_splits; s++) {
-            const float l = ml[2 * s + 1];
-            const float o = l > 0.f ? __ldcg(po + (size_t)s * hs) : 0.f;
-            const float w = l > 0.f ? expf(ml[2 * s] - M) : 0.f;
-            num = fmaf(w, o, num);
-            den = fmaf(w, l, den);
-        }
-        P.out[(size_t)head * hs + d] = num / den;
-    }
 }
 
 template <typename T, int MAXQ>
@@ -298,7 +111,7 @@ int attention_launch(slai_ctx* ctx, const AttnLaunch& A) {
     P.part_o = reinterpret_cast<float*>(scratch);
     P.part_ml = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + ((po + 255) & ~(size_t)255));
     P.counters = ctx->d_counters;
-    const size_t smem = (size_t)4 * (A.kv_mul * A.head_size + A.kv_mul * chunk_max + ATT_WARPS * A.kv_mul * A.head_size + 2 * A.kv_mul);
+    const size_t smem = 4 * attn_item_floats(A.kv_mul, A.head_size, chunk_max);
     SLAI_REQUIRE(ctx, smem <= 160 * 1024, SLAI_ERR_SHAPE, "attention: shared memory %zu too large", smem);
     SLAI_REQUIRE(ctx, n_splits <= 2 * P.hs, SLAI_ERR_SHAPE, "attention: context too long for head_size=%d", P.hs);
     const bool f16 = A.kv_dtype == SLAI_KV_F16;
@@ -381,7 +194,7 @@ SLAI_API int slai_attention_static(slai_ctx* ctx, const slai_attn_params* p, con
     P.part_o = reinterpret_cast<float*>(base);
     P.part_ml = reinterpret_cast<float*>(base + ((po + 255) & ~(size_t)255));
     P.counters = tickets;
-    const size_t smem = (size_t)4 * (kv_mul * hs + kv_mul * chunk_max + ATT_WARPS * kv_mul * hs + 2 * kv_mul);
+    const size_t smem = 4 * attn_item_floats(kv_mul, hs, chunk_max);
     SLAI_REQUIRE(ctx, smem <= 160 * 1024, SLAI_ERR_SHAPE, "attention: shared memory %zu too large", smem);
     SLAI_REQUIRE(ctx, n_splits <= 2 * P.hs, SLAI_ERR_SHAPE, "attention: context too long for head_size=%d", P.hs);
     const bool f16 = kv_dtype == SLAI_KV_F16;

@@ -162,3 +162,21 @@ int launch_embed_q8(slai_ctx* ctx, float* x, const slai_qmatrix* wte, const int*
                     const int* d_pos, bool pdl);
 int launch_argmax(slai_ctx* ctx, const float* v, int64_t n, int32_t* d_out, bool pdl);
 int launch_advance(slai_ctx* ctx, int* d_token, int* d_pos, const int32_t* d_next, int32_t* d_history, bool pdl);
+
+// decode.cu: all layers of a token in one persistent kernel (Llama family, one weight format for all matrices)
+struct DecodeLayersDesc {
+    int fmt, dim, hidden, n_heads, kv_mul, head_size, seq_len;
+};
+struct DecodeLayersPlan {
+    size_t dig_region = 0, smem = 0, part_o_bytes = 0, part_ml_bytes = 0;
+    int nstage = 0, n_splits = 0, chunk_max = 0, att_item_floats = 0;
+};
+size_t gemv_dig_region(int fmt, int K);
+int decode_layers_prepare(slai_ctx* ctx, const DecodeLayersDesc& desc, DecodeLayersPlan* plan);
+int decode_layers_launch(slai_ctx* ctx, int fmt, const void* d_prog, const void* d_att, int n_layers, int n_kv, int kv_mul,
+                         bool kv_f16, const DecodeLayersPlan& plan);
+size_t decode_gemv_params_bytes();
+size_t decode_attn_params_bytes();
+int decode_fill_gemv(slai_ctx* ctx, const GemvLaunch& L, const DecodeLayersPlan& plan, void* h_out);
+void decode_fill_attn(slai_ctx* ctx, const DecodeLayersDesc& desc, const DecodeLayersPlan& plan, const float* q, const void* kc,
+                      const void* vc, const int* d_pos, float* out, float* part_o, float* part_ml, void* h_out);

@@ -551,3 +551,8 @@ __device__ void gemv_phase(const GemvParams& P, Ring& R, unsigned char* smem_raw
 }
 
 }  // namespace gemvk
+
+// gemv.cu: validate a launch description and turn it into kernel parameters (dig_region / nstage 0 = size them
+// for this launch alone).
+int gemv_fill_params(slai_ctx* ctx, const GemvLaunch& L, size_t dig_region, int nstage, gemvk::GemvParams& P, size_t* smem_out,
+                     int* grid_out);

@@ -88,7 +88,89 @@ struct slai_llama {
     const float* rope_theta = nullptr;
     GraphSet graphs;
     int launches = 0;
+    // fused path: all layers in one persistent kernel (decode.cu)
+    int fused_state = 0;  // 0 not prepared, 1 ready, -1 not eligible
+    int fused_fmt = 0;
+    DecodeLayersPlan plan;
+    void *d_prog = nullptr, *d_att = nullptr;
+    float *f_part_o = nullptr, *f_part_ml = nullptr;
 };
+
+static void llama_drop_fused(slai_llama* m) {
+    if (m->d_prog || m->d_att || m->f_part_o || m->f_part_ml) cudaStreamSynchronize(m->ctx->stream);
+    cudaFree(m->d_prog); cudaFree(m->d_att); cudaFree(m->f_part_o); cudaFree(m->f_part_ml);
+    m->d_prog = m->d_att = nullptr;
+    m->f_part_o = m->f_part_ml = nullptr;
+    m->fused_state = 0;
+}
+
+// Builds the program of the persistent decode kernel when every layer matrix has the same quantised format.
+static int llama_prepare_fused(slai_llama* m) {
+    slai_ctx* ctx = m->ctx;
+    const slai_llama_config& c = m->cfg;
+    m->fused_state = -1;
+    const char* nf = getenv("SLAI_NO_FUSED");
+    if (nf && nf[0] == '1') return SLAI_OK;
+    if (c.rope_variant != 0 || m->kv_mul > 8) return SLAI_OK;
+    const int fmt = m->layers[0].wq ? m->layers[0].wq->fmt : 0;
+    if (fmt != SLAI_FMT_Q4_K && fmt != SLAI_FMT_Q5_K && fmt != SLAI_FMT_Q6_K && fmt != SLAI_FMT_Q8_0) return SLAI_OK;
+    for (auto& w : m->layers) {
+        const slai_qmatrix* ms[7] = {w.wq, w.wk, w.wv, w.wo, w.wgate, w.wup, w.wdown};
+        for (auto* q : ms)
+            if (!q || q->fmt != fmt) return SLAI_OK;
+        if (!w.attn_norm || !w.ffn_norm) return SLAI_OK;
+    }
+    DecodeLayersDesc desc{fmt, c.dim, c.hidden_dim, c.n_q_heads, m->kv_mul, m->head_size, c.seq_len};
+    cudaGetLastError();
+    if (decode_layers_prepare(ctx, desc, &m->plan) != SLAI_OK) return SLAI_OK;  // does not fit: keep the per-kernel path
+    const size_t gb = decode_gemv_params_bytes(), ab = decode_attn_params_bytes();
+    std::vector<unsigned char> hprog(gb * 4 * c.n_layers), hatt(ab * c.n_layers);
+    if (cudaMalloc(&m->f_part_o, m->plan.part_o_bytes + 256) != cudaSuccess || cudaMalloc(&m->f_part_ml, m->plan.part_ml_bytes + 256) != cudaSuccess ||
+        cudaMalloc(&m->d_prog, hprog.size()) != cudaSuccess || cudaMalloc(&m->d_att, hatt.size()) != cudaSuccess) {
+        cudaGetLastError();
+        llama_drop_fused(m);
+        m->fused_state = -1;
+        return SLAI_OK;
+    }
+    int* d_pos = m->sc.d + 1;
+    const size_t esz = c.kv_dtype == SLAI_KV_F16 ? 2 : 4;
+    for (int l = 0; l < c.n_layers; l++) {
+        const LlamaLayer& w = m->layers[l];
+        void* kc = (char*)m->kcache + (size_t)l * m->kv_layer_elems * esz;
+        void* vc = (char*)m->vcache + (size_t)l * m->kv_layer_elems * esz;
+        GemvLaunch L[4];
+        L[0].fmt = fmt; L[0].K = c.dim; L[0].nseg = 3;
+        L[0].seg[0] = seg_of(w.wq, 0, c.dim, w.bq, 0, 0);
+        L[0].seg[1] = seg_of(w.wk, 0, m->kv_dim, w.bk, 0, 1);
+        L[0].seg[2] = seg_of(w.wv, 0, m->kv_dim, w.bv, 0, 2);
+        L[0].v = m->x; L[0].out = m->q; L[0].pro = PRO_RMS; L[0].norm_w = w.attn_norm; L[0].eps = c.rms_norm_eps;
+        L[0].epi = EPI_QKV; L[0].rope = 1; L[0].rope_theta = m->rope_theta; L[0].head_size = m->head_size;
+        L[0].d_pos = d_pos; L[0].kcache = kc; L[0].vcache = vc; L[0].kv_dtype = c.kv_dtype;
+        L[0].kv_pos_stride = m->head_size; L[0].kv_head_stride = (int64_t)c.seq_len * m->head_size;
+        L[1].fmt = fmt; L[1].K = c.dim; L[1].nseg = 1; L[1].seg[0] = seg_of(w.wo, 0, c.dim, nullptr, 0, 0);
+        L[1].v = m->xb; L[1].out = m->x; L[1].resid = m->x; L[1].epi = EPI_RESID;
+        L[2].fmt = fmt; L[2].K = c.dim; L[2].nseg = 2;
+        L[2].seg[0] = seg_of(w.wgate, 0, c.hidden_dim, nullptr, 0, 0);
+        L[2].seg[1] = seg_of(w.wup, 0, c.hidden_dim, nullptr, 0, 0);
+        L[2].v = m->x; L[2].out = m->hb; L[2].pro = PRO_RMS; L[2].norm_w = w.ffn_norm; L[2].eps = c.rms_norm_eps; L[2].epi = EPI_SILU;
+        L[3].fmt = fmt; L[3].K = c.hidden_dim; L[3].nseg = 1; L[3].seg[0] = seg_of(w.wdown, 0, c.dim, nullptr, 0, 0);
+        L[3].v = m->hb; L[3].out = m->x; L[3].resid = m->x; L[3].epi = EPI_RESID;
+        for (int k = 0; k < 4; k++) {
+            int rc = decode_fill_gemv(ctx, L[k], m->plan, hprog.data() + gb * (4 * l + k));
+            if (rc) {
+                llama_drop_fused(m);
+                m->fused_state = -1;
+                return SLAI_OK;
+            }
+        }
+        decode_fill_attn(ctx, desc, m->plan, m->q, kc, vc, d_pos, m->xb, m->f_part_o, m->f_part_ml, hatt.data() + ab * l);
+    }
+    SLAI_CHECK_CUDA(ctx, cudaMemcpy(m->d_prog, hprog.data(), hprog.size(), cudaMemcpyHostToDevice));
+    SLAI_CHECK_CUDA(ctx, cudaMemcpy(m->d_att, hatt.data(), hatt.size(), cudaMemcpyHostToDevice));
+    m->fused_fmt = fmt;
+    m->fused_state = 1;
+    return SLAI_OK;
+}
 
 static int llama_record(slai_llama* m, int kind) {
     slai_ctx* ctx = m->ctx;
@@ -104,7 +186,14 @@ static int llama_record(slai_llama* m, int kind) {
     if (rc) return rc;
     n++;
     const size_t esz = c.kv_dtype == SLAI_KV_F16 ? 2 : 4;
-    for (int l = 0; l < c.n_layers; l++) {
+    if (m->fused_state == 1) {
+        // all layers in one persistent kernel
+        if ((rc = decode_layers_launch(ctx, m->fused_fmt, m->d_prog, m->d_att, c.n_layers, c.n_kv_heads, m->kv_mul,
+                                       c.kv_dtype == SLAI_KV_F16, m->plan)))
+            return rc;
+        n += 2;  // barrier reset + kernel
+    }
+    for (int l = 0; l < (m->fused_state == 1 ? 0 : c.n_layers); l++) {
         const LlamaLayer& w = m->layers[l];
         SLAI_REQUIRE(ctx, w.wq && w.wk && w.wv && w.wo && w.wgate && w.wup && w.wdown && w.attn_norm && w.ffn_norm,
                      SLAI_ERR_INVALID_ARG, "llama: layer %d has unset weights", l);
@@ -218,9 +307,16 @@ static int llama_record(slai_llama* m, int kind) {
     return SLAI_OK;
 }
 
+static int model_prepare(slai_llama* m) { return m->fused_state == 0 ? llama_prepare_fused(m) : SLAI_OK; }
+static int model_prepare(struct slai_gpt2*) { return SLAI_OK; }
+
 template <class M, class RecordFn>
 static int run_graph(M* m, int kind, RecordFn record) {
     slai_ctx* ctx = m->ctx;
+    {
+        int rc = model_prepare(m);
+        if (rc) return rc;
+    }
     if (!m->graphs.use_graph) return record(m, kind);
     if (!m->graphs.warmed[kind]) {
         m->graphs.warmed[kind] = true;
@@ -231,14 +327,17 @@ static int run_graph(M* m, int kind, RecordFn record) {
         SLAI_CHECK_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
         int rc = record(m, kind);
         cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
-        if (rc) {
-            if (graph) cudaGraphDestroy(graph);
-            return rc;
+        if (rc == SLAI_OK && e == cudaSuccess) {
+            e = cudaGraphInstantiate(&m->graphs.exec[kind], graph, 0);
+            if (e != cudaSuccess) m->graphs.exec[kind] = nullptr;
         }
-        SLAI_CHECK_CUDA(ctx, e);
-        e = cudaGraphInstantiate(&m->graphs.exec[kind], graph, 0);
-        cudaGraphDestroy(graph);
-        SLAI_CHECK_CUDA(ctx, e);
+        if (graph) cudaGraphDestroy(graph);
+        if (rc != SLAI_OK || e != cudaSuccess) {
+            // some launches (e.g. cooperative ones on older drivers) cannot be captured: run eagerly from now on
+            cudaGetLastError();
+            m->graphs.use_graph = false;
+            return record(m, kind);
+        }
     }
     SLAI_CHECK_CUDA(ctx, cudaGraphLaunch(m->graphs.exec[kind], ctx->stream));
     return SLAI_OK;
@@ -295,6 +394,7 @@ SLAI_API int slai_llama_destroy(slai_llama* m) {
     if (!m) return SLAI_OK;
     cudaStreamSynchronize(m->ctx->stream);
     destroy_graphs(m->graphs);
+    llama_drop_fused(m);
     for (auto& l : m->layers) {
         cudaFree(l.attn_norm); cudaFree(l.ffn_norm); cudaFree(l.bq); cudaFree(l.bk); cudaFree(l.bv);
     }
@@ -310,6 +410,7 @@ SLAI_API int slai_llama_set_matrix(slai_llama* m, int id, int layer, const slai_
     slai_ctx* ctx = m->ctx;
     const slai_llama_config& c = m->cfg;
     destroy_graphs(m->graphs);
+    llama_drop_fused(m);
     auto shape_is = [&](int64_t r, int64_t k) { return w->nrows == r && w->ncols == k; };
     if (id == SLAI_W_OUTPUT) {
         SLAI_REQUIRE(ctx, shape_is(c.vocab_size, c.dim), SLAI_ERR_SHAPE, "llama: output matrix must be vocab x dim");
@@ -341,6 +442,7 @@ static int llama_set_f32_impl(slai_llama* m, int id, int layer, const float* dat
     slai_ctx* ctx = m->ctx;
     const slai_llama_config& c = m->cfg;
     destroy_graphs(m->graphs);
+    llama_drop_fused(m);
     if (id == SLAI_W_TOKEN_EMBD) {
         SLAI_REQUIRE(ctx, n == (int64_t)c.vocab_size * c.dim, SLAI_ERR_SHAPE, "llama: token_embd needs vocab*dim floats");
         int rc = copy_f32(ctx, &m->token_embd, data, n, dev);
