@@ -251,12 +251,8 @@ def main():
         run_reference(args, rank, world)
         return
 
-    dist = None
-    if world > 1:
-        import torch
-        import torch.distributed as dist
-        torch.cuda.set_device(local)
-        dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local))
+    from slai_b200.replicas import ReplicaGroup
+    group = ReplicaGroup(backend="nccl")
 
     from slai_b200 import synth
     from slai_b200.ops import Backend, LlmContext
@@ -274,8 +270,7 @@ def main():
     tok = int(prompt[-1])
 
     def barrier():
-        if dist is not None:
-            dist.barrier()
+        group.barrier()
         backend.synchronize()
 
     # ---- device-resident decode: W warm-up tokens, then K timed tokens ----
@@ -306,11 +301,7 @@ def main():
     e2e_s = time.perf_counter() - t0
     barrier()
 
-    if dist is not None:
-        import torch
-        t = torch.tensor([ms, e2e_s], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_s = float(t[0]), float(t[1])
+    ms, e2e_s = group.max_over_ranks([ms, e2e_s])
 
     if rank == 0:
         value = world * K / (ms * 1e-3)
@@ -348,9 +339,7 @@ def main():
                                               "+ the logits gemv of the same model on the host; token time = 32 x layer + logits"}
         print(json.dumps(line), flush=True)
     backend.lib.slai_free_host(backend.h, pinned)
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
+    group.close()
 
 
 if __name__ == "__main__":

@@ -16,10 +16,16 @@ namespace {
 
 template <typename T, int MAXQ>
 __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnParams P) {
-    extern __shared__ __align__(16) float sm[];
+    extern __shared__ __align__(16) unsigned char sm[];
+    SLAI_TL_BEGIN(999)
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    attn_item<T, MAXQ>(P, blockIdx.x, blockIdx.y, threadIdx.x, sm, 0);
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the next kernel may start fetching its weights
+    {
+        const int n = __ldcg(P.d_pos) + 1;
+        const int ns = attn_splits(P, n);
+        if ((int)blockIdx.y < ns) attn_item<T, MAXQ>(P, blockIdx.x, blockIdx.y, ns, n, threadIdx.x, sm, 0);
+    }
+    SLAI_TL_MARK(2)
 }
 
 template <typename T, int MAXQ>
@@ -63,21 +69,38 @@ int ensure_scratch(slai_ctx* ctx, size_t bytes) {
     return SLAI_OK;
 }
 
-static int pick_splits(slai_ctx* ctx, int n_kv, int n_max) {
-    // About two blocks per SM, at least 32 and at most 1024 positions per block.
-    int n_splits = (2 * ctx->sm_count + n_kv - 1) / n_kv;
-    if (n_splits > (n_max + 31) / 32) n_splits = (n_max + 31) / 32;
+static int pick_splits(int head_size, int esz, int n_max) {
+    // One split per tile of positions, at most 64 (the kernel uses fewer while the context is short).
+    const int tile = attn_tile_pos(head_size, esz);
+    int n_splits = (n_max + tile - 1) / tile;
     if (n_splits < 1) n_splits = 1;
     if (n_splits > 64) n_splits = 64;
-    while ((n_max + n_splits - 1) / n_splits > 1024) n_splits++;
     return n_splits;
 }
 
 size_t attention_scratch_bytes(slai_ctx* ctx, int n_heads, int kv_mul, int head_size, int max_pos) {
-    const int n_splits = pick_splits(ctx, n_heads / kv_mul, max_pos + 1);
+    (void)ctx; (void)kv_mul;
+    const int n_splits = pick_splits(head_size, 4, max_pos + 1);  // the f32 tile holds fewer positions: most splits
     const size_t po = (size_t)n_heads * n_splits * head_size * 4;
     const size_t pml = (size_t)n_heads * n_splits * 2 * 4;
     return ((po + 255) & ~(size_t)255) + pml + 256;
+}
+
+// Tile size, split count, copy width and shared memory of a launch.
+static int attn_geometry(slai_ctx* ctx, AttnParams& P, int kv_dtype, int n_max, size_t* smem) {
+    const int esz = kv_dtype == SLAI_KV_F16 ? 2 : 4;
+#ifdef SLAI_TRACE
+    P.tr = nullptr;
+#endif
+    P.tile_pos = attn_tile_pos(P.hs, esz);
+    P.n_splits = pick_splits(P.hs, esz, n_max);
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(P.kc) | reinterpret_cast<uintptr_t>(P.vc) | (uintptr_t)(P.pos_stride * esz) |
+                           (uintptr_t)(P.head_stride * esz) | (uintptr_t)(P.hs * esz);
+    SLAI_REQUIRE(ctx, (bits & 3) == 0, SLAI_ERR_INVALID_ARG, "attention: caches and strides must be 4-byte aligned");
+    P.vec16 = (bits & 15) == 0;
+    *smem = attn_item_bytes(P.kv_mul, P.hs, esz, P.tile_pos, P.n_splits);
+    SLAI_REQUIRE(ctx, *smem <= 160 * 1024, SLAI_ERR_SHAPE, "attention: shared memory %zu too large", *smem);
+    return SLAI_OK;
 }
 
 int attention_launch(slai_ctx* ctx, const AttnLaunch& A) {
@@ -88,10 +111,16 @@ int attention_launch(slai_ctx* ctx, const AttnLaunch& A) {
     const int n_kv = A.n_heads / A.kv_mul;
     SLAI_REQUIRE(ctx, n_kv <= 1024, SLAI_ERR_SHAPE, "attention: too many KV heads");
     const int n_max = A.max_pos + 1;
-    const int n_splits = pick_splits(ctx, n_kv, n_max);
-    const int chunk_max = (n_max + n_splits - 1) / n_splits;
-
-    const size_t po = (size_t)A.n_heads * n_splits * A.head_size * 4;
+    AttnParams P;
+    P.q = A.q; P.kc = A.kcache; P.vc = A.vcache;
+    P.pos_stride = A.pos_stride; P.head_stride = A.head_stride;
+    P.n_heads = A.n_heads; P.kv_mul = A.kv_mul; P.hs = A.head_size;
+    size_t smem = 0;
+    {
+        int rc = attn_geometry(ctx, P, A.kv_dtype, n_max, &smem);
+        if (rc) return rc;
+    }
+    const size_t po = (size_t)A.n_heads * P.n_splits * A.head_size * 4;
     const size_t need = attention_scratch_bytes(ctx, A.n_heads, A.kv_mul, A.head_size, A.max_pos);
     void* scratch = A.scratch;
     if (!scratch) {
@@ -102,18 +131,11 @@ int attention_launch(slai_ctx* ctx, const AttnLaunch& A) {
         SLAI_REQUIRE(ctx, A.scratch_bytes >= need, SLAI_ERR_INVALID_ARG, "attention: scratch too small");
     }
 
-    AttnParams P;
-    P.q = A.q; P.kc = A.kcache; P.vc = A.vcache;
-    P.pos_stride = A.pos_stride; P.head_stride = A.head_stride;
-    P.n_heads = A.n_heads; P.kv_mul = A.kv_mul; P.hs = A.head_size;
-    P.d_pos = A.d_pos; P.n_splits = n_splits; P.chunk_max = chunk_max;
+    P.d_pos = A.d_pos;
     P.out = A.out;
     P.part_o = reinterpret_cast<float*>(scratch);
     P.part_ml = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + ((po + 255) & ~(size_t)255));
     P.counters = ctx->d_counters;
-    const size_t smem = 4 * attn_item_floats(A.kv_mul, A.head_size, chunk_max);
-    SLAI_REQUIRE(ctx, smem <= 160 * 1024, SLAI_ERR_SHAPE, "attention: shared memory %zu too large", smem);
-    SLAI_REQUIRE(ctx, n_splits <= 2 * P.hs, SLAI_ERR_SHAPE, "attention: context too long for head_size=%d", P.hs);
     const bool f16 = A.kv_dtype == SLAI_KV_F16;
     if (A.kv_mul == 1) return f16 ? launch_t<__half, 1>(ctx, P, n_kv, smem, A.pdl) : launch_t<float, 1>(ctx, P, n_kv, smem, A.pdl);
     if (A.kv_mul <= 4) return f16 ? launch_t<__half, 4>(ctx, P, n_kv, smem, A.pdl) : launch_t<float, 4>(ctx, P, n_kv, smem, A.pdl);
@@ -161,9 +183,16 @@ SLAI_API int slai_attention_static(slai_ctx* ctx, const slai_attn_params* p, con
     SLAI_REQUIRE(ctx, n_kv <= 1024, SLAI_ERR_SHAPE, "attention: too many KV heads");
     SLAI_REQUIRE(ctx, ctx->device >= 0 && ctx->device < STATIC_MAX_DEVICES, SLAI_ERR_INVALID_ARG, "attention: device index out of range");
 
-    const int n_splits = pick_splits(ctx, n_kv, pos + 1);
-    const int chunk_max = (pos + 1 + n_splits - 1) / n_splits;
-    const size_t po = (size_t)n_heads * n_splits * hs * 4;
+    AttnParams P;
+    P.q = d_q; P.kc = d_key_cache; P.vc = d_value_cache;
+    P.pos_stride = p->kv_dim; P.head_stride = hs;
+    P.n_heads = n_heads; P.kv_mul = kv_mul; P.hs = hs;
+    size_t smem = 0;
+    {
+        int rc = attn_geometry(ctx, P, kv_dtype, pos + 1, &smem);
+        if (rc) return rc;
+    }
+    const size_t po = (size_t)n_heads * P.n_splits * hs * 4;
     const size_t need = attention_scratch_bytes(ctx, n_heads, kv_mul, hs, pos);
     SLAI_REQUIRE(ctx, need <= STATIC_PART_BYTES, SLAI_ERR_SHAPE,
                  "slai_attention_static: this shape needs %zu bytes of split scratch, the built-in array holds %zu "
@@ -185,18 +214,11 @@ SLAI_API int slai_attention_static(slai_ctx* ctx, const slai_attn_params* p, con
     static_set_pos_kernel<<<1, 1, 0, ctx->stream>>>(d_pos, pos);
     SLAI_CHECK_CUDA(ctx, cudaGetLastError());
 
-    AttnParams P;
-    P.q = d_q; P.kc = d_key_cache; P.vc = d_value_cache;
-    P.pos_stride = p->kv_dim; P.head_stride = hs;
-    P.n_heads = n_heads; P.kv_mul = kv_mul; P.hs = hs;
-    P.d_pos = d_pos; P.n_splits = n_splits; P.chunk_max = chunk_max;
+    P.d_pos = d_pos;
     P.out = d_xb;
     P.part_o = reinterpret_cast<float*>(base);
     P.part_ml = reinterpret_cast<float*>(base + ((po + 255) & ~(size_t)255));
     P.counters = tickets;
-    const size_t smem = 4 * attn_item_floats(kv_mul, hs, chunk_max);
-    SLAI_REQUIRE(ctx, smem <= 160 * 1024, SLAI_ERR_SHAPE, "attention: shared memory %zu too large", smem);
-    SLAI_REQUIRE(ctx, n_splits <= 2 * P.hs, SLAI_ERR_SHAPE, "attention: context too long for head_size=%d", P.hs);
     const bool f16 = kv_dtype == SLAI_KV_F16;
     if (kv_mul == 1) return f16 ? launch_t<__half, 1>(ctx, P, n_kv, smem, false) : launch_t<float, 1>(ctx, P, n_kv, smem, false);
     if (kv_mul <= 4) return f16 ? launch_t<__half, 4>(ctx, P, n_kv, smem, false) : launch_t<float, 4>(ctx, P, n_kv, smem, false);

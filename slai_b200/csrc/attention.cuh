@@ -16,202 +16,300 @@ struct AttnParams {
     long long pos_stride, head_stride;
     int n_heads, kv_mul, hs;
     const int* d_pos;
-    int n_splits, chunk_max;
+    int n_splits;   // most splits a KV head is cut into (stride of the partial buffers)
+    int tile_pos;   // positions staged in shared memory at a time
+    int vec16;      // rows can be copied in 16-byte pieces (alignment of bases, strides and row length)
     float* out;
     float* part_o;   // [n_heads][n_splits][hs]
     float* part_ml;  // [n_heads][n_splits][2]
     unsigned int* counters;  // [n_kv_heads]
+#ifdef SLAI_TRACE
+    unsigned long long* tr;  // debug build only: timestamps of the first item of sub-block 0
+#endif
 };
-
-// Two consecutive cache elements as floats.  L2 loads (ld.global.cg): inside the persistent decode kernel the
-// newest cache entry was written by another SM during the same launch, so L1 must not be trusted.
-template <typename T> struct Ld2;
-template <> struct Ld2<__half> {
-    __device__ static float2 ld(const __half* p) {
-        const unsigned int u = __ldcg(reinterpret_cast<const unsigned int*>(p));
-        return __half22float2(*reinterpret_cast<const __half2*>(&u));
+#ifdef SLAI_TRACE
+#define ATT_TRACE(k)                                                   \
+    if (P.tr && tid == 0 && bar_id <= 1) {                             \
+        unsigned long long gt;                                         \
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));          \
+        if (P.tr[k] == 0) P.tr[k] = gt;                                \
     }
-};
-template <> struct Ld2<float> {
-    __device__ static float2 ld(const float* p) { return __ldcg(reinterpret_cast<const float2*>(p)); }
-};
+#else
+#define ATT_TRACE(k)
+#endif
 
 // Barrier over the ATT_THREADS threads that work on one item (named barrier `id`; id 0 with a 128-thread block is
 // the block-wide barrier).
 __device__ __forceinline__ void att_sync(int id) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(ATT_THREADS) : "memory"); }
 
-// Floats of shared memory one item needs.
-__host__ __device__ inline size_t attn_item_floats(int kv_mul, int hs, int chunk_max) {
-    return (size_t)kv_mul * hs + (size_t)kv_mul * chunk_max + (size_t)ATT_WARPS * kv_mul * hs + 2 * (size_t)kv_mul + 4;
+// Shared memory of one item, in bytes: q | scores | running (max, sum, rescale) | flag | K tile (rows padded by
+// 16 bytes: the four threads of a position and the eight positions of a warp then hit 32 different banks) | V tile.
+// The merge of the splits reuses the tile area for the (max, sum) pairs of all splits.
+__host__ __device__ inline size_t attn_k_stride(int hs, int esz) { return (size_t)hs * esz + 16; }
+__host__ __device__ inline size_t attn_head_bytes(int kv_mul, int hs, int tile_pos) {
+    return (((size_t)kv_mul * hs + (size_t)kv_mul * tile_pos + 4 * (size_t)kv_mul + 4) * 4 + 15) & ~(size_t)15;
+}
+__host__ __device__ inline size_t attn_item_bytes(int kv_mul, int hs, int esz, int tile_pos, int n_splits) {
+    size_t tiles = tile_pos * attn_k_stride(hs, esz) + (size_t)tile_pos * hs * esz;
+    const size_t merge = (size_t)kv_mul * n_splits * 2 * 4;
+    if (merge > tiles) tiles = merge;
+    return attn_head_bytes(kv_mul, hs, tile_pos) + ((tiles + 15) & ~(size_t)15);
+}
+// Positions per tile: about 8 KB of K (and of V) per item, a multiple of 8, at most 32.
+__host__ __device__ inline int attn_tile_pos(int hs, int esz) {
+    int t = (8192 / (hs * esz)) & ~7;
+    return t < 8 ? 8 : t > 32 ? 32 : t;
+}
+// Splits actually used at `n` positions: one per tile, up to the maximum.
+__device__ __forceinline__ int attn_splits(const AttnParams& P, int n) {
+    const int want = (n + P.tile_pos - 1) / P.tile_pos;
+    return want < 1 ? 1 : want > P.n_splits ? P.n_splits : want;
 }
 
-// One work item = (KV head, split of the positions), processed by ATT_THREADS threads with thread index `tid`,
-// shared memory `sm` (attn_item_floats floats) and barrier `bar_id`.
+template <typename T> struct Elem;
+template <> struct Elem<__half> {
+    __device__ static __forceinline__ float2 ld2(const unsigned char* p) { return __half22float2(*reinterpret_cast<const __half2*>(p)); }
+    __device__ static __forceinline__ float ld1(const unsigned char* p) { return __half2float(*reinterpret_cast<const __half*>(p)); }
+};
+template <> struct Elem<float> {
+    __device__ static __forceinline__ float2 ld2(const unsigned char* p) { return *reinterpret_cast<const float2*>(p); }
+    __device__ static __forceinline__ float ld1(const unsigned char* p) { return *reinterpret_cast<const float*>(p); }
+};
+
+// Copy `rows` rows of K and of V (row_bytes each, row_pitch bytes apart in memory) into shared memory.  All the
+// loads of a batch (eight per thread) are issued before the first store, so a tile costs one trip to memory.
+// L2 loads (ld.global.cg): inside the persistent decode kernel the newest row was written by another SM during
+// the same launch, so L1 must not be trusted.
+template <typename V>
+__device__ __forceinline__ void load_tiles(const unsigned char* kg, const unsigned char* vg, size_t row_pitch, int row_bytes, int rows,
+                                           unsigned char* k_s, int k_stride, unsigned char* v_s, int tid) {
+    const int ppr = row_bytes / (int)sizeof(V);
+    const int half = rows * ppr, total = 2 * half;
+    for (int base = 0; base < total; base += 8 * ATT_THREADS) {
+        V buf[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int idx = base + tid + u * ATT_THREADS;
+            if (idx < total) {
+                const int isv = idx >= half, j = idx - isv * half, r = j / ppr, c = j - r * ppr;
+                buf[u] = __ldcg(reinterpret_cast<const V*>((isv ? vg : kg) + (size_t)r * row_pitch) + c);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int idx = base + tid + u * ATT_THREADS;
+            if (idx < total) {
+                const int isv = idx >= half, j = idx - isv * half, r = j / ppr, c = j - r * ppr;
+                unsigned char* dst = isv ? v_s + (size_t)r * row_bytes : k_s + (size_t)r * k_stride;
+                reinterpret_cast<V*>(dst)[c] = buf[u];
+            }
+        }
+    }
+}
+
+// One work item = (KV head, split `split` of `ns`) at `n` positions, processed by ATT_THREADS threads with thread
+// index `tid`, shared memory `smb` (attn_item_bytes) and barrier `bar_id`.  The split's positions are walked in
+// tiles with a running (max, sum) per query head (the usual streaming softmax); the partial output of the split is
+// the un-normalised weighted sum of V relative to the final max.
 template <typename T, int MAXQ>
-__device__ void attn_item(const AttnParams& P, int kvh, int split, int tid, float* sm, int bar_id) {
-    const int hs = P.hs, kv_mul = P.kv_mul;
-    float* q_s = sm;                                 // [kv_mul][hs]
-    float* sc_s = q_s + kv_mul * hs;                 // [kv_mul][chunk_max]
-    float* red_s = sc_s + kv_mul * P.chunk_max;      // [ATT_WARPS][kv_mul][hs]
-    float* ml_s = red_s + ATT_WARPS * kv_mul * hs;   // [kv_mul][2]
-    int* is_last_p = reinterpret_cast<int*>(ml_s + 2 * kv_mul);
+__device__ __forceinline__ void attn_item(const AttnParams& P, int kvh, int split, int ns, int n, int tid, unsigned char* smb, int bar_id) {
+    constexpr int ESZ = (int)sizeof(T);
+    const int hs = P.hs, kv_mul = P.kv_mul, TP = P.tile_pos;
+    float* q_s = reinterpret_cast<float*>(smb);       // [kv_mul][hs]
+    float* sc_s = q_s + kv_mul * hs;                   // [kv_mul][TP]
+    float* st_s = sc_s + kv_mul * TP;                  // [kv_mul][4]: running max, running sum, rescale of this tile
+    int* is_last_p = reinterpret_cast<int*>(st_s + 4 * kv_mul);
+    unsigned char* k_s = smb + attn_head_bytes(kv_mul, hs, TP);
+    const int k_stride = (int)attn_k_stride(hs, ESZ);
+    const int row_bytes = hs * ESZ;
+    unsigned char* v_s = k_s + (size_t)TP * k_stride;
     const int lane = tid & 31, warp = tid >> 5;
 
-    const int n = __ldcg(P.d_pos) + 1;
-    const int chunk = (n + P.n_splits - 1) / P.n_splits;
+    const int chunk = (n + ns - 1) / ns;
     const int t0 = split * chunk;
     const int t1 = min(n, t0 + chunk);
-    const int cnt = max(0, t1 - t0);
 
-    for (int i = tid; i < kv_mul * hs; i += ATT_THREADS) q_s[i] = __ldcg(P.q + (size_t)kvh * kv_mul * hs + i);
-    att_sync(bar_id);
+    const unsigned char* kbase = reinterpret_cast<const unsigned char*>(P.kc) + ((size_t)kvh * P.head_stride) * ESZ;
+    const unsigned char* vbase = reinterpret_cast<const unsigned char*>(P.vc) + ((size_t)kvh * P.head_stride) * ESZ;
+    const size_t row_pitch = (size_t)P.pos_stride * ESZ;
+    const float sqrt_hs = sqrtf((float)hs);
 
-    const T* kbase = reinterpret_cast<const T*>(P.kc) + (size_t)kvh * P.head_stride;
-    const T* vbase = reinterpret_cast<const T*>(P.vc) + (size_t)kvh * P.head_stride;
-    const float inv_sqrt = sqrtf((float)hs);
-
-    // Phase 1: scores.  Eight lanes per position, four positions per warp iteration.
-    {
-        const int sub = lane >> 3, l8 = lane & 7;
-        for (int i0 = warp * 4; i0 < cnt; i0 += ATT_WARPS * 4) {
-            const int i = i0 + sub;
-            float part[MAXQ];
+    ATT_TRACE(0)
+    // q: loads first, stores after the first tile's loads are in flight
+    float qr[2 * MAXQ];
 #pragma unroll
-            for (int h = 0; h < MAXQ; h++) part[h] = 0.f;
-            if (i < cnt) {
-                const T* kp = kbase + (size_t)(t0 + i) * P.pos_stride;
-                for (int e = l8; e < (hs >> 1); e += 8) {
-                    const float2 k2 = Ld2<T>::ld(kp + 2 * e);
+    for (int u = 0; u < 2 * MAXQ; u++) {
+        const int i = tid + u * ATT_THREADS;
+        qr[u] = i < kv_mul * hs ? __ldcg(P.q + (size_t)kvh * kv_mul * hs + i) : 0.f;
+    }
+    if (tid < kv_mul) {
+        st_s[4 * tid] = -INFINITY;
+        st_s[4 * tid + 1] = 0.f;
+        st_s[4 * tid + 2] = 0.f;
+    }
+    float acc[MAXQ][2];
+#pragma unroll
+    for (int h = 0; h < MAXQ; h++) acc[h][0] = acc[h][1] = 0.f;
+
+    for (int tt = t0; tt < t1; tt += TP) {
+        const int cnt = min(TP, t1 - tt);
+        if (tt != t0) att_sync(bar_id);  // the previous tile has been consumed
+        if (P.vec16)
+            load_tiles<uint4>(kbase + (size_t)tt * row_pitch, vbase + (size_t)tt * row_pitch, row_pitch, row_bytes, cnt, k_s, k_stride, v_s, tid);
+        else
+            load_tiles<unsigned int>(kbase + (size_t)tt * row_pitch, vbase + (size_t)tt * row_pitch, row_pitch, row_bytes, cnt, k_s, k_stride, v_s, tid);
+        if (tt == t0) {
+#pragma unroll
+            for (int u = 0; u < 2 * MAXQ; u++) {
+                const int i = tid + u * ATT_THREADS;
+                if (i < kv_mul * hs) q_s[i] = qr[u];
+            }
+        }
+        att_sync(bar_id);
+        ATT_TRACE(1)
+        // scores: four threads per position, 32 positions per pass
+        {
+            const int c = tid & 3;
+            for (int i0 = 0; i0 < cnt; i0 += 32) {
+                const int i = i0 + (tid >> 2);
+                float part[MAXQ];
+#pragma unroll
+                for (int h = 0; h < MAXQ; h++) part[h] = 0.f;
+                if (i < cnt) {
+                    const unsigned char* kp = k_s + (size_t)i * k_stride;
+                    for (int e = c; e < (hs >> 1); e += 4) {
+                        const float2 k2 = Elem<T>::ld2(kp + 2 * e * ESZ);
+#pragma unroll
+                        for (int h = 0; h < MAXQ; h++)
+                            if (h < kv_mul) part[h] = fmaf(k2.y, q_s[h * hs + 2 * e + 1], fmaf(k2.x, q_s[h * hs + 2 * e], part[h]));
+                    }
+                }
+#pragma unroll
+                for (int h = 0; h < MAXQ; h++) {
+                    part[h] += __shfl_xor_sync(0xffffffffu, part[h], 1);
+                    part[h] += __shfl_xor_sync(0xffffffffu, part[h], 2);
+                }
+                if (i < cnt && c == 0) {
 #pragma unroll
                     for (int h = 0; h < MAXQ; h++)
-                        if (h < kv_mul) part[h] = fmaf(k2.y, q_s[h * hs + 2 * e + 1], fmaf(k2.x, q_s[h * hs + 2 * e], part[h]));
+                        if (h < kv_mul) sc_s[h * TP + i] = part[h] / sqrt_hs;
                 }
             }
+        }
+        att_sync(bar_id);
+        // running softmax per query head
+        for (int h = warp; h < kv_mul; h += ATT_WARPS) {
+            const float m_old = st_s[4 * h], l_old = st_s[4 * h + 1];
+            float m = m_old;
+            for (int i = lane; i < cnt; i += 32) m = fmaxf(m, sc_s[h * TP + i]);
 #pragma unroll
-            for (int h = 0; h < MAXQ; h++) {
-                part[h] += __shfl_xor_sync(0xffffffffu, part[h], 1);
-                part[h] += __shfl_xor_sync(0xffffffffu, part[h], 2);
-                part[h] += __shfl_xor_sync(0xffffffffu, part[h], 4);
+            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            float l = 0.f;
+            for (int i = lane; i < cnt; i += 32) {
+                const float p = expf(sc_s[h * TP + i] - m);
+                sc_s[h * TP + i] = p;
+                l += p;
             }
-            if (i < cnt && l8 == 0) {
 #pragma unroll
-                for (int h = 0; h < MAXQ; h++)
-                    if (h < kv_mul) sc_s[h * P.chunk_max + i] = part[h] / inv_sqrt;
+            for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+            __syncwarp();
+            if (lane == 0) {
+                const float resc = m_old == -INFINITY ? 0.f : expf(m_old - m);
+                st_s[4 * h] = m;
+                st_s[4 * h + 1] = l_old * resc + l;
+                st_s[4 * h + 2] = resc;
             }
         }
-    }
-    att_sync(bar_id);
-    // Phase 1b: local softmax numerators per query head.
-    for (int h = warp; h < kv_mul; h += ATT_WARPS) {
-        float m = -INFINITY;
-        for (int i = lane; i < cnt; i += 32) m = fmaxf(m, sc_s[h * P.chunk_max + i]);
+        att_sync(bar_id);
+        ATT_TRACE(2)
+        // weighted sum of V: thread `tid` owns dims tid and tid + 128
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        float l = 0.f;
-        for (int i = lane; i < cnt; i += 32) {
-            const float p = expf(sc_s[h * P.chunk_max + i] - m);
-            sc_s[h * P.chunk_max + i] = p;
-            l += p;
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
-        if (lane == 0) {
-            ml_s[2 * h] = m;
-            ml_s[2 * h + 1] = l;
-        }
-    }
-    att_sync(bar_id);
-    // Phase 2: weighted sum of V.  A warp takes every ATT_WARPS-th position; a lane owns dims 64j+2*lane.
-    float acc[MAXQ][MAX_J][2];
-#pragma unroll
-    for (int h = 0; h < MAXQ; h++)
-#pragma unroll
-        for (int j = 0; j < MAX_J; j++) acc[h][j][0] = acc[h][j][1] = 0.f;
-    for (int i = warp; i < cnt; i += ATT_WARPS) {
-        const T* vp = vbase + (size_t)(t0 + i) * P.pos_stride;
-#pragma unroll
-        for (int j = 0; j < MAX_J; j++) {
-            const int d = 64 * j + 2 * lane;
+        for (int jj = 0; jj < 2; jj++) {
+            const int d = tid + jj * ATT_THREADS;
             if (d < hs) {
-                const float2 v2 = Ld2<T>::ld(vp + d);
+                float a[MAXQ];
 #pragma unroll
-                for (int h = 0; h < MAXQ; h++)
-                    if (h < kv_mul) {
-                        const float p = sc_s[h * P.chunk_max + i];
-                        acc[h][j][0] = fmaf(p, v2.x, acc[h][j][0]);
-                        acc[h][j][1] = fmaf(p, v2.y, acc[h][j][1]);
-                    }
-            }
-        }
-    }
+                for (int h = 0; h < MAXQ; h++) a[h] = h < kv_mul ? acc[h][jj] * st_s[4 * h + 2] : 0.f;
+                for (int i = 0; i < cnt; i++) {
+                    const float v = Elem<T>::ld1(v_s + (size_t)i * row_bytes + (size_t)d * ESZ);
 #pragma unroll
-    for (int h = 0; h < MAXQ; h++)
-        if (h < kv_mul)
-#pragma unroll
-            for (int j = 0; j < MAX_J; j++) {
-                const int d = 64 * j + 2 * lane;
-                if (d < hs) {
-                    red_s[(warp * kv_mul + h) * hs + d] = acc[h][j][0];
-                    red_s[(warp * kv_mul + h) * hs + d + 1] = acc[h][j][1];
+                    for (int h = 0; h < MAXQ; h++)
+                        if (h < kv_mul) a[h] = fmaf(sc_s[h * TP + i], v, a[h]);
                 }
-            }
-    att_sync(bar_id);
-    for (int i = tid; i < kv_mul * hs; i += ATT_THREADS) {
-        const int h = i / hs, d = i % hs;
-        float o = 0.f;
 #pragma unroll
-        for (int w = 0; w < ATT_WARPS; w++) o += red_s[(w * kv_mul + h) * hs + d];
-        const int head = kvh * kv_mul + h;
-        if (P.n_splits == 1) {
-            P.out[(size_t)head * hs + d] = o / ml_s[2 * h + 1];
-        } else {
-            P.part_o[((size_t)head * P.n_splits + split) * hs + d] = o;
+                for (int h = 0; h < MAXQ; h++) acc[h][jj] = a[h];
+            }
         }
     }
-    if (P.n_splits == 1) return;
+    ATT_TRACE(3)
+    // partial (or final) output
+#pragma unroll
+    for (int jj = 0; jj < 2; jj++) {
+        const int d = tid + jj * ATT_THREADS;
+        if (d < hs) {
+#pragma unroll
+            for (int h = 0; h < MAXQ; h++)
+                if (h < kv_mul) {
+                    const int head = kvh * kv_mul + h;
+                    if (ns == 1) P.out[(size_t)head * hs + d] = acc[h][jj] / st_s[4 * h + 1];
+                    else P.part_o[((size_t)head * P.n_splits + split) * hs + d] = acc[h][jj];
+                }
+        }
+    }
+    if (ns == 1) return;
     if (tid < kv_mul) {
         const int head = kvh * kv_mul + tid;
-        P.part_ml[((size_t)head * P.n_splits + split) * 2] = ml_s[2 * tid];
-        P.part_ml[((size_t)head * P.n_splits + split) * 2 + 1] = ml_s[2 * tid + 1];
+        P.part_ml[((size_t)head * P.n_splits + split) * 2] = st_s[4 * tid];
+        P.part_ml[((size_t)head * P.n_splits + split) * 2 + 1] = st_s[4 * tid + 1];
     }
     __threadfence();
+    ATT_TRACE(4)
     att_sync(bar_id);
     if (tid == 0) {
         const unsigned int ticket = atomicAdd(&P.counters[kvh], 1u);
-        *is_last_p = (ticket == (unsigned int)P.n_splits - 1);
+        *is_last_p = (ticket == (unsigned int)ns - 1);
         if (*is_last_p) P.counters[kvh] = 0;  // ready for the next launch
     }
     att_sync(bar_id);
+    ATT_TRACE(5)
     if (!*is_last_p) return;
     __threadfence();
     // Merge the splits of this KV head (fixed order over splits).  The (max, sum) pairs of all splits are first
-    // brought into shared memory with independent loads, then every thread merges one output element.
-    float* ml_all = red_s;  // kv_mul * n_splits * 2 floats (n_splits <= 64 <= 2 * head_size fits the reduce buffer)
+    // brought into shared memory with independent loads, then every thread merges its output elements, eight
+    // independent loads at a time.
+    float* ml_all = reinterpret_cast<float*>(k_s);  // kv_mul * ns * 2 floats (attn_item_bytes reserves them)
     {
-        const float* src = P.part_ml + (size_t)kvh * kv_mul * P.n_splits * 2;
-        for (int i = tid; i < kv_mul * P.n_splits * 2; i += ATT_THREADS) ml_all[i] = __ldcg(src + i);
+        for (int i = tid; i < kv_mul * ns * 2; i += ATT_THREADS) {
+            const int h = i / (2 * ns), r = i - h * 2 * ns;
+            ml_all[i] = __ldcg(P.part_ml + ((size_t)(kvh * kv_mul + h) * P.n_splits) * 2 + r);
+        }
     }
     att_sync(bar_id);
     for (int i = tid; i < kv_mul * hs; i += ATT_THREADS) {
         const int h = i / hs, d = i % hs;
         const int head = kvh * kv_mul + h;
-        const float* ml = ml_all + h * P.n_splits * 2;
+        const float* ml = ml_all + h * ns * 2;
         float M = -INFINITY;
-        for (int s = 0; s < P.n_splits; s++)
+        for (int s = 0; s < ns; s++)
             if (ml[2 * s + 1] > 0.f) M = fmaxf(M, ml[2 * s]);
         const float* po = P.part_o + ((size_t)head * P.n_splits) * hs + d;
         float num = 0.f, den = 0.f;
-#pragma unroll 8
-        for (int s = 0; s < P.n_splits; s++) {
-            const float l = ml[2 * s + 1];
-            const float o = l > 0.f ? __ldcg(po + (size_t)s * hs) : 0.f;
-            const float w = l > 0.f ? expf(ml[2 * s] - M) : 0.f;
-            num = fmaf(w, o, num);
-            den = fmaf(w, l, den);
+        for (int s0 = 0; s0 < ns; s0 += 8) {
+            float o[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) o[u] = s0 + u < ns ? __ldcg(po + (size_t)(s0 + u) * hs) : 0.f;
+#pragma unroll
+            for (int u = 0; u < 8; u++)
+                if (s0 + u < ns) {
+                    const float l = ml[2 * (s0 + u) + 1];
+                    const float w = l > 0.f ? expf(ml[2 * (s0 + u)] - M) : 0.f;
+                    num = fmaf(w, l > 0.f ? o[u] : 0.f, num);
+                    den = fmaf(w, l, den);
+                }
         }
         P.out[(size_t)head * hs + d] = num / den;
     }
+    ATT_TRACE(6)
 }
-
 
 }  // namespace attn

@@ -163,20 +163,65 @@ int launch_embed_q8(slai_ctx* ctx, float* x, const slai_qmatrix* wte, const int*
 int launch_argmax(slai_ctx* ctx, const float* v, int64_t n, int32_t* d_out, bool pdl);
 int launch_advance(slai_ctx* ctx, int* d_token, int* d_pos, const int32_t* d_next, int32_t* d_history, bool pdl);
 
+#if defined(SLAI_TRACE) && defined(__CUDACC__)
+// debug build only: timeline of kernels as seen by thread 0 of block 0 (kernel id, start, end in globaltimer ns)
+extern __device__ unsigned long long g_tl[3 * 4096];
+extern __device__ unsigned int g_tl_count;
+#define SLAI_TL_BEGIN(id)                                                              \
+    unsigned int tl_idx = 0xffffffffu;                                                 \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {                      \
+        tl_idx = atomicAdd(&g_tl_count, 1u) & 4095u;                                   \
+        unsigned long long gt;                                                         \
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));                          \
+        g_tl[3 * tl_idx] = (id);                                                       \
+        g_tl[3 * tl_idx + 1] = gt;                                                     \
+    }
+#define SLAI_TL_MARK(slot)                                                             \
+    if (tl_idx != 0xffffffffu) {                                                       \
+        unsigned long long gt;                                                         \
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));                          \
+        g_tl[3 * tl_idx + (slot)] = gt;                                                \
+    }
+#else
+#define SLAI_TL_BEGIN(id)
+#define SLAI_TL_MARK(slot)
+#endif
+
 // decode.cu: all layers of a token in one persistent kernel (Llama family, one weight format for all matrices)
 struct DecodeLayersDesc {
-    int fmt, dim, hidden, n_heads, kv_mul, head_size, seq_len;
+    int fmt, dim, hidden, n_heads, kv_mul, head_size, seq_len, kv_f16;
 };
 struct DecodeLayersPlan {
     size_t dig_region = 0, smem = 0, part_o_bytes = 0, part_ml_bytes = 0;
-    int nstage = 0, n_splits = 0, chunk_max = 0, att_item_floats = 0;
+    int nstage = 0, n_splits = 0;
+};
+// Per-layer pointers of the persistent decode kernel.  They travel in the kernel's parameter block (constant
+// bank): the ring producer and every phase read them with no memory latency.
+struct DecodeLayerPtrs {
+    const uint8_t *wq, *wk, *wv, *wo, *wgate, *wup, *wdown;  // tile-major quantised matrices
+    const float *attn_norm, *ffn_norm, *bq, *bk, *bv;        // biases may be null
+    void *kcache, *vcache;                                   // this layer's slice of the caches
+};
+constexpr int DECODE_MAX_LAYERS = 96;
+struct DecodeParams {
+    // geometry (decode_layers_prepare)
+    int fmt, dim, hidden, kv_dim, n_heads, n_kv, kv_mul, head_size, seq_len, n_layers;
+    int nsteps_dim, nsteps_hidden;               // tile-step blocks per tile for K = dim / K = hidden
+    int items_base[4], items_rem[4];             // per GEMV of a layer: items per block of threads (base, +1 for the first rem)
+    long long tile_bytes_dim, tile_bytes_hidden;  // bytes of a 16-row tile
+    int nstage, step_bytes, stage_stride, dig_region;
+    int n_splits, tile_pos, att_item_bytes, vec16;
+    unsigned int *bar, *err_flag, *counters;
+    // the model's buffers (caller)
+    float eps;
+    const float* rope_theta;
+    const int* d_pos;
+    int kv_f16;
+    float *x, *xb, *q, *hb;
+    float *part_o, *part_ml;
+    DecodeLayerPtrs layer[DECODE_MAX_LAYERS];
 };
 size_t gemv_dig_region(int fmt, int K);
-int decode_layers_prepare(slai_ctx* ctx, const DecodeLayersDesc& desc, DecodeLayersPlan* plan);
-int decode_layers_launch(slai_ctx* ctx, int fmt, const void* d_prog, const void* d_att, int n_layers, int n_kv, int kv_mul,
-                         bool kv_f16, const DecodeLayersPlan& plan);
-size_t decode_gemv_params_bytes();
-size_t decode_attn_params_bytes();
-int decode_fill_gemv(slai_ctx* ctx, const GemvLaunch& L, const DecodeLayersPlan& plan, void* h_out);
-void decode_fill_attn(slai_ctx* ctx, const DecodeLayersDesc& desc, const DecodeLayersPlan& plan, const float* q, const void* kc,
-                      const void* vc, const int* d_pos, float* out, float* part_o, float* part_ml, void* h_out);
+// Sizes shared memory, ring depth and the attention split for `desc`, and fills the geometry fields of `D`.
+int decode_layers_prepare(slai_ctx* ctx, const DecodeLayersDesc& desc, DecodeLayersPlan* plan, DecodeParams* D);
+int decode_layers_launch(slai_ctx* ctx, const DecodeParams& D, const DecodeLayersPlan& plan);

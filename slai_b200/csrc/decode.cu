@@ -16,17 +16,120 @@
 using namespace gemvk;
 using attn::AttnParams;
 
-struct DecodeParams {
-    const GemvParams* prog;  // device array: 4 entries per layer (QKV, O, gate/up, down)
-    const AttnParams* att;   // device array: one entry per layer
-    int n_layers;
-    int n_kv;                // KV heads
-    int att_item_floats;     // shared-memory floats per attention item
-    unsigned int* bar;       // grid barrier counter, zero at launch
-    unsigned int* err_flag;
-};
+#ifdef SLAI_TRACE
+// debug build only: per block of threads 32 x (globaltimer, clock64) taken in one layer of the token
+__device__ unsigned long long g_dtrace[256 * 32 * 2];
+__device__ unsigned long long g_ptrace[4 * 256 * 8 * 2];   // per GEMV phase of that layer: the phase's own trace points
+__device__ unsigned long long g_wtrace[4 * 256 * 16 * 4];  // per GEMV phase, block of threads and warp
+#define DTRACE(k)                                                          \
+    if (l == 8 && threadIdx.x == 0) {                                      \
+        unsigned long long gt;                                             \
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));              \
+        g_dtrace[(blockIdx.x * 32 + (k)) * 2] = gt;                        \
+        g_dtrace[(blockIdx.x * 32 + (k)) * 2 + 1] = (unsigned long long)clock64(); \
+    }
+#else
+#define DTRACE(k)
+#endif
 
 namespace {
+
+// The program of the ring producer: entry 4*l + k is GEMV k (QKV, O, gate/up, down) of layer l.  Everything comes
+// from the kernel's parameter block.
+struct LayerProg {
+    const DecodeParams& D;
+    __device__ __forceinline__ int size() const { return 4 * D.n_layers; }
+    __device__ __forceinline__ ProgGeom geom(int idx) const {
+        const int k = idx & 3;
+        ProgGeom g;
+        g.nsteps = k == 3 ? D.nsteps_hidden : D.nsteps_dim;
+        g.nmat = k == 2 ? 2 : 1;
+        g.items_base = D.items_base[k];
+        g.items_rem = D.items_rem[k];
+        return g;
+    }
+    __device__ __forceinline__ const uint8_t* tile_ptr(int idx, int item, int mat) const {
+        const DecodeLayerPtrs& W = D.layer[idx >> 2];
+        const int k = idx & 3;
+        if (k == 0) {
+            const int t1 = D.dim >> 4, t2 = (D.dim + D.kv_dim) >> 4;
+            const uint8_t* w = W.wq;
+            int t = item;
+            if (item >= t1) { w = W.wk; t = item - t1; }
+            if (item >= t2) { w = W.wv; t = item - t2; }
+            return w + (size_t)t * D.tile_bytes_dim;
+        }
+        if (k == 1) return W.wo + (size_t)item * D.tile_bytes_dim;
+        if (k == 2) return (mat ? W.wup : W.wgate) + (size_t)item * D.tile_bytes_dim;
+        return W.wdown + (size_t)item * D.tile_bytes_hidden;
+    }
+};
+
+// Parameters of GEMV phase k (0 QKV, 1 O, 2 gate/up, 3 down) of layer l, assembled in registers from the
+// parameter block.
+__device__ __forceinline__ GemvParams phase_params(const DecodeParams& D, int l, int k) {
+    const DecodeLayerPtrs& W = D.layer[l];
+    const bool qkv = k == 0, op = k == 1, gu = k == 2, dn = k == 3;
+    GemvParams P{};
+    P.nstage = D.nstage;
+    P.step_bytes = D.step_bytes;
+    P.stage_stride = D.stage_stride;
+    P.dig_region = D.dig_region;
+    P.err_flag = D.err_flag;
+    P.eps = D.eps;
+    P.nseg = qkv ? 3 : gu ? 2 : 1;
+    P.nmat = gu ? 2 : 1;
+    P.K = dn ? D.hidden : D.dim;
+    P.nsteps = dn ? D.nsteps_hidden : D.nsteps_dim;
+    P.n_items = qkv ? (D.dim + 2 * D.kv_dim) >> 4 : gu ? D.hidden >> 4 : D.dim >> 4;
+    P.items_base = D.items_base[k];
+    P.items_rem = D.items_rem[k];
+    P.seg[0].w = qkv ? W.wq : op ? W.wo : gu ? W.wgate : W.wdown;
+    P.seg[0].tile_bytes = dn ? D.tile_bytes_hidden : D.tile_bytes_dim;
+    P.seg[0].rows = gu ? D.hidden : D.dim;
+    P.seg[0].bias = qkv ? W.bq : nullptr;
+    P.seg[1].w = qkv ? W.wk : W.wup;
+    P.seg[1].tile_bytes = D.tile_bytes_dim;
+    P.seg[1].rows = qkv ? D.kv_dim : D.hidden;
+    P.seg[1].tile0 = D.dim >> 4;
+    P.seg[1].bias = qkv ? W.bk : nullptr;
+    P.seg[1].role = 1;
+    P.seg[2].w = W.wv;
+    P.seg[2].tile_bytes = D.tile_bytes_dim;
+    P.seg[2].rows = D.kv_dim;
+    P.seg[2].tile0 = (D.dim + D.kv_dim) >> 4;
+    P.seg[2].bias = W.bv;
+    P.seg[2].role = 2;
+    P.v = (qkv || gu) ? D.x : op ? D.xb : D.hb;
+    P.out = qkv ? D.q : gu ? D.hb : D.x;
+    P.resid = D.x;
+    P.norm_w = qkv ? W.attn_norm : W.ffn_norm;
+    P.rope = 1; P.rope_theta = D.rope_theta; P.head_size = D.head_size; P.d_pos = D.d_pos;
+    P.kcache = W.kcache; P.vcache = W.vcache; P.kv_f16 = D.kv_f16;
+    P.kv_pos_stride = D.head_size; P.kv_head_stride = (long long)D.seq_len * D.head_size;
+#ifdef SLAI_TRACE
+    if (l == 8) {
+        P.trace = g_ptrace + k * 256 * 8 * 2;
+        P.wtrace = g_wtrace + k * 256 * 16 * 4;
+    }
+#endif
+    return P;
+}
+
+__device__ __forceinline__ AttnParams attn_params(const DecodeParams& D, int l) {
+    const DecodeLayerPtrs& W = D.layer[l];
+    AttnParams A;
+    A.q = D.q; A.kc = W.kcache; A.vc = W.vcache;
+    A.pos_stride = D.head_size; A.head_stride = (long long)D.seq_len * D.head_size;
+    A.n_heads = D.n_heads; A.kv_mul = D.kv_mul; A.hs = D.head_size;
+    A.d_pos = D.d_pos; A.n_splits = D.n_splits; A.tile_pos = D.tile_pos; A.vec16 = D.vec16;
+    A.out = D.xb; A.part_o = D.part_o; A.part_ml = D.part_ml;
+    A.counters = D.counters;
+#ifdef SLAI_TRACE
+    A.tr = l == 8 ? g_dtrace + (blockIdx.x * 32 + 16) * 2 : nullptr;
+#endif
+    return A;
+}
 
 // Grid-wide barrier: every block of threads arrives once per epoch; bounded spin (error flag 2 on expiry).
 __device__ __forceinline__ void grid_sync(const DecodeParams& D, unsigned int& epoch) {
@@ -56,12 +159,26 @@ template <typename KV, int MAXQ>
 __device__ __forceinline__ void attention_phase(const DecodeParams& D, const AttnParams& A, unsigned char* smem_raw) {
     const int sub = threadIdx.x >> 7, tid = threadIdx.x & 127;
     if (sub >= 4) return;  // (THREADS is 512: never taken; keeps the mapping explicit)
-    float* sm = reinterpret_cast<float*>(smem_raw) + (size_t)sub * D.att_item_floats;
-    const int n_items = D.n_kv * A.n_splits;
+    unsigned char* sm = smem_raw + (size_t)sub * D.att_item_bytes;
+    const int n = __ldcg(A.d_pos) + 1;
+    const int ns = attn::attn_splits(A, n);
+    const int n_items = D.n_kv * ns;
     for (int item = blockIdx.x * 4 + sub; item < n_items; item += gridDim.x * 4) {
-        const int kvh = item / A.n_splits, split = item - kvh * A.n_splits;
-        attn::attn_item<KV, MAXQ>(A, kvh, split, tid, sm, 1 + sub);
+        const int kvh = item / ns, split = item - kvh * ns;
+        attn::attn_item<KV, MAXQ>(A, kvh, split, ns, n, tid, sm, 1 + sub);
         attn::att_sync(1 + sub);  // the item's shared memory is reused by the next one
+    }
+}
+
+// The next layer's norm weights are read by every block of threads right after a barrier: pull them into L2
+// while this layer runs (one 128-byte line per thread of one block of threads).
+__device__ __forceinline__ void prefetch_norms(const DecodeParams& D, int l) {
+    if (l >= D.n_layers || (int)blockIdx.x != l % (int)gridDim.x) return;
+    const DecodeLayerPtrs& W = D.layer[l];
+    const int lines = (D.dim * 4 + 127) >> 7;
+    for (int i = threadIdx.x; i < 2 * lines; i += THREADS) {
+        const char* p = reinterpret_cast<const char*>(i < lines ? W.attn_norm : W.ffn_norm) + (size_t)(i < lines ? i : i - lines) * 128;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
     }
 }
 
@@ -69,20 +186,36 @@ template <class F, typename KV, int MAXQ>
 __global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const __grid_constant__ DecodeParams D) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     Ring R;
-    ring_init(R, D.prog, 4 * D.n_layers, smem_raw, threadIdx.x & 31, threadIdx.x >> 5);
+    const LayerProg prog{D};
+    ring_init(R, prog, D.dig_region, D.nstage, D.stage_stride, D.step_bytes, D.err_flag, smem_raw, threadIdx.x & 31, threadIdx.x >> 5);
     unsigned int epoch = 0;
+    // One copy of the GEMV phase serves the four GEMVs of a layer (k = 0 QKV, 1 O, 2 gate/up, 3 down): the
+    // code of a whole layer then fits the instruction cache and stays there from layer to layer.
+    constexpr int PRO_MASK = (1 << PRO_NONE) | (1 << PRO_RMS);
+    constexpr int EPI_MASK = (1 << EPI_QKV) | (1 << EPI_RESID) | (1 << EPI_SILU);
     for (int l = 0; l < D.n_layers; l++) {
-        const GemvParams* pp = D.prog + 4 * l;
-        gemv_phase<F, 1, PRO_RMS, EPI_QKV>(pp[0], R, smem_raw, l == 0);
-        grid_sync(D, epoch);
-        attention_phase<KV, MAXQ>(D, D.att[l], smem_raw);
-        grid_sync(D, epoch);
-        gemv_phase<F, 1, PRO_NONE, EPI_RESID>(pp[1], R, smem_raw, false);
-        grid_sync(D, epoch);
-        gemv_phase<F, 2, PRO_RMS, EPI_SILU>(pp[2], R, smem_raw, false);
-        grid_sync(D, epoch);
-        gemv_phase<F, 1, PRO_NONE, EPI_RESID>(pp[3], R, smem_raw, false);
-        if (l + 1 < D.n_layers) grid_sync(D, epoch);
+        prefetch_norms(D, l + 1);
+#pragma unroll 1
+        for (int k = 0; k < 4; k++) {
+            DTRACE(k == 0 ? 0 : 2 * k + 2)
+            {
+                const GemvParams P = phase_params(D, l, k);
+                const int nmat = k == 2 ? 2 : 1;
+                const int pro = (k == 0 || k == 2) ? PRO_RMS : PRO_NONE;
+                const int epi = k == 0 ? EPI_QKV : k == 2 ? EPI_SILU : EPI_RESID;
+                gemv_phase<F, PRO_MASK, EPI_MASK>(P, R, prog, smem_raw, nmat, pro, epi);
+            }
+            DTRACE(k == 0 ? 1 : 2 * k + 3)
+            if (k < 3 || l + 1 < D.n_layers) grid_sync(D, epoch);
+            if (k == 0) {
+                DTRACE(2)
+                const AttnParams A = attn_params(D, l);
+                attention_phase<KV, MAXQ>(D, A, smem_raw);
+                DTRACE(3)
+                grid_sync(D, epoch);
+            }
+        }
+        DTRACE(10)
     }
 }
 
@@ -109,33 +242,39 @@ int launch_k(slai_ctx* ctx, const DecodeParams& D, size_t smem) {
 }
 
 template <class F>
-int launch_f(slai_ctx* ctx, const DecodeParams& D, size_t smem, bool kv_f16, int kv_mul) {
-    if (kv_mul == 1) return kv_f16 ? launch_k<F, __half, 1>(ctx, D, smem) : launch_k<F, float, 1>(ctx, D, smem);
+int launch_f(slai_ctx* ctx, const DecodeParams& D, size_t smem) {
+    const bool kv_f16 = D.kv_f16 != 0;
+    if (D.kv_mul == 1) return kv_f16 ? launch_k<F, __half, 1>(ctx, D, smem) : launch_k<F, float, 1>(ctx, D, smem);
     return kv_f16 ? launch_k<F, __half, 8>(ctx, D, smem) : launch_k<F, float, 8>(ctx, D, smem);
 }
 
 }  // namespace
 
-int decode_layers_prepare(slai_ctx* ctx, const DecodeLayersDesc& desc, DecodeLayersPlan* plan) {
+int decode_layers_prepare(slai_ctx* ctx, const DecodeLayersDesc& desc, DecodeLayersPlan* plan, DecodeParams* D) {
     // Common shared-memory geometry of all phases: the staging region must hold the widest activation vector
     // and four attention items; the ring depth follows from what is left.
     const int n_kv = desc.n_heads / desc.kv_mul;
-    int n_splits = (4 * ctx->sm_count) / n_kv;
-    if (n_splits > 64) n_splits = 64;
-    if (n_splits > 2 * desc.head_size) n_splits = 2 * desc.head_size;
-    if (n_splits < 1) n_splits = 1;
-    while ((desc.seq_len + n_splits - 1) / n_splits > 1024) n_splits++;
-    SLAI_REQUIRE(ctx, n_splits <= 2 * desc.head_size, SLAI_ERR_SHAPE, "decode: context too long for the fused path");
-    const int chunk_max = (desc.seq_len + n_splits - 1) / n_splits;
-    const size_t item_floats = (attn::attn_item_floats(desc.kv_mul, desc.head_size, chunk_max) + 3) & ~(size_t)3;
+    const int kv_dim = n_kv * desc.head_size;
+    SLAI_REQUIRE(ctx, desc.dim % 16 == 0 && desc.hidden % 16 == 0 && kv_dim % 16 == 0, SLAI_ERR_SHAPE,
+                 "decode: dimensions must be multiples of 16 for the fused path");
+    const int esz = desc.kv_f16 ? 2 : 4;
     size_t dig = gemv_dig_region(desc.fmt, desc.dim);
     const size_t dig2 = gemv_dig_region(desc.fmt, desc.hidden);
     if (dig2 > dig) dig = dig2;
-    if (4 * item_floats * 4 > dig) dig = (4 * item_floats * 4 + 127) & ~(size_t)127;
+    // Attention runs four items per block of threads in the staging region plus the partial-sum buffer behind it
+    // (both idle during that phase).  The tile shrinks until four items fit.
+    int tile_pos = attn::attn_tile_pos(desc.head_size, esz);
+    int n_splits = 0;
+    size_t item_bytes = 0;
+    for (;; tile_pos -= 8) {
+        SLAI_REQUIRE(ctx, tile_pos >= 8, SLAI_ERR_SHAPE, "decode: attention items do not fit in shared memory");
+        n_splits = (desc.seq_len + tile_pos - 1) / tile_pos;
+        if (n_splits > 64) n_splits = 64;
+        item_bytes = attn::attn_item_bytes(desc.kv_mul, desc.head_size, esz, tile_pos, n_splits);
+        if (4 * item_bytes <= dig + (size_t)RED_FLOATS * 4) break;
+    }
     plan->dig_region = dig;
     plan->n_splits = n_splits;
-    plan->chunk_max = chunk_max;
-    plan->att_item_floats = (int)item_floats;
     plan->part_o_bytes = (size_t)desc.n_heads * n_splits * desc.head_size * 4;
     plan->part_ml_bytes = (size_t)desc.n_heads * n_splits * 2 * 4;
     // ring depth: probe with the widest phase
@@ -152,49 +291,50 @@ int decode_layers_prepare(slai_ctx* ctx, const DecodeLayersDesc& desc, DecodeLay
     if (rc) return rc;
     plan->nstage = P.nstage;
     plan->smem = smem;
-    return SLAI_OK;
-}
-
-int decode_layers_launch(slai_ctx* ctx, int fmt, const void* d_prog, const void* d_att, int n_layers, int n_kv, int kv_mul,
-                         bool kv_f16, const DecodeLayersPlan& plan) {
-    DecodeParams D;
-    D.prog = reinterpret_cast<const GemvParams*>(d_prog);
-    D.att = reinterpret_cast<const AttnParams*>(d_att);
-    D.n_layers = n_layers;
-    D.n_kv = n_kv;
-    D.att_item_floats = plan.att_item_floats;
-    D.bar = ctx->d_counters + 3100;
-    D.err_flag = ctx->d_counters + 3000;
-    SLAI_CHECK_CUDA(ctx, cudaMemsetAsync(D.bar, 0, sizeof(unsigned int), ctx->stream));
-    switch (fmt) {
-        case SLAI_FMT_Q4_K: return launch_f<Q4K>(ctx, D, plan.smem, kv_f16, kv_mul);
-        case SLAI_FMT_Q5_K: return launch_f<Q5K>(ctx, D, plan.smem, kv_f16, kv_mul);
-        case SLAI_FMT_Q6_K: return launch_f<Q6K>(ctx, D, plan.smem, kv_f16, kv_mul);
-        case SLAI_FMT_Q8_0: return launch_f<Q80>(ctx, D, plan.smem, kv_f16, kv_mul);
+    D->fmt = desc.fmt; D->dim = desc.dim; D->hidden = desc.hidden; D->kv_dim = kv_dim; D->n_heads = desc.n_heads; D->n_kv = n_kv;
+    D->kv_mul = desc.kv_mul; D->head_size = desc.head_size; D->seq_len = desc.seq_len;
+    D->nsteps_dim = (int)layout::num_steps(desc.fmt, desc.dim);
+    D->nsteps_hidden = (int)layout::num_steps(desc.fmt, desc.hidden);
+    D->tile_bytes_dim = (long long)layout::tile_bytes(desc.fmt, desc.dim);
+    D->tile_bytes_hidden = (long long)layout::tile_bytes(desc.fmt, desc.hidden);
+    {
+        const int G = ctx->sm_count;
+        const int n_items[4] = {(desc.dim + 2 * kv_dim) / 16, desc.dim / 16, desc.hidden / 16, desc.dim / 16};
+        for (int k = 0; k < 4; k++) {
+            D->items_base[k] = n_items[k] / G;
+            D->items_rem[k] = n_items[k] % G;
+        }
     }
-    return slai_set_error(ctx, SLAI_ERR_UNSUPPORTED_FORMAT, "decode: format %d has no fused kernel", fmt);
-}
-
-// Host-side builders used by model.cu (keep the parameter structs private to the CUDA files).
-size_t decode_gemv_params_bytes() { return sizeof(GemvParams); }
-size_t decode_attn_params_bytes() { return sizeof(AttnParams); }
-
-int decode_fill_gemv(slai_ctx* ctx, const GemvLaunch& L, const DecodeLayersPlan& plan, void* h_out) {
-    GemvParams P;
-    int rc = gemv_fill_params(ctx, L, plan.dig_region, plan.nstage, P, nullptr, nullptr);
-    if (rc) return rc;
-    memcpy(h_out, &P, sizeof(P));
+    D->nstage = P.nstage; D->step_bytes = P.step_bytes; D->stage_stride = P.stage_stride; D->dig_region = (int)dig;
+    D->n_splits = n_splits; D->tile_pos = tile_pos; D->att_item_bytes = (int)item_bytes;
+    D->bar = ctx->d_counters + 3100;
+    D->err_flag = ctx->d_counters + 3000;
+    D->counters = ctx->d_counters;
     return SLAI_OK;
 }
 
-void decode_fill_attn(slai_ctx* ctx, const DecodeLayersDesc& desc, const DecodeLayersPlan& plan, const float* q, const void* kc,
-                      const void* vc, const int* d_pos, float* out, float* part_o, float* part_ml, void* h_out) {
-    AttnParams A;
-    A.q = q; A.kc = kc; A.vc = vc;
-    A.pos_stride = desc.head_size; A.head_stride = (long long)desc.seq_len * desc.head_size;
-    A.n_heads = desc.n_heads; A.kv_mul = desc.kv_mul; A.hs = desc.head_size;
-    A.d_pos = d_pos; A.n_splits = plan.n_splits; A.chunk_max = plan.chunk_max;
-    A.out = out; A.part_o = part_o; A.part_ml = part_ml;
-    A.counters = ctx->d_counters;
-    memcpy(h_out, &A, sizeof(A));
+int decode_layers_launch(slai_ctx* ctx, const DecodeParams& D, const DecodeLayersPlan& plan) {
+    SLAI_REQUIRE(ctx, D.n_layers >= 1 && D.n_layers <= DECODE_MAX_LAYERS, SLAI_ERR_SHAPE, "decode: %d layers (fused path holds up to %d)",
+                 D.n_layers, DECODE_MAX_LAYERS);
+    SLAI_CHECK_CUDA(ctx, cudaMemsetAsync(D.bar, 0, sizeof(unsigned int), ctx->stream));
+    switch (D.fmt) {
+        case SLAI_FMT_Q4_K: return launch_f<Q4K>(ctx, D, plan.smem);
+        case SLAI_FMT_Q5_K: return launch_f<Q5K>(ctx, D, plan.smem);
+        case SLAI_FMT_Q6_K: return launch_f<Q6K>(ctx, D, plan.smem);
+        case SLAI_FMT_Q8_0: return launch_f<Q80>(ctx, D, plan.smem);
+    }
+    return slai_set_error(ctx, SLAI_ERR_UNSUPPORTED_FORMAT, "decode: format %d has no fused kernel", D.fmt);
 }
+
+#ifdef SLAI_TRACE
+SLAI_API int slai_debug_decode_trace(void* h_out, size_t bytes) { return (int)cudaMemcpyFromSymbol(h_out, g_dtrace, bytes); }
+SLAI_API int slai_debug_decode_trace_reset() {
+    void* p = nullptr;
+    cudaGetSymbolAddress(&p, g_dtrace);
+    return (int)cudaMemset(p, 0, sizeof(g_dtrace));
+}
+SLAI_API int slai_debug_phase_trace(void* h_p, size_t pbytes, void* h_w, size_t wbytes) {
+    int rc = (int)cudaMemcpyFromSymbol(h_p, g_ptrace, pbytes);
+    return rc ? rc : (int)cudaMemcpyFromSymbol(h_w, g_wtrace, wbytes);
+}
+#endif

@@ -14,13 +14,19 @@ namespace {
 template <class F, int NMAT, int PRO, int EPI>
 __global__ void __launch_bounds__(THREADS, 1) gemv_kernel(const __grid_constant__ GemvParams P) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
+    SLAI_TL_BEGIN(100 * NMAT + 10 * PRO + EPI)
     SLAI_TRACE_POINT(0)
     Ring R;
-    ring_init(R, &P, 1, smem_raw, threadIdx.x & 31, threadIdx.x >> 5);
+    const OneProg prog{P};
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // The weights do not depend on the kernel this one may be launched behind (programmatic dependent launch):
+    // the ring starts filling while that kernel drains.
+    ring_init(R, prog, P.dig_region, P.nstage, P.stage_stride, P.step_bytes, P.err_flag, smem_raw, lane, warp);
     SLAI_TRACE_POINT(1)
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    gemv_phase<F, NMAT, PRO, EPI>(P, R, smem_raw, true);
+    gemv_phase<F, 1 << PRO, 1 << EPI>(P, R, prog, smem_raw, NMAT, PRO, EPI);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    SLAI_TL_MARK(2)
 }
 
 // Dense f32 matrix (GpuQuantMatrix::F32): one warp per row.
@@ -136,8 +142,10 @@ int gemv_fill_params(slai_ctx* ctx, const GemvLaunch& L, size_t dig_region, int 
     P.d_pos = L.d_pos; P.kcache = L.kcache; P.vcache = L.vcache; P.kv_f16 = (L.kv_dtype == SLAI_KV_F16);
     P.kv_pos_stride = L.kv_pos_stride; P.kv_head_stride = L.kv_head_stride;
     P.err_flag = ctx->d_counters + 3000;
+    P.pdl = L.pdl ? 1 : 0;
 #ifdef SLAI_TRACE
     P.trace = reinterpret_cast<unsigned long long*>(ctx->d_scratch);  // the debug driver sizes the scratch first
+    P.wtrace = nullptr;
 #endif
     const size_t need = gemv_dig_region(L.fmt, K);
     if (dig_region == 0) dig_region = need;
@@ -158,7 +166,10 @@ int gemv_fill_params(slai_ctx* ctx, const GemvLaunch& L, size_t dig_region, int 
     }
     P.nstage = nstage;
     if (smem_out) *smem_out = fixed + (size_t)nstage * per_stage;
-    if (grid_out) *grid_out = P.n_items < ctx->sm_count ? P.n_items : ctx->sm_count;
+    const int grid = P.n_items < ctx->sm_count ? P.n_items : ctx->sm_count;
+    P.items_base = P.n_items / grid;
+    P.items_rem = P.n_items % grid;
+    if (grid_out) *grid_out = grid;
     return SLAI_OK;
 }
 

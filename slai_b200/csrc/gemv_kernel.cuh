@@ -48,6 +48,7 @@ struct GemvParams {
     int nmat;        // 2: gate/up pair (segments 0 and 1 processed tile by tile together), else 1
     int K;
     int n_items;     // 16-row tiles (nmat == 2: tiles of seg[0])
+    int items_base, items_rem;  // items per block of threads: base each, one more for the first `rem`
     int nsteps;      // tile-step blocks per tile
     int nstage;      // ring depth per warp
     int step_bytes;  // bytes of a tile-step block
@@ -68,8 +69,10 @@ struct GemvParams {
     int kv_f16;
     long long kv_pos_stride, kv_head_stride;
     unsigned int* err_flag;
+    int pdl;  // launched with programmatic stream serialization
 #ifdef SLAI_TRACE
-    unsigned long long* trace;  // debug build only: per block of threads 8 x (globaltimer, clock64)
+    unsigned long long* trace;   // debug build only: per block of threads 8 x (globaltimer, clock64)
+    unsigned long long* wtrace;  // debug build only: per warp (loop start, loop end, cycles waiting for the ring, units)
 #endif
 };
 
@@ -153,9 +156,12 @@ __device__ __forceinline__ float max4(const float4& x) { return fmaxf(fmaxf(fabs
 // [2^25, 2^26), rounding to integers, split into four base-128 digit planes (gemv_frag.cuh), and per-sub-block
 // digit sums (for the `- dmin*m * sum(v)` term of Q4_K / Q5_K and the -32 offset of Q6_K).  Returns 1/scale.
 // The vector is read once (L2 loads: inside the persistent kernel it was written by other SMs during the same
-// launch, so L1 must not be trusted) and kept in registers between the passes when K <= 12288.
-template <int PRO, int SV_GRAN, bool CACHED, class Hook>
-__device__ float stage_impl(const GemvParams& P, const Smem& S, float* stat, int Kp, Hook after_loads) {
+// launch, so L1 must not be trusted) and kept in registers between the passes when K <= 12288; longer vectors are
+// read again in each pass.  The code is kept small on purpose (the digit pass is one rolled loop that rotates the
+// register copy): it runs once per phase, straight out of a cold instruction cache.
+template <int SV_GRAN, bool HAS_LN>
+__device__ __forceinline__ float stage_vector(const int PRO_ARG, const GemvParams& P, const Smem& S, float* stat, int Kp) {
+    const int PRO = (!HAS_LN && PRO_ARG == PRO_LN) ? PRO_RMS : PRO_ARG;  // LayerNorm code only where it can occur
     const int K = P.K;
     const int tid = threadIdx.x;
     const float4* v4 = reinterpret_cast<const float4*>(P.v);
@@ -163,55 +169,61 @@ __device__ float stage_impl(const GemvParams& P, const Smem& S, float* stat, int
     const float4* b4p = reinterpret_cast<const float4*>(P.norm_b);
     const int n4 = K >> 2, np4 = Kp >> 2;
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-    float4 xr[CACHED ? STAGE_REGS : 1];
-    if (CACHED) {
+    const bool cached = np4 <= STAGE_REGS * THREADS;
+    float4 xr[STAGE_REGS];
 #pragma unroll
-        for (int r = 0; r < STAGE_REGS; r++) {
-            const int i = tid + r * THREADS;
-            xr[r] = i < n4 ? __ldcg(v4 + i) : zero4;
-        }
-    }
-    after_loads();  // the vector's loads are in flight ahead of whatever this issues
-    // element group of register slot r (CACHED) or of loop round r (not CACHED)
-#define SLAI_STAGE_LOOP(...)                                                            \
-    if (CACHED) {                                                                       \
-        _Pragma("unroll") for (int r = 0; r < STAGE_REGS; r++) {                        \
-            const int i = tid + r * THREADS;                                            \
-            float4 x = xr[r];                                                           \
-            __VA_ARGS__                                                                 \
-        }                                                                               \
-    } else {                                                                            \
-        for (int i = tid; i < np4; i += THREADS) {                                      \
-            float4 x = i < n4 ? __ldcg(v4 + i) : zero4;                                 \
-            __VA_ARGS__                                                                 \
-        }                                                                               \
+    for (int r = 0; r < STAGE_REGS; r++) {
+        const int i = tid + r * THREADS;
+        xr[r] = (cached && i < n4) ? __ldcg(v4 + i) : zero4;
     }
     float mul = 1.f, sub = 0.f;
     float sum = 0.f, mx = 0.f;
-    if (PRO == PRO_LN) {
-        SLAI_STAGE_LOOP({ sum += (x.x + x.y) + (x.z + x.w); })
+    if (HAS_LN && PRO == PRO_LN) {
+        if (cached) {
+#pragma unroll
+            for (int r = 0; r < STAGE_REGS; r++) sum += (xr[r].x + xr[r].y) + (xr[r].z + xr[r].w);
+        } else {
+#pragma unroll 1
+            for (int i = tid; i < n4; i += THREADS) {
+                const float4 x = __ldcg(v4 + i);
+                sum += (x.x + x.y) + (x.z + x.w);
+            }
+        }
         block_sum_max(sum, mx, stat);
         sub = sum / (float)K;
         sum = 0.f;
     }
-    SLAI_STAGE_LOOP({
-        if (i < n4) {
+    {
+        float4 t[STAGE_REGS];
+#pragma unroll
+        for (int r = 0; r < STAGE_REGS; r++) t[r] = xr[r];
+#pragma unroll 1
+        for (int i = tid; i < n4; i += THREADS) {
+            float4 x;
+            if (cached) {
+                x = t[0];
+#pragma unroll
+                for (int r = 0; r + 1 < STAGE_REGS; r++) t[r] = t[r + 1];
+            } else {
+                x = __ldcg(v4 + i);
+            }
             if (PRO == PRO_NONE) {
                 mx = fmaxf(mx, max4(x));
             } else {
                 const float4 w = __ldg(w4p + i);
-                if (PRO == PRO_LN) { x.x -= sub; x.y -= sub; x.z -= sub; x.w -= sub; }
+                if (HAS_LN && PRO == PRO_LN) { x.x -= sub; x.y -= sub; x.z -= sub; x.w -= sub; }
                 sum += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
                 mx = fmaxf(mx, max4(make_float4(x.x * w.x, x.y * w.y, x.z * w.z, x.w * w.w)));
             }
         }
-    })
+    }
     block_sum_max(sum, mx, stat);
     if (PRO != PRO_NONE) {
         mul = 1.0f / sqrtf(sum / (float)K + P.eps);
         mx *= mul;
-        if (PRO == PRO_LN && P.norm_b) {
+        if (HAS_LN && PRO == PRO_LN && P.norm_b) {
             float mb = 0.f, dummy = 0.f;
+#pragma unroll 1
             for (int i = tid; i < n4; i += THREADS) mb = fmaxf(mb, max4(__ldg(b4p + i)));
             block_sum_max(dummy, mb, stat);
             mx += mb;
@@ -219,61 +231,58 @@ __device__ float stage_impl(const GemvParams& P, const Smem& S, float* stat, int
     }
     float scale = 1.f;
     if (mx > 0.f && mx < 3.0e38f) {
-        int e;
-        frexpf(mx, &e);  // mx = f * 2^e, f in [0.5, 1)
+        int e = (int)((__float_as_uint(mx) >> 23) & 0xffu) - 126;  // mx = f * 2^e with f in [0.5, 1) (normal numbers)
+        if ((__float_as_uint(mx) >> 23) == 0u) e = -126;              // subnormal: scale as the smallest normal
         e = e < -90 ? -90 : e;
-        scale = ldexpf(1.0f, 26 - e);
+        scale = __uint_as_float((uint32_t)(127 + 26 - e) << 23);       // 2^(26 - e), exact
     }
     unsigned char* dig = reinterpret_cast<unsigned char*>(__cvta_shared_to_generic(S.dig));
     int4* sv = reinterpret_cast<int4*>(__cvta_shared_to_generic(S.sv));
-    SLAI_STAGE_LOOP({
-        if (i < np4) {  // np4 is a multiple of 64: whole warps take the branch together
-            if (i < n4) {
-                if (PRO == PRO_RMS) {
-                    const float4 w = __ldg(w4p + i);
-                    x.x = (x.x * mul) * w.x; x.y = (x.y * mul) * w.y; x.z = (x.z * mul) * w.z; x.w = (x.w * mul) * w.w;
-                } else if (PRO == PRO_LN) {
-                    const float4 w = __ldg(w4p + i);
-                    x.x = ((x.x - sub) * mul) * w.x; x.y = ((x.y - sub) * mul) * w.y;
-                    x.z = ((x.z - sub) * mul) * w.z; x.w = ((x.w - sub) * mul) * w.w;
-                    if (P.norm_b) {
-                        const float4 b = __ldg(b4p + i);
-                        x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
-                    }
-                }
-            }
-            int d0[4], d1[4], d2[4], d3[4];
-            split_digits(__float2int_rn(x.x * scale), d0);
-            split_digits(__float2int_rn(x.y * scale), d1);
-            split_digits(__float2int_rn(x.z * scale), d2);
-            split_digits(__float2int_rn(x.w * scale), d3);
-            int s[4];
-            _Pragma("unroll") for (int p = 0; p < 4; p++) {
-                const uint32_t word = (uint32_t)(d0[p] & 0xFF) | ((uint32_t)(d1[p] & 0xFF) << 8) | ((uint32_t)(d2[p] & 0xFF) << 16) |
-                                      ((uint32_t)(d3[p] & 0xFF) << 24);
-                *reinterpret_cast<uint32_t*>(dig + (size_t)p * S.plane + 4 * i) = word;
-                s[p] = (d0[p] + d1[p]) + (d2[p] + d3[p]);
-            }
-            if (SV_GRAN > 0) {
-                _Pragma("unroll") for (int p = 0; p < 4; p++) {
-                    s[p] += __shfl_xor_sync(0xffffffffu, s[p], 1);
-                    s[p] += __shfl_xor_sync(0xffffffffu, s[p], 2);
-                    if (SV_GRAN == 32) s[p] += __shfl_xor_sync(0xffffffffu, s[p], 4);
-                }
-                constexpr int LANES = SV_GRAN > 0 ? SV_GRAN / 4 : 1;  // float4 groups per sub-block
-                if ((tid & (LANES - 1)) == 0) sv[i / LANES] = make_int4(s[0], s[1], s[2], s[3]);
+#pragma unroll 1
+    for (int i = tid; i < np4; i += THREADS) {  // np4 is a multiple of 64: whole warps run each round together
+        float4 x;
+        if (cached) {
+            x = xr[0];
+#pragma unroll
+            for (int r = 0; r + 1 < STAGE_REGS; r++) xr[r] = xr[r + 1];
+        } else {
+            x = i < n4 ? __ldcg(v4 + i) : zero4;
+        }
+        if (i < n4 && PRO != PRO_NONE) {
+            const float4 w = __ldg(w4p + i);
+            if (HAS_LN && PRO == PRO_LN) { x.x -= sub; x.y -= sub; x.z -= sub; x.w -= sub; }
+            x.x = (x.x * mul) * w.x; x.y = (x.y * mul) * w.y; x.z = (x.z * mul) * w.z; x.w = (x.w * mul) * w.w;
+            if (HAS_LN && PRO == PRO_LN && P.norm_b) {
+                const float4 b = __ldg(b4p + i);
+                x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
             }
         }
-    })
-#undef SLAI_STAGE_LOOP
+        int d0[4], d1[4], d2[4], d3[4];
+        split_digits(__float2int_rn(x.x * scale), d0);
+        split_digits(__float2int_rn(x.y * scale), d1);
+        split_digits(__float2int_rn(x.z * scale), d2);
+        split_digits(__float2int_rn(x.w * scale), d3);
+        int sd[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const uint32_t word = (uint32_t)(d0[q] & 0xFF) | ((uint32_t)(d1[q] & 0xFF) << 8) | ((uint32_t)(d2[q] & 0xFF) << 16) |
+                                  ((uint32_t)(d3[q] & 0xFF) << 24);
+            *reinterpret_cast<uint32_t*>(dig + (size_t)q * S.plane + 4 * i) = word;
+            sd[q] = (d0[q] + d1[q]) + (d2[q] + d3[q]);
+        }
+        if (SV_GRAN > 0) {
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                sd[q] += __shfl_xor_sync(0xffffffffu, sd[q], 1);
+                sd[q] += __shfl_xor_sync(0xffffffffu, sd[q], 2);
+                if (SV_GRAN == 32) sd[q] += __shfl_xor_sync(0xffffffffu, sd[q], 4);
+            }
+            constexpr int LANES = SV_GRAN > 0 ? SV_GRAN / 4 : 1;  // float4 groups per sub-block
+            if ((tid & (LANES - 1)) == 0) sv[i / LANES] = make_int4(sd[0], sd[1], sd[2], sd[3]);
+        }
+    }
     __syncthreads();
     return 1.0f / scale;
-}
-
-template <int PRO, int SV_GRAN, class Hook>
-__device__ float stage_vector(const GemvParams& P, const Smem& S, float* stat, int Kp, Hook after_loads) {
-    if ((Kp >> 2) <= STAGE_REGS * THREADS) return stage_impl<PRO, SV_GRAN, true>(P, S, stat, Kp, after_loads);
-    return stage_impl<PRO, SV_GRAN, false>(P, S, stat, Kp, after_loads);
 }
 
 __device__ __forceinline__ float gelu_ref(float x) {
@@ -287,9 +296,93 @@ __device__ __forceinline__ int seg_of_tile(const GemvParams& P, int tile) {
     if (P.nseg > 2 && tile >= P.seg[2].tile0) s = 2;
     return s;
 }
+// Segment `s` by value through selects: the parameters may live in registers (persistent decode kernel), where a
+// dynamically indexed array would be spilled to local memory.
+__device__ __forceinline__ GemvSeg seg_pick(const GemvParams& P, int s) {
+    GemvSeg r = P.seg[0];
+    if (P.nseg > 1 && s == 1) r = P.seg[1];
+    if (P.nseg > 2 && s == 2) r = P.seg[2];
+    return r;
+}
+
+// A *program* tells the ring producer what to stream: entry i is a GEMV phase with `nsteps` blocks per tile,
+// `nmat` matrices per item and items dealt to the blocks of threads as `items_base` each plus one more for the
+// first `items_rem`; tile_ptr gives the first block of (item, matrix).  The stand-alone kernel's program is its
+// one parameter block.
+struct ProgGeom {
+    int nsteps, nmat, items_base, items_rem;
+};
+struct OneProg {
+    const GemvParams& P;
+    __device__ __forceinline__ int size() const { return 1; }
+    __device__ __forceinline__ ProgGeom geom(int) const { return ProgGeom{P.nsteps, P.nmat, P.items_base, P.items_rem}; }
+    __device__ __forceinline__ const uint8_t* tile_ptr(int, int item, int mat) const {
+        const int sidx = P.nmat == 2 ? mat : seg_of_tile(P, item);
+        const uint8_t* w = P.seg[0].w;
+        long long tb = P.seg[0].tile_bytes;
+        int t0 = 0;
+        if (sidx == 1) { w = P.seg[1].w; tb = P.seg[1].tile_bytes; t0 = P.seg[1].tile0; }
+        if (sidx == 2) { w = P.seg[2].w; tb = P.seg[2].tile_bytes; t0 = P.seg[2].tile0; }
+        const int tile = P.nmat == 2 ? item : item - t0;
+        return w + (size_t)tile * tb;
+    }
+};
 
 // ---------------------------------------------------------------------------------------------
-// Per-warp ring state and the producer that walks a program of GEMV phases.
+// Work split.  A block of threads owns `n_local` consecutive items starting at `i0`; they are processed in waves
+// of WAVE items, and the wave's sequence of (item, matrix, step) units is cut into WARPS equal pieces.  A cursor
+// walks one warp's piece; the consumer and the ring producer (which runs `nstage` units ahead) each have one.
+// Everything here is division-free: it runs at every phase change, out of a cold instruction cache.
+// ---------------------------------------------------------------------------------------------
+struct Split {
+    int i0, n_local, n_waves, upi, nsteps, nmat;
+};
+__device__ __forceinline__ Split make_split(const ProgGeom& g) {
+    Split s;
+    const int b = (int)blockIdx.x;
+    s.i0 = b * g.items_base + min(b, g.items_rem);
+    s.n_local = g.items_base + (b < g.items_rem ? 1 : 0);
+    s.n_waves = (s.n_local + WAVE - 1) / WAVE;
+    s.nsteps = g.nsteps;
+    s.nmat = g.nmat;
+    s.upi = g.nsteps * g.nmat;
+    return s;
+}
+struct Cursor {
+    int wave, u, u1, li, mat, step;
+};
+// Position the cursor on this warp's piece of wave `c.wave`.
+__device__ __forceinline__ void cursor_wave(Cursor& c, const Split& s, int warp) {
+    const int items = min(WAVE, s.n_local - c.wave * WAVE);
+    const int U = items * s.upi;
+    c.u = (U * warp) / WARPS;
+    c.u1 = (U * (warp + 1)) / WARPS;
+    int rem = c.u;
+    c.li = 0;
+    while (rem >= s.upi) {  // at most WAVE rounds
+        rem -= s.upi;
+        c.li++;
+    }
+    c.mat = 0;
+    if (rem >= s.nsteps) {  // only with two matrices per item
+        rem -= s.nsteps;
+        c.mat = 1;
+    }
+    c.step = rem;
+}
+// After the last step of a (item, matrix) run: first step of the next one.
+__device__ __forceinline__ void cursor_next_run(Cursor& c, const Split& s) {
+    c.step = 0;
+    if (s.nmat == 2 && c.mat == 0) {
+        c.mat = 1;
+    } else {
+        c.mat = 0;
+        c.li++;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Per-warp ring state and the producer that walks the program.
 // ---------------------------------------------------------------------------------------------
 struct Ring {
     uint32_t mbar, ring;      // shared-space addresses of this warp's barriers and stages
@@ -300,70 +393,37 @@ struct Ring {
     bool alive;
     unsigned int* err_flag;
     // producer
-    const GemvParams* prog;
-    int n_prog, p_idx;
-    int i0, n_local, n_waves, upi, nsteps, nmat;  // geometry of program entry p_idx for this block of threads
-    int p_wave, p_u, p_u1, p_li, p_mat, p_step, p_stage;
+    int p_idx, p_stage;
+    Split ps;
+    Cursor pc;
     const uint8_t* p_ptr;
 };
 
 // Shared-memory layout: [staged vector: dig_region bytes][red RED_FLOATS f32][stat 64 f32][mbar][ring]
 __device__ __forceinline__ uint32_t smem_fixed_bytes(int dig_region) { return (uint32_t)dig_region + RED_FLOATS * 4 + 64 * 4; }
 
-// this warp's unit range inside wave `wv` of a phase with `n_local` tiles of `upi` units
-__device__ __forceinline__ void wave_range(int n_local, int upi, int wv, int warp, int& u0, int& u1) {
-    const int items = min(WAVE, n_local - wv * WAVE);
-    const int U = items * upi;
-    u0 = (U * warp) / WARPS;
-    u1 = (U * (warp + 1)) / WARPS;
-}
-
-__device__ __forceinline__ const uint8_t* prod_base(const Ring& R, int li, int mat) {
-    const GemvParams& P = R.prog[R.p_idx];
-    const int item = R.i0 + R.p_wave * WAVE + li;
-    const int sidx = R.nmat == 2 ? mat : seg_of_tile(P, item);
-    const GemvSeg& sg = P.seg[sidx];
-    const int tile = R.nmat == 2 ? item : item - sg.tile0;
-    return sg.w + (size_t)tile * sg.tile_bytes;
-}
-__device__ __forceinline__ void prod_seek(Ring& R) {  // divisions only here (once per wave)
-    if (R.p_u < R.p_u1) {
-        R.p_li = R.p_u / R.upi;
-        const int rem = R.p_u - R.p_li * R.upi;
-        R.p_mat = R.nmat == 2 ? rem / R.nsteps : 0;
-        R.p_step = rem - R.p_mat * R.nsteps;
-        R.p_ptr = prod_base(R, R.p_li, R.p_mat) + (size_t)R.p_step * R.step_bytes;
-    }
-}
-__device__ __forceinline__ void prod_enter(Ring& R, int warp) {  // load the geometry of program entry p_idx
-    if (R.p_idx >= R.n_prog) return;
-    const GemvParams& P = R.prog[R.p_idx];
-    R.nsteps = P.nsteps;
-    R.nmat = P.nmat;
-    R.upi = P.nsteps * P.nmat;
-    R.i0 = (int)(((long long)P.n_items * blockIdx.x) / gridDim.x);
-    const int i1 = (int)(((long long)P.n_items * (blockIdx.x + 1)) / gridDim.x);
-    R.n_local = i1 - R.i0;
-    R.n_waves = (R.n_local + WAVE - 1) / WAVE;
-    R.p_wave = 0;
-    R.p_u = R.p_u1 = 0;
-    if (R.n_waves > 0) {
-        wave_range(R.n_local, R.upi, 0, warp, R.p_u, R.p_u1);
-        prod_seek(R);
-    }
+template <class Prog>
+__device__ __forceinline__ void prod_point(Ring& R, const Prog& prog) {  // address of the cursor's unit
+    if (R.pc.u < R.pc.u1)
+        R.p_ptr = prog.tile_ptr(R.p_idx, R.ps.i0 + R.pc.wave * WAVE + R.pc.li, R.pc.mat) + (size_t)R.pc.step * R.step_bytes;
 }
 // Issue the copy of the next block of this warp's sequence (if any) into the next ring stage.
-__device__ __forceinline__ void prod_issue(Ring& R, int lane, int warp) {
-    while (R.p_idx < R.n_prog && (R.p_wave >= R.n_waves || R.p_u >= R.p_u1)) {  // skip exhausted waves / phases
-        if (R.p_wave < R.n_waves && ++R.p_wave < R.n_waves) {
-            wave_range(R.n_local, R.upi, R.p_wave, warp, R.p_u, R.p_u1);
-            prod_seek(R);
-        } else {
-            R.p_idx++;
-            prod_enter(R, warp);
+template <class Prog>
+__device__ __forceinline__ void prod_issue(Ring& R, const Prog& prog, int lane, int warp) {
+    while (R.p_idx < prog.size() && R.pc.u >= R.pc.u1) {  // piece exhausted: next wave, else next program entry
+        if (++R.pc.wave >= R.ps.n_waves) {
+            if (++R.p_idx >= prog.size()) break;
+            R.ps = make_split(prog.geom(R.p_idx));
+            R.pc.wave = 0;
+            if (R.ps.n_waves == 0) {
+                R.pc.u = R.pc.u1 = 0;
+                continue;
+            }
         }
+        cursor_wave(R.pc, R.ps, warp);
+        prod_point(R, prog);
     }
-    if (R.p_idx >= R.n_prog) return;
+    if (R.p_idx >= prog.size()) return;
     if (lane == 0) {
         const uint32_t mb = R.mbar + 8 * R.p_stage;
         mbar_expect_tx(mb, R.step_bytes);
@@ -371,103 +431,106 @@ __device__ __forceinline__ void prod_issue(Ring& R, int lane, int warp) {
     }
     if (++R.p_stage == R.nstage) R.p_stage = 0;
     R.p_ptr += R.step_bytes;
-    if (++R.p_u < R.p_u1 && ++R.p_step == R.nsteps) {  // next (tile, matrix)
-        R.p_step = 0;
-        if (R.nmat == 2 && R.p_mat == 0) {
-            R.p_mat = 1;
-        } else {
-            R.p_mat = 0;
-            R.p_li++;
-        }
-        R.p_ptr = prod_base(R, R.p_li, R.p_mat);
+    if (++R.pc.u < R.pc.u1 && ++R.pc.step == R.ps.nsteps) {  // next (item, matrix)
+        cursor_next_run(R.pc, R.ps);
+        prod_point(R, prog);
     }
 }
 
-// Set up the ring of this warp for a program; P0 is the first entry (all entries share the ring geometry).
-__device__ __forceinline__ void ring_init(Ring& R, const GemvParams* prog, int n_prog, unsigned char* smem_raw, int lane, int warp) {
-    const GemvParams& P0 = prog[0];
+// Set up the ring of this warp (all program entries share the ring geometry) and start the stream: the first
+// `nstage` blocks are requested here.
+template <class Prog>
+__device__ __forceinline__ void ring_init(Ring& R, const Prog& prog, int dig_region, int nstage, int stage_stride, int step_bytes,
+                                          unsigned int* err_flag, unsigned char* smem_raw, int lane, int warp) {
     const uint32_t base = (uint32_t)__cvta_generic_to_shared(smem_raw);
-    const uint32_t mbar_base = base + smem_fixed_bytes(P0.dig_region);
+    const uint32_t mbar_base = base + smem_fixed_bytes(dig_region);
     const uint32_t ring_base = (mbar_base + WARPS * MAX_STAGES * 8 + 127u) & ~127u;
-    R.nstage = P0.nstage;
-    R.stage_stride = P0.stage_stride;
-    R.step_bytes = P0.step_bytes;
+    R.nstage = nstage;
+    R.stage_stride = stage_stride;
+    R.step_bytes = step_bytes;
     R.mbar = mbar_base + warp * MAX_STAGES * 8;
     R.ring = ring_base + warp * R.nstage * R.stage_stride;
     R.c_stage = 0;
     R.c_phase = 0;
     R.alive = true;
-    R.err_flag = P0.err_flag;
-    R.prog = prog;
-    R.n_prog = n_prog;
-    R.p_idx = 0;
+    R.err_flag = err_flag;
     R.p_stage = 0;
     R.p_ptr = nullptr;
-    R.p_li = R.p_mat = R.p_step = 0;
-    R.n_waves = 0;
-    R.p_wave = 0;
     if (lane == 0) {
         for (int s = 0; s < R.nstage; s++) mbar_init(R.mbar + 8 * s, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncwarp();
-    prod_enter(R, warp);
+    // park the producer "before" entry 0 with an exhausted piece: the first prod_issue walks into it
+    R.p_idx = -1;
+    R.ps.n_waves = 0;
+    R.ps.nsteps = 1;
+    R.ps.nmat = 1;
+    R.ps.upi = 1;
+    R.ps.i0 = R.ps.n_local = 0;
+    R.pc.wave = 0;
+    R.pc.u = R.pc.u1 = 0;
+    R.pc.li = R.pc.mat = R.pc.step = 0;
+#pragma unroll 1
+    for (int s = 0; s < R.nstage; s++) prod_issue(R, prog, lane, warp);
 }
 
 // ---------------------------------------------------------------------------------------------
-// One GEMV phase (consumer side).  `first` : this is the first phase of the launch, whose ring fill has not
-// been issued yet (it is issued right behind the activation loads).
+// One GEMV phase (consumer side).
 // ---------------------------------------------------------------------------------------------
-template <class F, int NMAT, int PRO, int EPI>
-__device__ void gemv_phase(const GemvParams& P, Ring& R, unsigned char* smem_raw, bool first) {
+// NMAT (1, or 2 for the gate/up pair), PRO and EPI are compile-time constants in the stand-alone kernels (the
+// function is inlined and the branches fold) and run-time values in the persistent decode kernel, which keeps ONE
+// copy of this code for all its phases so that it stays in the instruction cache from layer to layer.
+// PRO_MASK / EPI_MASK: bit i set = value i can occur (code for the others is not generated).
+template <class F, int PRO_MASK, int EPI_MASK, class Prog>
+__device__ __forceinline__ void gemv_phase(const GemvParams& P, Ring& R, const Prog& prog, unsigned char* smem_raw,
+                                           const int NMAT, const int PRO, const int EPI) {
+#define SLAI_EPI_IS(x) ((((EPI_MASK) >> (x)) & 1) && EPI == (x))
     const int K = P.K;
     const int Kp = (K + 255) & ~255;
-    constexpr int SV_BYTES_PER_256 = F::SV_GRAN > 0 ? 256 / F::SV_GRAN * 16 : 0;
     Smem S;
     S.dig = (uint32_t)__cvta_generic_to_shared(smem_raw);
     S.plane = Kp + 32;  // planes 32 bytes apart modulo 128: the four digit columns of a sub-block hit different banks
     S.sv = S.dig + 4 * S.plane;
     float* red = reinterpret_cast<float*>(smem_raw + P.dig_region);
     float* stat = red + RED_FLOATS;
-    (void)SV_BYTES_PER_256;
 
     const int tid = threadIdx.x, warp = tid >> 5;
     LaneCtx L;
     lane_init(L, tid & 31, S);
 
-    const int nsteps = P.nsteps;
-    const int upi = nsteps * NMAT;
-    const int i0 = (int)(((long long)P.n_items * blockIdx.x) / gridDim.x);
-    const int i1 = (int)(((long long)P.n_items * (blockIdx.x + 1)) / gridDim.x);
-    const int n_local = i1 - i0;
-    const int n_waves = (n_local + WAVE - 1) / WAVE;
+    const Split sp = make_split(ProgGeom{P.nsteps, NMAT, P.items_base, P.items_rem});
 
     for (int i = tid; i < WAVE * WARPS * NMAT * 16; i += THREADS) red[i] = 0.f;
     SLAI_TRACE_POINT(2)
-    // The activation vector's loads go out first; the first ring fill follows them into the memory system.
-    const float inv_scale = stage_vector<PRO, F::SV_GRAN>(P, S, stat, Kp, [&]() {
-        if (first)
-            for (int s = 0; s < R.nstage; s++) prod_issue(R, L.lane, warp);
-    });
+    const float inv_scale = stage_vector<F::SV_GRAN, ((PRO_MASK >> PRO_LN) & 1) != 0>(PRO, P, S, stat, Kp);
     SLAI_TRACE_POINT(3)
 
-    for (int wv = 0; wv < n_waves; wv++) {
-        int u, u1;
-        wave_range(n_local, upi, wv, warp, u, u1);
-        while (u < u1) {
-            // one run of consecutive units inside the same (tile, matrix)
-            const int li = u / upi, rem = u - li * upi;
-            const int mat = NMAT == 2 ? rem / nsteps : 0;
-            int step = rem - mat * nsteps;
-            const int run_end = min(u1, u + (nsteps - step));
+#ifdef SLAI_TRACE
+    long long w_t0 = clock64(), w_wait = 0, w_units = 0;
+#endif
+    Cursor c;
+    for (c.wave = 0; c.wave < sp.n_waves; c.wave++) {
+        cursor_wave(c, sp, warp);
+        while (c.u < c.u1) {
+            // one run of consecutive steps inside the same (item, matrix)
+            const int run_end = min(c.u1, c.u + (sp.nsteps - c.step));
             float accA = 0.f, accB = 0.f;
-            for (; u < run_end; u++, step++) {
+#pragma unroll 1
+            for (; c.u < run_end; c.u++, c.step++) {
+#ifdef SLAI_TRACE
+                const long long w_a = clock64();
+#endif
                 if (R.alive) R.alive = mbar_wait(R.mbar + 8 * R.c_stage, R.c_phase, R.err_flag);
-                F::compute(R.ring + R.c_stage * R.stage_stride, step, L, S, accA, accB);
+#ifdef SLAI_TRACE
+                w_wait += clock64() - w_a;
+                w_units++;
+#endif
+                F::compute(R.ring + R.c_stage * R.stage_stride, c.step, L, S, accA, accB);
                 __syncwarp();
                 if (L.lane == 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                prod_issue(R, L.lane, warp);  // refill the stage just consumed
+                prod_issue(R, prog, L.lane, warp);  // refill the stage just consumed
                 if (++R.c_stage == R.nstage) {
                     R.c_stage = 0;
                     R.c_phase ^= 1;
@@ -477,12 +540,23 @@ __device__ void gemv_phase(const GemvParams& P, Ring& R, unsigned char* smem_raw
             accA += __shfl_xor_sync(0xffffffffu, accA, 2);
             accB += __shfl_xor_sync(0xffffffffu, accB, 1);
             accB += __shfl_xor_sync(0xffffffffu, accB, 2);
-            if (L.t == 0) {  // a warp has at most one run per (tile, matrix): plain stores
-                float* dst = red + ((li * WARPS + warp) * NMAT + mat) * 16;
+            if (L.t == 0) {  // a warp has at most one run per (item, matrix): plain stores
+                float* dst = red + ((c.li * WARPS + warp) * NMAT + c.mat) * 16;
                 dst[L.g] = accA;
                 dst[L.g + 8] = accB;
             }
+            cursor_next_run(c, sp);
         }
+        const int wv = c.wave, n_waves = sp.n_waves, n_local = sp.n_local, i0 = sp.i0;
+#ifdef SLAI_TRACE
+        if (P.wtrace && L.lane == 0 && wv + 1 == n_waves) {
+            unsigned long long* wt = P.wtrace + (blockIdx.x * WARPS + warp) * 4;
+            wt[0] = w_t0;
+            wt[1] = clock64();
+            wt[2] = w_wait;
+            wt[3] = w_units;
+        }
+#endif
         SLAI_TRACE_POINT(4)
         __syncthreads();
         SLAI_TRACE_POINT(5)
@@ -491,32 +565,33 @@ __device__ void gemv_phase(const GemvParams& P, Ring& R, unsigned char* smem_raw
         if (tid < items * 16) {
             const int li = tid >> 4, r = tid & 15;
             const int item = i0 + wv * WAVE + li;
-            float val[NMAT];
+            float val[2] = {0.f, 0.f};
 #pragma unroll
-            for (int mat = 0; mat < NMAT; mat++) {
-                float s = 0.f;
+            for (int mat = 0; mat < 2; mat++)
+                if (mat < NMAT) {
+                    float s = 0.f;
 #pragma unroll
-                for (int w = 0; w < WARPS; w++) s += red[((li * WARPS + w) * NMAT + mat) * 16 + r];
-                val[mat] = s * inv_scale;
-            }
+                    for (int w = 0; w < WARPS; w++) s += red[((li * WARPS + w) * NMAT + mat) * 16 + r];
+                    val[mat] = s * inv_scale;
+                }
             const int sidx = NMAT == 2 ? 0 : seg_of_tile(P, item);
-            const GemvSeg& sg = P.seg[sidx];
+            const GemvSeg sg = seg_pick(P, sidx);
             const int row_in_seg = (NMAT == 2 ? item : item - sg.tile0) * 16 + r;
             const bool valid = row_in_seg < sg.rows;
             const int orow = sg.out_off + row_in_seg;
             const float bias = (sg.bias && valid) ? sg.bias[row_in_seg] : 0.f;
-            if (EPI == EPI_STORE) {
+            if (SLAI_EPI_IS(EPI_STORE)) {
                 if (valid) P.out[orow] = val[0] + bias;
-            } else if (EPI == EPI_RESID) {
+            } else if (SLAI_EPI_IS(EPI_RESID)) {
                 if (valid) P.out[orow] = __ldcg(P.resid + orow) + (val[0] + bias);
-            } else if (EPI == EPI_SILU) {
+            } else if (SLAI_EPI_IS(EPI_SILU)) {
                 if (valid) {
                     const float gt = val[0], up = val[NMAT - 1];
                     P.out[orow] = up * (gt / (1.0f + expf(-gt)));
                 }
-            } else if (EPI == EPI_GELU) {
+            } else if (SLAI_EPI_IS(EPI_GELU)) {
                 if (valid) P.out[orow] = gelu_ref(val[0] + bias);
-            } else if (EPI == EPI_QKV) {
+            } else if (SLAI_EPI_IS(EPI_QKV)) {
                 float y = val[0] + bias;
                 const int pos = __ldcg(P.d_pos);
                 // rows 2i, 2i+1 of a tile sit in neighbouring lanes of the same half-warp
@@ -548,6 +623,7 @@ __device__ void gemv_phase(const GemvParams& P, Ring& R, unsigned char* smem_raw
             __syncthreads();
         }
     }
+#undef SLAI_EPI_IS
 }
 
 }  // namespace gemvk

@@ -92,26 +92,27 @@ struct slai_llama {
     int fused_state = 0;  // 0 not prepared, 1 ready, -1 not eligible
     int fused_fmt = 0;
     DecodeLayersPlan plan;
-    void *d_prog = nullptr, *d_att = nullptr;
+    DecodeParams* dparams = nullptr;  // parameter block of the persistent kernel (host copy, passed by value at launch)
     float *f_part_o = nullptr, *f_part_ml = nullptr;
 };
 
 static void llama_drop_fused(slai_llama* m) {
-    if (m->d_prog || m->d_att || m->f_part_o || m->f_part_ml) cudaStreamSynchronize(m->ctx->stream);
-    cudaFree(m->d_prog); cudaFree(m->d_att); cudaFree(m->f_part_o); cudaFree(m->f_part_ml);
-    m->d_prog = m->d_att = nullptr;
+    if (m->f_part_o || m->f_part_ml) cudaStreamSynchronize(m->ctx->stream);
+    cudaFree(m->f_part_o); cudaFree(m->f_part_ml);
+    delete m->dparams;
+    m->dparams = nullptr;
     m->f_part_o = m->f_part_ml = nullptr;
     m->fused_state = 0;
 }
 
-// Builds the program of the persistent decode kernel when every layer matrix has the same quantised format.
+// Describes the model to the persistent decode kernel when every layer matrix has the same quantised format.
 static int llama_prepare_fused(slai_llama* m) {
     slai_ctx* ctx = m->ctx;
     const slai_llama_config& c = m->cfg;
     m->fused_state = -1;
     const char* nf = getenv("SLAI_NO_FUSED");
     if (nf && nf[0] == '1') return SLAI_OK;
-    if (c.rope_variant != 0 || m->kv_mul > 8) return SLAI_OK;
+    if (c.rope_variant != 0 || m->kv_mul > 8 || c.n_layers > DECODE_MAX_LAYERS) return SLAI_OK;
     const int fmt = m->layers[0].wq ? m->layers[0].wq->fmt : 0;
     if (fmt != SLAI_FMT_Q4_K && fmt != SLAI_FMT_Q5_K && fmt != SLAI_FMT_Q6_K && fmt != SLAI_FMT_Q8_0) return SLAI_OK;
     for (auto& w : m->layers) {
@@ -120,53 +121,48 @@ static int llama_prepare_fused(slai_llama* m) {
             if (!q || q->fmt != fmt) return SLAI_OK;
         if (!w.attn_norm || !w.ffn_norm) return SLAI_OK;
     }
-    DecodeLayersDesc desc{fmt, c.dim, c.hidden_dim, c.n_q_heads, m->kv_mul, m->head_size, c.seq_len};
+    DecodeLayersDesc desc{fmt, c.dim, c.hidden_dim, c.n_q_heads, m->kv_mul, m->head_size, c.seq_len, c.kv_dtype == SLAI_KV_F16};
     cudaGetLastError();
-    if (decode_layers_prepare(ctx, desc, &m->plan) != SLAI_OK) return SLAI_OK;  // does not fit: keep the per-kernel path
-    const size_t gb = decode_gemv_params_bytes(), ab = decode_attn_params_bytes();
-    std::vector<unsigned char> hprog(gb * 4 * c.n_layers), hatt(ab * c.n_layers);
-    if (cudaMalloc(&m->f_part_o, m->plan.part_o_bytes + 256) != cudaSuccess || cudaMalloc(&m->f_part_ml, m->plan.part_ml_bytes + 256) != cudaSuccess ||
-        cudaMalloc(&m->d_prog, hprog.size()) != cudaSuccess || cudaMalloc(&m->d_att, hatt.size()) != cudaSuccess) {
+    DecodeParams* D = new DecodeParams();
+    memset(D, 0, sizeof(*D));
+    m->dparams = D;
+    auto give_up = [&]() {
         cudaGetLastError();
         llama_drop_fused(m);
         m->fused_state = -1;
         return SLAI_OK;
-    }
-    int* d_pos = m->sc.d + 1;
+    };
+    if (decode_layers_prepare(ctx, desc, &m->plan, D) != SLAI_OK) return give_up();  // does not fit: keep the per-kernel path
+    if (cudaMalloc(&m->f_part_o, m->plan.part_o_bytes + 256) != cudaSuccess || cudaMalloc(&m->f_part_ml, m->plan.part_ml_bytes + 256) != cudaSuccess)
+        return give_up();
     const size_t esz = c.kv_dtype == SLAI_KV_F16 ? 2 : 4;
+    D->n_layers = c.n_layers;
+    D->eps = c.rms_norm_eps;
+    D->rope_theta = m->rope_theta;
+    D->d_pos = m->sc.d + 1;
+    D->kv_f16 = c.kv_dtype == SLAI_KV_F16;
+    D->x = m->x; D->xb = m->xb; D->q = m->q; D->hb = m->hb;
+    D->part_o = m->f_part_o; D->part_ml = m->f_part_ml;
+    {
+        const uintptr_t bits = reinterpret_cast<uintptr_t>(m->kcache) | reinterpret_cast<uintptr_t>(m->vcache) |
+                               (uintptr_t)(m->kv_layer_elems * esz) | (uintptr_t)((size_t)c.seq_len * m->head_size * esz) |
+                               (uintptr_t)(m->head_size * esz);
+        if (bits & 3) return give_up();
+        D->vec16 = (bits & 15) == 0;
+    }
     for (int l = 0; l < c.n_layers; l++) {
         const LlamaLayer& w = m->layers[l];
-        void* kc = (char*)m->kcache + (size_t)l * m->kv_layer_elems * esz;
-        void* vc = (char*)m->vcache + (size_t)l * m->kv_layer_elems * esz;
-        GemvLaunch L[4];
-        L[0].fmt = fmt; L[0].K = c.dim; L[0].nseg = 3;
-        L[0].seg[0] = seg_of(w.wq, 0, c.dim, w.bq, 0, 0);
-        L[0].seg[1] = seg_of(w.wk, 0, m->kv_dim, w.bk, 0, 1);
-        L[0].seg[2] = seg_of(w.wv, 0, m->kv_dim, w.bv, 0, 2);
-        L[0].v = m->x; L[0].out = m->q; L[0].pro = PRO_RMS; L[0].norm_w = w.attn_norm; L[0].eps = c.rms_norm_eps;
-        L[0].epi = EPI_QKV; L[0].rope = 1; L[0].rope_theta = m->rope_theta; L[0].head_size = m->head_size;
-        L[0].d_pos = d_pos; L[0].kcache = kc; L[0].vcache = vc; L[0].kv_dtype = c.kv_dtype;
-        L[0].kv_pos_stride = m->head_size; L[0].kv_head_stride = (int64_t)c.seq_len * m->head_size;
-        L[1].fmt = fmt; L[1].K = c.dim; L[1].nseg = 1; L[1].seg[0] = seg_of(w.wo, 0, c.dim, nullptr, 0, 0);
-        L[1].v = m->xb; L[1].out = m->x; L[1].resid = m->x; L[1].epi = EPI_RESID;
-        L[2].fmt = fmt; L[2].K = c.dim; L[2].nseg = 2;
-        L[2].seg[0] = seg_of(w.wgate, 0, c.hidden_dim, nullptr, 0, 0);
-        L[2].seg[1] = seg_of(w.wup, 0, c.hidden_dim, nullptr, 0, 0);
-        L[2].v = m->x; L[2].out = m->hb; L[2].pro = PRO_RMS; L[2].norm_w = w.ffn_norm; L[2].eps = c.rms_norm_eps; L[2].epi = EPI_SILU;
-        L[3].fmt = fmt; L[3].K = c.hidden_dim; L[3].nseg = 1; L[3].seg[0] = seg_of(w.wdown, 0, c.dim, nullptr, 0, 0);
-        L[3].v = m->hb; L[3].out = m->x; L[3].resid = m->x; L[3].epi = EPI_RESID;
-        for (int k = 0; k < 4; k++) {
-            int rc = decode_fill_gemv(ctx, L[k], m->plan, hprog.data() + gb * (4 * l + k));
-            if (rc) {
-                llama_drop_fused(m);
-                m->fused_state = -1;
-                return SLAI_OK;
-            }
-        }
-        decode_fill_attn(ctx, desc, m->plan, m->q, kc, vc, d_pos, m->xb, m->f_part_o, m->f_part_ml, hatt.data() + ab * l);
+        const slai_qmatrix* kd[6] = {w.wq, w.wk, w.wv, w.wo, w.wgate, w.wup};
+        for (auto* q : kd)
+            if (q->tile_bytes != D->tile_bytes_dim) return give_up();
+        if (w.wdown->tile_bytes != D->tile_bytes_hidden) return give_up();
+        DecodeLayerPtrs& P = D->layer[l];
+        P.wq = w.wq->data; P.wk = w.wk->data; P.wv = w.wv->data; P.wo = w.wo->data;
+        P.wgate = w.wgate->data; P.wup = w.wup->data; P.wdown = w.wdown->data;
+        P.attn_norm = w.attn_norm; P.ffn_norm = w.ffn_norm; P.bq = w.bq; P.bk = w.bk; P.bv = w.bv;
+        P.kcache = (char*)m->kcache + (size_t)l * m->kv_layer_elems * esz;
+        P.vcache = (char*)m->vcache + (size_t)l * m->kv_layer_elems * esz;
     }
-    SLAI_CHECK_CUDA(ctx, cudaMemcpy(m->d_prog, hprog.data(), hprog.size(), cudaMemcpyHostToDevice));
-    SLAI_CHECK_CUDA(ctx, cudaMemcpy(m->d_att, hatt.data(), hatt.size(), cudaMemcpyHostToDevice));
     m->fused_fmt = fmt;
     m->fused_state = 1;
     return SLAI_OK;
@@ -188,9 +184,7 @@ static int llama_record(slai_llama* m, int kind) {
     const size_t esz = c.kv_dtype == SLAI_KV_F16 ? 2 : 4;
     if (m->fused_state == 1) {
         // all layers in one persistent kernel
-        if ((rc = decode_layers_launch(ctx, m->fused_fmt, m->d_prog, m->d_att, c.n_layers, c.n_kv_heads, m->kv_mul,
-                                       c.kv_dtype == SLAI_KV_F16, m->plan)))
-            return rc;
+        if ((rc = decode_layers_launch(ctx, *m->dparams, m->plan))) return rc;
         n += 2;  // barrier reset + kernel
     }
     for (int l = 0; l < (m->fused_state == 1 ? 0 : c.n_layers); l++) {
@@ -334,6 +328,8 @@ static int run_graph(M* m, int kind, RecordFn record) {
         if (graph) cudaGraphDestroy(graph);
         if (rc != SLAI_OK || e != cudaSuccess) {
             // some launches (e.g. cooperative ones on older drivers) cannot be captured: run eagerly from now on
+            fprintf(stderr, "slai_b200: CUDA graph capture of the decode step failed (%s); launching eagerly\n",
+                    e != cudaSuccess ? cudaGetErrorString(e) : "record error");
             cudaGetLastError();
             m->graphs.use_graph = false;
             return record(m, kind);

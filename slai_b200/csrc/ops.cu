@@ -882,6 +882,15 @@ SLAI_API int slai_synth_normal_f32(slai_ctx* ctx, float* d_out, int64_t n, uint6
 }
 
 #ifdef SLAI_TRACE
+__device__ unsigned long long g_tl[3 * 4096];
+__device__ unsigned int g_tl_count;
+SLAI_API int slai_debug_timeline(void* h_out, size_t bytes, unsigned int* count) {
+    int rc = (int)cudaMemcpyFromSymbol(h_out, g_tl, bytes);
+    if (rc == 0) rc = (int)cudaMemcpyFromSymbol(count, g_tl_count, 4);
+    unsigned int zero = 0;
+    if (rc == 0) rc = (int)cudaMemcpyToSymbol(g_tl_count, &zero, 4);
+    return rc;
+}
 // debug build only (never part of the shipped library): device address of the context's scratch buffer
 SLAI_API void* slai_debug_scratch(slai_ctx* ctx) { return ctx ? ctx->d_scratch : nullptr; }
 #endif
