@@ -65,7 +65,10 @@ enum slai_kv_dtype { SLAI_KV_F32 = 0, SLAI_KV_F16 = 1 };
 /* ---- context: LlmOps::new / LlmContext::begin_submission / submit (context.rs:47-96) ---------------- */
 int slai_ctx_create(int device, slai_ctx** out);
 int slai_ctx_destroy(slai_ctx* ctx);
-int slai_ctx_sync(slai_ctx* ctx); /* backend.synchronize() (chat_llama2.rs:222-223); blocking */
+/* backend.synchronize() (chat_llama2.rs:222-223); blocking.  Also reports SLAI_ERR_TIMEOUT when a bounded wait
+ * inside a kernel (weight ring, grid barrier) ran out since the last call: every device-side wait has an
+ * iteration limit and raises a flag instead of hanging. */
+int slai_ctx_sync(slai_ctx* ctx);
 const char* slai_last_error_string(slai_ctx* ctx);
 void* slai_ctx_stream(slai_ctx* ctx); /* the cudaStream_t all work of this context is enqueued on */
 int slai_device_count(void);
@@ -80,6 +83,20 @@ int slai_write_buffer(slai_ctx* ctx, void* d_dst, const void* h_src, size_t byte
 int slai_read_buffer(slai_ctx* ctx, void* h_dst, const void* d_src, size_t bytes);  /* blocking         */
 int slai_malloc_host(slai_ctx* ctx, size_t bytes, void** h_out); /* pinned host memory */
 int slai_free_host(slai_ctx* ctx, void* h_ptr);
+
+/* ---- recorded passes: B::Encoder / begin_pass ... submit (context.rs:63-96, slai-bench main.rs:199-219) -- */
+/* The reference records operator launches into an encoder and submits them together.  Here: every operator call
+ * between `slai_pass_begin` and `slai_pass_end` is recorded (CUDA stream capture) instead of run; the recorded pass
+ * is replayed with `slai_pass_launch` (`times` back-to-back replays, no host work between the kernels).
+ * Calls that allocate or block (matrix creation, reads, the first `slai_attention` at a new size) cannot be
+ * recorded: run the sequence once eagerly first.  Arguments are frozen at record time; buffers a recorded call
+ * uses must stay allocated until the pass is destroyed, and nothing may be freed or copied synchronously while
+ * recording (both synchronise the device, which ends the recording with an error). */
+typedef struct slai_pass slai_pass;
+int slai_pass_begin(slai_ctx* ctx);
+int slai_pass_end(slai_ctx* ctx, slai_pass** out);
+int slai_pass_launch(slai_ctx* ctx, slai_pass* pass, int times);
+int slai_pass_destroy(slai_ctx* ctx, slai_pass* pass);
 
 /* ---- stream timing: the GPU timestamp queries of crates/slai-bench/src/main.rs:198,221-242 ---------- */
 int slai_timer_start(slai_ctx* ctx);          /* records an event on the stream */

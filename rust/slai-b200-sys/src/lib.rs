@@ -4,7 +4,7 @@
 use std::os::raw::{c_char, c_void};
 
 macro_rules! opaque { ($($n:ident),*) => { $(#[repr(C)] pub struct $n { _private: [u8; 0] })* } }
-opaque!(slai_ctx, slai_qmatrix, slai_llama, slai_gpt2);
+opaque!(slai_ctx, slai_qmatrix, slai_llama, slai_gpt2, slai_pass);
 
 pub const SLAI_OK: i32 = 0;
 pub const SLAI_ERR_INVALID_ARG: i32 = 1;
@@ -46,6 +46,10 @@ extern "C" {
     pub fn slai_read_buffer(ctx: *mut slai_ctx, h_dst: *mut c_void, d_src: *const c_void, bytes: usize) -> i32;
     pub fn slai_malloc_host(ctx: *mut slai_ctx, bytes: usize, h_out: *mut *mut c_void) -> i32;
     pub fn slai_free_host(ctx: *mut slai_ctx, h_ptr: *mut c_void) -> i32;
+    pub fn slai_pass_begin(ctx: *mut slai_ctx) -> i32;
+    pub fn slai_pass_end(ctx: *mut slai_ctx, out: *mut *mut slai_pass) -> i32;
+    pub fn slai_pass_launch(ctx: *mut slai_ctx, pass: *mut slai_pass, times: i32) -> i32;
+    pub fn slai_pass_destroy(ctx: *mut slai_ctx, pass: *mut slai_pass) -> i32;
     pub fn slai_timer_start(ctx: *mut slai_ctx) -> i32;
     pub fn slai_timer_stop(ctx: *mut slai_ctx, ms: *mut f32) -> i32;
     pub fn slai_qmatrix_create(ctx: *mut slai_ctx, fmt: i32, nrows: i64, ncols: i64, h_blocks: *const c_void, nbytes: usize, out: *mut *mut slai_qmatrix) -> i32;

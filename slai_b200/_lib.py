@@ -64,6 +64,10 @@ SIGNATURES = {
     "slai_read_buffer": (C.c_int, [_vp, _vp, _vp, _sz]),
     "slai_malloc_host": (C.c_int, [_vp, _sz, _pp]),
     "slai_free_host": (C.c_int, [_vp, _vp]),
+    "slai_pass_begin": (C.c_int, [_vp]),
+    "slai_pass_end": (C.c_int, [_vp, _pp]),
+    "slai_pass_launch": (C.c_int, [_vp, _vp, C.c_int]),
+    "slai_pass_destroy": (C.c_int, [_vp, _vp]),
     "slai_timer_start": (C.c_int, [_vp]),
     "slai_timer_stop": (C.c_int, [_vp, C.POINTER(_f)]),
     "slai_qmatrix_create": (C.c_int, [_vp, C.c_int, _i64, _i64, _vp, _sz, _pp]),

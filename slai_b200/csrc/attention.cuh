@@ -42,20 +42,22 @@ struct AttnParams {
 // the block-wide barrier).
 __device__ __forceinline__ void att_sync(int id) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(ATT_THREADS) : "memory"); }
 
-// Shared memory of one item, in bytes: q | scores | running (max, sum, rescale) | flag | K tile (rows padded by
-// 16 bytes: the four threads of a position and the eight positions of a warp then hit 32 different banks) | V tile.
-// The merge of the splits reuses the tile area for the (max, sum) pairs of all splits.
+// Shared memory of one item, in bytes: q | scores | running (max, sum, rescale) | flag | one tile buffer that holds
+// the K rows (padded by 16 bytes: the four threads of a position and the eight positions of a warp then hit 32
+// different banks) and, once the scores are done, the V rows.  The merge of the splits reuses the tile buffer for
+// the (max, sum) pairs of all splits.
 __host__ __device__ inline size_t attn_k_stride(int hs, int esz) { return (size_t)hs * esz + 16; }
 __host__ __device__ inline size_t attn_head_bytes(int kv_mul, int hs, int tile_pos) {
     return (((size_t)kv_mul * hs + (size_t)kv_mul * tile_pos + 4 * (size_t)kv_mul + 4) * 4 + 15) & ~(size_t)15;
 }
 __host__ __device__ inline size_t attn_item_bytes(int kv_mul, int hs, int esz, int tile_pos, int n_splits) {
-    size_t tiles = tile_pos * attn_k_stride(hs, esz) + (size_t)tile_pos * hs * esz;
-    const size_t merge = (size_t)kv_mul * n_splits * 2 * 4;
-    if (merge > tiles) tiles = merge;
-    return attn_head_bytes(kv_mul, hs, tile_pos) + ((tiles + 15) & ~(size_t)15);
+    size_t tile = tile_pos * attn_k_stride(hs, esz);
+    const size_t merge = (size_t)kv_mul * n_splits * 4 * 4;  // (max, sum) pairs of all splits, then their weights
+    if (merge > tile) tile = merge;
+    return attn_head_bytes(kv_mul, hs, tile_pos) + ((tile + 15) & ~(size_t)15);
 }
-// Positions per tile: about 8 KB of K (and of V) per item, a multiple of 8, at most 32.
+// Positions per tile: at most 8 KB of K (and of V) per item -- four 16-byte pieces per thread and matrix -- a
+// multiple of 8, at most 32.
 __host__ __device__ inline int attn_tile_pos(int hs, int esz) {
     int t = (8192 / (hs * esz)) & ~7;
     return t < 8 ? 8 : t > 32 ? 32 : t;
@@ -76,34 +78,46 @@ template <> struct Elem<float> {
     __device__ static __forceinline__ float ld1(const unsigned char* p) { return *reinterpret_cast<const float*>(p); }
 };
 
-// Copy `rows` rows of K and of V (row_bytes each, row_pitch bytes apart in memory) into shared memory.  All the
-// loads of a batch (eight per thread) are issued before the first store, so a tile costs one trip to memory.
-// L2 loads (ld.global.cg): inside the persistent decode kernel the newest row was written by another SM during
-// the same launch, so L1 must not be trusted.
-template <typename V>
-__device__ __forceinline__ void load_tiles(const unsigned char* kg, const unsigned char* vg, size_t row_pitch, int row_bytes, int rows,
-                                           unsigned char* k_s, int k_stride, unsigned char* v_s, int tid) {
-    const int ppr = row_bytes / (int)sizeof(V);
-    const int half = rows * ppr, total = 2 * half;
-    for (int base = 0; base < total; base += 8 * ATT_THREADS) {
-        V buf[8];
+// Rows of a tile travel as pieces of type V (16 bytes, or 4 when something is not 16-byte aligned); thread `tid`
+// owns pieces tid, tid + 128, ...  A batch is NB pieces per thread: all its loads are issued before anything waits
+// for them, so a tile costs one trip to memory.  L2 loads (ld.global.cg): inside the persistent decode kernel the
+// newest row was written by another SM during the same launch, so L1 must not be trusted.
+struct Pieces {  // (row, column) of this thread's four 16-byte pieces; the same for every tile of an item
+    int r[4], c[4];
+    __device__ __forceinline__ void init(int ppr, int tid) {
+        int rr = tid / ppr, cc = tid - rr * ppr;
+        const int dr = ATT_THREADS / ppr, dc = ATT_THREADS - dr * ppr;
 #pragma unroll
-        for (int u = 0; u < 8; u++) {
-            const int idx = base + tid + u * ATT_THREADS;
-            if (idx < total) {
-                const int isv = idx >= half, j = idx - isv * half, r = j / ppr, c = j - r * ppr;
-                buf[u] = __ldcg(reinterpret_cast<const V*>((isv ? vg : kg) + (size_t)r * row_pitch) + c);
+        for (int u = 0; u < 4; u++) {
+            r[u] = rr;
+            c[u] = cc;
+            rr += dr;
+            cc += dc;
+            if (cc >= ppr) {
+                cc -= ppr;
+                rr++;
             }
         }
+    }
+};
+__device__ __forceinline__ void load_pieces(uint4 (&buf)[4], const Pieces& w, const unsigned char* g, size_t row_pitch, int rows) {
 #pragma unroll
-        for (int u = 0; u < 8; u++) {
-            const int idx = base + tid + u * ATT_THREADS;
-            if (idx < total) {
-                const int isv = idx >= half, j = idx - isv * half, r = j / ppr, c = j - r * ppr;
-                unsigned char* dst = isv ? v_s + (size_t)r * row_bytes : k_s + (size_t)r * k_stride;
-                reinterpret_cast<V*>(dst)[c] = buf[u];
-            }
-        }
+    for (int u = 0; u < 4; u++)
+        if (w.r[u] < rows) buf[u] = __ldcg(reinterpret_cast<const uint4*>(g + (size_t)w.r[u] * row_pitch) + w.c[u]);
+}
+__device__ __forceinline__ void store_pieces(const uint4 (&buf)[4], const Pieces& w, unsigned char* s, int row_stride, int rows) {
+#pragma unroll
+    for (int u = 0; u < 4; u++)
+        if (w.r[u] < rows) reinterpret_cast<uint4*>(s + (size_t)w.r[u] * row_stride)[w.c[u]] = buf[u];
+}
+// Slow path (something is not 16-byte aligned): 4-byte pieces, one at a time.
+__device__ __forceinline__ void copy_rows_u32(const unsigned char* g, size_t row_pitch, int row_bytes, int rows, unsigned char* s,
+                                              int row_stride, int tid) {
+    const int ppr = row_bytes >> 2, total = rows * ppr;
+#pragma unroll 1
+    for (int idx = tid; idx < total; idx += ATT_THREADS) {
+        const int r = idx / ppr, c = idx - r * ppr;
+        reinterpret_cast<unsigned int*>(s + (size_t)r * row_stride)[c] = __ldcg(reinterpret_cast<const unsigned int*>(g + (size_t)r * row_pitch) + c);
     }
 }
 
@@ -122,7 +136,6 @@ __device__ __forceinline__ void attn_item(const AttnParams& P, int kvh, int spli
     unsigned char* k_s = smb + attn_head_bytes(kv_mul, hs, TP);
     const int k_stride = (int)attn_k_stride(hs, ESZ);
     const int row_bytes = hs * ESZ;
-    unsigned char* v_s = k_s + (size_t)TP * k_stride;
     const int lane = tid & 31, warp = tid >> 5;
 
     const int chunk = (n + ns - 1) / ns;
@@ -150,14 +163,25 @@ __device__ __forceinline__ void attn_item(const AttnParams& P, int kvh, int spli
     float acc[MAXQ][2];
 #pragma unroll
     for (int h = 0; h < MAXQ; h++) acc[h][0] = acc[h][1] = 0.f;
+    Pieces pw;
+    pw.init(row_bytes >> 4, tid);
 
+#pragma unroll 1
     for (int tt = t0; tt < t1; tt += TP) {
         const int cnt = min(TP, t1 - tt);
         if (tt != t0) att_sync(bar_id);  // the previous tile has been consumed
-        if (P.vec16)
-            load_tiles<uint4>(kbase + (size_t)tt * row_pitch, vbase + (size_t)tt * row_pitch, row_pitch, row_bytes, cnt, k_s, k_stride, v_s, tid);
-        else
-            load_tiles<unsigned int>(kbase + (size_t)tt * row_pitch, vbase + (size_t)tt * row_pitch, row_pitch, row_bytes, cnt, k_s, k_stride, v_s, tid);
+        // K goes to the tile buffer; V is requested in the same trip and waits in registers until K is done with
+        uint4 vb[4];
+        {
+            if (P.vec16) {
+                uint4 kb[4];
+                load_pieces(kb, pw, kbase + (size_t)tt * row_pitch, row_pitch, cnt);
+                load_pieces(vb, pw, vbase + (size_t)tt * row_pitch, row_pitch, cnt);
+                store_pieces(kb, pw, k_s, k_stride, cnt);
+            } else {
+                copy_rows_u32(kbase + (size_t)tt * row_pitch, row_pitch, row_bytes, cnt, k_s, k_stride, tid);
+            }
+        }
         if (tt == t0) {
 #pragma unroll
             for (int u = 0; u < 2 * MAXQ; u++) {
@@ -170,6 +194,8 @@ __device__ __forceinline__ void attn_item(const AttnParams& P, int kvh, int spli
         // scores: four threads per position, 32 positions per pass
         {
             const int c = tid & 3;
+#pragma unroll 1
+#pragma unroll 1
             for (int i0 = 0; i0 < cnt; i0 += 32) {
                 const int i = i0 + (tid >> 2);
                 float part[MAXQ];
@@ -177,6 +203,8 @@ __device__ __forceinline__ void attn_item(const AttnParams& P, int kvh, int spli
                 for (int h = 0; h < MAXQ; h++) part[h] = 0.f;
                 if (i < cnt) {
                     const unsigned char* kp = k_s + (size_t)i * k_stride;
+#pragma unroll 4
+#pragma unroll 4
                     for (int e = c; e < (hs >> 1); e += 4) {
                         const float2 k2 = Elem<T>::ld2(kp + 2 * e * ESZ);
 #pragma unroll
@@ -197,14 +225,20 @@ __device__ __forceinline__ void attn_item(const AttnParams& P, int kvh, int spli
             }
         }
         att_sync(bar_id);
+        // the K rows are done with: V takes their place (read by the last step of this tile)
+        if (P.vec16) store_pieces(vb, pw, k_s, row_bytes, cnt);
+        else copy_rows_u32(vbase + (size_t)tt * row_pitch, row_pitch, row_bytes, cnt, k_s, row_bytes, tid);
         // running softmax per query head
+#pragma unroll 1
         for (int h = warp; h < kv_mul; h += ATT_WARPS) {
             const float m_old = st_s[4 * h], l_old = st_s[4 * h + 1];
             float m = m_old;
+#pragma unroll 1
             for (int i = lane; i < cnt; i += 32) m = fmaxf(m, sc_s[h * TP + i]);
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
             float l = 0.f;
+#pragma unroll 1
             for (int i = lane; i < cnt; i += 32) {
                 const float p = expf(sc_s[h * TP + i] - m);
                 sc_s[h * TP + i] = p;
@@ -230,8 +264,10 @@ __device__ __forceinline__ void attn_item(const AttnParams& P, int kvh, int spli
                 float a[MAXQ];
 #pragma unroll
                 for (int h = 0; h < MAXQ; h++) a[h] = h < kv_mul ? acc[h][jj] * st_s[4 * h + 2] : 0.f;
+#pragma unroll 4
+#pragma unroll 4
                 for (int i = 0; i < cnt; i++) {
-                    const float v = Elem<T>::ld1(v_s + (size_t)i * row_bytes + (size_t)d * ESZ);
+                    const float v = Elem<T>::ld1(k_s + (size_t)i * row_bytes + (size_t)d * ESZ);
 #pragma unroll
                     for (int h = 0; h < MAXQ; h++)
                         if (h < kv_mul) a[h] = fmaf(sc_s[h * TP + i], v, a[h]);
@@ -274,37 +310,49 @@ __device__ __forceinline__ void attn_item(const AttnParams& P, int kvh, int spli
     ATT_TRACE(5)
     if (!*is_last_p) return;
     __threadfence();
-    // Merge the splits of this KV head (fixed order over splits).  The (max, sum) pairs of all splits are first
-    // brought into shared memory with independent loads, then every thread merges its output elements, eight
-    // independent loads at a time.
-    float* ml_all = reinterpret_cast<float*>(k_s);  // kv_mul * ns * 2 floats (attn_item_bytes reserves them)
-    {
-        for (int i = tid; i < kv_mul * ns * 2; i += ATT_THREADS) {
-            const int h = i / (2 * ns), r = i - h * 2 * ns;
-            ml_all[i] = __ldcg(P.part_ml + ((size_t)(kvh * kv_mul + h) * P.n_splits) * 2 + r);
-        }
+    // Merge the splits of this KV head (fixed order over splits).  The (max, sum) pairs of all splits come into
+    // shared memory with independent loads and are turned into weights once; every thread then combines its
+    // output elements, sixteen independent loads at a time.
+    float* ml_all = reinterpret_cast<float*>(k_s);  // [kv_mul][ns][2] (max, sum), then [kv_mul][ns][2] (weight, weight*sum)
+    float* w_all = ml_all + kv_mul * ns * 2;
+#pragma unroll 1
+    for (int i = tid; i < kv_mul * ns * 2; i += ATT_THREADS) {
+        const int h = i / (2 * ns), r = i - h * 2 * ns;
+        ml_all[i] = __ldcg(P.part_ml + ((size_t)(kvh * kv_mul + h) * P.n_splits) * 2 + r);
     }
     att_sync(bar_id);
-    for (int i = tid; i < kv_mul * hs; i += ATT_THREADS) {
-        const int h = i / hs, d = i % hs;
-        const int head = kvh * kv_mul + h;
+#pragma unroll 1
+    for (int i = tid; i < kv_mul * ns; i += ATT_THREADS) {
+        const int h = i / ns;
         const float* ml = ml_all + h * ns * 2;
         float M = -INFINITY;
+#pragma unroll 1
         for (int s = 0; s < ns; s++)
             if (ml[2 * s + 1] > 0.f) M = fmaxf(M, ml[2 * s]);
+        const float l = ml_all[2 * i + 1];
+        const float w = l > 0.f ? expf(ml_all[2 * i] - M) : 0.f;
+        w_all[2 * i] = w;
+        w_all[2 * i + 1] = w * l;
+    }
+    att_sync(bar_id);
+#pragma unroll 1
+    for (int i = tid; i < kv_mul * hs; i += ATT_THREADS) {
+        const int h = i / hs, d = i - h * hs;
+        const int head = kvh * kv_mul + h;
+        const float* wl = w_all + h * ns * 2;
         const float* po = P.part_o + ((size_t)head * P.n_splits) * hs + d;
         float num = 0.f, den = 0.f;
-        for (int s0 = 0; s0 < ns; s0 += 8) {
-            float o[8];
+#pragma unroll 1
+        for (int s0 = 0; s0 < ns; s0 += 16) {
+            float o[16];
 #pragma unroll
-            for (int u = 0; u < 8; u++) o[u] = s0 + u < ns ? __ldcg(po + (size_t)(s0 + u) * hs) : 0.f;
+            for (int u = 0; u < 16; u++) o[u] = s0 + u < ns ? __ldcg(po + (size_t)(s0 + u) * hs) : 0.f;
 #pragma unroll
-            for (int u = 0; u < 8; u++)
+            for (int u = 0; u < 16; u++)
                 if (s0 + u < ns) {
-                    const float l = ml[2 * (s0 + u) + 1];
-                    const float w = l > 0.f ? expf(ml[2 * (s0 + u)] - M) : 0.f;
-                    num = fmaf(w, l > 0.f ? o[u] : 0.f, num);
-                    den = fmaf(w, l, den);
+                    const float w = wl[2 * (s0 + u)];
+                    num = fmaf(w, w > 0.f ? o[u] : 0.f, num);
+                    den += wl[2 * (s0 + u) + 1];
                 }
         }
         P.out[(size_t)head * hs + d] = num / den;

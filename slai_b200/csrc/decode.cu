@@ -156,11 +156,10 @@ __device__ __forceinline__ void grid_sync(const DecodeParams& D, unsigned int& e
 
 // Attention phase: four items (KV head, split) at a time per block of threads, 128 threads each.
 template <typename KV, int MAXQ>
-__device__ __forceinline__ void attention_phase(const DecodeParams& D, const AttnParams& A, unsigned char* smem_raw) {
+__device__ __forceinline__ void attention_phase(const DecodeParams& D, const AttnParams& A, int n, unsigned char* smem_raw) {
     const int sub = threadIdx.x >> 7, tid = threadIdx.x & 127;
     if (sub >= 4) return;  // (THREADS is 512: never taken; keeps the mapping explicit)
     unsigned char* sm = smem_raw + (size_t)sub * D.att_item_bytes;
-    const int n = __ldcg(A.d_pos) + 1;
     const int ns = attn::attn_splits(A, n);
     const int n_items = D.n_kv * ns;
     for (int item = blockIdx.x * 4 + sub; item < n_items; item += gridDim.x * 4) {
@@ -189,6 +188,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const __grid_
     const LayerProg prog{D};
     ring_init(R, prog, D.dig_region, D.nstage, D.stage_stride, D.step_bytes, D.err_flag, smem_raw, threadIdx.x & 31, threadIdx.x >> 5);
     unsigned int epoch = 0;
+    const int n_pos = __ldcg(D.d_pos) + 1;  // positions in the cache after this token (fixed for the launch)
     // One copy of the GEMV phase serves the four GEMVs of a layer (k = 0 QKV, 1 O, 2 gate/up, 3 down): the
     // code of a whole layer then fits the instruction cache and stays there from layer to layer.
     constexpr int PRO_MASK = (1 << PRO_NONE) | (1 << PRO_RMS);
@@ -199,18 +199,23 @@ __global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const __grid_
         for (int k = 0; k < 4; k++) {
             DTRACE(k == 0 ? 0 : 2 * k + 2)
             {
-                const GemvParams P = phase_params(D, l, k);
+                GemvParams P = phase_params(D, l, k);
+                P.pos1 = n_pos;
                 const int nmat = k == 2 ? 2 : 1;
                 const int pro = (k == 0 || k == 2) ? PRO_RMS : PRO_NONE;
                 const int epi = k == 0 ? EPI_QKV : k == 2 ? EPI_SILU : EPI_RESID;
+#ifndef SIZE_NO_GEMV
                 gemv_phase<F, PRO_MASK, EPI_MASK>(P, R, prog, smem_raw, nmat, pro, epi);
+#endif
             }
             DTRACE(k == 0 ? 1 : 2 * k + 3)
             if (k < 3 || l + 1 < D.n_layers) grid_sync(D, epoch);
             if (k == 0) {
                 DTRACE(2)
                 const AttnParams A = attn_params(D, l);
-                attention_phase<KV, MAXQ>(D, A, smem_raw);
+#ifndef SIZE_NO_ATTN
+                attention_phase<KV, MAXQ>(D, A, n_pos, smem_raw);
+#endif
                 DTRACE(3)
                 grid_sync(D, epoch);
             }
@@ -268,7 +273,11 @@ int decode_layers_prepare(slai_ctx* ctx, const DecodeLayersDesc& desc, DecodeLay
     size_t item_bytes = 0;
     for (;; tile_pos -= 8) {
         SLAI_REQUIRE(ctx, tile_pos >= 8, SLAI_ERR_SHAPE, "decode: attention items do not fit in shared memory");
+        // one split per tile while they all run at once (four per block of threads); longer contexts walk several
+        // tiles per split instead of queueing more splits
         n_splits = (desc.seq_len + tile_pos - 1) / tile_pos;
+        const int at_once = (4 * ctx->sm_count) / n_kv;
+        if (n_splits > at_once) n_splits = at_once < 1 ? 1 : at_once;
         if (n_splits > 64) n_splits = 64;
         item_bytes = attn::attn_item_bytes(desc.kv_mul, desc.head_size, esz, tile_pos, n_splits);
         if (4 * item_bytes <= dig + (size_t)RED_FLOATS * 4) break;

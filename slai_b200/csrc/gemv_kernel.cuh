@@ -64,6 +64,7 @@ struct GemvParams {
     const float* rope_theta;
     int head_size;
     const int* d_pos;
+    int pos1;        // position + 1 when the caller already knows it (0: read d_pos)
     void* kcache;
     void* vcache;
     int kv_f16;
@@ -193,29 +194,28 @@ __device__ __forceinline__ float stage_vector(const int PRO_ARG, const GemvParam
         sub = sum / (float)K;
         sum = 0.f;
     }
-    {
-        float4 t[STAGE_REGS];
-#pragma unroll
-        for (int r = 0; r < STAGE_REGS; r++) t[r] = xr[r];
-#pragma unroll 1
-        for (int i = tid; i < n4; i += THREADS) {
-            float4 x;
-            if (cached) {
-                x = t[0];
-#pragma unroll
-                for (int r = 0; r + 1 < STAGE_REGS; r++) t[r] = t[r + 1];
-            } else {
-                x = __ldcg(v4 + i);
-            }
-            if (PRO == PRO_NONE) {
-                mx = fmaxf(mx, max4(x));
-            } else {
-                const float4 w = __ldg(w4p + i);
-                if (HAS_LN && PRO == PRO_LN) { x.x -= sub; x.y -= sub; x.z -= sub; x.w -= sub; }
-                sum += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
-                mx = fmaxf(mx, max4(make_float4(x.x * w.x, x.y * w.y, x.z * w.z, x.w * w.w)));
-            }
+    auto stats = [&](float4 x, const float4& w) {
+        if (PRO == PRO_NONE) {
+            mx = fmaxf(mx, max4(x));
+        } else {
+            if (HAS_LN && PRO == PRO_LN) { x.x -= sub; x.y -= sub; x.z -= sub; x.w -= sub; }
+            sum += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+            mx = fmaxf(mx, max4(make_float4(x.x * w.x, x.y * w.y, x.z * w.z, x.w * w.w)));
         }
+    };
+    if (cached) {
+        float4 wr[STAGE_REGS];  // norm weights: all requested before the first is used
+#pragma unroll
+        for (int r = 0; r < STAGE_REGS; r++) {
+            const int i = tid + r * THREADS;
+            wr[r] = (PRO != PRO_NONE && i < n4) ? __ldg(w4p + i) : zero4;
+        }
+#pragma unroll
+        for (int r = 0; r < STAGE_REGS; r++)
+            if (tid + r * THREADS < n4) stats(xr[r], wr[r]);
+    } else {
+#pragma unroll 1
+        for (int i = tid; i < n4; i += THREADS) stats(__ldcg(v4 + i), PRO != PRO_NONE ? __ldg(w4p + i) : zero4);
     }
     block_sum_max(sum, mx, stat);
     if (PRO != PRO_NONE) {
@@ -249,7 +249,7 @@ __device__ __forceinline__ float stage_vector(const int PRO_ARG, const GemvParam
             x = i < n4 ? __ldcg(v4 + i) : zero4;
         }
         if (i < n4 && PRO != PRO_NONE) {
-            const float4 w = __ldg(w4p + i);
+            const float4 w = __ldg(w4p + i);  // L1 hit: the statistics pass has read it
             if (HAS_LN && PRO == PRO_LN) { x.x -= sub; x.y -= sub; x.z -= sub; x.w -= sub; }
             x.x = (x.x * mul) * w.x; x.y = (x.y * mul) * w.y; x.z = (x.z * mul) * w.z; x.w = (x.w * mul) * w.w;
             if (HAS_LN && PRO == PRO_LN && P.norm_b) {
@@ -593,7 +593,7 @@ __device__ __forceinline__ void gemv_phase(const GemvParams& P, Ring& R, const P
                 if (valid) P.out[orow] = gelu_ref(val[0] + bias);
             } else if (SLAI_EPI_IS(EPI_QKV)) {
                 float y = val[0] + bias;
-                const int pos = __ldcg(P.d_pos);
+                const int pos = P.pos1 > 0 ? P.pos1 - 1 : __ldcg(P.d_pos);
                 // rows 2i, 2i+1 of a tile sit in neighbouring lanes of the same half-warp
                 const float other = __shfl_xor_sync(__activemask(), y, 1);
                 if (P.rope && sg.role < 2) {

@@ -84,6 +84,14 @@ SLAI_API int slai_ctx_destroy(slai_ctx* ctx) {
 SLAI_API int slai_ctx_sync(slai_ctx* ctx) {
     if (!ctx) return SLAI_ERR_INVALID_ARG;
     SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    // Every wait inside the kernels (ring barriers, grid barrier) is bounded; one that ran out raised this flag.
+    unsigned int flag = 0;
+    SLAI_CHECK_CUDA(ctx, cudaMemcpy(&flag, ctx->d_counters + 3000, sizeof(flag), cudaMemcpyDeviceToHost));
+    if (flag) {
+        cudaMemset(ctx->d_counters + 3000, 0, sizeof(flag));
+        return slai_set_error(ctx, SLAI_ERR_TIMEOUT, "a bounded wait inside a kernel ran out (%s); results of the last launches are invalid",
+                              flag == 1 ? "weight ring" : "grid barrier");
+    }
     return SLAI_OK;
 }
 SLAI_API const char* slai_last_error_string(slai_ctx* ctx) { return ctx ? ctx->last_error.c_str() : g_noctx_error.c_str(); }
@@ -139,6 +147,51 @@ SLAI_API int slai_free_host(slai_ctx* ctx, void* h_ptr) {
     SLAI_CHECK_CUDA(ctx, cudaFreeHost(h_ptr));
     return SLAI_OK;
 }
+// ---- recorded passes ---------------------------------------------------------------------------------
+struct slai_pass {
+    cudaGraphExec_t exec = nullptr;
+};
+SLAI_API int slai_pass_begin(slai_ctx* ctx) {
+    if (!ctx) return SLAI_ERR_INVALID_ARG;
+    SLAI_CHECK_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+    return SLAI_OK;
+}
+SLAI_API int slai_pass_end(slai_ctx* ctx, slai_pass** out) {
+    if (!ctx || !out) return SLAI_ERR_INVALID_ARG;
+    *out = nullptr;
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+    if (e != cudaSuccess || !graph) {
+        cudaGetLastError();
+        return slai_set_error(ctx, SLAI_ERR_CUDA, "pass: recording failed (%s); a recorded call allocated or blocked",
+                              cudaGetErrorString(e));
+    }
+    slai_pass* p = new slai_pass();
+    e = cudaGraphInstantiate(&p->exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) {
+        delete p;
+        cudaGetLastError();
+        return slai_set_error(ctx, SLAI_ERR_CUDA, "pass: %s", cudaGetErrorString(e));
+    }
+    *out = p;
+    return SLAI_OK;
+}
+SLAI_API int slai_pass_launch(slai_ctx* ctx, slai_pass* pass, int times) {
+    if (!ctx || !pass || !pass->exec || times < 0) return SLAI_ERR_INVALID_ARG;
+    for (int i = 0; i < times; i++) SLAI_CHECK_CUDA(ctx, cudaGraphLaunch(pass->exec, ctx->stream));
+    return SLAI_OK;
+}
+SLAI_API int slai_pass_destroy(slai_ctx* ctx, slai_pass* pass) {
+    if (!ctx) return SLAI_ERR_INVALID_ARG;
+    if (pass) {
+        cudaStreamSynchronize(ctx->stream);
+        if (pass->exec) cudaGraphExecDestroy(pass->exec);
+        delete pass;
+    }
+    return SLAI_OK;
+}
+
 SLAI_API int slai_timer_start(slai_ctx* ctx) {
     if (!ctx) return SLAI_ERR_INVALID_ARG;
     SLAI_CHECK_CUDA(ctx, cudaEventRecord(ctx->ev0, ctx->stream));

@@ -40,6 +40,9 @@ class Backend:
         return p.value
 
     def free(self, ptr: int):
+        if getattr(self, "_recording", False):
+            self._deferred.append(ptr)  # a free would invalidate the recording (it synchronises the device)
+            return
         self.check(self.lib.slai_free(self.h, C.c_void_p(ptr)))
 
     def write_buffer(self, dst: int, src: np.ndarray):
@@ -72,6 +75,11 @@ class Backend:
         self.check(self.lib.slai_ctx_device_info(self.h, name, 128, C.byref(sms)))
         return name.value.decode(), sms.value
 
+    def record(self) -> "RecordedPass":
+        """Record the operator calls made inside the `with` block instead of running them (the reference's encoder:
+        begin_pass ... submit, context.rs:63-96); replay with `.launch(times)`."""
+        return RecordedPass(self)
+
     def timer_start(self):
         self.check(self.lib.slai_timer_start(self.h))
 
@@ -84,6 +92,42 @@ class Backend:
         if getattr(self, "h", None):
             self.lib.slai_ctx_destroy(self.h)
             self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class RecordedPass:
+    def __init__(self, backend: "Backend"):
+        self.backend = backend
+        self.h = C.c_void_p()
+
+    def __enter__(self):
+        self.backend._deferred = []
+        self.backend._recording = True
+        self.backend.check(self.backend.lib.slai_pass_begin(self.backend.h))
+        return self
+
+    def __exit__(self, et, ev, tb):
+        rc = self.backend.lib.slai_pass_end(self.backend.h, C.byref(self.h))
+        self.backend._recording = False
+        for ptr in self.backend._deferred:  # buffers dropped by the garbage collector while recording
+            self.backend.free(ptr)
+        self.backend._deferred = []
+        if et is None:
+            self.backend.check(rc)
+        return False
+
+    def launch(self, times: int = 1):
+        self.backend.check(self.backend.lib.slai_pass_launch(self.backend.h, self.h, times))
+
+    def close(self):
+        if self.h:
+            self.backend.lib.slai_pass_destroy(self.backend.h, self.h)
+            self.h = C.c_void_p()
 
     def __del__(self):
         try:
@@ -193,7 +237,7 @@ class GpuQuantMatrix:
 
     def __del__(self):
         try:
-            if self.backend.h and self.h:
+            if self.backend.h and self.h and not getattr(self.backend, "_recording", False):
                 self.backend.lib.slai_qmatrix_destroy(self.h)
                 self.h = None
         except Exception:

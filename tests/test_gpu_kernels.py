@@ -84,6 +84,32 @@ def test_gemv_parity(backend, ctx, fmt, shape):
     assert rel_l2(got, ref64) < 1e-5  # far inside the budget: the f16 split keeps ~22 bits of the activations
 
 
+def test_recorded_pass_replays_operator_calls(backend, ctx):
+    """slai_pass_*: calls made while recording do not run; a replay gives the eager results, twice in a row, and
+    `times` replays leave the same output."""
+    M, K = 512, 1024
+    rng = np.random.default_rng(3)
+    mats = [GpuQuantMatrix(backend, f, M, K, synth.quantize(f, synth.normal_matrix(f, M, K))) for f in (synth.FMT_Q4_K, synth.FMT_Q8_0)]
+    v = backend.vector(rng.standard_normal(K).astype(np.float32))
+    eager = []
+    for m in mats:
+        o = backend.zeros(M)
+        ctx.matmul_quant_assign(o, m, v)
+        eager.append(o.to_numpy())
+    outs = [backend.zeros(M) for _ in mats]
+    with backend.record() as rec:
+        for o, m in zip(outs, mats):
+            ctx.matmul_quant_assign(o, m, v)
+    backend.synchronize()
+    assert all(not o.to_numpy().any() for o in outs)  # nothing ran yet
+    for times in (1, 3):
+        rec.launch(times)
+        backend.synchronize()
+        for o, e in zip(outs, eager):
+            assert np.array_equal(bits(o.to_numpy()), bits(e))
+    rec.close()
+
+
 @pytest.mark.parametrize("fmt", FMTS)
 def test_gemv_random_bit_patterns(backend, ctx, fmt):
     """Blocks of random bits (every scale / quant code occurs), the input style of the reference benchmark."""
