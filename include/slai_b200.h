@@ -98,6 +98,19 @@ int slai_pass_end(slai_ctx* ctx, slai_pass** out);
 int slai_pass_launch(slai_ctx* ctx, slai_pass* pass, int times);
 int slai_pass_destroy(slai_ctx* ctx, slai_pass* pass);
 
+/* ---- tensor-parallel group (no counterpart in the reference, which runs a model on one device) ---------- */
+/* One process (or thread) per GPU, one context each.  Rank 0 asks for an id, the host program hands the 128 bytes
+ * to the other ranks by any means (a torch.distributed / MPI broadcast, a file), every rank calls slai_tp_init
+ * (collective: returns when all ranks have joined).  Models created afterwards with tp_size > 1 in their
+ * configuration take weights that the caller has already sharded and exchange one sum
+ * of `dim` floats after the attention output projection and after the FFN down projection of every layer
+ * (NCCL all-reduce over NVLink on the context's stream). */
+#define SLAI_TP_ID_BYTES 128
+int slai_tp_unique_id(slai_ctx* ctx, void* h_id);                             /* h_id: SLAI_TP_ID_BYTES bytes out */
+int slai_tp_init(slai_ctx* ctx, const void* h_id, int rank, int size);        /* blocking, collective */
+int slai_tp_all_reduce_sum(slai_ctx* ctx, const float* d_in, float* d_out, int64_t n); /* in place allowed */
+int slai_tp_shutdown(slai_ctx* ctx);                                          /* blocking, collective */
+
 /* ---- stream timing: the GPU timestamp queries of crates/slai-bench/src/main.rs:198,221-242 ---------- */
 int slai_timer_start(slai_ctx* ctx);          /* records an event on the stream */
 int slai_timer_stop(slai_ctx* ctx, float* ms); /* records, waits, returns elapsed milliseconds; blocking */

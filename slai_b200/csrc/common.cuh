@@ -30,7 +30,13 @@ struct slai_ctx {
     size_t scratch_bytes = 0;
     std::vector<RopeTable> rope_tables;
     unsigned int* d_counters = nullptr;  // tickets for "last block finishes" reductions (zeroed)
+    // tensor-parallel group (tp.cu): NCCL communicator of this context's rank, null when not sharded
+    void* tp_comm = nullptr;
+    int tp_rank = 0, tp_size = 1;
 };
+
+// tp.cu: sum of `n` floats over the ranks of the context's group, on the context's stream
+int tp_all_reduce_sum(slai_ctx* ctx, const float* d_in, float* d_out, int64_t n);
 
 int slai_set_error(slai_ctx* ctx, int code, const char* fmt, ...);
 

@@ -70,7 +70,11 @@ struct LlamaLayer {
 struct slai_llama {
     slai_ctx* ctx = nullptr;
     slai_llama_config cfg;
-    int kv_dim = 0, head_size = 0, kv_mul = 0;
+    int kv_dim = 0, head_size = 0, kv_mul = 0;  // kv_dim: this rank's share
+    // tensor-parallel shares of this rank (equal to the global sizes when tp_size == 1): query rows, query heads,
+    // FFN rows; x (dim floats) is replicated, xpart receives a row-parallel GEMV's partial before the exchange
+    int q_dim = 0, n_q_local = 0, hidden = 0, tp = 1;
+    float* xpart = nullptr;
     std::vector<LlamaLayer> layers;
     const slai_qmatrix* output = nullptr;
     const slai_qmatrix* embd_q = nullptr;
@@ -114,7 +118,7 @@ static int llama_prepare_fused(slai_llama* m) {
     // kernels are specialised at compile time and overlap through programmatic dependent launch).
     const char* nf = getenv("SLAI_FUSED");
     if (!(nf && nf[0] == '1')) return SLAI_OK;
-    if (c.rope_variant != 0 || m->kv_mul > 8 || c.n_layers > DECODE_MAX_LAYERS) return SLAI_OK;
+    if (c.rope_variant != 0 || m->kv_mul > 8 || c.n_layers > DECODE_MAX_LAYERS || m->tp > 1) return SLAI_OK;
     const int fmt = m->layers[0].wq ? m->layers[0].wq->fmt : 0;
     if (fmt != SLAI_FMT_Q4_K && fmt != SLAI_FMT_Q5_K && fmt != SLAI_FMT_Q6_K && fmt != SLAI_FMT_Q8_0) return SLAI_OK;
     for (auto& w : m->layers) {
@@ -184,6 +188,24 @@ static int llama_record(slai_llama* m, int kind) {
     if (rc) return rc;
     n++;
     const size_t esz = c.kv_dtype == SLAI_KV_F16 ? 2 : 4;
+    // A row-parallel GEMV (each rank holds a K range of every row): x += W v.  Sharded: the partial goes to xpart
+    // (rank 0 adds the residual), then one sum over the ranks writes x on every rank.
+    auto row_parallel = [&](GemvLaunch& L) -> int {
+        int r;
+        if (m->tp == 1) {
+            n++;
+            return gemv_launch(ctx, L);
+        }
+        L.out = m->xpart;
+        if (ctx->tp_rank != 0) {
+            L.resid = nullptr;
+            L.epi = EPI_STORE;
+        }
+        if ((r = gemv_launch(ctx, L))) return r;
+        if ((r = tp_all_reduce_sum(ctx, m->xpart, m->x, c.dim))) return r;
+        n += 2;
+        return SLAI_OK;
+    };
     if (m->fused_state == 1) {
         // all layers in one persistent kernel
         if ((rc = decode_layers_launch(ctx, *m->dparams, m->plan))) return rc;
@@ -210,7 +232,7 @@ static int llama_record(slai_llama* m, int kind) {
             return gemv_launch(ctx, L);
         };
         SLAI_REQUIRE(ctx, fuse_rope, SLAI_ERR_INVALID_ARG, "llama: the NeoX RoPE variant is served by slai_rope, not by the fused decode path");
-        GemvSeg sq = seg_of(w.wq, 0, c.dim, w.bq, 0, 0), sk = seg_of(w.wk, 0, m->kv_dim, w.bk, 0, 1),
+        GemvSeg sq = seg_of(w.wq, 0, m->q_dim, w.bq, 0, 0), sk = seg_of(w.wk, 0, m->kv_dim, w.bk, 0, 1),
                 sv = seg_of(w.wv, 0, m->kv_dim, w.bv, 0, 2);
         if (w.wq->fmt == w.wk->fmt && w.wk->fmt == w.wv->fmt) {
             GemvSeg s3[3] = {sq, sk, sv};
@@ -225,7 +247,7 @@ static int llama_record(slai_llama* m, int kind) {
             AttnLaunch A;
             A.q = m->q; A.kcache = kc; A.vcache = vc; A.kv_dtype = c.kv_dtype;
             A.pos_stride = m->head_size; A.head_stride = (int64_t)c.seq_len * m->head_size;
-            A.n_heads = c.n_q_heads; A.kv_mul = m->kv_mul; A.head_size = m->head_size;
+            A.n_heads = m->n_q_local; A.kv_mul = m->kv_mul; A.head_size = m->head_size;
             A.d_pos = d_pos; A.max_pos = c.seq_len - 1; A.out = m->xb; A.pdl = pdl;
             A.scratch = m->attn_scratch; A.scratch_bytes = m->attn_scratch_bytes;
             if ((rc = attention_launch(ctx, A))) return rc;
@@ -234,17 +256,16 @@ static int llama_record(slai_llama* m, int kind) {
         // 3. x += Wo xb                                                         transformer.rs:352-355
         {
             GemvLaunch L;
-            L.fmt = w.wo->fmt; L.K = c.dim; L.nseg = 1; L.seg[0] = seg_of(w.wo, 0, c.dim, nullptr, 0, 0);
+            L.fmt = w.wo->fmt; L.K = m->q_dim; L.nseg = 1; L.seg[0] = seg_of(w.wo, 0, c.dim, nullptr, 0, 0);
             L.v = m->xb; L.out = m->x; L.resid = m->x; L.epi = EPI_RESID; L.pdl = pdl;
-            if ((rc = gemv_launch(ctx, L))) return rc;
-            n++;
+            if ((rc = row_parallel(L))) return rc;
         }
         // 4. xb = rmsnorm(x); hb = silu(Wgate xb) * (Wup xb)                    transformer.rs:356-361
         if (w.wgate->fmt == w.wup->fmt) {
             GemvLaunch L;
             L.fmt = w.wgate->fmt; L.K = c.dim; L.nseg = 2;
-            L.seg[0] = seg_of(w.wgate, 0, c.hidden_dim, nullptr, 0, 0);
-            L.seg[1] = seg_of(w.wup, 0, c.hidden_dim, nullptr, 0, 0);
+            L.seg[0] = seg_of(w.wgate, 0, m->hidden, nullptr, 0, 0);
+            L.seg[1] = seg_of(w.wup, 0, m->hidden, nullptr, 0, 0);
             L.v = m->x; L.out = m->hb; L.pro = PRO_RMS; L.norm_w = w.ffn_norm; L.eps = c.rms_norm_eps; L.epi = EPI_SILU;
             L.pdl = pdl;
             if ((rc = gemv_launch(ctx, L))) return rc;
@@ -253,22 +274,21 @@ static int llama_record(slai_llama* m, int kind) {
             for (int i = 0; i < 2; i++) {
                 const slai_qmatrix* wm = i == 0 ? w.wgate : w.wup;
                 GemvLaunch L;
-                L.fmt = wm->fmt; L.K = c.dim; L.nseg = 1; L.seg[0] = seg_of(wm, 0, c.hidden_dim, nullptr, 0, 0);
+                L.fmt = wm->fmt; L.K = c.dim; L.nseg = 1; L.seg[0] = seg_of(wm, 0, m->hidden, nullptr, 0, 0);
                 L.v = m->x; L.out = i == 0 ? m->hb : m->hb2; L.pro = PRO_RMS; L.norm_w = w.ffn_norm; L.eps = c.rms_norm_eps;
                 L.epi = EPI_STORE; L.pdl = pdl;
                 if ((rc = gemv_launch(ctx, L))) return rc;
                 n++;
             }
-            if ((rc = slai_silu_gate(ctx, m->hb, m->hb2, c.hidden_dim))) return rc;
+            if ((rc = slai_silu_gate(ctx, m->hb, m->hb2, m->hidden))) return rc;
             n++;
         }
         // 5. x += Wdown hb                                                      transformer.rs:362-365
         {
             GemvLaunch L;
-            L.fmt = w.wdown->fmt; L.K = c.hidden_dim; L.nseg = 1; L.seg[0] = seg_of(w.wdown, 0, c.dim, nullptr, 0, 0);
+            L.fmt = w.wdown->fmt; L.K = m->hidden; L.nseg = 1; L.seg[0] = seg_of(w.wdown, 0, c.dim, nullptr, 0, 0);
             L.v = m->hb; L.out = m->x; L.resid = m->x; L.epi = EPI_RESID; L.pdl = pdl;
-            if ((rc = gemv_launch(ctx, L))) return rc;
-            n++;
+            if ((rc = row_parallel(L))) return rc;
         }
     }
     // logits = Wout rmsnorm(x)                                                  transformer.rs:368-375
@@ -354,17 +374,28 @@ SLAI_API int slai_llama_create(slai_ctx* ctx, const slai_llama_config* cfg, slai
     m->ctx = ctx;
     m->cfg = c;
     // derived sizes: Llama2Config::derived_configs (models/llama2/cpu.rs:111-143)
+    m->tp = c.tp_size > 1 ? c.tp_size : 1;
+    if (m->tp > 1) {
+        SLAI_REQUIRE(ctx, ctx->tp_comm && ctx->tp_size == c.tp_size && ctx->tp_rank == c.tp_rank, SLAI_ERR_INVALID_ARG,
+                     "llama: tp_rank/tp_size %d/%d do not match the context's group (slai_tp_init)", c.tp_rank, c.tp_size);
+        SLAI_REQUIRE(ctx, c.n_kv_heads % m->tp == 0 && c.hidden_dim % m->tp == 0 && (c.hidden_dim / m->tp) % 16 == 0, SLAI_ERR_SHAPE,
+                     "llama: %d KV heads / hidden %d do not split over %d ranks", c.n_kv_heads, c.hidden_dim, m->tp);
+    }
     m->head_size = c.dim / c.n_q_heads;
-    m->kv_dim = c.dim * c.n_kv_heads / c.n_q_heads;
     m->kv_mul = c.n_q_heads / c.n_kv_heads;
+    m->n_q_local = c.n_q_heads / m->tp;
+    m->q_dim = m->n_q_local * m->head_size;
+    m->kv_dim = c.n_kv_heads / m->tp * m->head_size;
+    m->hidden = c.hidden_dim / m->tp;
     m->layers.resize(c.n_layers);
     const size_t esz = c.kv_dtype == SLAI_KV_F16 ? 2 : 4;
     m->kv_layer_elems = (size_t)c.seq_len * m->kv_dim;
     const char* ng = getenv("SLAI_NO_GRAPH");
     m->graphs.use_graph = !(ng && ng[0] == '1');
     m->history_cap = c.seq_len + 8;
-    m->attn_scratch_bytes = attention_scratch_bytes(ctx, c.n_q_heads, m->kv_mul, m->head_size, c.seq_len - 1);
+    m->attn_scratch_bytes = attention_scratch_bytes(ctx, m->n_q_local, m->kv_mul, m->head_size, c.seq_len - 1);
     bool ok = cudaMalloc(&m->x, (size_t)c.dim * 4) == cudaSuccess && cudaMalloc(&m->xb, (size_t)c.dim * 4) == cudaSuccess &&
+              cudaMalloc(&m->xpart, (size_t)c.dim * 4) == cudaSuccess &&
               cudaMalloc(&m->q, (size_t)c.dim * 4) == cudaSuccess && cudaMalloc(&m->hb, (size_t)c.hidden_dim * 4) == cudaSuccess &&
               cudaMalloc(&m->hb2, (size_t)c.hidden_dim * 4) == cudaSuccess &&
               cudaMalloc(&m->logits, (size_t)c.vocab_size * 4) == cudaSuccess &&
@@ -397,7 +428,7 @@ SLAI_API int slai_llama_destroy(slai_llama* m) {
         cudaFree(l.attn_norm); cudaFree(l.ffn_norm); cudaFree(l.bq); cudaFree(l.bk); cudaFree(l.bv);
     }
     cudaFree(m->token_embd); cudaFree(m->out_norm);
-    cudaFree(m->x); cudaFree(m->xb); cudaFree(m->q); cudaFree(m->hb); cudaFree(m->hb2); cudaFree(m->logits);
+    cudaFree(m->x); cudaFree(m->xb); cudaFree(m->xpart); cudaFree(m->q); cudaFree(m->hb); cudaFree(m->hb2); cudaFree(m->logits);
     cudaFree(m->kcache); cudaFree(m->vcache); cudaFree(m->sc.d); cudaFree(m->d_history); cudaFree(m->attn_scratch);
     delete m;
     return SLAI_OK;
@@ -423,13 +454,13 @@ SLAI_API int slai_llama_set_matrix(slai_llama* m, int id, int layer, const slai_
     SLAI_REQUIRE(ctx, layer >= 0 && layer < c.n_layers, SLAI_ERR_INVALID_ARG, "llama: layer %d out of range", layer);
     LlamaLayer& l = m->layers[layer];
     switch (id) {
-        case SLAI_W_Q: SLAI_REQUIRE(ctx, shape_is(c.dim, c.dim), SLAI_ERR_SHAPE, "llama: attn_q must be dim x dim"); l.wq = w; break;
+        case SLAI_W_Q: SLAI_REQUIRE(ctx, shape_is(m->q_dim, c.dim), SLAI_ERR_SHAPE, "llama: attn_q must be (dim / tp) x dim"); l.wq = w; break;
         case SLAI_W_K: SLAI_REQUIRE(ctx, shape_is(m->kv_dim, c.dim), SLAI_ERR_SHAPE, "llama: attn_k must be kv_dim x dim"); l.wk = w; break;
         case SLAI_W_V: SLAI_REQUIRE(ctx, shape_is(m->kv_dim, c.dim), SLAI_ERR_SHAPE, "llama: attn_v must be kv_dim x dim"); l.wv = w; break;
-        case SLAI_W_O: SLAI_REQUIRE(ctx, shape_is(c.dim, c.dim), SLAI_ERR_SHAPE, "llama: attn_output must be dim x dim"); l.wo = w; break;
-        case SLAI_W_GATE: SLAI_REQUIRE(ctx, shape_is(c.hidden_dim, c.dim), SLAI_ERR_SHAPE, "llama: ffn_gate must be hidden x dim"); l.wgate = w; break;
-        case SLAI_W_UP: SLAI_REQUIRE(ctx, shape_is(c.hidden_dim, c.dim), SLAI_ERR_SHAPE, "llama: ffn_up must be hidden x dim"); l.wup = w; break;
-        case SLAI_W_DOWN: SLAI_REQUIRE(ctx, shape_is(c.dim, c.hidden_dim), SLAI_ERR_SHAPE, "llama: ffn_down must be dim x hidden"); l.wdown = w; break;
+        case SLAI_W_O: SLAI_REQUIRE(ctx, shape_is(c.dim, m->q_dim), SLAI_ERR_SHAPE, "llama: attn_output must be dim x (dim / tp)"); l.wo = w; break;
+        case SLAI_W_GATE: SLAI_REQUIRE(ctx, shape_is(m->hidden, c.dim), SLAI_ERR_SHAPE, "llama: ffn_gate must be (hidden / tp) x dim"); l.wgate = w; break;
+        case SLAI_W_UP: SLAI_REQUIRE(ctx, shape_is(m->hidden, c.dim), SLAI_ERR_SHAPE, "llama: ffn_up must be (hidden / tp) x dim"); l.wup = w; break;
+        case SLAI_W_DOWN: SLAI_REQUIRE(ctx, shape_is(c.dim, m->hidden), SLAI_ERR_SHAPE, "llama: ffn_down must be dim x (hidden / tp)"); l.wdown = w; break;
         default: return slai_set_error(ctx, SLAI_ERR_INVALID_ARG, "llama: weight id %d is not a matrix", id);
     }
     return SLAI_OK;
@@ -461,7 +492,7 @@ static int llama_set_f32_impl(slai_llama* m, int id, int layer, const float* dat
     switch (id) {
         case SLAI_W_ATTN_NORM: dst = &l.attn_norm; break;
         case SLAI_W_FFN_NORM: dst = &l.ffn_norm; break;
-        case SLAI_W_BQ: dst = &l.bq; break;
+        case SLAI_W_BQ: dst = &l.bq; want = m->q_dim; break;
         case SLAI_W_BK: dst = &l.bk; want = m->kv_dim; break;
         case SLAI_W_BV: dst = &l.bv; want = m->kv_dim; break;
         default: return slai_set_error(ctx, SLAI_ERR_INVALID_ARG, "llama: weight id %d is not an f32 vector", id);

@@ -75,6 +75,7 @@ SLAI_API int slai_ctx_destroy(slai_ctx* ctx) {
     if (ctx->d_scratch) cudaFree(ctx->d_scratch);
     if (ctx->d_counters) cudaFree(ctx->d_counters);
     cudaEventDestroy(ctx->ev0);
+    slai_tp_shutdown(ctx);
     cudaEventDestroy(ctx->ev1);
     cudaStreamDestroy(ctx->stream);
     delete ctx;

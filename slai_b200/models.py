@@ -69,10 +69,14 @@ LLAMA2_70B = Llama2Config(dim=8192, hidden_dim=28672, n_layers=80, n_q_heads=64,
 class Llama2:
     """Llama2State + Llama2Weights + Llama2::launch behind one handle."""
 
-    def __init__(self, backend: Backend, config: Llama2Config):
+    def __init__(self, backend: Backend, config: Llama2Config, tp_rank: int = 0, tp_size: int = 1):
+        """`config` is the whole model's; with tp_size > 1 (after `slai_b200.tp.join_group`) the matrices attached
+        must be this rank's shards (`slai_b200.tp.shard_shapes`)."""
         self.backend, self.config = backend, config
+        self.tp_rank, self.tp_size = tp_rank, tp_size
         c = _CLlamaConfig(config.dim, config.hidden_dim, config.n_layers, config.n_q_heads, config.n_kv_heads, config.vocab_size,
-                          config.seq_len, config.rope_base_freq, config.rms_norm_eps, config.rope_variant, config.kv_dtype, 0, 1)
+                          config.seq_len, config.rope_base_freq, config.rms_norm_eps, config.rope_variant, config.kv_dtype,
+                          tp_rank, tp_size)
         h = C.c_void_p()
         backend.check(backend.lib.slai_llama_create(backend.h, C.byref(c), C.byref(h)))
         self.h = h
