@@ -242,7 +242,63 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_tp(args, group):
+    """BASELINE configs[4] (Llama-2-70B architecture, Q4_K + Q6_K logits, fp16 KV, batch 1) sharded over all ranks:
+    tensor parallel, one all-reduce per half-layer.  Not the default workload: `--tp`."""
+    from slai_b200 import synth, tp
+    from slai_b200.models import LLAMA2_70B, Llama2Config
+    from slai_b200.ops import Backend
+    rank, world = group.rank, group.world
+    backend = Backend(group.local_rank)
+    cfg = LLAMA2_70B if args.tp_layers <= 0 else Llama2Config(**{**LLAMA2_70B.__dict__, "n_layers": args.tp_layers})
+    if world > 1:
+        tp.join_group(backend, rank, world, tp.torch_broadcast)
+        m = tp.synthetic_llama_device_tp(backend, cfg, synth.FMT_Q4_K, synth.FMT_Q6_K, rank, world)
+    else:
+        from slai_b200.models import synthetic_llama_device
+        m = synthetic_llama_device(backend, cfg, synth.FMT_Q4_K, synth.FMT_Q6_K)
+    peak, peak_src = measured_peaks()
+    K, W = args.steps, args.warmup
+    PL = args.prompt_len
+    rng = np.random.default_rng(42)
+    prompt = rng.integers(0, cfg.vocab_size, size=PL).astype(np.int32)
+    m.prefill(prompt[:-1], 0)
+    tok, pos = int(prompt[-1]), PL - 1
+    warm = m.generate(tok, pos, W)
+    tok, pos = int(warm[-1]), pos + W
+    sampler = ClockSampler(group.local_rank)
+    group.barrier()
+    backend.synchronize()
+    backend.timer_start()
+    toks = m.generate(tok, pos, K)
+    ms = backend.timer_stop()
+    group.barrier()
+    clocks = sampler.stop()
+    ids = group.gather_ids(toks)
+    (ms,) = group.max_over_ranks([ms])
+    if rank == 0:
+        per_rank = tp.bytes_per_token_per_rank(cfg, synth.FMT_Q4_K, synth.FMT_Q6_K, world)
+        kv = float(np.mean([cfg.kv_bytes_at(p) for p in range(pos, pos + K)])) / world
+        t = ms * 1e-3 / K
+        line = {"metric": "decode tok/s bs1 (Llama-2-70B Q4_K, tensor parallel)", "value": K / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
+                "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "f32", "data": "synthetic (shards seeded per rank)",
+                "config": {"workload": "llama2-70b-arch q4_k (q6_k logits) bs1 decode, fp16 KV (BASELINE configs[4])", "n_layers": cfg.n_layers,
+                           "prompt_len": PL, "parallelism": f"tp{world}", "exchange": "NCCL all-reduce of 8192 f32 after wo and w_down"},
+                "clocks": clocks, "launches_per_token": m.launches_per_token(), "gpu_launches": m.launches_per_token() * K,
+                "ranks_agree": all(r == ids[0] for r in ids),
+                "roofline": {"bound": "hbm", "per_gpu_bytes_per_token": per_rank + kv, "achieved": (per_rank + kv) / t / 1e9, "peak": peak,
+                             "unit": "GB/s", "frac": (per_rank + kv) / t / 1e9 / peak, "peak_source": peak_src}}
+        print(json.dumps(line), flush=True)
+    m.close()
+    if world > 1:
+        backend.check(backend.lib.slai_tp_shutdown(backend.h))
+    group.close()
+
+
 def main():
+    # NCCL's version banner and debug lines go to stderr: stdout carries the one JSON line
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
@@ -251,6 +307,8 @@ def main():
     ap.add_argument("--gemv", action="store_true", help="also run the 16-case quantised GEMV microbenchmark")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--prompt-len", type=int, default=512, help="prompt length (512 = the benchmark; smaller for profiling)")
+    ap.add_argument("--tp", action="store_true", help="Llama-2-70B architecture sharded over all ranks instead of 7B replicas")
+    ap.add_argument("--tp-layers", type=int, default=0, help="with --tp: fewer layers than 80 (0 = the full model)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     global PROMPT_LEN
@@ -265,6 +323,9 @@ def main():
 
     from slai_b200.replicas import ReplicaGroup
     group = ReplicaGroup(backend="nccl")
+    if args.tp:
+        run_tp(args, group)
+        return
 
     from slai_b200 import synth
     from slai_b200.ops import Backend, LlmContext
