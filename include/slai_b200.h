@@ -110,6 +110,15 @@ int slai_tp_unique_id(slai_ctx* ctx, void* h_id);                             /*
 int slai_tp_init(slai_ctx* ctx, const void* h_id, int rank, int size);        /* blocking, collective */
 int slai_tp_all_reduce_sum(slai_ctx* ctx, const float* d_in, float* d_out, int64_t n); /* in place allowed */
 int slai_tp_shutdown(slai_ctx* ctx);                                          /* blocking, collective */
+/* Optional: exchange over peer memory instead of NCCL (ranks = separate processes on GPUs of one NVLink domain).
+ * Every rank exports its exchange region (a CUDA IPC handle), the host program gathers the handles of all ranks in
+ * rank order and every rank attaches them; the host must let all ranks finish attaching (a barrier) before the
+ * first decode call.  Models created afterwards store their partial rows straight into the peers' regions from the
+ * producing kernel's epilogue and sum them in the consuming kernel's prologue (no collective kernel).  Waits on
+ * peers are bounded: a rank that never arrives shows up as SLAI_ERR_TIMEOUT at the next slai_ctx_sync. */
+#define SLAI_TP_HANDLE_BYTES 64
+int slai_tp_peer_export(slai_ctx* ctx, void* h_handle);            /* h_handle: SLAI_TP_HANDLE_BYTES bytes out; blocking */
+int slai_tp_peer_attach(slai_ctx* ctx, const void* h_handles);     /* tp_size x SLAI_TP_HANDLE_BYTES bytes, rank order */
 
 /* ---- stream timing: the GPU timestamp queries of crates/slai-bench/src/main.rs:198,221-242 ---------- */
 int slai_timer_start(slai_ctx* ctx);          /* records an event on the stream */

@@ -54,6 +54,8 @@ extern "C" {
     pub fn slai_tp_init(ctx: *mut slai_ctx, h_id: *const c_void, rank: i32, size: i32) -> i32;
     pub fn slai_tp_all_reduce_sum(ctx: *mut slai_ctx, d_in: *const f32, d_out: *mut f32, n: i64) -> i32;
     pub fn slai_tp_shutdown(ctx: *mut slai_ctx) -> i32;
+    pub fn slai_tp_peer_export(ctx: *mut slai_ctx, h_handle: *mut c_void) -> i32;
+    pub fn slai_tp_peer_attach(ctx: *mut slai_ctx, h_handles: *const c_void) -> i32;
     pub fn slai_timer_start(ctx: *mut slai_ctx) -> i32;
     pub fn slai_timer_stop(ctx: *mut slai_ctx, ms: *mut f32) -> i32;
     pub fn slai_qmatrix_create(ctx: *mut slai_ctx, fmt: i32, nrows: i64, ncols: i64, h_blocks: *const c_void, nbytes: usize, out: *mut *mut slai_qmatrix) -> i32;

@@ -72,6 +72,8 @@ SIGNATURES = {
     "slai_tp_init": (C.c_int, [_vp, _vp, C.c_int, C.c_int]),
     "slai_tp_all_reduce_sum": (C.c_int, [_vp, _vp, _vp, _i64]),
     "slai_tp_shutdown": (C.c_int, [_vp]),
+    "slai_tp_peer_export": (C.c_int, [_vp, _vp]),
+    "slai_tp_peer_attach": (C.c_int, [_vp, _vp]),
     "slai_timer_start": (C.c_int, [_vp]),
     "slai_timer_stop": (C.c_int, [_vp, C.POINTER(_f)]),
     "slai_qmatrix_create": (C.c_int, [_vp, C.c_int, _i64, _i64, _vp, _sz, _pp]),

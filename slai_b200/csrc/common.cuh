@@ -19,6 +19,18 @@ struct RopeTable {
     float* d_theta;  // head_size/2 inverse frequencies, computed on the host with libm powf
 };
 
+// Tensor-parallel exchange over peer memory (tp.cu): every rank owns a region [2 parities][ranks][XCHG_MAX_DIM]
+// floats followed by [2][ranks] sequence flags; peers store their partial vectors straight into it over NVLink.
+constexpr int XCHG_MAX_RANKS = 8;
+constexpr int XCHG_MAX_DIM = 16384;
+struct PeerExchange {
+    int ranks, rank;
+    float* slot_at[XCHG_MAX_RANKS];          // base of every rank's region (own region included), as seen from here
+    unsigned int* flags_at[XCHG_MAX_RANKS];  // base of every rank's flag block
+    unsigned int* d_tokseq;                  // device scalar: tokens decoded so far (one tick per token)
+    unsigned int* d_ticket;                  // "last block of the producing kernel" counter
+};
+
 struct slai_ctx {
     int device = 0;
     int sm_count = 0;
@@ -33,10 +45,15 @@ struct slai_ctx {
     // tensor-parallel group (tp.cu): NCCL communicator of this context's rank, null when not sharded
     void* tp_comm = nullptr;
     int tp_rank = 0, tp_size = 1;
+    PeerExchange xchg = {};     // filled by slai_tp_peer_attach
+    void* xchg_region = nullptr;  // this rank's region (device memory, exported to the peers)
+    bool xchg_ready = false;
 };
 
 // tp.cu: sum of `n` floats over the ranks of the context's group, on the context's stream
 int tp_all_reduce_sum(slai_ctx* ctx, const float* d_in, float* d_out, int64_t n);
+// tp.cu: one more token decoded (sequence numbers of the peer exchange derive from it)
+int tp_tick(slai_ctx* ctx);
 
 int slai_set_error(slai_ctx* ctx, int code, const char* fmt, ...);
 
@@ -99,9 +116,11 @@ enum GemvEpilogue {
     EPI_RESID = 1,     // out[r] = resid[r] + acc (+bias)       (out may alias resid)
     EPI_SILU = 2,      // segments 0/1 = gate/up: out[r] = up * gate / (1 + exp(-gate))
     EPI_GELU = 3,      // out[r] = gelu(acc + bias)
-    EPI_QKV = 4        // segments q,k,v: optional bias, optional adjacent-pair RoPE on q,k; q -> out f32,
+    EPI_QKV = 4,       // segments q,k,v: optional bias, optional adjacent-pair RoPE on q,k; q -> out f32,
                        // k,v -> KV cache at position *d_pos
+    EPI_XCHG = 5       // tensor parallel: acc (+resid on rank 0) stored into every rank's exchange slot (PeerExchange)
 };
+
 
 struct GemvSeg {
     const uint8_t* w = nullptr;   // first tile of the segment (tile-major data; F32: first row)
@@ -137,6 +156,12 @@ struct GemvLaunch {
     int64_t kv_pos_stride = 0;     // elements between positions
     int64_t kv_head_stride = 0;    // elements between heads
     bool pdl = false;              // launch with programmatic stream serialization
+    // tensor-parallel exchange over peer memory (null: not used)
+    const PeerExchange* xchg = nullptr;
+    int xchg_out_idx1 = 0;         // EPI_XCHG: index + 1 of this exchange inside the token
+    int xchg_in_idx1 = 0;          // > 0: the input vector is the sum over ranks of exchange idx (instead of `v`)
+    int xchg_per_token = 0;
+    float* xsum_out = nullptr;     // with xchg_in: where block 0 leaves the summed vector
 };
 
 int gemv_launch(slai_ctx* ctx, const GemvLaunch& L);

@@ -11,7 +11,7 @@ using namespace gemvk;
 
 namespace {
 
-template <class F, int NMAT, int PRO, int EPI>
+template <class F, int NMAT, int PRO, int EPI, bool XIN = false>
 __global__ void __launch_bounds__(THREADS, 1) gemv_kernel(const __grid_constant__ GemvParams P) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     SLAI_TL_BEGIN(100 * NMAT + 10 * PRO + EPI)
@@ -24,7 +24,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_kernel(const __grid_constant_
     ring_init(R, prog, P.dig_region, P.nstage, P.stage_stride, P.step_bytes, P.err_flag, smem_raw, lane, warp);
     SLAI_TRACE_POINT(1)
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    gemv_phase<F, 1 << PRO, 1 << EPI>(P, R, prog, smem_raw, NMAT, PRO, EPI);
+    gemv_phase<F, 1 << PRO, 1 << EPI, XIN>(P, R, prog, smem_raw, NMAT, PRO, EPI);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     SLAI_TL_MARK(2)
 }
@@ -42,9 +42,9 @@ __global__ void gemv_f32_kernel(float* out, const float* w, const float* v, int 
     if (lane == 0) out[row] = acc;
 }
 
-template <class F, int NMAT, int PRO, int EPI>
+template <class F, int NMAT, int PRO, int EPI, bool XIN = false>
 int launch_inst(slai_ctx* ctx, const GemvParams& P, int grid, size_t smem, bool pdl) {
-    auto kern = gemv_kernel<F, NMAT, PRO, EPI>;
+    auto kern = gemv_kernel<F, NMAT, PRO, EPI, XIN>;
     static bool attr_done = false;  // per instantiation
     if (!attr_done) {
         SLAI_CHECK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT));
@@ -68,6 +68,16 @@ template <class F>
 int launch_fmt(slai_ctx* ctx, const GemvParams& P, const GemvLaunch& L, int grid, size_t smem) {
     const bool pdl = L.pdl;
 #define GO(NMAT, PRO, EPI) return launch_inst<F, NMAT, PRO, EPI>(ctx, P, grid, smem, pdl)
+    if (L.xchg_in_idx1 > 0) {  // tensor parallel: the input is an incoming exchange (RmsNorm consumers only)
+        if (L.pro == PRO_RMS && L.epi == EPI_QKV) return launch_inst<F, 1, PRO_RMS, EPI_QKV, true>(ctx, P, grid, smem, pdl);
+        if (L.pro == PRO_RMS && L.epi == EPI_SILU) return launch_inst<F, 2, PRO_RMS, EPI_SILU, true>(ctx, P, grid, smem, pdl);
+        if (L.pro == PRO_RMS && L.epi == EPI_STORE) return launch_inst<F, 1, PRO_RMS, EPI_STORE, true>(ctx, P, grid, smem, pdl);
+        return slai_set_error(ctx, SLAI_ERR_INVALID_ARG, "gemv: no kernel consumes an exchange with prologue/epilogue %d/%d", L.pro, L.epi);
+    }
+    if (L.epi == EPI_XCHG) {
+        if (L.pro == PRO_NONE) GO(1, PRO_NONE, EPI_XCHG);
+        return slai_set_error(ctx, SLAI_ERR_INVALID_ARG, "gemv: the exchange epilogue takes no prologue");
+    }
     switch (L.epi) {
         case EPI_STORE:
             if (L.pro == PRO_NONE) GO(1, PRO_NONE, EPI_STORE);
@@ -143,6 +153,35 @@ int gemv_fill_params(slai_ctx* ctx, const GemvLaunch& L, size_t dig_region, int 
     P.kv_pos_stride = L.kv_pos_stride; P.kv_head_stride = L.kv_head_stride;
     P.err_flag = ctx->d_counters + 3000;
     P.pdl = L.pdl ? 1 : 0;
+    P.xr = 0;
+    P.xi_slots = nullptr;
+    if (L.xchg) {
+        const PeerExchange& X = *L.xchg;
+        SLAI_REQUIRE(ctx, X.ranks >= 2 && X.ranks <= XCHG_MAX_RANKS, SLAI_ERR_INVALID_ARG, "gemv: exchange group of %d ranks", X.ranks);
+        P.xr = X.ranks;
+        P.xrank = X.rank;
+        P.x_tokseq = X.d_tokseq;
+        P.x_ticket = X.d_ticket;
+        P.x_per_token = (unsigned int)L.xchg_per_token;
+        P.xo_idx1 = (unsigned int)L.xchg_out_idx1;
+        P.xi_idx1 = (unsigned int)L.xchg_in_idx1;
+        P.xsum_out = L.xsum_out;
+        if (L.epi == EPI_XCHG) {
+            SLAI_REQUIRE(ctx, L.xchg_out_idx1 > 0 && L.nseg == 1 && L.seg[0].rows <= XCHG_MAX_DIM, SLAI_ERR_SHAPE, "gemv: bad outgoing exchange");
+            const int par = (L.xchg_out_idx1 - 1) & 1;
+            for (int r = 0; r < X.ranks; r++) {
+                P.xo_slot[r] = X.slot_at[r] + ((size_t)par * X.ranks + X.rank) * XCHG_MAX_DIM;
+                P.xo_flag[r] = X.flags_at[r] + par * X.ranks + X.rank;
+            }
+        }
+        if (L.xchg_in_idx1 > 0) {
+            SLAI_REQUIRE(ctx, K <= XCHG_MAX_DIM && (K >> 2) <= STAGE_REGS * THREADS && L.xsum_out, SLAI_ERR_SHAPE,
+                         "gemv: incoming exchange of %d floats does not fit the staging registers", K);
+            const int par = (L.xchg_in_idx1 - 1) & 1;
+            P.xi_slots = X.slot_at[X.rank] + (size_t)par * X.ranks * XCHG_MAX_DIM;
+            P.xi_flags = X.flags_at[X.rank] + par * X.ranks;
+        }
+    }
 #ifdef SLAI_TRACE
     P.trace = reinterpret_cast<unsigned long long*>(ctx->d_scratch);  // the debug driver sizes the scratch first
     P.wtrace = nullptr;

@@ -71,6 +71,16 @@ struct GemvParams {
     long long kv_pos_stride, kv_head_stride;
     unsigned int* err_flag;
     int pdl;  // launched with programmatic stream serialization
+    // tensor-parallel exchange over peer memory (xr == 0: unused)
+    int xr, xrank;                       // ranks in the group, this rank
+    float* xo_slot[XCHG_MAX_RANKS];      // EPI_XCHG: this rank's slot of the outgoing exchange in every rank's region
+    unsigned int* xo_flag[XCHG_MAX_RANKS];  // and the flag that announces it there
+    unsigned int xo_idx1, xi_idx1, x_per_token;  // exchange index + 1 inside the token (out / in), exchanges per token
+    const float* xi_slots;               // incoming exchange in this rank's region: [ranks][XCHG_MAX_DIM] (null: read `v`)
+    const unsigned int* xi_flags;        // [ranks]
+    const unsigned int* x_tokseq;        // device scalar: tokens decoded so far
+    unsigned int* x_ticket;
+    float* xsum_out;                     // block 0 leaves the summed incoming vector here
 #ifdef SLAI_TRACE
     unsigned long long* trace;   // debug build only: per block of threads 8 x (globaltimer, clock64)
     unsigned long long* wtrace;  // debug build only: per warp (loop start, loop end, cycles waiting for the ring, units)
@@ -153,6 +163,56 @@ __device__ __forceinline__ void block_sum_max(float& s, float& m, float* stat) {
 
 __device__ __forceinline__ float max4(const float4& x) { return fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w))); }
 
+// ---- tensor-parallel exchange over peer memory ----------------------------------------------------------------
+// Sequence number of exchange `idx1` of the current token: flags only ever grow, so a flag >= seq means "this
+// rank's partial of this exchange has arrived".
+__device__ __forceinline__ unsigned int xchg_seq(const GemvParams& P, unsigned int idx1) {
+    return __ldcg(P.x_tokseq) * P.x_per_token + idx1;
+}
+// Wait (bounded) until every rank's partial of the incoming exchange is in this rank's region.  One thread per
+// rank polls; on expiry the error flag is raised and the kernel goes on with whatever is there.
+__device__ __forceinline__ void xchg_wait_in(const GemvParams& P) {
+    if ((int)threadIdx.x < P.xr) {
+        const unsigned int want = xchg_seq(P, P.xi_idx1);
+        const unsigned int* f = P.xi_flags + threadIdx.x;
+        for (int it = 0;; it++) {
+            unsigned int v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+            if (v >= want) break;
+            if (it > (1 << 21)) {
+                atomicExch(P.err_flag, 3u);
+                break;
+            }
+            if (it > 32) __nanosleep(64);
+        }
+    }
+    __syncthreads();
+}
+// Sum over the ranks, in rank order, of element group i of the incoming exchange (identical on every rank).
+__device__ __forceinline__ float4 xchg_gather(const GemvParams& P, int i) {
+    float4 a = __ldcg(reinterpret_cast<const float4*>(P.xi_slots) + i);
+    for (int r = 1; r < P.xr; r++) {
+        const float4 b = __ldcg(reinterpret_cast<const float4*>(P.xi_slots + (size_t)r * XCHG_MAX_DIM) + i);
+        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+    }
+    return a;
+}
+// After a block's last exchange stores: make them visible system-wide; the last block of the kernel then raises
+// this rank's flag in every rank's region.
+__device__ __forceinline__ void xchg_publish(const GemvParams& P) {
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int ticket = atomicAdd(P.x_ticket, 1u);
+        if (ticket == gridDim.x - 1) {
+            *P.x_ticket = 0;
+            __threadfence_system();
+            const unsigned int seq = xchg_seq(P, P.xo_idx1);
+            for (int r = 0; r < P.xr; r++) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(P.xo_flag[r]), "r"(seq) : "memory");
+        }
+    }
+}
+
 // Stage the activation vector: optional normalisation, power-of-two scaling so that max|v| lands in
 // [2^25, 2^26), rounding to integers, split into four base-128 digit planes (gemv_frag.cuh), and per-sub-block
 // digit sums (for the `- dmin*m * sum(v)` term of Q4_K / Q5_K and the -32 offset of Q6_K).  Returns 1/scale.
@@ -160,7 +220,9 @@ __device__ __forceinline__ float max4(const float4& x) { return fmaxf(fmaxf(fabs
 // launch, so L1 must not be trusted) and kept in registers between the passes when K <= 12288; longer vectors are
 // read again in each pass.  The code is kept small on purpose (the digit pass is one rolled loop that rotates the
 // register copy): it runs once per phase, straight out of a cold instruction cache.
-template <int SV_GRAN, bool HAS_LN>
+// XIN: the vector is the sum over ranks of an incoming tensor-parallel exchange (K <= 24576 so that it stays in
+// registers); block 0 also writes the sum to P.xsum_out.
+template <int SV_GRAN, bool HAS_LN, bool XIN>
 __device__ __forceinline__ float stage_vector(const int PRO_ARG, const GemvParams& P, const Smem& S, float* stat, int Kp) {
     const int PRO = (!HAS_LN && PRO_ARG == PRO_LN) ? PRO_RMS : PRO_ARG;  // LayerNorm code only where it can occur
     const int K = P.K;
@@ -172,10 +234,16 @@ __device__ __forceinline__ float stage_vector(const int PRO_ARG, const GemvParam
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
     const bool cached = np4 <= STAGE_REGS * THREADS;
     float4 xr[STAGE_REGS];
+    if (XIN) xchg_wait_in(P);
 #pragma unroll
     for (int r = 0; r < STAGE_REGS; r++) {
         const int i = tid + r * THREADS;
-        xr[r] = (cached && i < n4) ? __ldcg(v4 + i) : zero4;
+        if (XIN) {
+            xr[r] = i < n4 ? xchg_gather(P, i) : zero4;
+            if (blockIdx.x == 0 && i < n4) reinterpret_cast<float4*>(P.xsum_out)[i] = xr[r];
+        } else {
+            xr[r] = (cached && i < n4) ? __ldcg(v4 + i) : zero4;
+        }
     }
     float mul = 1.f, sub = 0.f;
     float sum = 0.f, mx = 0.f;
@@ -483,7 +551,7 @@ __device__ __forceinline__ void ring_init(Ring& R, const Prog& prog, int dig_reg
 // function is inlined and the branches fold) and run-time values in the persistent decode kernel, which keeps ONE
 // copy of this code for all its phases so that it stays in the instruction cache from layer to layer.
 // PRO_MASK / EPI_MASK: bit i set = value i can occur (code for the others is not generated).
-template <class F, int PRO_MASK, int EPI_MASK, class Prog>
+template <class F, int PRO_MASK, int EPI_MASK, bool XIN = false, class Prog>
 __device__ __forceinline__ void gemv_phase(const GemvParams& P, Ring& R, const Prog& prog, unsigned char* smem_raw,
                                            const int NMAT, const int PRO, const int EPI) {
 #define SLAI_EPI_IS(x) ((((EPI_MASK) >> (x)) & 1) && EPI == (x))
@@ -504,7 +572,7 @@ __device__ __forceinline__ void gemv_phase(const GemvParams& P, Ring& R, const P
 
     for (int i = tid; i < WAVE * WARPS * NMAT * 16; i += THREADS) red[i] = 0.f;
     SLAI_TRACE_POINT(2)
-    const float inv_scale = stage_vector<F::SV_GRAN, ((PRO_MASK >> PRO_LN) & 1) != 0>(PRO, P, S, stat, Kp);
+    const float inv_scale = stage_vector<F::SV_GRAN, ((PRO_MASK >> PRO_LN) & 1) != 0, XIN>(PRO, P, S, stat, Kp);
     SLAI_TRACE_POINT(3)
 
 #ifdef SLAI_TRACE
@@ -584,6 +652,12 @@ __device__ __forceinline__ void gemv_phase(const GemvParams& P, Ring& R, const P
                 if (valid) P.out[orow] = val[0] + bias;
             } else if (SLAI_EPI_IS(EPI_RESID)) {
                 if (valid) P.out[orow] = __ldcg(P.resid + orow) + (val[0] + bias);
+            } else if (SLAI_EPI_IS(EPI_XCHG)) {
+                if (valid) {
+                    float y = val[0] + bias;
+                    if (P.xrank == 0) y += __ldcg(P.resid + orow);
+                    for (int rk = 0; rk < P.xr; rk++) P.xo_slot[rk][orow] = y;
+                }
             } else if (SLAI_EPI_IS(EPI_SILU)) {
                 if (valid) {
                     const float gt = val[0], up = val[NMAT - 1];
@@ -623,6 +697,7 @@ __device__ __forceinline__ void gemv_phase(const GemvParams& P, Ring& R, const P
             __syncthreads();
         }
     }
+    if (SLAI_EPI_IS(EPI_XCHG)) xchg_publish(P);  // every block of the grid, once
 #undef SLAI_EPI_IS
 }
 

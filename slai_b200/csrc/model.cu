@@ -190,9 +190,43 @@ static int llama_record(slai_llama* m, int kind) {
     const size_t esz = c.kv_dtype == SLAI_KV_F16 ? 2 : 4;
     // A row-parallel GEMV (each rank holds a K range of every row): x += W v.  Sharded: the partial goes to xpart
     // (rank 0 adds the residual), then one sum over the ranks writes x on every rank.
+    // With the ranks' exchange regions mapped into each other (slai_tp_peer_attach) there is no collective at
+    // all: the row-parallel GEMV stores its partial rows into every rank's region (EPI_XCHG) and the next GEMV
+    // sums them while staging its input (xchg_in), leaving the new x behind for the residual of the one after.
+    bool use_x = m->tp > 1 && ctx->xchg_ready && c.dim <= XCHG_MAX_DIM && c.dim <= 12288;
+    {
+        const char* e = getenv("SLAI_TP_NCCL");
+        if (e && e[0] == '1') use_x = false;
+        const slai_qmatrix* wo_ = m->output ? m->output : (m->embd_q ? m->embd_q : &m->embd_as_matrix);
+        if (wo_->fmt == SLAI_FMT_F32) use_x = false;
+        for (auto& w : m->layers)
+            if (!w.wq || !w.wk || !w.wv || !w.wgate || !w.wup || w.wq->fmt != w.wk->fmt || w.wk->fmt != w.wv->fmt || w.wgate->fmt != w.wup->fmt)
+                use_x = false;
+    }
+    int xi = 0;  // exchanges issued so far in this token
+    if (use_x) {
+        if ((rc = tp_tick(ctx))) return rc;
+        n++;
+    }
+    auto consume_exchange = [&](GemvLaunch& L) {  // the input of L is the sum of the last exchange
+        if (use_x && xi > 0) {
+            L.xchg = &ctx->xchg;
+            L.xchg_in_idx1 = xi;
+            L.xchg_per_token = 2 * c.n_layers;
+            L.xsum_out = m->x;
+        }
+    };
     auto row_parallel = [&](GemvLaunch& L) -> int {
         int r;
         if (m->tp == 1) {
+            n++;
+            return gemv_launch(ctx, L);
+        }
+        if (use_x) {
+            L.xchg = &ctx->xchg;
+            L.epi = EPI_XCHG;
+            L.xchg_out_idx1 = ++xi;
+            L.xchg_per_token = 2 * c.n_layers;
             n++;
             return gemv_launch(ctx, L);
         }
@@ -228,6 +262,7 @@ static int llama_record(slai_llama* m, int kind) {
             L.d_pos = d_pos; L.kcache = kc; L.vcache = vc; L.kv_dtype = c.kv_dtype;
             L.kv_pos_stride = m->head_size; L.kv_head_stride = (int64_t)c.seq_len * m->head_size;
             L.pdl = pdl;
+            consume_exchange(L);
             n++;
             return gemv_launch(ctx, L);
         };
@@ -268,6 +303,7 @@ static int llama_record(slai_llama* m, int kind) {
             L.seg[1] = seg_of(w.wup, 0, m->hidden, nullptr, 0, 0);
             L.v = m->x; L.out = m->hb; L.pro = PRO_RMS; L.norm_w = w.ffn_norm; L.eps = c.rms_norm_eps; L.epi = EPI_SILU;
             L.pdl = pdl;
+            consume_exchange(L);
             if ((rc = gemv_launch(ctx, L))) return rc;
             n++;
         } else {
@@ -306,6 +342,7 @@ static int llama_record(slai_llama* m, int kind) {
         L.fmt = wout->fmt; L.K = c.dim; L.nseg = 1; L.seg[0] = seg_of(wout, 0, c.vocab_size, nullptr, 0, 0);
         L.v = m->x; L.out = m->logits; L.pro = PRO_RMS; L.norm_w = m->out_norm; L.eps = c.rms_norm_eps; L.epi = EPI_STORE;
         L.pdl = pdl;
+        consume_exchange(L);
         if ((rc = gemv_launch(ctx, L))) return rc;
         n++;
     }

@@ -87,8 +87,86 @@ SLAI_API int slai_tp_init(slai_ctx* ctx, const void* h_id, int rank, int size) {
     return SLAI_OK;
 }
 
+// ---- exchange over peer memory ---------------------------------------------------------------------------------
+// NCCL's all-reduce costs a kernel launch and 10-20 us for the 32 KB this path exchanges.  With the ranks'
+// exchange regions mapped into each other (CUDA IPC, NVLink peer access) the producing GEMV stores its partial
+// rows straight into every rank's region and the consuming GEMV sums the partials while it stages its input:
+// no extra kernel, one NVLink store latency.  Plain peer stores and loads only; every wait is bounded.
+namespace {
+constexpr size_t XCHG_FLOATS = (size_t)2 * XCHG_MAX_RANKS * XCHG_MAX_DIM;
+constexpr size_t XCHG_BYTES = XCHG_FLOATS * 4 + 4096;  // flags [2][ranks], token counter and ticket in the last page
+
+__global__ void tp_tick_kernel(unsigned int* tokseq) { *tokseq += 1; }
+
+void fill_exchange(PeerExchange& X, int r, void* base) {
+    X.slot_at[r] = reinterpret_cast<float*>(base);
+    X.flags_at[r] = reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(base) + XCHG_FLOATS * 4);
+}
+}  // namespace
+
+static_assert(sizeof(cudaIpcMemHandle_t) == SLAI_TP_HANDLE_BYTES, "SLAI_TP_HANDLE_BYTES must equal sizeof(cudaIpcMemHandle_t)");
+
+int tp_tick(slai_ctx* ctx) {
+    tp_tick_kernel<<<1, 1, 0, ctx->stream>>>(ctx->xchg.d_tokseq);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    return SLAI_OK;
+}
+
+SLAI_API int slai_tp_peer_export(slai_ctx* ctx, void* h_handle) {
+    if (!ctx || !h_handle) return SLAI_ERR_INVALID_ARG;
+    SLAI_REQUIRE(ctx, ctx->tp_size >= 2 && ctx->tp_size <= XCHG_MAX_RANKS, SLAI_ERR_INVALID_ARG,
+                 "tp: the peer exchange serves groups of 2..%d ranks (join one with slai_tp_init first)", XCHG_MAX_RANKS);
+    SLAI_REQUIRE(ctx, !ctx->xchg_region, SLAI_ERR_INVALID_ARG, "tp: the exchange region is already exported");
+    SLAI_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
+    SLAI_CHECK_CUDA(ctx, cudaMalloc(&ctx->xchg_region, XCHG_BYTES));
+    SLAI_CHECK_CUDA(ctx, cudaMemset(ctx->xchg_region, 0, XCHG_BYTES));
+    SLAI_CHECK_CUDA(ctx, cudaDeviceSynchronize());
+    cudaIpcMemHandle_t h;
+    SLAI_CHECK_CUDA(ctx, cudaIpcGetMemHandle(&h, ctx->xchg_region));
+    memcpy(h_handle, &h, sizeof(h));
+    return SLAI_OK;
+}
+
+SLAI_API int slai_tp_peer_attach(slai_ctx* ctx, const void* h_handles) {
+    if (!ctx || !h_handles) return SLAI_ERR_INVALID_ARG;
+    SLAI_REQUIRE(ctx, ctx->xchg_region && !ctx->xchg_ready, SLAI_ERR_INVALID_ARG, "tp: export this rank's region first (once)");
+    SLAI_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
+    PeerExchange& X = ctx->xchg;
+    X.ranks = ctx->tp_size;
+    X.rank = ctx->tp_rank;
+    for (int r = 0; r < X.ranks; r++) {
+        void* base = ctx->xchg_region;
+        if (r != X.rank) {
+            cudaIpcMemHandle_t h;
+            memcpy(&h, reinterpret_cast<const char*>(h_handles) + (size_t)r * sizeof(h), sizeof(h));
+            cudaError_t e = cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess);
+            if (e != cudaSuccess) {
+                cudaGetLastError();
+                return slai_set_error(ctx, SLAI_ERR_CUDA, "tp: cannot map rank %d's exchange region (%s); ranks must be separate processes "
+                                      "on GPUs with peer access", r, cudaGetErrorString(e));
+            }
+        }
+        fill_exchange(X, r, base);
+    }
+    unsigned int* local = X.flags_at[X.rank];
+    X.d_tokseq = local + 512;  // same page, away from the flags the peers write
+    X.d_ticket = local + 576;
+    ctx->xchg_ready = true;
+    return SLAI_OK;
+}
+
 SLAI_API int slai_tp_shutdown(slai_ctx* ctx) {
     if (!ctx) return SLAI_ERR_INVALID_ARG;
+    if (ctx->xchg_region) {
+        cudaStreamSynchronize(ctx->stream);
+        if (ctx->xchg_ready)
+            for (int r = 0; r < ctx->xchg.ranks; r++)
+                if (r != ctx->xchg.rank && ctx->xchg.slot_at[r]) cudaIpcCloseMemHandle(ctx->xchg.slot_at[r]);
+        cudaFree(ctx->xchg_region);
+        ctx->xchg_region = nullptr;
+        ctx->xchg_ready = false;
+        ctx->xchg = PeerExchange{};
+    }
     if (ctx->tp_comm) {
         cudaStreamSynchronize(ctx->stream);
         g_nccl.CommDestroy(reinterpret_cast<ncclComm_t>(ctx->tp_comm));

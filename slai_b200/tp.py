@@ -21,6 +21,7 @@ from .models import LLAMA_MATRICES, Llama2, Llama2Config
 from .ops import Backend, GpuQuantMatrix, GpuVector
 
 TP_ID_BYTES = 128
+TP_HANDLE_BYTES = 64
 ROW_PARALLEL = ("wo", "w_down")
 
 
@@ -79,6 +80,31 @@ def join_group(backend: Backend, rank: int, size: int, broadcast) -> None:
     ident = broadcast(ident)
     buf = (C.c_ubyte * TP_ID_BYTES).from_buffer_copy(ident)
     backend.check(backend.lib.slai_tp_init(backend.h, buf, rank, size))
+
+
+def enable_peer_exchange(backend: Backend, size: int, all_gather, barrier) -> None:
+    """Collective.  Maps every rank's exchange region into every other rank (CUDA IPC over NVLink peer access): the
+    per-half-layer sums then need no collective kernel.  `all_gather(obj)` returns the list of all ranks' objects in
+    rank order; `barrier()` returns when every rank has called it."""
+    buf = (C.c_ubyte * TP_HANDLE_BYTES)()
+    backend.check(backend.lib.slai_tp_peer_export(backend.h, buf))
+    handles = all_gather(bytes(buf))
+    blob = b"".join(handles)
+    assert len(blob) == size * TP_HANDLE_BYTES
+    backend.check(backend.lib.slai_tp_peer_attach(backend.h, (C.c_ubyte * len(blob)).from_buffer_copy(blob)))
+    barrier()
+
+
+def torch_all_gather(obj):
+    import torch.distributed as dist
+    out = [None] * dist.get_world_size()
+    dist.all_gather_object(out, obj)
+    return out
+
+
+def torch_barrier():
+    import torch.distributed as dist
+    dist.barrier()
 
 
 def torch_broadcast(obj):

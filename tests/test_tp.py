@@ -160,17 +160,28 @@ def _gpu_rank(rank, world, port, q):
     s = v.to_numpy()
     cfg = _cfg()
     weights = synthetic_llama_host(cfg, synth.FMT_Q4_K, seed=11, std=0.05, embd_std=1.0)
+
+    def run(m):
+        outs, toks = [], []
+        tok = 3
+        for pos in range(8):
+            lg, nxt = m.forward_logits(pos, tok)
+            outs.append(lg.copy())
+            toks.append(nxt)
+            tok = [17, 599, 42, 5, 6, 7, 8, 9][pos]
+        gen = m.generate(tok, 8, 24)
+        backend.synchronize()  # raises if a bounded wait on a peer ran out
+        return np.stack(outs), toks, list(gen), m.launches_per_token()
+
+    # 1. the exchange as an NCCL all-reduce between the kernels
     m = tp.llama_from_host_tp(backend, cfg, weights, synth.FMT_Q4_K, None, rank, world)
-    outs, toks = [], []
-    tok = 3
-    for pos in range(8):
-        lg, nxt = m.forward_logits(pos, tok)
-        outs.append(lg.copy())
-        toks.append(nxt)
-        tok = [17, 599, 42, 5, 6, 7, 8, 9][pos]
-    gen = m.generate(tok, 8, 24)
-    backend.synchronize()
-    q.put((rank, s, np.stack(outs), toks, list(gen), m.launches_per_token()))
+    nccl = run(m)
+    m.close()
+    # 2. the exchange over peer memory, inside the GEMV kernels (same sums in the same order: identical bits)
+    tp.enable_peer_exchange(backend, world, tp.torch_all_gather, tp.torch_barrier)
+    m = tp.llama_from_host_tp(backend, cfg, weights, synth.FMT_Q4_K, None, rank, world)
+    peer = run(m)
+    q.put((rank, s, nccl[0], nccl[1], nccl[2], nccl[3], peer[0], peer[2], peer[3]))
     dist.barrier()
     m.close()
     backend.check(backend.lib.slai_tp_shutdown(backend.h))
@@ -212,3 +223,7 @@ def test_two_gpu_tensor_parallel_llama_matches_oracle():
     assert got[0][4] == got[1][4]                     # and generate the same tokens
     assert np.allclose(got[0][1], 3.0) and np.allclose(got[1][1], 3.0)
     assert got[0][5] == 3 + cfg.n_layers * 7 + 1      # embed + (5 kernels + 2 exchanges) per layer + logits + argmax + advance
+    for r in range(2):                                # peer-memory exchange: no collective launches, identical results
+        assert np.array_equal(got[r][6], got[r][2])
+        assert got[r][7] == got[r][4]
+        assert got[r][8] == 3 + cfg.n_layers * 5 + 1 + 1   # + the token tick
