@@ -251,8 +251,13 @@ def run_tp(args, group):
     rank, world = group.rank, group.world
     backend = Backend(group.local_rank)
     cfg = LLAMA2_70B if args.tp_layers <= 0 else Llama2Config(**{**LLAMA2_70B.__dict__, "n_layers": args.tp_layers})
+    exchange = "none"
     if world > 1:
         tp.join_group(backend, rank, world, tp.torch_broadcast)
+        exchange = "NCCL all-reduce of 8192 f32 after wo and w_down"
+        if not args.tp_nccl:
+            tp.enable_peer_exchange(backend, world, tp.torch_all_gather, tp.torch_barrier)
+            exchange = "peer-memory stores from the wo / w_down kernels, summed in the next kernel's prologue (no collective kernel)"
         m = tp.synthetic_llama_device_tp(backend, cfg, synth.FMT_Q4_K, synth.FMT_Q6_K, rank, world)
     else:
         from slai_b200.models import synthetic_llama_device
@@ -284,7 +289,7 @@ def run_tp(args, group):
                 "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "f32", "data": "synthetic (shards seeded per rank)",
                 "config": {"workload": "llama2-70b-arch q4_k (q6_k logits) bs1 decode, fp16 KV (BASELINE configs[4])", "n_layers": cfg.n_layers,
-                           "prompt_len": PL, "parallelism": f"tp{world}", "exchange": "NCCL all-reduce of 8192 f32 after wo and w_down"},
+                           "prompt_len": PL, "parallelism": f"tp{world}", "exchange": exchange},
                 "clocks": clocks, "launches_per_token": m.launches_per_token(), "gpu_launches": m.launches_per_token() * K,
                 "ranks_agree": all(r == ids[0] for r in ids),
                 "roofline": {"bound": "hbm", "per_gpu_bytes_per_token": per_rank + kv, "achieved": (per_rank + kv) / t / 1e9, "peak": peak,
@@ -309,6 +314,7 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=512, help="prompt length (512 = the benchmark; smaller for profiling)")
     ap.add_argument("--tp", action="store_true", help="Llama-2-70B architecture sharded over all ranks instead of 7B replicas")
     ap.add_argument("--tp-layers", type=int, default=0, help="with --tp: fewer layers than 80 (0 = the full model)")
+    ap.add_argument("--tp-nccl", action="store_true", help="with --tp: exchange through NCCL all-reduce instead of peer memory")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     global PROMPT_LEN

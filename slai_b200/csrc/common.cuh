@@ -19,16 +19,15 @@ struct RopeTable {
     float* d_theta;  // head_size/2 inverse frequencies, computed on the host with libm powf
 };
 
-// Tensor-parallel exchange over peer memory (tp.cu): every rank owns a region [2 parities][ranks][XCHG_MAX_DIM]
-// floats followed by [2][ranks] sequence flags; peers store their partial vectors straight into it over NVLink.
+// Tensor-parallel exchange over peer memory (tp.cu): every rank owns a region [2 parities][ranks][XCHG_MAX_DIM] of
+// (value, sequence tag) pairs; peers store their partial vectors straight into it over NVLink, one 8-byte store per
+// element, and the reader knows an element has arrived when its tag equals the exchange's sequence number.
 constexpr int XCHG_MAX_RANKS = 8;
 constexpr int XCHG_MAX_DIM = 16384;
 struct PeerExchange {
     int ranks, rank;
-    float* slot_at[XCHG_MAX_RANKS];          // base of every rank's region (own region included), as seen from here
-    unsigned int* flags_at[XCHG_MAX_RANKS];  // base of every rank's flag block
-    unsigned int* d_tokseq;                  // device scalar: tokens decoded so far (one tick per token)
-    unsigned int* d_ticket;                  // "last block of the producing kernel" counter
+    uint2* slot_at[XCHG_MAX_RANKS];  // base of every rank's region (own region included), as seen from here
+    unsigned int* d_tokseq;          // device scalar (local): tokens decoded so far (one tick per token)
 };
 
 struct slai_ctx {

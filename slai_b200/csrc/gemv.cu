@@ -161,7 +161,6 @@ int gemv_fill_params(slai_ctx* ctx, const GemvLaunch& L, size_t dig_region, int 
         P.xr = X.ranks;
         P.xrank = X.rank;
         P.x_tokseq = X.d_tokseq;
-        P.x_ticket = X.d_ticket;
         P.x_per_token = (unsigned int)L.xchg_per_token;
         P.xo_idx1 = (unsigned int)L.xchg_out_idx1;
         P.xi_idx1 = (unsigned int)L.xchg_in_idx1;
@@ -169,17 +168,13 @@ int gemv_fill_params(slai_ctx* ctx, const GemvLaunch& L, size_t dig_region, int 
         if (L.epi == EPI_XCHG) {
             SLAI_REQUIRE(ctx, L.xchg_out_idx1 > 0 && L.nseg == 1 && L.seg[0].rows <= XCHG_MAX_DIM, SLAI_ERR_SHAPE, "gemv: bad outgoing exchange");
             const int par = (L.xchg_out_idx1 - 1) & 1;
-            for (int r = 0; r < X.ranks; r++) {
-                P.xo_slot[r] = X.slot_at[r] + ((size_t)par * X.ranks + X.rank) * XCHG_MAX_DIM;
-                P.xo_flag[r] = X.flags_at[r] + par * X.ranks + X.rank;
-            }
+            for (int r = 0; r < X.ranks; r++) P.xo_slot[r] = X.slot_at[r] + ((size_t)par * X.ranks + X.rank) * XCHG_MAX_DIM;
         }
         if (L.xchg_in_idx1 > 0) {
             SLAI_REQUIRE(ctx, K <= XCHG_MAX_DIM && (K >> 2) <= STAGE_REGS * THREADS && L.xsum_out, SLAI_ERR_SHAPE,
                          "gemv: incoming exchange of %d floats does not fit the staging registers", K);
             const int par = (L.xchg_in_idx1 - 1) & 1;
             P.xi_slots = X.slot_at[X.rank] + (size_t)par * X.ranks * XCHG_MAX_DIM;
-            P.xi_flags = X.flags_at[X.rank] + par * X.ranks;
         }
     }
 #ifdef SLAI_TRACE

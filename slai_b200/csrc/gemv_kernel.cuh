@@ -73,13 +73,10 @@ struct GemvParams {
     int pdl;  // launched with programmatic stream serialization
     // tensor-parallel exchange over peer memory (xr == 0: unused)
     int xr, xrank;                       // ranks in the group, this rank
-    float* xo_slot[XCHG_MAX_RANKS];      // EPI_XCHG: this rank's slot of the outgoing exchange in every rank's region
-    unsigned int* xo_flag[XCHG_MAX_RANKS];  // and the flag that announces it there
+    uint2* xo_slot[XCHG_MAX_RANKS];      // EPI_XCHG: this rank's slot of the outgoing exchange in every rank's region
     unsigned int xo_idx1, xi_idx1, x_per_token;  // exchange index + 1 inside the token (out / in), exchanges per token
-    const float* xi_slots;               // incoming exchange in this rank's region: [ranks][XCHG_MAX_DIM] (null: read `v`)
-    const unsigned int* xi_flags;        // [ranks]
+    const uint2* xi_slots;               // incoming exchange in this rank's region: [ranks][XCHG_MAX_DIM] (null: read `v`)
     const unsigned int* x_tokseq;        // device scalar: tokens decoded so far
-    unsigned int* x_ticket;
     float* xsum_out;                     // block 0 leaves the summed incoming vector here
 #ifdef SLAI_TRACE
     unsigned long long* trace;   // debug build only: per block of threads 8 x (globaltimer, clock64)
@@ -164,53 +161,42 @@ __device__ __forceinline__ void block_sum_max(float& s, float& m, float* stat) {
 __device__ __forceinline__ float max4(const float4& x) { return fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w))); }
 
 // ---- tensor-parallel exchange over peer memory ----------------------------------------------------------------
-// Sequence number of exchange `idx1` of the current token: flags only ever grow, so a flag >= seq means "this
-// rank's partial of this exchange has arrived".
+// Every element travels as one 8-byte store (value, sequence tag).  The tag of exchange `idx1` of the current token
+// only ever grows from exchange to exchange, so "tag == seq" means "this rank's partial of this exchange has
+// arrived": no flags, no fences, one NVLink store latency.
 __device__ __forceinline__ unsigned int xchg_seq(const GemvParams& P, unsigned int idx1) {
     return __ldcg(P.x_tokseq) * P.x_per_token + idx1;
 }
-// Wait (bounded) until every rank's partial of the incoming exchange is in this rank's region.  One thread per
-// rank polls; on expiry the error flag is raised and the kernel goes on with whatever is there.
-__device__ __forceinline__ void xchg_wait_in(const GemvParams& P) {
-    if ((int)threadIdx.x < P.xr) {
-        const unsigned int want = xchg_seq(P, P.xi_idx1);
-        const unsigned int* f = P.xi_flags + threadIdx.x;
-        for (int it = 0;; it++) {
-            unsigned int v;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-            if (v >= want) break;
-            if (it > (1 << 21)) {
-                atomicExch(P.err_flag, 3u);
-                break;
+// Sum over the ranks, in rank order, of element group i (four floats) of the incoming exchange; identical on every
+// rank.  Polls (bounded) until all four tags of every rank match; on expiry the error flag is raised and the
+// kernel goes on with whatever is there.
+__device__ __forceinline__ void xchg_load(const uint4* src, uint4& a, uint4& b) {
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(src) : "memory");
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(src + 1) : "memory");
+}
+__device__ __forceinline__ float4 xchg_gather(const GemvParams& P, int i, unsigned int seq) {
+    const uint4* src = reinterpret_cast<const uint4*>(P.xi_slots + 4 * (size_t)i);
+    constexpr size_t RANK_STRIDE = (size_t)XCHG_MAX_DIM * sizeof(uint2) / sizeof(uint4);
+    uint4 a[XCHG_MAX_RANKS], b[XCHG_MAX_RANKS];
+#pragma unroll
+    for (int r = 0; r < XCHG_MAX_RANKS; r++)  // all ranks' loads go out together: one trip when everything has arrived
+        if (r < P.xr) xchg_load(src + r * RANK_STRIDE, a[r], b[r]);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int r = 0; r < XCHG_MAX_RANKS; r++)
+        if (r < P.xr) {
+            for (int it = 0; !(a[r].y == seq && a[r].w == seq && b[r].y == seq && b[r].w == seq); it++) {
+                if (it > (1 << 20)) {
+                    atomicExch(P.err_flag, 3u);
+                    break;
+                }
+                if (it > 16) __nanosleep(100);
+                xchg_load(src + r * RANK_STRIDE, a[r], b[r]);
             }
-            if (it > 32) __nanosleep(64);
+            acc.x += __uint_as_float(a[r].x); acc.y += __uint_as_float(a[r].z);
+            acc.z += __uint_as_float(b[r].x); acc.w += __uint_as_float(b[r].z);
         }
-    }
-    __syncthreads();
-}
-// Sum over the ranks, in rank order, of element group i of the incoming exchange (identical on every rank).
-__device__ __forceinline__ float4 xchg_gather(const GemvParams& P, int i) {
-    float4 a = __ldcg(reinterpret_cast<const float4*>(P.xi_slots) + i);
-    for (int r = 1; r < P.xr; r++) {
-        const float4 b = __ldcg(reinterpret_cast<const float4*>(P.xi_slots + (size_t)r * XCHG_MAX_DIM) + i);
-        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
-    }
-    return a;
-}
-// After a block's last exchange stores: make them visible system-wide; the last block of the kernel then raises
-// this rank's flag in every rank's region.
-__device__ __forceinline__ void xchg_publish(const GemvParams& P) {
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const unsigned int ticket = atomicAdd(P.x_ticket, 1u);
-        if (ticket == gridDim.x - 1) {
-            *P.x_ticket = 0;
-            __threadfence_system();
-            const unsigned int seq = xchg_seq(P, P.xo_idx1);
-            for (int r = 0; r < P.xr; r++) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(P.xo_flag[r]), "r"(seq) : "memory");
-        }
-    }
+    return acc;
 }
 
 // Stage the activation vector: optional normalisation, power-of-two scaling so that max|v| lands in
@@ -234,12 +220,12 @@ __device__ __forceinline__ float stage_vector(const int PRO_ARG, const GemvParam
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
     const bool cached = np4 <= STAGE_REGS * THREADS;
     float4 xr[STAGE_REGS];
-    if (XIN) xchg_wait_in(P);
+    const unsigned int xseq = XIN ? xchg_seq(P, P.xi_idx1) : 0u;
 #pragma unroll
     for (int r = 0; r < STAGE_REGS; r++) {
         const int i = tid + r * THREADS;
         if (XIN) {
-            xr[r] = i < n4 ? xchg_gather(P, i) : zero4;
+            xr[r] = i < n4 ? xchg_gather(P, i, xseq) : zero4;
             if (blockIdx.x == 0 && i < n4) reinterpret_cast<float4*>(P.xsum_out)[i] = xr[r];
         } else {
             xr[r] = (cached && i < n4) ? __ldcg(v4 + i) : zero4;
@@ -656,7 +642,8 @@ __device__ __forceinline__ void gemv_phase(const GemvParams& P, Ring& R, const P
                 if (valid) {
                     float y = val[0] + bias;
                     if (P.xrank == 0) y += __ldcg(P.resid + orow);
-                    for (int rk = 0; rk < P.xr; rk++) P.xo_slot[rk][orow] = y;
+                    const uint2 pkt = make_uint2(__float_as_uint(y), xchg_seq(P, P.xo_idx1));
+                    for (int rk = 0; rk < P.xr; rk++) P.xo_slot[rk][orow] = pkt;  // one 8-byte store each: value and tag together
                 }
             } else if (SLAI_EPI_IS(EPI_SILU)) {
                 if (valid) {
@@ -697,7 +684,6 @@ __device__ __forceinline__ void gemv_phase(const GemvParams& P, Ring& R, const P
             __syncthreads();
         }
     }
-    if (SLAI_EPI_IS(EPI_XCHG)) xchg_publish(P);  // every block of the grid, once
 #undef SLAI_EPI_IS
 }
 

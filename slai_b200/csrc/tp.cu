@@ -90,18 +90,14 @@ SLAI_API int slai_tp_init(slai_ctx* ctx, const void* h_id, int rank, int size) {
 // ---- exchange over peer memory ---------------------------------------------------------------------------------
 // NCCL's all-reduce costs a kernel launch and 10-20 us for the 32 KB this path exchanges.  With the ranks'
 // exchange regions mapped into each other (CUDA IPC, NVLink peer access) the producing GEMV stores its partial
-// rows straight into every rank's region and the consuming GEMV sums the partials while it stages its input:
-// no extra kernel, one NVLink store latency.  Plain peer stores and loads only; every wait is bounded.
+// rows straight into every rank's region -- each element as one 8-byte (value, sequence tag) store -- and the
+// consuming GEMV sums the partials while it stages its input, polling the tags: no extra kernel, no flags or
+// fences, one NVLink store latency.  Plain peer stores and local loads only; every wait is bounded.
 namespace {
-constexpr size_t XCHG_FLOATS = (size_t)2 * XCHG_MAX_RANKS * XCHG_MAX_DIM;
-constexpr size_t XCHG_BYTES = XCHG_FLOATS * 4 + 4096;  // flags [2][ranks], token counter and ticket in the last page
+constexpr size_t XCHG_ELEMS = (size_t)2 * XCHG_MAX_RANKS * XCHG_MAX_DIM;
+constexpr size_t XCHG_BYTES = XCHG_ELEMS * sizeof(uint2) + 4096;  // the token counter lives in the last page
 
 __global__ void tp_tick_kernel(unsigned int* tokseq) { *tokseq += 1; }
-
-void fill_exchange(PeerExchange& X, int r, void* base) {
-    X.slot_at[r] = reinterpret_cast<float*>(base);
-    X.flags_at[r] = reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(base) + XCHG_FLOATS * 4);
-}
 }  // namespace
 
 static_assert(sizeof(cudaIpcMemHandle_t) == SLAI_TP_HANDLE_BYTES, "SLAI_TP_HANDLE_BYTES must equal sizeof(cudaIpcMemHandle_t)");
@@ -146,11 +142,9 @@ SLAI_API int slai_tp_peer_attach(slai_ctx* ctx, const void* h_handles) {
                                       "on GPUs with peer access", r, cudaGetErrorString(e));
             }
         }
-        fill_exchange(X, r, base);
+        X.slot_at[r] = reinterpret_cast<uint2*>(base);
     }
-    unsigned int* local = X.flags_at[X.rank];
-    X.d_tokseq = local + 512;  // same page, away from the flags the peers write
-    X.d_ticket = local + 576;
+    X.d_tokseq = reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(ctx->xchg_region) + XCHG_ELEMS * sizeof(uint2));
     ctx->xchg_ready = true;
     return SLAI_OK;
 }
