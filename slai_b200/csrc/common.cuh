@@ -27,6 +27,7 @@ constexpr int XCHG_MAX_DIM = 16384;
 struct PeerExchange {
     int ranks, rank;
     uint2* slot_at[XCHG_MAX_RANKS];  // base of every rank's region (own region included), as seen from here
+    uint2* local_sum;                // [2 parities][XCHG_MAX_DIM]: this GPU's two-level sums (never written by peers)
     unsigned int* d_tokseq;          // device scalar (local): tokens decoded so far (one tick per token)
 };
 

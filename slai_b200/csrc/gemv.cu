@@ -155,6 +155,7 @@ int gemv_fill_params(slai_ctx* ctx, const GemvLaunch& L, size_t dig_region, int 
     P.pdl = L.pdl ? 1 : 0;
     P.xr = 0;
     P.xi_slots = nullptr;
+    P.xl_sum = nullptr;
     if (L.xchg) {
         const PeerExchange& X = *L.xchg;
         SLAI_REQUIRE(ctx, X.ranks >= 2 && X.ranks <= XCHG_MAX_RANKS, SLAI_ERR_INVALID_ARG, "gemv: exchange group of %d ranks", X.ranks);
@@ -175,6 +176,12 @@ int gemv_fill_params(slai_ctx* ctx, const GemvLaunch& L, size_t dig_region, int 
                          "gemv: incoming exchange of %d floats does not fit the staging registers", K);
             const int par = (L.xchg_in_idx1 - 1) & 1;
             P.xi_slots = X.slot_at[X.rank] + (size_t)par * X.ranks * XCHG_MAX_DIM;
+            static int two_level_from = -1;  // group size from which blocks share the sum (SLAI_TP_TWO_LEVEL overrides)
+            if (two_level_from < 0) {
+                const char* e = getenv("SLAI_TP_TWO_LEVEL");
+                two_level_from = e ? atoi(e) : 4;
+            }
+            P.xl_sum = X.ranks >= two_level_from ? X.local_sum + (size_t)par * XCHG_MAX_DIM : nullptr;
         }
     }
 #ifdef SLAI_TRACE

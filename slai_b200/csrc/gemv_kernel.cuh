@@ -77,7 +77,9 @@ struct GemvParams {
     unsigned int xo_idx1, xi_idx1, x_per_token;  // exchange index + 1 inside the token (out / in), exchanges per token
     const uint2* xi_slots;               // incoming exchange in this rank's region: [ranks][XCHG_MAX_DIM] (null: read `v`)
     const unsigned int* x_tokseq;        // device scalar: tokens decoded so far
-    float* xsum_out;                     // block 0 leaves the summed incoming vector here
+    float* xsum_out;                     // the summed incoming vector is left here (for the residual of the next exchange)
+    uint2* xl_sum;                       // non-null: two-level sum -- each block sums a slice over the ranks into this local
+                                         // tagged buffer, then every block reads the whole sum from it
 #ifdef SLAI_TRACE
     unsigned long long* trace;   // debug build only: per block of threads 8 x (globaltimer, clock64)
     unsigned long long* wtrace;  // debug build only: per warp (loop start, loop end, cycles waiting for the ring, units)
@@ -199,6 +201,22 @@ __device__ __forceinline__ float4 xchg_gather(const GemvParams& P, int i, unsign
     return acc;
 }
 
+// Element group i of the two-level sum, from this GPU's own tagged buffer (written by the block that owns the slice).
+__device__ __forceinline__ float4 xchg_local(const GemvParams& P, int i, unsigned int seq) {
+    const uint4* src = reinterpret_cast<const uint4*>(P.xl_sum + 4 * (size_t)i);
+    uint4 a, b;
+    xchg_load(src, a, b);
+    for (int it = 0; !(a.y == seq && a.w == seq && b.y == seq && b.w == seq); it++) {
+        if (it > (1 << 20)) {
+            atomicExch(P.err_flag, 3u);
+            break;
+        }
+        if (it > 16) __nanosleep(100);
+        xchg_load(src, a, b);
+    }
+    return make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
+}
+
 // Stage the activation vector: optional normalisation, power-of-two scaling so that max|v| lands in
 // [2^25, 2^26), rounding to integers, split into four base-128 digit planes (gemv_frag.cuh), and per-sub-block
 // digit sums (for the `- dmin*m * sum(v)` term of Q4_K / Q5_K and the -32 offset of Q6_K).  Returns 1/scale.
@@ -221,12 +239,28 @@ __device__ __forceinline__ float stage_vector(const int PRO_ARG, const GemvParam
     const bool cached = np4 <= STAGE_REGS * THREADS;
     float4 xr[STAGE_REGS];
     const unsigned int xseq = XIN ? xchg_seq(P, P.xi_idx1) : 0u;
+    if (XIN && P.xl_sum) {
+        // Two-level sum (many ranks): reading every rank's partial in every block would move ranks x 64 KB through L2
+        // per block.  Each block sums only its slice over the ranks and publishes it, tagged, in a local buffer.
+        const int g0 = (int)(((long long)n4 * blockIdx.x) / gridDim.x), g1 = (int)(((long long)n4 * (blockIdx.x + 1)) / gridDim.x);
+        for (int i = g0 + tid; i < g1; i += THREADS) {
+            const float4 sum = xchg_gather(P, i, xseq);
+            reinterpret_cast<float4*>(P.xsum_out)[i] = sum;
+            uint4* dst = reinterpret_cast<uint4*>(P.xl_sum + 4 * (size_t)i);
+            dst[0] = make_uint4(__float_as_uint(sum.x), xseq, __float_as_uint(sum.y), xseq);
+            dst[1] = make_uint4(__float_as_uint(sum.z), xseq, __float_as_uint(sum.w), xseq);
+        }
+    }
 #pragma unroll
     for (int r = 0; r < STAGE_REGS; r++) {
         const int i = tid + r * THREADS;
         if (XIN) {
-            xr[r] = i < n4 ? xchg_gather(P, i, xseq) : zero4;
-            if (blockIdx.x == 0 && i < n4) reinterpret_cast<float4*>(P.xsum_out)[i] = xr[r];
+            if (P.xl_sum) {
+                xr[r] = i < n4 ? xchg_local(P, i, xseq) : zero4;
+            } else {
+                xr[r] = i < n4 ? xchg_gather(P, i, xseq) : zero4;
+                if (blockIdx.x == 0 && i < n4) reinterpret_cast<float4*>(P.xsum_out)[i] = xr[r];
+            }
         } else {
             xr[r] = (cached && i < n4) ? __ldcg(v4 + i) : zero4;
         }

@@ -95,7 +95,8 @@ SLAI_API int slai_tp_init(slai_ctx* ctx, const void* h_id, int rank, int size) {
 // fences, one NVLink store latency.  Plain peer stores and local loads only; every wait is bounded.
 namespace {
 constexpr size_t XCHG_ELEMS = (size_t)2 * XCHG_MAX_RANKS * XCHG_MAX_DIM;
-constexpr size_t XCHG_BYTES = XCHG_ELEMS * sizeof(uint2) + 4096;  // the token counter lives in the last page
+constexpr size_t XCHG_LOCAL_ELEMS = (size_t)2 * XCHG_MAX_DIM;  // two-level sums of this GPU
+constexpr size_t XCHG_BYTES = (XCHG_ELEMS + XCHG_LOCAL_ELEMS) * sizeof(uint2) + 4096;  // the token counter lives in the last page
 
 __global__ void tp_tick_kernel(unsigned int* tokseq) { *tokseq += 1; }
 }  // namespace
@@ -144,7 +145,8 @@ SLAI_API int slai_tp_peer_attach(slai_ctx* ctx, const void* h_handles) {
         }
         X.slot_at[r] = reinterpret_cast<uint2*>(base);
     }
-    X.d_tokseq = reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(ctx->xchg_region) + XCHG_ELEMS * sizeof(uint2));
+    X.local_sum = reinterpret_cast<uint2*>(ctx->xchg_region) + XCHG_ELEMS;
+    X.d_tokseq = reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(ctx->xchg_region) + (XCHG_ELEMS + XCHG_LOCAL_ELEMS) * sizeof(uint2));
     ctx->xchg_ready = true;
     return SLAI_OK;
 }
