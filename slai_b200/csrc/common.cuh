@@ -156,6 +156,8 @@ struct GemvLaunch {
     int64_t kv_pos_stride = 0;     // elements between positions
     int64_t kv_head_stride = 0;    // elements between heads
     bool pdl = false;              // launch with programmatic stream serialization
+    const void* prefetch = nullptr;  // what the next kernel reads first (e.g. its norm weights): pulled into L2 meanwhile
+    size_t prefetch_bytes = 0;
     // tensor-parallel exchange over peer memory (null: not used)
     const PeerExchange* xchg = nullptr;
     int xchg_out_idx1 = 0;         // EPI_XCHG: index + 1 of this exchange inside the token

@@ -22,10 +22,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_kernel(const __grid_constant_
     // The weights do not depend on the kernel this one may be launched behind (programmatic dependent launch):
     // the ring starts filling while that kernel drains.
     ring_init(R, prog, P.dig_region, P.nstage, P.stage_stride, P.step_bytes, P.err_flag, smem_raw, lane, warp);
+    // Let the next kernel's blocks be scheduled as this kernel's blocks leave their SMs (it parks in its own
+    // griddepcontrol.wait until this grid has completed): the hand-over costs no grid-wide launch latency.
+    if (P.pdl == 2) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // Pull data the *next* kernel reads first (its norm weights) into L2 while this one runs.
+    if (P.pf_lines > 0 && (int)blockIdx.x == (int)gridDim.x - 1)
+        for (int i = threadIdx.x; i < P.pf_lines; i += THREADS) asm volatile("prefetch.global.L2 [%0];" ::"l"(P.pf_ptr + (size_t)i * 128));
     SLAI_TRACE_POINT(1)
     asm volatile("griddepcontrol.wait;" ::: "memory");
     gemv_phase<F, 1 << PRO, 1 << EPI, XIN>(P, R, prog, smem_raw, NMAT, PRO, EPI);
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (P.pdl != 2) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     SLAI_TL_MARK(2)
 }
 
@@ -152,7 +158,14 @@ int gemv_fill_params(slai_ctx* ctx, const GemvLaunch& L, size_t dig_region, int 
     P.d_pos = L.d_pos; P.pos1 = 0; P.kcache = L.kcache; P.vcache = L.vcache; P.kv_f16 = (L.kv_dtype == SLAI_KV_F16);
     P.kv_pos_stride = L.kv_pos_stride; P.kv_head_stride = L.kv_head_stride;
     P.err_flag = ctx->d_counters + 3000;
-    P.pdl = L.pdl ? 1 : 0;
+    static int pdl_early = -1;
+    if (pdl_early < 0) {
+        const char* e = getenv("SLAI_PDL_EARLY");
+        pdl_early = (e && e[0] == '0') ? 0 : 1;
+    }
+    P.pdl = L.pdl ? (pdl_early ? 2 : 1) : 0;
+    P.pf_ptr = reinterpret_cast<const char*>(L.prefetch);
+    P.pf_lines = L.prefetch ? (int)((L.prefetch_bytes + 127) / 128) : 0;
     P.xr = 0;
     P.xi_slots = nullptr;
     P.xl_sum = nullptr;

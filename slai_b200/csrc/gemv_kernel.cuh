@@ -70,7 +70,9 @@ struct GemvParams {
     int kv_f16;
     long long kv_pos_stride, kv_head_stride;
     unsigned int* err_flag;
-    int pdl;  // launched with programmatic stream serialization
+    int pdl;  // launched with programmatic stream serialization (2: trigger the dependent launch at the start)
+    const char* pf_ptr;  // memory the next kernel reads first: prefetched into L2 by one block (pf_lines x 128 bytes)
+    int pf_lines;
     // tensor-parallel exchange over peer memory (xr == 0: unused)
     int xr, xrank;                       // ranks in the group, this rank
     uint2* xo_slot[XCHG_MAX_RANKS];      // EPI_XCHG: this rank's slot of the outgoing exchange in every rank's region

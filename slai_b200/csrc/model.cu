@@ -293,6 +293,7 @@ static int llama_record(slai_llama* m, int kind) {
             GemvLaunch L;
             L.fmt = w.wo->fmt; L.K = m->q_dim; L.nseg = 1; L.seg[0] = seg_of(w.wo, 0, c.dim, nullptr, 0, 0);
             L.v = m->xb; L.out = m->x; L.resid = m->x; L.epi = EPI_RESID; L.pdl = pdl;
+            L.prefetch = w.ffn_norm; L.prefetch_bytes = (size_t)c.dim * 4;
             if ((rc = row_parallel(L))) return rc;
         }
         // 4. xb = rmsnorm(x); hb = silu(Wgate xb) * (Wup xb)                    transformer.rs:356-361
@@ -324,6 +325,7 @@ static int llama_record(slai_llama* m, int kind) {
             GemvLaunch L;
             L.fmt = w.wdown->fmt; L.K = m->hidden; L.nseg = 1; L.seg[0] = seg_of(w.wdown, 0, c.dim, nullptr, 0, 0);
             L.v = m->hb; L.out = m->x; L.resid = m->x; L.epi = EPI_RESID; L.pdl = pdl;
+            L.prefetch = l + 1 < c.n_layers ? m->layers[l + 1].attn_norm : m->out_norm; L.prefetch_bytes = (size_t)c.dim * 4;
             if ((rc = row_parallel(L))) return rc;
         }
     }
