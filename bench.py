@@ -1,6 +1,6 @@
 #!/usr/bin/env python
 """Benchmark of the decode hot path: Llama-2-7B architecture, Q4_K weights (Q6_K logits matrix), batch 1,
-fp16 KV cache, 512-token prompt, greedy decoding (BASELINE configs[2]).  Synthetic seeded weights generated on
+fp16 KV cache, 512-token prompt, greedy decoding (the headline benchmark configuration).  Synthetic seeded weights generated on
 the GPU stand in for a checkpoint.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--gemv]
@@ -29,7 +29,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 PROMPT_LEN = 512
-WORKLOAD = "llama2-7b-arch q4_k (q6_k logits) bs1 decode, 512-token prompt, fp16 KV (BASELINE configs[2])"
+WORKLOAD = "llama2-7b-arch q4_k (q6_k logits) bs1 decode, 512-token prompt, fp16 KV (the headline benchmark configuration)"
 
 
 def measured_peaks():
@@ -144,7 +144,7 @@ def time_dominant_kernel(backend, ctx, cfg, mats, rounds=8):
 
 
 def gemv_microbench(backend, ctx, peak):
-    """BASELINE configs[1]: quantised GEMV on the four Llama-2-7B shapes x four formats, rotating over enough
+    """The GEMV microbenchmark configuration: quantised GEMV on the four Llama-2-7B shapes x four formats, rotating over enough
     distinct weight copies that the working set exceeds L2."""
     from slai_b200 import synth
     from slai_b200.ops import GpuQuantMatrix
@@ -243,7 +243,7 @@ def run_reference(args, rank, world):
 
 
 def run_tp(args, group):
-    """BASELINE configs[4] (Llama-2-70B architecture, Q4_K + Q6_K logits, fp16 KV, batch 1) sharded over all ranks:
+    """The 70B benchmark configuration (Llama-2-70B architecture, Q4_K + Q6_K logits, fp16 KV, batch 1) sharded over all ranks:
     tensor parallel, one all-reduce per half-layer.  Not the default workload: `--tp`."""
     from slai_b200 import synth, tp
     from slai_b200.models import LLAMA2_70B, Llama2Config
@@ -288,7 +288,7 @@ def run_tp(args, group):
         line = {"metric": "decode tok/s bs1 (Llama-2-70B Q4_K, tensor parallel)", "value": K / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
                 "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "f32", "data": "synthetic (shards seeded per rank)",
-                "config": {"workload": "llama2-70b-arch q4_k (q6_k logits) bs1 decode, fp16 KV (BASELINE configs[4])", "n_layers": cfg.n_layers,
+                "config": {"workload": "llama2-70b-arch q4_k (q6_k logits) bs1 decode, fp16 KV", "n_layers": cfg.n_layers,
                            "prompt_len": PL, "parallelism": f"tp{world}", "exchange": exchange},
                 "clocks": clocks, "launches_per_token": m.launches_per_token(), "gpu_launches": m.launches_per_token() * K,
                 "ranks_agree": all(r == ids[0] for r in ids),

@@ -187,6 +187,9 @@ int slai_mul_assign(slai_ctx* ctx, float* d_a, const float* d_b, int64_t n);
 int slai_copy(slai_ctx* ctx, float* d_dst, const float* d_src, int64_t n);
 
 /* ---- Sampler::sample_argmax (models/sampler.rs:55-57): first maximal index, on the device ------------ */
+/* Sampler::sample (models/sampler.rs:33-131) with the uniform random number `coin` in [0, 1) given by the caller;
+ * d_logits is overwritten with the probabilities, as in the reference. */
+int slai_sample(slai_ctx* ctx, float* d_logits, int64_t n, float temperature, float topp, float coin, int32_t* d_token_out);
 int slai_argmax(slai_ctx* ctx, const float* d_v, int64_t n, int32_t* d_index_out);
 
 /* ---- BatchedMultiqueryAttention::launch (ops/batched_multiquery_attention.rs:32-100) ------------------
@@ -252,6 +255,11 @@ int slai_llama_decode(slai_llama* m, int32_t token, int32_t pos, float* h_logits
 /* `n` greedy steps without host round trips: feeds each argmax back as the next token, starting with
  * `token` at `pos`; writes the n produced token ids to h_tokens.  Blocking. */
 int slai_llama_generate(slai_llama* m, int32_t token, int32_t pos, int32_t n, int32_t* h_tokens);
+/* The same loop with Sampler::sample (models/sampler.rs:33-54) on the device instead of greedy: temperature 0 is
+ * greedy; topp outside (0, 1) draws from the whole distribution.  The uniform number of step i is the top 24 bits of
+ * splitmix64(seed + i) / 2^24 (the reference draws from an unseeded generator, :43). */
+int slai_llama_generate_sampled(slai_llama* m, int32_t token, int32_t pos, int32_t n, float temperature, float topp, uint64_t seed,
+                                int32_t* h_tokens);
 /* Prompt processing: tokens[0..n) at positions pos0.. ; fills the KV cache.  If h_last_logits is non-NULL
  * it receives the logits of the last prompt token.  Blocking. */
 int slai_llama_prefill(slai_llama* m, const int32_t* h_tokens, int32_t n, int32_t pos0, float* h_last_logits);

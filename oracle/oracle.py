@@ -185,6 +185,14 @@ def attention(q, key_cache, value_cache, *, seq_len, kv_dim, kv_mul, n_heads, he
     return xb, att
 
 
+def sample(logits, temperature: float, topp: float, coin: float):
+    """`Sampler::sample` with the random draw `coin` given; returns (token id, probabilities)."""
+    p = _f32(logits).copy()
+    lib().ora_sample.restype = C.c_int
+    lib().ora_sample.argtypes = [C.c_void_p, C.c_int64, C.c_float, C.c_float, C.c_float]
+    return int(lib().ora_sample(_p(p), p.size, temperature, topp, coin)), p
+
+
 def argmax(v) -> int:
     v = _f32(v)
     return int(lib().ora_argmax(_p(v), v.size))

@@ -462,6 +462,47 @@ ORA_API int ora_argmax(const float* v, int64_t n) {
     return (int)best;
 }
 
+// crates/slai/src/models/sampler.rs:33-131: temperature, softmax, then either a draw from the whole distribution
+// (sample_mult, :63-78) or nucleus sampling (sample_topp, :85-131: candidates >= (1 - topp) / (n - 1), stable sort by
+// descending probability, truncation where the cumulative probability exceeds topp, draw inside the truncated
+// list).  The reference draws `coin` from an unseeded generator (:43); here it is an argument.  `logits` is
+// overwritten with the probabilities, as in the reference.
+ORA_API int ora_sample(float* logits, int64_t n, float temperature, float topp, float coin) {
+    if (temperature == 0.0f) return ora_argmax(logits, n);
+    for (int64_t i = 0; i < n; i++) logits[i] /= temperature;
+    ora_softmax(logits, n);
+    if (topp <= 0.0f || topp >= 1.0f) {
+        float cdf = 0.0f;
+        for (int64_t i = 0; i < n; i++) {
+            cdf += logits[i];
+            if (coin < cdf) return (int)i;
+        }
+        return (int)(n - 1);
+    }
+    const float cutoff = (1.0f - topp) / ((float)n - 1.0f);
+    std::vector<std::pair<float, int>> cand;
+    for (int64_t i = 0; i < n; i++)
+        if (logits[i] >= cutoff) cand.push_back({logits[i], (int)i});
+    std::stable_sort(cand.begin(), cand.end(), [](const std::pair<float, int>& a, const std::pair<float, int>& b) { return a.first > b.first; });
+    const int n0 = (int)cand.size();
+    float cumulative = 0.0f;
+    int last = n0 - 1;
+    for (int i = 0; i < n0; i++) {
+        cumulative += cand[i].first;
+        if (cumulative > topp) {
+            last = i;
+            break;
+        }
+    }
+    const float r = coin * cumulative;
+    float cdf = 0.0f;
+    for (int i = 0; i <= last; i++) {
+        cdf += cand[i].first;
+        if (r < cdf) return cand[i].second;
+    }
+    return cand[last].second;
+}
+
 // ---------------------------------------------------------------------------------------------
 // Models: dense f32 weights supplied by the caller (already dequantised, as the reference does
 // at load: models/llama2/cpu.rs:200-219; models/gpt2/cpu.rs:113-217).

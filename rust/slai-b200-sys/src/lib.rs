@@ -88,6 +88,8 @@ extern "C" {
     pub fn slai_llama_set_f32_device(m: *mut slai_llama, weight_id: i32, layer: i32, d_data: *const f32, n: i64) -> i32;
     pub fn slai_llama_decode(m: *mut slai_llama, token: i32, pos: i32, h_logits: *mut f32, next_token: *mut i32) -> i32;
     pub fn slai_llama_generate(m: *mut slai_llama, token: i32, pos: i32, n: i32, h_tokens: *mut i32) -> i32;
+    pub fn slai_llama_generate_sampled(m: *mut slai_llama, token: i32, pos: i32, n: i32, temperature: f32, topp: f32, seed: u64, h_tokens: *mut i32) -> i32;
+    pub fn slai_sample(ctx: *mut slai_ctx, d_logits: *mut f32, n: i64, temperature: f32, topp: f32, coin: f32, d_token_out: *mut i32) -> i32;
     pub fn slai_llama_prefill(m: *mut slai_llama, h_tokens: *const i32, n: i32, pos0: i32, h_last_logits: *mut f32) -> i32;
     pub fn slai_llama_read_state(m: *mut slai_llama, which: i32, h_out: *mut f32, n: i64) -> i32;
     pub fn slai_llama_launches_per_token(m: *const slai_llama) -> i32;

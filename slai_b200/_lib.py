@@ -106,6 +106,8 @@ SIGNATURES = {
     "slai_llama_set_f32_device": (C.c_int, [_vp, C.c_int, C.c_int, _vp, _i64]),
     "slai_llama_decode": (C.c_int, [_vp, _i32, _i32, _vp, C.POINTER(_i32)]),
     "slai_llama_generate": (C.c_int, [_vp, _i32, _i32, _i32, _vp]),
+    "slai_llama_generate_sampled": (C.c_int, [_vp, _i32, _i32, _i32, C.c_float, C.c_float, C.c_uint64, _vp]),
+    "slai_sample": (C.c_int, [_vp, _vp, _i64, C.c_float, C.c_float, C.c_float, _vp]),
     "slai_llama_prefill": (C.c_int, [_vp, _vp, _i32, _i32, _vp]),
     "slai_llama_read_state": (C.c_int, [_vp, C.c_int, _vp, _i64]),
     "slai_llama_launches_per_token": (C.c_int, [_vp]),

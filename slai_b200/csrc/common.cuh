@@ -194,6 +194,12 @@ int launch_embed_f32(slai_ctx* ctx, float* x, const float* table, int dim, const
 int launch_embed_q8(slai_ctx* ctx, float* x, const slai_qmatrix* wte, const int* d_token, const float* wpe,
                     const int* d_pos, bool pdl);
 int launch_argmax(slai_ctx* ctx, const float* v, int64_t n, int32_t* d_out, bool pdl);
+// sampler.cu
+size_t sampler_params_bytes();
+size_t sampler_scratch_bytes(int n);
+int sampler_set_params(slai_ctx* ctx, void* d_params, float temperature, float topp, unsigned long long seed);
+int launch_sample(slai_ctx* ctx, float* d_logits, int n, const void* d_params, const int* d_step, float host_coin, bool use_host_coin,
+                  void* d_scratch, int32_t* d_out, bool pdl);
 int launch_advance(slai_ctx* ctx, int* d_token, int* d_pos, const int32_t* d_next, int32_t* d_history, bool pdl);
 
 #if defined(SLAI_TRACE) && defined(__CUDACC__)

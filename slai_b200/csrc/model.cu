@@ -15,11 +15,11 @@ struct Scalars {  // device ints: [0] token, [1] pos, [2] step, [3] next
     int* d = nullptr;
 };
 
-enum GraphKind { G_DECODE = 0, G_GENERATE = 1, G_FORCED = 2, G_COUNT = 3 };
+enum GraphKind { G_DECODE = 0, G_GENERATE = 1, G_FORCED = 2, G_SAMPLED = 3, G_COUNT = 4 };
 
 struct GraphSet {
-    cudaGraphExec_t exec[G_COUNT] = {nullptr, nullptr, nullptr};
-    bool warmed[G_COUNT] = {false, false, false};  // first token of a kind runs eagerly (sets kernel attributes)
+    cudaGraphExec_t exec[G_COUNT] = {};
+    bool warmed[G_COUNT] = {};  // first token of a kind runs eagerly (sets kernel attributes)
     bool use_graph = true;
 };
 
@@ -75,6 +75,7 @@ struct slai_llama {
     // FFN rows; x (dim floats) is replicated, xpart receives a row-parallel GEMV's partial before the exchange
     int q_dim = 0, n_q_local = 0, hidden = 0, tp = 1;
     float* xpart = nullptr;
+    void *d_samp = nullptr, *d_samp_scratch = nullptr;  // sampler parameters and sort scratch (slai_llama_generate_sampled)
     std::vector<LlamaLayer> layers;
     const slai_qmatrix* output = nullptr;
     const slai_qmatrix* embd_q = nullptr;
@@ -348,9 +349,11 @@ static int llama_record(slai_llama* m, int kind) {
         if ((rc = gemv_launch(ctx, L))) return rc;
         n++;
     }
-    if ((rc = launch_argmax(ctx, m->logits, c.vocab_size, m->sc.d + 3, pdl))) return rc;
+    if (kind == G_SAMPLED) rc = launch_sample(ctx, m->logits, c.vocab_size, m->d_samp, m->sc.d + 2, 0.f, false, m->d_samp_scratch, m->sc.d + 3, pdl);
+    else rc = launch_argmax(ctx, m->logits, c.vocab_size, m->sc.d + 3, pdl);
+    if (rc) return rc;
     n++;
-    if (kind == G_GENERATE) {
+    if (kind == G_GENERATE || kind == G_SAMPLED) {
         if ((rc = launch_advance(ctx, d_token, d_pos, m->sc.d + 3, m->d_history, pdl))) return rc;
         n++;
     } else if (kind == G_FORCED) {
@@ -469,6 +472,7 @@ SLAI_API int slai_llama_destroy(slai_llama* m) {
     cudaFree(m->token_embd); cudaFree(m->out_norm);
     cudaFree(m->x); cudaFree(m->xb); cudaFree(m->xpart); cudaFree(m->q); cudaFree(m->hb); cudaFree(m->hb2); cudaFree(m->logits);
     cudaFree(m->kcache); cudaFree(m->vcache); cudaFree(m->sc.d); cudaFree(m->d_history); cudaFree(m->attn_scratch);
+    cudaFree(m->d_samp); cudaFree(m->d_samp_scratch);
     delete m;
     return SLAI_OK;
 }
@@ -569,7 +573,8 @@ static int decode_impl(M* m, RecordFn record, int vocab, int seq_len, int32_t to
 }
 
 template <class M, class RecordFn>
-static int generate_impl(M* m, RecordFn record, int vocab, int seq_len, int32_t token, int32_t pos, int32_t n, int32_t* h_tokens) {
+static int generate_impl(M* m, RecordFn record, int vocab, int seq_len, int32_t token, int32_t pos, int32_t n, int32_t* h_tokens,
+                         int kind = G_GENERATE) {
     slai_ctx* ctx = m->ctx;
     SLAI_REQUIRE(ctx, token >= 0 && token < vocab, SLAI_ERR_INVALID_ARG, "generate: token %d out of range", token);
     SLAI_REQUIRE(ctx, n > 0 && pos >= 0 && pos + n <= seq_len && n <= m->history_cap, SLAI_ERR_INVALID_ARG,
@@ -577,7 +582,7 @@ static int generate_impl(M* m, RecordFn record, int vocab, int seq_len, int32_t 
     int rc = set_scalars(m, token, pos, 0);
     if (rc) return rc;
     for (int i = 0; i < n; i++)
-        if ((rc = run_graph(m, G_GENERATE, record))) return rc;
+        if ((rc = run_graph(m, kind, record))) return rc;
     if (h_tokens) SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(h_tokens, m->d_history, (size_t)n * 4, cudaMemcpyDeviceToHost, ctx->stream));
     SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return SLAI_OK;
@@ -608,6 +613,19 @@ static int prefill_impl(M* m, RecordFn record, int vocab, int seq_len, const int
 SLAI_API int slai_llama_decode(slai_llama* m, int32_t token, int32_t pos, float* h_logits, int32_t* next_token) {
     if (!m) return SLAI_ERR_INVALID_ARG;
     return decode_impl(m, llama_record, m->cfg.vocab_size, m->cfg.seq_len, token, pos, h_logits, next_token);
+}
+SLAI_API int slai_llama_generate_sampled(slai_llama* m, int32_t token, int32_t pos, int32_t n, float temperature, float topp, uint64_t seed,
+                                         int32_t* h_tokens) {
+    if (!m) return SLAI_ERR_INVALID_ARG;
+    slai_ctx* ctx = m->ctx;
+    SLAI_REQUIRE(ctx, temperature >= 0.0f, SLAI_ERR_INVALID_ARG, "generate: negative temperature");
+    if (!m->d_samp) {
+        SLAI_CHECK_CUDA(ctx, cudaMalloc(&m->d_samp, sampler_params_bytes()));
+        SLAI_CHECK_CUDA(ctx, cudaMalloc(&m->d_samp_scratch, sampler_scratch_bytes(m->cfg.vocab_size)));
+    }
+    int rc = sampler_set_params(ctx, m->d_samp, temperature, topp, seed);
+    if (rc) return rc;
+    return generate_impl(m, llama_record, m->cfg.vocab_size, m->cfg.seq_len, token, pos, n, h_tokens, G_SAMPLED);
 }
 SLAI_API int slai_llama_generate(slai_llama* m, int32_t token, int32_t pos, int32_t n, int32_t* h_tokens) {
     if (!m) return SLAI_ERR_INVALID_ARG;

@@ -116,6 +116,13 @@ class Llama2:
         self.backend.check(self.backend.lib.slai_llama_generate(self.h, token, pos, n, out.ctypes.data_as(C.c_void_p)))
         return out
 
+    def generate_sampled(self, token: int, pos: int, n: int, temperature: float, topp: float, seed: int) -> np.ndarray:
+        """The generate loop with `Sampler::sample` (models/sampler.rs:33-54) on the device; see `sample_coin`."""
+        out = np.empty(n, dtype=np.int32)
+        self.backend.check(self.backend.lib.slai_llama_generate_sampled(self.h, token, pos, n, temperature, topp, seed,
+                                                                        out.ctypes.data_as(C.c_void_p)))
+        return out
+
     def prefill(self, tokens, pos0: int = 0, want_logits: bool = False):
         t = np.ascontiguousarray(tokens, dtype=np.int32)
         logits = np.empty(self.config.vocab_size, dtype=np.float32) if want_logits else None
@@ -143,6 +150,16 @@ class Llama2:
             self.close()
         except Exception:
             pass
+
+
+def sample_coin(seed: int, step: int) -> float:
+    """The uniform number the device sampler uses at step `step`: top 24 bits of splitmix64(seed + step) / 2^24."""
+    m = (1 << 64) - 1
+    x = (seed + step + 0x9E3779B97F4A7C15) & m
+    x = ((x ^ (x >> 30)) * 0xBF58476D1CE4E5B9) & m
+    x = ((x ^ (x >> 27)) * 0x94D049BB133111EB) & m
+    x ^= x >> 31
+    return float((x >> 40) & 0xFFFFFF) / 16777216.0
 
 
 def _seed(base: int, name: str, layer: int) -> list[int]:

@@ -359,6 +359,14 @@ class LlmContext:
     def kv_append(self, key_cache, value_cache, k, v, kv_dim: int, pos: int, kv_dtype: int = KV_F32):
         self.backend.check(self.lib.slai_kv_append(self.h, _ptr(key_cache), _ptr(value_cache), kv_dtype, _ptr(k), _ptr(v), kv_dim, pos))
 
+    def sample(self, logits: GpuVector, temperature: float, topp: float, coin: float) -> int:
+        """`Sampler::sample` (models/sampler.rs:33-54) on the device, the uniform number `coin` given; `logits` is
+        overwritten with the probabilities."""
+        out = GpuVector(self.backend, 1, np.int32)
+        self.backend.check(self.backend.lib.slai_sample(self.backend.h, C.c_void_p(logits.ptr), logits.n, temperature, topp, coin,
+                                                        C.c_void_p(out.ptr)))
+        return int(out.to_numpy()[0])
+
     # Sampler::sample_argmax (models/sampler.rs:55-57)
     def argmax(self, v) -> int:
         out = self.backend.zeros(1, np.int32)

@@ -8,7 +8,7 @@
    ql/qh[k]=8i+k, d bits=123`) with the values `Block*::dequantize()` yields for them, computed by the CPU
    oracle and — when the `gguf` python package is importable — required to equal its independent
    dequantiser bit for bit before being written.
-2. tiny_llama_greedy.npz — BASELINE config 1 (tiny Llama-2 architecture, Q8_0, 16-token seeded prompt, 128
+2. tiny_llama_greedy.npz — the tiny-Llama benchmark configuration (tiny Llama-2 architecture, Q8_0, 16-token seeded prompt, 128
    greedy tokens) run through the CPU oracle: prompt, generated ids and the top-1/top-2 logit margin per step.
 
 The reference itself cannot be run here (Rust, no toolchain), so these are oracle outputs pinned against

@@ -147,7 +147,7 @@ def test_gemv_activation_range(backend, ctx, scale):
 
 @pytest.mark.parametrize("fmt", FMTS)
 def test_gemv_full_size_device_blocks(backend, ctx, fmt):
-    """BASELINE config 2's largest shape (32000 x 4096) with blocks generated on the device; the same bytes are
+    """The GEMV benchmark's largest shape (32000 x 4096) with blocks generated on the device; the same bytes are
     read back for the oracle.  Also checks linearity W(a x + y) = a W x + W y, a size-independent property."""
     M, K = 32000, 4096
     m = GpuQuantMatrix.synthetic(backend, fmt, M, K, seed=1234 + fmt, std=0.02, keep_raw=True)

@@ -16,7 +16,7 @@ GOLD = os.path.join(os.path.dirname(__file__), "golden")
 
 
 def test_tiny_llama_greedy_matches_fixture(backend):
-    """BASELINE config 1: 16-token prompt, 128 greedy tokens, Q8_0; ids equal the committed oracle run."""
+    """The tiny-Llama benchmark configuration: 16-token prompt, 128 greedy tokens, Q8_0; ids equal the committed oracle run."""
     g = np.load(os.path.join(GOLD, "tiny_llama_greedy.npz"))
     cfg = Llama2Config(**{**TINY_LLAMA.__dict__, "kv_dtype": _lib.KV_F32})
     w = synthetic_llama_host(cfg, synth.FMT_Q8_0, seed=int(g["seed"][0]))

@@ -145,7 +145,7 @@ def test_attention_vs_numpy():
 
 
 def test_tiny_llama_fixture_reproduces():
-    """BASELINE config 1 through the oracle reproduces the committed greedy ids (first 24 steps checked here;
+    """The tiny-Llama benchmark configuration through the oracle reproduces the committed greedy ids (first 24 steps checked here;
     tests/golden/make_golden.py wrote all 128)."""
     from slai_b200.models import TINY_LLAMA as cfg, synthetic_llama_host
     g = np.load(os.path.join(GOLD, "tiny_llama_greedy.npz"))

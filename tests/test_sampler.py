@@ -1,0 +1,125 @@
+"""Sampler (models/sampler.rs): the oracle's restatement against a direct numpy transcription, and the device sampler
+against the oracle for greedy, whole-distribution and nucleus draws."""
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+
+
+def numpy_sample(logits, temperature, topp, coin):
+    """Straight transcription of Sampler::sample with f32 sequential sums."""
+    x = np.asarray(logits, dtype=np.float32)
+    if temperature == 0.0:
+        return int(np.argmax(x)), None
+    x = x / np.float32(temperature)
+    e = np.exp(x - x.max()).astype(np.float32)
+    s = np.float32(0)
+    for v in e:
+        s = np.float32(s + v)
+    p = (e / s).astype(np.float32)
+    n = p.size
+    if topp <= 0.0 or topp >= 1.0:
+        c = np.float32(0)
+        for i, v in enumerate(p):
+            c = np.float32(c + v)
+            if coin < c:
+                return i, p
+        return n - 1, p
+    cutoff = np.float32((np.float32(1.0) - np.float32(topp)) / (np.float32(n) - np.float32(1.0)))
+    idx = [i for i in range(n) if p[i] >= cutoff]
+    idx.sort(key=lambda i: -float(p[i]))  # stable
+    cum, last = np.float32(0), len(idx) - 1
+    for k, i in enumerate(idx):
+        cum = np.float32(cum + p[i])
+        if cum > np.float32(topp):
+            last = k
+            break
+    r = np.float32(np.float32(coin) * cum)
+    c = np.float32(0)
+    for k in range(last + 1):
+        c = np.float32(c + p[idx[k]])
+        if r < c:
+            return idx[k], p
+    return idx[last], p
+
+
+CASES = [(0.0, 0.9), (1.0, 0.0), (0.7, 1.0), (1.0, 0.9), (0.8, 0.5), (1.3, 0.95), (0.5, 0.1)]
+
+
+def test_oracle_sampler_matches_transcription():
+    rng = np.random.default_rng(5)
+    for n, spread in ((50, 1.0), (1000, 3.0), (4000, 0.5)):
+        logits = (rng.standard_normal(n) * spread).astype(np.float32)
+        for temperature, topp in CASES:
+            for coin in (0.0, 0.013, 0.37, 0.5, 0.81, 0.999):
+                got, _ = O.sample(logits, temperature, topp, coin)
+                want, _ = numpy_sample(logits, temperature, topp, coin)
+                assert got == want, (n, temperature, topp, coin)
+
+
+def boundary_margin(p, topp, coin):
+    """Distance of the draw from the nearest boundary of the cumulative distribution it is compared with (so that
+    few-ulp differences between summation orders cannot change the result)."""
+    p = p.astype(np.float64)
+    n = p.size
+    if topp <= 0.0 or topp >= 1.0:
+        return float(np.min(np.abs(np.cumsum(p) - coin)))
+    cutoff = (1.0 - topp) / (n - 1.0)
+    cand = np.sort(p[p >= cutoff])[::-1]
+    cum = np.cumsum(cand)
+    over = np.nonzero(cum > topp)[0]
+    last = int(over[0]) if over.size else cand.size - 1
+    m = float(np.min(np.abs(cum[: last + 1] - coin * cum[last])))
+    return min(m, float(np.min(np.abs(cum - topp))), float(np.min(np.abs(p - cutoff))))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,spread", [(1000, 3.0), (32000, 2.0), (50257, 0.7), (5000, 0.05)])
+def test_device_sampler_matches_oracle(backend, ctx, n, spread):
+    rng = np.random.default_rng(n)
+    logits = (rng.standard_normal(n) * spread).astype(np.float32)
+    logits[rng.integers(0, n, 5)] = logits.max()  # ties at the top: greedy must take the first
+    checked = 0
+    for temperature, topp in CASES:
+        for coin in (0.0, 0.013, 0.37, 0.5, 0.81, 0.999):
+            want, p = O.sample(logits, temperature, topp, coin)
+            v = backend.vector(logits)
+            got = ctx.sample(v, temperature, topp, coin)
+            if temperature == 0.0:
+                assert got == want == int(np.argmax(logits))
+                continue
+            probs = v.to_numpy()
+            assert np.allclose(probs, p, rtol=2e-6, atol=1e-12)
+            if boundary_margin(p, topp, coin) > 1e-5:
+                assert got == want, (temperature, topp, coin)
+                checked += 1
+    assert checked >= 20
+
+
+@pytest.mark.gpu
+def test_generate_sampled_follows_the_oracle(backend):
+    from helpers import oracle_llama
+    from slai_b200 import _lib, synth
+    from slai_b200.models import Llama2Config, llama_from_host, sample_coin, synthetic_llama_host
+    cfg = Llama2Config(dim=256, hidden_dim=512, n_layers=2, n_q_heads=4, n_kv_heads=4, vocab_size=800, seq_len=64, kv_dtype=_lib.KV_F32)
+    w = synthetic_llama_host(cfg, synth.FMT_Q8_0, seed=21, std=0.08, embd_std=1.0)
+    m = llama_from_host(backend, cfg, w, synth.FMT_Q8_0)
+    ref = oracle_llama(cfg, w, synth.FMT_Q8_0, nthreads=2)
+    temperature, topp, seed, n = 0.9, 0.9, 1234, 24
+    got = m.generate_sampled(7, 0, n, temperature, topp, seed)
+    again = m.generate_sampled(7, 0, n, temperature, topp, seed)
+    assert list(got) == list(again)                     # seeded: reproducible
+    other = m.generate_sampled(7, 0, n, temperature, topp, seed + 1)
+    assert list(other) != list(got)
+    assert list(m.generate_sampled(7, 0, n, 0.0, topp, seed)) == list(m.generate(7, 0, n))   # temperature 0 = greedy
+    tok, agree = 7, 0
+    for step in range(n):
+        logits = ref.forward(tok, step)
+        coin = sample_coin(seed, step)
+        want, p = O.sample(logits, temperature, topp, coin)
+        if boundary_margin(p, topp, coin) < 1e-4:
+            break   # a draw too close to a boundary to pin: the two sequences may legitimately part here
+        assert got[step] == want, step
+        agree += 1
+        tok = want
+    assert agree >= 8
