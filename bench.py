@@ -242,6 +242,41 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_gpt2(args):
+    """The GPT-2 XL benchmark configuration (48 layers, dim 1600, 25 heads, FFN 6400, vocab 50257, tied logits, Q8_0
+    weights, fp16 KV, batch 1): 128-token prompt, then the timed greedy tokens.  Not the default workload: `--gpt2`."""
+    from slai_b200 import synth
+    from slai_b200.models import GPT2_XL, synthetic_gpt2_device
+    from slai_b200.ops import Backend
+    backend = Backend(0)
+    p = GPT2_XL
+    m = synthetic_gpt2_device(backend, p, synth.FMT_Q8_0, seed=0)
+    peak, peak_src = measured_peaks()
+    K, W, PL = args.steps, args.warmup, 128
+    rng = np.random.default_rng(42)
+    prompt = rng.integers(0, p.n_vocab, size=PL).astype(np.int32)
+    m.prefill(prompt[:-1], 0)
+    warm = m.generate(int(prompt[-1]), PL - 1, W)
+    tok, pos = int(warm[-1]), PL - 1 + W
+    sampler = ClockSampler(0)
+    backend.synchronize()
+    backend.timer_start()
+    toks = m.generate(tok, pos, K)
+    ms = backend.timer_stop()
+    clocks = sampler.stop()
+    esz = 2
+    kv = float(np.mean([2 * p.n_layer * p.n_embd * esz * (q + 1) for q in range(pos, pos + K)]))
+    bytes_tok = p.weight_bytes_per_token(synth.FMT_Q8_0) + kv
+    t = ms * 1e-3 / K
+    line = {"metric": "decode tok/s bs1 (GPT-2 XL Q8_0)", "value": K / (ms * 1e-3), "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "gpt2-xl-arch q8_0 bs1 decode, 128-token prompt, fp16 KV", "decode_positions": [pos, pos + K - 1]},
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "bytes_per_token": bytes_tok, "achieved": bytes_tok / t / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": bytes_tok / t / 1e9 / peak, "peak_source": peak_src}}
+    print(json.dumps(line), flush=True)
+
+
 def run_tp(args, group):
     """The 70B benchmark configuration (Llama-2-70B architecture, Q4_K + Q6_K logits, fp16 KV, batch 1) sharded over all ranks:
     tensor parallel, one all-reduce per half-layer.  Not the default workload: `--tp`."""
@@ -312,6 +347,7 @@ def main():
     ap.add_argument("--gemv", action="store_true", help="also run the 16-case quantised GEMV microbenchmark")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--prompt-len", type=int, default=512, help="prompt length (512 = the benchmark; smaller for profiling)")
+    ap.add_argument("--gpt2", action="store_true", help="GPT-2 XL architecture (Q8_0) instead of Llama-2-7B; one GPU")
     ap.add_argument("--tp", action="store_true", help="Llama-2-70B architecture sharded over all ranks instead of 7B replicas")
     ap.add_argument("--tp-layers", type=int, default=0, help="with --tp: fewer layers than 80 (0 = the full model)")
     ap.add_argument("--tp-nccl", action="store_true", help="with --tp: exchange through NCCL all-reduce instead of peer memory")
@@ -327,6 +363,10 @@ def main():
         run_reference(args, rank, world)
         return
 
+    if args.gpt2:
+        if rank == 0:
+            run_gpt2(args)
+        return
     from slai_b200.replicas import ReplicaGroup
     group = ReplicaGroup(backend="nccl")
     if args.tp:

@@ -148,6 +148,7 @@ struct GemvLaunch {
     // EPI_QKV
     int rope = 0;                  // 1: rotate adjacent pairs of q and k
     const float* rope_theta = nullptr;  // head_size/2 inverse frequencies
+    const float* rope_cs = nullptr;     // optional: (cos, sin) of this token's angles, head_size/2 pairs (else sincosf in the epilogue)
     int head_size = 0;
     const int* d_pos = nullptr;    // device scalar: position (RoPE angle and KV slot)
     void* kcache = nullptr;        // layer base of the K cache
@@ -190,9 +191,9 @@ const float* rope_table(slai_ctx* ctx, int head_size, float base);
 
 // ops.cu helpers used by the models
 int launch_embed_f32(slai_ctx* ctx, float* x, const float* table, int dim, const int* d_token, const float* wpe,
-                     const int* d_pos, bool pdl);
+                     const int* d_pos, bool pdl, const float* rope_theta = nullptr, float* rope_cs = nullptr, int rope_half = 0);
 int launch_embed_q8(slai_ctx* ctx, float* x, const slai_qmatrix* wte, const int* d_token, const float* wpe,
-                    const int* d_pos, bool pdl);
+                    const int* d_pos, bool pdl, const float* rope_theta = nullptr, float* rope_cs = nullptr, int rope_half = 0);
 int launch_argmax(slai_ctx* ctx, const float* v, int64_t n, int32_t* d_out, bool pdl);
 // sampler.cu
 size_t sampler_params_bytes();

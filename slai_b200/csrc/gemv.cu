@@ -154,7 +154,7 @@ int gemv_fill_params(slai_ctx* ctx, const GemvLaunch& L, size_t dig_region, int 
     P.step_bytes = layout::step_bytes(L.fmt);
     P.stage_stride = (P.step_bytes + 127) & ~127;
     P.v = L.v; P.out = L.out; P.norm_w = L.norm_w; P.norm_b = L.norm_b; P.eps = L.eps;
-    P.resid = L.resid; P.rope = L.rope; P.rope_theta = L.rope_theta; P.head_size = L.head_size;
+    P.resid = L.resid; P.rope = L.rope; P.rope_theta = L.rope_theta; P.rope_cs = L.rope_cs; P.head_size = L.head_size;
     P.d_pos = L.d_pos; P.pos1 = 0; P.kcache = L.kcache; P.vcache = L.vcache; P.kv_f16 = (L.kv_dtype == SLAI_KV_F16);
     P.kv_pos_stride = L.kv_pos_stride; P.kv_head_stride = L.kv_head_stride;
     P.err_flag = ctx->d_counters + 3000;
@@ -189,10 +189,13 @@ int gemv_fill_params(slai_ctx* ctx, const GemvLaunch& L, size_t dig_region, int 
                          "gemv: incoming exchange of %d floats does not fit the staging registers", K);
             const int par = (L.xchg_in_idx1 - 1) & 1;
             P.xi_slots = X.slot_at[X.rank] + (size_t)par * X.ranks * XCHG_MAX_DIM;
-            static int two_level_from = -1;  // group size from which blocks share the sum (SLAI_TP_TWO_LEVEL overrides)
+            // Group size from which the blocks share one sum (SLAI_TP_TWO_LEVEL=<ranks>).  Off by default: measured at
+            // eight ranks the two-level sum (6.18 ms per 70B token) does not beat every block summing all ranks' partials
+            // itself (5.99 ms); the extra local round trip costs what the smaller L2 volume saves.
+            static int two_level_from = -1;
             if (two_level_from < 0) {
                 const char* e = getenv("SLAI_TP_TWO_LEVEL");
-                two_level_from = e ? atoi(e) : 4;
+                two_level_from = e ? atoi(e) : 1 << 30;
             }
             P.xl_sum = X.ranks >= two_level_from ? X.local_sum + (size_t)par * XCHG_MAX_DIM : nullptr;
         }

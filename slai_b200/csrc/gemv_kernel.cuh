@@ -62,6 +62,7 @@ struct GemvParams {
     const float* resid;
     int rope;
     const float* rope_theta;
+    const float* rope_cs;  // (cos, sin) pairs of the current position, or null
     int head_size;
     const int* d_pos;
     int pos1;        // position + 1 when the caller already knows it (0: read d_pos)
@@ -695,9 +696,13 @@ __device__ __forceinline__ void gemv_phase(const GemvParams& P, Ring& R, const P
                 const float other = __shfl_xor_sync(__activemask(), y, 1);
                 if (P.rope && sg.role < 2) {
                     const int hd = (row_in_seg & ~1) % P.head_size;
-                    const float ang = (float)pos * P.rope_theta[hd >> 1];
                     float sn, cs;
-                    sincosf(ang, &sn, &cs);
+                    if (P.rope_cs) {
+                        cs = __ldcg(P.rope_cs + hd);
+                        sn = __ldcg(P.rope_cs + hd + 1);
+                    } else {
+                        sincosf((float)pos * P.rope_theta[hd >> 1], &sn, &cs);
+                    }
                     y = (r & 1) ? (sn * other + cs * y) : (cs * y - sn * other);
                 }
                 if (valid) {

@@ -75,6 +75,7 @@ struct slai_llama {
     // FFN rows; x (dim floats) is replicated, xpart receives a row-parallel GEMV's partial before the exchange
     int q_dim = 0, n_q_local = 0, hidden = 0, tp = 1;
     float* xpart = nullptr;
+    float* rope_cs = nullptr;  // (cos, sin) of the current token's RoPE angles, written by the embedding kernel
     void *d_samp = nullptr, *d_samp_scratch = nullptr;  // sampler parameters and sort scratch (slai_llama_generate_sampled)
     std::vector<LlamaLayer> layers;
     const slai_qmatrix* output = nullptr;
@@ -184,8 +185,9 @@ static int llama_record(slai_llama* m, int kind) {
     int* d_pos = m->sc.d + 1;
     int rc;
     SLAI_REQUIRE(ctx, m->out_norm && (m->token_embd || m->embd_q), SLAI_ERR_INVALID_ARG, "llama: embedding / output norm not set");
-    if (m->embd_q) rc = launch_embed_q8(ctx, m->x, m->embd_q, d_token, nullptr, nullptr, false);
-    else rc = launch_embed_f32(ctx, m->x, m->token_embd, c.dim, d_token, nullptr, nullptr, false);
+    const bool table = c.rope_variant == 0 && m->head_size / 2 <= 256;
+    if (m->embd_q) rc = launch_embed_q8(ctx, m->x, m->embd_q, d_token, nullptr, d_pos, false, m->rope_theta, table ? m->rope_cs : nullptr, m->head_size / 2);
+    else rc = launch_embed_f32(ctx, m->x, m->token_embd, c.dim, d_token, nullptr, d_pos, false, m->rope_theta, table ? m->rope_cs : nullptr, m->head_size / 2);
     if (rc) return rc;
     n++;
     const size_t esz = c.kv_dtype == SLAI_KV_F16 ? 2 : 4;
@@ -260,6 +262,7 @@ static int llama_record(slai_llama* m, int kind) {
             for (int i = 0; i < nseg; i++) L.seg[i] = segs[i];
             L.v = m->x; L.out = m->q; L.pro = PRO_RMS; L.norm_w = w.attn_norm; L.eps = c.rms_norm_eps;
             L.epi = EPI_QKV; L.rope = fuse_rope ? 1 : 0; L.rope_theta = m->rope_theta; L.head_size = m->head_size;
+            L.rope_cs = table ? m->rope_cs : nullptr;
             L.d_pos = d_pos; L.kcache = kc; L.vcache = vc; L.kv_dtype = c.kv_dtype;
             L.kv_pos_stride = m->head_size; L.kv_head_stride = (int64_t)c.seq_len * m->head_size;
             L.pdl = pdl;
@@ -437,7 +440,7 @@ SLAI_API int slai_llama_create(slai_ctx* ctx, const slai_llama_config* cfg, slai
     m->history_cap = c.seq_len + 8;
     m->attn_scratch_bytes = attention_scratch_bytes(ctx, m->n_q_local, m->kv_mul, m->head_size, c.seq_len - 1);
     bool ok = cudaMalloc(&m->x, (size_t)c.dim * 4) == cudaSuccess && cudaMalloc(&m->xb, (size_t)c.dim * 4) == cudaSuccess &&
-              cudaMalloc(&m->xpart, (size_t)c.dim * 4) == cudaSuccess &&
+              cudaMalloc(&m->xpart, (size_t)c.dim * 4) == cudaSuccess && cudaMalloc(&m->rope_cs, 2 * 256 * 4) == cudaSuccess &&
               cudaMalloc(&m->q, (size_t)c.dim * 4) == cudaSuccess && cudaMalloc(&m->hb, (size_t)c.hidden_dim * 4) == cudaSuccess &&
               cudaMalloc(&m->hb2, (size_t)c.hidden_dim * 4) == cudaSuccess &&
               cudaMalloc(&m->logits, (size_t)c.vocab_size * 4) == cudaSuccess &&
@@ -472,7 +475,7 @@ SLAI_API int slai_llama_destroy(slai_llama* m) {
     cudaFree(m->token_embd); cudaFree(m->out_norm);
     cudaFree(m->x); cudaFree(m->xb); cudaFree(m->xpart); cudaFree(m->q); cudaFree(m->hb); cudaFree(m->hb2); cudaFree(m->logits);
     cudaFree(m->kcache); cudaFree(m->vcache); cudaFree(m->sc.d); cudaFree(m->d_history); cudaFree(m->attn_scratch);
-    cudaFree(m->d_samp); cudaFree(m->d_samp_scratch);
+    cudaFree(m->d_samp); cudaFree(m->d_samp_scratch); cudaFree(m->rope_cs);
     delete m;
     return SLAI_OK;
 }

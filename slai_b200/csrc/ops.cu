@@ -556,16 +556,22 @@ __global__ void kv_append_kernel<__half>(__half* kc, __half* vc, const float* k,
     }
 }
 
-// first maximal index (nalgebra `imax`): ties resolve to the smaller index
-__global__ void argmax_kernel(const float* v, long long n, int* out) {
+// first maximal index (nalgebra `imax`): ties resolve to the smaller index.  ARG_BLOCKS blocks scan a slice each;
+// the last one to finish (ticket) combines the per-block results.
+constexpr int ARG_BLOCKS = 32, ARG_THREADS = 256;
+__device__ __forceinline__ bool arg_better(float a, int ai, float b, int bi) { return a > b || (a == b && ai < bi); }
+__global__ void __launch_bounds__(ARG_THREADS) argmax_kernel(const float* v, long long n, int* out, unsigned int* work /* ticket, then ARG_BLOCKS x (value, index) */) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    __shared__ float sv[32];
-    __shared__ int si[32];
+    __shared__ float sv[ARG_THREADS / 32];
+    __shared__ int si[ARG_THREADS / 32];
+    __shared__ int s_last;
     float best = -INFINITY;
     int bi = 0x7fffffff;
-    for (long long i = threadIdx.x; i < n; i += blockDim.x) {
+    const long long per = (n + ARG_BLOCKS - 1) / ARG_BLOCKS;
+    const long long lo = per * blockIdx.x, hi = lo + per < n ? lo + per : n;
+    for (long long i = lo + threadIdx.x; i < hi; i += ARG_THREADS) {
         const float x = v[i];
-        if (x > best || (x == best && (int)i < bi)) {
+        if (arg_better(x, (int)i, best, bi)) {
             best = x;
             bi = (int)i;
         }
@@ -574,7 +580,7 @@ __global__ void argmax_kernel(const float* v, long long n, int* out) {
     for (int o = 16; o > 0; o >>= 1) {
         const float ob = __shfl_xor_sync(0xffffffffu, best, o);
         const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ob > best || (ob == best && oi < bi)) {
+        if (arg_better(ob, oi, best, bi)) {
             best = ob;
             bi = oi;
         }
@@ -585,17 +591,46 @@ __global__ void argmax_kernel(const float* v, long long n, int* out) {
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        for (int w = 1; w < (int)(blockDim.x >> 5); w++)
-            if (sv[w] > best || (sv[w] == best && si[w] < bi)) {
+        for (int w = 1; w < ARG_THREADS / 32; w++)
+            if (arg_better(sv[w], si[w], best, bi)) {
                 best = sv[w];
                 bi = si[w];
             }
-        *out = bi == 0x7fffffff ? 0 : bi;
+        work[1 + 2 * blockIdx.x] = __float_as_uint(best);
+        work[2 + 2 * blockIdx.x] = (unsigned int)bi;
+        __threadfence();
+        const unsigned int t = atomicAdd(work, 1u);
+        s_last = t == gridDim.x - 1;
+        if (s_last) {
+            *work = 0;
+            __threadfence();
+            for (int b = 0; b < (int)gridDim.x; b++) {
+                const float ob = __uint_as_float(__ldcg(work + 1 + 2 * b));
+                const int oi = (int)__ldcg(work + 2 + 2 * b);
+                if (arg_better(ob, oi, best, bi)) {
+                    best = ob;
+                    bi = oi;
+                }
+            }
+            *out = bi == 0x7fffffff ? 0 : bi;
+        }
     }
 }
 
-__global__ void embed_f32_kernel(float* x, const float* table, int dim, const int* d_token, const float* wpe, const int* d_pos) {
+// cos / sin of the token's RoPE angles, once per token (the q/k/v kernels of all layers read the pairs instead of
+// evaluating sincosf in their epilogues)
+__device__ __forceinline__ void rope_pairs(const float* theta, float* cs, int half, const int* d_pos) {
+    if (cs && blockIdx.x == 0 && (int)threadIdx.x < half) {
+        float sn, c;
+        sincosf((float)(*d_pos) * theta[threadIdx.x], &sn, &c);
+        cs[2 * threadIdx.x] = c;
+        cs[2 * threadIdx.x + 1] = sn;
+    }
+}
+__global__ void embed_f32_kernel(float* x, const float* table, int dim, const int* d_token, const float* wpe, const int* d_pos,
+                                 const float* theta, float* cs, int half) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    rope_pairs(theta, cs, half, d_pos);
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= dim) return;
     float y = table[(size_t)(*d_token) * dim + i];
@@ -603,8 +638,9 @@ __global__ void embed_f32_kernel(float* x, const float* table, int dim, const in
     x[i] = y;
 }
 __global__ void embed_q_kernel(float* x, int fmt, const uint8_t* data, int dim, const int* d_token, const float* wpe,
-                               const int* d_pos) {
+                               const int* d_pos, const float* theta, float* cs, int half) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    rope_pairs(theta, cs, half, d_pos);
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= dim) return;
     const long long row = *d_token;
@@ -767,17 +803,18 @@ SLAI_API int slai_argmax(slai_ctx* ctx, const float* d_v, int64_t n, int32_t* d_
 }
 
 int launch_argmax(slai_ctx* ctx, const float* v, int64_t n, int32_t* d_out, bool pdl) {
-    return launch_pdl(ctx, argmax_kernel, dim3(1), dim3(1024), pdl, v, (long long)n, (int*)d_out);
+    return launch_pdl(ctx, argmax_kernel, dim3(ARG_BLOCKS), dim3(ARG_THREADS), pdl, v, (long long)n, (int*)d_out, ctx->d_counters + 1100);
 }
 int launch_embed_f32(slai_ctx* ctx, float* x, const float* table, int dim, const int* d_token, const float* wpe,
-                     const int* d_pos, bool pdl) {
-    return launch_pdl(ctx, embed_f32_kernel, dim3((dim + NT - 1) / NT), dim3(NT), pdl, x, table, dim, d_token, wpe, d_pos);
+                     const int* d_pos, bool pdl, const float* rope_theta, float* rope_cs, int rope_half) {
+    return launch_pdl(ctx, embed_f32_kernel, dim3((dim + NT - 1) / NT), dim3(NT), pdl, x, table, dim, d_token, wpe, d_pos, rope_theta,
+                      rope_cs, rope_half);
 }
 int launch_embed_q8(slai_ctx* ctx, float* x, const slai_qmatrix* wte, const int* d_token, const float* wpe,
-                    const int* d_pos, bool pdl) {
+                    const int* d_pos, bool pdl, const float* rope_theta, float* rope_cs, int rope_half) {
     const int dim = (int)wte->ncols;
     return launch_pdl(ctx, embed_q_kernel, dim3((dim + NT - 1) / NT), dim3(NT), pdl, x, wte->fmt, (const uint8_t*)wte->data, dim,
-                      d_token, wpe, d_pos);
+                      d_token, wpe, d_pos, rope_theta, rope_cs, rope_half);
 }
 int launch_advance(slai_ctx* ctx, int* d_token, int* d_pos, const int32_t* d_next, int32_t* d_history, bool pdl) {
     // d_history[-1] is not used; the step counter lives right after the position scalar (see models)
