@@ -42,7 +42,6 @@ struct slai_ctx {
     size_t scratch_bytes = 0;
     std::vector<RopeTable> rope_tables;
     unsigned int* d_counters = nullptr;  // tickets for "last block finishes" reductions (zeroed)
-    void* d_split_slots = nullptr;       // GEMV hand-over slots: [256 blocks][2][16] (partial sum, tag), zeroed
     // tensor-parallel group (tp.cu): NCCL communicator of this context's rank, null when not sharded
     void* tp_comm = nullptr;
     int tp_rank = 0, tp_size = 1;
@@ -158,7 +157,6 @@ struct GemvLaunch {
     int64_t kv_pos_stride = 0;     // elements between positions
     int64_t kv_head_stride = 0;    // elements between heads
     bool pdl = false;              // launch with programmatic stream serialization
-    bool allow_unit_split = true;  // the blocks may share units instead of whole tiles (needs all blocks resident together)
     const void* prefetch = nullptr;  // what the next kernel reads first (e.g. its norm weights): pulled into L2 meanwhile
     size_t prefetch_bytes = 0;
     // tensor-parallel exchange over peer memory (null: not used)

@@ -46,7 +46,6 @@ struct LayerProg {
         g.nmat = k == 2 ? 2 : 1;
         g.items_base = D.items_base[k];
         g.items_rem = D.items_rem[k];
-        g.units_base = g.units_rem = 0;
         return g;
     }
     __device__ __forceinline__ const uint8_t* tile_ptr(int idx, int item, int mat) const {
@@ -85,7 +84,6 @@ __device__ __forceinline__ GemvParams phase_params(const DecodeParams& D, int l,
     P.n_items = qkv ? (D.dim + 2 * D.kv_dim) >> 4 : gu ? D.hidden >> 4 : D.dim >> 4;
     P.items_base = D.items_base[k];
     P.items_rem = D.items_rem[k];
-    P.units_base = P.units_rem = 0;
     P.seg[0].w = qkv ? W.wq : op ? W.wo : gu ? W.wgate : W.wdown;
     P.seg[0].tile_bytes = dn ? D.tile_bytes_hidden : D.tile_bytes_dim;
     P.seg[0].rows = gu ? D.hidden : D.dim;

@@ -226,24 +226,6 @@ int gemv_fill_params(slai_ctx* ctx, const GemvLaunch& L, size_t dig_region, int 
     const int grid = P.n_items < ctx->sm_count ? P.n_items : ctx->sm_count;
     P.items_base = P.n_items / grid;
     P.items_rem = P.n_items % grid;
-    // Whole items leave some blocks one item short of the others (768 tiles on 148 SMs: 5 or 6; 256 tiles: 1 or 2).
-    // When every block gets at least one item's worth of units (an item then spans at most two neighbouring blocks),
-    // the units are shared equally instead and the items cut at block borders are completed through the hand-over
-    // slots.
-    P.units_base = P.units_rem = 0;
-    P.split_slots = nullptr;
-    static int unit_split = -1;
-    if (unit_split < 0) {
-        const char* e = getenv("SLAI_GEMV_UNIT_SPLIT");
-        unit_split = (e && e[0] == '1') ? 1 : 0;
-    }
-    const long long units = (long long)P.n_items * P.nsteps * P.nmat;
-    if (unit_split && L.allow_unit_split && grid == ctx->sm_count && P.items_rem != 0 && units / grid >= (long long)P.nsteps * P.nmat &&
-        grid <= 256) {
-        P.units_base = (int)(units / grid);
-        P.units_rem = (int)(units % grid);
-        P.split_slots = reinterpret_cast<uint2*>(ctx->d_split_slots);
-    }
     if (grid_out) *grid_out = grid;
     return SLAI_OK;
 }

@@ -49,9 +49,6 @@ struct GemvParams {
     int K;
     int n_items;     // 16-row tiles (nmat == 2: tiles of seg[0])
     int items_base, items_rem;  // items per block of threads: base each, one more for the first `rem`
-    int units_base, units_rem;  // > 0: units per block of threads instead (items cut at block borders are completed
-                                // through `split_slots`)
-    uint2* split_slots;         // [blocks][2 matrices][16 rows] (partial sum, ready tag) handed to the previous block
     int nsteps;      // tile-step blocks per tile
     int nstage;      // ring depth per warp
     int step_bytes;  // bytes of a tile-step block
@@ -405,14 +402,11 @@ __device__ __forceinline__ GemvSeg seg_pick(const GemvParams& P, int s) {
 // one parameter block.
 struct ProgGeom {
     int nsteps, nmat, items_base, items_rem;
-    int units_base, units_rem;  // > 0: the blocks of threads share the *units* equally instead (a tile may then span two blocks)
 };
 struct OneProg {
     const GemvParams& P;
     __device__ __forceinline__ int size() const { return 1; }
-    __device__ __forceinline__ ProgGeom geom(int) const {
-        return ProgGeom{P.nsteps, P.nmat, P.items_base, P.items_rem, P.units_base, P.units_rem};
-    }
+    __device__ __forceinline__ ProgGeom geom(int) const { return ProgGeom{P.nsteps, P.nmat, P.items_base, P.items_rem}; }
     __device__ __forceinline__ const uint8_t* tile_ptr(int, int item, int mat) const {
         const int sidx = P.nmat == 2 ? mat : seg_of_tile(P, item);
         const uint8_t* w = P.seg[0].w;
@@ -433,29 +427,16 @@ struct OneProg {
 // ---------------------------------------------------------------------------------------------
 struct Split {
     int i0, n_local, n_waves, upi, nsteps, nmat;
-    int v_begin, v_end;  // this block's units, counted from the first unit of item i0 (whole items: 0 .. n_local * upi)
 };
 __device__ __forceinline__ Split make_split(const ProgGeom& g) {
     Split s;
     const int b = (int)blockIdx.x;
+    s.i0 = b * g.items_base + min(b, g.items_rem);
+    s.n_local = g.items_base + (b < g.items_rem ? 1 : 0);
+    s.n_waves = (s.n_local + WAVE - 1) / WAVE;
     s.nsteps = g.nsteps;
     s.nmat = g.nmat;
     s.upi = g.nsteps * g.nmat;
-    if (g.units_base > 0) {
-        // equal shares of units: the first and the last item of the share may be cut (two divisions per phase)
-        const int ub = b * g.units_base + min(b, g.units_rem);
-        const int nu = g.units_base + (b < g.units_rem ? 1 : 0);
-        s.i0 = ub / s.upi;
-        s.v_begin = ub - s.i0 * s.upi;
-        s.v_end = s.v_begin + nu;
-        s.n_local = (s.v_end + s.upi - 1) / s.upi;
-    } else {
-        s.i0 = b * g.items_base + min(b, g.items_rem);
-        s.n_local = g.items_base + (b < g.items_rem ? 1 : 0);
-        s.v_begin = 0;
-        s.v_end = s.n_local * s.upi;
-    }
-    s.n_waves = (s.n_local + WAVE - 1) / WAVE;
     return s;
 }
 struct Cursor {
@@ -464,12 +445,9 @@ struct Cursor {
 // Position the cursor on this warp's piece of wave `c.wave`.
 __device__ __forceinline__ void cursor_wave(Cursor& c, const Split& s, int warp) {
     const int items = min(WAVE, s.n_local - c.wave * WAVE);
-    const int w0 = c.wave * WAVE * s.upi;                      // first unit of the wave
-    const int a = max(s.v_begin - w0, 0);                      // the block's units inside the wave: [a, b)
-    const int b = min(s.v_end - w0, items * s.upi);
-    const int U = b - a;
-    c.u = a + (U * warp) / WARPS;
-    c.u1 = a + (U * (warp + 1)) / WARPS;
+    const int U = items * s.upi;
+    c.u = (U * warp) / WARPS;
+    c.u1 = (U * (warp + 1)) / WARPS;
     int rem = c.u;
     c.li = 0;
     while (rem >= s.upi) {  // at most WAVE rounds
@@ -613,7 +591,7 @@ __device__ __forceinline__ void gemv_phase(const GemvParams& P, Ring& R, const P
     LaneCtx L;
     lane_init(L, tid & 31, S);
 
-    const Split sp = make_split(ProgGeom{P.nsteps, NMAT, P.items_base, P.items_rem, P.units_base, P.units_rem});
+    const Split sp = make_split(ProgGeom{P.nsteps, NMAT, P.items_base, P.items_rem});
 
     for (int i = tid; i < WAVE * WARPS * NMAT * 16; i += THREADS) red[i] = 0.f;
     SLAI_TRACE_POINT(2)
@@ -679,40 +657,18 @@ __device__ __forceinline__ void gemv_phase(const GemvParams& P, Ring& R, const P
             const int li = tid >> 4, r = tid & 15;
             const int item = i0 + wv * WAVE + li;
             float val[2] = {0.f, 0.f};
-            // An item cut at a block border: the block holding its tail hands its partial sums to the block holding
-            // its head (it computes them first, the head's owner needs them last), which finishes the rows.
-            const int t_lo = (wv * WAVE + li) * sp.upi;
-            const bool head_cut = t_lo < sp.v_begin, tail_cut = t_lo + sp.upi > sp.v_end;
 #pragma unroll
             for (int mat = 0; mat < 2; mat++)
                 if (mat < NMAT) {
                     float s = 0.f;
 #pragma unroll
                     for (int w = 0; w < WARPS; w++) s += red[((li * WARPS + w) * NMAT + mat) * 16 + r];
-                    if (head_cut) {
-                        P.split_slots[(blockIdx.x * 2 + mat) * 16 + r] = make_uint2(__float_as_uint(s), 1u);
-                    } else if (tail_cut) {
-                        uint2* slot = P.split_slots + ((blockIdx.x + 1) * 2 + mat) * 16 + r;
-                        uint2 got;
-                        for (int it = 0;; it++) {
-                            asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(got.x), "=r"(got.y) : "l"(slot) : "memory");
-                            if (got.y == 1u) break;
-                            if (it > (1 << 20)) {
-                                atomicExch(P.err_flag, 4u);
-                                got.x = 0u;
-                                break;
-                            }
-                            if (it > 16) __nanosleep(100);
-                        }
-                        *slot = make_uint2(0u, 0u);  // empty again for the next launch
-                        s += __uint_as_float(got.x);
-                    }
                     val[mat] = s * inv_scale;
                 }
             const int sidx = NMAT == 2 ? 0 : seg_of_tile(P, item);
             const GemvSeg sg = seg_pick(P, sidx);
             const int row_in_seg = (NMAT == 2 ? item : item - sg.tile0) * 16 + r;
-            const bool valid = row_in_seg < sg.rows && !head_cut;  // a head-cut item is finished by the previous block
+            const bool valid = row_in_seg < sg.rows;
             const int orow = sg.out_off + row_in_seg;
             const float bias = (sg.bias && valid) ? sg.bias[row_in_seg] : 0.f;
             if (SLAI_EPI_IS(EPI_STORE)) {

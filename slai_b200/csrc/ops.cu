@@ -57,8 +57,7 @@ SLAI_API int slai_ctx_create(int device, slai_ctx** out) {
     if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaEventCreate(&ctx->ev0) != cudaSuccess || cudaEventCreate(&ctx->ev1) != cudaSuccess ||
         cudaMalloc(&ctx->d_counters, 4096 * sizeof(unsigned int)) != cudaSuccess ||
-        cudaMemset(ctx->d_counters, 0, 4096 * sizeof(unsigned int)) != cudaSuccess ||
-        cudaMalloc(&ctx->d_split_slots, 256 * 2 * 16 * 8) != cudaSuccess || cudaMemset(ctx->d_split_slots, 0, 256 * 2 * 16 * 8) != cudaSuccess) {
+        cudaMemset(ctx->d_counters, 0, 4096 * sizeof(unsigned int)) != cudaSuccess) {
         delete ctx;
         return SLAI_ERR_CUDA;
     }
@@ -75,7 +74,6 @@ SLAI_API int slai_ctx_destroy(slai_ctx* ctx) {
     for (auto& t : ctx->rope_tables) cudaFree(t.d_theta);
     if (ctx->d_scratch) cudaFree(ctx->d_scratch);
     if (ctx->d_counters) cudaFree(ctx->d_counters);
-    if (ctx->d_split_slots) cudaFree(ctx->d_split_slots);
     cudaEventDestroy(ctx->ev0);
     slai_tp_shutdown(ctx);
     cudaEventDestroy(ctx->ev1);
@@ -93,7 +91,7 @@ SLAI_API int slai_ctx_sync(slai_ctx* ctx) {
     if (flag) {
         cudaMemset(ctx->d_counters + 3000, 0, sizeof(flag));
         return slai_set_error(ctx, SLAI_ERR_TIMEOUT, "a bounded wait inside a kernel ran out (%s); results of the last launches are invalid",
-                              flag == 1 ? "weight ring" : flag == 2 ? "grid barrier" : flag == 3 ? "tensor-parallel peer" : "neighbouring block");
+                              flag == 1 ? "weight ring" : flag == 2 ? "grid barrier" : "tensor-parallel peer");
     }
     return SLAI_OK;
 }
