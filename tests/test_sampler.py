@@ -134,10 +134,10 @@ def test_generate_sampled_follows_the_oracle(backend):
     from slai_b200 import _lib, synth
     from slai_b200.models import Llama2Config, llama_from_host, sample_coin, synthetic_llama_host
     cfg = Llama2Config(dim=256, hidden_dim=512, n_layers=2, n_q_heads=4, n_kv_heads=4, vocab_size=800, seq_len=64, kv_dtype=_lib.KV_F32)
-    w = synthetic_llama_host(cfg, synth.FMT_Q8_0, seed=21, std=0.08, embd_std=1.0)
+    w = synthetic_llama_host(cfg, synth.FMT_Q8_0, seed=21, std=0.2, embd_std=1.0)
     m = llama_from_host(backend, cfg, w, synth.FMT_Q8_0)
     ref = oracle_llama(cfg, w, synth.FMT_Q8_0, nthreads=2)
-    temperature, topp, seed, n = 0.9, 0.9, 1234, 24
+    temperature, topp, seed, n = 0.3, 0.8, 1234, 24   # peaked enough that every draw is pinned (checked with the oracle)
     got = m.generate_sampled(7, 0, n, temperature, topp, seed)
     again = m.generate_sampled(7, 0, n, temperature, topp, seed)
     assert list(got) == list(again)                     # seeded: reproducible
@@ -154,4 +154,4 @@ def test_generate_sampled_follows_the_oracle(backend):
         assert got[step] == want, step
         agree += 1
         tok = want
-    assert agree >= 4
+    assert agree >= 12
