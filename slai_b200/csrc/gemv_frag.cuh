@@ -55,12 +55,22 @@ SLAI_HD void scale_min_k4(int j, uint32_t s0, uint32_t s1, uint32_t s2, uint32_t
 
 // ---- activation digits -------------------------------------------------------------------------
 // V (|V| <= 2^26) -> four balanced base-128 digits, most significant first.
+// low seven bits of V as a signed number in [-64, 63] (the balanced digit V mod 128)
+SLAI_HD int low7(int V) {
+#ifdef __CUDA_ARCH__
+    int d;
+    asm("bfe.s32 %0, %1, 0, 7;" : "=r"(d) : "r"(V));
+    return d;
+#else
+    return ((V + 64) & 127) - 64;
+#endif
+}
 SLAI_HD void split_digits(int V, int (&d)[4]) {
-    d[3] = ((V + 64) & 127) - 64;
+    d[3] = low7(V);
     V = (V - d[3]) >> 7;
-    d[2] = ((V + 64) & 127) - 64;
+    d[2] = low7(V);
     V = (V - d[2]) >> 7;
-    d[1] = ((V + 64) & 127) - 64;
+    d[1] = low7(V);
     V = (V - d[1]) >> 7;
     d[0] = V;
 }

@@ -356,10 +356,11 @@ __device__ __forceinline__ float stage_vector(const int PRO_ARG, const GemvParam
         int sd[4];
 #pragma unroll
         for (int q = 0; q < 4; q++) {
-            const uint32_t word = (uint32_t)(d0[q] & 0xFF) | ((uint32_t)(d1[q] & 0xFF) << 8) | ((uint32_t)(d2[q] & 0xFF) << 16) |
-                                  ((uint32_t)(d3[q] & 0xFF) << 24);
+            // low bytes of the four digits, packed with byte permutes; their sum with one dot-product instruction
+            const uint32_t lo = __byte_perm((uint32_t)d0[q], (uint32_t)d1[q], 0x0040), hi = __byte_perm((uint32_t)d2[q], (uint32_t)d3[q], 0x0040);
+            const uint32_t word = __byte_perm(lo, hi, 0x5410);
             *reinterpret_cast<uint32_t*>(dig + (size_t)q * S.plane + 4 * i) = word;
-            sd[q] = (d0[q] + d1[q]) + (d2[q] + d3[q]);
+            sd[q] = __dp4a((int)word, 0x01010101, 0);
         }
         if (SV_GRAN > 0) {
 #pragma unroll
