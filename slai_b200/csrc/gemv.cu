@@ -212,14 +212,19 @@ int gemv_fill_params(slai_ctx* ctx, const GemvLaunch& L, size_t dig_region, int 
     const size_t per_stage = (size_t)WARPS * P.stage_stride;
     if (nstage <= 0) {
         SLAI_REQUIRE(ctx, fixed + 2 * per_stage <= SMEM_LIMIT, SLAI_ERR_SHAPE, "gemv: K=%d does not fit in shared memory", K);
-        nstage = (int)((SMEM_LIMIT - fixed) / per_stage);
-        if (nstage > 6) nstage = 6;
+        const int fit = (int)((SMEM_LIMIT - fixed) / per_stage);
+        // Two stages in flight per warp for the K-quants (three otherwise) measured fastest: a deeper first fill asks for
+        // most of the matrix at once and delays the activation loads of the staging pass behind it.
+        const bool kquant = L.fmt == SLAI_FMT_Q4_K || L.fmt == SLAI_FMT_Q5_K || L.fmt == SLAI_FMT_Q6_K;
+        nstage = kquant ? 2 : 3;
         static int stage_env = -1;
         if (stage_env < 0) {
             const char* e = getenv("SLAI_GEMV_STAGES");
             stage_env = e ? atoi(e) : 0;
         }
-        if (stage_env >= 2 && stage_env <= nstage) nstage = stage_env;
+        if (stage_env >= 2) nstage = stage_env;
+        if (nstage > fit) nstage = fit;
+        if (nstage > MAX_STAGES) nstage = MAX_STAGES;
     }
     P.nstage = nstage;
     if (smem_out) *smem_out = fixed + (size_t)nstage * per_stage;
