@@ -302,6 +302,10 @@ def run_tp(args, group):
     PL = args.prompt_len
     rng = np.random.default_rng(42)
     prompt = rng.integers(0, cfg.vocab_size, size=PL).astype(np.int32)
+    # The peer exchange waits a bounded time (about a second) for the other ranks' partial sums: start the first step together,
+    # not whenever each rank has finished building its shard.
+    backend.synchronize()
+    group.barrier()
     m.prefill(prompt[:-1], 0)
     tok, pos = int(prompt[-1]), PL - 1
     warm = m.generate(tok, pos, W)

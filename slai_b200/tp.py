@@ -85,7 +85,10 @@ def join_group(backend: Backend, rank: int, size: int, broadcast) -> None:
 def enable_peer_exchange(backend: Backend, size: int, all_gather, barrier) -> None:
     """Collective.  Maps every rank's exchange region into every other rank (CUDA IPC over NVLink peer access): the
     per-half-layer sums then need no collective kernel.  `all_gather(obj)` returns the list of all ranks' objects in
-    rank order; `barrier()` returns when every rank has called it."""
+    rank order; `barrier()` returns when every rank has called it.
+
+    The kernels wait a bounded time (about a second) for a peer's partial sums, then raise the context's error flag:
+    call a host barrier after loading the weights, before the first decode step, so that the ranks start together."""
     buf = (C.c_ubyte * TP_HANDLE_BYTES)()
     backend.check(backend.lib.slai_tp_peer_export(backend.h, buf))
     handles = all_gather(bytes(buf))
