@@ -32,6 +32,14 @@ PROMPT_LEN = 512
 WORKLOAD = "llama2-7b-arch q4_k (q6_k logits) bs1 decode, 512-token prompt, fp16 KV (the headline benchmark configuration)"
 
 
+def workload_config(world: int, steps: int, warmup: int) -> dict:
+    """The `config` object of the JSON line, identical for the CUDA arm and the reference arm."""
+    first = PROMPT_LEN - 1 + warmup
+    return {"workload": WORKLOAD, "prompt_len": PROMPT_LEN, "decode_positions": [first, first + steps - 1],
+            "parallelism": "single GPU" if world == 1 else f"replicas x{world} (path does not shard at this model size)",
+            "l2": "every token streams 3.75 GB of weights, far larger than the 126 MB L2 (no flush needed)"}
+
+
 def measured_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -114,8 +122,10 @@ def build_model(backend, seed=0):
     return cfg, m, mats, raw
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of gemv_kernel<Q4_K> on 11008x4096, from the committed ncu capture
-DOMINANT_KERNEL_DRAM_BYTES = 25_414_400
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of gemv_kernel<Q4_K> on 11008x4096 from an ncu capture of
+# `python -m slai_b200.microbench --fmt q4_k --M 11008 --K 4096 --copies 8` (688 tiles x 16 steps x 2368-byte blocks = 26 068 992
+# bytes of weights, the 2.8 % above the GGUF byte count being the unpacked scales, plus the input vector)
+DOMINANT_KERNEL_DRAM_BYTES = 26_121_000
 
 
 def time_dominant_kernel(backend, ctx, cfg, mats, rounds=8):
@@ -176,57 +186,72 @@ def gemv_microbench(backend, ctx, peak):
     return res
 
 
-def cpu_layer_times(cfg, raw, pos, nthreads, reps=2):
-    """The reference's CPU path on layer 0 and the logits matrix of the benchmark model: weights dequantised to
-    f32 at load (models/llama2/cpu.rs:200-219), dense f32 gemv per matrix (:370-376), attention over `pos`+1
-    positions.  Returns (seconds per layer, seconds for the logits gemv)."""
-    from oracle import oracle as O
+def host_layer_blocks(cfg, seed=0):
+    """Layer 0 and the logits matrix of the benchmark model as raw GGUF blocks made on the host (numpy quantisers of
+    slai_b200/synth.py): what the reference arm runs on, with no GPU and no CUDA library involved."""
     from slai_b200 import synth
-    shapes = cfg.matrix_shapes()
-    W = {}
-    for name, (r, c) in shapes.items():
-        W[name] = O.dequantize(synth.FMT_Q4_K, raw[name].raw.to_numpy()).reshape(r, c)
-    Wout = O.dequantize(synth.FMT_Q6_K, raw["output"].raw.to_numpy()).reshape(cfg.vocab_size, cfg.dim)
-    rng = np.random.default_rng(0)
-    x = rng.standard_normal(cfg.dim).astype(np.float32)
-    ones = np.ones(cfg.dim, np.float32)
-    kc = rng.standard_normal((pos + 1, cfg.kv_dim)).astype(np.float32)
-    vc = rng.standard_normal((pos + 1, cfg.kv_dim)).astype(np.float32)
-    best_layer, best_out = 1e9, 1e9
-    for _ in range(reps):
-        t0 = time.perf_counter()
-        xb = O.rms_norm(x, ones, cfg.rms_norm_eps)
-        q = O.gemv_f32(W["wq"], xb, nthreads)
-        k = O.gemv_f32(W["wk"], xb, nthreads)
-        v = O.gemv_f32(W["wv"], xb, nthreads)
-        q, k = O.rope(q, k, cfg.head_size, cfg.kv_dim, pos)
-        kc[pos], vc[pos] = k, v
-        att, _ = O.attention(q, kc, vc, seq_len=pos + 1, kv_dim=cfg.kv_dim, kv_mul=1, n_heads=cfg.n_q_heads, head_size=cfg.head_size, pos=pos)
-        x2 = x + O.gemv_f32(W["wo"], att, nthreads)
-        xb = O.rms_norm(x2, ones, cfg.rms_norm_eps)
-        hb = O.silu_gate(O.gemv_f32(W["w_gate"], xb, nthreads), O.gemv_f32(W["w_up"], xb, nthreads))
-        x2 = x2 + O.gemv_f32(W["w_down"], hb, nthreads)
-        t1 = time.perf_counter()
-        logits = O.gemv_f32(Wout, O.rms_norm(x2, ones, cfg.rms_norm_eps), nthreads)
-        t2 = time.perf_counter()
-        best_layer, best_out = min(best_layer, t1 - t0), min(best_out, t2 - t1)
-    return best_layer, best_out
+    raw = {}
+    for i, (name, (r, c)) in enumerate(cfg.matrix_shapes().items()):
+        raw[name] = synth.quantize(synth.FMT_Q4_K, synth.normal_matrix(seed * 1_000_003 + i + 1, r, c, 0.02))
+    raw["output"] = synth.quantize(synth.FMT_Q6_K, synth.normal_matrix(seed * 1_000_003 + 7_000_002, cfg.vocab_size, cfg.dim, 0.02))
+    return raw
+
+
+class CpuLayer:
+    """The reference's CPU path on layer 0 and the logits matrix of the benchmark model: weights dequantised to f32
+    at load (models/llama2/cpu.rs:200-219), dense f32 gemv per matrix (:370-376), attention over `pos`+1 positions."""
+
+    def __init__(self, cfg, raw_blocks):
+        from oracle import oracle as O
+        from slai_b200 import synth
+        self.cfg = cfg
+        self.W = {name: O.dequantize(synth.FMT_Q4_K, raw_blocks[name]).reshape(r, c) for name, (r, c) in cfg.matrix_shapes().items()}
+        self.Wout = O.dequantize(synth.FMT_Q6_K, raw_blocks["output"]).reshape(cfg.vocab_size, cfg.dim)
+        rng = np.random.default_rng(0)
+        self.x = rng.standard_normal(cfg.dim).astype(np.float32)
+        self.kc = rng.standard_normal((cfg.seq_len, cfg.kv_dim)).astype(np.float32)
+        self.vc = rng.standard_normal((cfg.seq_len, cfg.kv_dim)).astype(np.float32)
+
+    def times(self, pos, nthreads, reps=2):
+        """(seconds per layer, seconds for the logits gemv), best of `reps`."""
+        from oracle import oracle as O
+        cfg, W, x = self.cfg, self.W, self.x
+        ones = np.ones(cfg.dim, np.float32)
+        kc, vc = self.kc[: pos + 1], self.vc[: pos + 1]
+        best_layer, best_out = 1e9, 1e9
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            xb = O.rms_norm(x, ones, cfg.rms_norm_eps)
+            q = O.gemv_f32(W["wq"], xb, nthreads)
+            k = O.gemv_f32(W["wk"], xb, nthreads)
+            v = O.gemv_f32(W["wv"], xb, nthreads)
+            q, k = O.rope(q, k, cfg.head_size, cfg.kv_dim, pos)
+            kc[pos], vc[pos] = k, v
+            att, _ = O.attention(q, kc, vc, seq_len=pos + 1, kv_dim=cfg.kv_dim, kv_mul=1, n_heads=cfg.n_q_heads, head_size=cfg.head_size, pos=pos)
+            x2 = x + O.gemv_f32(W["wo"], att, nthreads)
+            xb = O.rms_norm(x2, ones, cfg.rms_norm_eps)
+            hb = O.silu_gate(O.gemv_f32(W["w_gate"], xb, nthreads), O.gemv_f32(W["w_up"], xb, nthreads))
+            x2 = x2 + O.gemv_f32(W["w_down"], hb, nthreads)
+            t1 = time.perf_counter()
+            O.gemv_f32(self.Wout, O.rms_norm(x2, ones, cfg.rms_norm_eps), nthreads)
+            t2 = time.perf_counter()
+            best_layer, best_out = min(best_layer, t1 - t0), min(best_out, t2 - t1)
+        return best_layer, best_out
 
 
 def run_reference(args, rank, world):
     """Reference arm: the reference's CPU implementation of the path (the oracle port; the Rust reference cannot be
     built here) with all host threads, on a bounded sample per step: one full layer + the logits GEMV of the same
-    model, extrapolated to 32 layers."""
+    model shape, extrapolated to 32 layers.  Runs on the host alone: the CUDA library is not loaded."""
     if rank != 0:
         return
-    from slai_b200.ops import Backend
-    backend = Backend(0)
-    cfg, m, mats, raw = build_model(backend)
+    from slai_b200.models import LLAMA2_7B
+    cfg = LLAMA2_7B
+    layer = CpuLayer(cfg, host_layer_blocks(cfg))
     nthreads = os.cpu_count() or 1
-    pos = PROMPT_LEN
     times = []
     for i in range(args.warmup + args.steps):
-        tl, to = cpu_layer_times(cfg, raw, pos + i, nthreads, reps=1)
+        tl, to = layer.times(PROMPT_LEN - 1 + i, nthreads, reps=1)
         if i >= args.warmup:
             times.append(cfg.n_layers * tl + to)
     ms = 1e3 * float(np.mean(times))
@@ -234,7 +259,7 @@ def run_reference(args, rank, world):
     line = {"impl": "reference", "metric": "decode tok/s bs1 (Llama-2-7B Q4_K)", "value": val, "unit": "tok/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "prompt_len": PROMPT_LEN},
+            "config": workload_config(world, args.steps, args.warmup),
             "cpu_baseline": {"value": val, "unit": "tok/s", "cores": nthreads, "kind": "port",
                              "sample": "per step: one full layer (7 dense f32 gemvs on dequantised weights, attention over the "
                                        "prompt) + the logits gemv on the host, layer time x32"},
@@ -277,36 +302,66 @@ def run_gpt2(args):
     print(json.dumps(line), flush=True)
 
 
-def run_tp(args, group):
-    """The 70B benchmark configuration (Llama-2-70B architecture, Q4_K + Q6_K logits, fp16 KV, batch 1) sharded over all ranks:
-    tensor parallel, one all-reduce per half-layer.  Not the default workload: `--tp`."""
+def _tp_bit_identity(backend, group, cfg70):
+    """Two layers of the 70B shape decoded twice, the half-layer sums once through NCCL all-reduce and once through
+    the peer-memory exchange inside the GEMV kernels: same logits bit for bit and same greedy ids."""
+    from slai_b200 import synth, tp
+    from slai_b200.models import Llama2Config
+    small = Llama2Config(**{**cfg70.__dict__, "n_layers": 2, "seq_len": 64})
+    res = []
+    for force_nccl in (True, False):
+        if force_nccl:
+            os.environ["SLAI_TP_NCCL"] = "1"
+        else:
+            os.environ.pop("SLAI_TP_NCCL", None)
+        m = tp.synthetic_llama_device_tp(backend, small, synth.FMT_Q4_K, synth.FMT_Q6_K, group.rank, group.world, seed=3)
+        backend.synchronize()
+        group.barrier()
+        lg, _ = m.forward_logits(0, 11)
+        ids = list(m.generate(12, 1, 16))
+        res.append((lg.copy(), ids))
+        m.close()
+    os.environ.pop("SLAI_TP_NCCL", None)
+    same = bool(np.array_equal(res[0][0].view(np.uint32), res[1][0].view(np.uint32)) and res[0][1] == res[1][1])
+    (agree,) = group.sum_over_ranks([1.0 if same else 0.0])
+    return agree == group.world
+
+
+def measure_tp(args, group, n_layers=0, prompt_len=1024, steps=None, warmup=None, nccl_only=False):
+    """The 70B benchmark configuration (Llama-2-70B architecture, Q4_K + Q6_K logits, fp16 KV, batch 1, 1024-token
+    prompt) sharded over all ranks: tensor parallel, one sum per half-layer, logits matrix sharded by rows.  Returns the
+    record rank 0 reports (None on the other ranks).  At one rank it is the unsharded model on one GPU."""
     from slai_b200 import synth, tp
     from slai_b200.models import LLAMA2_70B, Llama2Config
     from slai_b200.ops import Backend
     rank, world = group.rank, group.world
     backend = Backend(group.local_rank)
-    cfg = LLAMA2_70B if args.tp_layers <= 0 else Llama2Config(**{**LLAMA2_70B.__dict__, "n_layers": args.tp_layers})
-    exchange = "none"
+    cfg = LLAMA2_70B if n_layers <= 0 else Llama2Config(**{**LLAMA2_70B.__dict__, "n_layers": n_layers})
+    K = steps or min(args.steps, 64)
+    W = warmup or max(3, min(args.warmup, 8))
+    exchange, identical = "none (one GPU)", None
     if world > 1:
         tp.join_group(backend, rank, world, tp.torch_broadcast)
         exchange = "NCCL all-reduce of 8192 f32 after wo and w_down"
-        if not args.tp_nccl:
+        if not nccl_only:
             tp.enable_peer_exchange(backend, world, tp.torch_all_gather, tp.torch_barrier)
             exchange = "peer-memory stores from the wo / w_down kernels, summed in the next kernel's prologue (no collective kernel)"
+            identical = _tp_bit_identity(backend, group, cfg)
         m = tp.synthetic_llama_device_tp(backend, cfg, synth.FMT_Q4_K, synth.FMT_Q6_K, rank, world)
     else:
         from slai_b200.models import synthetic_llama_device
         m = synthetic_llama_device(backend, cfg, synth.FMT_Q4_K, synth.FMT_Q6_K)
     peak, peak_src = measured_peaks()
-    K, W = args.steps, args.warmup
-    PL = args.prompt_len
+    PL = prompt_len
     rng = np.random.default_rng(42)
     prompt = rng.integers(0, cfg.vocab_size, size=PL).astype(np.int32)
     # The peer exchange waits a bounded time (about a second) for the other ranks' partial sums: start the first step together,
     # not whenever each rank has finished building its shard.
     backend.synchronize()
     group.barrier()
+    t0 = time.perf_counter()
     m.prefill(prompt[:-1], 0)
+    prefill_s = time.perf_counter() - t0
     tok, pos = int(prompt[-1]), PL - 1
     warm = m.generate(tok, pos, W)
     tok, pos = int(warm[-1]), pos + W
@@ -319,24 +374,36 @@ def run_tp(args, group):
     group.barrier()
     clocks = sampler.stop()
     ids = group.gather_ids(toks)
-    (ms,) = group.max_over_ranks([ms])
+    ms, prefill_s = group.max_over_ranks([ms, prefill_s])
+    rec = None
     if rank == 0:
         per_rank = tp.bytes_per_token_per_rank(cfg, synth.FMT_Q4_K, synth.FMT_Q6_K, world)
         kv = float(np.mean([cfg.kv_bytes_at(p) for p in range(pos, pos + K)])) / world
         t = ms * 1e-3 / K
-        line = {"metric": "decode tok/s bs1 (Llama-2-70B Q4_K, tensor parallel)", "value": K / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
-                "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-                "dtype": "f32", "data": "synthetic (shards seeded per rank)",
-                "config": {"workload": "llama2-70b-arch q4_k (q6_k logits) bs1 decode, fp16 KV", "n_layers": cfg.n_layers,
-                           "prompt_len": PL, "parallelism": f"tp{world}", "exchange": exchange},
-                "clocks": clocks, "launches_per_token": m.launches_per_token(), "gpu_launches": m.launches_per_token() * K,
-                "ranks_agree": all(r == ids[0] for r in ids),
-                "roofline": {"bound": "hbm", "per_gpu_bytes_per_token": per_rank + kv, "achieved": (per_rank + kv) / t / 1e9, "peak": peak,
-                             "unit": "GB/s", "frac": (per_rank + kv) / t / 1e9 / peak, "peak_source": peak_src}}
-        print(json.dumps(line), flush=True)
+        rec = {"metric": "decode tok/s bs1 (Llama-2-70B Q4_K, tensor parallel)", "value": K / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
+               "steps": K, "warmup": W, "ms_per_step": ms / K, "scaling": "strong",
+               "config": {"workload": "llama2-70b-arch q4_k (q6_k logits) bs1 decode, fp16 KV", "n_layers": cfg.n_layers,
+                          "prompt_len": PL, "decode_positions": [pos, pos + K - 1], "parallelism": f"tp{world}", "exchange": exchange,
+                          "logits": "output matrix sharded by rows, logits all-gathered" if world > 1 else "whole output matrix"},
+               "prefill_s": prefill_s, "prefill": "sequential single-token steps",
+               "clocks": clocks, "launches_per_token": m.launches_per_token(), "gpu_launches": m.launches_per_token() * K,
+               "ranks_agree": all(r == ids[0] for r in ids), "nccl_and_peer_exchange_bit_identical": identical,
+               "roofline": {"bound": "hbm", "per_gpu_bytes_per_token": per_rank + kv, "achieved": (per_rank + kv) / t / 1e9, "peak": peak,
+                            "unit": "GB/s", "frac": (per_rank + kv) / t / 1e9 / peak, "peak_source": peak_src}}
     m.close()
     if world > 1:
         backend.check(backend.lib.slai_tp_shutdown(backend.h))
+    backend.close()
+    return rec
+
+
+def run_tp(args, group):
+    """`--tp`: only the sharded 70B measurement, as the one JSON line."""
+    rec = measure_tp(args, group, n_layers=args.tp_layers, prompt_len=args.prompt_len if args.prompt_len != 512 else 1024,
+                     steps=args.steps, warmup=args.warmup, nccl_only=args.tp_nccl)
+    if rec is not None:
+        rec.update({"higher_is_better": True, "vs_baseline": None, "dtype": "f32", "data": "synthetic (shards seeded per rank)"})
+        print(json.dumps(rec), flush=True)
     group.close()
 
 
@@ -355,6 +422,7 @@ def main():
     ap.add_argument("--tp", action="store_true", help="Llama-2-70B architecture sharded over all ranks instead of 7B replicas")
     ap.add_argument("--tp-layers", type=int, default=0, help="with --tp: fewer layers than 80 (0 = the full model)")
     ap.add_argument("--tp-nccl", action="store_true", help="with --tp: exchange through NCCL all-reduce instead of peer memory")
+    ap.add_argument("--no-tp", action="store_true", help="skip the sharded 70B measurement that the default run attaches as `tp`")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     global PROMPT_LEN
@@ -425,6 +493,30 @@ def main():
     barrier()
 
     ms, e2e_s = group.max_over_ranks([ms, e2e_s])
+    algo, per, nl = time_dominant_kernel(backend, ctx, cfg, mats) if rank == 0 else (0, 1.0, 0)
+    launches_per_token = m.launches_per_token()
+    backend.lib.slai_free_host(backend.h, pinned)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        nthreads = os.cpu_count() or 1
+        layer = CpuLayer(cfg, {name: qm.raw.to_numpy() for name, qm in raw.items()})  # the very bytes the GPU model holds
+        tl, to = layer.times(PROMPT_LEN, nthreads, reps=2)
+        tl1, to1 = layer.times(PROMPT_LEN, 1, reps=1)
+        cpu = {"value": 1.0 / (cfg.n_layers * tl + to), "unit": "tok/s", "cores": nthreads, "kind": "port",
+               "single_thread_value": 1.0 / (cfg.n_layers * tl1 + to1),
+               "sample": "one full layer (f32-dequantised weights, 7 dense gemvs, attention over 513 positions) "
+                         "+ the logits gemv of the same model on the host; token time = 32 x layer + logits"}
+        del layer
+    gemv_table = gemv_microbench(backend, ctx, peak) if (rank == 0 and args.gemv) else None
+    # The 7B path does not shard; the path that does (the 70B configuration) is measured next, over the same ranks, and
+    # attached to the line: one model split over the GPUs, strong scaling.
+    del m, mats, raw
+    tp_rec = None
+    if not args.no_tp:
+        try:
+            tp_rec = measure_tp(args, group)
+        except Exception as e:  # the headline line is still reported
+            tp_rec = {"error": f"{type(e).__name__}: {e}"}
 
     if rank == 0:
         value = world * K / (ms * 1e-3)
@@ -433,37 +525,29 @@ def main():
         kv_mean = float(np.mean([cfg.kv_bytes_at(p) for p in range(pos_first, pos_last + 1)]))
         small = (2 * cfg.n_layers + 1) * cfg.dim * 4 + cfg.dim * 4
         token_bytes = wbytes + kv_mean + small
-        algo, per, nl = time_dominant_kernel(backend, ctx, cfg, mats)
         line = {
             "metric": "decode tok/s bs1 (Llama-2-7B Q4_K)", "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "prompt_len": PROMPT_LEN, "decode_positions": [pos_first, pos_last],
-                       "parallelism": "single GPU" if world == 1 else f"replicas x{world} (path does not shard at this model size)",
-                       "l2": "every token streams 3.75 GB of weights, far larger than the 126 MB L2 (no flush needed)"},
+            "config": workload_config(world, K, W),
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 16, "d2h_bytes_per_step": cfg.vocab_size * 4 + 4},
-            "gpu_launches": m.launches_per_token() * K,
-            "launches_per_token": m.launches_per_token(),
+            "gpu_launches": launches_per_token * K,
+            "launches_per_token": launches_per_token,
             "token_roofline": {"bytes_per_token": token_bytes, "roofline_tok_s": peak * 1e9 / token_bytes,
                                "frac": (value / world) / (peak * 1e9 / token_bytes), "peak_source": peak_src},
             "roofline": {"bound": "hbm", "kernel": "gemv_kernel<Q4K> 11008x4096 (all 32 gate matrices in turn, 813 MB > L2)",
                          "achieved": algo / per / 1e9, "peak": peak, "unit": "GB/s", "frac": algo / per / 1e9 / peak,
                          "traffic": DOMINANT_KERNEL_DRAM_BYTES, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of this "
-                         "kernel on this shape (profiles/gemv_q4k_11008x4096_ncu_full.md); algorithmic bytes %d" % algo,
+                         "kernel on this shape (one captured launch of the GEMV microbenchmark); algorithmic bytes %d" % algo,
                          "launches_timed": nl, "us_per_launch": per * 1e6, "peak_source": peak_src},
         }
-        if args.gemv:
-            line["gemv_microbench"] = gemv_microbench(backend, ctx, peak)
-        if world == 1 and not args.no_cpu:
-            nthreads = os.cpu_count() or 1
-            tl, to = cpu_layer_times(cfg, raw, PROMPT_LEN, nthreads, reps=2)
-            tl1, to1 = cpu_layer_times(cfg, raw, PROMPT_LEN, 1, reps=1)
-            line["cpu_baseline"] = {"value": 1.0 / (cfg.n_layers * tl + to), "unit": "tok/s", "cores": nthreads, "kind": "port",
-                                    "single_thread_value": 1.0 / (cfg.n_layers * tl1 + to1),
-                                    "sample": "one full layer (f32-dequantised weights, 7 dense gemvs, attention over 513 positions) "
-                                              "+ the logits gemv of the same model on the host; token time = 32 x layer + logits"}
+        if gemv_table is not None:
+            line["gemv_microbench"] = gemv_table
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        if tp_rec is not None:
+            line["tp"] = tp_rec
         print(json.dumps(line), flush=True)
-    backend.lib.slai_free_host(backend.h, pinned)
     group.close()
 
 

@@ -69,11 +69,17 @@ int slai_ctx_destroy(slai_ctx* ctx);
  * inside a kernel (weight ring, grid barrier) ran out since the last call: every device-side wait has an
  * iteration limit and raises a flag instead of hanging. */
 int slai_ctx_sync(slai_ctx* ctx);
+/* Rounds a device-side wait polls before it gives up (default 2^20, about a second).  No counterpart in the
+ * reference, whose dispatches never wait on one another.  Applies to launches described after the call; a host
+ * that supervises its ranks itself can shorten it to detect a missing peer sooner.  rounds >= 16. */
+int slai_ctx_set_wait_limit(slai_ctx* ctx, uint32_t rounds);
 const char* slai_last_error_string(slai_ctx* ctx);
 void* slai_ctx_stream(slai_ctx* ctx); /* the cudaStream_t all work of this context is enqueued on */
 int slai_device_count(void);
 /* Device name and number of SMs of the context's GPU. */
 int slai_ctx_device_info(slai_ctx* ctx, char* name, int name_len, int* sm_count);
+/* Free and total bytes of the context's GPU (cudaMemGetInfo). */
+int slai_ctx_mem_info(slai_ctx* ctx, size_t* free_bytes, size_t* total_bytes);
 
 /* ---- buffers: Backend::write_buffer / read_buffer (slang-hal, used at chat_llama2.rs:180-230) ------- */
 int slai_malloc(slai_ctx* ctx, size_t bytes, void** d_out);
@@ -102,7 +108,8 @@ int slai_pass_destroy(slai_ctx* ctx, slai_pass* pass);
 /* One process (or thread) per GPU, one context each.  Rank 0 asks for an id, the host program hands the 128 bytes
  * to the other ranks by any means (a torch.distributed / MPI broadcast, a file), every rank calls slai_tp_init
  * (collective: returns when all ranks have joined).  Models created afterwards with tp_size > 1 in their
- * configuration take weights that the caller has already sharded and exchange one sum
+ * configuration take weights that the caller has already sharded (column-parallel matrices by rows, row-parallel
+ * ones by columns on block boundaries, each rank its own KV heads) and exchange one sum
  * of `dim` floats after the attention output projection and after the FFN down projection of every layer
  * (NCCL all-reduce over NVLink on the context's stream). */
 #define SLAI_TP_ID_BYTES 128
@@ -119,6 +126,21 @@ int slai_tp_shutdown(slai_ctx* ctx);                                          /*
 #define SLAI_TP_HANDLE_BYTES 64
 int slai_tp_peer_export(slai_ctx* ctx, void* h_handle);            /* h_handle: SLAI_TP_HANDLE_BYTES bytes out; blocking */
 int slai_tp_peer_attach(slai_ctx* ctx, const void* h_handles);     /* tp_size x SLAI_TP_HANDLE_BYTES bytes, rank order */
+/* The two operators a caller that assembles its own sharded transformer needs (the models use them internally; no
+ * counterpart in the reference).  `index` numbers the exchanges inside one token (0 .. per_token-1, alternating
+ * buffers), slai_tp_token_tick starts a new token.
+ *  - slai_gemv_quant_partial: this rank's partial of a row-parallel product, W v (+ d_resid on rank 0), stored as
+ *    (value, tag) pairs into every rank's region from the kernel's epilogue.
+ *  - slai_gemv_quant_reduced: d_out = W rmsnorm(s) where s = the sum over ranks of exchange `index`, formed while
+ *    the kernel stages its input (bounded polls on the tags); s is also left in d_sum_out (ncols floats). */
+int slai_tp_token_tick(slai_ctx* ctx);
+int slai_gemv_quant_partial(slai_ctx* ctx, const slai_qmatrix* w, const float* d_v, const float* d_resid, int index, int per_token);
+int slai_gemv_quant_reduced(slai_ctx* ctx, float* d_out, const slai_qmatrix* w, const float* d_norm_w, float eps, int index,
+                            int per_token, float* d_sum_out);
+/* Single-GPU stand-in for slai_tp_peer_attach: the context's own region plays every rank's, and the caller plays
+ * the ranks one after another by calling again with another `rank` (2 <= ranks <= 8).  For checking the exchange
+ * arithmetic and its time-out path without a second GPU; models do not use it. */
+int slai_tp_peer_loopback(slai_ctx* ctx, int ranks, int rank);
 
 /* ---- stream timing: the GPU timestamp queries of crates/slai-bench/src/main.rs:198,221-242 ---------- */
 int slai_timer_start(slai_ctx* ctx);          /* records an event on the stream */
@@ -204,16 +226,19 @@ int slai_attention(slai_ctx* ctx, const slai_attn_params* p, const float* d_q, c
                    const void* d_value_cache, int kv_dtype, float* d_xb);
 /* ---- slai_attention for callers that may not allocate.  This entry point has no counterpart in the
  * reference (whose scratch tensors always come from its backend's allocator).
- * Same arguments and result as slai_attention, but the call reaches no allocator at all (no cudaMalloc /
- * cudaFree, nothing that allocates behind the scenes): the split partials, the per-head tickets and the
- * position scalar live in a device array that is part of the library image, SLAI_ATTENTION_STATIC_MAX_SCRATCH_BYTES
- * (+ 4 KiB) per GPU that loads the library, held until the process exits.  It is meant for hosts that receive
- * their device memory once and must stay off the driver allocator afterwards (an engine that partitions the GPU
- * among its subsystems, a serving loop whose latency path may not synchronise on cudaMalloc / cudaFree).
- *  - Shapes whose partials exceed the array are rejected with SLAI_ERR_SHAPE and a message naming both sizes;
- *    use slai_attention for those.
- *  - The first call on a device resolves the array's device address (cudaGetSymbolAddress) with that device made
- *    current; make that first call before starting any stream capture.
+ * Same arguments and result as slai_attention, but the call itself requests no memory (no cudaMalloc / cudaFree,
+ * no allocating library routine): the split partials, the per-head tickets and the position scalar live in a
+ * device array that is part of the library image, SLAI_ATTENTION_STATIC_MAX_SCRATCH_BYTES + 4352 bytes per GPU
+ * that loads the library, held until the process exits.  It is meant for hosts that receive their device memory
+ * once and must stay off the driver allocator afterwards (an engine that partitions the GPU among its subsystems,
+ * a serving loop whose latency path may not synchronise on cudaMalloc / cudaFree).
+ *  - Shapes whose partials at the LAST position of the cache (seq_len - 1) exceed the array are rejected with
+ *    SLAI_ERR_SHAPE and a message naming both sizes, from the first call on; use slai_attention for those.
+ *  - The first call on a device does the one-time set-up: it resolves the array's device address
+ *    (cudaGetSymbolAddress, with that device current) and is the first launch of the attention kernel there, so the
+ *    CUDA runtime loads the kernel image and applies its shared-memory attribute then (the runtime may take
+ *    device memory of its own for that).  Make that first call before starting any stream capture; from the second
+ *    call on the free device memory does not change.  The caller's current device is left as it was.
  *  - All calls share the one array and it keeps the last call's contents: each call re-zeroes the tickets it uses
  *    and rewrites the position; two calls whose kernels overlap on the GPU (different contexts / streams on the
  *    same device) race on it.  Calls on one context are ordered by its stream and are safe. */

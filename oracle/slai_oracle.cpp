@@ -485,6 +485,18 @@ ORA_API int ora_sample(float* logits, int64_t n, float temperature, float topp, 
         if (logits[i] >= cutoff) cand.push_back({logits[i], (int)i});
     std::stable_sort(cand.begin(), cand.end(), [](const std::pair<float, int>& a, const std::pair<float, int>& b) { return a.first > b.first; });
     const int n0 = (int)cand.size();
+    if (n0 == 0) {  // the reference panics on `n0 - 1` here; defined as the greedy choice (first maximal index, else 0)
+        int best = 0;
+        float bv = -INFINITY;
+        bool any = false;
+        for (int64_t i = 0; i < n; i++)
+            if (logits[i] > bv) {
+                bv = logits[i];
+                best = (int)i;
+                any = true;
+            }
+        return any ? best : 0;
+    }
     float cumulative = 0.0f;
     int last = n0 - 1;
     for (int i = 0; i < n0; i++) {

@@ -1,5 +1,5 @@
 //! Raw FFI bindings to `libslai_b200.so` (C ABI: `include/slai_b200.h`).
-//! One declaration per exported function; see INTEGRATION.md for how slai's operator wrappers call them.
+//! One declaration per exported function; the safe wrappers over them live in the `slai-b200` crate next to this one.
 #![allow(non_camel_case_types)]
 use std::os::raw::{c_char, c_void};
 
@@ -35,9 +35,15 @@ extern "C" {
     pub fn slai_ctx_create(device: i32, out: *mut *mut slai_ctx) -> i32;
     pub fn slai_ctx_destroy(ctx: *mut slai_ctx) -> i32;
     pub fn slai_ctx_sync(ctx: *mut slai_ctx) -> i32;
+    pub fn slai_ctx_set_wait_limit(ctx: *mut slai_ctx, rounds: u32) -> i32;
+    pub fn slai_tp_token_tick(ctx: *mut slai_ctx) -> i32;
+    pub fn slai_gemv_quant_partial(ctx: *mut slai_ctx, w: *const slai_qmatrix, d_v: *const f32, d_resid: *const f32, index: i32, per_token: i32) -> i32;
+    pub fn slai_gemv_quant_reduced(ctx: *mut slai_ctx, d_out: *mut f32, w: *const slai_qmatrix, d_norm_w: *const f32, eps: f32, index: i32, per_token: i32, d_sum_out: *mut f32) -> i32;
+    pub fn slai_tp_peer_loopback(ctx: *mut slai_ctx, ranks: i32, rank: i32) -> i32;
     pub fn slai_last_error_string(ctx: *mut slai_ctx) -> *const c_char;
     pub fn slai_ctx_stream(ctx: *mut slai_ctx) -> *mut c_void;
     pub fn slai_device_count() -> i32;
+    pub fn slai_ctx_mem_info(ctx: *mut slai_ctx, free_bytes: *mut usize, total_bytes: *mut usize) -> i32;
     pub fn slai_ctx_device_info(ctx: *mut slai_ctx, name: *mut c_char, name_len: i32, sm_count: *mut i32) -> i32;
     pub fn slai_malloc(ctx: *mut slai_ctx, bytes: usize, d_out: *mut *mut c_void) -> i32;
     pub fn slai_free(ctx: *mut slai_ctx, d_ptr: *mut c_void) -> i32;

@@ -53,10 +53,16 @@ SIGNATURES = {
     "slai_ctx_create": (C.c_int, [C.c_int, _pp]),
     "slai_ctx_destroy": (C.c_int, [_vp]),
     "slai_ctx_sync": (C.c_int, [_vp]),
+    "slai_ctx_set_wait_limit": (C.c_int, [_vp, C.c_uint32]),
+    "slai_tp_token_tick": (C.c_int, [_vp]),
+    "slai_gemv_quant_partial": (C.c_int, [_vp, _vp, _vp, _vp, C.c_int, C.c_int]),
+    "slai_gemv_quant_reduced": (C.c_int, [_vp, _vp, _vp, _vp, _f, C.c_int, C.c_int, _vp]),
+    "slai_tp_peer_loopback": (C.c_int, [_vp, C.c_int, C.c_int]),
     "slai_last_error_string": (C.c_char_p, [_vp]),
     "slai_ctx_stream": (_vp, [_vp]),
     "slai_device_count": (C.c_int, []),
     "slai_ctx_device_info": (C.c_int, [_vp, C.c_char_p, C.c_int, C.POINTER(C.c_int)]),
+    "slai_ctx_mem_info": (C.c_int, [_vp, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
     "slai_malloc": (C.c_int, [_vp, _sz, _pp]),
     "slai_free": (C.c_int, [_vp, _vp]),
     "slai_memset": (C.c_int, [_vp, _vp, C.c_int, _sz]),

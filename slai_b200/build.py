@@ -30,9 +30,12 @@ def _stale(target: str, deps: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, trace: bool = False) -> str:
+    """trace=True builds libslai_b200_trace.so with -DSLAI_TRACE (device-side timeline, read by slai_b200/trace.py)."""
     hdrs = [os.path.join(CSRC, h) for h in HEADERS]
-    objdir = os.path.join(HERE, "build")
+    objdir = os.path.join(HERE, "build_trace" if trace else "build")
+    lib = os.path.join(HERE, "libslai_b200_trace.so") if trace else LIB
+    flags = NVCC_FLAGS + (["-DSLAI_TRACE"] if trace else [])
     os.makedirs(objdir, exist_ok=True)
     jobs = []
     objs = []
@@ -41,7 +44,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         op = os.path.join(objdir, src.replace(".cu", ".o"))
         objs.append(op)
         if force or _stale(op, [sp] + hdrs):
-            jobs.append([_nvcc(), *NVCC_FLAGS, "-c", sp, "-o", op] + (["-Xptxas", "-v"] if verbose else []))
+            jobs.append([_nvcc(), *flags, "-c", sp, "-o", op] + (["-Xptxas", "-v"] if verbose else []))
 
     def run(cmd):
         r = subprocess.run(cmd, capture_output=True, text=True)
@@ -54,11 +57,11 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if verbose:
         for l in logs:
             sys.stderr.write(l)
-    if jobs or force or _stale(LIB, objs):
-        run([_nvcc(), "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC",
+    if jobs or force or _stale(lib, objs):
+        run([_nvcc(), "-shared", "-o", lib, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC",
              "-lcudart", "-ldl"])
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, trace="--trace" in sys.argv))

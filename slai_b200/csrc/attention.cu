@@ -17,28 +17,42 @@ namespace {
 template <typename T, int MAXQ>
 __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnParams P) {
     extern __shared__ __align__(16) unsigned char sm[];
-    SLAI_TL_BEGIN(999)
+#ifdef SLAI_TRACE
+    unsigned long long tl0 = slai_globaltimer(), tl1 = 0;
+#endif
+    prefetch_plan_issue(P.ahead, (int)(blockIdx.x + gridDim.x * blockIdx.y), (int)(gridDim.x * gridDim.y), (int)threadIdx.x, ATT_THREADS);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the next kernel may start fetching its weights
+#ifdef SLAI_TRACE
+    tl1 = slai_globaltimer();
+#endif
     {
         const int n = __ldcg(P.d_pos) + 1;
         const int ns = attn_splits(P, n);
         if ((int)blockIdx.y < ns) attn_item<T, MAXQ>(P, blockIdx.x, blockIdx.y, ns, n, threadIdx.x, sm, 0);
     }
-    SLAI_TL_MARK(2)
+#ifdef SLAI_TRACE
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && P.tl) {
+        unsigned long long st[TL_SLOTS] = {};
+        st[0] = tl0;
+        st[4] = tl1;
+        st[13] = slai_globaltimer();
+        slai_tl_append(P.tl, 999, st);
+    }
+#endif
 }
 
 template <typename T, int MAXQ>
 int launch_t(slai_ctx* ctx, const AttnParams& P, int n_kv, size_t smem, bool pdl) {
     auto kern = attn_kernel<T, MAXQ>;
-    static bool attr_done = false;
-    if (!attr_done) {
+    static PerDeviceOnce attr;
+    if (attr.need(ctx->device)) {
         SLAI_CHECK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
         // Same shared-memory carve-out as the GEMV kernels it alternates with: no reconfiguration between launches.
         const char* co = getenv("SLAI_ATTN_CARVEOUT");
         if (!(co && co[0] == '0'))
             SLAI_CHECK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-        attr_done = true;
+        attr.set(ctx->device);
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n_kv, P.n_splits);
@@ -58,13 +72,13 @@ int launch_t(slai_ctx* ctx, const AttnParams& P, int n_kv, size_t smem, bool pdl
 
 int ensure_scratch(slai_ctx* ctx, size_t bytes) {
     if (ctx->scratch_bytes >= bytes) return SLAI_OK;
-    if (ctx->d_scratch) {
-        SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-        cudaFree(ctx->d_scratch);
-        ctx->d_scratch = nullptr;
-        ctx->scratch_bytes = 0;
-    }
-    SLAI_CHECK_CUDA(ctx, cudaMalloc(&ctx->d_scratch, bytes));
+    // Grow-only, and the outgrown buffer is kept until the context goes: a pass recorded earlier (slai_pass_*) still
+    // launches kernels that point at it.  Growing at least doubles, so the retired buffers sum to less than the live one.
+    if (bytes < 2 * ctx->scratch_bytes) bytes = 2 * ctx->scratch_bytes;
+    void* fresh = nullptr;
+    SLAI_CHECK_CUDA(ctx, cudaMalloc(&fresh, bytes));
+    if (ctx->d_scratch) ctx->retired_scratch.push_back(ctx->d_scratch);
+    ctx->d_scratch = fresh;
     ctx->scratch_bytes = bytes;
     return SLAI_OK;
 }
@@ -89,9 +103,6 @@ size_t attention_scratch_bytes(slai_ctx* ctx, int n_heads, int kv_mul, int head_
 // Tile size, split count, copy width and shared memory of a launch.
 static int attn_geometry(slai_ctx* ctx, AttnParams& P, int kv_dtype, int n_max, size_t* smem) {
     const int esz = kv_dtype == SLAI_KV_F16 ? 2 : 4;
-#ifdef SLAI_TRACE
-    P.tr = nullptr;
-#endif
     P.tile_pos = attn_tile_pos(P.hs, esz);
     P.n_splits = pick_splits(P.hs, esz, n_max);
     const uintptr_t bits = reinterpret_cast<uintptr_t>(P.kc) | reinterpret_cast<uintptr_t>(P.vc) | (uintptr_t)(P.pos_stride * esz) |
@@ -133,9 +144,13 @@ int attention_launch(slai_ctx* ctx, const AttnLaunch& A) {
 
     P.d_pos = A.d_pos;
     P.out = A.out;
+    P.ahead = A.ahead;
+#ifdef SLAI_TRACE
+    P.tl = ctx->tl;
+#endif
     P.part_o = reinterpret_cast<float*>(scratch);
     P.part_ml = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + ((po + 255) & ~(size_t)255));
-    P.counters = ctx->d_counters;
+    P.counters = ctx->d_counters + CNT_ATTN_TICKETS;
     const bool f16 = A.kv_dtype == SLAI_KV_F16;
     if (A.kv_mul == 1) return f16 ? launch_t<__half, 1>(ctx, P, n_kv, smem, A.pdl) : launch_t<float, 1>(ctx, P, n_kv, smem, A.pdl);
     if (A.kv_mul <= 4) return f16 ? launch_t<__half, 4>(ctx, P, n_kv, smem, A.pdl) : launch_t<float, 4>(ctx, P, n_kv, smem, A.pdl);
@@ -171,6 +186,7 @@ __global__ void static_set_pos_kernel(int* dst, int pos) { *dst = pos; }
 SLAI_API int slai_attention_static(slai_ctx* ctx, const slai_attn_params* p, const float* d_q, const void* d_key_cache,
                                    const void* d_value_cache, int kv_dtype, float* d_xb) {
     if (!ctx || !p || !d_q || !d_key_cache || !d_value_cache || !d_xb) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     SLAI_REQUIRE(ctx, p->pos < p->seq_len, SLAI_ERR_SHAPE, "attention: pos=%u >= seq_len=%u", p->pos, p->seq_len);
     SLAI_REQUIRE(ctx, p->kv_mul >= 1 && p->kv_mul <= 8 && p->n_heads % p->kv_mul == 0 &&
                           p->kv_dim == p->n_heads / p->kv_mul * p->head_size,
@@ -193,13 +209,14 @@ SLAI_API int slai_attention_static(slai_ctx* ctx, const slai_attn_params* p, con
         if (rc) return rc;
     }
     const size_t po = (size_t)n_heads * P.n_splits * hs * 4;
-    const size_t need = attention_scratch_bytes(ctx, n_heads, kv_mul, hs, pos);
+    // Sized for the last position of this cache, not the current one: a shape that will not fit later in the
+    // generation is refused at its first call.
+    const size_t need = attention_scratch_bytes(ctx, n_heads, kv_mul, hs, (int)p->seq_len - 1);
     SLAI_REQUIRE(ctx, need <= STATIC_PART_BYTES, SLAI_ERR_SHAPE,
-                 "slai_attention_static: this shape needs %zu bytes of split scratch, the built-in array holds %zu "
-                 "(use slai_attention, which allocates)", need, STATIC_PART_BYTES);
+                 "slai_attention_static: this shape needs %zu bytes of split scratch at seq_len=%u, the built-in array holds %zu "
+                 "(use slai_attention, which allocates)", need, p->seq_len, STATIC_PART_BYTES);
 
-    // Set-up, once per device: resolve the array's device address with that device current.
-    SLAI_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
+    // Set-up, once per device: resolve the array's device address with that device current (SLAI_ENTER made it so).
     if (!g_attn_static_ptr[ctx->device]) {
         void* sym = nullptr;
         SLAI_CHECK_CUDA(ctx, cudaGetSymbolAddress(&sym, g_attn_static));

@@ -23,20 +23,11 @@ struct AttnParams {
     float* part_o;   // [n_heads][n_splits][hs]
     float* part_ml;  // [n_heads][n_splits][2]
     unsigned int* counters;  // [n_kv_heads]
+    PrefetchPlan ahead;      // weights of a later kernel, pulled into L2 by all blocks at the start
 #ifdef SLAI_TRACE
-    unsigned long long* tr;  // debug build only: timestamps of the first item of sub-block 0
+    unsigned long long* tl = nullptr;  // trace build only: the context's launch timeline
 #endif
 };
-#ifdef SLAI_TRACE
-#define ATT_TRACE(k)                                                   \
-    if (P.tr && tid == 0 && bar_id <= 1) {                             \
-        unsigned long long gt;                                         \
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));          \
-        if (P.tr[k] == 0) P.tr[k] = gt;                                \
-    }
-#else
-#define ATT_TRACE(k)
-#endif
 
 // Barrier over the ATT_THREADS threads that work on one item (named barrier `id`; id 0 with a 128-thread block is
 // the block-wide barrier).
@@ -146,8 +137,6 @@ __device__ __forceinline__ void attn_item(const AttnParams& P, int kvh, int spli
     const unsigned char* vbase = reinterpret_cast<const unsigned char*>(P.vc) + ((size_t)kvh * P.head_stride) * ESZ;
     const size_t row_pitch = (size_t)P.pos_stride * ESZ;
     const float sqrt_hs = sqrtf((float)hs);
-
-    ATT_TRACE(0)
     // q: loads first, stores after the first tile's loads are in flight
     float qr[2 * MAXQ];
 #pragma unroll
@@ -190,7 +179,6 @@ __device__ __forceinline__ void attn_item(const AttnParams& P, int kvh, int spli
             }
         }
         att_sync(bar_id);
-        ATT_TRACE(1)
         // scores: four threads per position, 32 positions per pass
         {
             const int c = tid & 3;
@@ -255,7 +243,6 @@ __device__ __forceinline__ void attn_item(const AttnParams& P, int kvh, int spli
             }
         }
         att_sync(bar_id);
-        ATT_TRACE(2)
         // weighted sum of V: thread `tid` owns dims tid and tid + 128
 #pragma unroll
         for (int jj = 0; jj < 2; jj++) {
@@ -277,7 +264,6 @@ __device__ __forceinline__ void attn_item(const AttnParams& P, int kvh, int spli
             }
         }
     }
-    ATT_TRACE(3)
     // partial (or final) output
 #pragma unroll
     for (int jj = 0; jj < 2; jj++) {
@@ -299,7 +285,6 @@ __device__ __forceinline__ void attn_item(const AttnParams& P, int kvh, int spli
         P.part_ml[((size_t)head * P.n_splits + split) * 2 + 1] = st_s[4 * tid + 1];
     }
     __threadfence();
-    ATT_TRACE(4)
     att_sync(bar_id);
     if (tid == 0) {
         const unsigned int ticket = atomicAdd(&P.counters[kvh], 1u);
@@ -307,7 +292,6 @@ __device__ __forceinline__ void attn_item(const AttnParams& P, int kvh, int spli
         if (*is_last_p) P.counters[kvh] = 0;  // ready for the next launch
     }
     att_sync(bar_id);
-    ATT_TRACE(5)
     if (!*is_last_p) return;
     __threadfence();
     // Merge the splits of this KV head (fixed order over splits).  The (max, sum) pairs of all splits come into
@@ -357,7 +341,6 @@ __device__ __forceinline__ void attn_item(const AttnParams& P, int kvh, int spli
         }
         P.out[(size_t)head * hs + d] = num / den;
     }
-    ATT_TRACE(6)
 }
 
 }  // namespace attn

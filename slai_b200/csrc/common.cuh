@@ -5,6 +5,7 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <atomic>
 #include <string>
 #include <vector>
 #include <unordered_map>
@@ -40,22 +41,65 @@ struct slai_ctx {
     bool use_pdl = true;            // programmatic dependent launch between decode kernels
     void* d_scratch = nullptr;      // attention split partials etc.
     size_t scratch_bytes = 0;
+    std::vector<void*> retired_scratch;  // outgrown scratch buffers: recorded passes may still point at them, freed with the context
     std::vector<RopeTable> rope_tables;
-    unsigned int* d_counters = nullptr;  // tickets for "last block finishes" reductions (zeroed)
+    unsigned long long* trace_buf = nullptr;  // trace build only: per-block stamps of the last 64 GEMV launches
+    unsigned long long trace_launches = 0;
+    unsigned long long* tl = nullptr;         // trace build only: the launch timeline
+    unsigned int* d_counters = nullptr;  // CNT_WORDS zeroed words, see the map below
+    unsigned int wait_limit = 1u << 20;  // rounds a bounded device-side wait polls before it gives up (slai_ctx_set_wait_limit)
     // tensor-parallel group (tp.cu): NCCL communicator of this context's rank, null when not sharded
     void* tp_comm = nullptr;
     int tp_rank = 0, tp_size = 1;
     PeerExchange xchg = {};     // filled by slai_tp_peer_attach
     void* xchg_region = nullptr;  // this rank's region (device memory, exported to the peers)
     bool xchg_ready = false;
+    bool xchg_loopback = false;   // slai_tp_peer_loopback: the region stands in for every rank's (single-GPU testing)
 };
 
 // tp.cu: sum of `n` floats over the ranks of the context's group, on the context's stream
 int tp_all_reduce_sum(slai_ctx* ctx, const float* d_in, float* d_out, int64_t n);
+// tp.cu: concatenation in rank order of every rank's `n` floats, on the context's stream
+int tp_all_gather(slai_ctx* ctx, const float* d_in, float* d_out, int64_t n);
 // tp.cu: one more token decoded (sequence numbers of the peer exchange derive from it)
 int tp_tick(slai_ctx* ctx);
 
+// Map of slai_ctx::d_counters (unsigned words, all zero between launches).
+constexpr int CNT_ATTN_TICKETS = 0;    // one ticket per KV head (<= 1024): last split of a head merges the partials
+constexpr int CNT_ARGMAX = 1100;       // ticket, then per-block (value, index) pairs of the multi-block argmax
+constexpr int CNT_ATTN_POS = 2048;     // position scalar of the stand-alone slai_attention
+constexpr int CNT_ERR_FLAG = 3000;     // raised by a bounded wait that ran out (1 weight ring, 2 grid barrier, 3 peer exchange)
+constexpr int CNT_GRID_BAR = 3100;     // grid barrier of the persistent decode kernel
+constexpr int CNT_WORDS = 4096;
+
 int slai_set_error(slai_ctx* ctx, int code, const char* fmt, ...);
+int slai_check_wait_flag(slai_ctx* ctx);  // ops.cu: SLAI_ERR_TIMEOUT if a bounded device-side wait ran out (stream must be idle)
+
+// Every exported function runs with its context's device current and puts the caller's device back on return, so
+// several contexts (one per GPU) can be driven from one thread.
+struct DeviceGuard {
+    int prev = -1;
+    bool switched = false;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) == cudaSuccess && prev != dev) switched = cudaSetDevice(dev) == cudaSuccess;
+    }
+    ~DeviceGuard() {
+        if (switched) cudaSetDevice(prev);
+    }
+    DeviceGuard(const DeviceGuard&) = delete;
+    DeviceGuard& operator=(const DeviceGuard&) = delete;
+};
+#define SLAI_ENTER(ctx) DeviceGuard slai_device_guard_((ctx)->device)
+
+// Kernel attributes (the dynamic shared-memory opt-in) are per device: one flag per device and kernel instantiation.
+constexpr int SLAI_MAX_DEVICES = 64;
+struct PerDeviceOnce {
+    std::atomic<bool> done[SLAI_MAX_DEVICES];
+    bool need(int dev) const { return dev < 0 || dev >= SLAI_MAX_DEVICES || !done[dev].load(std::memory_order_acquire); }
+    void set(int dev) {
+        if (dev >= 0 && dev < SLAI_MAX_DEVICES) done[dev].store(true, std::memory_order_release);
+    }
+};
 
 #define SLAI_CHECK_CUDA(ctx, expr)                                                                 \
     do {                                                                                           \
@@ -69,6 +113,35 @@ int slai_set_error(slai_ctx* ctx, int code, const char* fmt, ...);
     do {                                                                                           \
         if (!(cond)) return slai_set_error((ctx), (code), __VA_ARGS__);                            \
     } while (0)
+
+// ------------------------------------------------------------------------------------------------
+// Weights that a LATER kernel of the decode step will stream, pulled into L2 by the blocks of the current kernel as
+// soon as they start.  A decode kernel spends microseconds in phases that move no weight bytes (waiting for its
+// predecessor, staging its input vector, the epilogue); with the next kernel's weights requested one kernel ahead
+// the HBM stream runs through those phases and the next kernel's ring fills from L2.
+// ------------------------------------------------------------------------------------------------
+struct PrefetchPlan {
+    const char* ptr[3] = {nullptr, nullptr, nullptr};  // 16-byte aligned
+    unsigned long long bytes[3] = {0, 0, 0};
+};
+#ifdef __CUDACC__
+// Chunk c of a range goes to block c % nblocks, thread c / nblocks: every block issues a few requests, spread over
+// the whole range.  The requests are fire-and-forget (no completion is awaited, nothing lands in the SM).
+__device__ __forceinline__ void prefetch_plan_issue(const PrefetchPlan& pf, int block, int nblocks, int tid, int nthreads) {
+    constexpr unsigned long long CH = 8192;
+#pragma unroll
+    for (int r = 0; r < 3; r++) {
+        const unsigned long long n = pf.bytes[r];
+        if (n == 0) continue;
+        const long long nch = (long long)((n + CH - 1) / CH);
+        for (long long c = block + (long long)nblocks * tid; c < nch; c += (long long)nblocks * nthreads) {
+            const unsigned long long off = (unsigned long long)c * CH;
+            const unsigned int len = (unsigned int)((n - off < CH ? n - off : CH) & ~15ull);
+            if (len) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(pf.ptr[r] + off), "r"(len) : "memory");
+        }
+    }
+}
+#endif
 
 // ------------------------------------------------------------------------------------------------
 // Quantized matrix as stored on the device: tile-major blocks of 16 rows x one K step (layout.cuh);
@@ -159,6 +232,7 @@ struct GemvLaunch {
     bool pdl = false;              // launch with programmatic stream serialization
     const void* prefetch = nullptr;  // what the next kernel reads first (e.g. its norm weights): pulled into L2 meanwhile
     size_t prefetch_bytes = 0;
+    PrefetchPlan ahead;              // weights of a later kernel: pulled into L2 by this one (see PrefetchPlan)
     // tensor-parallel exchange over peer memory (null: not used)
     const PeerExchange* xchg = nullptr;
     int xchg_out_idx1 = 0;         // EPI_XCHG: index + 1 of this exchange inside the token
@@ -183,6 +257,7 @@ struct AttnLaunch {
     bool pdl;
     void* scratch;      // split partials; NULL = the context's scratch (grown on demand, not graph-safe)
     size_t scratch_bytes;
+    PrefetchPlan ahead; // weights of a later kernel: pulled into L2 by this one
 };
 size_t attention_scratch_bytes(slai_ctx* ctx, int n_heads, int kv_mul, int head_size, int max_pos);
 int attention_launch(slai_ctx* ctx, const AttnLaunch& A);
@@ -201,30 +276,33 @@ size_t sampler_scratch_bytes(int n);
 int sampler_set_params(slai_ctx* ctx, void* d_params, float temperature, float topp, unsigned long long seed);
 int launch_sample(slai_ctx* ctx, float* d_logits, int n, const void* d_params, const int* d_step, float host_coin, bool use_host_coin,
                   void* d_scratch, int32_t* d_out, bool pdl);
-int launch_advance(slai_ctx* ctx, int* d_token, int* d_pos, const int32_t* d_next, int32_t* d_history, bool pdl);
+int launch_advance(slai_ctx* ctx, int* d_token, int* d_pos, const int32_t* d_next, int32_t* d_history, int vocab, bool pdl);
 
+// ------------------------------------------------------------------------------------------------
+// Trace build (-DSLAI_TRACE, `python -m slai_b200.build --trace` -> libslai_b200_trace.so; reader: slai_b200/trace.py).
+// Thread 0 of every GEMV block stamps %globaltimer at fixed points into the context's trace buffer; block 0 of every
+// GEMV / attention launch appends one record {kernel id, 7 stamps} to a device-side timeline, in execution order.
+// It works inside CUDA graphs, so the decode step is seen exactly as it runs.  The shipped library has none of it.
+// ------------------------------------------------------------------------------------------------
+#ifdef SLAI_TRACE
+constexpr int TL_SLOTS = 16, TL_CAP = 4096;  // slai_ctx::tl: TL_CAP records of TL_SLOTS words, then the record counter
+constexpr int TRACE_POINTS = 16, TRACE_BLOCKS = 256;  // per launch: stamps of every block (slai_ctx::trace_buf, 64 launches deep)
+#endif
 #if defined(SLAI_TRACE) && defined(__CUDACC__)
-// debug build only: timeline of kernels as seen by thread 0 of block 0 (kernel id, start, end in globaltimer ns)
-extern __device__ unsigned long long g_tl[3 * 4096];
-extern __device__ unsigned int g_tl_count;
-#define SLAI_TL_BEGIN(id)                                                              \
-    unsigned int tl_idx = 0xffffffffu;                                                 \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {                      \
-        tl_idx = atomicAdd(&g_tl_count, 1u) & 4095u;                                   \
-        unsigned long long gt;                                                         \
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));                          \
-        g_tl[3 * tl_idx] = (id);                                                       \
-        g_tl[3 * tl_idx + 1] = gt;                                                     \
-    }
-#define SLAI_TL_MARK(slot)                                                             \
-    if (tl_idx != 0xffffffffu) {                                                       \
-        unsigned long long gt;                                                         \
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));                          \
-        g_tl[3 * tl_idx + (slot)] = gt;                                                \
-    }
-#else
-#define SLAI_TL_BEGIN(id)
-#define SLAI_TL_MARK(slot)
+__device__ __forceinline__ unsigned long long slai_globaltimer() {
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
+    return gt;
+}
+// stamps[0..14] of block 0 of the launch.  GEMV: 0 start, 1 barriers initialised, 2 first weight blocks requested,
+// 3 dependents released and look-ahead issued, 4 predecessor done, 5 partial sums cleared, 6 input loaded and its
+// statistics summed per thread, 7 statistics reduced over the block, 8 digits written, 9 staged (barrier), 10 main
+// loop done, 11 partial sums complete (barrier), 12 epilogue done, 13 end.  Attention: 0 start, 4 predecessor done, 13 end.
+__device__ __forceinline__ void slai_tl_append(unsigned long long* tl, unsigned long long id, const unsigned long long* stamps) {
+    const unsigned long long i = atomicAdd(tl + TL_SLOTS * TL_CAP, 1ull) % TL_CAP;
+    tl[TL_SLOTS * i] = id;
+    for (int k = 0; k < TL_SLOTS - 1; k++) tl[TL_SLOTS * i + 1 + k] = stamps[k];
+}
 #endif
 
 // decode.cu: all layers of a token in one persistent kernel (Llama family, one weight format for all matrices)
@@ -252,6 +330,7 @@ struct DecodeParams {
     int nstage, step_bytes, stage_stride, dig_region;
     int n_splits, tile_pos, att_item_bytes, vec16;
     unsigned int *bar, *err_flag, *counters;
+    unsigned int wait_limit;
     // the model's buffers (caller)
     float eps;
     const float* rope_theta;

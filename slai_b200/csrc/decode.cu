@@ -16,21 +16,6 @@
 using namespace gemvk;
 using attn::AttnParams;
 
-#ifdef SLAI_TRACE
-// debug build only: per block of threads 32 x (globaltimer, clock64) taken in one layer of the token
-__device__ unsigned long long g_dtrace[256 * 32 * 2];
-__device__ unsigned long long g_ptrace[4 * 256 * 8 * 2];   // per GEMV phase of that layer: the phase's own trace points
-__device__ unsigned long long g_wtrace[4 * 256 * 16 * 4];  // per GEMV phase, block of threads and warp
-#define DTRACE(k)                                                          \
-    if (l == 8 && threadIdx.x == 0) {                                      \
-        unsigned long long gt;                                             \
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));              \
-        g_dtrace[(blockIdx.x * 32 + (k)) * 2] = gt;                        \
-        g_dtrace[(blockIdx.x * 32 + (k)) * 2 + 1] = (unsigned long long)clock64(); \
-    }
-#else
-#define DTRACE(k)
-#endif
 
 namespace {
 
@@ -76,6 +61,7 @@ __device__ __forceinline__ GemvParams phase_params(const DecodeParams& D, int l,
     P.stage_stride = D.stage_stride;
     P.dig_region = D.dig_region;
     P.err_flag = D.err_flag;
+    P.wait_limit = D.wait_limit;
     P.eps = D.eps;
     P.nseg = qkv ? 3 : gu ? 2 : 1;
     P.nmat = gu ? 2 : 1;
@@ -108,10 +94,8 @@ __device__ __forceinline__ GemvParams phase_params(const DecodeParams& D, int l,
     P.kcache = W.kcache; P.vcache = W.vcache; P.kv_f16 = D.kv_f16;
     P.kv_pos_stride = D.head_size; P.kv_head_stride = (long long)D.seq_len * D.head_size;
 #ifdef SLAI_TRACE
-    if (l == 8) {
-        P.trace = g_ptrace + k * 256 * 8 * 2;
-        P.wtrace = g_wtrace + k * 256 * 16 * 4;
-    }
+    P.trace = nullptr;
+    P.tl = nullptr;
 #endif
     return P;
 }
@@ -125,9 +109,6 @@ __device__ __forceinline__ AttnParams attn_params(const DecodeParams& D, int l) 
     A.d_pos = D.d_pos; A.n_splits = D.n_splits; A.tile_pos = D.tile_pos; A.vec16 = D.vec16;
     A.out = D.xb; A.part_o = D.part_o; A.part_ml = D.part_ml;
     A.counters = D.counters;
-#ifdef SLAI_TRACE
-    A.tr = l == 8 ? g_dtrace + (blockIdx.x * 32 + 16) * 2 : nullptr;
-#endif
     return A;
 }
 
@@ -143,7 +124,7 @@ __device__ __forceinline__ void grid_sync(const DecodeParams& D, unsigned int& e
             unsigned int v;
             asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(v) : "l"(D.bar) : "memory");
             if (v >= target) break;
-            if (it > (1 << 22)) {
+            if ((unsigned int)it > 4u * D.wait_limit) {
                 atomicExch(D.err_flag, 2u);
                 break;
             }
@@ -186,7 +167,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const __grid_
     extern __shared__ __align__(128) unsigned char smem_raw[];
     Ring R;
     const LayerProg prog{D};
-    ring_init(R, prog, D.dig_region, D.nstage, D.stage_stride, D.step_bytes, D.err_flag, smem_raw, threadIdx.x & 31, threadIdx.x >> 5);
+    ring_init(R, prog, D.dig_region, D.nstage, D.stage_stride, D.step_bytes, D.err_flag, D.wait_limit, smem_raw, threadIdx.x & 31, threadIdx.x >> 5);
     unsigned int epoch = 0;
     const int n_pos = __ldcg(D.d_pos) + 1;  // positions in the cache after this token (fixed for the launch)
     // One copy of the GEMV phase serves the four GEMVs of a layer (k = 0 QKV, 1 O, 2 gate/up, 3 down): the
@@ -197,7 +178,6 @@ __global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const __grid_
         prefetch_norms(D, l + 1);
 #pragma unroll 1
         for (int k = 0; k < 4; k++) {
-            DTRACE(k == 0 ? 0 : 2 * k + 2)
             {
                 GemvParams P = phase_params(D, l, k);
                 P.pos1 = n_pos;
@@ -208,29 +188,25 @@ __global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const __grid_
                 gemv_phase<F, PRO_MASK, EPI_MASK>(P, R, prog, smem_raw, nmat, pro, epi);
 #endif
             }
-            DTRACE(k == 0 ? 1 : 2 * k + 3)
             if (k < 3 || l + 1 < D.n_layers) grid_sync(D, epoch);
             if (k == 0) {
-                DTRACE(2)
                 const AttnParams A = attn_params(D, l);
 #ifndef SIZE_NO_ATTN
                 attention_phase<KV, MAXQ>(D, A, n_pos, smem_raw);
 #endif
-                DTRACE(3)
                 grid_sync(D, epoch);
             }
         }
-        DTRACE(10)
     }
 }
 
 template <class F, typename KV, int MAXQ>
 int launch_k(slai_ctx* ctx, const DecodeParams& D, size_t smem) {
     auto kern = decode_layers_kernel<F, KV, MAXQ>;
-    static bool attr_done = false;
-    if (!attr_done) {
+    static PerDeviceOnce attr;
+    if (attr.need(ctx->device)) {
         SLAI_CHECK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT));
-        attr_done = true;
+        attr.set(ctx->device);
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctx->sm_count);
@@ -316,8 +292,9 @@ int decode_layers_prepare(slai_ctx* ctx, const DecodeLayersDesc& desc, DecodeLay
     }
     D->nstage = P.nstage; D->step_bytes = P.step_bytes; D->stage_stride = P.stage_stride; D->dig_region = (int)dig;
     D->n_splits = n_splits; D->tile_pos = tile_pos; D->att_item_bytes = (int)item_bytes;
-    D->bar = ctx->d_counters + 3100;
-    D->err_flag = ctx->d_counters + 3000;
+    D->bar = ctx->d_counters + CNT_GRID_BAR;
+    D->err_flag = ctx->d_counters + CNT_ERR_FLAG;
+    D->wait_limit = ctx->wait_limit;
     D->counters = ctx->d_counters;
     return SLAI_OK;
 }
@@ -335,15 +312,3 @@ int decode_layers_launch(slai_ctx* ctx, const DecodeParams& D, const DecodeLayer
     return slai_set_error(ctx, SLAI_ERR_UNSUPPORTED_FORMAT, "decode: format %d has no fused kernel", D.fmt);
 }
 
-#ifdef SLAI_TRACE
-SLAI_API int slai_debug_decode_trace(void* h_out, size_t bytes) { return (int)cudaMemcpyFromSymbol(h_out, g_dtrace, bytes); }
-SLAI_API int slai_debug_decode_trace_reset() {
-    void* p = nullptr;
-    cudaGetSymbolAddress(&p, g_dtrace);
-    return (int)cudaMemset(p, 0, sizeof(g_dtrace));
-}
-SLAI_API int slai_debug_phase_trace(void* h_p, size_t pbytes, void* h_w, size_t wbytes) {
-    int rc = (int)cudaMemcpyFromSymbol(h_p, g_ptrace, pbytes);
-    return rc ? rc : (int)cudaMemcpyFromSymbol(h_w, g_wtrace, wbytes);
-}
-#endif

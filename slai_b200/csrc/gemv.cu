@@ -14,25 +14,37 @@ namespace {
 template <class F, int NMAT, int PRO, int EPI, bool XIN = false>
 __global__ void __launch_bounds__(THREADS, 1) gemv_kernel(const __grid_constant__ GemvParams P) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    SLAI_TL_BEGIN(100 * NMAT + 10 * PRO + EPI)
     SLAI_TRACE_POINT(0)
     Ring R;
     const OneProg prog{P};
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     // The weights do not depend on the kernel this one may be launched behind (programmatic dependent launch):
     // the ring starts filling while that kernel drains.
-    ring_init(R, prog, P.dig_region, P.nstage, P.stage_stride, P.step_bytes, P.err_flag, smem_raw, lane, warp);
+    #ifdef SLAI_TRACE
+    ring_init(R, prog, P.dig_region, P.nstage, P.stage_stride, P.step_bytes, P.err_flag, P.wait_limit, smem_raw, lane, warp, P.trace);
+#else
+    ring_init(R, prog, P.dig_region, P.nstage, P.stage_stride, P.step_bytes, P.err_flag, P.wait_limit, smem_raw, lane, warp);
+#endif
     // Let the next kernel's blocks be scheduled as this kernel's blocks leave their SMs (it parks in its own
     // griddepcontrol.wait until this grid has completed): the hand-over costs no grid-wide launch latency.
     if (P.pdl == 2) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    prefetch_plan_issue(P.ahead, (int)blockIdx.x, (int)gridDim.x, (int)threadIdx.x, THREADS);
     // Pull data the *next* kernel reads first (its norm weights) into L2 while this one runs.
     if (P.pf_lines > 0 && (int)blockIdx.x == (int)gridDim.x - 1)
         for (int i = threadIdx.x; i < P.pf_lines; i += THREADS) asm volatile("prefetch.global.L2 [%0];" ::"l"(P.pf_ptr + (size_t)i * 128));
-    SLAI_TRACE_POINT(1)
+    // partial-sum buffer cleared while the predecessor drains (same layout as in gemv_phase)
+    for (int i = threadIdx.x; i < WAVE * WARPS * NMAT * 16; i += THREADS) reinterpret_cast<float*>(smem_raw + P.dig_region)[i] = 0.f;
+    SLAI_TRACE_POINT(3)
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    gemv_phase<F, 1 << PRO, 1 << EPI, XIN>(P, R, prog, smem_raw, NMAT, PRO, EPI);
+    SLAI_TRACE_POINT(4)
+    gemv_phase<F, 1 << PRO, 1 << EPI, XIN>(P, R, prog, smem_raw, NMAT, PRO, EPI, true);
     if (P.pdl != 2) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    SLAI_TL_MARK(2)
+#ifdef SLAI_TRACE
+    if (blockIdx.x == 0 && threadIdx.x == 0 && P.trace) {
+        P.trace[13] = slai_globaltimer();
+        slai_tl_append(P.tl, 1000 * (P.K / 256) + 100 * NMAT + 10 * PRO + EPI, P.trace);
+    }
+#endif
 }
 
 // Dense f32 matrix (GpuQuantMatrix::F32): one warp per row.
@@ -51,10 +63,10 @@ __global__ void gemv_f32_kernel(float* out, const float* w, const float* v, int 
 template <class F, int NMAT, int PRO, int EPI, bool XIN = false>
 int launch_inst(slai_ctx* ctx, const GemvParams& P, int grid, size_t smem, bool pdl) {
     auto kern = gemv_kernel<F, NMAT, PRO, EPI, XIN>;
-    static bool attr_done = false;  // per instantiation
-    if (!attr_done) {
+    static PerDeviceOnce attr;  // per instantiation
+    if (attr.need(ctx->device)) {
         SLAI_CHECK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT));
-        attr_done = true;
+        attr.set(ctx->device);
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
@@ -112,12 +124,13 @@ int launch_fmt(slai_ctx* ctx, const GemvParams& P, const GemvLaunch& L, int grid
 
 }  // namespace
 
-// Bytes of shared memory the staged activation vector of a K-element phase needs (digit planes + digit sums).
+// Bytes of shared memory the staged activation vector of a K-element phase needs (zero page, digit planes, digit
+// sums: 16 bytes per sub-block in both representations of gemv_formats.cuh).
 size_t gemv_dig_region(int fmt, int K) {
     const int Kp = (K + 255) & ~255;
     const int sv_gran = (fmt == SLAI_FMT_Q4_K || fmt == SLAI_FMT_Q5_K) ? 32 : fmt == SLAI_FMT_Q6_K ? 16 : 0;
     const size_t sv_bytes = sv_gran ? (size_t)(Kp / sv_gran) * 16 : 0;
-    return (((size_t)4 * (Kp + 32) + sv_bytes) + 127) & ~(size_t)127;
+    return ((size_t)gemvfmt::ZERO_BYTES + ((size_t)4 * (Kp + 32) + sv_bytes) + 127) & ~(size_t)127;
 }
 
 // Validate a launch description and turn it into kernel parameters.  `dig_region` = 0: size it for this K.
@@ -157,7 +170,8 @@ int gemv_fill_params(slai_ctx* ctx, const GemvLaunch& L, size_t dig_region, int 
     P.resid = L.resid; P.rope = L.rope; P.rope_theta = L.rope_theta; P.rope_cs = L.rope_cs; P.head_size = L.head_size;
     P.d_pos = L.d_pos; P.pos1 = 0; P.kcache = L.kcache; P.vcache = L.vcache; P.kv_f16 = (L.kv_dtype == SLAI_KV_F16);
     P.kv_pos_stride = L.kv_pos_stride; P.kv_head_stride = L.kv_head_stride;
-    P.err_flag = ctx->d_counters + 3000;
+    P.err_flag = ctx->d_counters + CNT_ERR_FLAG;
+    P.wait_limit = ctx->wait_limit;
     static int pdl_early = -1;
     if (pdl_early < 0) {
         const char* e = getenv("SLAI_PDL_EARLY");
@@ -166,6 +180,7 @@ int gemv_fill_params(slai_ctx* ctx, const GemvLaunch& L, size_t dig_region, int 
     P.pdl = L.pdl ? (pdl_early ? 2 : 1) : 0;
     P.pf_ptr = reinterpret_cast<const char*>(L.prefetch);
     P.pf_lines = L.prefetch ? (int)((L.prefetch_bytes + 127) / 128) : 0;
+    P.ahead = L.ahead;
     P.xr = 0;
     P.xi_slots = nullptr;
     P.xl_sum = nullptr;
@@ -201,8 +216,9 @@ int gemv_fill_params(slai_ctx* ctx, const GemvLaunch& L, size_t dig_region, int 
         }
     }
 #ifdef SLAI_TRACE
-    P.trace = reinterpret_cast<unsigned long long*>(ctx->d_scratch);  // the debug driver sizes the scratch first
-    P.wtrace = nullptr;
+    // every launch stamps into its own slot of a 64-deep ring: consecutive kernels overlap under dependent launch
+    P.trace = ctx->trace_buf + (size_t)(ctx->trace_launches++ % 64) * TRACE_BLOCKS * TRACE_POINTS;
+    P.tl = ctx->tl;
 #endif
     const size_t need = gemv_dig_region(L.fmt, K);
     if (dig_region == 0) dig_region = need;

@@ -35,32 +35,14 @@ SLAI_HD uint4 lds16(uint32_t addr) {
     return r;
 #endif
 }
-// Predicated loads: lanes with pred == false get zeros and do not touch shared memory (no branch).
-SLAI_HD uint4 lds16_if(bool pred, uint32_t addr) {
+SLAI_HD uint32_t lds32(uint32_t addr) {
 #ifdef __CUDA_ARCH__
-    uint4 r;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %5, 0;\n\tmov.u32 %0, 0;\n\tmov.u32 %1, 0;\n\tmov.u32 %2, 0;\n\tmov.u32 %3, 0;\n\t"
-        "@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n\t}"
-        : "=&r"(r.x), "=&r"(r.y), "=&r"(r.z), "=&r"(r.w)
-        : "r"(addr), "r"((uint32_t)pred));
+    uint32_t r;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(r) : "r"(addr));
     return r;
 #else
-    uint4 r = make_uint4(0u, 0u, 0u, 0u);
-    if (pred) memcpy(&r, hostemu::warp->smem + addr, 16);
-    return r;
-#endif
-}
-SLAI_HD uint2 lds8_if(bool pred, uint32_t addr) {
-#ifdef __CUDA_ARCH__
-    uint2 r;
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %3, 0;\n\tmov.u32 %0, 0;\n\tmov.u32 %1, 0;\n\t@p ld.shared.v2.u32 {%0,%1}, [%2];\n\t}"
-                 : "=&r"(r.x), "=&r"(r.y)
-                 : "r"(addr), "r"((uint32_t)pred));
-    return r;
-#else
-    uint2 r = make_uint2(0u, 0u);
-    if (pred) memcpy(&r, hostemu::warp->smem + addr, 8);
+    uint32_t r;
+    memcpy(&r, hostemu::warp->smem + addr, 4);
     return r;
 #endif
 }
@@ -102,15 +84,32 @@ SLAI_HD float fma(float a, float b, float c) {
     return (float)((double)a * (double)b + (double)c);  // single rounding, like fmaf
 #endif
 }
-// D = A(16x32, row, s8) * B(32x8, col, s8) + D (s32).  Lane (g = lane/4, t = lane%4):
-//   a0 = A[g][4t..4t+3], a1 = A[g+8][4t..], a2 = A[g][16+4t..], a3 = A[g+8][16+4t..]   (4 x s8 per register)
+// D = A(16x32, row) * B(32x8, col, s8) + D (s32); A holds s8 or (UA) u8 values.  Lane (g = lane/4, t = lane%4):
+//   a0 = A[g][4t..4t+3], a1 = A[g+8][4t..], a2 = A[g][16+4t..], a3 = A[g+8][16+4t..]   (4 x 8 bit per register)
 //   b0 = B[4t..4t+3][g], b1 = B[16+4t..][g];   c0,c1 = D[g][2t..2t+1], c2,c3 = D[g+8][2t..2t+1]
-SLAI_HD void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+// ZERO: D = A * B (the accumulator input is the constant zero, no registers are cleared first).
+template <bool UA, bool ZERO>
+SLAI_HD void mma_i8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
 #ifdef __CUDA_ARCH__
-    asm(
-        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    if (ZERO) {
+        if (UA)
+            asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+        else
+            asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+    } else {
+        if (UA)
+            asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+        else
+            asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
 #else
     hostemu::Warp* W = hostemu::warp;
     const int lane = hostemu::lane;
@@ -120,7 +119,8 @@ SLAI_HD void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t
     auto A = [&](int row, int k) {
         const int l = (row & 7) * 4 + ((k & 15) >> 2);
         const int reg = (row >= 8 ? 1 : 0) + (k >= 16 ? 2 : 0);
-        return (int)(signed char)((W->a[l][reg] >> (8 * (k & 3))) & 0xFF);
+        const uint32_t byte = (W->a[l][reg] >> (8 * (k & 3))) & 0xFF;
+        return UA ? (int)byte : (int)(signed char)byte;
     };
     auto B = [&](int k, int n) {
         const int l = n * 4 + ((k & 15) >> 2);
@@ -130,7 +130,7 @@ SLAI_HD void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t
     const int g = lane >> 2, t = lane & 3;
     for (int i = 0; i < 4; i++) {
         const int row = g + (i >= 2 ? 8 : 0), col = 2 * t + (i & 1);
-        int s = c[i];
+        int s = ZERO ? 0 : c[i];
         for (int k = 0; k < 32; k++) s += A(row, k) * B(k, col);
         c[i] = s;
     }
@@ -144,52 +144,77 @@ namespace gemvfmt {
 
 using namespace frag;
 
-// Shared-space byte addresses of the staged activation vector: four planes of s8 digits (plane p at
-// dig + p*plane, element k at byte k) and per-sub-block digit sums (4 x s32 per sub-block of SV_GRAN elements).
+// Shared-space byte addresses of the staged activation vector:
+//   dig   four planes of s8 digits (plane p at dig + p*plane, element k at byte k)
+//   sv    per-sub-block digit sums: Q6_K 4 x s32 per 16 elements; Q4_K / Q5_K a byte table for the tensor
+//         cores, per 256-element step eight rows (digit plane q, part: row 2q = high, 2q+1 = low base-128 digit of
+//         the sum) of 16 bytes: byte j = sub-block j of the step, bytes 8..15 zero
+//   zero  256 zero bytes: lanes whose B column belongs to the other sub-block read their operand here
 struct Smem {
-    uint32_t dig, plane, sv;
+    uint32_t dig, plane, sv, zero;
 };
+constexpr int ZERO_BYTES = 256;
 
 struct LaneCtx {
     int lane, g, t;
-    bool bact;        // this lane supplies non-zero B values (its column belongs to its own sub-block)
-    uint32_t bdig;    // digit plane of this lane's B column (g & 3)
+    uint32_t bbase;   // this lane's B operand of step s, sub-block offset o is at bbase + s * bmul + o
+    uint32_t bmul;    // bytes of digits per step (0 for lanes that read zeros)
     float wd0, wd1;   // weights of the two digits whose sums this lane holds (digits 2(t&1), 2(t&1)+1)
+    float wq;         // weight of digit plane t (Q4_K / Q5_K: the lane holds that plane's sum for the minimum term)
 };
 
+// F::BOFF(t): byte offset inside a step's digits of the first operand of lane t; F::STEP digits per step;
+// F::PRESCALE: factor the integer sums carry (folded into the digit weights).
+template <class F>
 SLAI_HD void lane_init(LaneCtx& L, int lane, const Smem& S) {
     L.lane = lane;
     L.g = lane >> 2;
     L.t = lane & 3;
-    L.bact = (L.t >> 1) == (L.g >> 2);
-    L.bdig = S.dig + (L.g & 3) * S.plane;
-    L.wd0 = digit_weight(2 * (L.t & 1));
-    L.wd1 = digit_weight(2 * (L.t & 1) + 1);
+    const bool bact = (L.t >> 1) == (L.g >> 2);  // the lane's column belongs to its own sub-block
+    L.bbase = bact ? S.dig + (L.g & 3) * S.plane + F::boff(L.t) : S.zero;
+    L.bmul = bact ? F::STEP : 0;
+    L.wd0 = digit_weight(2 * (L.t & 1)) * F::PRESCALE;
+    L.wd1 = digit_weight(2 * (L.t & 1) + 1) * F::PRESCALE;
+    L.wq = digit_weight(L.t);
 }
 
 SLAI_HD float combine(int p0, int p1, const LaneCtx& L) { return prim::fma((float)p1, L.wd1, (float)p0 * L.wd0); }
+SLAI_HD uint32_t byte_of(uint32_t w, int i) { return (w >> (8 * i)) & 0xFFu; }
 
 // Every format provides
 //   STEP      elements of K per tile-step block          SV_GRAN  elements per digit-sum entry (0: none)
 //   compute   one tile-step block at shared address `blk` (K step number `step`): accumulates rows g and g+8
 // ---- Q4_K / Q5_K ---------------------------------------------------------------------------
+// Block header (layout.cuh): row r at 20 r = { f16 d, f16 dmin, u8 sc[8] in lane order, u8 m[8] }.
+//  * main term: per (ci, nib) two MMAs give the lane the sums of its own sub-block for two digits; they are
+//    multiplied by the sub-block's 6-bit scale and added up in integers.  Q4_K feeds the high nibbles unshifted
+//    (16 q as u8) and multiplies the low-nibble scales by 16 instead: every sum carries the factor 16.
+//  * minimum term: sum_j m[r][j] * S_j (S_j = digit sums of sub-block j) is one more MMA per step: A = the m bytes
+//    of the 16 rows, B = the byte table of the sums; lane t ends up with the sum for digit plane t.
 template <bool FIVE>
 struct K45 {
     static constexpr int FMT = FIVE ? 13 : 12;
     static constexpr int STEP = 256;
     static constexpr int SV_GRAN = 32;
+    static constexpr float PRESCALE = FIVE ? 1.0f : 0.0625f;
+    static constexpr int QOFF = FIVE ? 320 + 512 : 320;
+    SLAI_HD static uint32_t boff(int t) { return 64 * (t >> 1) + 16 * (t & 1); }
     SLAI_HD static void compute(uint32_t blk, int step, const LaneCtx& L, const Smem& S, float& accA, float& accB) {
-        const uint4 hA = prim::lds16(blk + 16 * L.g), hB = prim::lds16(blk + 16 * (L.g + 8));
-        uint4 hqA = hA, hqB = hB;
+        const uint32_t hA = blk + 20 * L.g, hB = hA + 160;
+        const uint32_t ddA = prim::lds32(hA), ddB = prim::lds32(hB);
+        const uint32_t scA = prim::lds32(hA + 4 + 4 * (L.t >> 1)), scB = prim::lds32(hB + 4 + 4 * (L.t >> 1));
+        const uint32_t mA = prim::lds32(hA + 12 + 4 * (L.t & 1)), mB = prim::lds32(hB + 12 + 4 * (L.t & 1));
+        const uint32_t bq = prim::lds32(S.sv + 128 * step + 16 * L.g + 4 * L.t);
+        int cq[4];
+        prim::mma_i8<true, true>(cq, mA, mB, 0u, 0u, bq, 0u);
+        uint4 hqA = make_uint4(0u, 0u, 0u, 0u), hqB = hqA;
         if (FIVE) {
-            hqA = prim::lds16(blk + 256 + 32 * L.g + 16 * (L.t & 1));
-            hqB = prim::lds16(blk + 256 + 32 * (L.g + 8) + 16 * (L.t & 1));
+            hqA = prim::lds16(blk + 320 + 32 * L.g + 16 * (L.t & 1));
+            hqB = prim::lds16(blk + 320 + 32 * (L.g + 8) + 16 * (L.t & 1));
         }
-        const uint32_t q0 = blk + (FIVE ? 768 : 256) + 16 * L.lane;
-        const int tsh = 16 * (L.t >> 1);  // this lane's sub-blocks are 2(t>>1)+nib (+4 for ci = 1)
-        const uint32_t yA = hA.y >> tsh, zA = hA.z >> tsh, wA = hA.w >> tsh;
-        const uint32_t yB = hB.y >> tsh, zB = hB.z >> tsh, wB = hB.w >> tsh;
-        int PA0 = 0, PA1 = 0, QA0 = 0, QA1 = 0, PB0 = 0, PB1 = 0, QB0 = 0, QB1 = 0;
+        const uint32_t q0 = blk + QOFF + 16 * L.lane;
+        const uint32_t ba = L.bbase + (uint32_t)step * L.bmul;
+        int PA0 = 0, PA1 = 0, PB0 = 0, PB1 = 0;
 #pragma unroll
         for (int ci = 0; ci < 2; ci++) {
             const uint4 qA = prim::lds16(q0 + (ci * 2) * 512), qB = prim::lds16(q0 + (ci * 2 + 1) * 512);
@@ -198,37 +223,32 @@ struct K45 {
             const uint32_t hBx = hqB.x >> hsh, hBy = hqB.y >> hsh, hBz = hqB.z >> hsh, hBw = hqB.w >> hsh;
 #pragma unroll
             for (int nib = 0; nib < 2; nib++) {
-                const int j = 4 * ci + 2 * (L.t >> 1) + nib;  // sub-block (of 32) inside the super-block
-                const uint4 bv = prim::lds16_if(L.bact, L.bdig + 256 * step + 32 * j + 16 * (L.t & 1));
-                int c[4] = {0, 0, 0, 0};
+                // sub-block 4 ci + 2 (t >> 1) + nib of the step
+                const uint4 bv = prim::lds16(ba + 128 * ci + 32 * nib);
+                int c[4];
+                uint32_t sA = byte_of(scA, 2 * ci + nib), sB = byte_of(scB, 2 * ci + nib);
                 if (FIVE) {
-                    prim::mma_s8(c, q5_nibs(qA.x, hAx, nib), q5_nibs(qB.x, hBx, nib), q5_nibs(qA.y, hAy, nib), q5_nibs(qB.y, hBy, nib), bv.x, bv.y);
-                    prim::mma_s8(c, q5_nibs(qA.z, hAz, nib), q5_nibs(qB.z, hBz, nib), q5_nibs(qA.w, hAw, nib), q5_nibs(qB.w, hBw, nib), bv.z, bv.w);
+                    prim::mma_i8<true, true>(c, q5_nibs(qA.x, hAx, nib), q5_nibs(qB.x, hBx, nib), q5_nibs(qA.y, hAy, nib), q5_nibs(qB.y, hBy, nib), bv.x, bv.y);
+                    prim::mma_i8<true, false>(c, q5_nibs(qA.z, hAz, nib), q5_nibs(qB.z, hBz, nib), q5_nibs(qA.w, hAw, nib), q5_nibs(qB.w, hBw, nib), bv.z, bv.w);
                 } else {
-                    prim::mma_s8(c, q4_nibs(qA.x, nib), q4_nibs(qB.x, nib), q4_nibs(qA.y, nib), q4_nibs(qB.y, nib), bv.x, bv.y);
-                    prim::mma_s8(c, q4_nibs(qA.z, nib), q4_nibs(qB.z, nib), q4_nibs(qA.w, nib), q4_nibs(qB.w, nib), bv.z, bv.w);
+                    const uint32_t mk = nib ? 0xF0F0F0F0u : 0x0F0F0F0Fu;
+                    prim::mma_i8<true, true>(c, qA.x & mk, qB.x & mk, qA.y & mk, qB.y & mk, bv.x, bv.y);
+                    prim::mma_i8<true, false>(c, qA.z & mk, qB.z & mk, qA.w & mk, qB.w & mk, bv.z, bv.w);
+                    if (nib == 0) {
+                        sA <<= 4;
+                        sB <<= 4;
+                    }
                 }
-                const uint2 sv = prim::lds8(S.sv + 16 * (step * 8 + j) + 8 * (L.t & 1));
-                int scA, mA, scB, mB;
-                if (ci == 0) {
-                    scA = (yA >> (8 * nib)) & 63; mA = (zA >> (8 * nib)) & 63;
-                    scB = (yB >> (8 * nib)) & 63; mB = (zB >> (8 * nib)) & 63;
-                } else {
-                    scA = ((wA >> (8 * nib)) & 0xF) | (((yA >> (8 * nib + 6)) & 3) << 4);
-                    mA = ((wA >> (8 * nib + 4)) & 0xF) | (((zA >> (8 * nib + 6)) & 3) << 4);
-                    scB = ((wB >> (8 * nib)) & 0xF) | (((yB >> (8 * nib + 6)) & 3) << 4);
-                    mB = ((wB >> (8 * nib + 4)) & 0xF) | (((zB >> (8 * nib + 6)) & 3) << 4);
-                }
-                PA0 += scA * c[0]; PA1 += scA * c[1]; QA0 += mA * (int)sv.x; QA1 += mA * (int)sv.y;
-                PB0 += scB * c[2]; PB1 += scB * c[3]; QB0 += mB * (int)sv.x; QB1 += mB * (int)sv.y;
+                PA0 += (int)sA * c[0]; PA1 += (int)sA * c[1];
+                PB0 += (int)sB * c[2]; PB1 += (int)sB * c[3];
             }
         }
-        const float dA = prim::h2f(hA.x & 0xFFFF), mnA = prim::h2f(hA.x >> 16);
-        const float dB = prim::h2f(hB.x & 0xFFFF), mnB = prim::h2f(hB.x >> 16);
+        const float dA = prim::h2f(ddA & 0xFFFF), mnA = prim::h2f(ddA >> 16);
+        const float dB = prim::h2f(ddB & 0xFFFF), mnB = prim::h2f(ddB >> 16);
         accA = prim::fma(dA, combine(PA0, PA1, L), accA);
-        accA = prim::fma(-mnA, combine(QA0, QA1, L), accA);
+        accA = prim::fma(-mnA, (float)(cq[0] * 128 + cq[1]) * L.wq, accA);
         accB = prim::fma(dB, combine(PB0, PB1, L), accB);
-        accB = prim::fma(-mnB, combine(QB0, QB1, L), accB);
+        accB = prim::fma(-mnB, (float)(cq[2] * 128 + cq[3]) * L.wq, accB);
     }
 };
 using Q4K = K45<false>;
@@ -239,8 +259,11 @@ struct Q6K {
     static constexpr int FMT = 14;
     static constexpr int STEP = 256;
     static constexpr int SV_GRAN = 16;
+    static constexpr float PRESCALE = 1.0f;
+    SLAI_HD static uint32_t boff(int t) { return 16 * (t >> 1) + 8 * (t & 1); }
     SLAI_HD static void compute(uint32_t blk, int step, const LaneCtx& L, const Smem& S, float& accA, float& accB) {
         int PA0 = 0, PA1 = 0, PB0 = 0, PB1 = 0;
+        const uint32_t ba = L.bbase + (uint32_t)step * L.bmul;
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             const uint2 qhA = prim::lds8(blk + 2048 + (h * 2) * 256 + 8 * L.lane), qhB = prim::lds8(blk + 2048 + (h * 2 + 1) * 256 + 8 * L.lane);
@@ -254,10 +277,10 @@ struct Q6K {
                     const int sh = 2 * pair + 4 * nib;
                     const int j8 = 4 * nib + 2 * pair + (L.t >> 1);  // sub-block (of 16) inside the half
                     const int j = 16 * step + 8 * h + j8;
-                    const uint2 bv = prim::lds8_if(L.bact, L.bdig + 16 * j + 8 * (L.t & 1));
-                    int c[4] = {0, 0, 0, 0};
-                    prim::mma_s8(c, q6_nibs(qlA.x, qhA.x >> sh, nib), q6_nibs(qlB.x, qhB.x >> sh, nib), q6_nibs(qlA.y, qhA.y >> sh, nib),
-                                 q6_nibs(qlB.y, qhB.y >> sh, nib), bv.x, bv.y);
+                    const uint2 bv = prim::lds8(ba + 128 * h + 64 * nib + 32 * pair);
+                    int c[4];
+                    prim::mma_i8<false, true>(c, q6_nibs(qlA.x, qhA.x >> sh, nib), q6_nibs(qlB.x, qhB.x >> sh, nib), q6_nibs(qlA.y, qhA.y >> sh, nib),
+                                              q6_nibs(qlB.y, qhB.y >> sh, nib), bv.x, bv.y);
                     const uint2 sv = prim::lds8(S.sv + 16 * j + 8 * (L.t & 1));
                     // int8 scale of sub-block j8: byte j8 of the half's 8 scale bytes
                     const uint32_t wsA = j8 < 4 ? scwA.x : scwA.y, wsB = j8 < 4 ? scwB.x : scwB.y;
@@ -278,15 +301,18 @@ struct Q80 {
     static constexpr int FMT = 8;
     static constexpr int STEP = 128;
     static constexpr int SV_GRAN = 0;
+    static constexpr float PRESCALE = 1.0f;
+    SLAI_HD static uint32_t boff(int t) { return 32 * (t >> 1) + 16 * (t & 1); }
     SLAI_HD static void compute(uint32_t blk, int step, const LaneCtx& L, const Smem& S, float& accA, float& accB) {
+        const uint32_t ba = L.bbase + (uint32_t)step * L.bmul;
 #pragma unroll
         for (int ci = 0; ci < 2; ci++) {
             const int b = 2 * ci + (L.t >> 1);  // GGUF block inside the step
             const uint4 qA = prim::lds16(blk + 128 + (ci * 2) * 512 + 16 * L.lane), qB = prim::lds16(blk + 128 + (ci * 2 + 1) * 512 + 16 * L.lane);
-            const uint4 bv = prim::lds16_if(L.bact, L.bdig + 128 * step + 32 * b + 16 * (L.t & 1));
-            int c[4] = {0, 0, 0, 0};
-            prim::mma_s8(c, qA.x, qB.x, qA.y, qB.y, bv.x, bv.y);
-            prim::mma_s8(c, qA.z, qB.z, qA.w, qB.w, bv.z, bv.w);
+            const uint4 bv = prim::lds16(ba + 64 * ci);
+            int c[4];
+            prim::mma_i8<false, true>(c, qA.x, qB.x, qA.y, qB.y, bv.x, bv.y);
+            prim::mma_i8<false, false>(c, qA.z, qB.z, qA.w, qB.w, bv.z, bv.w);
             const float sA = prim::h2f(prim::lds_u16(blk + 8 * L.g + 2 * b)), sB = prim::h2f(prim::lds_u16(blk + 8 * (L.g + 8) + 2 * b));
             accA = prim::fma(sA, combine(c[0], c[1], L), accA);
             accB = prim::fma(sB, combine(c[2], c[3], L), accB);

@@ -5,8 +5,8 @@
 //     integer MMA m16n8k32 (s8 x s8 -> s32): its A registers are packed quants, four per register, obtained
 //     from the GGUF nibbles / bytes with one or two logic instructions (no int->float conversion).
 //   * The f32 activation vector is scaled by a power of two and rounded to a 27-bit fixed-point integer
-//     V_k, which is split into four signed base-128 digits (V = d0*2^21 + d1*2^14 + d2*2^7 + d3, each digit
-//     in [-64, 63]).  The digits occupy four of the eight MMA columns, so `sum_k q_k * V_k` is evaluated
+//     V_k, which is split into four signed base-256 digits (V = d3*2^24 + d2*2^16 + d1*2^8 + d0, the low three
+//     in [-128, 127]).  The digits occupy four of the eight MMA columns, so `sum_k q_k * V_k` is evaluated
 //     exactly in integer arithmetic (the only rounding is that of V_k, relative 2^-26 of max|v|).
 //   * The other factor of two in the columns separates two sub-blocks with different scales: lanes t < 2
 //     carry one sub-block, lanes t >= 2 another, and B holds the digits of a sub-block only in its own four
@@ -54,27 +54,30 @@ SLAI_HD void scale_min_k4(int j, uint32_t s0, uint32_t s1, uint32_t s2, uint32_t
 }
 
 // ---- activation digits -------------------------------------------------------------------------
-// V (|V| <= 2^26) -> four balanced base-128 digits, most significant first.
-// low seven bits of V as a signed number in [-64, 63] (the balanced digit V mod 128)
-SLAI_HD int low7(int V) {
+// V (|V| <= 2^26 + 1) -> four signed base-256 digits, V = d3*2^24 + d2*2^16 + d1*2^8 + d0 with d0..d2 in [-128, 127]:
+// adding 0x808080 turns the three low bytes of the two's-complement word into the digits biased by 128, and flipping
+// their top bits removes the bias -- two instructions for all four digits, packed one per byte (byte i = digit i).
+SLAI_HD uint32_t digits_word(int V) { return ((uint32_t)V + 0x00808080u) ^ 0x00808080u; }
+// Transpose four elements' digit words into four plane words (plane p = digit p of the four elements, in order).
+SLAI_HD uint32_t perm_bytes(uint32_t a, uint32_t b, uint32_t sel) {
 #ifdef __CUDA_ARCH__
-    int d;
-    asm("bfe.s32 %0, %1, 0, 7;" : "=r"(d) : "r"(V));
-    return d;
+    return __byte_perm(a, b, sel);
 #else
-    return ((V + 64) & 127) - 64;
+    const uint64_t both = ((uint64_t)b << 32) | a;
+    uint32_t r = 0;
+    for (int i = 0; i < 4; i++) r |= (uint32_t)((both >> (8 * ((sel >> (4 * i)) & 7))) & 0xFF) << (8 * i);
+    return r;
 #endif
 }
-SLAI_HD void split_digits(int V, int (&d)[4]) {
-    d[3] = low7(V);
-    V = (V - d[3]) >> 7;
-    d[2] = low7(V);
-    V = (V - d[2]) >> 7;
-    d[1] = low7(V);
-    V = (V - d[1]) >> 7;
-    d[0] = V;
+SLAI_HD void digit_planes(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, uint32_t (&plane)[4]) {
+    const uint32_t t0 = perm_bytes(w0, w1, 0x5140), t1 = perm_bytes(w2, w3, 0x5140);
+    const uint32_t t2 = perm_bytes(w0, w1, 0x7362), t3 = perm_bytes(w2, w3, 0x7362);
+    plane[0] = perm_bytes(t0, t1, 0x5410);
+    plane[1] = perm_bytes(t0, t1, 0x7632);
+    plane[2] = perm_bytes(t2, t3, 0x5410);
+    plane[3] = perm_bytes(t2, t3, 0x7632);
 }
-// weight of digit i: 2^(21 - 7 i)
-SLAI_HD float digit_weight(int i) { return i == 0 ? 2097152.0f : i == 1 ? 16384.0f : i == 2 ? 128.0f : 1.0f; }
+// weight of digit plane i: 256^i
+SLAI_HD float digit_weight(int i) { return i == 0 ? 1.0f : i == 1 ? 256.0f : i == 2 ? 65536.0f : 16777216.0f; }
 
 }  // namespace frag

@@ -16,7 +16,7 @@
 // streaming the next phase's weights while the block of threads waits at the grid barrier between phases.
 //
 // Arithmetic.  Packed quants, four per register, go to the integer tensor-core MMA (mma.sync.m16n8k32 s8)
-// against base-128 digit planes of the activation vector, staged once per phase in shared memory
+// against base-256 digit planes of the activation vector, staged once per phase in shared memory
 // (gemv_frag.cuh); block scales are applied to the per-sub-block integer sums.
 //
 // Every mbarrier wait is bounded; on expiry the warp raises the error flag and stops waiting.
@@ -71,9 +71,11 @@ struct GemvParams {
     int kv_f16;
     long long kv_pos_stride, kv_head_stride;
     unsigned int* err_flag;
+    unsigned int wait_limit;  // rounds a bounded wait polls before it raises err_flag and goes on
     int pdl;  // launched with programmatic stream serialization (2: trigger the dependent launch at the start)
     const char* pf_ptr;  // memory the next kernel reads first: prefetched into L2 by one block (pf_lines x 128 bytes)
     int pf_lines;
+    PrefetchPlan ahead;  // weights of a later kernel, pulled into L2 by all blocks at the start
     // tensor-parallel exchange over peer memory (xr == 0: unused)
     int xr, xrank;                       // ranks in the group, this rank
     uint2* xo_slot[XCHG_MAX_RANKS];      // EPI_XCHG: this rank's slot of the outgoing exchange in every rank's region
@@ -84,19 +86,14 @@ struct GemvParams {
     uint2* xl_sum;                       // non-null: two-level sum -- each block sums a slice over the ranks into this local
                                          // tagged buffer, then every block reads the whole sum from it
 #ifdef SLAI_TRACE
-    unsigned long long* trace;   // debug build only: per block of threads 8 x (globaltimer, clock64)
-    unsigned long long* wtrace;  // debug build only: per warp (loop start, loop end, cycles waiting for the ring, units)
+    unsigned long long* trace;   // trace build only: per block of threads TRACE_POINTS globaltimer stamps
+    unsigned long long* tl;      // trace build only: the context's launch timeline
 #endif
 };
 
 #ifdef SLAI_TRACE
-#define SLAI_TRACE_POINT(k)                                                                     \
-    if (threadIdx.x == 0 && P.trace) {                                                           \
-        unsigned long long gt;                                                                   \
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));                                    \
-        P.trace[(blockIdx.x * 8 + (k)) * 2] = gt;                                                \
-        P.trace[(blockIdx.x * 8 + (k)) * 2 + 1] = (unsigned long long)clock64();                 \
-    }
+#define SLAI_TRACE_POINT(k) \
+    if (threadIdx.x == 0 && P.trace) P.trace[blockIdx.x * TRACE_POINTS + (k)] = slai_globaltimer();
 #else
 #define SLAI_TRACE_POINT(k)
 #endif
@@ -118,8 +115,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t a, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait: returns false (and raises the error flag) if the phase does not complete.
-__device__ __forceinline__ bool mbar_wait(uint32_t a, uint32_t parity, unsigned int* err_flag) {
-    for (int i = 0; i < (1 << 20); i++) {
+__device__ __forceinline__ bool mbar_wait(uint32_t a, uint32_t parity, unsigned int limit, unsigned int* err_flag) {
+    for (unsigned int i = 0; i < limit; i++) {
         if (mbar_try_wait(a, parity)) return true;
         if (i > 1024) __nanosleep(64);
     }
@@ -191,7 +188,7 @@ __device__ __forceinline__ float4 xchg_gather(const GemvParams& P, int i, unsign
     for (int r = 0; r < XCHG_MAX_RANKS; r++)
         if (r < P.xr) {
             for (int it = 0; !(a[r].y == seq && a[r].w == seq && b[r].y == seq && b[r].w == seq); it++) {
-                if (it > (1 << 20)) {
+                if ((unsigned int)it > P.wait_limit) {
                     atomicExch(P.err_flag, 3u);
                     break;
                 }
@@ -210,7 +207,7 @@ __device__ __forceinline__ float4 xchg_local(const GemvParams& P, int i, unsigne
     uint4 a, b;
     xchg_load(src, a, b);
     for (int it = 0; !(a.y == seq && a.w == seq && b.y == seq && b.w == seq); it++) {
-        if (it > (1 << 20)) {
+        if ((unsigned int)it > P.wait_limit) {
             atomicExch(P.err_flag, 3u);
             break;
         }
@@ -221,7 +218,7 @@ __device__ __forceinline__ float4 xchg_local(const GemvParams& P, int i, unsigne
 }
 
 // Stage the activation vector: optional normalisation, power-of-two scaling so that max|v| lands in
-// [2^25, 2^26), rounding to integers, split into four base-128 digit planes (gemv_frag.cuh), and per-sub-block
+// [2^25, 2^26), rounding to integers, split into four base-256 digit planes (gemv_frag.cuh), and per-sub-block
 // digit sums (for the `- dmin*m * sum(v)` term of Q4_K / Q5_K and the -32 offset of Q6_K).  Returns 1/scale.
 // The vector is read once (L2 loads: inside the persistent kernel it was written by other SMs during the same
 // launch, so L1 must not be trusted) and kept in registers between the passes when K <= 12288; longer vectors are
@@ -308,7 +305,9 @@ __device__ __forceinline__ float stage_vector(const int PRO_ARG, const GemvParam
 #pragma unroll 1
         for (int i = tid; i < n4; i += THREADS) stats(__ldcg(v4 + i), PRO != PRO_NONE ? __ldg(w4p + i) : zero4);
     }
+    SLAI_TRACE_POINT(6)
     block_sum_max(sum, mx, stat);
+    SLAI_TRACE_POINT(7)
     if (PRO != PRO_NONE) {
         mul = 1.0f / sqrtf(sum / (float)K + P.eps);
         mx *= mul;
@@ -329,6 +328,8 @@ __device__ __forceinline__ float stage_vector(const int PRO_ARG, const GemvParam
     }
     unsigned char* dig = reinterpret_cast<unsigned char*>(__cvta_shared_to_generic(S.dig));
     int4* sv = reinterpret_cast<int4*>(__cvta_shared_to_generic(S.sv));
+    unsigned char* svb = reinterpret_cast<unsigned char*>(sv);  // Q4_K / Q5_K: byte table of the sums (gemv_formats.cuh)
+    if (tid < ZERO_BYTES / 4) reinterpret_cast<uint32_t*>(__cvta_shared_to_generic(S.zero))[tid] = 0u;
 #pragma unroll 1
     for (int i = tid; i < np4; i += THREADS) {  // np4 is a multiple of 64: whole warps run each round together
         float4 x;
@@ -348,19 +349,15 @@ __device__ __forceinline__ float stage_vector(const int PRO_ARG, const GemvParam
                 x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
             }
         }
-        int d0[4], d1[4], d2[4], d3[4];
-        split_digits(__float2int_rn(x.x * scale), d0);
-        split_digits(__float2int_rn(x.y * scale), d1);
-        split_digits(__float2int_rn(x.z * scale), d2);
-        split_digits(__float2int_rn(x.w * scale), d3);
+        // four digits per element in one word (two instructions each), then a 4 x 4 byte transpose into plane words
+        uint32_t pw[4];
+        digit_planes(digits_word(__float2int_rn(x.x * scale)), digits_word(__float2int_rn(x.y * scale)),
+                     digits_word(__float2int_rn(x.z * scale)), digits_word(__float2int_rn(x.w * scale)), pw);
         int sd[4];
 #pragma unroll
         for (int q = 0; q < 4; q++) {
-            // low bytes of the four digits, packed with byte permutes; their sum with one dot-product instruction
-            const uint32_t lo = __byte_perm((uint32_t)d0[q], (uint32_t)d1[q], 0x0040), hi = __byte_perm((uint32_t)d2[q], (uint32_t)d3[q], 0x0040);
-            const uint32_t word = __byte_perm(lo, hi, 0x5410);
-            *reinterpret_cast<uint32_t*>(dig + (size_t)q * S.plane + 4 * i) = word;
-            sd[q] = __dp4a((int)word, 0x01010101, 0);
+            *reinterpret_cast<uint32_t*>(dig + (size_t)q * S.plane + 4 * i) = pw[q];
+            sd[q] = __dp4a((int)pw[q], 0x01010101, 0);  // sum of the four digits
         }
         if (SV_GRAN > 0) {
 #pragma unroll
@@ -370,9 +367,26 @@ __device__ __forceinline__ float stage_vector(const int PRO_ARG, const GemvParam
                 if (SV_GRAN == 32) sd[q] += __shfl_xor_sync(0xffffffffu, sd[q], 4);
             }
             constexpr int LANES = SV_GRAN > 0 ? SV_GRAN / 4 : 1;  // float4 groups per sub-block
-            if ((tid & (LANES - 1)) == 0) sv[i / LANES] = make_int4(sd[0], sd[1], sd[2], sd[3]);
+            if (SV_GRAN == 32) {
+                // sub-block J = i / 8 of step J / 8: every sum (|sum| <= 4096) as two base-128 digits, one byte row per
+                // (digit plane, part); bytes 8..15 of the sub-block's own row index are the zero half of that row
+                if ((tid & 7) == 0) {
+                    const int J = i >> 3;
+                    unsigned char* tab = svb + (J >> 3) * 128;
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const int hi = (sd[q] + 64) >> 7, lo = sd[q] - (hi << 7);
+                        tab[(2 * q) * 16 + (J & 7)] = (unsigned char)hi;
+                        tab[(2 * q + 1) * 16 + (J & 7)] = (unsigned char)lo;
+                    }
+                    *reinterpret_cast<uint2*>(tab + (J & 7) * 16 + 8) = make_uint2(0u, 0u);
+                }
+            } else if ((tid & (LANES - 1)) == 0) {
+                sv[i / LANES] = make_int4(sd[0], sd[1], sd[2], sd[3]);
+            }
         }
     }
+    SLAI_TRACE_POINT(8)
     __syncthreads();
     return 1.0f / scale;
 }
@@ -484,6 +498,7 @@ struct Ring {
     uint32_t c_phase;
     bool alive;
     unsigned int* err_flag;
+    unsigned int wait_limit;
     // producer
     int p_idx, p_stage;
     Split ps;
@@ -491,7 +506,7 @@ struct Ring {
     const uint8_t* p_ptr;
 };
 
-// Shared-memory layout: [staged vector: dig_region bytes][red RED_FLOATS f32][stat 64 f32][mbar][ring]
+// Shared-memory layout: [staged vector: dig_region bytes = zero page, digit planes, digit sums][red RED_FLOATS f32][stat 64 f32][mbar][ring]
 __device__ __forceinline__ uint32_t smem_fixed_bytes(int dig_region) { return (uint32_t)dig_region + RED_FLOATS * 4 + 64 * 4; }
 
 template <class Prog>
@@ -533,7 +548,8 @@ __device__ __forceinline__ void prod_issue(Ring& R, const Prog& prog, int lane, 
 // `nstage` blocks are requested here.
 template <class Prog>
 __device__ __forceinline__ void ring_init(Ring& R, const Prog& prog, int dig_region, int nstage, int stage_stride, int step_bytes,
-                                          unsigned int* err_flag, unsigned char* smem_raw, int lane, int warp) {
+                                          unsigned int* err_flag, unsigned int wait_limit, unsigned char* smem_raw, int lane, int warp,
+                                          unsigned long long* trace = nullptr) {
     const uint32_t base = (uint32_t)__cvta_generic_to_shared(smem_raw);
     const uint32_t mbar_base = base + smem_fixed_bytes(dig_region);
     const uint32_t ring_base = (mbar_base + WARPS * MAX_STAGES * 8 + 127u) & ~127u;
@@ -546,6 +562,7 @@ __device__ __forceinline__ void ring_init(Ring& R, const Prog& prog, int dig_reg
     R.c_phase = 0;
     R.alive = true;
     R.err_flag = err_flag;
+    R.wait_limit = wait_limit;
     R.p_stage = 0;
     R.p_ptr = nullptr;
     if (lane == 0) {
@@ -554,6 +571,9 @@ __device__ __forceinline__ void ring_init(Ring& R, const Prog& prog, int dig_reg
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncwarp();
+#ifdef SLAI_TRACE
+    if (threadIdx.x == 0 && trace) trace[blockIdx.x * TRACE_POINTS + 1] = slai_globaltimer();
+#endif
     // park the producer "before" entry 0 with an exhausted piece: the first prod_issue walks into it
     R.p_idx = -1;
     R.ps.n_waves = 0;
@@ -566,6 +586,9 @@ __device__ __forceinline__ void ring_init(Ring& R, const Prog& prog, int dig_reg
     R.pc.li = R.pc.mat = R.pc.step = 0;
 #pragma unroll 1
     for (int s = 0; s < R.nstage; s++) prod_issue(R, prog, lane, warp);
+#ifdef SLAI_TRACE
+    if (threadIdx.x == 0 && trace) trace[blockIdx.x * TRACE_POINTS + 2] = slai_globaltimer();
+#endif
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -577,12 +600,13 @@ __device__ __forceinline__ void ring_init(Ring& R, const Prog& prog, int dig_reg
 // PRO_MASK / EPI_MASK: bit i set = value i can occur (code for the others is not generated).
 template <class F, int PRO_MASK, int EPI_MASK, bool XIN = false, class Prog>
 __device__ __forceinline__ void gemv_phase(const GemvParams& P, Ring& R, const Prog& prog, unsigned char* smem_raw,
-                                           const int NMAT, const int PRO, const int EPI) {
+                                           const int NMAT, const int PRO, const int EPI, const bool red_cleared = false) {
 #define SLAI_EPI_IS(x) ((((EPI_MASK) >> (x)) & 1) && EPI == (x))
     const int K = P.K;
     const int Kp = (K + 255) & ~255;
     Smem S;
-    S.dig = (uint32_t)__cvta_generic_to_shared(smem_raw);
+    S.zero = (uint32_t)__cvta_generic_to_shared(smem_raw);
+    S.dig = S.zero + ZERO_BYTES;
     S.plane = Kp + 32;  // planes 32 bytes apart modulo 128: the four digit columns of a sub-block hit different banks
     S.sv = S.dig + 4 * S.plane;
     float* red = reinterpret_cast<float*>(smem_raw + P.dig_region);
@@ -590,20 +614,39 @@ __device__ __forceinline__ void gemv_phase(const GemvParams& P, Ring& R, const P
 
     const int tid = threadIdx.x, warp = tid >> 5;
     LaneCtx L;
-    lane_init(L, tid & 31, S);
+    lane_init<F>(L, tid & 31, S);
 
     const Split sp = make_split(ProgGeom{P.nsteps, NMAT, P.items_base, P.items_rem});
 
-    for (int i = tid; i < WAVE * WARPS * NMAT * 16; i += THREADS) red[i] = 0.f;
-    SLAI_TRACE_POINT(2)
+    if (!red_cleared)
+        for (int i = tid; i < WAVE * WARPS * NMAT * 16; i += THREADS) red[i] = 0.f;
+    SLAI_TRACE_POINT(5)
     const float inv_scale = stage_vector<F::SV_GRAN, ((PRO_MASK >> PRO_LN) & 1) != 0, XIN>(PRO, P, S, stat, Kp);
-    SLAI_TRACE_POINT(3)
+    SLAI_TRACE_POINT(9)
 
-#ifdef SLAI_TRACE
-    long long w_t0 = clock64(), w_wait = 0, w_units = 0;
-#endif
     Cursor c;
     for (c.wave = 0; c.wave < sp.n_waves; c.wave++) {
+        // Epilogue operands that do not depend on the products (residual, bias, RoPE cos / sin) are requested now and
+        // used after the loop: their L2 latency hides behind the wave instead of standing at the end of the kernel.
+        float e_resid = 0.f, e_bias = 0.f, e_cs = 1.f, e_sn = 0.f;
+        {
+            const int items = min(WAVE, sp.n_local - c.wave * WAVE);
+            if (tid < items * 16) {
+                const int li = tid >> 4, r = tid & 15;
+                const int item = sp.i0 + c.wave * WAVE + li;
+                const GemvSeg sg = seg_pick(P, NMAT == 2 ? 0 : seg_of_tile(P, item));
+                const int row_in_seg = (NMAT == 2 ? item : item - sg.tile0) * 16 + r;
+                const bool valid = row_in_seg < sg.rows;
+                const int orow = sg.out_off + row_in_seg;
+                if (sg.bias && valid) e_bias = sg.bias[row_in_seg];
+                if ((SLAI_EPI_IS(EPI_RESID) || (SLAI_EPI_IS(EPI_XCHG) && P.xrank == 0)) && valid) e_resid = __ldcg(P.resid + orow);
+                if (SLAI_EPI_IS(EPI_QKV) && P.rope && sg.role < 2 && P.rope_cs) {
+                    const int hd = (row_in_seg & ~1) % P.head_size;
+                    e_cs = __ldcg(P.rope_cs + hd);
+                    e_sn = __ldcg(P.rope_cs + hd + 1);
+                }
+            }
+        }
         cursor_wave(c, sp, warp);
         while (c.u < c.u1) {
             // one run of consecutive steps inside the same (item, matrix)
@@ -611,14 +654,7 @@ __device__ __forceinline__ void gemv_phase(const GemvParams& P, Ring& R, const P
             float accA = 0.f, accB = 0.f;
 #pragma unroll 1
             for (; c.u < run_end; c.u++, c.step++) {
-#ifdef SLAI_TRACE
-                const long long w_a = clock64();
-#endif
-                if (R.alive) R.alive = mbar_wait(R.mbar + 8 * R.c_stage, R.c_phase, R.err_flag);
-#ifdef SLAI_TRACE
-                w_wait += clock64() - w_a;
-                w_units++;
-#endif
+                if (R.alive) R.alive = mbar_wait(R.mbar + 8 * R.c_stage, R.c_phase, R.wait_limit, R.err_flag);
                 F::compute(R.ring + R.c_stage * R.stage_stride, c.step, L, S, accA, accB);
                 __syncwarp();
                 if (L.lane == 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -640,18 +676,9 @@ __device__ __forceinline__ void gemv_phase(const GemvParams& P, Ring& R, const P
             cursor_next_run(c, sp);
         }
         const int wv = c.wave, n_waves = sp.n_waves, n_local = sp.n_local, i0 = sp.i0;
-#ifdef SLAI_TRACE
-        if (P.wtrace && L.lane == 0 && wv + 1 == n_waves) {
-            unsigned long long* wt = P.wtrace + (blockIdx.x * WARPS + warp) * 4;
-            wt[0] = w_t0;
-            wt[1] = clock64();
-            wt[2] = w_wait;
-            wt[3] = w_units;
-        }
-#endif
-        SLAI_TRACE_POINT(4)
+        SLAI_TRACE_POINT(10)
         __syncthreads();
-        SLAI_TRACE_POINT(5)
+        SLAI_TRACE_POINT(11)
         // Epilogue of the wave: thread (li, r) adds the 16 partials of its row in warp order.
         const int items = min(WAVE, n_local - wv * WAVE);
         if (tid < items * 16) {
@@ -671,15 +698,15 @@ __device__ __forceinline__ void gemv_phase(const GemvParams& P, Ring& R, const P
             const int row_in_seg = (NMAT == 2 ? item : item - sg.tile0) * 16 + r;
             const bool valid = row_in_seg < sg.rows;
             const int orow = sg.out_off + row_in_seg;
-            const float bias = (sg.bias && valid) ? sg.bias[row_in_seg] : 0.f;
+            const float bias = e_bias;
             if (SLAI_EPI_IS(EPI_STORE)) {
                 if (valid) P.out[orow] = val[0] + bias;
             } else if (SLAI_EPI_IS(EPI_RESID)) {
-                if (valid) P.out[orow] = __ldcg(P.resid + orow) + (val[0] + bias);
+                if (valid) P.out[orow] = e_resid + (val[0] + bias);
             } else if (SLAI_EPI_IS(EPI_XCHG)) {
                 if (valid) {
                     float y = val[0] + bias;
-                    if (P.xrank == 0) y += __ldcg(P.resid + orow);
+                    if (P.xrank == 0) y += e_resid;
                     const uint2 pkt = make_uint2(__float_as_uint(y), xchg_seq(P, P.xo_idx1));
                     for (int rk = 0; rk < P.xr; rk++) P.xo_slot[rk][orow] = pkt;  // one 8-byte store each: value and tag together
                 }
@@ -699,8 +726,8 @@ __device__ __forceinline__ void gemv_phase(const GemvParams& P, Ring& R, const P
                     const int hd = (row_in_seg & ~1) % P.head_size;
                     float sn, cs;
                     if (P.rope_cs) {
-                        cs = __ldcg(P.rope_cs + hd);
-                        sn = __ldcg(P.rope_cs + hd + 1);
+                        cs = e_cs;
+                        sn = e_sn;
                     } else {
                         sincosf((float)pos * P.rope_theta[hd >> 1], &sn, &cs);
                     }
@@ -719,7 +746,7 @@ __device__ __forceinline__ void gemv_phase(const GemvParams& P, Ring& R, const P
                 }
             }
         }
-        SLAI_TRACE_POINT(6)
+        SLAI_TRACE_POINT(12)
         if (wv + 1 < n_waves) {  // the partial buffer is reused by the next wave
             __syncthreads();
             for (int i = tid; i < WAVE * WARPS * NMAT * 16; i += THREADS) red[i] = 0.f;

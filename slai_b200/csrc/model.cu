@@ -45,6 +45,35 @@ void destroy_graphs(GraphSet& g) {
     for (int i = 0; i < G_COUNT; i++) g.warmed[i] = false;
 }
 
+// Bytes of later weights one kernel asks for ahead of time (PrefetchPlan).  SLAI_AHEAD_MB=0 switches the scheme off.
+size_t ahead_cap_bytes() {
+    static long long cap = -1;
+    if (cap < 0) {
+        const char* e = getenv("SLAI_AHEAD_MB");
+        cap = (e ? atoll(e) : 32) << 20;
+    }
+    return (size_t)cap;
+}
+// Plan for bytes [from, from + cap) of the concatenation of up to three quantised matrices, taken in equal shares
+// from each (they are streamed side by side: q/k/v tiles in turn, gate and up tile by tile).
+PrefetchPlan plan_ahead(const slai_qmatrix* const* ms, int n, size_t from_each, size_t cap) {
+    PrefetchPlan p;
+    if (cap == 0 || n <= 0) return p;
+    size_t total = 0;
+    for (int i = 0; i < n; i++) total += (ms[i] && ms[i]->fmt != SLAI_FMT_F32 && ms[i]->bytes > from_each) ? ms[i]->bytes - from_each : 0;
+    if (total == 0) return p;
+    for (int i = 0; i < n && i < 3; i++) {
+        if (!ms[i] || ms[i]->fmt == SLAI_FMT_F32 || ms[i]->bytes <= from_each) continue;
+        const size_t avail = ms[i]->bytes - from_each;
+        size_t take = total <= cap ? avail : (size_t)((double)avail * (double)cap / (double)total);
+        take &= ~(size_t)15;
+        p.ptr[i] = reinterpret_cast<const char*>(ms[i]->data) + (from_each & ~(size_t)15);
+        p.bytes[i] = take;
+    }
+    return p;
+}
+PrefetchPlan plan_ahead1(const slai_qmatrix* m, size_t from, size_t cap) { return plan_ahead(&m, 1, from, cap); }
+
 GemvSeg seg_of(const slai_qmatrix* m, int row0, int rows, const float* bias, int out_off, int role) {
     GemvSeg s;  // row0 is a multiple of 16 (checked where fused matrices are attached)
     s.w = m->fmt == SLAI_FMT_F32 ? m->data + (size_t)row0 * m->tile_bytes : m->data + (size_t)(row0 / 16) * m->tile_bytes;
@@ -84,6 +113,8 @@ struct slai_llama {
     float* token_embd = nullptr;  // [vocab][dim] f32
     float* out_norm = nullptr;
     float *x = nullptr, *xb = nullptr, *q = nullptr, *hb = nullptr, *hb2 = nullptr, *logits = nullptr;
+    float* logits_part = nullptr;  // tensor parallel with a row-sharded output matrix: this rank's vocab / tp logits
+    bool out_sharded = false;
     void *kcache = nullptr, *vcache = nullptr;
     size_t kv_layer_elems = 0;
     Scalars sc;
@@ -254,6 +285,12 @@ static int llama_record(slai_llama* m, int kind) {
                      SLAI_ERR_INVALID_ARG, "llama: layer %d has unset weights", l);
         void* kc = (char*)m->kcache + (size_t)l * m->kv_layer_elems * esz;
         void* vc = (char*)m->vcache + (size_t)l * m->kv_layer_elems * esz;
+        // Weights are requested one kernel ahead (PrefetchPlan): QKV asks for Wo, attention for the first `cap` bytes of
+        // gate / up, O for their rest, gate/up for Wdown, Wdown for the next layer's q / k / v.
+        const size_t cap = ahead_cap_bytes();
+        const slai_qmatrix* gu[2] = {w.wgate, w.wup};
+        const size_t gu_total = (w.wgate ? w.wgate->bytes : 0) + (w.wup ? w.wup->bytes : 0);
+        const size_t gu_first = gu_total <= cap ? (size_t)-1 >> 1 : (size_t)((double)(w.wgate ? w.wgate->bytes : 0) * (double)cap / (double)gu_total) & ~(size_t)15;
         // 1. xb = rmsnorm(x); q = Wq xb; k,v -> cache[pos]; RoPE(q,k)          transformer.rs:327-347
         const bool fuse_rope = c.rope_variant == 0;
         auto qkv_launch = [&](int nseg, const GemvSeg* segs, int fmt) {
@@ -266,6 +303,7 @@ static int llama_record(slai_llama* m, int kind) {
             L.d_pos = d_pos; L.kcache = kc; L.vcache = vc; L.kv_dtype = c.kv_dtype;
             L.kv_pos_stride = m->head_size; L.kv_head_stride = (int64_t)c.seq_len * m->head_size;
             L.pdl = pdl;
+            L.ahead = plan_ahead1(w.wo, 0, cap);  // the attention kernel in between streams the KV cache, not weights
             consume_exchange(L);
             n++;
             return gemv_launch(ctx, L);
@@ -289,6 +327,7 @@ static int llama_record(slai_llama* m, int kind) {
             A.n_heads = m->n_q_local; A.kv_mul = m->kv_mul; A.head_size = m->head_size;
             A.d_pos = d_pos; A.max_pos = c.seq_len - 1; A.out = m->xb; A.pdl = pdl;
             A.scratch = m->attn_scratch; A.scratch_bytes = m->attn_scratch_bytes;
+            A.ahead = plan_ahead(gu, 2, 0, cap);
             if ((rc = attention_launch(ctx, A))) return rc;
             n++;
         }
@@ -298,6 +337,7 @@ static int llama_record(slai_llama* m, int kind) {
             L.fmt = w.wo->fmt; L.K = m->q_dim; L.nseg = 1; L.seg[0] = seg_of(w.wo, 0, c.dim, nullptr, 0, 0);
             L.v = m->xb; L.out = m->x; L.resid = m->x; L.epi = EPI_RESID; L.pdl = pdl;
             L.prefetch = w.ffn_norm; L.prefetch_bytes = (size_t)c.dim * 4;
+            L.ahead = plan_ahead(gu, 2, gu_first, cap);  // what the attention kernel's plan left of gate / up
             if ((rc = row_parallel(L))) return rc;
         }
         // 4. xb = rmsnorm(x); hb = silu(Wgate xb) * (Wup xb)                    transformer.rs:356-361
@@ -308,6 +348,7 @@ static int llama_record(slai_llama* m, int kind) {
             L.seg[1] = seg_of(w.wup, 0, m->hidden, nullptr, 0, 0);
             L.v = m->x; L.out = m->hb; L.pro = PRO_RMS; L.norm_w = w.ffn_norm; L.eps = c.rms_norm_eps; L.epi = EPI_SILU;
             L.pdl = pdl;
+            L.ahead = plan_ahead1(w.wdown, 0, cap);
             consume_exchange(L);
             if ((rc = gemv_launch(ctx, L))) return rc;
             n++;
@@ -330,6 +371,12 @@ static int llama_record(slai_llama* m, int kind) {
             L.fmt = w.wdown->fmt; L.K = m->hidden; L.nseg = 1; L.seg[0] = seg_of(w.wdown, 0, c.dim, nullptr, 0, 0);
             L.v = m->hb; L.out = m->x; L.resid = m->x; L.epi = EPI_RESID; L.pdl = pdl;
             L.prefetch = l + 1 < c.n_layers ? m->layers[l + 1].attn_norm : m->out_norm; L.prefetch_bytes = (size_t)c.dim * 4;
+            if (l + 1 < c.n_layers) {
+                const slai_qmatrix* nx[3] = {m->layers[l + 1].wq, m->layers[l + 1].wk, m->layers[l + 1].wv};
+                L.ahead = plan_ahead(nx, 3, 0, cap);
+            } else {
+                L.ahead = plan_ahead1(m->output ? m->output : m->embd_q, 0, cap);
+            }
             if ((rc = row_parallel(L))) return rc;
         }
     }
@@ -345,23 +392,33 @@ static int llama_record(slai_llama* m, int kind) {
         n++;
     } else {
         GemvLaunch L;
-        L.fmt = wout->fmt; L.K = c.dim; L.nseg = 1; L.seg[0] = seg_of(wout, 0, c.vocab_size, nullptr, 0, 0);
-        L.v = m->x; L.out = m->logits; L.pro = PRO_RMS; L.norm_w = m->out_norm; L.eps = c.rms_norm_eps; L.epi = EPI_STORE;
+        const int vrows = m->out_sharded ? c.vocab_size / m->tp : c.vocab_size;
+        L.fmt = wout->fmt; L.K = c.dim; L.nseg = 1; L.seg[0] = seg_of(wout, 0, vrows, nullptr, 0, 0);
+        L.v = m->x; L.out = m->out_sharded ? m->logits_part : m->logits; L.pro = PRO_RMS; L.norm_w = m->out_norm; L.eps = c.rms_norm_eps;
+        L.epi = EPI_STORE;
         L.pdl = pdl;
+        {   // the next token starts with layer 0's q / k / v again
+            const slai_qmatrix* nx[3] = {m->layers[0].wq, m->layers[0].wk, m->layers[0].wv};
+            L.ahead = plan_ahead(nx, 3, 0, ahead_cap_bytes());
+        }
         consume_exchange(L);
         if ((rc = gemv_launch(ctx, L))) return rc;
         n++;
+        if (m->out_sharded) {  // every rank's slice of the logits, in rank order = vocabulary order
+            if ((rc = tp_all_gather(ctx, m->logits_part, m->logits, vrows))) return rc;
+            n++;
+        }
     }
     if (kind == G_SAMPLED) rc = launch_sample(ctx, m->logits, c.vocab_size, m->d_samp, m->sc.d + 2, 0.f, false, m->d_samp_scratch, m->sc.d + 3, pdl);
     else rc = launch_argmax(ctx, m->logits, c.vocab_size, m->sc.d + 3, pdl);
     if (rc) return rc;
     n++;
     if (kind == G_GENERATE || kind == G_SAMPLED) {
-        if ((rc = launch_advance(ctx, d_token, d_pos, m->sc.d + 3, m->d_history, pdl))) return rc;
+        if ((rc = launch_advance(ctx, d_token, d_pos, m->sc.d + 3, m->d_history, c.vocab_size, pdl))) return rc;
         n++;
     } else if (kind == G_FORCED) {
         // next token comes from the prompt: history[] holds tokens[1..]; advance copies history[step]
-        if ((rc = launch_advance(ctx, d_token, d_pos, nullptr, m->d_history, pdl))) return rc;
+        if ((rc = launch_advance(ctx, d_token, d_pos, nullptr, m->d_history, c.vocab_size, pdl))) return rc;
         n++;
     }
     m->launches = n;
@@ -408,6 +465,7 @@ static int run_graph(M* m, int kind, RecordFn record) {
 
 SLAI_API int slai_llama_create(slai_ctx* ctx, const slai_llama_config* cfg, slai_llama** out) {
     if (!ctx || !cfg || !out) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     *out = nullptr;
     const slai_llama_config& c = *cfg;
     SLAI_REQUIRE(ctx, c.dim > 0 && c.hidden_dim > 0 && c.n_layers > 0 && c.n_q_heads > 0 && c.n_kv_heads > 0 && c.vocab_size > 0 &&
@@ -415,17 +473,18 @@ SLAI_API int slai_llama_create(slai_ctx* ctx, const slai_llama_config* cfg, slai
     SLAI_REQUIRE(ctx, c.dim % c.n_q_heads == 0 && c.n_q_heads % c.n_kv_heads == 0, SLAI_ERR_SHAPE, "llama: head counts do not divide");
     SLAI_REQUIRE(ctx, (c.dim / c.n_q_heads) % 2 == 0, SLAI_ERR_SHAPE, "llama: odd head size");
     SLAI_REQUIRE(ctx, c.kv_dtype == SLAI_KV_F16 || c.kv_dtype == SLAI_KV_F32, SLAI_ERR_INVALID_ARG, "llama: unknown kv_dtype");
+    const int tp = c.tp_size > 1 ? c.tp_size : 1;
+    if (tp > 1) {  // (checked before anything is allocated)
+        SLAI_REQUIRE(ctx, ctx->tp_comm && ctx->tp_size == c.tp_size && ctx->tp_rank == c.tp_rank, SLAI_ERR_INVALID_ARG,
+                     "llama: tp_rank/tp_size %d/%d do not match the context's group (slai_tp_init)", c.tp_rank, c.tp_size);
+        SLAI_REQUIRE(ctx, c.n_kv_heads % tp == 0 && c.hidden_dim % tp == 0 && (c.hidden_dim / tp) % 16 == 0, SLAI_ERR_SHAPE,
+                     "llama: %d KV heads / hidden %d do not split over %d ranks", c.n_kv_heads, c.hidden_dim, tp);
+    }
     slai_llama* m = new slai_llama();
     m->ctx = ctx;
     m->cfg = c;
     // derived sizes: Llama2Config::derived_configs (models/llama2/cpu.rs:111-143)
-    m->tp = c.tp_size > 1 ? c.tp_size : 1;
-    if (m->tp > 1) {
-        SLAI_REQUIRE(ctx, ctx->tp_comm && ctx->tp_size == c.tp_size && ctx->tp_rank == c.tp_rank, SLAI_ERR_INVALID_ARG,
-                     "llama: tp_rank/tp_size %d/%d do not match the context's group (slai_tp_init)", c.tp_rank, c.tp_size);
-        SLAI_REQUIRE(ctx, c.n_kv_heads % m->tp == 0 && c.hidden_dim % m->tp == 0 && (c.hidden_dim / m->tp) % 16 == 0, SLAI_ERR_SHAPE,
-                     "llama: %d KV heads / hidden %d do not split over %d ranks", c.n_kv_heads, c.hidden_dim, m->tp);
-    }
+    m->tp = tp;
     m->head_size = c.dim / c.n_q_heads;
     m->kv_mul = c.n_q_heads / c.n_kv_heads;
     m->n_q_local = c.n_q_heads / m->tp;
@@ -466,6 +525,7 @@ SLAI_API int slai_llama_create(slai_ctx* ctx, const slai_llama_config* cfg, slai
 
 SLAI_API int slai_llama_destroy(slai_llama* m) {
     if (!m) return SLAI_OK;
+    SLAI_ENTER(m->ctx);
     cudaStreamSynchronize(m->ctx->stream);
     destroy_graphs(m->graphs);
     llama_drop_fused(m);
@@ -474,6 +534,7 @@ SLAI_API int slai_llama_destroy(slai_llama* m) {
     }
     cudaFree(m->token_embd); cudaFree(m->out_norm);
     cudaFree(m->x); cudaFree(m->xb); cudaFree(m->xpart); cudaFree(m->q); cudaFree(m->hb); cudaFree(m->hb2); cudaFree(m->logits);
+    cudaFree(m->logits_part);
     cudaFree(m->kcache); cudaFree(m->vcache); cudaFree(m->sc.d); cudaFree(m->d_history); cudaFree(m->attn_scratch);
     cudaFree(m->d_samp); cudaFree(m->d_samp_scratch); cudaFree(m->rope_cs);
     delete m;
@@ -482,13 +543,20 @@ SLAI_API int slai_llama_destroy(slai_llama* m) {
 
 SLAI_API int slai_llama_set_matrix(slai_llama* m, int id, int layer, const slai_qmatrix* w) {
     if (!m || !w) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(m->ctx);
     slai_ctx* ctx = m->ctx;
     const slai_llama_config& c = m->cfg;
     destroy_graphs(m->graphs);
     llama_drop_fused(m);
     auto shape_is = [&](int64_t r, int64_t k) { return w->nrows == r && w->ncols == k; };
     if (id == SLAI_W_OUTPUT) {
-        SLAI_REQUIRE(ctx, shape_is(c.vocab_size, c.dim), SLAI_ERR_SHAPE, "llama: output matrix must be vocab x dim");
+        // tensor parallel: either the whole matrix on every rank, or this rank's vocab / tp consecutive rows (the
+        // logits are then gathered from all ranks after the product)
+        const bool part = m->tp > 1 && c.vocab_size % (16 * m->tp) == 0 && shape_is(c.vocab_size / m->tp, c.dim);
+        SLAI_REQUIRE(ctx, part || shape_is(c.vocab_size, c.dim), SLAI_ERR_SHAPE, "llama: output matrix must be vocab x dim%s",
+                     m->tp > 1 ? " (or vocab / tp x dim, vocab / tp a multiple of 16)" : "");
+        if (part && !m->logits_part) SLAI_CHECK_CUDA(ctx, cudaMalloc(&m->logits_part, (size_t)c.vocab_size / m->tp * 4));
+        m->out_sharded = part;
         m->output = w;
         return SLAI_OK;
     }
@@ -514,6 +582,7 @@ SLAI_API int slai_llama_set_matrix(slai_llama* m, int id, int layer, const slai_
 
 static int llama_set_f32_impl(slai_llama* m, int id, int layer, const float* data, int64_t n, bool dev) {
     if (!m || !data) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(m->ctx);
     slai_ctx* ctx = m->ctx;
     const slai_llama_config& c = m->cfg;
     destroy_graphs(m->graphs);
@@ -571,7 +640,10 @@ static int decode_impl(M* m, RecordFn record, int vocab, int seq_len, int32_t to
     if ((rc = run_graph(m, G_DECODE, record))) return rc;
     if (h_logits) SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(h_logits, m->logits, (size_t)vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
     if (next_token) SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(next_token, m->sc.d + 3, 4, cudaMemcpyDeviceToHost, ctx->stream));
-    if (h_logits || next_token) SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (h_logits || next_token) {
+        SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        return slai_check_wait_flag(ctx);  // a step whose bounded wait ran out must not hand out its token
+    }
     return SLAI_OK;
 }
 
@@ -588,7 +660,7 @@ static int generate_impl(M* m, RecordFn record, int vocab, int seq_len, int32_t 
         if ((rc = run_graph(m, kind, record))) return rc;
     if (h_tokens) SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(h_tokens, m->d_history, (size_t)n * 4, cudaMemcpyDeviceToHost, ctx->stream));
     SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    return SLAI_OK;
+    return slai_check_wait_flag(ctx);
 }
 
 template <class M, class RecordFn>
@@ -610,16 +682,18 @@ static int prefill_impl(M* m, RecordFn record, int vocab, int seq_len, const int
         if ((rc = run_graph(m, G_FORCED, record))) return rc;
     if (h_last_logits) SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(h_last_logits, m->logits, (size_t)vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
     SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    return SLAI_OK;
+    return slai_check_wait_flag(ctx);
 }
 
 SLAI_API int slai_llama_decode(slai_llama* m, int32_t token, int32_t pos, float* h_logits, int32_t* next_token) {
     if (!m) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(m->ctx);
     return decode_impl(m, llama_record, m->cfg.vocab_size, m->cfg.seq_len, token, pos, h_logits, next_token);
 }
 SLAI_API int slai_llama_generate_sampled(slai_llama* m, int32_t token, int32_t pos, int32_t n, float temperature, float topp, uint64_t seed,
                                          int32_t* h_tokens) {
     if (!m) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(m->ctx);
     slai_ctx* ctx = m->ctx;
     SLAI_REQUIRE(ctx, temperature >= 0.0f, SLAI_ERR_INVALID_ARG, "generate: negative temperature");
     if (!m->d_samp) {
@@ -632,14 +706,17 @@ SLAI_API int slai_llama_generate_sampled(slai_llama* m, int32_t token, int32_t p
 }
 SLAI_API int slai_llama_generate(slai_llama* m, int32_t token, int32_t pos, int32_t n, int32_t* h_tokens) {
     if (!m) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(m->ctx);
     return generate_impl(m, llama_record, m->cfg.vocab_size, m->cfg.seq_len, token, pos, n, h_tokens);
 }
 SLAI_API int slai_llama_prefill(slai_llama* m, const int32_t* h_tokens, int32_t n, int32_t pos0, float* h_last_logits) {
     if (!m) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(m->ctx);
     return prefill_impl(m, llama_record, m->cfg.vocab_size, m->cfg.seq_len, h_tokens, n, pos0, h_last_logits);
 }
 SLAI_API int slai_llama_read_state(slai_llama* m, int which, float* h_out, int64_t n) {
     if (!m || !h_out) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(m->ctx);
     const float* src = nullptr;
     int64_t cap = 0;
     switch (which) {
@@ -757,10 +834,10 @@ static int gpt2_record(slai_gpt2* m, int kind) {
     if ((rc = launch_argmax(ctx, m->logits, c.n_vocab, m->sc.d + 3, pdl))) return rc;
     n++;
     if (kind == G_GENERATE) {
-        if ((rc = launch_advance(ctx, d_token, d_pos, m->sc.d + 3, m->d_history, pdl))) return rc;
+        if ((rc = launch_advance(ctx, d_token, d_pos, m->sc.d + 3, m->d_history, c.n_vocab, pdl))) return rc;
         n++;
     } else if (kind == G_FORCED) {
-        if ((rc = launch_advance(ctx, d_token, d_pos, nullptr, m->d_history, pdl))) return rc;
+        if ((rc = launch_advance(ctx, d_token, d_pos, nullptr, m->d_history, c.n_vocab, pdl))) return rc;
         n++;
     }
     m->launches = n;
@@ -769,6 +846,7 @@ static int gpt2_record(slai_gpt2* m, int kind) {
 
 SLAI_API int slai_gpt2_create(slai_ctx* ctx, const slai_gpt2_config* cfg, slai_gpt2** out) {
     if (!ctx || !cfg || !out) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     *out = nullptr;
     const slai_gpt2_config& c = *cfg;
     SLAI_REQUIRE(ctx, c.n_vocab > 0 && c.n_seq > 0 && c.n_embd > 0 && c.n_head > 0 && c.n_layer > 0 && c.ff_len > 0, SLAI_ERR_INVALID_ARG,
@@ -809,6 +887,7 @@ SLAI_API int slai_gpt2_create(slai_ctx* ctx, const slai_gpt2_config* cfg, slai_g
 
 SLAI_API int slai_gpt2_destroy(slai_gpt2* m) {
     if (!m) return SLAI_OK;
+    SLAI_ENTER(m->ctx);
     cudaStreamSynchronize(m->ctx->stream);
     destroy_graphs(m->graphs);
     for (auto& l : m->layers) {
@@ -824,6 +903,7 @@ SLAI_API int slai_gpt2_destroy(slai_gpt2* m) {
 
 SLAI_API int slai_gpt2_set_matrix(slai_gpt2* m, int id, int layer, const slai_qmatrix* w) {
     if (!m || !w) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(m->ctx);
     slai_ctx* ctx = m->ctx;
     const slai_gpt2_config& c = m->cfg;
     destroy_graphs(m->graphs);
@@ -851,6 +931,7 @@ SLAI_API int slai_gpt2_set_matrix(slai_gpt2* m, int id, int layer, const slai_qm
 
 SLAI_API int slai_gpt2_set_f32(slai_gpt2* m, int id, int layer, const float* h_data, int64_t n) {
     if (!m || !h_data) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(m->ctx);
     slai_ctx* ctx = m->ctx;
     const slai_gpt2_config& c = m->cfg;
     destroy_graphs(m->graphs);
@@ -880,13 +961,16 @@ SLAI_API int slai_gpt2_set_f32(slai_gpt2* m, int id, int layer, const float* h_d
 
 SLAI_API int slai_gpt2_decode(slai_gpt2* m, int32_t token, int32_t pos, float* h_logits, int32_t* next_token) {
     if (!m) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(m->ctx);
     return decode_impl(m, gpt2_record, m->cfg.n_vocab, m->cfg.n_seq, token, pos, h_logits, next_token);
 }
 SLAI_API int slai_gpt2_generate(slai_gpt2* m, int32_t token, int32_t pos, int32_t n, int32_t* h_tokens) {
     if (!m) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(m->ctx);
     return generate_impl(m, gpt2_record, m->cfg.n_vocab, m->cfg.n_seq, token, pos, n, h_tokens);
 }
 SLAI_API int slai_gpt2_prefill(slai_gpt2* m, const int32_t* h_tokens, int32_t n, int32_t pos0, float* h_last_logits) {
     if (!m) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(m->ctx);
     return prefill_impl(m, gpt2_record, m->cfg.n_vocab, m->cfg.n_seq, h_tokens, n, pos0, h_last_logits);
 }

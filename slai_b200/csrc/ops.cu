@@ -45,7 +45,7 @@ SLAI_API int slai_ctx_create(int device, slai_ctx** out) {
     if (device < 0 || device >= n) return SLAI_ERR_INVALID_ARG;
     slai_ctx* ctx = new slai_ctx();
     ctx->device = device;
-    if (cudaSetDevice(device) != cudaSuccess) { delete ctx; return SLAI_ERR_CUDA; }
+    DeviceGuard guard(device);
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) { delete ctx; return SLAI_ERR_CUDA; }
     if (prop.major != 10) {
@@ -56,11 +56,20 @@ SLAI_API int slai_ctx_create(int device, slai_ctx** out) {
     ctx->sm_count = prop.multiProcessorCount;
     if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaEventCreate(&ctx->ev0) != cudaSuccess || cudaEventCreate(&ctx->ev1) != cudaSuccess ||
-        cudaMalloc(&ctx->d_counters, 4096 * sizeof(unsigned int)) != cudaSuccess ||
-        cudaMemset(ctx->d_counters, 0, 4096 * sizeof(unsigned int)) != cudaSuccess) {
+        cudaMalloc(&ctx->d_counters, CNT_WORDS * sizeof(unsigned int)) != cudaSuccess ||
+        cudaMemset(ctx->d_counters, 0, CNT_WORDS * sizeof(unsigned int)) != cudaSuccess) {
         delete ctx;
         return SLAI_ERR_CUDA;
     }
+#ifdef SLAI_TRACE
+    if (cudaMalloc(&ctx->trace_buf, (size_t)64 * TRACE_BLOCKS * TRACE_POINTS * 8) != cudaSuccess ||
+        cudaMemset(ctx->trace_buf, 0, (size_t)64 * TRACE_BLOCKS * TRACE_POINTS * 8) != cudaSuccess ||
+        cudaMalloc(&ctx->tl, ((size_t)TL_SLOTS * TL_CAP + 1) * 8) != cudaSuccess ||
+        cudaMemset(ctx->tl, 0, ((size_t)TL_SLOTS * TL_CAP + 1) * 8) != cudaSuccess) {
+        delete ctx;
+        return SLAI_ERR_CUDA;
+    }
+#endif
     const char* pdl = getenv("SLAI_NO_PDL");
     ctx->use_pdl = !(pdl && pdl[0] == '1');
     *out = ctx;
@@ -69,10 +78,11 @@ SLAI_API int slai_ctx_create(int device, slai_ctx** out) {
 
 SLAI_API int slai_ctx_destroy(slai_ctx* ctx) {
     if (!ctx) return SLAI_OK;
-    cudaSetDevice(ctx->device);
+    SLAI_ENTER(ctx);
     cudaStreamSynchronize(ctx->stream);
     for (auto& t : ctx->rope_tables) cudaFree(t.d_theta);
     if (ctx->d_scratch) cudaFree(ctx->d_scratch);
+    for (void* p : ctx->retired_scratch) cudaFree(p);
     if (ctx->d_counters) cudaFree(ctx->d_counters);
     cudaEventDestroy(ctx->ev0);
     slai_tp_shutdown(ctx);
@@ -82,23 +92,35 @@ SLAI_API int slai_ctx_destroy(slai_ctx* ctx) {
     return SLAI_OK;
 }
 
-SLAI_API int slai_ctx_sync(slai_ctx* ctx) {
-    if (!ctx) return SLAI_ERR_INVALID_ARG;
-    SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    // Every wait inside the kernels (ring barriers, grid barrier) is bounded; one that ran out raised this flag.
+// After a synchronisation: did a bounded wait inside a kernel run out since the last check?
+int slai_check_wait_flag(slai_ctx* ctx) {
+    // Every wait inside the kernels (ring barriers, grid barrier, peer polls) is bounded; one that ran out raised this flag.
     unsigned int flag = 0;
-    SLAI_CHECK_CUDA(ctx, cudaMemcpy(&flag, ctx->d_counters + 3000, sizeof(flag), cudaMemcpyDeviceToHost));
+    SLAI_CHECK_CUDA(ctx, cudaMemcpy(&flag, ctx->d_counters + CNT_ERR_FLAG, sizeof(flag), cudaMemcpyDeviceToHost));
     if (flag) {
-        cudaMemset(ctx->d_counters + 3000, 0, sizeof(flag));
+        cudaMemset(ctx->d_counters + CNT_ERR_FLAG, 0, sizeof(flag));
         return slai_set_error(ctx, SLAI_ERR_TIMEOUT, "a bounded wait inside a kernel ran out (%s); results of the last launches are invalid",
                               flag == 1 ? "weight ring" : flag == 2 ? "grid barrier" : "tensor-parallel peer");
     }
+    return SLAI_OK;
+}
+SLAI_API int slai_ctx_sync(slai_ctx* ctx) {
+    if (!ctx) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
+    SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return slai_check_wait_flag(ctx);
+}
+SLAI_API int slai_ctx_set_wait_limit(slai_ctx* ctx, uint32_t rounds) {
+    if (!ctx) return SLAI_ERR_INVALID_ARG;
+    SLAI_REQUIRE(ctx, rounds >= 16, SLAI_ERR_INVALID_ARG, "wait limit of %u rounds is too short for a healthy launch", rounds);
+    ctx->wait_limit = rounds;  // read when a launch is described: passes and graphs recorded earlier keep theirs
     return SLAI_OK;
 }
 SLAI_API const char* slai_last_error_string(slai_ctx* ctx) { return ctx ? ctx->last_error.c_str() : g_noctx_error.c_str(); }
 SLAI_API void* slai_ctx_stream(slai_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
 SLAI_API int slai_ctx_device_info(slai_ctx* ctx, char* name, int name_len, int* sm_count) {
     if (!ctx) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     cudaDeviceProp prop;
     SLAI_CHECK_CUDA(ctx, cudaGetDeviceProperties(&prop, ctx->device));
     if (name && name_len > 0) snprintf(name, name_len, "%s", prop.name);
@@ -106,8 +128,16 @@ SLAI_API int slai_ctx_device_info(slai_ctx* ctx, char* name, int name_len, int* 
     return SLAI_OK;
 }
 
+SLAI_API int slai_ctx_mem_info(slai_ctx* ctx, size_t* free_bytes, size_t* total_bytes) {
+    if (!ctx || !free_bytes || !total_bytes) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
+    SLAI_CHECK_CUDA(ctx, cudaMemGetInfo(free_bytes, total_bytes));
+    return SLAI_OK;
+}
+
 SLAI_API int slai_malloc(slai_ctx* ctx, size_t bytes, void** d_out) {
     if (!ctx || !d_out) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     cudaError_t e = cudaMalloc(d_out, bytes ? bytes : 16);
     if (e == cudaErrorMemoryAllocation) {
         cudaGetLastError();
@@ -118,33 +148,39 @@ SLAI_API int slai_malloc(slai_ctx* ctx, size_t bytes, void** d_out) {
 }
 SLAI_API int slai_free(slai_ctx* ctx, void* d_ptr) {
     if (!ctx) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     SLAI_CHECK_CUDA(ctx, cudaFree(d_ptr));
     return SLAI_OK;
 }
 SLAI_API int slai_memset(slai_ctx* ctx, void* d_ptr, int value, size_t bytes) {
     if (!ctx) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     SLAI_CHECK_CUDA(ctx, cudaMemsetAsync(d_ptr, value, bytes, ctx->stream));
     return SLAI_OK;
 }
 SLAI_API int slai_write_buffer(slai_ctx* ctx, void* d_dst, const void* h_src, size_t bytes) {
     if (!ctx) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(d_dst, h_src, bytes, cudaMemcpyHostToDevice, ctx->stream));
     return SLAI_OK;
 }
 SLAI_API int slai_read_buffer(slai_ctx* ctx, void* h_dst, const void* d_src, size_t bytes) {
     if (!ctx) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(h_dst, d_src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
     SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return SLAI_OK;
 }
 SLAI_API int slai_malloc_host(slai_ctx* ctx, size_t bytes, void** h_out) {
     if (!ctx || !h_out) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     SLAI_CHECK_CUDA(ctx, cudaMallocHost(h_out, bytes ? bytes : 16));
     return SLAI_OK;
 }
 SLAI_API int slai_free_host(slai_ctx* ctx, void* h_ptr) {
     if (!ctx) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     SLAI_CHECK_CUDA(ctx, cudaFreeHost(h_ptr));
     return SLAI_OK;
 }
@@ -154,11 +190,13 @@ struct slai_pass {
 };
 SLAI_API int slai_pass_begin(slai_ctx* ctx) {
     if (!ctx) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     SLAI_CHECK_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
     return SLAI_OK;
 }
 SLAI_API int slai_pass_end(slai_ctx* ctx, slai_pass** out) {
     if (!ctx || !out) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     *out = nullptr;
     cudaGraph_t graph = nullptr;
     cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
@@ -180,11 +218,13 @@ SLAI_API int slai_pass_end(slai_ctx* ctx, slai_pass** out) {
 }
 SLAI_API int slai_pass_launch(slai_ctx* ctx, slai_pass* pass, int times) {
     if (!ctx || !pass || !pass->exec || times < 0) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     for (int i = 0; i < times; i++) SLAI_CHECK_CUDA(ctx, cudaGraphLaunch(pass->exec, ctx->stream));
     return SLAI_OK;
 }
 SLAI_API int slai_pass_destroy(slai_ctx* ctx, slai_pass* pass) {
     if (!ctx) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     if (pass) {
         cudaStreamSynchronize(ctx->stream);
         if (pass->exec) cudaGraphExecDestroy(pass->exec);
@@ -195,11 +235,13 @@ SLAI_API int slai_pass_destroy(slai_ctx* ctx, slai_pass* pass) {
 
 SLAI_API int slai_timer_start(slai_ctx* ctx) {
     if (!ctx) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     SLAI_CHECK_CUDA(ctx, cudaEventRecord(ctx->ev0, ctx->stream));
     return SLAI_OK;
 }
 SLAI_API int slai_timer_stop(slai_ctx* ctx, float* ms) {
     if (!ctx || !ms) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     SLAI_CHECK_CUDA(ctx, cudaEventRecord(ctx->ev1, ctx->stream));
     SLAI_CHECK_CUDA(ctx, cudaEventSynchronize(ctx->ev1));
     SLAI_CHECK_CUDA(ctx, cudaEventElapsedTime(ms, ctx->ev0, ctx->ev1));
@@ -238,17 +280,13 @@ __device__ float dequant_elem(int fmt, const uint8_t* data, long long K, long lo
     const uint8_t* b = data + ((row >> 4) * ns + (k >> 8)) * layout::step_bytes(fmt);
     const int e = (int)(k & 255);
     if (fmt == SLAI_FMT_Q4_K || fmt == SLAI_FMT_Q5_K) {
-        const uint8_t* h = b + 16 * r;
+        const uint8_t* h = b + layout::K45_HDR_ROW * r;
         const float d = dev_h2f(h[0] | (h[1] << 8)), mn = dev_h2f(h[2] | (h[3] << 8));
         const int G = e >> 6, half = (e >> 5) & 1, l = e & 31;
-        const uint8_t qb = b[layout::qbyte_off(fmt == SLAI_FMT_Q4_K ? 256 : 768, r, 32 * G + l)];
+        const uint8_t qb = b[layout::qbyte_off(fmt == SLAI_FMT_Q4_K ? layout::K45_HDR : layout::K45_HDR + 512, r, 32 * G + l)];
         int q = half ? (qb >> 4) : (qb & 0xF);
-        if (fmt == SLAI_FMT_Q5_K) q += ((b[256 + 32 * r + l] >> (2 * G + half)) & 1) ? 16 : 0;
-        const uint32_t s0 = h[4] | (h[5] << 8) | (h[6] << 16) | ((uint32_t)h[7] << 24);
-        const uint32_t s1 = h[8] | (h[9] << 8) | (h[10] << 16) | ((uint32_t)h[11] << 24);
-        const uint32_t s2 = h[12] | (h[13] << 8) | (h[14] << 16) | ((uint32_t)h[15] << 24);
-        uint32_t sc, m;
-        frag::scale_min_k4(2 * G + half, s0, s1, s2, sc, m);
+        if (fmt == SLAI_FMT_Q5_K) q += ((b[layout::K45_HDR + 32 * r + l] >> (2 * G + half)) & 1) ? 16 : 0;
+        const uint32_t sc = h[layout::k45_sc_off(2 * G + half)], m = h[12 + 2 * G + half];  // unpacked at upload
         const float d1 = __fmul_rn(d, (float)sc), m1 = __fmul_rn(mn, (float)m);
         return __fsub_rn(__fmul_rn(d1, (float)q), m1);
     }
@@ -303,6 +341,7 @@ static int qmatrix_alloc(slai_ctx* ctx, int fmt, int64_t nrows, int64_t ncols, s
 SLAI_API int slai_qmatrix_create_from_device(slai_ctx* ctx, int fmt, int64_t nrows, int64_t ncols, const void* d_blocks,
                                              size_t nbytes, slai_qmatrix** out) {
     if (!ctx) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     int rc = qmatrix_alloc(ctx, fmt, nrows, ncols, nbytes, out);
     if (rc) return rc;
     slai_qmatrix* m = *out;
@@ -322,6 +361,7 @@ SLAI_API int slai_qmatrix_create_from_device(slai_ctx* ctx, int fmt, int64_t nro
 SLAI_API int slai_qmatrix_create(slai_ctx* ctx, int fmt, int64_t nrows, int64_t ncols, const void* h_blocks, size_t nbytes,
                                  slai_qmatrix** out) {
     if (!ctx) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     SLAI_REQUIRE(ctx, h_blocks, SLAI_ERR_INVALID_ARG, "qmatrix: null block pointer");
     void* tmp = nullptr;
     cudaError_t e = cudaMalloc(&tmp, nbytes ? nbytes : 16);
@@ -340,6 +380,7 @@ SLAI_API int slai_qmatrix_create(slai_ctx* ctx, int fmt, int64_t nrows, int64_t 
 
 SLAI_API int slai_qmatrix_destroy(slai_qmatrix* m) {
     if (!m) return SLAI_OK;
+    SLAI_ENTER(m->ctx);
     if (m->owns && m->data) {
         cudaStreamSynchronize(m->ctx->stream);
         cudaFree(m->data);
@@ -349,6 +390,7 @@ SLAI_API int slai_qmatrix_destroy(slai_qmatrix* m) {
 }
 SLAI_API int slai_qmatrix_shape(const slai_qmatrix* m, int* fmt, int64_t* nrows, int64_t* ncols) {
     if (!m) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(m->ctx);
     if (fmt) *fmt = m->fmt;
     if (nrows) *nrows = m->nrows;
     if (ncols) *ncols = m->ncols;
@@ -358,6 +400,7 @@ SLAI_API size_t slai_qmatrix_device_bytes(const slai_qmatrix* m) { return m ? m-
 
 SLAI_API int slai_qmatrix_dequantize(slai_ctx* ctx, const slai_qmatrix* m, float* d_out) {
     if (!ctx || !m || !d_out) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     const long long total = m->nrows * m->ncols;
     dequant_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(m->fmt, m->data, 0, m->nrows, m->ncols, d_out);
     SLAI_CHECK_CUDA(ctx, cudaGetLastError());
@@ -365,6 +408,7 @@ SLAI_API int slai_qmatrix_dequantize(slai_ctx* ctx, const slai_qmatrix* m, float
 }
 SLAI_API int slai_qmatrix_dequantize_row(slai_ctx* ctx, const slai_qmatrix* m, int64_t row, float* d_out) {
     if (!ctx || !m || !d_out) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     SLAI_REQUIRE(ctx, row >= 0 && row < m->nrows, SLAI_ERR_INVALID_ARG, "dequantize_row: row %lld out of range", (long long)row);
     dequant_kernel<<<(unsigned)((m->ncols + 255) / 256), 256, 0, ctx->stream>>>(m->fmt, m->data, row, 1, m->ncols, d_out);
     SLAI_CHECK_CUDA(ctx, cudaGetLastError());
@@ -373,6 +417,7 @@ SLAI_API int slai_qmatrix_dequantize_row(slai_ctx* ctx, const slai_qmatrix* m, i
 
 SLAI_API int slai_gemv_quant(slai_ctx* ctx, float* d_out, const slai_qmatrix* w, const float* d_v, int n_batch) {
     if (!ctx || !w || !d_out || !d_v) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     SLAI_REQUIRE(ctx, n_batch >= 1 && n_batch <= 8, SLAI_ERR_INVALID_ARG, "gemv: n_batch=%d must be in 1..8", n_batch);
     for (int b = 0; b < n_batch; b++) {
         GemvLaunch L;
@@ -539,6 +584,8 @@ __global__ void rope_kernel(int neox, float* q, long long q_len, float* k, int h
     }
 }
 
+__global__ void set_int_kernel(int* dst, int value) { *dst = value; }
+
 template <typename T>
 __global__ void kv_append_kernel(T* kc, T* vc, const float* k, const float* v, int kv_dim, long long off) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -651,7 +698,7 @@ __global__ void embed_q_kernel(float* x, int fmt, const uint8_t* data, int dim, 
 // Advance the device-side loop state without a host round trip: pos <- pos + 1, step <- step + 1 and
 //   greedy (d_next != NULL): token <- *d_next, history[step] <- *d_next
 //   forced (d_next == NULL): token <- history[step]   (prompt processing)
-__global__ void advance_kernel(int* d_token, int* d_pos, const int* d_next, int* d_history, int* d_step) {
+__global__ void advance_kernel(int* d_token, int* d_pos, const int* d_next, int* d_history, int* d_step, int vocab) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int step = *d_step;
     int nx;
@@ -661,6 +708,7 @@ __global__ void advance_kernel(int* d_token, int* d_pos, const int* d_next, int*
     } else {
         nx = d_history[step];
     }
+    nx = nx < 0 ? 0 : (nx >= vocab ? vocab - 1 : nx);  // whatever a kernel produced, the embedding lookup stays inside its table
     *d_token = nx;
     *d_pos = *d_pos + 1;
     *d_step = step + 1;
@@ -685,6 +733,7 @@ int launch_pdl(slai_ctx* ctx, void (*kern)(Args...), dim3 grid, dim3 block, bool
 
 SLAI_API int slai_rms_norm(slai_ctx* ctx, float* d_out, const float* d_x, const float* d_w, int64_t n, float eps) {
     if (!ctx || !d_out || !d_x || !d_w || n <= 0) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     rms_norm_kernel<<<1, 1024, 0, ctx->stream>>>(d_out, d_x, d_w, n, eps);
     SLAI_CHECK_CUDA(ctx, cudaGetLastError());
     return SLAI_OK;
@@ -692,12 +741,14 @@ SLAI_API int slai_rms_norm(slai_ctx* ctx, float* d_out, const float* d_x, const 
 SLAI_API int slai_layernorm(slai_ctx* ctx, float* d_out, const float* d_x, int64_t n, float eps, const float* d_gamma,
                             const float* d_beta) {
     if (!ctx || !d_out || !d_x || n <= 0) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     layernorm_kernel<<<1, 1024, 0, ctx->stream>>>(d_out, d_x, n, eps, d_gamma, d_beta);
     SLAI_CHECK_CUDA(ctx, cudaGetLastError());
     return SLAI_OK;
 }
 SLAI_API int slai_softmax_cols(slai_ctx* ctx, float* d_m, int64_t nrows, int64_t ncols, int64_t col_stride) {
     if (!ctx || !d_m || nrows <= 0 || ncols <= 0) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     SLAI_REQUIRE(ctx, col_stride >= nrows, SLAI_ERR_SHAPE, "softmax: col_stride < nrows");
     softmax_cols_kernel<<<(unsigned)ncols, NT, 0, ctx->stream>>>(d_m, nrows, col_stride);
     SLAI_CHECK_CUDA(ctx, cudaGetLastError());
@@ -705,12 +756,14 @@ SLAI_API int slai_softmax_cols(slai_ctx* ctx, float* d_m, int64_t nrows, int64_t
 }
 SLAI_API int slai_silu_gate(slai_ctx* ctx, float* d_h1, const float* d_h2, int64_t n) {
     if (!ctx || !d_h1 || !d_h2 || n <= 0) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     silu_gate_kernel<<<(unsigned)((n + NT - 1) / NT), NT, 0, ctx->stream>>>(d_h1, d_h2, n);
     SLAI_CHECK_CUDA(ctx, cudaGetLastError());
     return SLAI_OK;
 }
 SLAI_API int slai_unary(slai_ctx* ctx, int op, float* d_dst, const float* d_src, int64_t n, const float args4[4]) {
     if (!ctx || !d_dst || !d_src || n <= 0) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     SLAI_REQUIRE(ctx, op >= 0 && op <= 20, SLAI_ERR_INVALID_ARG, "unary: unknown op %d", op);
     const float a0 = args4 ? args4[0] : 0.f, a1 = args4 ? args4[1] : 0.f;
     long long blocks = (n + NT - 1) / NT;
@@ -721,6 +774,7 @@ SLAI_API int slai_unary(slai_ctx* ctx, int op, float* d_dst, const float* d_src,
 }
 static int binary(slai_ctx* ctx, int mode, float* a, const float* b, int64_t n) {
     if (!ctx || !a || !b || n <= 0) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     binary_kernel<<<(unsigned)((n + NT - 1) / NT), NT, 0, ctx->stream>>>(mode, a, b, n);
     SLAI_CHECK_CUDA(ctx, cudaGetLastError());
     return SLAI_OK;
@@ -749,6 +803,7 @@ const float* rope_table(slai_ctx* ctx, int head_size, float base) {
 SLAI_API int slai_rope(slai_ctx* ctx, int variant, float* d_q, int64_t q_len, float* d_k, int head_size, int kv_dim, int pos,
                        float base_freq) {
     if (!ctx || !d_q || !d_k) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     // the reference asserts even lengths and len(q) >= len(k) (ops/rope.rs:58-63)
     SLAI_REQUIRE(ctx, q_len > 0 && q_len % 2 == 0 && kv_dim % 2 == 0 && kv_dim <= q_len, SLAI_ERR_SHAPE,
                  "rope: q_len=%lld and kv_dim=%d must be even with kv_dim <= q_len", (long long)q_len, kv_dim);
@@ -766,6 +821,7 @@ SLAI_API int slai_rope(slai_ctx* ctx, int variant, float* d_q, int64_t q_len, fl
 SLAI_API int slai_kv_append(slai_ctx* ctx, void* d_key_cache, void* d_value_cache, int kv_dtype, const float* d_k,
                             const float* d_v, int kv_dim, int pos) {
     if (!ctx || !d_key_cache || !d_value_cache || !d_k || !d_v || kv_dim <= 0 || pos < 0) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     const long long off = (long long)pos * kv_dim;
     const unsigned blocks = (kv_dim + NT - 1) / NT;
     if (kv_dtype == SLAI_KV_F16)
@@ -781,14 +837,18 @@ SLAI_API int slai_kv_append(slai_ctx* ctx, void* d_key_cache, void* d_value_cach
 SLAI_API int slai_attention(slai_ctx* ctx, const slai_attn_params* p, const float* d_q, const void* d_key_cache,
                             const void* d_value_cache, int kv_dtype, float* d_xb) {
     if (!ctx || !p || !d_q || !d_key_cache || !d_value_cache || !d_xb) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     SLAI_REQUIRE(ctx, p->pos < p->seq_len, SLAI_ERR_SHAPE, "attention: pos=%u >= seq_len=%u", p->pos, p->seq_len);
     SLAI_REQUIRE(ctx, p->kv_mul > 0 && p->n_heads % p->kv_mul == 0 && p->kv_dim == p->n_heads / p->kv_mul * p->head_size,
                  SLAI_ERR_SHAPE, "attention: inconsistent head counts");
     SLAI_REQUIRE(ctx, kv_dtype == SLAI_KV_F16 || kv_dtype == SLAI_KV_F32, SLAI_ERR_INVALID_ARG, "attention: unknown cache type");
     // position scalar on the device (the kernels read it from memory so that CUDA graphs can be replayed)
-    int* d_pos = reinterpret_cast<int*>(ctx->d_counters + 2048);
+    // (written by a one-thread kernel that takes the value as an argument: a memcpy from this stack frame would leave a
+    // dangling host pointer in a recorded pass)
+    int* d_pos = reinterpret_cast<int*>(ctx->d_counters + CNT_ATTN_POS);
     const int pos = (int)p->pos;
-    SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(d_pos, &pos, sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
+    set_int_kernel<<<1, 1, 0, ctx->stream>>>(d_pos, pos);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
     AttnLaunch A;
     A.q = d_q; A.kcache = d_key_cache; A.vcache = d_value_cache; A.kv_dtype = kv_dtype;
     A.pos_stride = p->kv_dim; A.head_stride = p->head_size;
@@ -799,11 +859,12 @@ SLAI_API int slai_attention(slai_ctx* ctx, const slai_attn_params* p, const floa
 
 SLAI_API int slai_argmax(slai_ctx* ctx, const float* d_v, int64_t n, int32_t* d_index_out) {
     if (!ctx || !d_v || !d_index_out || n <= 0) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     return launch_argmax(ctx, d_v, n, d_index_out, false);
 }
 
 int launch_argmax(slai_ctx* ctx, const float* v, int64_t n, int32_t* d_out, bool pdl) {
-    return launch_pdl(ctx, argmax_kernel, dim3(ARG_BLOCKS), dim3(ARG_THREADS), pdl, v, (long long)n, (int*)d_out, ctx->d_counters + 1100);
+    return launch_pdl(ctx, argmax_kernel, dim3(ARG_BLOCKS), dim3(ARG_THREADS), pdl, v, (long long)n, (int*)d_out, ctx->d_counters + CNT_ARGMAX);
 }
 int launch_embed_f32(slai_ctx* ctx, float* x, const float* table, int dim, const int* d_token, const float* wpe,
                      const int* d_pos, bool pdl, const float* rope_theta, float* rope_cs, int rope_half) {
@@ -816,10 +877,10 @@ int launch_embed_q8(slai_ctx* ctx, float* x, const slai_qmatrix* wte, const int*
     return launch_pdl(ctx, embed_q_kernel, dim3((dim + NT - 1) / NT), dim3(NT), pdl, x, wte->fmt, (const uint8_t*)wte->data, dim,
                       d_token, wpe, d_pos, rope_theta, rope_cs, rope_half);
 }
-int launch_advance(slai_ctx* ctx, int* d_token, int* d_pos, const int32_t* d_next, int32_t* d_history, bool pdl) {
+int launch_advance(slai_ctx* ctx, int* d_token, int* d_pos, const int32_t* d_next, int32_t* d_history, int vocab, bool pdl) {
     // d_history[-1] is not used; the step counter lives right after the position scalar (see models)
     return launch_pdl(ctx, advance_kernel, dim3(1), dim3(1), pdl, d_token, d_pos, (const int*)d_next, (int*)d_history,
-                      d_pos + 1);
+                      d_pos + 1, vocab);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -957,6 +1018,7 @@ __global__ void synth_blocks_kernel(int fmt, uint8_t* out, long long nblocks, ui
 
 SLAI_API int slai_synth_blocks(slai_ctx* ctx, int fmt, int64_t nrows, int64_t ncols, uint64_t seed, float std, void* d_blocks) {
     if (!ctx || !d_blocks) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     const int be = fmt_block_elems(fmt);
     SLAI_REQUIRE(ctx, be > 1, SLAI_ERR_UNSUPPORTED_FORMAT, "synth: format %d has no generator", fmt);
     SLAI_REQUIRE(ctx, nrows > 0 && ncols > 0 && ncols % be == 0, SLAI_ERR_SHAPE, "synth: bad shape");
@@ -967,21 +1029,43 @@ SLAI_API int slai_synth_blocks(slai_ctx* ctx, int fmt, int64_t nrows, int64_t nc
 }
 SLAI_API int slai_synth_normal_f32(slai_ctx* ctx, float* d_out, int64_t n, uint64_t seed, float std) {
     if (!ctx || !d_out || n <= 0) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     synth_normal_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(d_out, n, seed, std);
     SLAI_CHECK_CUDA(ctx, cudaGetLastError());
     return SLAI_OK;
 }
 
 #ifdef SLAI_TRACE
-__device__ unsigned long long g_tl[3 * 4096];
-__device__ unsigned int g_tl_count;
-SLAI_API int slai_debug_timeline(void* h_out, size_t bytes, unsigned int* count) {
-    int rc = (int)cudaMemcpyFromSymbol(h_out, g_tl, bytes);
-    if (rc == 0) rc = (int)cudaMemcpyFromSymbol(count, g_tl_count, 4);
-    unsigned int zero = 0;
-    if (rc == 0) rc = (int)cudaMemcpyToSymbol(g_tl_count, &zero, 4);
-    return rc;
+// Trace build only (see common.cuh).  slai_debug_timeline copies the launch records out and restarts the timeline;
+// slai_debug_block_trace copies the per-block stamps of the most recent GEMV launch (TRACE_BLOCKS x TRACE_POINTS x u64).
+SLAI_API int slai_debug_timeline(slai_ctx* ctx, void* h_out, size_t bytes, unsigned int* count) {
+    if (!ctx || !ctx->tl || !h_out || !count) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
+    const size_t all = (size_t)TL_SLOTS * TL_CAP * 8;
+    if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) return SLAI_ERR_CUDA;
+    unsigned long long n = 0;
+    if (cudaMemcpy(h_out, ctx->tl, bytes < all ? bytes : all, cudaMemcpyDeviceToHost) != cudaSuccess ||
+        cudaMemcpy(&n, ctx->tl + TL_SLOTS * TL_CAP, 8, cudaMemcpyDeviceToHost) != cudaSuccess ||
+        cudaMemset(ctx->tl + TL_SLOTS * TL_CAP, 0, 8) != cudaSuccess)
+        return SLAI_ERR_CUDA;
+    *count = (unsigned int)n;
+    return SLAI_OK;
 }
-// debug build only (never part of the shipped library): device address of the context's scratch buffer
-SLAI_API void* slai_debug_scratch(slai_ctx* ctx) { return ctx ? ctx->d_scratch : nullptr; }
+// The whole ring: 64 launches x TRACE_BLOCKS x TRACE_POINTS stamps; *launches = GEMV launches described so far (the
+// launch with index i stamped into slot i % 64).
+SLAI_API int slai_debug_trace_ring(slai_ctx* ctx, void* h_out, size_t bytes, unsigned long long* launches) {
+    if (!ctx || !ctx->trace_buf || !h_out || !launches) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
+    const size_t all = (size_t)64 * TRACE_BLOCKS * TRACE_POINTS * 8;
+    if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) return SLAI_ERR_CUDA;
+    *launches = ctx->trace_launches;
+    return (int)cudaMemcpy(h_out, ctx->trace_buf, bytes < all ? bytes : all, cudaMemcpyDeviceToHost);
+}
+SLAI_API int slai_debug_block_trace(slai_ctx* ctx, void* h_out, size_t bytes) {
+    if (!ctx || !ctx->trace_buf) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
+    const unsigned long long last = ctx->trace_launches ? (ctx->trace_launches - 1) % 64 : 0;
+    const size_t all = (size_t)TRACE_BLOCKS * TRACE_POINTS * 8;
+    return (int)cudaMemcpy(h_out, ctx->trace_buf + last * TRACE_BLOCKS * TRACE_POINTS, bytes < all ? bytes : all, cudaMemcpyDeviceToHost);
+}
 #endif

@@ -167,6 +167,23 @@ __global__ void __launch_bounds__(ST) sample_kernel(float* logits, int n, const 
     for (int i = i0; i < i1; i++) cnt += logits[i] >= cutoff;
     int n0;
     int off = block_excl_scan(cnt, shi, n0);
+    if (n0 == 0) {
+        // No probability reaches the cutoff (top-p below 1/n on a flat distribution, or non-finite logits).  The
+        // reference underflows `n0 - 1` and panics there (models/sampler.rs:98-113); defined here as the greedy choice
+        // over the probabilities: first maximal index, 0 if nothing compares.
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int i = i0; i < i1; i++)
+            if (logits[i] > best) {
+                best = logits[i];
+                bi = i;
+            }
+        const float m = block_max(best, shf);
+        if (best == m && bi != 0x7fffffff) atomicMin(&s_idx, bi);
+        __syncthreads();
+        if (tid == 0) *out = s_idx == 0x7fffffff ? 0 : s_idx;
+        return;
+    }
     const bool in_smem = n0 <= SORT_SMEM;
     int n2 = 1;
     while (n2 < n0) n2 <<= 1;
@@ -259,6 +276,7 @@ int ensure_scratch(slai_ctx* ctx, size_t bytes);
 
 SLAI_API int slai_sample(slai_ctx* ctx, float* d_logits, int64_t n, float temperature, float topp, float coin, int32_t* d_token_out) {
     if (!ctx || !d_logits || !d_token_out) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
     SLAI_REQUIRE(ctx, n >= 2 && n <= (1 << 20), SLAI_ERR_SHAPE, "sample: vocabulary of %lld entries", (long long)n);
     SLAI_REQUIRE(ctx, temperature >= 0.0f && coin >= 0.0f && coin < 1.0f, SLAI_ERR_INVALID_ARG, "sample: temperature must be >= 0 and coin in [0, 1)");
     const size_t need = sampler_scratch_bytes((int)n) + 256;

@@ -75,6 +75,15 @@ class Backend:
         self.check(self.lib.slai_ctx_device_info(self.h, name, 128, C.byref(sms)))
         return name.value.decode(), sms.value
 
+    def mem_info(self):
+        free, total = C.c_size_t(), C.c_size_t()
+        self.check(self.lib.slai_ctx_mem_info(self.h, C.byref(free), C.byref(total)))
+        return free.value, total.value
+
+    def set_wait_limit(self, rounds: int):
+        """Rounds a bounded device-side wait polls before it gives up (SLAI_ERR_TIMEOUT at the next synchronisation)."""
+        self.check(self.lib.slai_ctx_set_wait_limit(self.h, rounds))
+
     def record(self) -> "RecordedPass":
         """Record the operator calls made inside the `with` block instead of running them (the reference's encoder:
         begin_pass ... submit, context.rs:63-96); replay with `.launch(times)`."""
@@ -305,6 +314,24 @@ class LlmContext:
         if len(b) != a.ncols * n_batch or len(out) != a.nrows * n_batch:
             raise SlaiError(_lib.ERR_SHAPE, f"Gemv: dimension mismatch ({a.nrows}x{a.ncols} * {len(b)} -> {len(out)})")
         self.backend.check(self.lib.slai_gemv_quant(self.h, _ptr(out), a.h, _ptr(b), n_batch))
+
+    # Tensor-parallel exchange operators (no counterpart in the reference): a row-parallel product whose partial goes
+    # to every rank's exchange region, and a product whose input is the sum over ranks of such an exchange.
+    def matmul_quant_partial(self, a: GpuQuantMatrix, b, resid, index: int, per_token: int):
+        if len(b) != a.ncols or (resid is not None and len(resid) != a.nrows):
+            raise SlaiError(_lib.ERR_SHAPE, "Gemv: dimension mismatch")
+        self.backend.check(self.lib.slai_gemv_quant_partial(self.h, a.h, _ptr(b), _ptr(resid), index, per_token))
+
+    def matmul_quant_reduced(self, out, a: GpuQuantMatrix, norm_w, eps: float, index: int, per_token: int, sum_out):
+        if len(out) != a.nrows or len(norm_w) != a.ncols or len(sum_out) != a.ncols:
+            raise SlaiError(_lib.ERR_SHAPE, "Gemv: dimension mismatch")
+        self.backend.check(self.lib.slai_gemv_quant_reduced(self.h, _ptr(out), a.h, _ptr(norm_w), eps, index, per_token, _ptr(sum_out)))
+
+    def token_tick(self):
+        self.backend.check(self.lib.slai_tp_token_tick(self.h))
+
+    def peer_loopback(self, ranks: int, rank: int):
+        self.backend.check(self.lib.slai_tp_peer_loopback(self.h, ranks, rank))
 
     # RmsNorm::launch (ops/rms_norm.rs:35-67); LlmContext::rms_norm_assign
     def rms_norm_assign(self, result, value, weight, eps: float = 1e-5):

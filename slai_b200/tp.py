@@ -4,7 +4,9 @@ Partition (per layer; `t` = group size, rank `r`):
   column-parallel (rows split, whole heads):  wq rows [r*dim/t, ...), wk / wv rows [r*kv_dim/t, ...),
                                               w_gate / w_up rows [r*hidden/t, ...)
   row-parallel (K split on block boundaries): wo columns [r*dim/t, ...), w_down columns [r*hidden/t, ...)
-  replicated: norm weights, embedding, output matrix, the residual stream x.
+  output matrix: rows [r*vocab/t, ...) when vocab/t is a multiple of 16 (each rank computes its slice of the logits,
+                 one all-gather puts the whole vector on every rank), else replicated
+  replicated: norm weights, embedding, the residual stream x.
 Each rank keeps the KV cache of its own KV heads; attention needs no exchange.  After wo and after w_down the
 partial `dim`-vectors are summed over the ranks (`slai_tp_all_reduce_sum`: NCCL over NVLink, inside the decode graph).
 The host program's own communication layer (torch.distributed here; anything else works) is used only to hand
@@ -55,15 +57,23 @@ def shard_blocks(name: str, blocks: np.ndarray, fmt: int, rows: int, cols: int, 
     return np.ascontiguousarray(part).reshape(-1)
 
 
-def shard_llama_host(config: Llama2Config, weights: dict, fmt: int, rank: int, size: int) -> dict:
+def output_rows(config: Llama2Config, size: int) -> int:
+    """Rows of the output matrix one rank holds: vocab / size when that is a whole number of 16-row tiles, else all."""
+    return config.vocab_size // size if config.vocab_size % (16 * size) == 0 else config.vocab_size
+
+
+def shard_llama_host(config: Llama2Config, weights: dict, fmt: int, rank: int, size: int, out_fmt: int | None = None) -> dict:
     """The weights dict of `synthetic_llama_host`, reduced to rank `rank`'s shards."""
     check_divisible(config, fmt, size)
+    out_fmt = fmt if out_fmt is None else out_fmt
     full = config.matrix_shapes()
     out = {}
     for (name, l), val in weights.items():
         if name in LLAMA_MATRICES:
             r, c = full[name]
             out[(name, l)] = shard_blocks(name, val, fmt, r, c, rank, size)
+        elif name == "output" and output_rows(config, size) != config.vocab_size:
+            out[(name, l)] = shard_blocks(name, val, out_fmt, config.vocab_size, config.dim, rank, size)
         else:
             out[(name, l)] = val
     return out
@@ -126,12 +136,12 @@ def llama_from_host_tp(backend: Backend, config: Llama2Config, weights: dict, fm
     out_fmt = fmt if out_fmt is None else out_fmt
     m = Llama2(backend, config, rank, size)
     shapes = shard_shapes(config, size)
-    for (name, l), val in shard_llama_host(config, weights, fmt, rank, size).items():
+    for (name, l), val in shard_llama_host(config, weights, fmt, rank, size, out_fmt).items():
         if name in LLAMA_MATRICES:
             r, c = shapes[name]
             m.set_matrix(name, l, GpuQuantMatrix(backend, fmt, r, c, val))
         elif name == "output":
-            m.set_matrix(name, -1, GpuQuantMatrix(backend, out_fmt, config.vocab_size, config.dim, val))
+            m.set_matrix(name, -1, GpuQuantMatrix(backend, out_fmt, output_rows(config, size), config.dim, val))
         else:
             m.set_f32(name, l, val)
     return m
@@ -141,7 +151,8 @@ def synthetic_llama_device_tp(backend: Backend, config: Llama2Config, fmt: int, 
                               std: float = 0.02) -> Llama2:
     """Benchmark-sized sharded model generated on the device.  Shards of different ranks are seeded independently
     (they are not slices of one global random matrix; throughput does not depend on that); everything replicated
-    (embedding, output matrix, norms) is seeded identically on all ranks so that the ranks decode the same tokens."""
+    (embedding, norms) is seeded identically on all ranks, and every rank sees the gathered logits, so that the ranks
+    decode the same tokens."""
     check_divisible(config, fmt, size)
     m = Llama2(backend, config, rank, size)
     sid = seed * 1_000_003
@@ -156,11 +167,13 @@ def synthetic_llama_device_tp(backend: Backend, config: Llama2Config, fmt: int, 
     m.set_f32("token_embd", -1, emb)
     del emb
     m.set_f32("out_norm", -1, np.ones(config.dim, dtype=np.float32))
-    m.set_matrix("output", -1, GpuQuantMatrix.synthetic(backend, out_fmt, config.vocab_size, config.dim, sid + 7_000_002, std))
+    vr = output_rows(config, size)
+    m.set_matrix("output", -1, GpuQuantMatrix.synthetic(backend, out_fmt, vr, config.dim,
+                                                        sid + 7_000_002 + (100_000 * (rank + 1) if vr != config.vocab_size else 0), std))
     return m
 
 
 def bytes_per_token_per_rank(config: Llama2Config, fmt: int, out_fmt: int, size: int) -> int:
-    """Packed weight bytes one rank streams per decoded token: its shard of every layer plus the replicated output matrix."""
+    """Packed weight bytes one rank streams per decoded token: its shard of every layer and of the output matrix."""
     per = sum(r * c for r, c in shard_shapes(config, size).values())
-    return int(config.n_layers * per * synth.BITS_PER_WEIGHT[fmt] / 8 + config.vocab_size * config.dim * synth.BITS_PER_WEIGHT[out_fmt] / 8)
+    return int(config.n_layers * per * synth.BITS_PER_WEIGHT[fmt] / 8 + output_rows(config, size) * config.dim * synth.BITS_PER_WEIGHT[out_fmt] / 8)

@@ -32,7 +32,7 @@ struct Job {
 template <class F>
 static void lane_body(Job* J, int lane) {
     LaneCtx L;
-    lane_init(L, lane, J->S);
+    lane_init<F>(L, lane, J->S);
     float a = 0.f, b = 0.f;
     for (int s = 0; s < J->nsteps; s++) F::compute(J->tile0 + (uint32_t)s * J->step_bytes, s, L, J->S, a, b);
     J->acc[lane][0] = a;
@@ -88,22 +88,35 @@ int main(int argc, char** argv) {
     const int sv_gran = (fmt == 12 || fmt == 13) ? 32 : fmt == 14 ? 16 : 0;
     const size_t sv_bytes = sv_gran ? (size_t)(Kp / sv_gran) * 16 : 0;
     const int plane = Kp + 32;
-    const size_t tile_off = (size_t)(4 * plane + sv_bytes + 127) & ~(size_t)127;
+    const size_t dig0 = ZERO_BYTES;
+    const size_t sv0 = dig0 + 4 * (size_t)plane;
+    const size_t tile_off = (size_t)(sv0 + sv_bytes + 127) & ~(size_t)127;
     std::vector<unsigned char> smem(tile_off + tile.size() + 64, 0);
     memcpy(smem.data() + tile_off, tile.data(), tile.size());
     float mx = 0.f;
     for (int k = 0; k < K; k++) mx = fmaxf(mx, fabsf(v[k]));
     float scale = 1.f;
     if (mx > 0.f) { int e; frexpf(mx, &e); if (e < -90) e = -90; scale = ldexpf(1.0f, 26 - e); }
-    int* sv = (int*)(smem.data() + 4 * plane);
+    std::vector<int> sums(sv_gran ? (size_t)(Kp / sv_gran) * 4 : 0, 0);
     for (int k = 0; k < Kp; k++) {
         const float x = k < K ? v[k] * scale : 0.f;
-        int d[4];
-        frag::split_digits((int)nearbyintf(x), d);
+        const uint32_t word = frag::digits_word((int)nearbyintf(x));
         for (int p = 0; p < 4; p++) {
-            smem[(size_t)p * plane + k] = (unsigned char)(d[p] & 0xFF);
-            if (sv_gran) sv[(k / sv_gran) * 4 + p] += d[p];
+            const int d = (int)(signed char)((word >> (8 * p)) & 0xFF);
+            smem[dig0 + (size_t)p * plane + k] = (unsigned char)(d & 0xFF);
+            if (sv_gran) sums[(k / sv_gran) * 4 + p] += d;
         }
+    }
+    if (sv_gran == 16) {  // Q6_K: 4 x s32 per sub-block
+        memcpy(smem.data() + sv0, sums.data(), sums.size() * 4);
+    } else if (sv_gran == 32) {  // Q4_K / Q5_K: byte table (two base-128 digits per sum), see gemv_formats.cuh
+        for (int J = 0; J < Kp / 32; J++)
+            for (int q = 0; q < 4; q++) {
+                const int sd = sums[J * 4 + q], hi = (sd + 64) >> 7, lo = sd - hi * 128;
+                unsigned char* tab = smem.data() + sv0 + (size_t)(J >> 3) * 128;
+                tab[(2 * q) * 16 + (J & 7)] = (unsigned char)(hi & 0xFF);
+                tab[(2 * q + 1) * 16 + (J & 7)] = (unsigned char)(lo & 0xFF);
+            }
     }
 
     hostemu::Warp W;
@@ -112,7 +125,7 @@ int main(int argc, char** argv) {
     Job J;
     J.fmt = fmt; J.K = K; J.W = &W;
     J.nsteps = nsteps; J.tile0 = (uint32_t)tile_off; J.step_bytes = sbytes;
-    J.S.dig = 0; J.S.plane = plane; J.S.sv = 4 * plane;
+    J.S.zero = 0; J.S.dig = (uint32_t)dig0; J.S.plane = plane; J.S.sv = (uint32_t)sv0;
     pthread_t th[32];
     ThreadArg args[32];
     for (int l = 0; l < 32; l++) { args[l] = {&J, l}; pthread_create(&th[l], nullptr, thread_main, &args[l]); }

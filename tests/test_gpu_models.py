@@ -38,6 +38,32 @@ def test_tiny_llama_greedy_matches_fixture(backend):
     assert got == list(g["tokens"][:8])
 
 
+@pytest.mark.parametrize("which", ["7b", "70b"])
+def test_headline_shape_llama_matches_the_oracle_fixture(backend, which):
+    """Llama at the headline dimensions (7B: dim 4096 / FFN 11008 / 32 heads x 128 / vocab 32000, 2 layers, 64-token
+    prompt; 70B: dim 8192 / FFN 28672 / 64 query + 8 KV heads, 1 layer, 16-token prompt), Q4_K + Q6_K logits, fp16 KV:
+    logits of the last prompt token within 1e-3 relative L2 of the committed oracle run and the first 64 greedy ids
+    identical (tests/golden/make_shape_golden.py wrote the fixture and chose the seed; the smallest top-1/top-2
+    margin of the run is stored with it)."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_shape_golden", os.path.join(GOLD, "make_shape_golden.py"))
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    g = np.load(os.path.join(GOLD, gen.SHAPES[which]["file"]))
+    cfg = gen.config(which)
+    w = gen.weights(which, int(g["seed"][0]))
+    m = llama_from_host(backend, cfg, w, synth.FMT_Q4_K, synth.FMT_Q6_K)
+    del w
+    prompt = g["prompt"]
+    logits = m.prefill(prompt, 0, want_logits=True)
+    assert rel_l2(logits, g["last_prompt_logits"]) < 1e-3
+    first = int(np.argmax(logits))
+    assert first == int(g["tokens"][0])
+    toks = m.generate(first, len(prompt), 63)
+    assert float(g["margins"].min()) > 4e-4          # the ids are pinned: top two logits clearly apart at every step
+    assert [first] + list(toks) == list(g["tokens"][:64])
+
+
 @pytest.mark.parametrize("fmt,out_fmt", [(synth.FMT_Q4_K, synth.FMT_Q6_K), (synth.FMT_Q5_K, synth.FMT_Q5_K), (synth.FMT_Q8_0, synth.FMT_Q8_0)])
 @pytest.mark.parametrize("kv_dtype", [_lib.KV_F32, _lib.KV_F16])
 def test_small_llama_logits_and_tokens(backend, fmt, out_fmt, kv_dtype):

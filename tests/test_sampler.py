@@ -155,3 +155,27 @@ def test_generate_sampled_follows_the_oracle(backend):
         agree += 1
         tok = want
     assert agree >= 12
+
+
+def test_oracle_empty_nucleus_is_the_greedy_choice():
+    """No probability reaches the cutoff (1 - topp)/(n - 1): the reference panics on `n0 - 1`; defined here as the
+    greedy choice over the probabilities (first maximal index)."""
+    n = 64
+    flat = np.zeros(n, dtype=np.float32)          # every p = 1/64 < cutoff = (1 - 0.001)/63
+    assert O.sample(flat, 1.0, 0.001, 0.5)[0] == 0
+    tilted = flat.copy()
+    tilted[17] = 1e-3                             # still below the cutoff, but the maximum
+    assert O.sample(tilted, 1.0, 0.001, 0.9)[0] == 17
+
+
+@pytest.mark.gpu
+def test_device_empty_nucleus_matches_oracle(backend, ctx):
+    for n, hot in ((64, None), (64, 17), (5000, 4999), (5000, None)):
+        logits = np.zeros(n, dtype=np.float32)
+        if hot is not None:
+            logits[hot] = 1e-3
+        for coin in (0.0, 0.5, 0.999):
+            want, _ = O.sample(logits, 1.0, 0.5 / n, coin)
+            got = ctx.sample(backend.vector(logits), 1.0, 0.5 / n, coin)
+            assert got == want == (hot if hot is not None else 0)
+            assert 0 <= got < n

@@ -21,7 +21,7 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 def _cfg():
     from slai_b200.models import Llama2Config
     from slai_b200 import _lib
-    return Llama2Config(dim=512, hidden_dim=1024, n_layers=2, n_q_heads=8, n_kv_heads=4, vocab_size=600, seq_len=48, kv_dtype=_lib.KV_F32)
+    return Llama2Config(dim=512, hidden_dim=1024, n_layers=2, n_q_heads=8, n_kv_heads=4, vocab_size=640, seq_len=48, kv_dtype=_lib.KV_F32)
 
 
 def _free_port():
@@ -36,10 +36,11 @@ def _free_port():
 class ShardedOracle:
     """One rank of a tensor-parallel Llama on the CPU, built from the oracle's operators."""
 
-    def __init__(self, cfg, weights, fmt, rank, size, all_reduce):
+    def __init__(self, cfg, weights, fmt, rank, size, all_reduce, all_gather):
         from oracle import oracle as O
         from slai_b200 import tp
-        self.O, self.cfg, self.size, self.all_reduce = O, cfg, size, all_reduce
+        self.O, self.cfg, self.size, self.all_reduce, self.all_gather = O, cfg, size, all_reduce, all_gather
+        self.out_rows = tp.output_rows(cfg, size)
         shapes = tp.shard_shapes(cfg, size)
         sh = tp.shard_llama_host(cfg, weights, fmt, rank, size)
         self.w = {}
@@ -47,7 +48,7 @@ class ShardedOracle:
             if name in shapes:
                 self.w[(name, l)] = O.dequantize(fmt, val).reshape(shapes[name])
             elif name == "output":
-                self.w[(name, l)] = O.dequantize(fmt, val).reshape(cfg.vocab_size, cfg.dim)
+                self.w[(name, l)] = O.dequantize(fmt, val).reshape(self.out_rows, cfg.dim)
             else:
                 self.w[(name, l)] = np.asarray(val, dtype=np.float32)
         self.hs = cfg.head_size
@@ -72,7 +73,8 @@ class ShardedOracle:
             xb = O.rms_norm(x, w[("ffn_norm", l)], c.rms_norm_eps)
             hb = O.silu_gate(O.gemv_f32(w[("w_gate", l)], xb), O.gemv_f32(w[("w_up", l)], xb))
             x = x + self.all_reduce(O.gemv_f32(w[("w_down", l)], hb))       # exchange 2
-        return O.gemv_f32(w[("output", -1)], O.rms_norm(x, w[("out_norm", -1)], c.rms_norm_eps))
+        part = O.gemv_f32(w[("output", -1)], O.rms_norm(x, w[("out_norm", -1)], c.rms_norm_eps))
+        return self.all_gather(part) if self.out_rows != c.vocab_size else part   # each rank holds vocab / size rows
 
 
 def _cpu_rank(rank, world, port, q):
@@ -90,7 +92,12 @@ def _cpu_rank(rank, world, port, q):
         dist.all_reduce(t)
         return t.numpy()
 
-    m = ShardedOracle(cfg, weights, synth.FMT_Q4_K, rank, world, all_reduce)
+    def all_gather(v):
+        parts = [torch.zeros(v.size, dtype=torch.float32) for _ in range(world)]
+        dist.all_gather(parts, torch.from_numpy(np.ascontiguousarray(v, dtype=np.float32).copy()))
+        return torch.cat(parts).numpy()
+
+    m = ShardedOracle(cfg, weights, synth.FMT_Q4_K, rank, world, all_reduce, all_gather)
     outs = [m.forward(tok, pos) for pos, tok in enumerate([3, 17, 599, 42])]
     q.put((rank, np.stack(outs)))
     dist.barrier()
@@ -129,8 +136,8 @@ def test_shard_shapes_and_divisibility():
         assert sh["wo"] == (8192, 8192 // size) and sh["w_down"] == (8192, 28672 // size) and sh["wk"] == (1024 // size, 8192)
         full = LLAMA2_70B.weight_bytes_per_token(synth.FMT_Q4_K, synth.FMT_Q6_K)
         per = tp.bytes_per_token_per_rank(LLAMA2_70B, synth.FMT_Q4_K, synth.FMT_Q6_K, size)
-        out = 32000 * 8192 * synth.BITS_PER_WEIGHT[synth.FMT_Q6_K] / 8
-        assert abs((per - out) * size + out - full) < 1e-6 * full
+        assert tp.output_rows(LLAMA2_70B, size) == 32000 // size
+        assert abs(per * size - full) < 1e-6 * full   # everything is sharded: the ranks' bytes add up to the model's
     with pytest.raises(ValueError):
         tp.check_divisible(LLAMA2_7B, synth.FMT_Q4_K, 8)  # 11008 / 8 = 1376 is not a multiple of 256
     rng = np.random.default_rng(0)
@@ -175,11 +182,14 @@ def _gpu_rank(rank, world, port, q):
 
     # 1. the exchange as an NCCL all-reduce between the kernels
     m = tp.llama_from_host_tp(backend, cfg, weights, synth.FMT_Q4_K, None, rank, world)
+    assert tp.output_rows(cfg, world) == cfg.vocab_size // world   # the logits matrix is sharded too
+    tp.torch_barrier()   # the ranks start the first step together (peer polls are bounded)
     nccl = run(m)
     m.close()
     # 2. the exchange over peer memory, inside the GEMV kernels (same sums in the same order: identical bits)
     tp.enable_peer_exchange(backend, world, tp.torch_all_gather, tp.torch_barrier)
     m = tp.llama_from_host_tp(backend, cfg, weights, synth.FMT_Q4_K, None, rank, world)
+    tp.torch_barrier()
     peer = run(m)
     q.put((rank, s, nccl[0], nccl[1], nccl[2], nccl[3], peer[0], peer[2], peer[3]))
     dist.barrier()
@@ -222,8 +232,8 @@ def test_two_gpu_tensor_parallel_llama_matches_oracle():
     assert np.array_equal(got[0][2], got[1][2])       # bitwise: both ranks hold the same residual stream
     assert got[0][4] == got[1][4]                     # and generate the same tokens
     assert np.allclose(got[0][1], 3.0) and np.allclose(got[1][1], 3.0)
-    assert got[0][5] == 3 + cfg.n_layers * 7 + 1      # embed + (5 kernels + 2 exchanges) per layer + logits + argmax + advance
+    assert got[0][5] == 3 + cfg.n_layers * 7 + 1 + 1  # embed + (5 kernels + 2 exchanges) per layer + logits + gather + argmax + advance
     for r in range(2):                                # peer-memory exchange: no collective launches, identical results
         assert np.array_equal(got[r][6], got[r][2])
         assert got[r][7] == got[r][4]
-        assert got[r][8] == 3 + cfg.n_layers * 5 + 1 + 1   # + the token tick
+        assert got[r][8] == 3 + cfg.n_layers * 5 + 1 + 1 + 1   # + the token tick, + the logits gather
