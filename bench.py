@@ -264,7 +264,7 @@ def run_reference(args, rank, world):
                              "sample": "per step: one full layer (7 dense f32 gemvs on dequantised weights, attention over the "
                                        "prompt) + the logits gemv on the host, layer time x32"},
             "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def run_gpt2(args):
@@ -299,7 +299,7 @@ def run_gpt2(args):
             "clocks": clocks,
             "roofline": {"bound": "hbm", "bytes_per_token": bytes_tok, "achieved": bytes_tok / t / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": bytes_tok / t / 1e9 / peak, "peak_source": peak_src}}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def _tp_bit_identity(backend, group, cfg70):
@@ -403,12 +403,30 @@ def run_tp(args, group):
                      steps=args.steps, warmup=args.warmup, nccl_only=args.tp_nccl)
     if rec is not None:
         rec.update({"higher_is_better": True, "vs_baseline": None, "dtype": "f32", "data": "synthetic (shards seeded per rank)"})
-        print(json.dumps(rec), flush=True)
+        emit(rec)
     group.close()
 
 
+_RESULT_FD = None
+
+
+def emit(line: dict) -> None:
+    """The one JSON line, on the process's original standard output."""
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def main():
-    # NCCL's version banner and debug lines go to stderr: stdout carries the one JSON line
+    # Libraries print to file descriptor 1 as they please (NCCL's version banner, for one): everything written there during
+    # the run is sent to stderr, and the one JSON line goes to the original standard output.
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -547,7 +565,7 @@ def main():
             line["cpu_baseline"] = cpu
         if tp_rec is not None:
             line["tp"] = tp_rec
-        print(json.dumps(line), flush=True)
+        emit(line)
     group.close()
 
 
