@@ -48,6 +48,31 @@ def measured_peaks():
     return 6650.0, "fallback (6.65 TB/s earlier measurement on this pool)"
 
 
+def measured_tensor_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["bf16_tflops_sustained"]), "measured (MEASURED_PEAKS.json bf16_tflops_sustained)"
+    return 1400.0, "fallback (1.4 PFLOP/s sustained, earlier measurement on this pool)"
+
+
+def prefill_record(cfg, n_tokens, seconds, sequential_ms_per_token=None):
+    """Prompt processing of `n_tokens` through the tensor-core GEMM path: model FLOPs = 2 x layer weights x tokens (the
+    logits matrix is applied to the last token only).  Every model product is issued as three fp16 products
+    (hi*hi, hi*lo, lo*hi of fp16 operand pairs, f32 accumulation), so the tensor cores execute three times the model
+    FLOPs; both figures are given against the measured dense bf16 peak."""
+    peak, src = measured_tensor_peak()
+    layer_params = sum(r * c for r, c in cfg.matrix_shapes().values())
+    flops = 2.0 * cfg.n_layers * layer_params * n_tokens
+    rec = {"tokens": n_tokens, "seconds": seconds, "tok_s": n_tokens / seconds, "model_tflops": flops / seconds / 1e12,
+           "tensor_tflops_executed": 3 * flops / seconds / 1e12, "operands": "fp16 pairs (hi + lo) for weights and activations, f32 accumulators in TMEM",
+           "peak_tflops": peak, "frac_model": flops / seconds / 1e12 / peak, "frac_executed": 3 * flops / seconds / 1e12 / peak, "peak_source": src}
+    if sequential_ms_per_token:
+        rec["sequential_estimate_s"] = sequential_ms_per_token * 1e-3 * n_tokens
+        rec["speedup_vs_sequential"] = rec["sequential_estimate_s"] / seconds
+    return rec
+
+
 class ClockSampler:
     """nvidia-smi clock / throttle-reason samples during the timed region."""
 
@@ -359,6 +384,9 @@ def measure_tp(args, group, n_layers=0, prompt_len=1024, steps=None, warmup=None
     # not whenever each rank has finished building its shard.
     backend.synchronize()
     group.barrier()
+    m.prefill(prompt[:16], 0)  # warm-up; overwritten by the timed pass
+    backend.synchronize()
+    group.barrier()
     t0 = time.perf_counter()
     m.prefill(prompt[:-1], 0)
     prefill_s = time.perf_counter() - t0
@@ -385,7 +413,8 @@ def measure_tp(args, group, n_layers=0, prompt_len=1024, steps=None, warmup=None
                "config": {"workload": "llama2-70b-arch q4_k (q6_k logits) bs1 decode, fp16 KV", "n_layers": cfg.n_layers,
                           "prompt_len": PL, "decode_positions": [pos, pos + K - 1], "parallelism": f"tp{world}", "exchange": exchange,
                           "logits": "output matrix sharded by rows, logits all-gathered" if world > 1 else "whole output matrix"},
-               "prefill_s": prefill_s, "prefill": "sequential single-token steps",
+               "prefill_s": prefill_s,
+               "prefill": (prefill_record(cfg, PL - 1, prefill_s, ms / K) if world == 1 else "sequential single-token steps (the GEMM path serves one GPU)"),
                "clocks": clocks, "launches_per_token": m.launches_per_token(), "gpu_launches": m.launches_per_token() * K,
                "ranks_agree": all(r == ids[0] for r in ids), "nccl_and_peer_exchange_bit_identical": identical,
                "roofline": {"bound": "hbm", "per_gpu_bytes_per_token": per_rank + kv, "achieved": (per_rank + kv) / t / 1e9, "peak": peak,
@@ -474,7 +503,11 @@ def main():
 
     rng = np.random.default_rng(42 + rank)
     prompt = rng.integers(0, cfg.vocab_size, size=PROMPT_LEN).astype(np.int32)
+    m.prefill(prompt[:16], 0)  # warms the kernels up (buffers, attributes); overwritten by the timed pass
+    backend.synchronize()
+    t0 = time.perf_counter()
     m.prefill(prompt[:-1], 0)
+    prefill_s = time.perf_counter() - t0
     pos = PROMPT_LEN - 1
     tok = int(prompt[-1])
 
@@ -549,6 +582,7 @@ def main():
             "config": workload_config(world, K, W),
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 16, "d2h_bytes_per_step": cfg.vocab_size * 4 + 4},
+            "prefill": prefill_record(cfg, PROMPT_LEN - 1, prefill_s, ms / K),
             "gpu_launches": launches_per_token * K,
             "launches_per_token": launches_per_token,
             "token_roofline": {"bytes_per_token": token_bytes, "roofline_tok_s": peak * 1e9 / token_bytes,

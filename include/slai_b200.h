@@ -286,10 +286,16 @@ int slai_llama_generate(slai_llama* m, int32_t token, int32_t pos, int32_t n, in
 int slai_llama_generate_sampled(slai_llama* m, int32_t token, int32_t pos, int32_t n, float temperature, float topp, uint64_t seed,
                                 int32_t* h_tokens);
 /* Prompt processing: tokens[0..n) at positions pos0.. ; fills the KV cache.  If h_last_logits is non-NULL
- * it receives the logits of the last prompt token.  Blocking. */
+ * it receives the logits of the last prompt token.  Blocking.  The reference feeds the prompt through its decode step
+ * token by token (chat_llama2.rs:109-115); here prompts of 16 tokens or more go through every matrix together as
+ * GEMMs on the tensor cores (quantised matrices whose column count is a multiple of 64, one GPU), shorter ones and
+ * everything else through the decode step as there.  Same results within 1e-3 relative L2. */
 int slai_llama_prefill(slai_llama* m, const int32_t* h_tokens, int32_t n, int32_t pos0, float* h_last_logits);
 /* Debug/test access to Llama2State vectors: 0 x, 1 xb, 2 q, 3 hb, 4 logits.  Blocking. */
 int slai_llama_read_state(slai_llama* m, int which, float* h_out, int64_t n);
+/* Test access to the KV cache of one layer: positions 0..n_pos as f32, position-major like the reference's cache
+ * (h_keys / h_values: n_pos x kv_dim floats).  Blocking. */
+int slai_llama_read_kv(slai_llama* m, int layer, int n_pos, float* h_keys, float* h_values);
 /* Number of kernel launches issued for the last decoded token. */
 int slai_llama_launches_per_token(const slai_llama* m);
 

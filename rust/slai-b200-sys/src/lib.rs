@@ -98,6 +98,7 @@ extern "C" {
     pub fn slai_sample(ctx: *mut slai_ctx, d_logits: *mut f32, n: i64, temperature: f32, topp: f32, coin: f32, d_token_out: *mut i32) -> i32;
     pub fn slai_llama_prefill(m: *mut slai_llama, h_tokens: *const i32, n: i32, pos0: i32, h_last_logits: *mut f32) -> i32;
     pub fn slai_llama_read_state(m: *mut slai_llama, which: i32, h_out: *mut f32, n: i64) -> i32;
+    pub fn slai_llama_read_kv(m: *mut slai_llama, layer: i32, n_pos: i32, h_keys: *mut f32, h_values: *mut f32) -> i32;
     pub fn slai_llama_launches_per_token(m: *const slai_llama) -> i32;
     pub fn slai_gpt2_create(ctx: *mut slai_ctx, cfg: *const slai_gpt2_config, out: *mut *mut slai_gpt2) -> i32;
     pub fn slai_gpt2_destroy(m: *mut slai_gpt2) -> i32;

@@ -26,7 +26,18 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnParams P) {
 #ifdef SLAI_TRACE
     tl1 = slai_globaltimer();
 #endif
-    {
+    if (P.batch > 0) {  // prompt processing: one query token per blockIdx.z
+        const int b = (int)blockIdx.z;
+        AttnParams Q = P;
+        Q.q = P.q + (size_t)b * P.q_bs;
+        Q.out = P.out + (size_t)b * P.out_bs;
+        Q.part_o = P.part_o + (size_t)b * P.po_bs;
+        Q.part_ml = P.part_ml + (size_t)b * P.pml_bs;
+        Q.counters = P.counters + (size_t)b * gridDim.x;
+        const int n = P.pos0 + b + 1;
+        const int ns = attn_splits(Q, n);
+        if ((int)blockIdx.y < ns) attn_item<T, MAXQ>(Q, blockIdx.x, blockIdx.y, ns, n, threadIdx.x, sm, 0);
+    } else {
         const int n = __ldcg(P.d_pos) + 1;
         const int ns = attn_splits(P, n);
         if ((int)blockIdx.y < ns) attn_item<T, MAXQ>(P, blockIdx.x, blockIdx.y, ns, n, threadIdx.x, sm, 0);
@@ -55,7 +66,7 @@ int launch_t(slai_ctx* ctx, const AttnParams& P, int n_kv, size_t smem, bool pdl
         attr.set(ctx->device);
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(n_kv, P.n_splits);
+    cfg.gridDim = dim3(n_kv, P.n_splits, P.batch > 0 ? P.batch : 1);
     cfg.blockDim = dim3(ATT_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
@@ -132,7 +143,9 @@ int attention_launch(slai_ctx* ctx, const AttnLaunch& A) {
         if (rc) return rc;
     }
     const size_t po = (size_t)A.n_heads * P.n_splits * A.head_size * 4;
-    const size_t need = attention_scratch_bytes(ctx, A.n_heads, A.kv_mul, A.head_size, A.max_pos);
+    const size_t per_token = attention_scratch_bytes(ctx, A.n_heads, A.kv_mul, A.head_size, A.max_pos);
+    const size_t need = per_token * (size_t)(A.batch > 0 ? A.batch : 1);
+    SLAI_REQUIRE(ctx, A.batch == 0 || (A.scratch && A.batch_counters), SLAI_ERR_INVALID_ARG, "attention: a batch needs its own scratch and tickets");
     void* scratch = A.scratch;
     if (!scratch) {
         int rc = ensure_scratch(ctx, need);
@@ -150,7 +163,9 @@ int attention_launch(slai_ctx* ctx, const AttnLaunch& A) {
 #endif
     P.part_o = reinterpret_cast<float*>(scratch);
     P.part_ml = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + ((po + 255) & ~(size_t)255));
-    P.counters = ctx->d_counters + CNT_ATTN_TICKETS;
+    P.counters = A.batch > 0 ? A.batch_counters : ctx->d_counters + CNT_ATTN_TICKETS;
+    P.batch = A.batch; P.pos0 = A.pos0; P.q_bs = A.q_batch_stride; P.out_bs = A.out_batch_stride;
+    P.po_bs = (long long)(per_token / 4); P.pml_bs = (long long)(per_token / 4);  // every token's partials in its own slice of the scratch
     const bool f16 = A.kv_dtype == SLAI_KV_F16;
     if (A.kv_mul == 1) return f16 ? launch_t<__half, 1>(ctx, P, n_kv, smem, A.pdl) : launch_t<float, 1>(ctx, P, n_kv, smem, A.pdl);
     if (A.kv_mul <= 4) return f16 ? launch_t<__half, 4>(ctx, P, n_kv, smem, A.pdl) : launch_t<float, 4>(ctx, P, n_kv, smem, A.pdl);

@@ -24,6 +24,9 @@ struct AttnParams {
     float* part_ml;  // [n_heads][n_splits][2]
     unsigned int* counters;  // [n_kv_heads]
     PrefetchPlan ahead;      // weights of a later kernel, pulled into L2 by all blocks at the start
+    // batch of query tokens (blockIdx.z): per-token strides of q / out / partials / tickets; position of token b = pos0 + b
+    int batch = 0, pos0 = 0;
+    long long q_bs = 0, out_bs = 0, po_bs = 0, pml_bs = 0;
 #ifdef SLAI_TRACE
     unsigned long long* tl = nullptr;  // trace build only: the context's launch timeline
 #endif

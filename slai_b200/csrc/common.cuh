@@ -258,6 +258,13 @@ struct AttnLaunch {
     void* scratch;      // split partials; NULL = the context's scratch (grown on demand, not graph-safe)
     size_t scratch_bytes;
     PrefetchPlan ahead; // weights of a later kernel: pulled into L2 by this one
+    // A batch of query tokens (prompt processing): token b reads q + b * q_batch_stride, attends to positions
+    // 0..=pos0 + b, writes out + b * out_batch_stride; d_pos is ignored.  `scratch` then holds `batch` times the
+    // per-token partials and `batch_counters` one zeroed ticket per (token, KV head).
+    int batch = 0;
+    int pos0 = 0;
+    long long q_batch_stride = 0, out_batch_stride = 0;
+    unsigned int* batch_counters = nullptr;
 };
 size_t attention_scratch_bytes(slai_ctx* ctx, int n_heads, int kv_mul, int head_size, int max_pos);
 int attention_launch(slai_ctx* ctx, const AttnLaunch& A);
@@ -304,6 +311,27 @@ __device__ __forceinline__ void slai_tl_append(unsigned long long* tl, unsigned 
     for (int k = 0; k < TL_SLOTS - 1; k++) tl[TL_SLOTS * i + 1 + k] = stamps[k];
 }
 #endif
+
+// prefill.cu: prompt processing as GEMMs on the tcgen05 tensor cores
+struct PrefillGemm {
+    const slai_qmatrix* w = nullptr;  // quantised matrix [rows_total x K]; the first `rows` rows are used
+    int rows = 0;
+    const __half* x_hi = nullptr;     // activations as fp16 pairs (x = hi + lo), planes of [t_pad][K]
+    const __half* x_lo = nullptr;
+    int T = 0, t_pad = 0, NT = 0;     // valid tokens, allocated rows (multiple of NT), tokens per CTA tile
+    float* out = nullptr;             // [T][ldo], row m of the product at column out_off + m
+    int ldo = 0, out_off = 0;
+    const float* resid = nullptr;     // optional [T][ldr]: out = resid + product (may alias out)
+    int ldr = 0;
+    const float* bias = nullptr;      // optional [rows]
+};
+size_t prefill_gemm_smem(int NT);
+int prefill_gemm_launch(slai_ctx* ctx, const PrefillGemm& G);
+int prefill_split_launch(slai_ctx* ctx, const float* x, int ldx, const float* norm_w, float eps, int T, int K, __half* hi, __half* lo);
+int prefill_silu_split_launch(slai_ctx* ctx, const float* gate, const float* up, int T, int H, __half* hi, __half* lo);
+int prefill_embed_launch(slai_ctx* ctx, float* x, int dim, const int* d_tokens, int T, const float* table, const slai_qmatrix* qtable);
+int prefill_rope_kv_launch(slai_ctx* ctx, const float* qkv, int ld, int q_dim, int kv_dim, int head_size, int pos0, int T,
+                           const float* theta, int neox, float* q_out, void* kcache, void* vcache, int kv_f16, long long kv_head_stride);
 
 // decode.cu: all layers of a token in one persistent kernel (Llama family, one weight format for all matrices)
 struct DecodeLayersDesc {

@@ -7,6 +7,8 @@
 // down+residual), chained with programmatic dependent launch and captured once into a CUDA graph that is
 // replayed per token; token id and position live in device scalars, and greedy decoding / prompt
 // processing advance them on the device so the host only launches graphs.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace {
@@ -125,6 +127,14 @@ struct slai_llama {
     const float* rope_theta = nullptr;
     GraphSet graphs;
     int launches = 0;
+    // prompt processing as GEMMs (prefill.cu): buffers for `pf_cap` tokens, grown on demand
+    int pf_cap = 0, pf_attn_batch = 0;
+    float *pf_x = nullptr, *pf_qkv = nullptr, *pf_q = nullptr, *pf_xb = nullptr, *pf_g = nullptr, *pf_u = nullptr;
+    __half *pf_hi = nullptr, *pf_lo = nullptr;
+    int* pf_tokens = nullptr;
+    void* pf_attn_scratch = nullptr;
+    size_t pf_attn_scratch_bytes = 0;
+    unsigned int* pf_tickets = nullptr;
     // fused path: all layers in one persistent kernel (decode.cu)
     int fused_state = 0;  // 0 not prepared, 1 ready, -1 not eligible
     int fused_fmt = 0;
@@ -132,6 +142,19 @@ struct slai_llama {
     DecodeParams* dparams = nullptr;  // parameter block of the persistent kernel (host copy, passed by value at launch)
     float *f_part_o = nullptr, *f_part_ml = nullptr;
 };
+
+static void llama_drop_prefill(slai_llama* m) {
+    if (m->pf_cap) cudaStreamSynchronize(m->ctx->stream);
+    cudaFree(m->pf_x); cudaFree(m->pf_qkv); cudaFree(m->pf_q); cudaFree(m->pf_xb); cudaFree(m->pf_g); cudaFree(m->pf_u);
+    cudaFree(m->pf_hi); cudaFree(m->pf_lo); cudaFree(m->pf_tokens); cudaFree(m->pf_attn_scratch); cudaFree(m->pf_tickets);
+    m->pf_x = m->pf_qkv = m->pf_q = m->pf_xb = m->pf_g = m->pf_u = nullptr;
+    m->pf_hi = m->pf_lo = nullptr;
+    m->pf_tokens = nullptr;
+    m->pf_attn_scratch = nullptr;
+    m->pf_attn_scratch_bytes = 0;
+    m->pf_tickets = nullptr;
+    m->pf_cap = 0;
+}
 
 static void llama_drop_fused(slai_llama* m) {
     if (m->f_part_o || m->f_part_ml) cudaStreamSynchronize(m->ctx->stream);
@@ -529,6 +552,7 @@ SLAI_API int slai_llama_destroy(slai_llama* m) {
     cudaStreamSynchronize(m->ctx->stream);
     destroy_graphs(m->graphs);
     llama_drop_fused(m);
+    llama_drop_prefill(m);
     for (auto& l : m->layers) {
         cudaFree(l.attn_norm); cudaFree(l.ffn_norm); cudaFree(l.bq); cudaFree(l.bk); cudaFree(l.bv);
     }
@@ -685,6 +709,142 @@ static int prefill_impl(M* m, RecordFn record, int vocab, int seq_len, const int
     return slai_check_wait_flag(ctx);
 }
 
+// ---- prompt processing as GEMMs -----------------------------------------------------------------------------------------
+// The T prompt tokens go through every layer together (prefill.cu): per layer RmsNorm + fp16-pair split, q / k / v
+// GEMMs, RoPE + KV-cache write, causal attention (the decode kernel with one query token per blockIdx.z), output GEMM
+// with residual, RmsNorm + split, gate and up GEMMs, SiLU + split, down GEMM with residual.  Only the last token's
+// logits are needed: its row of the residual stream goes back into the decode state and the decode step's own final
+// norm + logits GEMV (+ greedy choice) run on it.
+static bool llama_prefill_eligible(const slai_llama* m, int n) {
+    const char* e = getenv("SLAI_PREFILL_SEQUENTIAL");
+    if (e && e[0] == '1') return false;
+    if (n < 16 || m->tp != 1 || m->kv_mul > 8) return false;
+    if (!m->out_norm || (!m->token_embd && !m->embd_q)) return false;
+    for (auto& w : m->layers) {
+        const slai_qmatrix* ms[7] = {w.wq, w.wk, w.wv, w.wo, w.wgate, w.wup, w.wdown};
+        for (auto* q : ms)
+            if (!q || q->fmt == SLAI_FMT_F32 || q->ncols % 64 != 0) return false;
+        if (!w.attn_norm || !w.ffn_norm) return false;
+    }
+    return true;
+}
+
+static int llama_prefill_reserve(slai_llama* m, int t_pad, int attn_batch, size_t attn_bytes, int n_kv) {
+    slai_ctx* ctx = m->ctx;
+    const slai_llama_config& c = m->cfg;
+    if (t_pad > m->pf_cap || attn_batch > m->pf_attn_batch) llama_drop_prefill(m);
+    if (!m->pf_cap) {
+        const size_t T = (size_t)t_pad;
+        const size_t kmax = (size_t)std::max(std::max(c.dim, m->hidden), m->q_dim);
+        bool ok = cudaMalloc(&m->pf_x, T * c.dim * 4) == cudaSuccess && cudaMalloc(&m->pf_qkv, T * (m->q_dim + 2 * m->kv_dim) * 4) == cudaSuccess &&
+                  cudaMalloc(&m->pf_q, T * m->q_dim * 4) == cudaSuccess && cudaMalloc(&m->pf_xb, T * m->q_dim * 4) == cudaSuccess &&
+                  cudaMalloc(&m->pf_g, T * m->hidden * 4) == cudaSuccess && cudaMalloc(&m->pf_u, T * m->hidden * 4) == cudaSuccess &&
+                  cudaMalloc(&m->pf_hi, T * kmax * 2) == cudaSuccess && cudaMalloc(&m->pf_lo, T * kmax * 2) == cudaSuccess &&
+                  cudaMalloc(&m->pf_tokens, T * 4) == cudaSuccess && cudaMalloc(&m->pf_tickets, (size_t)attn_batch * n_kv * 4) == cudaSuccess &&
+                  cudaMemsetAsync(m->pf_tickets, 0, (size_t)attn_batch * n_kv * 4, ctx->stream) == cudaSuccess;
+        if (!ok) {
+            cudaGetLastError();
+            llama_drop_prefill(m);
+            return slai_set_error(ctx, SLAI_ERR_OOM, "prefill: cannot allocate buffers for %d tokens", t_pad);
+        }
+        m->pf_cap = t_pad;
+        m->pf_attn_batch = attn_batch;
+    }
+    // attention partials of one batch of query tokens: sized by the last position of this prompt
+    if (m->pf_attn_scratch_bytes < attn_bytes) {
+        if (m->pf_attn_scratch) {
+            cudaStreamSynchronize(ctx->stream);
+            cudaFree(m->pf_attn_scratch);
+            m->pf_attn_scratch = nullptr;
+        }
+        if (cudaMalloc(&m->pf_attn_scratch, attn_bytes) != cudaSuccess) {
+            cudaGetLastError();
+            m->pf_attn_scratch_bytes = 0;
+            return slai_set_error(ctx, SLAI_ERR_OOM, "prefill: cannot allocate %zu bytes of attention scratch", attn_bytes);
+        }
+        m->pf_attn_scratch_bytes = attn_bytes;
+    }
+    return SLAI_OK;
+}
+
+static int llama_prefill_batched(slai_llama* m, const int32_t* h_tokens, int n, int pos0, float* h_last_logits) {
+    slai_ctx* ctx = m->ctx;
+    const slai_llama_config& c = m->cfg;
+    const int NT = std::min(256, (n + 15) / 16 * 16);
+    const int t_pad = (n + NT - 1) / NT * NT;
+    const int AB = 64;  // query tokens per attention launch
+    const int n_kv = m->n_q_local / m->kv_mul;
+    const size_t attn_per_token = attention_scratch_bytes(ctx, m->n_q_local, m->kv_mul, m->head_size, pos0 + n - 1);
+    int rc = llama_prefill_reserve(m, t_pad, AB, attn_per_token * AB, n_kv);
+    if (rc) return rc;
+    const size_t esz = c.kv_dtype == SLAI_KV_F16 ? 2 : 4;
+    const size_t kmax = (size_t)std::max(std::max(c.dim, m->hidden), m->q_dim);
+    SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(m->pf_tokens, h_tokens, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream));
+    SLAI_CHECK_CUDA(ctx, cudaMemsetAsync(m->pf_hi, 0, (size_t)m->pf_cap * kmax * 2, ctx->stream));  // rows beyond the prompt stay zero
+    SLAI_CHECK_CUDA(ctx, cudaMemsetAsync(m->pf_lo, 0, (size_t)m->pf_cap * kmax * 2, ctx->stream));
+    if ((rc = prefill_embed_launch(ctx, m->pf_x, c.dim, m->pf_tokens, n, m->embd_q ? nullptr : m->token_embd, m->embd_q))) return rc;
+    const int qkv_ld = m->q_dim + 2 * m->kv_dim;
+    auto gemm = [&](const slai_qmatrix* w, int rows, float* out, int ldo, int off, const float* resid, int ldr, const float* bias) {
+        PrefillGemm G;
+        G.w = w; G.rows = rows; G.x_hi = m->pf_hi; G.x_lo = m->pf_lo; G.T = n; G.t_pad = t_pad; G.NT = NT;
+        G.out = out; G.ldo = ldo; G.out_off = off; G.resid = resid; G.ldr = ldr; G.bias = bias;
+        return prefill_gemm_launch(ctx, G);
+    };
+    for (int l = 0; l < c.n_layers; l++) {
+        const LlamaLayer& w = m->layers[l];
+        void* kc = (char*)m->kcache + (size_t)l * m->kv_layer_elems * esz;
+        void* vc = (char*)m->vcache + (size_t)l * m->kv_layer_elems * esz;
+        // q, k, v                                                              transformer.rs:327-347
+        if ((rc = prefill_split_launch(ctx, m->pf_x, c.dim, w.attn_norm, c.rms_norm_eps, n, c.dim, m->pf_hi, m->pf_lo))) return rc;
+        if ((rc = gemm(w.wq, m->q_dim, m->pf_qkv, qkv_ld, 0, nullptr, 0, w.bq))) return rc;
+        if ((rc = gemm(w.wk, m->kv_dim, m->pf_qkv, qkv_ld, m->q_dim, nullptr, 0, w.bk))) return rc;
+        if ((rc = gemm(w.wv, m->kv_dim, m->pf_qkv, qkv_ld, m->q_dim + m->kv_dim, nullptr, 0, w.bv))) return rc;
+        if ((rc = prefill_rope_kv_launch(ctx, m->pf_qkv, qkv_ld, m->q_dim, m->kv_dim, m->head_size, pos0, n, m->rope_theta, c.rope_variant != 0,
+                                         m->pf_q, kc, vc, c.kv_dtype == SLAI_KV_F16, (long long)c.seq_len * m->head_size)))
+            return rc;
+        // attention, AB query tokens per launch                                transformer.rs:350
+        for (int t0 = 0; t0 < n; t0 += AB) {
+            const int nb = std::min(AB, n - t0);
+            AttnLaunch A;
+            A.q = m->pf_q + (size_t)t0 * m->q_dim; A.kcache = kc; A.vcache = vc; A.kv_dtype = c.kv_dtype;
+            A.pos_stride = m->head_size; A.head_stride = (int64_t)c.seq_len * m->head_size;
+            A.n_heads = m->n_q_local; A.kv_mul = m->kv_mul; A.head_size = m->head_size;
+            A.d_pos = nullptr; A.max_pos = pos0 + n - 1; A.out = m->pf_xb + (size_t)t0 * m->q_dim; A.pdl = false;
+            A.scratch = m->pf_attn_scratch; A.scratch_bytes = m->pf_attn_scratch_bytes;
+            A.batch = nb; A.pos0 = pos0 + t0; A.q_batch_stride = m->q_dim; A.out_batch_stride = m->q_dim; A.batch_counters = m->pf_tickets;
+            if ((rc = attention_launch(ctx, A))) return rc;
+        }
+        // x += Wo xb                                                           transformer.rs:352-355
+        if ((rc = prefill_split_launch(ctx, m->pf_xb, m->q_dim, nullptr, 0.f, n, m->q_dim, m->pf_hi, m->pf_lo))) return rc;
+        if ((rc = gemm(w.wo, c.dim, m->pf_x, c.dim, 0, m->pf_x, c.dim, nullptr))) return rc;
+        // FFN                                                                  transformer.rs:356-365
+        if ((rc = prefill_split_launch(ctx, m->pf_x, c.dim, w.ffn_norm, c.rms_norm_eps, n, c.dim, m->pf_hi, m->pf_lo))) return rc;
+        if ((rc = gemm(w.wgate, m->hidden, m->pf_g, m->hidden, 0, nullptr, 0, nullptr))) return rc;
+        if ((rc = gemm(w.wup, m->hidden, m->pf_u, m->hidden, 0, nullptr, 0, nullptr))) return rc;
+        if ((rc = prefill_silu_split_launch(ctx, m->pf_g, m->pf_u, n, m->hidden, m->pf_hi, m->pf_lo))) return rc;
+        if ((rc = gemm(w.wdown, c.dim, m->pf_x, c.dim, 0, m->pf_x, c.dim, nullptr))) return rc;
+    }
+    // the last token's state goes back to the decode step's vectors; final norm, logits and the greedy choice as there
+    SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(m->x, m->pf_x + (size_t)(n - 1) * c.dim, (size_t)c.dim * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    const slai_qmatrix* wout = m->output ? m->output : (m->embd_q ? m->embd_q : &m->embd_as_matrix);
+    if (wout->fmt == SLAI_FMT_F32) {
+        if ((rc = slai_rms_norm(ctx, m->xb, m->x, m->out_norm, c.dim, c.rms_norm_eps))) return rc;
+        GemvLaunch L;
+        L.fmt = SLAI_FMT_F32; L.K = c.dim; L.nseg = 1; L.seg[0] = seg_of(wout, 0, c.vocab_size, nullptr, 0, 0);
+        L.v = m->xb; L.out = m->logits; L.pdl = false;
+        if ((rc = gemv_launch(ctx, L))) return rc;
+    } else {
+        GemvLaunch L;
+        L.fmt = wout->fmt; L.K = c.dim; L.nseg = 1; L.seg[0] = seg_of(wout, 0, c.vocab_size, nullptr, 0, 0);
+        L.v = m->x; L.out = m->logits; L.pro = PRO_RMS; L.norm_w = m->out_norm; L.eps = c.rms_norm_eps; L.epi = EPI_STORE; L.pdl = false;
+        if ((rc = gemv_launch(ctx, L))) return rc;
+    }
+    if ((rc = launch_argmax(ctx, m->logits, c.vocab_size, m->sc.d + 3, false))) return rc;
+    if (h_last_logits) SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(h_last_logits, m->logits, (size_t)c.vocab_size * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return slai_check_wait_flag(ctx);
+}
+
 SLAI_API int slai_llama_decode(slai_llama* m, int32_t token, int32_t pos, float* h_logits, int32_t* next_token) {
     if (!m) return SLAI_ERR_INVALID_ARG;
     SLAI_ENTER(m->ctx);
@@ -712,6 +872,11 @@ SLAI_API int slai_llama_generate(slai_llama* m, int32_t token, int32_t pos, int3
 SLAI_API int slai_llama_prefill(slai_llama* m, const int32_t* h_tokens, int32_t n, int32_t pos0, float* h_last_logits) {
     if (!m) return SLAI_ERR_INVALID_ARG;
     SLAI_ENTER(m->ctx);
+    if (h_tokens && n >= 16 && pos0 >= 0 && pos0 + n <= m->cfg.seq_len && llama_prefill_eligible(m, n)) {
+        for (int i = 0; i < n; i++)
+            SLAI_REQUIRE(m->ctx, h_tokens[i] >= 0 && h_tokens[i] < m->cfg.vocab_size, SLAI_ERR_INVALID_ARG, "prefill: token %d out of range", h_tokens[i]);
+        return llama_prefill_batched(m, h_tokens, n, pos0, h_last_logits);
+    }
     return prefill_impl(m, llama_record, m->cfg.vocab_size, m->cfg.seq_len, h_tokens, n, pos0, h_last_logits);
 }
 SLAI_API int slai_llama_read_state(slai_llama* m, int which, float* h_out, int64_t n) {
@@ -729,6 +894,29 @@ SLAI_API int slai_llama_read_state(slai_llama* m, int which, float* h_out, int64
     }
     SLAI_REQUIRE(m->ctx, n > 0 && n <= cap, SLAI_ERR_SHAPE, "read_state: n=%lld exceeds %lld", (long long)n, (long long)cap);
     return slai_read_buffer(m->ctx, h_out, src, (size_t)n * 4);
+}
+SLAI_API int slai_llama_read_kv(slai_llama* m, int layer, int n_pos, float* h_keys, float* h_values) {
+    if (!m || !h_keys || !h_values) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(m->ctx);
+    slai_ctx* ctx = m->ctx;
+    const slai_llama_config& c = m->cfg;
+    SLAI_REQUIRE(ctx, layer >= 0 && layer < c.n_layers && n_pos > 0 && n_pos <= c.seq_len, SLAI_ERR_INVALID_ARG, "read_kv: layer %d / %d positions", layer, n_pos);
+    const size_t esz = c.kv_dtype == SLAI_KV_F16 ? 2 : 4;
+    const int n_kv = m->kv_dim / m->head_size, hs = m->head_size;
+    std::vector<unsigned char> raw((size_t)n_pos * hs * esz);
+    for (int which = 0; which < 2; which++) {
+        const char* base = (const char*)(which ? m->vcache : m->kcache) + (size_t)layer * m->kv_layer_elems * esz;
+        float* out = which ? h_values : h_keys;
+        for (int h = 0; h < n_kv; h++) {  // cache: [kv_head][position][head_size]; out: [position][kv_head * head_size]
+            SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(raw.data(), base + (size_t)h * c.seq_len * hs * esz, raw.size(), cudaMemcpyDeviceToHost, ctx->stream));
+            SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            for (int p = 0; p < n_pos; p++)
+                for (int d = 0; d < hs; d++)
+                    out[(size_t)p * m->kv_dim + h * hs + d] = esz == 2 ? __half2float(reinterpret_cast<const __half*>(raw.data())[(size_t)p * hs + d])
+                                                                       : reinterpret_cast<const float*>(raw.data())[(size_t)p * hs + d];
+        }
+    }
+    return SLAI_OK;
 }
 SLAI_API int slai_llama_launches_per_token(const slai_llama* m) { return m ? m->launches : 0; }
 

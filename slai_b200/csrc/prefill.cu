@@ -1,0 +1,501 @@
+// Prompt processing as dense contractions on the 5th-generation tensor cores (tcgen05, accumulators in tensor memory).
+//
+// The reference feeds a prompt one token at a time through its decode step (crates/slai-chat/src/chat_llama2.rs:109-115
+// loops forward_logits over the prompt; the operator sequence is Llama2::launch, crates/slai/src/models/llama2/
+// transformer.rs:316-381).  For a prompt of T tokens that streams every weight T times.  Here the T activation rows go
+// through each matrix together: Y[T x M] = X[T x K] W^T, the only place on this path where the work is a GEMM.
+//
+// Numerics.  Parity with the sequential path is the contract (logits and KV cache within 1e-3 relative L2, same greedy
+// continuation), and a single fp16 rounding of both operands per product (4e-4 per GEMM, compounding over 4 GEMMs x
+// layers) would spend that budget.  Both operands are therefore carried as fp16 pairs, v = hi + lo with
+// hi = fp16(v), lo = fp16(v - hi) (22 significant bits), and every 16-deep product is issued three times
+// (hi*hi, hi*lo, lo*hi) into the same f32 accumulator: about 2^-21 per product, the rest of the error is the f32
+// accumulation order.  The tensor cores have the headroom: the kernel is bound by dequantisation, not by MMA issue.
+//
+// One CTA computes a 128 (weight rows) x NT (tokens, <= 256) tile of Y^T over the whole K:
+//   * warps 2-5 (128 threads, one weight row each): read the row's packed quants of the next 64-element K slice from
+//     the tile-major matrix (the decode layout, layout.cuh), dequantise with the reference's rounding sequence, split
+//     into hi / lo and store them into the A operand tiles in the canonical K-major 128-byte-swizzled layout;
+//   * warp 0, one lane: TMA (cp.async.bulk.tensor.2d, no multicast: the tile is this CTA's own) brings the matching
+//     64-element slice of the activations' hi and lo planes [T_pad x K] into the B operand tiles, same swizzle;
+//   * warp 1, one lane: issues tcgen05.mma (kind::f16, M = 128, N = NT, K = 16) four slices x three products per stage
+//     and commits the stage's completion to an mbarrier, which frees the stage for the producers;
+//   * epilogue (warps 2-5 again): tcgen05.ld brings each thread one accumulator row (32 TMEM lanes per warp, the
+//     quadrant given by warp index mod 4), adds bias / residual and stores Y[t][row] with coalesced 128-byte rows.
+// Two stages of A and B (192 KB of shared memory at NT = 256), 1 CTA per SM, TMEM columns = NT rounded to a power of two.
+// Every mbarrier wait is bounded: on expiry the error flag is raised and the role leaves its loop; all roles then meet
+// at the final barrier and the tensor memory is released.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "dequant.cuh"
+
+namespace {
+
+constexpr int PF_THREADS = 192;
+constexpr int PF_BM = 128;          // weight rows per CTA
+constexpr int PF_BK = 64;           // K elements per stage (one 128-byte swizzle row of fp16)
+constexpr int PF_STAGES = 2;
+constexpr int PF_A_BYTES = PF_BM * PF_BK * 2;  // one A plane of a stage
+
+struct PrefillGemmParams {
+    const uint8_t* w;        // tile-major quantised matrix
+    long long tile_bytes;    // bytes of one 16-row tile (all K steps)
+    int fmt, M, K;           // matrix rows and columns
+    int T, NT;               // valid tokens, tokens per CTA tile (multiple of 16, <= 256)
+    float* out;              // [T][ldo]; row m goes to out[t * ldo + out_off + m]
+    int ldo, out_off;
+    const float* resid;      // optional [T][ldr]: out = resid + y (may alias out)
+    int ldr;
+    const float* bias;       // optional [M]
+    unsigned int* err_flag;
+    unsigned int wait_limit;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t a, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(a), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t a) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(a) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t a, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(a), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t a, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok)
+                 : "r"(a), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
+// Bounded wait: false (and the error flag raised) if the phase does not complete.
+__device__ __forceinline__ bool mbar_wait(uint32_t a, uint32_t parity, const PrefillGemmParams& P) {
+    for (unsigned int i = 0; i < P.wait_limit; i++) {
+        if (mbar_try(a, parity)) return true;
+        if (i > 64) __nanosleep(40);
+    }
+    atomicExch(P.err_flag, 5u);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t mbar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+                 "l"(map), "r"(mbar), "r"(x), "r"(y)
+                 : "memory");
+}
+// Shared-memory matrix descriptor of a K-major, 128-byte-swizzled operand tile (rows of 64 fp16 = 128 bytes, 8-row
+// groups 1024 bytes apart): start address / 16 in bits 0-13, leading offset (unused with this swizzle) 1 in bits 16-29,
+// stride between 8-row groups / 16 in bits 32-45, descriptor version 1 in bits 46-47, swizzle mode 2 (128 B) in bits 61-63.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor, kind::f16: f32 accumulator (bits 4-5 = 1), A and B fp16 (0), both K-major (bits 15, 16 = 0),
+// N / 8 in bits 17-22, M / 16 in bits 24-28.
+__device__ __forceinline__ uint32_t umma_idesc(int n) { return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(PF_BM >> 4) << 24); }
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t mbar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+// 64 dequantised values of one row into its 128-byte rows of the hi and lo A planes.  Chunk c (8 values, 16 bytes) of
+// row r lives at chunk position c ^ (r & 7) of the row (the 128-byte swizzle the tensor core expects).
+__device__ __forceinline__ void store_split8(unsigned char* a_hi, unsigned char* a_lo, int r, int c, const float (&v)[8]) {
+    __half2 h[4], l[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const __half h0 = __float2half_rn(v[2 * i]), h1 = __float2half_rn(v[2 * i + 1]);
+        h[i] = __halves2half2(h0, h1);
+        l[i] = __halves2half2(__float2half_rn(v[2 * i] - __half2float(h0)), __float2half_rn(v[2 * i + 1] - __half2float(h1)));
+    }
+    const int off = r * 128 + ((c ^ (r & 7)) << 4);
+    *reinterpret_cast<uint4*>(a_hi + off) = *reinterpret_cast<const uint4*>(h);
+    *reinterpret_cast<uint4*>(a_lo + off) = *reinterpret_cast<const uint4*>(l);
+}
+
+// Row `row` of the matrix, elements [k0, k0 + 64): dequantised, split and stored.  Q4_K / Q5_K read the two 16-byte
+// chunks of packed nibbles and the row's 20-byte header directly (a 64-element slice is one pair of sub-blocks);
+// the other formats go element by element.
+__device__ __forceinline__ void dequant_slice(const PrefillGemmParams& P, long long row, int r, int k0, unsigned char* a_hi,
+                                              unsigned char* a_lo) {
+    if (row >= P.M) {  // rows beyond the matrix: zeros (their outputs are never stored)
+        const float z[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < 8; c++) store_split8(a_hi, a_lo, r, c, z);
+        return;
+    }
+    if (P.fmt == SLAI_FMT_Q4_K || P.fmt == SLAI_FMT_Q5_K) {
+        const bool five = P.fmt == SLAI_FMT_Q5_K;
+        const int r16 = (int)(row & 15), G = (k0 >> 6) & 3;
+        const uint8_t* b = P.w + (row >> 4) * P.tile_bytes + (long long)(k0 >> 8) * layout::step_bytes(P.fmt);
+        const uint8_t* h = b + layout::K45_HDR_ROW * r16;
+        const uint32_t dd = *reinterpret_cast<const uint32_t*>(h);
+        const float d = dev_h2f(dd & 0xFFFFu), mn = dev_h2f(dd >> 16);
+        const int q0 = five ? layout::K45_HDR + 512 : layout::K45_HDR;
+        uint4 qw[2];
+        qw[0] = __ldg(reinterpret_cast<const uint4*>(b + layout::qbyte_off(q0, r16, 32 * G)));
+        qw[1] = __ldg(reinterpret_cast<const uint4*>(b + layout::qbyte_off(q0, r16, 32 * G + 16)));
+        uint4 hq[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
+        if (five) {
+            hq[0] = __ldg(reinterpret_cast<const uint4*>(b + layout::K45_HDR + 32 * r16));
+            hq[1] = __ldg(reinterpret_cast<const uint4*>(b + layout::K45_HDR + 32 * r16 + 16));
+        }
+        const unsigned char* qb = reinterpret_cast<const unsigned char*>(qw);
+        const unsigned char* hb = reinterpret_cast<const unsigned char*>(hq);
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            const int j = 2 * G + half;
+            const float d1 = __fmul_rn(d, (float)h[layout::k45_sc_off(j)]), m1 = __fmul_rn(mn, (float)h[12 + j]);
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int l = 8 * c + i;
+                    int q = half ? (qb[l] >> 4) : (qb[l] & 0xF);
+                    if (five) q += ((hb[l] >> (2 * G + half)) & 1) ? 16 : 0;
+                    v[i] = __fsub_rn(__fmul_rn(d1, (float)q), m1);
+                }
+                store_split8(a_hi, a_lo, r, 4 * half + c, v);
+            }
+        }
+        return;
+    }
+#pragma unroll 1
+    for (int c = 0; c < 8; c++) {
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = dequant_elem(P.fmt, P.w, P.K, row, k0 + 8 * c + i);
+        store_split8(a_hi, a_lo, r, c, v);
+    }
+}
+
+__global__ void __launch_bounds__(PF_THREADS, 1)
+prefill_gemm_kernel(const __grid_constant__ PrefillGemmParams P, const __grid_constant__ CUtensorMap map_hi,
+                    const __grid_constant__ CUtensorMap map_lo) {
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+    const int NT = P.NT;
+    const int b_bytes = NT * PF_BK * 2;  // one B plane of a stage
+    unsigned char* a_hi = smem;                              // [stage][128 x 128 B]
+    unsigned char* a_lo = a_hi + PF_STAGES * PF_A_BYTES;
+    unsigned char* b_hi = a_lo + PF_STAGES * PF_A_BYTES;     // [stage][NT x 128 B]
+    unsigned char* b_lo = b_hi + PF_STAGES * b_bytes;
+    __shared__ __align__(8) unsigned long long bars[3 * PF_STAGES + 1];
+    __shared__ uint32_t tmem_slot;
+    const uint32_t full_a = smem_u32(&bars[0]), full_b = smem_u32(&bars[PF_STAGES]), empty = smem_u32(&bars[2 * PF_STAGES]),
+                   accum = smem_u32(&bars[3 * PF_STAGES]);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int m0 = blockIdx.x * PF_BM, n0 = blockIdx.y * NT;
+    const int nk = P.K / PF_BK;
+    int ncols = 32;
+    while (ncols < NT) ncols <<= 1;
+
+    if (tid == 0) {
+        for (int s = 0; s < PF_STAGES; s++) {
+            mbar_init(full_a + 8 * s, 128);
+            mbar_init(full_b + 8 * s, 1);
+            mbar_init(empty + 8 * s, 1);
+        }
+        mbar_init(accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {  // the MMA warp owns the tensor-memory allocation
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(ncols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = tmem_slot;
+
+    if (warp == 0) {
+        // ---- activations: one lane drives the TMA ----
+        if (lane == 0) {
+            for (int s = 0; s < nk; s++) {
+                const int st = s % PF_STAGES;
+                if (s >= PF_STAGES && !mbar_wait(empty + 8 * st, ((s / PF_STAGES) - 1) & 1, P)) break;
+                mbar_expect_tx(full_b + 8 * st, 2 * b_bytes);
+                tma_load_2d(smem_u32(b_hi + st * b_bytes), &map_hi, s * PF_BK, n0, full_b + 8 * st);
+                tma_load_2d(smem_u32(b_lo + st * b_bytes), &map_lo, s * PF_BK, n0, full_b + 8 * st);
+            }
+        }
+    } else if (warp == 1) {
+        // ---- tensor cores: one lane issues, the stage is handed back when its products have been read ----
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(NT);
+            bool ok = true;
+            for (int s = 0; s < nk && ok; s++) {
+                const int st = s % PF_STAGES;
+                const uint32_t par = (s / PF_STAGES) & 1;
+                ok = mbar_wait(full_a + 8 * st, par, P) && mbar_wait(full_b + 8 * st, par, P);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t ah = smem_u32(a_hi + st * PF_A_BYTES), al = smem_u32(a_lo + st * PF_A_BYTES);
+                const uint32_t bh = smem_u32(b_hi + st * b_bytes), bl = smem_u32(b_lo + st * b_bytes);
+#pragma unroll
+                for (int kk = 0; kk < PF_BK / 16; kk++) {  // 16 elements = 32 bytes further along the swizzled row
+                    const uint64_t dah = umma_desc(ah + 32 * kk), dal = umma_desc(al + 32 * kk);
+                    const uint64_t dbh = umma_desc(bh + 32 * kk), dbl = umma_desc(bl + 32 * kk);
+                    umma_f16(tmem_d, dah, dbh, idesc, (s > 0 || kk > 0) ? 1u : 0u);
+                    umma_f16(tmem_d, dah, dbl, idesc, 1u);
+                    umma_f16(tmem_d, dal, dbh, idesc, 1u);
+                }
+                umma_commit(empty + 8 * st);
+            }
+            umma_commit(accum);  // arrives when everything issued above has completed (also after a bail-out)
+        }
+    } else {
+        // ---- weights: one row per thread, dequantised into the A planes ----
+        const int r = tid - 64;
+        const long long row = (long long)m0 + r;
+        bool ok = true;
+        for (int s = 0; s < nk && ok; s++) {
+            const int st = s % PF_STAGES;
+            if (s >= PF_STAGES) ok = mbar_wait(empty + 8 * st, ((s / PF_STAGES) - 1) & 1, P);
+            if (!ok) break;
+            dequant_slice(P, row, r, s * PF_BK, a_hi + st * PF_A_BYTES, a_lo + st * PF_A_BYTES);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core's reads
+            mbar_arrive(full_a + 8 * st);
+        }
+        // ---- epilogue: this thread's accumulator row, 16 tokens at a time ----
+        if (mbar_wait(accum, 0, P)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int quad = warp & 3;              // a warp reads the 32 TMEM lanes of its quadrant
+            const int orow = m0 + 32 * quad + lane;
+            const float bias = (P.bias && orow < P.M) ? P.bias[orow] : 0.f;
+            for (int c0 = 0; c0 < NT; c0 += 16) {
+                uint32_t v[16];
+                tmem_ld16(tmem_d + ((uint32_t)(32 * quad) << 16) + (uint32_t)c0, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (orow < P.M) {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        const int t = n0 + c0 + j;
+                        if (t < P.T) {
+                            float y = __uint_as_float(v[j]) + bias;
+                            if (P.resid) y = P.resid[(size_t)t * P.ldr + orow] + y;
+                            P.out[(size_t)t * P.ldo + P.out_off + orow] = y;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(ncols) : "memory");
+}
+
+// ---- small kernels around the GEMMs ---------------------------------------------------------------------------------
+__device__ __forceinline__ float block_sum256(float x, float* sh) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = x;
+    __syncthreads();
+    float t = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); w++) t += sh[w];
+    return t;
+}
+__device__ __forceinline__ void store_hi_lo(__half* hi, __half* lo, size_t i, float y) {
+    const __half h = __float2half_rn(y);
+    hi[i] = h;
+    lo[i] = __float2half_rn(y - __half2float(h));
+}
+
+// Row t of X (optionally RmsNorm'd: ops/rms_norm.rs:68-77) as fp16 hi / lo planes [T_pad][K].
+__global__ void prefill_split_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ norm_w, float eps, int K,
+                                     __half* __restrict__ hi, __half* __restrict__ lo) {
+    __shared__ float sh[32];
+    const int t = blockIdx.x;
+    const float* xr = x + (size_t)t * ldx;
+    float mul = 1.f;
+    if (norm_w) {
+        float s = 0.f;
+        for (int i = threadIdx.x; i < K; i += blockDim.x) s += xr[i] * xr[i];
+        s = block_sum256(s, sh);
+        mul = 1.0f / sqrtf(s / (float)K + eps);
+    }
+    for (int i = threadIdx.x; i < K; i += blockDim.x) {
+        const float y = norm_w ? __fmul_rn(__fmul_rn(xr[i], mul), norm_w[i]) : xr[i];
+        store_hi_lo(hi, lo, (size_t)t * K + i, y);
+    }
+}
+
+// hb = up * gate / (1 + exp(-gate)) (ops/silu.rs:50-58) straight into the hi / lo planes of the down projection's input.
+__global__ void prefill_silu_split_kernel(const float* __restrict__ gate, const float* __restrict__ up, int H, __half* __restrict__ hi,
+                                          __half* __restrict__ lo) {
+    const int t = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= H) return;
+    const float g = gate[(size_t)t * H + i], u = up[(size_t)t * H + i];
+    store_hi_lo(hi, lo, (size_t)t * H + i, u * (g / (1.0f + expf(-g))));
+}
+
+// x[t] = row token[t] of the embedding table (f32 table or quantised matrix).
+__global__ void prefill_embed_kernel(float* __restrict__ x, int dim, const int* __restrict__ tokens, const float* __restrict__ table,
+                                     int fmt, const uint8_t* __restrict__ qdata) {
+    const int t = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= dim) return;
+    const long long row = tokens[t];
+    x[(size_t)t * dim + i] = table ? table[row * dim + i] : dequant_elem(fmt, qdata, dim, row, i);
+}
+
+// RoPE (ops/rope.rs:88-125; both variants) on q and k of token t at position pos0 + t, q to its own buffer, k and v into
+// the cache ([kv_head][position][head_size], f16 or f32): the q/k/v epilogue of the decode step, for T tokens at once.
+__global__ void prefill_rope_kv_kernel(const float* __restrict__ qkv, int ld, int q_dim, int kv_dim, int head_size, int pos0,
+                                       const float* __restrict__ theta, int neox, float* __restrict__ q_out, void* kcache, void* vcache,
+                                       int kv_f16, long long kv_head_stride) {
+    const int t = blockIdx.y;
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;  // pair index over q then k; then plain copies of v
+    const int pos = pos0 + t;
+    const float* row = qkv + (size_t)t * ld;
+    const int nq = q_dim / 2, nk = kv_dim / 2;
+    if (p < nq + nk) {
+        const bool is_k = p >= nq;
+        const int i = is_k ? p - nq : p;
+        const float* src = row + (is_k ? q_dim : 0);
+        const int head = (2 * i) / head_size, j = (2 * i) % head_size;  // j: even offset inside the head
+        int a, b, fi;
+        if (neox) {
+            fi = j >> 1;
+            a = head * head_size + fi;
+            b = a + head_size / 2;
+        } else {
+            fi = j >> 1;
+            a = 2 * i;
+            b = a + 1;
+        }
+        float sn, cs;
+        sincosf((float)pos * theta[fi], &sn, &cs);
+        const float xa = src[a], xb = src[b];
+        const float ya = cs * xa - sn * xb, yb = sn * xa + cs * xb;
+        if (!is_k) {
+            q_out[(size_t)t * q_dim + a] = ya;
+            q_out[(size_t)t * q_dim + b] = yb;
+        } else {
+            const int ha = a / head_size, da = a % head_size, hb = b / head_size, db = b % head_size;
+            const long long oa = (long long)pos * head_size + ha * kv_head_stride + da, ob = (long long)pos * head_size + hb * kv_head_stride + db;
+            if (kv_f16) {
+                reinterpret_cast<__half*>(kcache)[oa] = __float2half_rn(ya);
+                reinterpret_cast<__half*>(kcache)[ob] = __float2half_rn(yb);
+            } else {
+                reinterpret_cast<float*>(kcache)[oa] = ya;
+                reinterpret_cast<float*>(kcache)[ob] = yb;
+            }
+        }
+    } else if (p < nq + nk + kv_dim) {
+        const int e = p - nq - nk;
+        const float y = row[q_dim + kv_dim + e];
+        const long long o = (long long)pos * head_size + (e / head_size) * kv_head_stride + e % head_size;
+        if (kv_f16) reinterpret_cast<__half*>(vcache)[o] = __float2half_rn(y);
+        else reinterpret_cast<float*>(vcache)[o] = y;
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// fp16 plane [rows][K] row-major -> boxes of 64 columns x `box_rows` rows, 128-byte swizzle (what umma_desc describes).
+int make_plane_map(slai_ctx* ctx, CUtensorMap* map, const __half* base, int rows, int K, int box_rows) {
+    EncodeTiledFn enc = encode_tiled();
+    SLAI_REQUIRE(ctx, enc, SLAI_ERR_CUDA, "prefill: the driver does not provide cuTensorMapEncodeTiled");
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)PF_BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(base), dims, strides, box, elem,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    SLAI_REQUIRE(ctx, r == CUDA_SUCCESS, SLAI_ERR_CUDA, "prefill: cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return SLAI_OK;
+}
+
+}  // namespace
+
+size_t prefill_gemm_smem(int NT) { return (size_t)PF_STAGES * (2 * PF_A_BYTES + 2 * (size_t)NT * PF_BK * 2) + 1024; }
+
+// Y[t][out_off + m] = (resid[t][m] +) sum_k W[m][k] X[t][k] (+ bias[m]) for t < T, with X given as hi / lo planes of
+// `t_pad` rows (a multiple of NT; rows >= T are zero).
+int prefill_gemm_launch(slai_ctx* ctx, const PrefillGemm& G) {
+    const slai_qmatrix* w = G.w;
+    SLAI_REQUIRE(ctx, w->fmt == SLAI_FMT_Q4_K || w->fmt == SLAI_FMT_Q5_K || w->fmt == SLAI_FMT_Q6_K || w->fmt == SLAI_FMT_Q8_0,
+                 SLAI_ERR_UNSUPPORTED_FORMAT, "prefill: format %d has no GEMM path", w->fmt);
+    SLAI_REQUIRE(ctx, w->ncols % PF_BK == 0 && G.NT % 16 == 0 && G.NT >= 16 && G.NT <= 256 && G.t_pad % G.NT == 0 && G.T <= G.t_pad,
+                 SLAI_ERR_SHAPE, "prefill: K=%lld / tile of %d tokens not supported", (long long)w->ncols, G.NT);
+    CUtensorMap map_hi, map_lo;
+    int rc = make_plane_map(ctx, &map_hi, G.x_hi, G.t_pad, (int)w->ncols, G.NT);
+    if (rc) return rc;
+    if ((rc = make_plane_map(ctx, &map_lo, G.x_lo, G.t_pad, (int)w->ncols, G.NT))) return rc;
+    PrefillGemmParams P;
+    P.w = w->data; P.tile_bytes = w->tile_bytes; P.fmt = w->fmt; P.M = G.rows; P.K = (int)w->ncols;
+    P.T = G.T; P.NT = G.NT; P.out = G.out; P.ldo = G.ldo; P.out_off = G.out_off; P.resid = G.resid; P.ldr = G.ldr; P.bias = G.bias;
+    P.err_flag = ctx->d_counters + CNT_ERR_FLAG;
+    P.wait_limit = ctx->wait_limit;
+    const size_t smem = prefill_gemm_smem(G.NT);
+    static PerDeviceOnce attr;
+    if (attr.need(ctx->device)) {
+        SLAI_CHECK_CUDA(ctx, cudaFuncSetAttribute(prefill_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_gemm_smem(256)));
+        attr.set(ctx->device);
+    }
+    const dim3 grid((unsigned)((G.rows + PF_BM - 1) / PF_BM), (unsigned)(G.t_pad / G.NT));
+    prefill_gemm_kernel<<<grid, PF_THREADS, smem, ctx->stream>>>(P, map_hi, map_lo);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    return SLAI_OK;
+}
+
+int prefill_split_launch(slai_ctx* ctx, const float* x, int ldx, const float* norm_w, float eps, int T, int K, __half* hi, __half* lo) {
+    prefill_split_kernel<<<T, 256, 0, ctx->stream>>>(x, ldx, norm_w, eps, K, hi, lo);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    return SLAI_OK;
+}
+int prefill_silu_split_launch(slai_ctx* ctx, const float* gate, const float* up, int T, int H, __half* hi, __half* lo) {
+    prefill_silu_split_kernel<<<dim3((H + 255) / 256, T), 256, 0, ctx->stream>>>(gate, up, H, hi, lo);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    return SLAI_OK;
+}
+int prefill_embed_launch(slai_ctx* ctx, float* x, int dim, const int* d_tokens, int T, const float* table, const slai_qmatrix* qtable) {
+    prefill_embed_kernel<<<dim3((dim + 255) / 256, T), 256, 0, ctx->stream>>>(x, dim, d_tokens, table, qtable ? qtable->fmt : 0,
+                                                                             qtable ? qtable->data : nullptr);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    return SLAI_OK;
+}
+int prefill_rope_kv_launch(slai_ctx* ctx, const float* qkv, int ld, int q_dim, int kv_dim, int head_size, int pos0, int T,
+                           const float* theta, int neox, float* q_out, void* kcache, void* vcache, int kv_f16, long long kv_head_stride) {
+    const int work = q_dim / 2 + kv_dim / 2 + kv_dim;
+    prefill_rope_kv_kernel<<<dim3((work + 255) / 256, T), 256, 0, ctx->stream>>>(qkv, ld, q_dim, kv_dim, head_size, pos0, theta, neox, q_out,
+                                                                                kcache, vcache, kv_f16, kv_head_stride);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    return SLAI_OK;
+}

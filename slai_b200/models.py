@@ -130,6 +130,14 @@ class Llama2:
                                                                logits.ctypes.data_as(C.c_void_p) if want_logits else None))
         return logits
 
+    def read_kv(self, layer: int, n_pos: int):
+        """Keys and values of one layer for positions 0..n_pos, each [n_pos, kv_dim] f32 (test access)."""
+        kvd = self.config.kv_dim // max(self.tp_size, 1) if hasattr(self, "tp_size") else self.config.kv_dim
+        k = np.empty((n_pos, kvd), dtype=np.float32)
+        v = np.empty((n_pos, kvd), dtype=np.float32)
+        self.backend.check(self.backend.lib.slai_llama_read_kv(self.h, layer, n_pos, k.ctypes.data_as(C.c_void_p), v.ctypes.data_as(C.c_void_p)))
+        return k, v
+
     def read_state(self, which: str) -> np.ndarray:
         idx = dict(x=0, xb=1, q=2, hb=3, logits=4)[which]
         n = dict(x=self.config.dim, xb=self.config.dim, q=self.config.dim, hb=self.config.hidden_dim, logits=self.config.vocab_size)[which]
