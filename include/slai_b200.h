@@ -44,8 +44,11 @@ enum slai_status {
     SLAI_ERR_OOM = 7
 };
 
-/* GGML tensor type ids as stored in GGUF files (gguf.rs:20-60).  Only F32, Q8_0, Q4_K, Q5_K and Q6_K
- * have kernels; the legacy formats are listed so callers get SLAI_ERR_UNSUPPORTED_FORMAT, not garbage. */
+/* GGML tensor type ids as stored in GGUF files (gguf.rs:20-60).  F32, Q8_0, Q4_K, Q5_K and Q6_K have kernels of
+ * their own.  The legacy formats (quantization.rs:47-199) are accepted at upload: Q4_0 and Q5_0 are re-expressed
+ * exactly as Q8_0 blocks (same f16 scale, quant - 8 / - 16 as int8), Q4_1, Q5_1 and Q8_K are dequantised to dense f32
+ * with the reference's rounding (what the reference does with tensors its quantised kernels do not take,
+ * gguf.rs:148-162).  F16 has no path: SLAI_ERR_UNSUPPORTED_FORMAT. */
 enum slai_format {
     SLAI_FMT_F32 = 0,
     SLAI_FMT_F16 = 1,

@@ -87,8 +87,8 @@ def _f32(a) -> np.ndarray:
     return np.ascontiguousarray(a, dtype=np.float32)
 
 
-BLOCK_BYTES = {FMT_F32: 4, FMT_Q8_0: 34, FMT_Q4_K: 144, FMT_Q5_K: 176, FMT_Q6_K: 210}
-BLOCK_ELEMS = {FMT_F32: 1, FMT_Q8_0: 32, FMT_Q4_K: 256, FMT_Q5_K: 256, FMT_Q6_K: 256}
+BLOCK_BYTES = {FMT_F32: 4, FMT_Q8_0: 34, FMT_Q4_K: 144, FMT_Q5_K: 176, FMT_Q6_K: 210, 2: 18, 3: 20, 6: 22, 7: 24, 15: 292}
+BLOCK_ELEMS = {FMT_F32: 1, FMT_Q8_0: 32, FMT_Q4_K: 256, FMT_Q5_K: 256, FMT_Q6_K: 256, 2: 32, 3: 32, 6: 32, 7: 32, 15: 256}
 
 
 def decode_f16(h: int) -> float:

@@ -225,6 +225,52 @@ ORA_API int ora_block_elems(int fmt) {
     return -1;
 }
 
+// ---- legacy 32-element formats and Q8_K (crates/slai/src/quantization.rs:47-199) -------------------------------
+// Q4_0 (:47-70): f16 d, 16 bytes; element j = low nibble of qs[j] - 8, element j + 16 = high nibble - 8; times d.
+static void dequant_q4_0(const uint8_t* b, float* out) {
+    const float d = ora_decode_f16((uint16_t)(b[0] | (b[1] << 8)));
+    for (int j = 0; j < 16; j++) {
+        const int x0 = (int)(b[2 + j] & 0x0F) - 8, x1 = (int)(b[2 + j] >> 4) - 8;
+        out[j] = (float)x0 * d;
+        out[j + 16] = (float)x1 * d;
+    }
+}
+// Q4_1 (:72-98): f16 d, f16 m, 16 bytes; nibble * d + m.
+static void dequant_q4_1(const uint8_t* b, float* out) {
+    const float d = ora_decode_f16((uint16_t)(b[0] | (b[1] << 8))), m = ora_decode_f16((uint16_t)(b[2] | (b[3] << 8)));
+    for (int j = 0; j < 16; j++) {
+        out[j] = (float)(b[4 + j] & 0x0F) * d + m;
+        out[j + 16] = (float)(b[4 + j] >> 4) * d + m;
+    }
+}
+// Q5_0 (:100-129): f16 d, 4 bytes of fifth bits (bit j for element j, bit j + 16 for element j + 16), 16 bytes; (q - 16) * d.
+static void dequant_q5_0(const uint8_t* b, float* out) {
+    const float d = ora_decode_f16((uint16_t)(b[0] | (b[1] << 8)));
+    const uint32_t qh = (uint32_t)b[2] | ((uint32_t)b[3] << 8) | ((uint32_t)b[4] << 16) | ((uint32_t)b[5] << 24);
+    for (int j = 0; j < 16; j++) {
+        const uint32_t xh0 = ((qh >> j) << 4) & 0x10, xh1 = (qh >> (j + 12)) & 0x10;
+        const int x0 = (int)(((uint32_t)b[6 + j] & 0x0F) | xh0) - 16, x1 = (int)(((uint32_t)b[6 + j] >> 4) | xh1) - 16;
+        out[j] = (float)x0 * d;
+        out[j + 16] = (float)x1 * d;
+    }
+}
+// Q5_1 (:131-163): f16 d, f16 m, fifth bits, 16 bytes; q * d + m.
+static void dequant_q5_1(const uint8_t* b, float* out) {
+    const float d = ora_decode_f16((uint16_t)(b[0] | (b[1] << 8))), m = ora_decode_f16((uint16_t)(b[2] | (b[3] << 8)));
+    const uint32_t qh = (uint32_t)b[4] | ((uint32_t)b[5] << 8) | ((uint32_t)b[6] << 16) | ((uint32_t)b[7] << 24);
+    for (int j = 0; j < 16; j++) {
+        const uint32_t xh0 = ((qh >> j) << 4) & 0x10, xh1 = (qh >> (j + 12)) & 0x10;
+        out[j] = (float)(((uint32_t)b[8 + j] & 0x0F) | xh0) * d + m;
+        out[j + 16] = (float)(((uint32_t)b[8 + j] >> 4) | xh1) * d + m;
+    }
+}
+// Q8_K (:168-199): f32 d, 256 int8, 16 i16 group sums (unused by the dequantiser); d * q.
+static void dequant_q8_k(const uint8_t* b, float* out) {
+    float d;
+    std::memcpy(&d, b, 4);
+    for (int j = 0; j < 256; j++) out[j] = d * (float)(int8_t)b[4 + j];
+}
+
 // Dequantise `nblocks` consecutive blocks (a GGUF tensor is rows of blocks in row-major order,
 // crates/slai/src/gguf.rs:116-131,596-676).  Returns 0 on success.
 ORA_API int ora_dequantize(int fmt, const void* blocks, int64_t nblocks, float* out) {
@@ -242,6 +288,21 @@ ORA_API int ora_dequantize(int fmt, const void* blocks, int64_t nblocks, float* 
             return 0;
         case ORA_FMT_Q6_K:
             for (int64_t i = 0; i < nblocks; i++) dequant_q6k((const BlockQ6K*)(p + i * 210), out + i * 256);
+            return 0;
+        case 2:
+            for (int64_t i = 0; i < nblocks; i++) dequant_q4_0(p + i * 18, out + i * 32);
+            return 0;
+        case 3:
+            for (int64_t i = 0; i < nblocks; i++) dequant_q4_1(p + i * 20, out + i * 32);
+            return 0;
+        case 6:
+            for (int64_t i = 0; i < nblocks; i++) dequant_q5_0(p + i * 22, out + i * 32);
+            return 0;
+        case 7:
+            for (int64_t i = 0; i < nblocks; i++) dequant_q5_1(p + i * 24, out + i * 32);
+            return 0;
+        case 15:
+            for (int64_t i = 0; i < nblocks; i++) dequant_q8_k(p + i * 292, out + i * 256);
             return 0;
     }
     return -1;

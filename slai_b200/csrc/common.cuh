@@ -149,7 +149,8 @@ __device__ __forceinline__ void prefetch_plan_issue(const PrefetchPlan& pf, int 
 // ------------------------------------------------------------------------------------------------
 struct slai_qmatrix {
     slai_ctx* ctx = nullptr;
-    int fmt = 0;
+    int fmt = 0;      // format of the device data (what the kernels see)
+    int src_fmt = 0;  // format of the blocks the caller uploaded (differs for the legacy formats, see legacy_device_format)
     int64_t nrows = 0, ncols = 0;
     int64_t tile_bytes = 0;  // bytes of one 16-row tile (F32: bytes of one row)
     uint8_t* data = nullptr;
@@ -157,10 +158,29 @@ struct slai_qmatrix {
     bool owns = true;
 };
 
+// The legacy 32-element formats and Q8_K have no kernels of their own.  Q4_0 and Q5_0 are re-expressed exactly as
+// Q8_0 at upload (same f16 scale, quant - 8 / - 16 as int8: (q - 8) * d is the very product Q8_0 evaluates); Q4_1,
+// Q5_1 (scale and offset) and Q8_K (f32 scale) are dequantised to dense f32 with the reference's rounding, which is
+// what the reference itself does with tensors its quantised kernels do not take (gguf.rs:148-162).
+static inline int legacy_device_format(int fmt) {
+    switch (fmt) {
+        case SLAI_FMT_Q4_0:
+        case SLAI_FMT_Q5_0: return SLAI_FMT_Q8_0;
+        case SLAI_FMT_Q4_1:
+        case SLAI_FMT_Q5_1:
+        case SLAI_FMT_Q8_K: return SLAI_FMT_F32;
+    }
+    return fmt;
+}
 static inline int fmt_block_elems(int fmt) {
     switch (fmt) {
         case SLAI_FMT_F32: return 1;
+        case SLAI_FMT_Q4_0:
+        case SLAI_FMT_Q4_1:
+        case SLAI_FMT_Q5_0:
+        case SLAI_FMT_Q5_1:
         case SLAI_FMT_Q8_0: return 32;
+        case SLAI_FMT_Q8_K:
         case SLAI_FMT_Q4_K:
         case SLAI_FMT_Q5_K:
         case SLAI_FMT_Q6_K: return 256;
@@ -170,6 +190,11 @@ static inline int fmt_block_elems(int fmt) {
 static inline int fmt_block_bytes(int fmt) {
     switch (fmt) {
         case SLAI_FMT_F32: return 4;
+        case SLAI_FMT_Q4_0: return 18;
+        case SLAI_FMT_Q4_1: return 20;
+        case SLAI_FMT_Q5_0: return 22;
+        case SLAI_FMT_Q5_1: return 24;
+        case SLAI_FMT_Q8_K: return 292;
         case SLAI_FMT_Q8_0: return 34;
         case SLAI_FMT_Q4_K: return 144;
         case SLAI_FMT_Q5_K: return 176;
@@ -226,6 +251,8 @@ struct GemvLaunch {
     const int* d_pos = nullptr;    // device scalar: position (RoPE angle and KV slot)
     void* kcache = nullptr;        // layer base of the K cache
     void* vcache = nullptr;
+    float* k_out = nullptr;        // EPI_QKV: the k rows go here as f32 (kv_dim floats) instead of the cache (a rotation that
+                                   // pairs rows half a head apart is applied afterwards, by rope_kv_store_launch)
     int kv_dtype = SLAI_KV_F16;
     int64_t kv_pos_stride = 0;     // elements between positions
     int64_t kv_head_stride = 0;    // elements between heads
@@ -330,6 +357,8 @@ int prefill_gemm_launch(slai_ctx* ctx, const PrefillGemm& G);
 int prefill_split_launch(slai_ctx* ctx, const float* x, int ldx, const float* norm_w, float eps, int T, int K, __half* hi, __half* lo);
 int prefill_silu_split_launch(slai_ctx* ctx, const float* gate, const float* up, int T, int H, __half* hi, __half* lo);
 int prefill_embed_launch(slai_ctx* ctx, float* x, int dim, const int* d_tokens, int T, const float* table, const slai_qmatrix* qtable);
+int rope_kv_store_launch(slai_ctx* ctx, float* q, const float* k, const float* v, int q_dim, int kv_dim, int head_size, const int* d_pos,
+                         const float* theta, int neox, void* kcache, void* vcache, int kv_f16, long long kv_head_stride, bool pdl);
 int prefill_rope_kv_launch(slai_ctx* ctx, const float* qkv, int ld, int q_dim, int kv_dim, int head_size, int pos0, int T,
                            const float* theta, int neox, float* q_out, void* kcache, void* vcache, int kv_f16, long long kv_head_stride);
 

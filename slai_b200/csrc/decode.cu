@@ -91,7 +91,7 @@ __device__ __forceinline__ GemvParams phase_params(const DecodeParams& D, int l,
     P.resid = D.x;
     P.norm_w = qkv ? W.attn_norm : W.ffn_norm;
     P.rope = 1; P.rope_theta = D.rope_theta; P.rope_cs = nullptr; P.head_size = D.head_size; P.d_pos = D.d_pos;
-    P.kcache = W.kcache; P.vcache = W.vcache; P.kv_f16 = D.kv_f16;
+    P.kcache = W.kcache; P.vcache = W.vcache; P.k_out = nullptr; P.kv_f16 = D.kv_f16;
     P.kv_pos_stride = D.head_size; P.kv_head_stride = (long long)D.seq_len * D.head_size;
 #ifdef SLAI_TRACE
     P.trace = nullptr;

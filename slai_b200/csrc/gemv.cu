@@ -168,7 +168,7 @@ int gemv_fill_params(slai_ctx* ctx, const GemvLaunch& L, size_t dig_region, int 
     P.stage_stride = (P.step_bytes + 127) & ~127;
     P.v = L.v; P.out = L.out; P.norm_w = L.norm_w; P.norm_b = L.norm_b; P.eps = L.eps;
     P.resid = L.resid; P.rope = L.rope; P.rope_theta = L.rope_theta; P.rope_cs = L.rope_cs; P.head_size = L.head_size;
-    P.d_pos = L.d_pos; P.pos1 = 0; P.kcache = L.kcache; P.vcache = L.vcache; P.kv_f16 = (L.kv_dtype == SLAI_KV_F16);
+    P.d_pos = L.d_pos; P.pos1 = 0; P.kcache = L.kcache; P.vcache = L.vcache; P.k_out = L.k_out; P.kv_f16 = (L.kv_dtype == SLAI_KV_F16);
     P.kv_pos_stride = L.kv_pos_stride; P.kv_head_stride = L.kv_head_stride;
     P.err_flag = ctx->d_counters + CNT_ERR_FLAG;
     P.wait_limit = ctx->wait_limit;

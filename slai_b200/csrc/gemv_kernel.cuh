@@ -68,6 +68,7 @@ struct GemvParams {
     int pos1;        // position + 1 when the caller already knows it (0: read d_pos)
     void* kcache;
     void* vcache;
+    float* k_out;    // EPI_QKV: k rows as f32 instead of the cache (null: cache)
     int kv_f16;
     long long kv_pos_stride, kv_head_stride;
     unsigned int* err_flag;
@@ -736,6 +737,8 @@ __device__ __forceinline__ void gemv_phase(const GemvParams& P, Ring& R, const P
                 if (valid) {
                     if (sg.role == 0) {
                         P.out[orow] = y;
+                    } else if (sg.role == 1 && P.k_out) {
+                        P.k_out[row_in_seg] = y;
                     } else {
                         void* cache = sg.role == 1 ? P.kcache : P.vcache;
                         const int head = row_in_seg / P.head_size, d = row_in_seg % P.head_size;

@@ -115,6 +115,7 @@ struct slai_llama {
     float* token_embd = nullptr;  // [vocab][dim] f32
     float* out_norm = nullptr;
     float *x = nullptr, *xb = nullptr, *q = nullptr, *hb = nullptr, *hb2 = nullptr, *logits = nullptr;
+    float *ktmp = nullptr, *vtmp = nullptr;  // k / v of the current token as f32 where the fused q/k/v epilogue cannot write the cache itself
     float* logits_part = nullptr;  // tensor parallel with a row-sharded output matrix: this rank's vocab / tp logits
     bool out_sharded = false;
     void *kcache = nullptr, *vcache = nullptr;
@@ -316,6 +317,54 @@ static int llama_record(slai_llama* m, int kind) {
         const size_t gu_first = gu_total <= cap ? (size_t)-1 >> 1 : (size_t)((double)(w.wgate ? w.wgate->bytes : 0) * (double)cap / (double)gu_total) & ~(size_t)15;
         // 1. xb = rmsnorm(x); q = Wq xb; k,v -> cache[pos]; RoPE(q,k)          transformer.rs:327-347
         const bool fuse_rope = c.rope_variant == 0;
+        const bool dense = w.wq->fmt == SLAI_FMT_F32 || w.wk->fmt == SLAI_FMT_F32 || w.wv->fmt == SLAI_FMT_F32 || w.wo->fmt == SLAI_FMT_F32 ||
+                           w.wgate->fmt == SLAI_FMT_F32 || w.wup->fmt == SLAI_FMT_F32 || w.wdown->fmt == SLAI_FMT_F32;
+        if (dense) {
+            // Dense f32 matrices (the legacy formats that are dequantised at upload, or f32 tensors of a file) have no fused
+            // prologues / epilogues: the layer is the reference's own operator sequence, one kernel each
+            // (transformer.rs:327-365), on the device-side position.
+            SLAI_REQUIRE(ctx, m->tp == 1, SLAI_ERR_INVALID_ARG, "llama: dense f32 layer matrices are not sharded");
+            auto plain = [&](const slai_qmatrix* wm, int rows, const float* v, float* out, const float* bias) -> int {
+                GemvLaunch L;
+                L.fmt = wm->fmt; L.K = (int)wm->ncols; L.nseg = 1; L.seg[0] = seg_of(wm, 0, rows, wm->fmt == SLAI_FMT_F32 ? nullptr : bias, 0, 0);
+                L.v = v; L.out = out; L.epi = EPI_STORE; L.pdl = false;
+                int r = gemv_launch(ctx, L);
+                n++;
+                if (!r && bias && wm->fmt == SLAI_FMT_F32) {
+                    r = slai_add_assign(ctx, out, bias, rows);
+                    n++;
+                }
+                return r;
+            };
+            if ((rc = slai_rms_norm(ctx, m->xb, m->x, w.attn_norm, c.dim, c.rms_norm_eps))) return rc;
+            if ((rc = plain(w.wq, m->q_dim, m->xb, m->q, w.bq))) return rc;
+            if ((rc = plain(w.wk, m->kv_dim, m->xb, m->ktmp, w.bk))) return rc;
+            if ((rc = plain(w.wv, m->kv_dim, m->xb, m->vtmp, w.bv))) return rc;
+            if ((rc = rope_kv_store_launch(ctx, m->q, m->ktmp, m->vtmp, m->q_dim, m->kv_dim, m->head_size, d_pos, m->rope_theta, c.rope_variant != 0,
+                                           kc, vc, c.kv_dtype == SLAI_KV_F16, (long long)c.seq_len * m->head_size, false)))
+                return rc;
+            n += 2;
+            {
+                AttnLaunch A;
+                A.q = m->q; A.kcache = kc; A.vcache = vc; A.kv_dtype = c.kv_dtype;
+                A.pos_stride = m->head_size; A.head_stride = (int64_t)c.seq_len * m->head_size;
+                A.n_heads = m->n_q_local; A.kv_mul = m->kv_mul; A.head_size = m->head_size;
+                A.d_pos = d_pos; A.max_pos = c.seq_len - 1; A.out = m->xb; A.pdl = false;
+                A.scratch = m->attn_scratch; A.scratch_bytes = m->attn_scratch_bytes;
+                if ((rc = attention_launch(ctx, A))) return rc;
+                n++;
+            }
+            if ((rc = plain(w.wo, c.dim, m->xb, m->xpart, nullptr))) return rc;
+            if ((rc = slai_add_assign(ctx, m->x, m->xpart, c.dim))) return rc;
+            if ((rc = slai_rms_norm(ctx, m->xb, m->x, w.ffn_norm, c.dim, c.rms_norm_eps))) return rc;
+            if ((rc = plain(w.wgate, m->hidden, m->xb, m->hb, nullptr))) return rc;
+            if ((rc = plain(w.wup, m->hidden, m->xb, m->hb2, nullptr))) return rc;
+            if ((rc = slai_silu_gate(ctx, m->hb, m->hb2, m->hidden))) return rc;
+            if ((rc = plain(w.wdown, c.dim, m->hb, m->xpart, nullptr))) return rc;
+            if ((rc = slai_add_assign(ctx, m->x, m->xpart, c.dim))) return rc;
+            n += 4;
+            continue;
+        }
         auto qkv_launch = [&](int nseg, const GemvSeg* segs, int fmt) {
             GemvLaunch L;
             L.fmt = fmt; L.K = c.dim; L.nseg = nseg;
@@ -325,13 +374,13 @@ static int llama_record(slai_llama* m, int kind) {
             L.rope_cs = table ? m->rope_cs : nullptr;
             L.d_pos = d_pos; L.kcache = kc; L.vcache = vc; L.kv_dtype = c.kv_dtype;
             L.kv_pos_stride = m->head_size; L.kv_head_stride = (int64_t)c.seq_len * m->head_size;
+            L.k_out = fuse_rope ? nullptr : m->ktmp;  // NeoX pairs rows half a head apart: rotated by the kernel that follows
             L.pdl = pdl;
             L.ahead = plan_ahead1(w.wo, 0, cap);  // the attention kernel in between streams the KV cache, not weights
             consume_exchange(L);
             n++;
             return gemv_launch(ctx, L);
         };
-        SLAI_REQUIRE(ctx, fuse_rope, SLAI_ERR_INVALID_ARG, "llama: the NeoX RoPE variant is served by slai_rope, not by the fused decode path");
         GemvSeg sq = seg_of(w.wq, 0, m->q_dim, w.bq, 0, 0), sk = seg_of(w.wk, 0, m->kv_dim, w.bk, 0, 1),
                 sv = seg_of(w.wv, 0, m->kv_dim, w.bv, 0, 2);
         if (w.wq->fmt == w.wk->fmt && w.wk->fmt == w.wv->fmt) {
@@ -341,6 +390,12 @@ static int llama_record(slai_llama* m, int kind) {
             if ((rc = qkv_launch(1, &sq, w.wq->fmt))) return rc;
             if ((rc = qkv_launch(1, &sk, w.wk->fmt))) return rc;
             if ((rc = qkv_launch(1, &sv, w.wv->fmt))) return rc;
+        }
+        if (!fuse_rope) {  // NeoX (rope.slang:58-86; variant chosen per model, transformer.rs:346-347): q in place, k into the cache
+            if ((rc = rope_kv_store_launch(ctx, m->q, m->ktmp, nullptr, m->q_dim, m->kv_dim, m->head_size, d_pos, m->rope_theta, 1, kc, vc,
+                                           c.kv_dtype == SLAI_KV_F16, (long long)c.seq_len * m->head_size, pdl)))
+                return rc;
+            n++;
         }
         // 2. xb = attention(q, cache)                                           transformer.rs:350,383-400
         {
@@ -525,6 +580,7 @@ SLAI_API int slai_llama_create(slai_ctx* ctx, const slai_llama_config* cfg, slai
               cudaMalloc(&m->xpart, (size_t)c.dim * 4) == cudaSuccess && cudaMalloc(&m->rope_cs, 2 * 256 * 4) == cudaSuccess &&
               cudaMalloc(&m->q, (size_t)c.dim * 4) == cudaSuccess && cudaMalloc(&m->hb, (size_t)c.hidden_dim * 4) == cudaSuccess &&
               cudaMalloc(&m->hb2, (size_t)c.hidden_dim * 4) == cudaSuccess &&
+              cudaMalloc(&m->ktmp, (size_t)c.dim * 4) == cudaSuccess && cudaMalloc(&m->vtmp, (size_t)c.dim * 4) == cudaSuccess &&
               cudaMalloc(&m->logits, (size_t)c.vocab_size * 4) == cudaSuccess &&
               cudaMalloc(&m->kcache, m->kv_layer_elems * c.n_layers * esz) == cudaSuccess &&
               cudaMalloc(&m->vcache, m->kv_layer_elems * c.n_layers * esz) == cudaSuccess &&
@@ -558,7 +614,7 @@ SLAI_API int slai_llama_destroy(slai_llama* m) {
     }
     cudaFree(m->token_embd); cudaFree(m->out_norm);
     cudaFree(m->x); cudaFree(m->xb); cudaFree(m->xpart); cudaFree(m->q); cudaFree(m->hb); cudaFree(m->hb2); cudaFree(m->logits);
-    cudaFree(m->logits_part);
+    cudaFree(m->logits_part); cudaFree(m->ktmp); cudaFree(m->vtmp);
     cudaFree(m->kcache); cudaFree(m->vcache); cudaFree(m->sc.d); cudaFree(m->d_history); cudaFree(m->attn_scratch);
     cudaFree(m->d_samp); cudaFree(m->d_samp_scratch); cudaFree(m->rope_cs);
     delete m;

@@ -269,6 +269,43 @@ __global__ void dequant_kernel(int fmt, const uint8_t* __restrict__ data, long l
     out[i] = fmt == SLAI_FMT_F32 ? reinterpret_cast<const float*>(data)[r * K + k] : dequant_elem(fmt, data, K, r, k);
 }
 
+// Legacy blocks (quantization.rs:47-199) at upload: Q4_0 / Q5_0 -> the same values as Q8_0 blocks; Q4_1 / Q5_1 / Q8_K -> f32.
+__device__ __forceinline__ int legacy_quant(int fmt, const uint8_t* b, int e) {  // element e (0..31) of a 32-element legacy block
+    const int j = e & 15, hi = e >> 4;
+    const int hdr = fmt == SLAI_FMT_Q4_0 ? 2 : fmt == SLAI_FMT_Q4_1 ? 4 : fmt == SLAI_FMT_Q5_0 ? 6 : 8;
+    int q = hi ? (b[hdr + j] >> 4) : (b[hdr + j] & 0x0F);
+    if (fmt == SLAI_FMT_Q5_0 || fmt == SLAI_FMT_Q5_1) {
+        const uint8_t* h = b + hdr - 4;
+        const uint32_t qh = (uint32_t)h[0] | ((uint32_t)h[1] << 8) | ((uint32_t)h[2] << 16) | ((uint32_t)h[3] << 24);
+        q |= hi ? (int)((qh >> (j + 12)) & 0x10) : (int)(((qh >> j) << 4) & 0x10);
+    }
+    return q;
+}
+__global__ void legacy_to_q8_0_kernel(int fmt, const uint8_t* __restrict__ raw, uint8_t* __restrict__ out, long long nblocks, int bb) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= nblocks * 32) return;
+    const long long blk = i >> 5;
+    const int e = (int)(i & 31);
+    const uint8_t* b = raw + blk * bb;
+    uint8_t* o = out + blk * 34;
+    if (e < 2) o[e] = b[e];  // the f16 scale
+    o[2 + e] = (uint8_t)(signed char)(legacy_quant(fmt, b, e) - (fmt == SLAI_FMT_Q4_0 ? 8 : 16));
+}
+__global__ void legacy_to_f32_kernel(int fmt, const uint8_t* __restrict__ raw, float* __restrict__ out, long long n, int be, int bb) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint8_t* b = raw + (i / be) * bb;
+    const int e = (int)(i % be);
+    if (fmt == SLAI_FMT_Q8_K) {
+        float d;
+        memcpy(&d, b, 4);
+        out[i] = __fmul_rn(d, (float)(signed char)b[4 + e]);
+        return;
+    }
+    const float d = dev_h2f(b[0] | (b[1] << 8)), m = dev_h2f(b[2] | (b[3] << 8));
+    out[i] = __fadd_rn(__fmul_rn((float)legacy_quant(fmt, b, e), d), m);  // Q4_1 / Q5_1: q * d + m
+}
+
 }  // namespace
 
 static int qmatrix_alloc(slai_ctx* ctx, int fmt, int64_t nrows, int64_t ncols, size_t nbytes, slai_qmatrix** out) {
@@ -276,7 +313,7 @@ static int qmatrix_alloc(slai_ctx* ctx, int fmt, int64_t nrows, int64_t ncols, s
     *out = nullptr;
     const int be = fmt_block_elems(fmt), bb = fmt_block_bytes(fmt);
     SLAI_REQUIRE(ctx, be > 0, SLAI_ERR_UNSUPPORTED_FORMAT,
-                 "qmatrix: GGML type %d is not supported (supported: F32, Q8_0, Q4_K, Q5_K, Q6_K)", fmt);
+                 "qmatrix: GGML type %d is not supported (supported: F32, Q8_0, Q4_K, Q5_K, Q6_K and the legacy Q4_0, Q4_1, Q5_0, Q5_1, Q8_K)", fmt);
     SLAI_REQUIRE(ctx, nrows > 0 && ncols > 0 && ncols % be == 0, SLAI_ERR_SHAPE,
                  "qmatrix: %lld x %lld is not a whole number of %d-element blocks per row", (long long)nrows,
                  (long long)ncols, be);
@@ -285,9 +322,9 @@ static int qmatrix_alloc(slai_ctx* ctx, int fmt, int64_t nrows, int64_t ncols, s
     SLAI_REQUIRE(ctx, nbytes == (size_t)nrows * (ncols / be) * bb, SLAI_ERR_SHAPE,
                  "qmatrix: expected %zu bytes of blocks, got %zu", (size_t)nrows * (ncols / be) * bb, nbytes);
     slai_qmatrix* m = new slai_qmatrix();
-    m->ctx = ctx; m->fmt = fmt; m->nrows = nrows; m->ncols = ncols;
-    m->tile_bytes = fmt == SLAI_FMT_F32 ? ncols * 4 : layout::tile_bytes(fmt, ncols);
-    m->bytes = (size_t)layout::matrix_bytes(fmt, nrows, ncols);
+    m->ctx = ctx; m->src_fmt = fmt; m->fmt = legacy_device_format(fmt); m->nrows = nrows; m->ncols = ncols;
+    m->tile_bytes = m->fmt == SLAI_FMT_F32 ? ncols * 4 : layout::tile_bytes(m->fmt, ncols);
+    m->bytes = (size_t)layout::matrix_bytes(m->fmt, nrows, ncols);
     cudaError_t e = cudaMalloc(&m->data, m->bytes + 256);
     if (e != cudaSuccess) {
         cudaGetLastError();
@@ -309,6 +346,21 @@ SLAI_API int slai_qmatrix_create_from_device(slai_ctx* ctx, int fmt, int64_t nro
     const long long nbk = ncols / be;
     if (fmt == SLAI_FMT_F32) {
         SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(m->data, d_blocks, nbytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    } else if (m->fmt != fmt && m->fmt == SLAI_FMT_F32) {  // Q4_1 / Q5_1 / Q8_K: dense f32
+        const long long n = nrows * ncols;
+        legacy_to_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(fmt, (const uint8_t*)d_blocks, (float*)m->data, n, be, bb);
+        SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    } else if (m->fmt != fmt) {  // Q4_0 / Q5_0: the same values as Q8_0 blocks, then the usual placement
+        const long long total = nrows * nbk;
+        uint8_t* q8 = nullptr;
+        SLAI_CHECK_CUDA(ctx, cudaMalloc(&q8, (size_t)total * 34));
+        legacy_to_q8_0_kernel<<<(unsigned)((total * 32 + 255) / 256), 256, 0, ctx->stream>>>(fmt, (const uint8_t*)d_blocks, q8, total, bb);
+        SLAI_CHECK_CUDA(ctx, cudaMemsetAsync(m->data, 0, m->bytes, ctx->stream));
+        place_kernel<<<(unsigned)((total + 127) / 128), 128, 0, ctx->stream>>>(SLAI_FMT_Q8_0, q8, m->data, nrows, nbk, ncols, 34);
+        cudaError_t e = cudaGetLastError();
+        cudaStreamSynchronize(ctx->stream);
+        cudaFree(q8);
+        SLAI_CHECK_CUDA(ctx, e);
     } else {
         SLAI_CHECK_CUDA(ctx, cudaMemsetAsync(m->data, 0, m->bytes, ctx->stream));  // padding rows / steps are zero
         const long long total = nrows * nbk;
@@ -351,7 +403,7 @@ SLAI_API int slai_qmatrix_destroy(slai_qmatrix* m) {
 SLAI_API int slai_qmatrix_shape(const slai_qmatrix* m, int* fmt, int64_t* nrows, int64_t* ncols) {
     if (!m) return SLAI_ERR_INVALID_ARG;
     SLAI_ENTER(m->ctx);
-    if (fmt) *fmt = m->fmt;
+    if (fmt) *fmt = m->src_fmt;
     if (nrows) *nrows = m->nrows;
     if (ncols) *ncols = m->ncols;
     return SLAI_OK;

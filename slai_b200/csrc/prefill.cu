@@ -359,28 +359,28 @@ __global__ void prefill_embed_kernel(float* __restrict__ x, int dim, const int* 
     x[(size_t)t * dim + i] = table ? table[row * dim + i] : dequant_elem(fmt, qdata, dim, row, i);
 }
 
-// RoPE (ops/rope.rs:88-125; both variants) on q and k of token t at position pos0 + t, q to its own buffer, k and v into
-// the cache ([kv_head][position][head_size], f16 or f32): the q/k/v epilogue of the decode step, for T tokens at once.
-__global__ void prefill_rope_kv_kernel(const float* __restrict__ qkv, int ld, int q_dim, int kv_dim, int head_size, int pos0,
-                                       const float* __restrict__ theta, int neox, float* __restrict__ q_out, void* kcache, void* vcache,
-                                       int kv_f16, long long kv_head_stride) {
+// RoPE (ops/rope.rs:88-125; both variants) on q and k of token t at position pos0 + t (or *d_pos + t), q to `q_out`
+// (may be its source), k and, when given, v into the cache ([kv_head][position][head_size], f16 or f32): the q/k/v
+// epilogue of the decode step for T tokens at once, and the decode step's own RoPE stage where the fused epilogue
+// cannot serve (pairs half a head apart, dense f32 matrices).
+__global__ void rope_kv_store_kernel(const float* __restrict__ q_src, const float* __restrict__ k_src, const float* __restrict__ v_src,
+                                     int ld, int q_dim, int kv_dim, int head_size, int pos0, const int* __restrict__ d_pos,
+                                     const float* __restrict__ theta, int neox, float* __restrict__ q_out, int ldq, void* kcache, void* vcache,
+                                     int kv_f16, long long kv_head_stride) {
     const int t = blockIdx.y;
     const int p = blockIdx.x * blockDim.x + threadIdx.x;  // pair index over q then k; then plain copies of v
-    const int pos = pos0 + t;
-    const float* row = qkv + (size_t)t * ld;
+    const int pos = (d_pos ? *d_pos : pos0) + t;
     const int nq = q_dim / 2, nk = kv_dim / 2;
     if (p < nq + nk) {
         const bool is_k = p >= nq;
         const int i = is_k ? p - nq : p;
-        const float* src = row + (is_k ? q_dim : 0);
-        const int head = (2 * i) / head_size, j = (2 * i) % head_size;  // j: even offset inside the head
-        int a, b, fi;
+        const float* src = (is_k ? k_src : q_src) + (size_t)t * ld;
+        const int head = (2 * i) / head_size, fi = ((2 * i) % head_size) >> 1;
+        int a, b;
         if (neox) {
-            fi = j >> 1;
             a = head * head_size + fi;
             b = a + head_size / 2;
         } else {
-            fi = j >> 1;
             a = 2 * i;
             b = a + 1;
         }
@@ -389,8 +389,8 @@ __global__ void prefill_rope_kv_kernel(const float* __restrict__ qkv, int ld, in
         const float xa = src[a], xb = src[b];
         const float ya = cs * xa - sn * xb, yb = sn * xa + cs * xb;
         if (!is_k) {
-            q_out[(size_t)t * q_dim + a] = ya;
-            q_out[(size_t)t * q_dim + b] = yb;
+            q_out[(size_t)t * ldq + a] = ya;
+            q_out[(size_t)t * ldq + b] = yb;
         } else {
             const int ha = a / head_size, da = a % head_size, hb = b / head_size, db = b % head_size;
             const long long oa = (long long)pos * head_size + ha * kv_head_stride + da, ob = (long long)pos * head_size + hb * kv_head_stride + db;
@@ -402,9 +402,9 @@ __global__ void prefill_rope_kv_kernel(const float* __restrict__ qkv, int ld, in
                 reinterpret_cast<float*>(kcache)[ob] = yb;
             }
         }
-    } else if (p < nq + nk + kv_dim) {
+    } else if (v_src && p < nq + nk + kv_dim) {
         const int e = p - nq - nk;
-        const float y = row[q_dim + kv_dim + e];
+        const float y = v_src[(size_t)t * ld + e];
         const long long o = (long long)pos * head_size + (e / head_size) * kv_head_stride + e % head_size;
         if (kv_f16) reinterpret_cast<__half*>(vcache)[o] = __float2half_rn(y);
         else reinterpret_cast<float*>(vcache)[o] = y;
@@ -494,8 +494,19 @@ int prefill_embed_launch(slai_ctx* ctx, float* x, int dim, const int* d_tokens, 
 int prefill_rope_kv_launch(slai_ctx* ctx, const float* qkv, int ld, int q_dim, int kv_dim, int head_size, int pos0, int T,
                            const float* theta, int neox, float* q_out, void* kcache, void* vcache, int kv_f16, long long kv_head_stride) {
     const int work = q_dim / 2 + kv_dim / 2 + kv_dim;
-    prefill_rope_kv_kernel<<<dim3((work + 255) / 256, T), 256, 0, ctx->stream>>>(qkv, ld, q_dim, kv_dim, head_size, pos0, theta, neox, q_out,
-                                                                                kcache, vcache, kv_f16, kv_head_stride);
+    rope_kv_store_kernel<<<dim3((work + 255) / 256, T), 256, 0, ctx->stream>>>(qkv, qkv + q_dim, qkv + q_dim + kv_dim, ld, q_dim, kv_dim, head_size,
+                                                                              pos0, nullptr, theta, neox, q_out, q_dim, kcache, vcache, kv_f16,
+                                                                              kv_head_stride);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    return SLAI_OK;
+}
+// One token at the device-side position: q rotated in place, k (and v when given) into the cache.
+int rope_kv_store_launch(slai_ctx* ctx, float* q, const float* k, const float* v, int q_dim, int kv_dim, int head_size, const int* d_pos,
+                         const float* theta, int neox, void* kcache, void* vcache, int kv_f16, long long kv_head_stride, bool pdl) {
+    const int work = q_dim / 2 + kv_dim / 2 + (v ? kv_dim : 0);
+    (void)pdl;
+    rope_kv_store_kernel<<<dim3((work + 255) / 256, 1), 256, 0, ctx->stream>>>(q, k, v, 0, q_dim, kv_dim, head_size, 0, d_pos, theta, neox, q, q_dim,
+                                                                              kcache, vcache, kv_f16, kv_head_stride);
     SLAI_CHECK_CUDA(ctx, cudaGetLastError());
     return SLAI_OK;
 }

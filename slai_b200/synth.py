@@ -14,11 +14,18 @@ from __future__ import annotations
 import numpy as np
 
 FMT_F32, FMT_Q8_0, FMT_Q4_K, FMT_Q5_K, FMT_Q6_K = 0, 8, 12, 13, 14
-FMT_NAMES = {FMT_F32: "f32", FMT_Q8_0: "q8_0", FMT_Q4_K: "q4_k", FMT_Q5_K: "q5_k", FMT_Q6_K: "q6_k"}
+# the legacy 32-element formats and Q8_K (crates/slai/src/quantization.rs:47-199): uploaded, not generated here
+FMT_Q4_0, FMT_Q4_1, FMT_Q5_0, FMT_Q5_1, FMT_Q8_K = 2, 3, 6, 7, 15
+LEGACY_FORMATS = (FMT_Q4_0, FMT_Q4_1, FMT_Q5_0, FMT_Q5_1, FMT_Q8_K)
+FMT_NAMES = {FMT_F32: "f32", FMT_Q8_0: "q8_0", FMT_Q4_K: "q4_k", FMT_Q5_K: "q5_k", FMT_Q6_K: "q6_k", FMT_Q4_0: "q4_0", FMT_Q4_1: "q4_1",
+             FMT_Q5_0: "q5_0", FMT_Q5_1: "q5_1", FMT_Q8_K: "q8_k"}
 FMT_BY_NAME = {v: k for k, v in FMT_NAMES.items()}
-BLOCK_BYTES = {FMT_F32: 4, FMT_Q8_0: 34, FMT_Q4_K: 144, FMT_Q5_K: 176, FMT_Q6_K: 210}
-BLOCK_ELEMS = {FMT_F32: 1, FMT_Q8_0: 32, FMT_Q4_K: 256, FMT_Q5_K: 256, FMT_Q6_K: 256}
-BITS_PER_WEIGHT = {FMT_F32: 32.0, FMT_Q8_0: 8.5, FMT_Q4_K: 4.5, FMT_Q5_K: 5.5, FMT_Q6_K: 6.5625}
+BLOCK_BYTES = {FMT_F32: 4, FMT_Q8_0: 34, FMT_Q4_K: 144, FMT_Q5_K: 176, FMT_Q6_K: 210, FMT_Q4_0: 18, FMT_Q4_1: 20, FMT_Q5_0: 22, FMT_Q5_1: 24,
+               FMT_Q8_K: 292}
+BLOCK_ELEMS = {FMT_F32: 1, FMT_Q8_0: 32, FMT_Q4_K: 256, FMT_Q5_K: 256, FMT_Q6_K: 256, FMT_Q4_0: 32, FMT_Q4_1: 32, FMT_Q5_0: 32, FMT_Q5_1: 32,
+               FMT_Q8_K: 256}
+BITS_PER_WEIGHT = {FMT_F32: 32.0, FMT_Q8_0: 8.5, FMT_Q4_K: 4.5, FMT_Q5_K: 5.5, FMT_Q6_K: 6.5625, FMT_Q4_0: 4.5, FMT_Q4_1: 5.0, FMT_Q5_0: 5.5,
+                   FMT_Q5_1: 6.0, FMT_Q8_K: 9.125}
 
 
 def _f16_bits(x: np.ndarray) -> np.ndarray:
@@ -134,7 +141,58 @@ def quantize_q6_k(x: np.ndarray) -> np.ndarray:
     return out.reshape(*lead, K // 256 * 210)
 
 
-_QUANTIZERS = {FMT_Q8_0: quantize_q8_0, FMT_Q4_K: quantize_q4_k, FMT_Q5_K: quantize_q5_k, FMT_Q6_K: quantize_q6_k}
+def _pack_legacy(q: np.ndarray, bits: int, headers: list) -> np.ndarray:
+    """q: [nb, 32] codes of `bits` (4 or 5) bits -> legacy block bytes: headers, [fifth bits,] 16 nibble bytes (element j
+    in the low nibble of byte j, element j + 16 in the high nibble; fifth bit of element e is bit e of the 4-byte word)."""
+    nb = q.shape[0]
+    parts = [h.reshape(nb, -1) for h in headers]
+    if bits == 5:
+        word = np.zeros(nb, dtype=np.uint32)
+        for e in range(32):
+            word |= ((q[:, e].astype(np.uint32) >> 4) & 1) << e
+        parts.append(word.reshape(nb, 1).view(np.uint8))
+    lo = q & 0x0F
+    parts.append((lo[:, :16] | (lo[:, 16:] << 4)).astype(np.uint8))
+    return np.concatenate(parts, axis=1)
+
+
+def quantize_legacy(fmt: int, x: np.ndarray) -> np.ndarray:
+    """Simple own-design quantisers for the legacy formats (quantization.rs:47-199 defines the blocks, not how to fill them):
+    Q4_0 / Q5_0 symmetric (d = absmax / 7 or / 15, code = round(x / d) + 8 or + 16), Q4_1 / Q5_1 affine (d = range / 15 or / 31,
+    m = min), Q8_K d = absmax / 127 as f32."""
+    x = np.asarray(x, dtype=np.float32)
+    lead, K = x.shape[:-1], x.shape[-1]
+    if fmt == FMT_Q8_K:
+        b = x.reshape(-1, 256)
+        d = (np.abs(b).max(axis=1) / np.float32(127.0)).astype(np.float32)
+        q = np.clip(np.rint(_safe_div(b, d[:, None])), -127, 127).astype(np.int8)
+        out = np.zeros((b.shape[0], 292), dtype=np.uint8)
+        out[:, 0:4] = d.reshape(-1, 1).view(np.uint8)
+        out[:, 4:260] = q.view(np.uint8)
+        out[:, 260:] = q.reshape(-1, 16, 16).astype(np.int16).sum(axis=2).astype(np.int16).view(np.uint8).reshape(-1, 32)
+        return out.reshape(*lead, K // 256 * 292)
+    b = x.reshape(-1, 32)
+    bits = 4 if fmt in (FMT_Q4_0, FMT_Q4_1) else 5
+    top = (1 << bits) - 1
+    if fmt in (FMT_Q4_0, FMT_Q5_0):
+        half = 1 << (bits - 1)
+        d = np.abs(b).max(axis=1) / np.float32(half - 1)
+        dv = _f16_val(d)
+        q = np.clip(np.rint(_safe_div(b, dv[:, None])) + half, 0, top).astype(np.uint8)
+        out = _pack_legacy(q, bits, [_f16_bits(d).reshape(-1, 1).view(np.uint8)])
+    else:
+        lo, hi = b.min(axis=1), b.max(axis=1)
+        d = (hi - lo) / np.float32(top)
+        dv, mv = _f16_val(d), _f16_val(lo)
+        q = np.clip(np.rint(_safe_div(b - mv[:, None], dv[:, None])), 0, top).astype(np.uint8)
+        out = _pack_legacy(q, bits, [_f16_bits(d).reshape(-1, 1).view(np.uint8), _f16_bits(lo).reshape(-1, 1).view(np.uint8)])
+    return out.reshape(*lead, K // 32 * BLOCK_BYTES[fmt])
+
+
+_QUANTIZERS = {FMT_Q8_0: quantize_q8_0, FMT_Q4_K: quantize_q4_k, FMT_Q5_K: quantize_q5_k, FMT_Q6_K: quantize_q6_k,
+               FMT_Q4_0: lambda x: quantize_legacy(FMT_Q4_0, x), FMT_Q4_1: lambda x: quantize_legacy(FMT_Q4_1, x),
+               FMT_Q5_0: lambda x: quantize_legacy(FMT_Q5_0, x), FMT_Q5_1: lambda x: quantize_legacy(FMT_Q5_1, x),
+               FMT_Q8_K: lambda x: quantize_legacy(FMT_Q8_K, x)}
 
 
 def quantize(fmt: int, x: np.ndarray) -> np.ndarray:
@@ -156,6 +214,12 @@ def random_blocks(fmt: int, M: int, K: int, rng: np.random.Generator) -> np.ndar
         raw[:, 0:4] = d.view(np.uint8).reshape(-1, 4)
     elif fmt == FMT_Q6_K:
         raw[:, 208:210] = d[:, 0:1].view(np.uint8)
+    elif fmt in (FMT_Q4_0, FMT_Q5_0):
+        raw[:, 0:2] = d[:, 0:1].view(np.uint8)
+    elif fmt in (FMT_Q4_1, FMT_Q5_1):
+        raw[:, 0:4] = d.view(np.uint8).reshape(-1, 4)
+    elif fmt == FMT_Q8_K:
+        raw[:, 0:4] = rng.uniform(1e-4, 2e-3, size=(M * nbk, 1)).astype(np.float32).view(np.uint8)
     return raw.reshape(M, nbk * BLOCK_BYTES[fmt])
 
 

@@ -69,6 +69,24 @@ def recipes():
         b[i, 192:208] = ((sc + 128) % 256 - 128).astype(np.int8).view(np.uint8)
         b[i, 208:210] = np.array([123], dtype=np.uint16).view(np.uint8)
     out[synth.FMT_Q6_K] = b
+    # legacy formats (ops/quantization.rs:85-148): 16 blocks each, qs[k] = 16 i + k, d = f16(1.234); Q4_1 m = raw bits 3,
+    # Q5_x qh = [1, 100, 200, 250], Q5_1 m = raw bits 125; Q8_K d = 1.234f, qs[k] = saturating (8 i - 127) + (k as i8), bsums 0
+    half = np.array([1.234], dtype=np.float32).astype(np.float16).view(np.uint8)
+    qh = np.array([1, 100, 200, 250], dtype=np.uint8)
+    for fmt, hdr in ((synth.FMT_Q4_0, [half]), (synth.FMT_Q4_1, [half, np.array([3], np.uint16).view(np.uint8)]),
+                     (synth.FMT_Q5_0, [half, qh]), (synth.FMT_Q5_1, [half, np.array([125], np.uint16).view(np.uint8), qh])):
+        b = np.zeros((16, synth.BLOCK_BYTES[fmt]), dtype=np.uint8)
+        h = np.concatenate(hdr)
+        for i in range(16):
+            b[i, :h.size] = h
+            b[i, h.size:] = (16 * i + np.arange(16)).astype(np.uint8)
+        out[fmt] = b
+    b = np.zeros((16, 292), dtype=np.uint8)
+    for i in range(16):
+        b[i, 0:4] = np.array([1.234], dtype=np.float32).view(np.uint8)
+        k = np.arange(256).astype(np.uint8).view(np.int8).astype(np.int32)
+        b[i, 4:260] = np.clip(8 * i - 127 + k, -128, 127).astype(np.int8).view(np.uint8)
+    out[synth.FMT_Q8_K] = b
     return out
 
 
@@ -77,12 +95,13 @@ def main():
     save = {}
     try:
         from gguf import quants, GGMLQuantizationType as T
-        tmap = {synth.FMT_Q8_0: T.Q8_0, synth.FMT_Q4_K: T.Q4_K, synth.FMT_Q5_K: T.Q5_K, synth.FMT_Q6_K: T.Q6_K}
+        tmap = {synth.FMT_Q8_0: T.Q8_0, synth.FMT_Q4_K: T.Q4_K, synth.FMT_Q5_K: T.Q5_K, synth.FMT_Q6_K: T.Q6_K, synth.FMT_Q4_0: T.Q4_0,
+                synth.FMT_Q4_1: T.Q4_1, synth.FMT_Q5_0: T.Q5_0, synth.FMT_Q5_1: T.Q5_1}
     except Exception:  # pragma: no cover
         quants, tmap = None, {}
     for fmt, blocks in rec.items():
         vals = O.dequantize(fmt, blocks)
-        if quants is not None:
+        if quants is not None and fmt in tmap:
             ref = quants.dequantize(blocks, tmap[fmt]).reshape(-1)
             assert np.array_equal(vals.view(np.uint32), ref.astype(np.float32).view(np.uint32)), synth.FMT_NAMES[fmt]
         name = synth.FMT_NAMES[fmt]

@@ -169,3 +169,33 @@ def test_model_from_gguf_matches_oracle(backend, tmp_path, fmt, tied):
         rl = ref.forward(tok, pos)
         assert rel_l2(lg, rl) < 1e-3, pos
         tok = O.argmax(rl)
+
+
+def test_reference_parse_fixture():
+    """The reference's own parse fixture (assets/gguf/dummy.gguf, copied to tests/golden/): version 3, fifteen metadata
+    entries covering every scalar type, strings and arrays, ten f32 tensors; read by this repository's reader and, when
+    it is importable, identically by the `gguf` python package."""
+    path = os.path.join(os.path.dirname(__file__), "golden", "dummy.gguf")
+    g = gguf_io.GgufFile(path)
+    assert g.version == 3 and len(g.metadata) == 15 and len(g.tensors) == 10
+    md = g.metadata
+    assert md["some.parameter.uint8"] == 0x12 and md["some.parameter.int8"] == -0x13
+    assert md["some.parameter.uint16"] == 0x1234 and md["some.parameter.int16"] == -0x1235
+    assert md["some.parameter.uint32"] == 0x12345678 and md["some.parameter.int32"] == -0x12345679
+    assert md["some.parameter.uint64"] == 0x123456789ABCDEF0 and md["some.parameter.int64"] == -0x123456789ABCDEF1
+    assert abs(md["some.parameter.float32"] - 0.123456789) < 1e-7 and abs(md["some.parameter.float64"] - 0.1234567890123456789) < 1e-15
+    assert md["some.parameter.bool"] is True and md["some.parameter.string"] == "hello world"
+    assert len(md["some.parameter.arr.i16"]) == 4 and len(md["some.parameter.arr.f32"]) == 3 and len(md["some.parameter.arr.str"]) == 3
+    for t in g.tensors.values():
+        assert t.ggml_type == 0 and t.data.size == 4 * int(np.prod(t.dims))
+    try:
+        from gguf import GGUFReader
+    except Exception:
+        g.close()
+        return
+    r = GGUFReader(path)
+    theirs = {t.name: t for t in r.tensors}
+    assert sorted(theirs) == sorted(g.tensors)
+    for name, t in g.tensors.items():
+        assert np.array_equal(np.frombuffer(bytes(t.data), dtype=np.uint8), np.asarray(theirs[name].data).view(np.uint8).reshape(-1))
+    g.close()
