@@ -10,7 +10,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libslai_b200.so")
-SOURCES = ["gemv.cu", "decode.cu", "attention.cu", "ops.cu", "model.cu", "tp.cu", "sampler.cu", "prefill.cu"]
+SOURCES = ["gemv.cu", "attention.cu", "ops.cu", "model.cu", "tp.cu", "sampler.cu", "prefill.cu"]
 HEADERS = ["common.cuh", "dequant.cuh", "gemv_frag.cuh", "gemv_formats.cuh", "gemv_kernel.cuh", "attention.cuh", "layout.cuh", os.path.join("..", "..", "include", "slai_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-fvisibility=hidden"]
@@ -35,7 +35,7 @@ def build(force: bool = False, verbose: bool = False, trace: bool = False) -> st
     hdrs = [os.path.join(CSRC, h) for h in HEADERS]
     objdir = os.path.join(HERE, "build_trace" if trace else "build")
     lib = os.path.join(HERE, "libslai_b200_trace.so") if trace else LIB
-    flags = NVCC_FLAGS + (["-DSLAI_TRACE"] if trace else [])
+    flags = NVCC_FLAGS + (["-DSLAI_TRACE"] if trace else []) + os.environ.get("SLAI_NVCC_EXTRA", "").split()
     os.makedirs(objdir, exist_ok=True)
     jobs = []
     objs = []

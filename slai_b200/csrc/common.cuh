@@ -69,7 +69,6 @@ constexpr int CNT_ATTN_TICKETS = 0;    // one ticket per KV head (<= 1024): last
 constexpr int CNT_ARGMAX = 1100;       // ticket, then per-block (value, index) pairs of the multi-block argmax
 constexpr int CNT_ATTN_POS = 2048;     // position scalar of the stand-alone slai_attention
 constexpr int CNT_ERR_FLAG = 3000;     // raised by a bounded wait that ran out (1 weight ring, 2 grid barrier, 3 peer exchange)
-constexpr int CNT_GRID_BAR = 3100;     // grid barrier of the persistent decode kernel
 constexpr int CNT_WORDS = 4096;
 
 int slai_set_error(slai_ctx* ctx, int code, const char* fmt, ...);
@@ -362,42 +361,4 @@ int rope_kv_store_launch(slai_ctx* ctx, float* q, const float* k, const float* v
 int prefill_rope_kv_launch(slai_ctx* ctx, const float* qkv, int ld, int q_dim, int kv_dim, int head_size, int pos0, int T,
                            const float* theta, int neox, float* q_out, void* kcache, void* vcache, int kv_f16, long long kv_head_stride);
 
-// decode.cu: all layers of a token in one persistent kernel (Llama family, one weight format for all matrices)
-struct DecodeLayersDesc {
-    int fmt, dim, hidden, n_heads, kv_mul, head_size, seq_len, kv_f16;
-};
-struct DecodeLayersPlan {
-    size_t dig_region = 0, smem = 0, part_o_bytes = 0, part_ml_bytes = 0;
-    int nstage = 0, n_splits = 0;
-};
-// Per-layer pointers of the persistent decode kernel.  They travel in the kernel's parameter block (constant
-// bank): the ring producer and every phase read them with no memory latency.
-struct DecodeLayerPtrs {
-    const uint8_t *wq, *wk, *wv, *wo, *wgate, *wup, *wdown;  // tile-major quantised matrices
-    const float *attn_norm, *ffn_norm, *bq, *bk, *bv;        // biases may be null
-    void *kcache, *vcache;                                   // this layer's slice of the caches
-};
-constexpr int DECODE_MAX_LAYERS = 96;
-struct DecodeParams {
-    // geometry (decode_layers_prepare)
-    int fmt, dim, hidden, kv_dim, n_heads, n_kv, kv_mul, head_size, seq_len, n_layers;
-    int nsteps_dim, nsteps_hidden;               // tile-step blocks per tile for K = dim / K = hidden
-    int items_base[4], items_rem[4];             // per GEMV of a layer: items per block of threads (base, +1 for the first rem)
-    long long tile_bytes_dim, tile_bytes_hidden;  // bytes of a 16-row tile
-    int nstage, step_bytes, stage_stride, dig_region;
-    int n_splits, tile_pos, att_item_bytes, vec16;
-    unsigned int *bar, *err_flag, *counters;
-    unsigned int wait_limit;
-    // the model's buffers (caller)
-    float eps;
-    const float* rope_theta;
-    const int* d_pos;
-    int kv_f16;
-    float *x, *xb, *q, *hb;
-    float *part_o, *part_ml;
-    DecodeLayerPtrs layer[DECODE_MAX_LAYERS];
-};
 size_t gemv_dig_region(int fmt, int K);
-// Sizes shared memory, ring depth and the attention split for `desc`, and fills the geometry fields of `D`.
-int decode_layers_prepare(slai_ctx* ctx, const DecodeLayersDesc& desc, DecodeLayersPlan* plan, DecodeParams* D);
-int decode_layers_launch(slai_ctx* ctx, const DecodeParams& D, const DecodeLayersPlan& plan);

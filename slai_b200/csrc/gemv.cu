@@ -12,19 +12,18 @@ using namespace gemvk;
 namespace {
 
 template <class F, int NMAT, int PRO, int EPI, bool XIN = false>
-__global__ void __launch_bounds__(THREADS, 1) gemv_kernel(const __grid_constant__ GemvParams P) {
+__global__ void __launch_bounds__(THREADS, SLAI_GEMV_MINB) gemv_kernel(const __grid_constant__ GemvParams P) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     SLAI_TRACE_POINT(0)
     Ring R;
-    const OneProg prog{P};
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    ring_setup<F>(R, P, smem_raw, lane, warp);
+    SLAI_TRACE_POINT(1)
     // The weights do not depend on the kernel this one may be launched behind (programmatic dependent launch):
     // the ring starts filling while that kernel drains.
-    #ifdef SLAI_TRACE
-    ring_init(R, prog, P.dig_region, P.nstage, P.stage_stride, P.step_bytes, P.err_flag, P.wait_limit, smem_raw, lane, warp, P.trace);
-#else
-    ring_init(R, prog, P.dig_region, P.nstage, P.stage_stride, P.step_bytes, P.err_flag, P.wait_limit, smem_raw, lane, warp);
-#endif
+    const Split sp = make_split(P);
+    ring_fill<F>(R, P, sp, warp);
+    SLAI_TRACE_POINT(2)
     // Let the next kernel's blocks be scheduled as this kernel's blocks leave their SMs (it parks in its own
     // griddepcontrol.wait until this grid has completed): the hand-over costs no grid-wide launch latency.
     if (P.pdl == 2) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -32,12 +31,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_kernel(const __grid_constant_
     // Pull data the *next* kernel reads first (its norm weights) into L2 while this one runs.
     if (P.pf_lines > 0 && (int)blockIdx.x == (int)gridDim.x - 1)
         for (int i = threadIdx.x; i < P.pf_lines; i += THREADS) asm volatile("prefetch.global.L2 [%0];" ::"l"(P.pf_ptr + (size_t)i * 128));
-    // partial-sum buffer cleared while the predecessor drains (same layout as in gemv_phase)
+    // partial-sum buffer cleared while the predecessor drains
     for (int i = threadIdx.x; i < WAVE * WARPS * NMAT * 16; i += THREADS) reinterpret_cast<float*>(smem_raw + P.dig_region)[i] = 0.f;
     SLAI_TRACE_POINT(3)
     asm volatile("griddepcontrol.wait;" ::: "memory");
     SLAI_TRACE_POINT(4)
-    gemv_phase<F, 1 << PRO, 1 << EPI, XIN>(P, R, prog, smem_raw, NMAT, PRO, EPI, true);
+    gemv_body<F, NMAT, PRO, EPI, XIN>(P, R, sp, smem_raw);
     if (P.pdl != 2) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 #ifdef SLAI_TRACE
     if (blockIdx.x == 0 && threadIdx.x == 0 && P.trace) {
@@ -165,7 +164,7 @@ int gemv_fill_params(slai_ctx* ctx, const GemvLaunch& L, size_t dig_region, int 
     P.K = K;
     P.nsteps = (int)layout::num_steps(L.fmt, K);
     P.step_bytes = layout::step_bytes(L.fmt);
-    P.stage_stride = (P.step_bytes + 127) & ~127;
+    P.stage_stride = (P.step_bytes + 8 + 127) & ~127;  // block + its mbarrier (RingGeom)
     P.v = L.v; P.out = L.out; P.norm_w = L.norm_w; P.norm_b = L.norm_b; P.eps = L.eps;
     P.resid = L.resid; P.rope = L.rope; P.rope_theta = L.rope_theta; P.rope_cs = L.rope_cs; P.head_size = L.head_size;
     P.d_pos = L.d_pos; P.pos1 = 0; P.kcache = L.kcache; P.vcache = L.vcache; P.k_out = L.k_out; P.kv_f16 = (L.kv_dtype == SLAI_KV_F16);
@@ -224,7 +223,7 @@ int gemv_fill_params(slai_ctx* ctx, const GemvLaunch& L, size_t dig_region, int 
     if (dig_region == 0) dig_region = need;
     SLAI_REQUIRE(ctx, dig_region >= need, SLAI_ERR_INVALID_ARG, "gemv: staging region too small");
     P.dig_region = (int)dig_region;
-    const size_t fixed = dig_region + (size_t)RED_FLOATS * 4 + 64 * 4 + WARPS * MAX_STAGES * 8 + 128;
+    const size_t fixed = dig_region + (size_t)RED_FLOATS * 4 + 64 * 4 + 128;
     const size_t per_stage = (size_t)WARPS * P.stage_stride;
     if (nstage <= 0) {
         SLAI_REQUIRE(ctx, fixed + 2 * per_stage <= SMEM_LIMIT, SLAI_ERR_SHAPE, "gemv: K=%d does not fit in shared memory", K);

@@ -194,6 +194,7 @@ SLAI_HD uint32_t byte_of(uint32_t w, int i) { return (w >> (8 * i)) & 0xFFu; }
 template <bool FIVE>
 struct K45 {
     static constexpr int FMT = FIVE ? 13 : 12;
+    static constexpr int STEP_BYTES = FIVE ? 2880 : 2368;
     static constexpr int STEP = 256;
     static constexpr int SV_GRAN = 32;
     static constexpr float PRESCALE = FIVE ? 1.0f : 0.0625f;
@@ -257,6 +258,7 @@ using Q5K = K45<true>;
 // ---- Q6_K ----------------------------------------------------------------------------------
 struct Q6K {
     static constexpr int FMT = 14;
+    static constexpr int STEP_BYTES = 3360;
     static constexpr int STEP = 256;
     static constexpr int SV_GRAN = 16;
     static constexpr float PRESCALE = 1.0f;
@@ -299,6 +301,7 @@ struct Q6K {
 // ---- Q8_0: a block is 4 GGUF blocks (128 values) ---------------------------------------------
 struct Q80 {
     static constexpr int FMT = 8;
+    static constexpr int STEP_BYTES = 2176;
     static constexpr int STEP = 128;
     static constexpr int SV_GRAN = 0;
     static constexpr float PRESCALE = 1.0f;

@@ -1,5 +1,4 @@
-// Device side of the dequant-GEMV: shared by the stand-alone GEMV kernel (gemv.cu) and the persistent
-// decode kernel that runs all layers of a token in one launch (decode.cu).
+// Device side of the dequant-GEMV kernel (gemv.cu).
 //
 // Shape.  One persistent block of 16 warps per SM.  The weights are stored tile-major (layout.cuh): the packed
 // data of 16 rows x one K step is one contiguous block.  Work is divided in two levels so that every SM and
@@ -11,9 +10,7 @@
 //
 // Data movement.  Every warp owns a private ring of shared-memory stages; one lane issues a bulk asynchronous
 // copy (cp.async.bulk, completion counted on an mbarrier) per block, always NSTAGE blocks ahead of the block
-// being consumed.  The producer walks a *program*: a list of GEMV phases.  For the stand-alone kernel the
-// program has one entry; in the persistent decode kernel it lists every GEMV of every layer, so the ring keeps
-// streaming the next phase's weights while the block of threads waits at the grid barrier between phases.
+// being consumed.  The ring starts filling before the wait for the predecessor (programmatic dependent launch).
 //
 // Arithmetic.  Packed quants, four per register, go to the integer tensor-core MMA (mma.sync.m16n8k32 s8)
 // against base-256 digit planes of the activation vector, staged once per phase in shared memory
@@ -35,8 +32,11 @@ using namespace gemvfmt;
 #define SLAI_GEMV_WARPS 16
 #endif
 constexpr int WARPS = SLAI_GEMV_WARPS;
+#ifndef SLAI_GEMV_MINB
+#define SLAI_GEMV_MINB 1
+#endif
 constexpr int THREADS = 32 * WARPS;
-constexpr int MAX_STAGES = 8;
+constexpr int MAX_STAGES = 8;  // ring depth limit (host side)
 constexpr int WAVE = 8;  // tiles whose partial sums are held in shared memory at a time
 constexpr int SMEM_LIMIT = 227 * 1024;
 constexpr int STAGE_REGS = 6;  // float4 per thread kept in registers between the staging passes (K <= 12288)
@@ -116,7 +116,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t a, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait: returns false (and raises the error flag) if the phase does not complete.
-__device__ __forceinline__ bool mbar_wait(uint32_t a, uint32_t parity, unsigned int limit, unsigned int* err_flag) {
+__device__ __noinline__ bool mbar_wait(uint32_t a, uint32_t parity, unsigned int limit, unsigned int* err_flag) {
     for (unsigned int i = 0; i < limit; i++) {
         if (mbar_try_wait(a, parity)) return true;
         if (i > 1024) __nanosleep(64);
@@ -331,16 +331,9 @@ __device__ __forceinline__ float stage_vector(const int PRO_ARG, const GemvParam
     int4* sv = reinterpret_cast<int4*>(__cvta_shared_to_generic(S.sv));
     unsigned char* svb = reinterpret_cast<unsigned char*>(sv);  // Q4_K / Q5_K: byte table of the sums (gemv_formats.cuh)
     if (tid < ZERO_BYTES / 4) reinterpret_cast<uint32_t*>(__cvta_shared_to_generic(S.zero))[tid] = 0u;
-#pragma unroll 1
-    for (int i = tid; i < np4; i += THREADS) {  // np4 is a multiple of 64: whole warps run each round together
-        float4 x;
-        if (cached) {
-            x = xr[0];
-#pragma unroll
-            for (int r = 0; r + 1 < STAGE_REGS; r++) xr[r] = xr[r + 1];
-        } else {
-            x = i < n4 ? __ldcg(v4 + i) : zero4;
-        }
+    // One float4 (elements 4i .. 4i+3): normalise, round to integers, digits, sums.  np4 is a multiple of 64, so whole
+    // warps take part in every call (the sums are reduced with shuffles).
+    auto convert = [&](float4 x, const int i) {
         if (i < n4 && PRO != PRO_NONE) {
             const float4 w = __ldg(w4p + i);  // L1 hit: the statistics pass has read it
             if (HAS_LN && PRO == PRO_LN) { x.x -= sub; x.y -= sub; x.z -= sub; x.w -= sub; }
@@ -354,24 +347,25 @@ __device__ __forceinline__ float stage_vector(const int PRO_ARG, const GemvParam
         uint32_t pw[4];
         digit_planes(digits_word(__float2int_rn(x.x * scale)), digits_word(__float2int_rn(x.y * scale)),
                      digits_word(__float2int_rn(x.z * scale)), digits_word(__float2int_rn(x.w * scale)), pw);
-        int sd[4];
 #pragma unroll
-        for (int q = 0; q < 4; q++) {
-            *reinterpret_cast<uint32_t*>(dig + (size_t)q * S.plane + 4 * i) = pw[q];
-            sd[q] = __dp4a((int)pw[q], 0x01010101, 0);  // sum of the four digits
-        }
+        for (int q = 0; q < 4; q++) *reinterpret_cast<uint32_t*>(dig + (size_t)q * S.plane + 4 * i) = pw[q];
         if (SV_GRAN > 0) {
-#pragma unroll
-            for (int q = 0; q < 4; q++) {
-                sd[q] += __shfl_xor_sync(0xffffffffu, sd[q], 1);
-                sd[q] += __shfl_xor_sync(0xffffffffu, sd[q], 2);
-                if (SV_GRAN == 32) sd[q] += __shfl_xor_sync(0xffffffffu, sd[q], 4);
-            }
             constexpr int LANES = SV_GRAN > 0 ? SV_GRAN / 4 : 1;  // float4 groups per sub-block
-            if (SV_GRAN == 32) {
-                // sub-block J = i / 8 of step J / 8: every sum (|sum| <= 4096) as two base-128 digits, one byte row per
-                // (digit plane, part); bytes 8..15 of the sub-block's own row index are the zero half of that row
-                if ((tid & 7) == 0) {
+            constexpr int BIAS = 512;                             // a float4's digit sum lies in [-512, 508]
+            // two biased sums per word, so that a shuffle round serves two digit planes
+            uint32_t s01 = (uint32_t)__dp4a((int)pw[0], 0x01010101, BIAS) | ((uint32_t)__dp4a((int)pw[1], 0x01010101, BIAS) << 16);
+            uint32_t s23 = (uint32_t)__dp4a((int)pw[2], 0x01010101, BIAS) | ((uint32_t)__dp4a((int)pw[3], 0x01010101, BIAS) << 16);
+#pragma unroll
+            for (int o = 1; o < LANES; o <<= 1) {
+                s01 += __shfl_xor_sync(0xffffffffu, s01, o);
+                s23 += __shfl_xor_sync(0xffffffffu, s23, o);
+            }
+            if ((tid & (LANES - 1)) == 0) {
+                const int sd[4] = {(int)(s01 & 0xFFFFu) - BIAS * LANES, (int)(s01 >> 16) - BIAS * LANES, (int)(s23 & 0xFFFFu) - BIAS * LANES,
+                                   (int)(s23 >> 16) - BIAS * LANES};
+                if (SV_GRAN == 32) {
+                    // sub-block J = i / 8 of step J / 8: every sum (|sum| <= 4096) as two base-128 digits, one byte row per
+                    // (digit plane, part); bytes 8..15 of the sub-block's own row index are the zero half of that row
                     const int J = i >> 3;
                     unsigned char* tab = svb + (J >> 3) * 128;
 #pragma unroll
@@ -381,11 +375,19 @@ __device__ __forceinline__ float stage_vector(const int PRO_ARG, const GemvParam
                         tab[(2 * q + 1) * 16 + (J & 7)] = (unsigned char)lo;
                     }
                     *reinterpret_cast<uint2*>(tab + (J & 7) * 16 + 8) = make_uint2(0u, 0u);
+                } else {
+                    sv[i / LANES] = make_int4(sd[0], sd[1], sd[2], sd[3]);
                 }
-            } else if ((tid & (LANES - 1)) == 0) {
-                sv[i / LANES] = make_int4(sd[0], sd[1], sd[2], sd[3]);
             }
         }
+    };
+    if (cached) {
+#pragma unroll
+        for (int r = 0; r < STAGE_REGS; r++)
+            if (tid + r * THREADS < np4) convert(xr[r], tid + r * THREADS);  // independent rounds: the compiler overlaps them
+    } else {
+#pragma unroll 1
+        for (int i = tid; i < np4; i += THREADS) convert(i < n4 ? __ldcg(v4 + i) : zero4, i);
     }
     SLAI_TRACE_POINT(8)
     __syncthreads();
@@ -412,59 +414,49 @@ __device__ __forceinline__ GemvSeg seg_pick(const GemvParams& P, int s) {
     return r;
 }
 
-// A *program* tells the ring producer what to stream: entry i is a GEMV phase with `nsteps` blocks per tile,
-// `nmat` matrices per item and items dealt to the blocks of threads as `items_base` each plus one more for the
-// first `items_rem`; tile_ptr gives the first block of (item, matrix).  The stand-alone kernel's program is its
-// one parameter block.
-struct ProgGeom {
-    int nsteps, nmat, items_base, items_rem;
-};
-struct OneProg {
-    const GemvParams& P;
-    __device__ __forceinline__ int size() const { return 1; }
-    __device__ __forceinline__ ProgGeom geom(int) const { return ProgGeom{P.nsteps, P.nmat, P.items_base, P.items_rem}; }
-    __device__ __forceinline__ const uint8_t* tile_ptr(int, int item, int mat) const {
-        const int sidx = P.nmat == 2 ? mat : seg_of_tile(P, item);
-        const uint8_t* w = P.seg[0].w;
-        long long tb = P.seg[0].tile_bytes;
-        int t0 = 0;
-        if (sidx == 1) { w = P.seg[1].w; tb = P.seg[1].tile_bytes; t0 = P.seg[1].tile0; }
-        if (sidx == 2) { w = P.seg[2].w; tb = P.seg[2].tile_bytes; t0 = P.seg[2].tile0; }
-        const int tile = P.nmat == 2 ? item : item - t0;
-        return w + (size_t)tile * tb;
-    }
-};
+// First tile-step block of (item, matrix): items are 16-row tiles (of segment 0 and 1 together for the gate/up pair).
+__device__ __forceinline__ const uint8_t* tile_ptr(const GemvParams& P, int item, int mat) {
+    const int sidx = P.nmat == 2 ? mat : seg_of_tile(P, item);
+    const uint8_t* w = P.seg[0].w;
+    long long tb = P.seg[0].tile_bytes;
+    int t0 = 0;
+    if (sidx == 1) { w = P.seg[1].w; tb = P.seg[1].tile_bytes; t0 = P.seg[1].tile0; }
+    if (sidx == 2) { w = P.seg[2].w; tb = P.seg[2].tile_bytes; t0 = P.seg[2].tile0; }
+    const int tile = P.nmat == 2 ? item : item - t0;
+    return w + (size_t)tile * tb;
+}
 
 // ---------------------------------------------------------------------------------------------
 // Work split.  A block of threads owns `n_local` consecutive items starting at `i0`; they are processed in waves
 // of WAVE items, and the wave's sequence of (item, matrix, step) units is cut into WARPS equal pieces.  A cursor
-// walks one warp's piece; the consumer and the ring producer (which runs `nstage` units ahead) each have one.
-// Everything here is division-free: it runs at every phase change, out of a cold instruction cache.
+// walks one warp's piece run by run (a run = consecutive steps of one (item, matrix)); the consumer and the ring
+// producer (which is `nstage` units ahead) each have one.  Division-free.
 // ---------------------------------------------------------------------------------------------
 struct Split {
     int i0, n_local, n_waves, upi, nsteps, nmat;
 };
-__device__ __forceinline__ Split make_split(const ProgGeom& g) {
+__device__ __forceinline__ Split make_split(const GemvParams& P) {
     Split s;
     const int b = (int)blockIdx.x;
-    s.i0 = b * g.items_base + min(b, g.items_rem);
-    s.n_local = g.items_base + (b < g.items_rem ? 1 : 0);
+    s.i0 = b * P.items_base + min(b, P.items_rem);
+    s.n_local = P.items_base + (b < P.items_rem ? 1 : 0);
     s.n_waves = (s.n_local + WAVE - 1) / WAVE;
-    s.nsteps = g.nsteps;
-    s.nmat = g.nmat;
-    s.upi = g.nsteps * g.nmat;
+    s.nsteps = P.nsteps;
+    s.nmat = P.nmat;
+    s.upi = P.nsteps * P.nmat;
     return s;
 }
 struct Cursor {
-    int wave, u, u1, li, mat, step;
+    int wave, li, mat, step;
+    int left;  // units of the piece not yet walked
 };
 // Position the cursor on this warp's piece of wave `c.wave`.
 __device__ __forceinline__ void cursor_wave(Cursor& c, const Split& s, int warp) {
     const int items = min(WAVE, s.n_local - c.wave * WAVE);
     const int U = items * s.upi;
-    c.u = (U * warp) / WARPS;
-    c.u1 = (U * (warp + 1)) / WARPS;
-    int rem = c.u;
+    const int u0 = (U * warp) / WARPS;
+    c.left = (U * (warp + 1)) / WARPS - u0;
+    int rem = u0;
     c.li = 0;
     while (rem >= s.upi) {  // at most WAVE rounds
         rem -= s.upi;
@@ -477,7 +469,7 @@ __device__ __forceinline__ void cursor_wave(Cursor& c, const Split& s, int warp)
     }
     c.step = rem;
 }
-// After the last step of a (item, matrix) run: first step of the next one.
+// After the last step of a run: first step of the next (item, matrix).
 __device__ __forceinline__ void cursor_next_run(Cursor& c, const Split& s) {
     c.step = 0;
     if (s.nmat == 2 && c.mat == 0) {
@@ -489,120 +481,133 @@ __device__ __forceinline__ void cursor_next_run(Cursor& c, const Split& s) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Per-warp ring state and the producer that walks the program.
+// Per-warp ring.  A stage is STRIDE bytes: one tile-step block and, in its last 8 bytes, the mbarrier its bulk copy
+// completes on.  The warp that consumes a stage refills it at once with the block `nstage` units further down its
+// sequence.  Stage size and barrier offset are compile-time constants of the format, and the request is one
+// predicated instruction sequence (no divergent branch), so the common path is a handful of instructions; run and
+// wave changes are off that path.
 // ---------------------------------------------------------------------------------------------
+template <class F>
+struct RingGeom {
+    static constexpr uint32_t STEP = F::STEP_BYTES;
+    static constexpr uint32_t STRIDE = (STEP + 8 + 127) & ~127u;
+    static constexpr uint32_t MBAR = STRIDE - 8;
+};
 struct Ring {
-    uint32_t mbar, ring;      // shared-space addresses of this warp's barriers and stages
-    int nstage;
-    uint32_t stage_stride, step_bytes;
-    int c_stage;
+    uint32_t base, end;       // shared-space addresses of this warp's stages [base, end)
+    uint32_t c_addr;          // stage consumed next
     uint32_t c_phase;
-    bool alive;
+    uint32_t lane0;           // 1 in the lane that requests the copies
+    unsigned int limit;       // polls a wait may take; 1 after a wait has expired (later waits give up at once)
     unsigned int* err_flag;
-    unsigned int wait_limit;
     // producer
-    int p_idx, p_stage;
-    Split ps;
     Cursor pc;
+    int p_run;                // units left in the producer's run (<= 0: nothing more to request)
     const uint8_t* p_ptr;
 };
 
-// Shared-memory layout: [staged vector: dig_region bytes = zero page, digit planes, digit sums][red RED_FLOATS f32][stat 64 f32][mbar][ring]
+// Shared-memory layout: [staged vector: dig_region bytes = zero page, digit planes, digit sums][red RED_FLOATS f32][stat 64 f32][ring]
 __device__ __forceinline__ uint32_t smem_fixed_bytes(int dig_region) { return (uint32_t)dig_region + RED_FLOATS * 4 + 64 * 4; }
 
-template <class Prog>
-__device__ __forceinline__ void prod_point(Ring& R, const Prog& prog) {  // address of the cursor's unit
-    if (R.pc.u < R.pc.u1)
-        R.p_ptr = prog.tile_ptr(R.p_idx, R.ps.i0 + R.pc.wave * WAVE + R.pc.li, R.pc.mat) + (size_t)R.pc.step * R.step_bytes;
-}
-// Issue the copy of the next block of this warp's sequence (if any) into the next ring stage.
-template <class Prog>
-__device__ __forceinline__ void prod_issue(Ring& R, const Prog& prog, int lane, int warp) {
-    while (R.p_idx < prog.size() && R.pc.u >= R.pc.u1) {  // piece exhausted: next wave, else next program entry
-        if (++R.pc.wave >= R.ps.n_waves) {
-            if (++R.p_idx >= prog.size()) break;
-            R.ps = make_split(prog.geom(R.p_idx));
-            R.pc.wave = 0;
-            if (R.ps.n_waves == 0) {
-                R.pc.u = R.pc.u1 = 0;
-                continue;
-            }
-        }
-        cursor_wave(R.pc, R.ps, warp);
-        prod_point(R, prog);
-    }
-    if (R.p_idx >= prog.size()) return;
-    if (lane == 0) {
-        const uint32_t mb = R.mbar + 8 * R.p_stage;
-        mbar_expect_tx(mb, R.step_bytes);
-        bulk_g2s(R.ring + R.p_stage * R.stage_stride, R.p_ptr, R.step_bytes, mb);
-    }
-    if (++R.p_stage == R.nstage) R.p_stage = 0;
-    R.p_ptr += R.step_bytes;
-    if (++R.pc.u < R.pc.u1 && ++R.pc.step == R.ps.nsteps) {  // next (item, matrix)
-        cursor_next_run(R.pc, R.ps);
-        prod_point(R, prog);
+// Bounded wait for the phase `parity` of the barrier at `a`.  On expiry the error flag is raised and `limit` drops to
+// one poll, so that the kernel still ends quickly.
+__device__ __forceinline__ void ring_wait(uint32_t a, uint32_t parity, unsigned int& limit, unsigned int* err_flag) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .u32 n;\n\tmov.u32 n, 0;\n"
+        "W:\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t@p bra D;\n\tadd.u32 n, n, 1;\n\tsetp.lt.u32 p, n, %3;\n\t@p bra W;\n\t"
+        "mov.u32 %0, 0;\n\tbra E;\n"
+        "D:\n\tmov.u32 %0, 1;\n"
+        "E:\n\t}"
+        : "=r"(ok)
+        : "r"(a), "r"(parity), "r"(limit)
+        : "memory");
+    if (!ok) {
+        atomicExch(err_flag, 1u);
+        limit = 1;
     }
 }
 
-// Set up the ring of this warp (all program entries share the ring geometry) and start the stream: the first
-// `nstage` blocks are requested here.
-template <class Prog>
-__device__ __forceinline__ void ring_init(Ring& R, const Prog& prog, int dig_region, int nstage, int stage_stride, int step_bytes,
-                                          unsigned int* err_flag, unsigned int wait_limit, unsigned char* smem_raw, int lane, int warp,
-                                          unsigned long long* trace = nullptr) {
+template <class F>
+__device__ __forceinline__ void prod_run(Ring& R, const GemvParams& P, const Split& sp) {
+    R.p_run = min(R.pc.left, sp.nsteps - R.pc.step);
+    R.pc.left -= R.p_run;
+    R.p_ptr = tile_ptr(P, sp.i0 + R.pc.wave * WAVE + R.pc.li, R.pc.mat) + (size_t)R.pc.step * RingGeom<F>::STEP;
+}
+// First non-empty piece from wave `pc.wave` on.
+template <class F>
+__device__ __forceinline__ void prod_open(Ring& R, const GemvParams& P, const Split& sp, int warp) {
+    R.p_run = 0;
+    for (; R.pc.wave < sp.n_waves; R.pc.wave++) {
+        cursor_wave(R.pc, sp, warp);
+        if (R.pc.left > 0) {
+            prod_run<F>(R, P, sp);
+            return;
+        }
+    }
+}
+template <class F>
+__device__ __forceinline__ void prod_advance(Ring& R, const GemvParams& P, const Split& sp, int warp) {
+    if (R.pc.left > 0) {
+        cursor_next_run(R.pc, sp);
+        prod_run<F>(R, P, sp);
+    } else {
+        R.pc.wave++;
+        prod_open<F>(R, P, sp, warp);
+    }
+}
+// Request the next block of the warp's sequence (if any) into the stage at `stage` (which this warp has finished
+// reading: the proxy fence orders those reads before the asynchronous write).
+template <class F>
+__device__ __forceinline__ void prod_step(Ring& R, const GemvParams& P, const Split& sp, uint32_t stage, int warp) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.gt.s32 p, %0, 0;\n\tsetp.ne.and.u32 p, %1, 0, p;\n\t"
+        "@p fence.proxy.async.shared::cta;\n\t"
+        "@p mbarrier.arrive.expect_tx.shared::cta.b64 _, [%2+%5], %4;\n\t"
+        "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%2], [%3], %4, [%2+%5];\n\t}"
+        :
+        : "r"(R.p_run), "r"(R.lane0), "r"(stage), "l"(R.p_ptr), "n"(RingGeom<F>::STEP), "n"(RingGeom<F>::MBAR)
+        : "memory");
+    R.p_ptr += RingGeom<F>::STEP;
+    if (--R.p_run == 0) prod_advance<F>(R, P, sp, warp);
+}
+
+// Barriers of this warp's ring; nothing is requested yet.
+template <class F>
+__device__ __forceinline__ void ring_setup(Ring& R, const GemvParams& P, unsigned char* smem_raw, int lane, int warp) {
     const uint32_t base = (uint32_t)__cvta_generic_to_shared(smem_raw);
-    const uint32_t mbar_base = base + smem_fixed_bytes(dig_region);
-    const uint32_t ring_base = (mbar_base + WARPS * MAX_STAGES * 8 + 127u) & ~127u;
-    R.nstage = nstage;
-    R.stage_stride = stage_stride;
-    R.step_bytes = step_bytes;
-    R.mbar = mbar_base + warp * MAX_STAGES * 8;
-    R.ring = ring_base + warp * R.nstage * R.stage_stride;
-    R.c_stage = 0;
+    const uint32_t ring_base = (base + smem_fixed_bytes(P.dig_region) + 127u) & ~127u;
+    R.base = ring_base + warp * P.nstage * RingGeom<F>::STRIDE;
+    R.end = R.base + P.nstage * RingGeom<F>::STRIDE;
+    R.c_addr = R.base;
     R.c_phase = 0;
-    R.alive = true;
-    R.err_flag = err_flag;
-    R.wait_limit = wait_limit;
-    R.p_stage = 0;
+    R.lane0 = lane == 0 ? 1u : 0u;
+    R.limit = P.wait_limit;
+    R.err_flag = P.err_flag;
+    R.p_run = 0;
     R.p_ptr = nullptr;
     if (lane == 0) {
-        for (int s = 0; s < R.nstage; s++) mbar_init(R.mbar + 8 * s, 1);
+        for (uint32_t a = R.base; a < R.end; a += RingGeom<F>::STRIDE) mbar_init(a + RingGeom<F>::MBAR, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncwarp();
-#ifdef SLAI_TRACE
-    if (threadIdx.x == 0 && trace) trace[blockIdx.x * TRACE_POINTS + 1] = slai_globaltimer();
-#endif
-    // park the producer "before" entry 0 with an exhausted piece: the first prod_issue walks into it
-    R.p_idx = -1;
-    R.ps.n_waves = 0;
-    R.ps.nsteps = 1;
-    R.ps.nmat = 1;
-    R.ps.upi = 1;
-    R.ps.i0 = R.ps.n_local = 0;
+}
+// Start the stream: the first `nstage` blocks of the warp's sequence.
+template <class F>
+__device__ __forceinline__ void ring_fill(Ring& R, const GemvParams& P, const Split& sp, int warp) {
     R.pc.wave = 0;
-    R.pc.u = R.pc.u1 = 0;
-    R.pc.li = R.pc.mat = R.pc.step = 0;
+    prod_open<F>(R, P, sp, warp);
 #pragma unroll 1
-    for (int s = 0; s < R.nstage; s++) prod_issue(R, prog, lane, warp);
-#ifdef SLAI_TRACE
-    if (threadIdx.x == 0 && trace) trace[blockIdx.x * TRACE_POINTS + 2] = slai_globaltimer();
-#endif
+    for (uint32_t a = R.base; a < R.end; a += RingGeom<F>::STRIDE) prod_step<F>(R, P, sp, a, warp);
 }
 
 // ---------------------------------------------------------------------------------------------
-// One GEMV phase (consumer side).
+// The GEMV after the predecessor's results are visible: stage the vector, main loop, epilogue.
 // ---------------------------------------------------------------------------------------------
-// NMAT (1, or 2 for the gate/up pair), PRO and EPI are compile-time constants in the stand-alone kernels (the
-// function is inlined and the branches fold) and run-time values in the persistent decode kernel, which keeps ONE
-// copy of this code for all its phases so that it stays in the instruction cache from layer to layer.
-// PRO_MASK / EPI_MASK: bit i set = value i can occur (code for the others is not generated).
-template <class F, int PRO_MASK, int EPI_MASK, bool XIN = false, class Prog>
-__device__ __forceinline__ void gemv_phase(const GemvParams& P, Ring& R, const Prog& prog, unsigned char* smem_raw,
-                                           const int NMAT, const int PRO, const int EPI, const bool red_cleared = false) {
-#define SLAI_EPI_IS(x) ((((EPI_MASK) >> (x)) & 1) && EPI == (x))
+template <class F, int NMAT, int PRO, int EPI, bool XIN>
+__device__ __forceinline__ void gemv_body(const GemvParams& P, Ring& R, const Split& sp, unsigned char* smem_raw) {
+#define SLAI_EPI_IS(x) (EPI == (x))
     const int K = P.K;
     const int Kp = (K + 255) & ~255;
     Smem S;
@@ -617,12 +622,8 @@ __device__ __forceinline__ void gemv_phase(const GemvParams& P, Ring& R, const P
     LaneCtx L;
     lane_init<F>(L, tid & 31, S);
 
-    const Split sp = make_split(ProgGeom{P.nsteps, NMAT, P.items_base, P.items_rem});
-
-    if (!red_cleared)
-        for (int i = tid; i < WAVE * WARPS * NMAT * 16; i += THREADS) red[i] = 0.f;
     SLAI_TRACE_POINT(5)
-    const float inv_scale = stage_vector<F::SV_GRAN, ((PRO_MASK >> PRO_LN) & 1) != 0, XIN>(PRO, P, S, stat, Kp);
+    const float inv_scale = stage_vector<F::SV_GRAN, PRO == PRO_LN, XIN>(PRO, P, S, stat, Kp);
     SLAI_TRACE_POINT(9)
 
     Cursor c;
@@ -649,22 +650,23 @@ __device__ __forceinline__ void gemv_phase(const GemvParams& P, Ring& R, const P
             }
         }
         cursor_wave(c, sp, warp);
-        while (c.u < c.u1) {
-            // one run of consecutive steps inside the same (item, matrix)
-            const int run_end = min(c.u1, c.u + (sp.nsteps - c.step));
+        while (c.left > 0) {
+            const int run = min(c.left, sp.nsteps - c.step);
             float accA = 0.f, accB = 0.f;
+            int step = c.step;
 #pragma unroll 1
-            for (; c.u < run_end; c.u++, c.step++) {
-                if (R.alive) R.alive = mbar_wait(R.mbar + 8 * R.c_stage, R.c_phase, R.wait_limit, R.err_flag);
-                F::compute(R.ring + R.c_stage * R.stage_stride, c.step, L, S, accA, accB);
+            for (int i = run; i > 0; i--, step++) {
+                ring_wait(R.c_addr + RingGeom<F>::MBAR, R.c_phase, R.limit, R.err_flag);
+                F::compute(R.c_addr, step, L, S, accA, accB);
                 __syncwarp();
-                if (L.lane == 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                prod_issue(R, prog, L.lane, warp);  // refill the stage just consumed
-                if (++R.c_stage == R.nstage) {
-                    R.c_stage = 0;
+                prod_step<F>(R, P, sp, R.c_addr, warp);  // refill the stage just consumed
+                R.c_addr += RingGeom<F>::STRIDE;
+                if (R.c_addr == R.end) {
+                    R.c_addr = R.base;
                     R.c_phase ^= 1;
                 }
             }
+            c.left -= run;
             accA += __shfl_xor_sync(0xffffffffu, accA, 1);
             accA += __shfl_xor_sync(0xffffffffu, accA, 2);
             accB += __shfl_xor_sync(0xffffffffu, accB, 1);

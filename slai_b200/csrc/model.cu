@@ -47,12 +47,13 @@ void destroy_graphs(GraphSet& g) {
     for (int i = 0; i < G_COUNT; i++) g.warmed[i] = false;
 }
 
-// Bytes of later weights one kernel asks for ahead of time (PrefetchPlan).  SLAI_AHEAD_MB=0 switches the scheme off.
+// Bytes of later weights one kernel asks for ahead of time (PrefetchPlan).  Off unless SLAI_AHEAD_MB is set: the main
+// loop consumes no faster from L2 than from HBM, so requests issued ahead only lengthen the hand-over (measured).
 size_t ahead_cap_bytes() {
     static long long cap = -1;
     if (cap < 0) {
         const char* e = getenv("SLAI_AHEAD_MB");
-        cap = (e ? atoll(e) : 32) << 20;
+        cap = (e ? atoll(e) : 0) << 20;
     }
     return (size_t)cap;
 }
@@ -136,12 +137,6 @@ struct slai_llama {
     void* pf_attn_scratch = nullptr;
     size_t pf_attn_scratch_bytes = 0;
     unsigned int* pf_tickets = nullptr;
-    // fused path: all layers in one persistent kernel (decode.cu)
-    int fused_state = 0;  // 0 not prepared, 1 ready, -1 not eligible
-    int fused_fmt = 0;
-    DecodeLayersPlan plan;
-    DecodeParams* dparams = nullptr;  // parameter block of the persistent kernel (host copy, passed by value at launch)
-    float *f_part_o = nullptr, *f_part_ml = nullptr;
 };
 
 static void llama_drop_prefill(slai_llama* m) {
@@ -155,80 +150,6 @@ static void llama_drop_prefill(slai_llama* m) {
     m->pf_attn_scratch_bytes = 0;
     m->pf_tickets = nullptr;
     m->pf_cap = 0;
-}
-
-static void llama_drop_fused(slai_llama* m) {
-    if (m->f_part_o || m->f_part_ml) cudaStreamSynchronize(m->ctx->stream);
-    cudaFree(m->f_part_o); cudaFree(m->f_part_ml);
-    delete m->dparams;
-    m->dparams = nullptr;
-    m->f_part_o = m->f_part_ml = nullptr;
-    m->fused_state = 0;
-}
-
-// Describes the model to the persistent decode kernel when every layer matrix has the same quantised format.
-static int llama_prepare_fused(slai_llama* m) {
-    slai_ctx* ctx = m->ctx;
-    const slai_llama_config& c = m->cfg;
-    m->fused_state = -1;
-    // Opt-in (SLAI_FUSED=1): at batch 1 on a 7B model the five-kernels-per-layer path is the faster one (its
-    // kernels are specialised at compile time and overlap through programmatic dependent launch).
-    const char* nf = getenv("SLAI_FUSED");
-    if (!(nf && nf[0] == '1')) return SLAI_OK;
-    if (c.rope_variant != 0 || m->kv_mul > 8 || c.n_layers > DECODE_MAX_LAYERS || m->tp > 1) return SLAI_OK;
-    const int fmt = m->layers[0].wq ? m->layers[0].wq->fmt : 0;
-    if (fmt != SLAI_FMT_Q4_K && fmt != SLAI_FMT_Q5_K && fmt != SLAI_FMT_Q6_K && fmt != SLAI_FMT_Q8_0) return SLAI_OK;
-    for (auto& w : m->layers) {
-        const slai_qmatrix* ms[7] = {w.wq, w.wk, w.wv, w.wo, w.wgate, w.wup, w.wdown};
-        for (auto* q : ms)
-            if (!q || q->fmt != fmt) return SLAI_OK;
-        if (!w.attn_norm || !w.ffn_norm) return SLAI_OK;
-    }
-    DecodeLayersDesc desc{fmt, c.dim, c.hidden_dim, c.n_q_heads, m->kv_mul, m->head_size, c.seq_len, c.kv_dtype == SLAI_KV_F16};
-    cudaGetLastError();
-    DecodeParams* D = new DecodeParams();
-    memset(D, 0, sizeof(*D));
-    m->dparams = D;
-    auto give_up = [&]() {
-        cudaGetLastError();
-        llama_drop_fused(m);
-        m->fused_state = -1;
-        return SLAI_OK;
-    };
-    if (decode_layers_prepare(ctx, desc, &m->plan, D) != SLAI_OK) return give_up();  // does not fit: keep the per-kernel path
-    if (cudaMalloc(&m->f_part_o, m->plan.part_o_bytes + 256) != cudaSuccess || cudaMalloc(&m->f_part_ml, m->plan.part_ml_bytes + 256) != cudaSuccess)
-        return give_up();
-    const size_t esz = c.kv_dtype == SLAI_KV_F16 ? 2 : 4;
-    D->n_layers = c.n_layers;
-    D->eps = c.rms_norm_eps;
-    D->rope_theta = m->rope_theta;
-    D->d_pos = m->sc.d + 1;
-    D->kv_f16 = c.kv_dtype == SLAI_KV_F16;
-    D->x = m->x; D->xb = m->xb; D->q = m->q; D->hb = m->hb;
-    D->part_o = m->f_part_o; D->part_ml = m->f_part_ml;
-    {
-        const uintptr_t bits = reinterpret_cast<uintptr_t>(m->kcache) | reinterpret_cast<uintptr_t>(m->vcache) |
-                               (uintptr_t)(m->kv_layer_elems * esz) | (uintptr_t)((size_t)c.seq_len * m->head_size * esz) |
-                               (uintptr_t)(m->head_size * esz);
-        if (bits & 3) return give_up();
-        D->vec16 = (bits & 15) == 0;
-    }
-    for (int l = 0; l < c.n_layers; l++) {
-        const LlamaLayer& w = m->layers[l];
-        const slai_qmatrix* kd[6] = {w.wq, w.wk, w.wv, w.wo, w.wgate, w.wup};
-        for (auto* q : kd)
-            if (q->tile_bytes != D->tile_bytes_dim) return give_up();
-        if (w.wdown->tile_bytes != D->tile_bytes_hidden) return give_up();
-        DecodeLayerPtrs& P = D->layer[l];
-        P.wq = w.wq->data; P.wk = w.wk->data; P.wv = w.wv->data; P.wo = w.wo->data;
-        P.wgate = w.wgate->data; P.wup = w.wup->data; P.wdown = w.wdown->data;
-        P.attn_norm = w.attn_norm; P.ffn_norm = w.ffn_norm; P.bq = w.bq; P.bk = w.bk; P.bv = w.bv;
-        P.kcache = (char*)m->kcache + (size_t)l * m->kv_layer_elems * esz;
-        P.vcache = (char*)m->vcache + (size_t)l * m->kv_layer_elems * esz;
-    }
-    m->fused_fmt = fmt;
-    m->fused_state = 1;
-    return SLAI_OK;
 }
 
 static int llama_record(slai_llama* m, int kind) {
@@ -298,12 +219,7 @@ static int llama_record(slai_llama* m, int kind) {
         n += 2;
         return SLAI_OK;
     };
-    if (m->fused_state == 1) {
-        // all layers in one persistent kernel
-        if ((rc = decode_layers_launch(ctx, *m->dparams, m->plan))) return rc;
-        n += 2;  // barrier reset + kernel
-    }
-    for (int l = 0; l < (m->fused_state == 1 ? 0 : c.n_layers); l++) {
+    for (int l = 0; l < c.n_layers; l++) {
         const LlamaLayer& w = m->layers[l];
         SLAI_REQUIRE(ctx, w.wq && w.wk && w.wv && w.wo && w.wgate && w.wup && w.wdown && w.attn_norm && w.ffn_norm,
                      SLAI_ERR_INVALID_ARG, "llama: layer %d has unset weights", l);
@@ -503,16 +419,10 @@ static int llama_record(slai_llama* m, int kind) {
     return SLAI_OK;
 }
 
-static int model_prepare(slai_llama* m) { return m->fused_state == 0 ? llama_prepare_fused(m) : SLAI_OK; }
-static int model_prepare(struct slai_gpt2*) { return SLAI_OK; }
 
 template <class M, class RecordFn>
 static int run_graph(M* m, int kind, RecordFn record) {
     slai_ctx* ctx = m->ctx;
-    {
-        int rc = model_prepare(m);
-        if (rc) return rc;
-    }
     if (!m->graphs.use_graph) return record(m, kind);
     if (!m->graphs.warmed[kind]) {
         m->graphs.warmed[kind] = true;
@@ -607,7 +517,6 @@ SLAI_API int slai_llama_destroy(slai_llama* m) {
     SLAI_ENTER(m->ctx);
     cudaStreamSynchronize(m->ctx->stream);
     destroy_graphs(m->graphs);
-    llama_drop_fused(m);
     llama_drop_prefill(m);
     for (auto& l : m->layers) {
         cudaFree(l.attn_norm); cudaFree(l.ffn_norm); cudaFree(l.bq); cudaFree(l.bk); cudaFree(l.bv);
@@ -627,7 +536,6 @@ SLAI_API int slai_llama_set_matrix(slai_llama* m, int id, int layer, const slai_
     slai_ctx* ctx = m->ctx;
     const slai_llama_config& c = m->cfg;
     destroy_graphs(m->graphs);
-    llama_drop_fused(m);
     auto shape_is = [&](int64_t r, int64_t k) { return w->nrows == r && w->ncols == k; };
     if (id == SLAI_W_OUTPUT) {
         // tensor parallel: either the whole matrix on every rank, or this rank's vocab / tp consecutive rows (the
@@ -666,7 +574,6 @@ static int llama_set_f32_impl(slai_llama* m, int id, int layer, const float* dat
     slai_ctx* ctx = m->ctx;
     const slai_llama_config& c = m->cfg;
     destroy_graphs(m->graphs);
-    llama_drop_fused(m);
     if (id == SLAI_W_TOKEN_EMBD) {
         SLAI_REQUIRE(ctx, n == (int64_t)c.vocab_size * c.dim, SLAI_ERR_SHAPE, "llama: token_embd needs vocab*dim floats");
         int rc = copy_f32(ctx, &m->token_embd, data, n, dev);

@@ -21,7 +21,7 @@ import sys
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-TRACE_LIB = os.path.join(_HERE, "libslai_b200_trace.so")
+TRACE_LIB = os.environ.get("SLAI_B200_TRACE_LIB") or os.path.join(_HERE, "libslai_b200_trace.so")
 
 PRO = {0: "", 1: "rms+", 2: "ln+"}
 EPI = {0: "store", 1: "resid", 2: "silu", 3: "gelu", 4: "qkv", 5: "xchg"}
@@ -38,7 +38,7 @@ def kernel_name(kid: int) -> str:
 
 SLOTS, CAP = 16, 4096
 # Stamps of a GEMV launch (block 0), see common.cuh: the columns printed are the differences between consecutive ones.
-COLS = (("init", 0, 1), ("fill", 1, 2), ("ahead", 2, 3), ("wait", 3, 4), ("clear", 4, 5), ("load", 5, 6), ("stats", 6, 7),
+COLS = (("init", 0, 1), ("fill", 1, 2), ("pre", 2, 3), ("wait", 3, 4), ("setup", 4, 5), ("load", 5, 6), ("stats", 6, 7),
         ("digits", 7, 8), ("bar", 8, 9), ("loop", 9, 10), ("sync", 10, 11), ("epi", 11, 12), ("exit", 12, 13))
 
 
@@ -89,7 +89,7 @@ def block_report(backend, nblocks):
     if rc != 0:
         raise RuntimeError(f"slai_debug_trace_ring failed ({rc})")
     ring = ring.reshape(64, 256, 16).astype(np.int64)
-    names = ["start", "init", "fill", "ahead", "waited", "clear", "loaded", "stats", "digits", "staged", "loop", "synced", "epi", "end"]
+    names = ["start", "init", "fill", "pre", "waited", "setup", "loaded", "stats", "digits", "staged", "loop", "synced", "epi", "end"]
     out = []
     for slot in range(64):
         t = ring[slot, :nblocks, :14].astype(np.float64) * 1e-3

@@ -199,8 +199,8 @@ def test_gemv_f32_matrix(backend, ctx):
 
 
 def test_errors(backend, ctx):
-    with pytest.raises(SlaiError) as e:  # legacy formats are listed in the enum but have no kernel
-        GpuQuantMatrix(backend, _lib.FMT_Q4_0, 4, 64, np.zeros(4 * 2 * 18, np.uint8))
+    with pytest.raises(SlaiError) as e:  # f16 tensors are listed in the enum but not accepted as matrices
+        GpuQuantMatrix(backend, _lib.FMT_F16, 4, 64, np.zeros(4 * 64 * 2, np.uint8))
     assert e.value.code == _lib.ERR_UNSUPPORTED_FORMAT
     with pytest.raises(SlaiError) as e:
         GpuQuantMatrix(backend, synth.FMT_Q4_K, 4, 300, np.zeros(4 * 144, np.uint8))

@@ -92,39 +92,6 @@ def test_small_llama_logits_and_tokens(backend, fmt, out_fmt, kv_dtype):
     assert n_match > 10
 
 
-@pytest.mark.parametrize("fmt,kv_dtype,heads", [(synth.FMT_Q4_K, _lib.KV_F16, (8, 8)), (synth.FMT_Q8_0, _lib.KV_F32, (8, 2)),
-                                                 (synth.FMT_Q6_K, _lib.KV_F16, (8, 1))])
-def test_persistent_decode_kernel_matches_oracle_and_per_kernel_path(backend, monkeypatch, fmt, kv_dtype, heads):
-    """SLAI_FUSED=1: all layers of a token in one persistent kernel (grid barriers, one weight stream).  Same logits
-    as the oracle within 1e-3 and the same greedy ids as the five-kernels-per-layer path, across a context long
-    enough for several attention tiles and splits."""
-    cfg = Llama2Config(dim=512, hidden_dim=1280, n_layers=3, n_q_heads=heads[0], n_kv_heads=heads[1], vocab_size=2000, seq_len=160,
-                       kv_dtype=kv_dtype)
-    w = synthetic_llama_host(cfg, fmt, fmt, seed=5, std=0.05, embd_std=1.0)
-    plain = llama_from_host(backend, cfg, w, fmt, fmt)
-    monkeypatch.setenv("SLAI_FUSED", "1")
-    fused = llama_from_host(backend, cfg, w, fmt, fmt)
-    ref = oracle_llama(cfg, w, fmt, fmt, kv_f16=(kv_dtype == _lib.KV_F16))
-    tok = 7
-    for pos in range(6):
-        lg, nxt = fused.forward_logits(pos, tok)
-        assert fused.launches_per_token() < plain_launches(cfg), "the persistent kernel did not run"
-        rl = ref.forward(tok, pos)
-        assert rel_l2(lg, rl) < 1e-3, pos
-        lg2, _ = plain.forward_logits(pos, tok)
-        assert rel_l2(lg, lg2) < 1e-4
-        tok = O.argmax(rl)
-    monkeypatch.delenv("SLAI_FUSED")
-    a = fused.generate(tok, 6, 150)
-    b = plain.generate(tok, 6, 150)
-    assert list(a) == list(b)
-    assert backend_error_flag(backend) == 0
-
-
-def plain_launches(cfg):
-    return 5 * cfg.n_layers  # embed + 5 per layer + logits + argmax + advance on the per-kernel path
-
-
 def backend_error_flag(backend):
     """Bounded waits inside the kernels raise a device flag instead of hanging; slai_ctx_sync reports it."""
     return backend.lib.slai_ctx_sync(backend.h)
