@@ -65,6 +65,9 @@ int launch_inst(slai_ctx* ctx, const GemvParams& P, int grid, size_t smem, bool 
     static PerDeviceOnce attr;  // per instantiation
     if (attr.need(ctx->device)) {
         SLAI_CHECK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT));
+        // One shared-memory carve-out for every launch whatever its ring and vector sizes: an SM changes its carve-out
+        // only when idle, which would hold back the blocks of the next kernel.
+        SLAI_CHECK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         attr.set(ctx->device);
     }
     cudaLaunchConfig_t cfg = {};

@@ -179,7 +179,13 @@ SLAI_HD void lane_init(LaneCtx& L, int lane, const Smem& S) {
 }
 
 SLAI_HD float combine(int p0, int p1, const LaneCtx& L) { return prim::fma((float)p1, L.wd1, (float)p0 * L.wd0); }
-SLAI_HD uint32_t byte_of(uint32_t w, int i) { return (w >> (8 * i)) & 0xFFu; }
+SLAI_HD uint32_t byte_of(uint32_t w, int i) {
+#ifdef __CUDA_ARCH__
+    return __byte_perm(w, 0u, 0x4440u | (uint32_t)i);  // one instruction
+#else
+    return (w >> (8 * i)) & 0xFFu;
+#endif
+}
 
 // Every format provides
 //   STEP      elements of K per tile-step block          SV_GRAN  elements per digit-sum entry (0: none)

@@ -292,8 +292,8 @@ __device__ __forceinline__ float stage_vector(const int PRO_ARG, const GemvParam
             mx = fmaxf(mx, max4(make_float4(x.x * w.x, x.y * w.y, x.z * w.z, x.w * w.w)));
         }
     };
+    float4 wr[STAGE_REGS];  // norm weights of the register copy: all requested before the first is used, kept for the digit pass
     if (cached) {
-        float4 wr[STAGE_REGS];  // norm weights: all requested before the first is used
 #pragma unroll
         for (int r = 0; r < STAGE_REGS; r++) {
             const int i = tid + r * THREADS;
@@ -333,9 +333,8 @@ __device__ __forceinline__ float stage_vector(const int PRO_ARG, const GemvParam
     if (tid < ZERO_BYTES / 4) reinterpret_cast<uint32_t*>(__cvta_shared_to_generic(S.zero))[tid] = 0u;
     // One float4 (elements 4i .. 4i+3): normalise, round to integers, digits, sums.  np4 is a multiple of 64, so whole
     // warps take part in every call (the sums are reduced with shuffles).
-    auto convert = [&](float4 x, const int i) {
+    auto convert = [&](float4 x, const float4& w, const int i) {
         if (i < n4 && PRO != PRO_NONE) {
-            const float4 w = __ldg(w4p + i);  // L1 hit: the statistics pass has read it
             if (HAS_LN && PRO == PRO_LN) { x.x -= sub; x.y -= sub; x.z -= sub; x.w -= sub; }
             x.x = (x.x * mul) * w.x; x.y = (x.y * mul) * w.y; x.z = (x.z * mul) * w.z; x.w = (x.w * mul) * w.w;
             if (HAS_LN && PRO == PRO_LN && P.norm_b) {
@@ -384,10 +383,11 @@ __device__ __forceinline__ float stage_vector(const int PRO_ARG, const GemvParam
     if (cached) {
 #pragma unroll
         for (int r = 0; r < STAGE_REGS; r++)
-            if (tid + r * THREADS < np4) convert(xr[r], tid + r * THREADS);  // independent rounds: the compiler overlaps them
+            if (tid + r * THREADS < np4) convert(xr[r], wr[r], tid + r * THREADS);  // independent rounds: the compiler overlaps them
     } else {
 #pragma unroll 1
-        for (int i = tid; i < np4; i += THREADS) convert(i < n4 ? __ldcg(v4 + i) : zero4, i);
+        for (int i = tid; i < np4; i += THREADS)
+            convert(i < n4 ? __ldcg(v4 + i) : zero4, (PRO != PRO_NONE && i < n4) ? __ldg(w4p + i) : zero4, i);
     }
     SLAI_TRACE_POINT(8)
     __syncthreads();
