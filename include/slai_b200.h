@@ -299,6 +299,19 @@ int slai_llama_read_state(slai_llama* m, int which, float* h_out, int64_t n);
 /* Test access to the KV cache of one layer: positions 0..n_pos as f32, position-major like the reference's cache
  * (h_keys / h_values: n_pos x kv_dim floats).  Blocking. */
 int slai_llama_read_kv(slai_llama* m, int layer, int n_pos, float* h_keys, float* h_values);
+/* Where a decode step spends its device time.  Classes (index of `us` / `launches`): 0 everything else (embedding,
+ * rotation, sampling, collectives, gaps between kernels), 1 norm + q/k/v GEMV + RoPE + cache append, 2 attention,
+ * 3 output projection + residual, 4 norm + gate/up GEMV + SiLU, 5 down projection + residual, 6 final norm + logits
+ * GEMV.  The step runs once outside the replayed graph, kernel after kernel (no overlap between launches), with events
+ * around each launch: the sum is therefore larger than the time of a replayed step; the split is what it is for.  It
+ * is a real step: position `pos` of the KV cache is written.  Replaces reading the reference's per-dispatch GPU
+ * timestamps (crates/slai/src/models/llama2/transformer.rs:316-381 runs each operator as its own dispatch). */
+typedef struct slai_llama_stats_t {
+    float us_total;
+    float us[7];
+    int32_t launches[7];
+} slai_llama_stats_t;
+int slai_llama_stats(slai_llama* m, int32_t token, int32_t pos, slai_llama_stats_t* out);
 /* Number of kernel launches issued for the last decoded token. */
 int slai_llama_launches_per_token(const slai_llama* m);
 

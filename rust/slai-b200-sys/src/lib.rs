@@ -26,6 +26,11 @@ pub struct slai_attn_params { pub seq_len: u32, pub kv_dim: u32, pub kv_mul: u32
 pub struct slai_llama_config { pub dim: i32, pub hidden_dim: i32, pub n_layers: i32, pub n_q_heads: i32, pub n_kv_heads: i32, pub vocab_size: i32,
     pub seq_len: i32, pub rope_base_freq: f32, pub rms_norm_eps: f32, pub rope_variant: i32, pub kv_dtype: i32, pub tp_rank: i32, pub tp_size: i32 }
 
+/// Device time of one decode step per kernel class (see `slai_llama_stats` in the C header).
+#[repr(C)]
+#[derive(Copy, Clone, Debug, Default)]
+pub struct slai_llama_stats_t { pub us_total: f32, pub us: [f32; 7], pub launches: [i32; 7] }
+
 /// `Gpt2Params` (crates/slai/src/models/gpt2/cpu.rs:19-35).
 #[repr(C)]
 #[derive(Copy, Clone, Debug)]
@@ -99,6 +104,7 @@ extern "C" {
     pub fn slai_llama_prefill(m: *mut slai_llama, h_tokens: *const i32, n: i32, pos0: i32, h_last_logits: *mut f32) -> i32;
     pub fn slai_llama_read_state(m: *mut slai_llama, which: i32, h_out: *mut f32, n: i64) -> i32;
     pub fn slai_llama_read_kv(m: *mut slai_llama, layer: i32, n_pos: i32, h_keys: *mut f32, h_values: *mut f32) -> i32;
+    pub fn slai_llama_stats(m: *mut slai_llama, token: i32, pos: i32, out: *mut slai_llama_stats_t) -> i32;
     pub fn slai_llama_launches_per_token(m: *const slai_llama) -> i32;
     pub fn slai_gpt2_create(ctx: *mut slai_ctx, cfg: *const slai_gpt2_config, out: *mut *mut slai_gpt2) -> i32;
     pub fn slai_gpt2_destroy(m: *mut slai_gpt2) -> i32;

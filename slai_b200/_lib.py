@@ -40,6 +40,12 @@ class LlamaConfig(C.Structure):
                 ("kv_dtype", C.c_int32), ("tp_rank", C.c_int32), ("tp_size", C.c_int32)]
 
 
+class LlamaStats(C.Structure):
+    """`slai_llama_stats_t`: microseconds and launches per kernel class of one decode step."""
+    CLASSES = ("other", "qkv", "attention", "wo", "gate_up", "down", "logits")
+    _fields_ = [("us_total", C.c_float), ("us", C.c_float * 7), ("launches", C.c_int32 * 7)]
+
+
 class Gpt2Config(C.Structure):
     _fields_ = [("n_vocab", C.c_int32), ("n_seq", C.c_int32), ("n_embd", C.c_int32), ("n_head", C.c_int32),
                 ("n_layer", C.c_int32), ("ff_len", C.c_int32), ("layernorm_eps", C.c_float), ("kv_dtype", C.c_int32)]
@@ -116,6 +122,7 @@ SIGNATURES = {
     "slai_sample": (C.c_int, [_vp, _vp, _i64, C.c_float, C.c_float, C.c_float, _vp]),
     "slai_llama_prefill": (C.c_int, [_vp, _vp, _i32, _i32, _vp]),
     "slai_llama_read_kv": (C.c_int, [_vp, C.c_int, C.c_int, _vp, _vp]),
+    "slai_llama_stats": (C.c_int, [_vp, C.c_int32, C.c_int32, _vp]),
     "slai_llama_read_state": (C.c_int, [_vp, C.c_int, _vp, _i64]),
     "slai_llama_launches_per_token": (C.c_int, [_vp]),
     "slai_gpt2_create": (C.c_int, [_vp, C.POINTER(Gpt2Config), _pp]),

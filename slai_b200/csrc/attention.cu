@@ -125,7 +125,15 @@ static int attn_geometry(slai_ctx* ctx, AttnParams& P, int kv_dtype, int n_max, 
     return SLAI_OK;
 }
 
+static int attention_launch_inner(slai_ctx* ctx, const AttnLaunch& A);
 int attention_launch(slai_ctx* ctx, const AttnLaunch& A) {
+    if (!ctx->stats_on) return attention_launch_inner(ctx, A);
+    int rc = slai_stats_mark(ctx, STATS_OTHER);
+    if (rc) return rc;
+    if ((rc = attention_launch_inner(ctx, A))) return rc;
+    return slai_stats_mark(ctx, STATS_ATTENTION);
+}
+static int attention_launch_inner(slai_ctx* ctx, const AttnLaunch& A) {
     SLAI_REQUIRE(ctx, A.kv_mul >= 1 && A.kv_mul <= 8 && A.n_heads % A.kv_mul == 0, SLAI_ERR_SHAPE,
                  "attention: kv_mul=%d must be in 1..8 and divide n_heads=%d", A.kv_mul, A.n_heads);
     SLAI_REQUIRE(ctx, A.head_size % 2 == 0 && A.head_size <= 64 * MAX_J, SLAI_ERR_SHAPE,

@@ -55,7 +55,15 @@ struct slai_ctx {
     void* xchg_region = nullptr;  // this rank's region (device memory, exported to the peers)
     bool xchg_ready = false;
     bool xchg_loopback = false;   // slai_tp_peer_loopback: the region stands in for every rank's (single-GPU testing)
+    // slai_llama_stats: while `stats_on`, the GEMV and attention launchers bracket their kernels with events
+    bool stats_on = false;
+    std::vector<cudaEvent_t> stats_ev;
+    std::vector<int> stats_cls;   // class of the interval that ends at the event of the same index (STATS_* below)
 };
+// Kernel classes of slai_llama_stats (index into slai_llama_stats_t::us).
+enum { STATS_OTHER = 0, STATS_QKV = 1, STATS_ATTENTION = 2, STATS_WO = 3, STATS_GATE_UP = 4, STATS_DOWN = 5, STATS_LOGITS = 6, STATS_CLASSES = 7 };
+// Ends an interval of class `cls` on the context's stream (no-op unless statistics are being taken).
+int slai_stats_mark(slai_ctx* ctx, int cls);
 
 // tp.cu: sum of `n` floats over the ranks of the context's group, on the context's stream
 int tp_all_reduce_sum(slai_ctx* ctx, const float* d_in, float* d_out, int64_t n);
@@ -259,6 +267,7 @@ struct GemvLaunch {
     const void* prefetch = nullptr;  // what the next kernel reads first (e.g. its norm weights): pulled into L2 meanwhile
     size_t prefetch_bytes = 0;
     PrefetchPlan ahead;              // weights of a later kernel: pulled into L2 by this one (see PrefetchPlan)
+    int stats_cls = -1;              // slai_llama_stats class of this launch (-1: derived from the epilogue)
     // tensor-parallel exchange over peer memory (null: not used)
     const PeerExchange* xchg = nullptr;
     int xchg_out_idx1 = 0;         // EPI_XCHG: index + 1 of this exchange inside the token

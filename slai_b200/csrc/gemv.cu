@@ -253,7 +253,18 @@ int gemv_fill_params(slai_ctx* ctx, const GemvLaunch& L, size_t dig_region, int 
     return SLAI_OK;
 }
 
+static int gemv_launch_inner(slai_ctx* ctx, const GemvLaunch& L);
 int gemv_launch(slai_ctx* ctx, const GemvLaunch& L) {
+    if (!ctx->stats_on) return gemv_launch_inner(ctx, L);
+    // statistics: what ran since the last mark is "other"; this kernel's class follows from its epilogue
+    int rc = slai_stats_mark(ctx, STATS_OTHER);
+    if (rc) return rc;
+    if ((rc = gemv_launch_inner(ctx, L))) return rc;
+    const int cls = L.stats_cls >= 0 ? L.stats_cls : L.epi == EPI_QKV ? STATS_QKV : L.epi == EPI_SILU ? STATS_GATE_UP
+                    : (L.epi == EPI_RESID || L.epi == EPI_XCHG) ? STATS_WO : STATS_OTHER;
+    return slai_stats_mark(ctx, cls);
+}
+static int gemv_launch_inner(slai_ctx* ctx, const GemvLaunch& L) {
     const int K = L.K;
     if (L.fmt == SLAI_FMT_F32) {
         SLAI_REQUIRE(ctx, L.nseg == 1 && L.pro == PRO_NONE && L.epi == EPI_STORE && !L.seg[0].bias, SLAI_ERR_INVALID_ARG,

@@ -363,7 +363,7 @@ static int llama_record(slai_llama* m, int kind) {
         {
             GemvLaunch L;
             L.fmt = w.wdown->fmt; L.K = m->hidden; L.nseg = 1; L.seg[0] = seg_of(w.wdown, 0, c.dim, nullptr, 0, 0);
-            L.v = m->hb; L.out = m->x; L.resid = m->x; L.epi = EPI_RESID; L.pdl = pdl;
+            L.v = m->hb; L.out = m->x; L.resid = m->x; L.epi = EPI_RESID; L.pdl = pdl; L.stats_cls = STATS_DOWN;
             L.prefetch = l + 1 < c.n_layers ? m->layers[l + 1].attn_norm : m->out_norm; L.prefetch_bytes = (size_t)c.dim * 4;
             if (l + 1 < c.n_layers) {
                 const slai_qmatrix* nx[3] = {m->layers[l + 1].wq, m->layers[l + 1].wk, m->layers[l + 1].wv};
@@ -391,6 +391,7 @@ static int llama_record(slai_llama* m, int kind) {
         L.v = m->x; L.out = m->out_sharded ? m->logits_part : m->logits; L.pro = PRO_RMS; L.norm_w = m->out_norm; L.eps = c.rms_norm_eps;
         L.epi = EPI_STORE;
         L.pdl = pdl;
+        L.stats_cls = STATS_LOGITS;
         {   // the next token starts with layer 0's q / k / v again
             const slai_qmatrix* nx[3] = {m->layers[0].wq, m->layers[0].wk, m->layers[0].wv};
             L.ahead = plan_ahead(nx, 3, 0, ahead_cap_bytes());
@@ -842,6 +843,47 @@ SLAI_API int slai_llama_prefill(slai_llama* m, const int32_t* h_tokens, int32_t 
     }
     return prefill_impl(m, llama_record, m->cfg.vocab_size, m->cfg.seq_len, h_tokens, n, pos0, h_last_logits);
 }
+// One decode step outside the graph and without programmatic dependent launch, with events around every GEMV and
+// attention launch: device time per kernel class.  The step is a real one (the KV cache is written at `pos`).
+SLAI_API int slai_llama_stats(slai_llama* m, int32_t token, int32_t pos, slai_llama_stats_t* out) {
+    if (!m || !out) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(m->ctx);
+    slai_ctx* ctx = m->ctx;
+    SLAI_REQUIRE(ctx, token >= 0 && token < m->cfg.vocab_size, SLAI_ERR_INVALID_ARG, "stats: token %d out of range", token);
+    SLAI_REQUIRE(ctx, pos >= 0 && pos < m->cfg.seq_len, SLAI_ERR_INVALID_ARG, "stats: pos %d out of range", pos);
+    int rc = set_scalars(m, token, pos, 0);
+    if (rc) return rc;
+    SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    const bool pdl = ctx->use_pdl;
+    ctx->use_pdl = false;
+    ctx->stats_on = true;
+    rc = slai_stats_mark(ctx, STATS_OTHER);
+    if (!rc) rc = llama_record(m, G_DECODE);
+    if (!rc) rc = slai_stats_mark(ctx, STATS_OTHER);
+    ctx->stats_on = false;
+    ctx->use_pdl = pdl;
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    memset(out, 0, sizeof(*out));
+    if (!rc && e == cudaSuccess) {
+        for (size_t i = 1; i < ctx->stats_ev.size(); i++) {
+            float ms = 0.f;
+            if (cudaEventElapsedTime(&ms, ctx->stats_ev[i - 1], ctx->stats_ev[i]) != cudaSuccess) continue;
+            const int cls = ctx->stats_cls[i];
+            out->us[cls] += ms * 1000.f;
+            out->us_total += ms * 1000.f;
+            if (cls != STATS_OTHER) out->launches[cls]++;
+        }
+        out->launches[STATS_OTHER] = m->launches;
+        for (int k = 1; k < STATS_CLASSES; k++) out->launches[STATS_OTHER] -= out->launches[k];
+    }
+    for (cudaEvent_t ev : ctx->stats_ev) cudaEventDestroy(ev);
+    ctx->stats_ev.clear();
+    ctx->stats_cls.clear();
+    if (rc) return rc;
+    if (e != cudaSuccess) return slai_set_error(ctx, SLAI_ERR_CUDA, "stats: %s", cudaGetErrorString(e));
+    return slai_check_wait_flag(ctx);
+}
+
 SLAI_API int slai_llama_read_state(slai_llama* m, int which, float* h_out, int64_t n) {
     if (!m || !h_out) return SLAI_ERR_INVALID_ARG;
     SLAI_ENTER(m->ctx);

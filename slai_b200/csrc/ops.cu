@@ -111,6 +111,16 @@ SLAI_API int slai_ctx_sync(slai_ctx* ctx) {
     SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return slai_check_wait_flag(ctx);
 }
+int slai_stats_mark(slai_ctx* ctx, int cls) {
+    if (!ctx->stats_on) return SLAI_OK;
+    cudaEvent_t e;
+    SLAI_CHECK_CUDA(ctx, cudaEventCreate(&e));
+    SLAI_CHECK_CUDA(ctx, cudaEventRecord(e, ctx->stream));
+    ctx->stats_ev.push_back(e);
+    ctx->stats_cls.push_back(cls);
+    return SLAI_OK;
+}
+
 SLAI_API int slai_ctx_set_wait_limit(slai_ctx* ctx, uint32_t rounds) {
     if (!ctx) return SLAI_ERR_INVALID_ARG;
     SLAI_REQUIRE(ctx, rounds >= 16, SLAI_ERR_INVALID_ARG, "wait limit of %u rounds is too short for a healthy launch", rounds);

@@ -130,6 +130,16 @@ class Llama2:
                                                                logits.ctypes.data_as(C.c_void_p) if want_logits else None))
         return logits
 
+    def stats(self, token: int, pos: int) -> dict:
+        """Device microseconds per kernel class of one (real) decode step run kernel after kernel outside the graph."""
+        from ._lib import LlamaStats
+        st = LlamaStats()
+        self.backend.check(self.backend.lib.slai_llama_stats(self.h, token, pos, C.byref(st)))
+        out = {"total_us": float(st.us_total)}
+        for i, name in enumerate(LlamaStats.CLASSES):
+            out[name] = {"us": float(st.us[i]), "launches": int(st.launches[i])}
+        return out
+
     def read_kv(self, layer: int, n_pos: int):
         """Keys and values of one layer for positions 0..n_pos, each [n_pos, kv_dim] f32 (test access)."""
         kvd = self.config.kv_dim // max(self.tp_size, 1) if hasattr(self, "tp_size") else self.config.kv_dim

@@ -37,6 +37,49 @@ def test_rust_binding_source_covers_the_header():
     assert not missing, missing
 
 
+def test_safe_rust_wrapper_calls_only_declared_functions_and_mirrors_the_operators():
+    """The safe crate (rust/slai-b200) is source only: check what can be checked without a Rust toolchain.  Every
+    `sys::slai_*` it calls is declared in the -sys crate with the same number of arguments, and the reference's operator
+    types each have a `launch`."""
+    import re
+    sysrs = open(os.path.join(ROOT, "rust", "slai-b200-sys", "src", "lib.rs")).read()
+    decl = {m.group(1): m.group(2) for m in re.finditer(r"pub fn (slai_\w+)\(([^)]*)\)", sysrs)}
+    src = ""
+    for f in ("lib.rs", "ops.rs", "models.rs"):
+        src += open(os.path.join(ROOT, "rust", "slai-b200", "src", f)).read()
+    calls = re.findall(r"sys::(slai_\w+)\(", src)
+    assert len(set(calls)) >= 35
+    for name in set(calls):
+        assert name in decl, name
+    # argument counts: split the call's argument text at top-level commas
+    for m in re.finditer(r"sys::(slai_\w+)\(", src):
+        i, depth, args, cur = m.end(), 1, [], ""
+        while depth:
+            ch = src[i]
+            if ch in "([{":
+                depth += 1
+            elif ch in ")]}":
+                depth -= 1
+                if depth == 0:
+                    break
+            if ch == "," and depth == 1:
+                args.append(cur)
+                cur = ""
+            else:
+                cur += ch
+            i += 1
+        if cur.strip():
+            args.append(cur)
+        want = len([a for a in decl[m.group(1)].split(",") if a.strip()])
+        assert len(args) == want, (m.group(1), len(args), want)
+    for op in ("GemvQuant", "RmsNorm", "RoPE", "Silu", "Unary", "BatchedMultiqueryAttention"):
+        assert re.search(r"impl " + op + r" \{.*?pub fn launch", src, re.S), op
+    for op in ("SoftMax", "LayerNorm"):
+        assert re.search(r"impl " + op + r" \{.*?pub fn launch_cols", src, re.S), op
+    for name in ("matmul_quant_assign", "add_assign", "mul_assign", "copy", "begin_submission", "submit", "forward_logits"):
+        assert f"pub fn {name}" in src, name
+
+
 def test_header_cites_reference_interfaces():
     src = open(os.path.join(ROOT, "include", "slai_b200.h")).read()
     for cite in ("gemv_quant.rs:206-312", "rms_norm.rs:35-67", "rope.rs:45-85", "silu.rs:24-48", "softmax.rs:22-40",

@@ -165,3 +165,26 @@ def test_gpt2_xl_shapes_one_layer(backend):
         rl = ref.forward(tok, pos)
         assert rel_l2(lg, rl) < 1e-3
         tok = O.argmax(rl)
+
+
+def test_llama_stats_accounts_for_every_kernel_class(backend):
+    """`slai_llama_stats`: one real decode step split by kernel class; the step leaves the same state as a plain one."""
+    cfg = Llama2Config(dim=256, hidden_dim=512, n_layers=3, n_q_heads=4, n_kv_heads=2, vocab_size=500, seq_len=64)
+    w = synthetic_llama_host(cfg, synth.FMT_Q4_K, seed=9, std=0.05, embd_std=1.0)
+    a = llama_from_host(backend, cfg, w, synth.FMT_Q4_K)
+    b = llama_from_host(backend, cfg, w, synth.FMT_Q4_K)
+    for pos, tok in enumerate([3, 17, 42]):
+        a.forward_logits(pos, tok)
+        b.forward_logits(pos, tok)
+    st = a.stats(7, 3)
+    lg, nxt = b.forward_logits(3, 7)
+    assert np.array_equal(a.read_state("logits"), lg)
+    for name in ("qkv", "attention", "wo", "gate_up", "down"):
+        assert st[name]["launches"] == cfg.n_layers and st[name]["us"] > 0, (name, st)
+    assert st["logits"]["launches"] == 1 and st["logits"]["us"] > 0
+    assert st["other"]["launches"] >= 1
+    parts = sum(st[k]["us"] for k in ("other", "qkv", "attention", "wo", "gate_up", "down", "logits"))
+    assert abs(parts - st["total_us"]) <= 1e-3 * st["total_us"] + 1.0
+    lg2, _ = a.forward_logits(4, nxt)   # the graph path still works after a statistics step
+    lg3, _ = b.forward_logits(4, nxt)
+    assert np.array_equal(lg2, lg3)
