@@ -147,34 +147,36 @@ def build_model(backend, seed=0):
     return cfg, m, mats, raw
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of gemv_kernel<Q4_K> on 11008x4096 from an ncu capture of
-# `python -m slai_b200.microbench --fmt q4_k --M 11008 --K 4096 --copies 8` (688 tiles x 16 steps x 2368-byte blocks = 26 068 992
-# bytes of weights, the 2.8 % above the GGUF byte count being the unpacked scales, plus the input vector)
-DOMINANT_KERNEL_DRAM_BYTES = 26_121_000
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate/up kernel on 2 x 11008 x 4096 Q4_K, from an ncu capture
+# of this benchmark (profiles/): 2 x 688 tiles x 16 steps x 2368-byte blocks = 52 137 984 bytes of weights (the 2.8 % above the
+# GGUF byte count being the unpacked scales) plus the vectors
+DOMINANT_KERNEL_DRAM_BYTES = 52_190_000
 
 
 def time_dominant_kernel(backend, ctx, cfg, mats, rounds=8):
-    """Average duration of the dominant kernel (the dequant-GEMV, here on the 11008x4096 Q4_K gate matrices of
-    all 32 layers in turn: 813 MB, larger than L2), CUDA events on the launching stream."""
+    """Average duration of the decode step's dominant kernel: RmsNorm + gate/up GEMV pair + SiLU (2 x 11008 x 4096 Q4_K, the
+    largest share of the step), run on the gate / up matrices of all 32 layers in turn (1.6 GB, larger than L2) as one
+    recorded pass, CUDA events on the launching stream.  Algorithmic bytes: both matrices' GGUF bytes + input + output."""
     from slai_b200 import synth
     x = backend.vector(np.random.default_rng(0).standard_normal(cfg.dim).astype(np.float32))
+    nw = backend.vector(np.ones(cfg.dim, dtype=np.float32))
     out = backend.zeros(cfg.hidden_dim)
-    gates = [mats[("w_gate", l)] for l in range(cfg.n_layers)]
-    for g in gates[:4]:
-        ctx.matmul_quant_assign(out, g, x)
+    pairs = [(mats[("w_gate", l)], mats[("w_up", l)]) for l in range(cfg.n_layers)]
+    for g, u in pairs[:4]:
+        ctx.ffn_gate_up(out, g, u, x, nw, 1e-5)
     backend.synchronize()
-    with backend.record() as rec:  # one recorded pass over the 32 matrices: no host work between the launches
-        for g in gates:
-            ctx.matmul_quant_assign(out, g, x)
+    with backend.record() as rec:  # one recorded pass over the 32 layers: no host work between the launches
+        for g, u in pairs:
+            ctx.ffn_gate_up(out, g, u, x, nw, 1e-5)
     rec.launch(2)
     backend.synchronize()
     backend.timer_start()
     rec.launch(rounds)
     ms = backend.timer_stop()
     rec.close()
-    n = rounds * len(gates)
+    n = rounds * len(pairs)
     per = ms / n * 1e-3
-    algo = synth.gemv_bytes(synth.FMT_Q4_K, cfg.hidden_dim, cfg.dim)
+    algo = 2 * synth.gemv_bytes(synth.FMT_Q4_K, cfg.hidden_dim, cfg.dim) - 4 * cfg.dim - 4 * cfg.hidden_dim  # one input, one output
     return algo, per, n
 
 
@@ -587,10 +589,11 @@ def main():
             "launches_per_token": launches_per_token,
             "token_roofline": {"bytes_per_token": token_bytes, "roofline_tok_s": peak * 1e9 / token_bytes,
                                "frac": (value / world) / (peak * 1e9 / token_bytes), "peak_source": peak_src},
-            "roofline": {"bound": "hbm", "kernel": "gemv_kernel<Q4K> 11008x4096 (all 32 gate matrices in turn, 813 MB > L2)",
+            "roofline": {"bound": "hbm", "kernel": "gemv_kernel<Q4_K, gate/up pair, rmsnorm, silu> 2 x 11008x4096: the decode step's dominant kernel "
+                                                   "(all 32 layers' pairs in turn, 1.6 GB > L2)",
                          "achieved": algo / per / 1e9, "peak": peak, "unit": "GB/s", "frac": algo / per / 1e9 / peak,
                          "traffic": DOMINANT_KERNEL_DRAM_BYTES, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of this "
-                         "kernel on this shape (one captured launch of the GEMV microbenchmark); algorithmic bytes %d" % algo,
+                         "kernel on this shape (one captured launch of this benchmark); algorithmic bytes %d" % algo,
                          "launches_timed": nl, "us_per_launch": per * 1e6, "peak_source": peak_src},
         }
         if gemv_table is not None:

@@ -180,6 +180,12 @@ int slai_synth_normal_f32(slai_ctx* ctx, float* d_out, int64_t n, uint64_t seed,
 /* ---- GemvQuant::launch (ops/gemv_quant.rs:206-312); LlmContext::matmul_quant_assign (context.rs:355-369)
  * d_out[b*M + i] = sum_k W[i][k] * d_v[b*K + k] for b < n_batch (1 <= n_batch <= 8). */
 int slai_gemv_quant(slai_ctx* ctx, float* d_out, const slai_qmatrix* w, const float* d_v, int n_batch);
+/* The feed-forward front half of a Llama layer as one kernel: out[hidden] = silu(Wgate n(x)) * (Wup n(x)) with
+ * n = RmsNorm by `d_norm_w` and `eps` (null weights: x is used as it is).  Replaces the four dispatches RmsNorm::launch,
+ * two GemvQuant::launch and Silu::launch of crates/slai/src/models/llama2/transformer.rs:356-361; both matrices must
+ * share one quantised format and shape. */
+int slai_ffn_gate_up(slai_ctx* ctx, float* d_out, const slai_qmatrix* w_gate, const slai_qmatrix* w_up, const float* d_x,
+                     const float* d_norm_w, float eps);
 
 /* ---- RmsNorm::launch (ops/rms_norm.rs:35-67): out[i] = (x[i] * rsqrt(mean(x^2) + eps)) * w[i] -------- */
 int slai_rms_norm(slai_ctx* ctx, float* d_out, const float* d_x, const float* d_w, int64_t n, float eps);

@@ -79,6 +79,7 @@ extern "C" {
     pub fn slai_synth_blocks(ctx: *mut slai_ctx, fmt: i32, nrows: i64, ncols: i64, seed: u64, std: f32, d_blocks: *mut c_void) -> i32;
     pub fn slai_synth_normal_f32(ctx: *mut slai_ctx, d_out: *mut f32, n: i64, seed: u64, std: f32) -> i32;
     pub fn slai_gemv_quant(ctx: *mut slai_ctx, d_out: *mut f32, w: *const slai_qmatrix, d_v: *const f32, n_batch: i32) -> i32;
+    pub fn slai_ffn_gate_up(ctx: *mut slai_ctx, d_out: *mut f32, w_gate: *const slai_qmatrix, w_up: *const slai_qmatrix, d_x: *const f32, d_norm_w: *const f32, eps: f32) -> i32;
     pub fn slai_rms_norm(ctx: *mut slai_ctx, d_out: *mut f32, d_x: *const f32, d_w: *const f32, n: i64, eps: f32) -> i32;
     pub fn slai_rope(ctx: *mut slai_ctx, variant: i32, d_q: *mut f32, q_len: i64, d_k: *mut f32, head_size: i32, kv_dim: i32, pos: i32, base_freq: f32) -> i32;
     pub fn slai_silu_gate(ctx: *mut slai_ctx, d_h1_inout: *mut f32, d_h2: *const f32, n: i64) -> i32;

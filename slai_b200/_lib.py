@@ -98,6 +98,7 @@ SIGNATURES = {
     "slai_synth_blocks": (C.c_int, [_vp, C.c_int, _i64, _i64, C.c_uint64, _f, _vp]),
     "slai_synth_normal_f32": (C.c_int, [_vp, _vp, _i64, C.c_uint64, _f]),
     "slai_gemv_quant": (C.c_int, [_vp, _vp, _vp, _vp, C.c_int]),
+    "slai_ffn_gate_up": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _f]),
     "slai_rms_norm": (C.c_int, [_vp, _vp, _vp, _vp, _i64, _f]),
     "slai_rope": (C.c_int, [_vp, C.c_int, _vp, _i64, _vp, C.c_int, C.c_int, C.c_int, _f]),
     "slai_silu_gate": (C.c_int, [_vp, _vp, _vp, _i64]),

@@ -457,6 +457,35 @@ SLAI_API int slai_gemv_quant(slai_ctx* ctx, float* d_out, const slai_qmatrix* w,
     return SLAI_OK;
 }
 
+// hb = silu(Wgate n(x)) * (Wup n(x)), n = RmsNorm with `d_norm_w` (null: no normalisation): the feed-forward front half
+// of a Llama layer in one kernel, both matrices streamed tile by tile side by side.
+SLAI_API int slai_ffn_gate_up(slai_ctx* ctx, float* d_out, const slai_qmatrix* w_gate, const slai_qmatrix* w_up, const float* d_x,
+                              const float* d_norm_w, float eps) {
+    if (!ctx || !w_gate || !w_up || !d_out || !d_x) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(ctx);
+    SLAI_REQUIRE(ctx, w_gate->fmt == w_up->fmt && w_gate->fmt != SLAI_FMT_F32, SLAI_ERR_UNSUPPORTED_FORMAT,
+                 "ffn_gate_up: both matrices must have the same quantised format");
+    SLAI_REQUIRE(ctx, w_gate->nrows == w_up->nrows && w_gate->ncols == w_up->ncols, SLAI_ERR_SHAPE, "ffn_gate_up: gate is %lldx%lld, up is %lldx%lld",
+                 (long long)w_gate->nrows, (long long)w_gate->ncols, (long long)w_up->nrows, (long long)w_up->ncols);
+    GemvLaunch L;
+    L.fmt = w_gate->fmt;
+    L.K = (int)w_gate->ncols;
+    L.nseg = 2;
+    for (int i = 0; i < 2; i++) {
+        const slai_qmatrix* w = i == 0 ? w_gate : w_up;
+        L.seg[i].w = w->data;
+        L.seg[i].tile_bytes = w->tile_bytes;
+        L.seg[i].rows = (int)w->nrows;
+    }
+    L.v = d_x;
+    L.out = d_out;
+    L.pro = d_norm_w ? PRO_RMS : PRO_NONE;
+    L.norm_w = d_norm_w;
+    L.eps = eps;
+    L.epi = EPI_SILU;
+    return gemv_launch(ctx, L);
+}
+
 // ------------------------------------------------------------------------------------------------
 // small operators
 // ------------------------------------------------------------------------------------------------

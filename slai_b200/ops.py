@@ -315,6 +315,10 @@ class LlmContext:
             raise SlaiError(_lib.ERR_SHAPE, f"Gemv: dimension mismatch ({a.nrows}x{a.ncols} * {len(b)} -> {len(out)})")
         self.backend.check(self.lib.slai_gemv_quant(self.h, _ptr(out), a.h, _ptr(b), n_batch))
 
+    def ffn_gate_up(self, out, w_gate: GpuQuantMatrix, w_up: GpuQuantMatrix, x, norm_w=None, eps: float = 1e-5):
+        """out = silu(Wgate n(x)) * (Wup n(x)), n = RmsNorm: the operators of transformer.rs:356-361 as one kernel."""
+        self.backend.check(self.lib.slai_ffn_gate_up(self.h, _ptr(out), w_gate.h, w_up.h, _ptr(x), _ptr(norm_w) if norm_w is not None else None, eps))
+
     # Tensor-parallel exchange operators (no counterpart in the reference): a row-parallel product whose partial goes
     # to every rank's exchange region, and a product whose input is the sum over ranks of such an exchange.
     def matmul_quant_partial(self, a: GpuQuantMatrix, b, resid, index: int, per_token: int):

@@ -189,6 +189,28 @@ def test_gemv_batch(backend, ctx):
         assert rel_l2(got[b], O.gemv_quant(fmt, blocks, v[b], M, K)) < GEMV_TOL
 
 
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("norm", [True, False])
+def test_ffn_gate_up_matches_the_four_operators(backend, ctx, fmt, norm):
+    """RmsNorm + two GEMVs + SiLU as one kernel (slai_ffn_gate_up) against the oracle's operators in sequence."""
+    H, K = 1100, 1024   # hidden not a multiple of 16: the last tile is padded
+    rng = np.random.default_rng(fmt + 7 * norm)
+    bg = synth.quantize(fmt, synth.normal_matrix(11, H, K))
+    bu = synth.quantize(fmt, synth.normal_matrix(12, H, K))
+    x = rng.standard_normal(K).astype(np.float32)
+    nw = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    g, u = GpuQuantMatrix(backend, fmt, H, K, bg), GpuQuantMatrix(backend, fmt, H, K, bu)
+    out = backend.zeros(H)
+    ctx.ffn_gate_up(out, g, u, backend.vector(x), backend.vector(nw) if norm else None, 1e-5)
+    xn = O.rms_norm(x, nw, 1e-5) if norm else x
+    hg, hu = O.gemv_quant(fmt, bg, xn, H, K), O.gemv_quant(fmt, bu, xn, H, K)
+    ref = hu * (hg / (1.0 + np.exp(-hg.astype(np.float64)))).astype(np.float32)
+    assert rel_l2(out.to_numpy(), ref) < GEMV_TOL
+    with pytest.raises(SlaiError) as e:
+        ctx.ffn_gate_up(out, g, GpuQuantMatrix(backend, fmt, H - 16, K, bu[: H - 16]), backend.vector(x))
+    assert e.value.code == _lib.ERR_SHAPE
+
+
 def test_gemv_f32_matrix(backend, ctx):
     M, K = 100, 288
     rng = np.random.default_rng(2)
