@@ -138,13 +138,15 @@ static int attention_launch_inner(slai_ctx* ctx, const AttnLaunch& A) {
                  "attention: kv_mul=%d must be in 1..8 and divide n_heads=%d", A.kv_mul, A.n_heads);
     SLAI_REQUIRE(ctx, A.head_size % 2 == 0 && A.head_size <= 64 * MAX_J, SLAI_ERR_SHAPE,
                  "attention: head_size=%d must be even and <= %d", A.head_size, 64 * MAX_J);
-    const int n_kv = A.n_heads / A.kv_mul;
-    SLAI_REQUIRE(ctx, n_kv <= 1024, SLAI_ERR_SHAPE, "attention: too many KV heads");
+    const int share = attn_kv_share(A.kv_mul);
+    const int n_kv = A.n_heads / A.kv_mul * share;  // virtual heads: the grid's x extent and the number of tickets
+    const int kv_mul = A.kv_mul / share;
+    SLAI_REQUIRE(ctx, n_kv <= 1024, SLAI_ERR_SHAPE, "attention: too many heads");
     const int n_max = A.max_pos + 1;
     AttnParams P;
     P.q = A.q; P.kc = A.kcache; P.vc = A.vcache;
     P.pos_stride = A.pos_stride; P.head_stride = A.head_stride;
-    P.n_heads = A.n_heads; P.kv_mul = A.kv_mul; P.hs = A.head_size;
+    P.n_heads = A.n_heads; P.kv_mul = kv_mul; P.kv_share = share; P.hs = A.head_size;
     size_t smem = 0;
     {
         int rc = attn_geometry(ctx, P, A.kv_dtype, n_max, &smem);
@@ -175,10 +177,11 @@ static int attention_launch_inner(slai_ctx* ctx, const AttnLaunch& A) {
     P.batch = A.batch; P.pos0 = A.pos0; P.q_bs = A.q_batch_stride; P.out_bs = A.out_batch_stride;
     P.po_bs = (long long)(per_token / 4); P.pml_bs = (long long)(per_token / 4);  // every token's partials in its own slice of the scratch
     const bool f16 = A.kv_dtype == SLAI_KV_F16;
-    if (A.kv_mul == 1) return f16 ? launch_t<__half, 1>(ctx, P, n_kv, smem, A.pdl) : launch_t<float, 1>(ctx, P, n_kv, smem, A.pdl);
-    if (A.kv_mul <= 4) return f16 ? launch_t<__half, 4>(ctx, P, n_kv, smem, A.pdl) : launch_t<float, 4>(ctx, P, n_kv, smem, A.pdl);
-    return f16 ? launch_t<__half, 8>(ctx, P, n_kv, smem, A.pdl) : launch_t<float, 8>(ctx, P, n_kv, smem, A.pdl);
+    if (kv_mul == 1) return f16 ? launch_t<__half, 1>(ctx, P, n_kv, smem, A.pdl) : launch_t<float, 1>(ctx, P, n_kv, smem, A.pdl);
+    return f16 ? launch_t<__half, 2>(ctx, P, n_kv, smem, A.pdl) : launch_t<float, 2>(ctx, P, n_kv, smem, A.pdl);
 }
+
+int attention_tickets(int n_heads, int kv_mul) { return n_heads / kv_mul * attn_kv_share(kv_mul); }
 
 // =================================================================================================
 // Attention without any allocation (slai_attention_static).

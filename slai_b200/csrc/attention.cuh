@@ -14,7 +14,8 @@ struct AttnParams {
     const void* kc;
     const void* vc;
     long long pos_stride, head_stride;
-    int n_heads, kv_mul, hs;
+    int n_heads, kv_mul, hs;  // kv_mul: query heads one work item serves (those of its virtual head)
+    int kv_share = 1;         // virtual heads per cache head: virtual head v reads the keys and values of cache head v / kv_share
     const int* d_pos;
     int n_splits;   // most splits a KV head is cut into (stride of the partial buffers)
     int tile_pos;   // positions staged in shared memory at a time
@@ -50,6 +51,10 @@ __host__ __device__ inline size_t attn_item_bytes(int kv_mul, int hs, int esz, i
     if (merge > tile) tile = merge;
     return attn_head_bytes(kv_mul, hs, tile_pos) + ((tile + 15) & ~(size_t)15);
 }
+// Grouped-query models would leave most SMs idle with one work item per (cache head, split): the query heads of a cache
+// head are therefore dealt to `attn_kv_share(kv_mul)` virtual heads of at most two query heads each, which read the same
+// keys and values (from L2 after the first).
+__host__ __device__ inline int attn_kv_share(int kv_mul) { return kv_mul <= 2 ? 1 : (kv_mul % 2 == 0 ? kv_mul / 2 : kv_mul); }
 // Positions per tile: at most 8 KB of K (and of V) per item -- four 16-byte pieces per thread and matrix -- a
 // multiple of 8, at most 32.
 __host__ __device__ inline int attn_tile_pos(int hs, int esz) {
@@ -115,7 +120,7 @@ __device__ __forceinline__ void copy_rows_u32(const unsigned char* g, size_t row
     }
 }
 
-// One work item = (KV head, split `split` of `ns`) at `n` positions, processed by ATT_THREADS threads with thread
+// One work item = (virtual KV head, split `split` of `ns`) at `n` positions, processed by ATT_THREADS threads with thread
 // index `tid`, shared memory `smb` (attn_item_bytes) and barrier `bar_id`.  The split's positions are walked in
 // tiles with a running (max, sum) per query head (the usual streaming softmax); the partial output of the split is
 // the un-normalised weighted sum of V relative to the final max.
@@ -136,8 +141,9 @@ __device__ __forceinline__ void attn_item(const AttnParams& P, int kvh, int spli
     const int t0 = split * chunk;
     const int t1 = min(n, t0 + chunk);
 
-    const unsigned char* kbase = reinterpret_cast<const unsigned char*>(P.kc) + ((size_t)kvh * P.head_stride) * ESZ;
-    const unsigned char* vbase = reinterpret_cast<const unsigned char*>(P.vc) + ((size_t)kvh * P.head_stride) * ESZ;
+    const int cache_head = P.kv_share > 1 ? kvh / P.kv_share : kvh;
+    const unsigned char* kbase = reinterpret_cast<const unsigned char*>(P.kc) + ((size_t)cache_head * P.head_stride) * ESZ;
+    const unsigned char* vbase = reinterpret_cast<const unsigned char*>(P.vc) + ((size_t)cache_head * P.head_stride) * ESZ;
     const size_t row_pitch = (size_t)P.pos_stride * ESZ;
     const float sqrt_hs = sqrtf((float)hs);
     // q: loads first, stores after the first tile's loads are in flight

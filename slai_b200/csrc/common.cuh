@@ -303,6 +303,7 @@ struct AttnLaunch {
 };
 size_t attention_scratch_bytes(slai_ctx* ctx, int n_heads, int kv_mul, int head_size, int max_pos);
 int attention_launch(slai_ctx* ctx, const AttnLaunch& A);
+int attention_tickets(int n_heads, int kv_mul);  // tickets (unsigned words) one query token's launch uses
 int ensure_scratch(slai_ctx* ctx, size_t bytes);
 const float* rope_table(slai_ctx* ctx, int head_size, float base);
 

@@ -303,8 +303,20 @@ __device__ __forceinline__ float stage_vector(const int PRO_ARG, const GemvParam
         for (int r = 0; r < STAGE_REGS; r++)
             if (tid + r * THREADS < n4) stats(xr[r], wr[r]);
     } else {
+        // long vectors: four loads in flight per thread and round (one at a time would pay the L2 latency every round)
 #pragma unroll 1
-        for (int i = tid; i < n4; i += THREADS) stats(__ldcg(v4 + i), PRO != PRO_NONE ? __ldg(w4p + i) : zero4);
+        for (int i0 = tid; i0 < n4; i0 += 4 * THREADS) {
+            float4 xb[4], wb[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int i = i0 + u * THREADS;
+                xb[u] = i < n4 ? __ldcg(v4 + i) : zero4;
+                wb[u] = (PRO != PRO_NONE && i < n4) ? __ldg(w4p + i) : zero4;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                if (i0 + u * THREADS < n4) stats(xb[u], wb[u]);
+        }
     }
     SLAI_TRACE_POINT(6)
     block_sum_max(sum, mx, stat);
@@ -386,8 +398,18 @@ __device__ __forceinline__ float stage_vector(const int PRO_ARG, const GemvParam
             if (tid + r * THREADS < np4) convert(xr[r], wr[r], tid + r * THREADS);  // independent rounds: the compiler overlaps them
     } else {
 #pragma unroll 1
-        for (int i = tid; i < np4; i += THREADS)
-            convert(i < n4 ? __ldcg(v4 + i) : zero4, (PRO != PRO_NONE && i < n4) ? __ldg(w4p + i) : zero4, i);
+        for (int i0 = tid; i0 < np4; i0 += 4 * THREADS) {
+            float4 xb[4], wb[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int i = i0 + u * THREADS;
+                xb[u] = i < n4 ? __ldcg(v4 + i) : zero4;
+                wb[u] = (PRO != PRO_NONE && i < n4) ? __ldg(w4p + i) : zero4;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                if (i0 + u * THREADS < np4) convert(xb[u], wb[u], i0 + u * THREADS);
+        }
     }
     SLAI_TRACE_POINT(8)
     __syncthreads();

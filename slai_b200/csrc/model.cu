@@ -737,7 +737,7 @@ static int llama_prefill_batched(slai_llama* m, const int32_t* h_tokens, int n, 
     const int NT = std::min(256, (n + 15) / 16 * 16);
     const int t_pad = (n + NT - 1) / NT * NT;
     const int AB = 64;  // query tokens per attention launch
-    const int n_kv = m->n_q_local / m->kv_mul;
+    const int n_kv = attention_tickets(m->n_q_local, m->kv_mul);  // tickets per query token (virtual heads of the attention kernel)
     const size_t attn_per_token = attention_scratch_bytes(ctx, m->n_q_local, m->kv_mul, m->head_size, pos0 + n - 1);
     int rc = llama_prefill_reserve(m, t_pad, AB, attn_per_token * AB, n_kv);
     if (rc) return rc;

@@ -6,7 +6,7 @@ adjacent pair whose concatenation has the highest vocabulary score); `Gpt2Tokeni
 crates/slai/src/models/gpt2/tokenizer.rs:105-217 (byte-level BPE over the pieces of a split pattern, merge ranks from the
 `tokenizer.ggml.merges` list, `<...>` spans looked up as whole special tokens); `ChatTemplate` follows
 crates/slai-chat/src/chat_template.rs:11-39 (the model's Jinja template with `bos_token`, `eos_token` and
-`add_generation_prompt = true`).  Vocabularies come from GGUF metadata (`gguf_io.read_gguf`) or from plain lists.
+`add_generation_prompt = true`).  Vocabularies come from GGUF metadata (`gguf_io.GgufFile(...).metadata`) or from plain lists.
 """
 from __future__ import annotations
 

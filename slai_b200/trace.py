@@ -1,7 +1,7 @@
 """Reader of the trace build's device-side timeline.
 
     python -m slai_b200.build --trace          # builds slai_b200/libslai_b200_trace.so (-DSLAI_TRACE)
-    python -m slai_b200.trace [--tokens 4] [--prompt 512] [--model 7b|gpt2xl]
+    python -m slai_b200.trace [--tokens 4] [--prompt 512] [--model 7b|70b|gpt2xl] [--layers N]
 
 The trace library stamps %globaltimer inside the decode kernels (block 0 of every GEMV / attention launch: start,
 ring requested, predecessor done, input staged, main loop done, partials reduced, end) and appends one record per
@@ -111,7 +111,8 @@ def main():
     ap.add_argument("--blocks", action="store_true", help="also print the per-block spread of the last GEMV launches")
     ap.add_argument("--tokens", type=int, default=4)
     ap.add_argument("--prompt", type=int, default=512)
-    ap.add_argument("--model", default="7b", choices=["7b", "gpt2xl"])
+    ap.add_argument("--model", default="7b", choices=["7b", "70b", "gpt2xl"])
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the architecture has (0 = all)")
     ap.add_argument("--json", action="store_true")
     a = ap.parse_args()
     if not os.path.exists(TRACE_LIB):
@@ -122,9 +123,12 @@ def main():
     backend = Backend(0)
     lib = backend.lib
     lib.slai_debug_timeline.restype = C.c_int
-    if a.model == "7b":
-        from .models import LLAMA2_7B, synthetic_llama_device
-        cfg = LLAMA2_7B
+    if a.model in ("7b", "70b"):
+        import dataclasses
+        from .models import LLAMA2_7B, LLAMA2_70B, synthetic_llama_device
+        cfg = LLAMA2_7B if a.model == "7b" else LLAMA2_70B
+        if a.layers > 0:
+            cfg = dataclasses.replace(cfg, n_layers=a.layers)
         m = synthetic_llama_device(backend, cfg, synth.FMT_Q4_K, synth.FMT_Q6_K)
         vocab = cfg.vocab_size
     else:

@@ -331,7 +331,9 @@ def test_rope(backend, ctx, variant, pos):
 @pytest.mark.parametrize("cfg", [(1024, 12, 1, 64, (0, 1, 7, 8, 100, 1023)),   # the reference's disabled test shape
                                  (256, 6, 1, 48, (0, 33, 255)),                  # tiny Llama heads (48)
                                  (4096, 32, 1, 128, (0, 640, 4095)),             # Llama-2-7B
-                                 (2048, 64, 8, 128, (5, 1500))])                 # Llama-2-70B GQA
+                                 (2048, 64, 8, 128, (5, 1500)),                  # Llama-2-70B GQA
+                                 (512, 12, 4, 64, (0, 300)), (512, 10, 5, 64, (0, 300)), (512, 12, 3, 64, (257,)),   # other group sizes
+                                 (512, 8, 2, 64, (300,))])
 def test_attention_parity(backend, ctx, kv_dtype, cfg):
     seq, nh, kvm, hs, positions = cfg
     nkv = nh // kvm
