@@ -386,7 +386,9 @@ def measure_tp(args, group, n_layers=0, prompt_len=1024, steps=None, warmup=None
     # not whenever each rank has finished building its shard.
     backend.synchronize()
     group.barrier()
-    m.prefill(prompt[:16], 0)  # warm-up; overwritten by the timed pass
+    # warm-up, overwritten by the timed pass: on one GPU the whole prompt, so that the prompt buffers (grown on demand and kept
+    # by the library) have their size before the timed pass, as for every prompt after a server's first
+    m.prefill(prompt[:-1] if world == 1 else prompt[:16], 0)
     backend.synchronize()
     group.barrier()
     t0 = time.perf_counter()
@@ -505,7 +507,9 @@ def main():
 
     rng = np.random.default_rng(42 + rank)
     prompt = rng.integers(0, cfg.vocab_size, size=PROMPT_LEN).astype(np.int32)
-    m.prefill(prompt[:16], 0)  # warms the kernels up (buffers, attributes); overwritten by the timed pass
+    # warm-up, overwritten by the timed pass: the whole prompt, so that the prompt buffers (grown on demand and kept by the
+    # library) have their size before the timed pass, as for every prompt after a server's first
+    m.prefill(prompt[:-1], 0)
     backend.synchronize()
     t0 = time.perf_counter()
     m.prefill(prompt[:-1], 0)

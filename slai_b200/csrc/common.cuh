@@ -368,6 +368,9 @@ int prefill_silu_split_launch(slai_ctx* ctx, const float* gate, const float* up,
 int prefill_embed_launch(slai_ctx* ctx, float* x, int dim, const int* d_tokens, int T, const float* table, const slai_qmatrix* qtable);
 int rope_kv_store_launch(slai_ctx* ctx, float* q, const float* k, const float* v, int q_dim, int kv_dim, int head_size, const int* d_pos,
                          const float* theta, int neox, void* kcache, void* vcache, int kv_f16, long long kv_head_stride, bool pdl);
+bool prefill_attention_supported(int head_size, int kv_f16, const void* kc, const void* vc, long long head_stride);
+int prefill_attention_launch(slai_ctx* ctx, const float* q, int q_ld, const void* kc, const void* vc, int kv_f16, long long head_stride, int head_size,
+                             int n_heads, int kv_mul, int pos0, int T, float* out, int out_ld);
 int prefill_rope_kv_launch(slai_ctx* ctx, const float* qkv, int ld, int q_dim, int kv_dim, int head_size, int pos0, int T,
                            const float* theta, int neox, float* q_out, void* kcache, void* vcache, int kv_f16, long long kv_head_stride);
 

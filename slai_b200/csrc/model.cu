@@ -750,7 +750,12 @@ static int llama_prefill_batched(slai_llama* m, const int32_t* h_tokens, int n, 
     const int qkv_ld = m->q_dim + 2 * m->kv_dim;
     auto gemm = [&](const slai_qmatrix* w, int rows, float* out, int ldo, int off, const float* resid, int ldr, const float* bias) {
         PrefillGemm G;
-        G.w = w; G.rows = rows; G.x_hi = m->pf_hi; G.x_lo = m->pf_lo; G.T = n; G.t_pad = t_pad; G.NT = NT;
+        // Fewer tokens per CTA tile while the grid would leave half of the SMs without a tile (4096-row matrices at 512 tokens:
+        // 64 CTAs of 256 tokens become 128 CTAs of 128); every CTA dequantises its weight rows itself, so no further.
+        int nt = NT;
+        const int m_tiles = (rows + 127) / 128;
+        while (nt > 64 && (nt / 2) % 16 == 0 && t_pad % (nt / 2) == 0 && m_tiles * (t_pad / nt) * 2 <= ctx->sm_count) nt /= 2;
+        G.w = w; G.rows = rows; G.x_hi = m->pf_hi; G.x_lo = m->pf_lo; G.T = n; G.t_pad = t_pad; G.NT = nt;
         G.out = out; G.ldo = ldo; G.out_off = off; G.resid = resid; G.ldr = ldr; G.bias = bias;
         return prefill_gemm_launch(ctx, G);
     };
@@ -766,8 +771,14 @@ static int llama_prefill_batched(slai_llama* m, const int32_t* h_tokens, int n, 
         if ((rc = prefill_rope_kv_launch(ctx, m->pf_qkv, qkv_ld, m->q_dim, m->kv_dim, m->head_size, pos0, n, m->rope_theta, c.rope_variant != 0,
                                          m->pf_q, kc, vc, c.kv_dtype == SLAI_KV_F16, (long long)c.seq_len * m->head_size)))
             return rc;
-        // attention, AB query tokens per launch                                transformer.rs:350
-        for (int t0 = 0; t0 < n; t0 += AB) {
+        // attention                                                            transformer.rs:350
+        const long long kv_head_stride = (long long)c.seq_len * m->head_size;
+        const bool tiled = prefill_attention_supported(m->head_size, c.kv_dtype == SLAI_KV_F16, kc, vc, kv_head_stride) && m->q_dim % 4 == 0;
+        if (tiled && (rc = prefill_attention_launch(ctx, m->pf_q, m->q_dim, kc, vc, c.kv_dtype == SLAI_KV_F16, kv_head_stride, m->head_size, m->n_q_local,
+                                                    m->kv_mul, pos0, n, m->pf_xb, m->q_dim)))
+            return rc;
+        // (head sizes the tiled kernel does not take: the decode step's kernel, AB query tokens per launch)
+        for (int t0 = 0; t0 < n && !tiled; t0 += AB) {
             const int nb = std::min(AB, n - t0);
             AttnLaunch A;
             A.q = m->pf_q + (size_t)t0 * m->q_dim; A.kcache = kc; A.vcache = vc; A.kv_dtype = c.kv_dtype;

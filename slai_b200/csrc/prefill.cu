@@ -13,15 +13,17 @@
 // accumulation order.  The tensor cores have the headroom: the kernel is bound by dequantisation, not by MMA issue.
 //
 // One CTA computes a 128 (weight rows) x NT (tokens, <= 256) tile of Y^T over the whole K:
-//   * warps 2-5 (128 threads, one weight row each): read the row's packed quants of the next 64-element K slice from
-//     the tile-major matrix (the decode layout, layout.cuh), dequantise with the reference's rounding sequence, split
-//     into hi / lo and store them into the A operand tiles in the canonical K-major 128-byte-swizzled layout;
+//   * warps 2-9 (256 threads, two per weight row, one 32-element half of the slice each): read the row's packed quants
+//     of the next 64-element K slice from the tile-major matrix (the decode layout, layout.cuh) one stage ahead of their
+//     use, dequantise with the reference's rounding sequence, split into hi / lo and store them into the A operand
+//     tiles in the canonical K-major 128-byte-swizzled layout;
 //   * warp 0, one lane: TMA (cp.async.bulk.tensor.2d, no multicast: the tile is this CTA's own) brings the matching
 //     64-element slice of the activations' hi and lo planes [T_pad x K] into the B operand tiles, same swizzle;
 //   * warp 1, one lane: issues tcgen05.mma (kind::f16, M = 128, N = NT, K = 16) four slices x three products per stage
 //     and commits the stage's completion to an mbarrier, which frees the stage for the producers;
-//   * epilogue (warps 2-5 again): tcgen05.ld brings each thread one accumulator row (32 TMEM lanes per warp, the
-//     quadrant given by warp index mod 4), adds bias / residual and stores Y[t][row] with coalesced 128-byte rows.
+//   * epilogue (warps 2-9 again): tcgen05.ld brings each thread one accumulator row (32 TMEM lanes per warp, the
+//     quadrant given by warp index mod 4; the two warps of a quadrant take alternate groups of 16 tokens), adds bias /
+//     residual and stores Y[t][row] with coalesced 128-byte rows.
 // Two stages of A and B (192 KB of shared memory at NT = 256), 1 CTA per SM, TMEM columns = NT rounded to a power of two.
 // Every mbarrier wait is bounded: on expiry the error flag is raised and the role leaves its loop; all roles then meet
 // at the final barrier and the tensor memory is released.
@@ -32,7 +34,8 @@
 
 namespace {
 
-constexpr int PF_THREADS = 192;
+constexpr int PF_DQ_THREADS = 256;  // dequantising threads: two per weight row (one 32-element sub-block each)
+constexpr int PF_THREADS = 64 + PF_DQ_THREADS;
 constexpr int PF_BM = 128;          // weight rows per CTA
 constexpr int PF_BK = 64;           // K elements per stage (one 128-byte swizzle row of fp16)
 constexpr int PF_STAGES = 2;
@@ -127,59 +130,57 @@ __device__ __forceinline__ void store_split8(unsigned char* a_hi, unsigned char*
     *reinterpret_cast<uint4*>(a_lo + off) = *reinterpret_cast<const uint4*>(l);
 }
 
-// Row `row` of the matrix, elements [k0, k0 + 64): dequantised, split and stored.  Q4_K / Q5_K read the two 16-byte
-// chunks of packed nibbles and the row's 20-byte header directly (a 64-element slice is one pair of sub-blocks);
-// the other formats go element by element.
-__device__ __forceinline__ void dequant_slice(const PrefillGemmParams& P, long long row, int r, int k0, unsigned char* a_hi,
-                                              unsigned char* a_lo) {
-    if (row >= P.M) {  // rows beyond the matrix: zeros (their outputs are never stored)
-        const float z[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int c = 0; c < 8; c++) store_split8(a_hi, a_lo, r, c, z);
-        return;
+// Half `part` (32 elements = one sub-block of Q4_K / Q5_K) of the slice [k0, k0 + 64) of row `row`.  For Q4_K / Q5_K the
+// packed bytes are fetched into registers (`slice_fetch`) a stage before they are turned into operand rows (`slice_emit`),
+// so that the loads' latency runs behind the previous stage's arithmetic; the other formats go element by element.
+struct SliceRegs {
+    uint4 q[2], hq[2];     // the 32 nibble bytes of the 64-element group, the row's 32 high-bit bytes (Q5_K)
+    uint32_t dd, sc, mb;   // f16 d | f16 dmin, scale and minimum of this thread's sub-block
+};
+__device__ __forceinline__ void slice_fetch(const PrefillGemmParams& P, long long row, int k0, int part, SliceRegs& R) {
+    const bool five = P.fmt == SLAI_FMT_Q5_K;
+    const int r16 = (int)(row & 15), G = (k0 >> 6) & 3;
+    const uint8_t* b = P.w + (row >> 4) * P.tile_bytes + (long long)(k0 >> 8) * layout::step_bytes(P.fmt);
+    const uint8_t* h = b + layout::K45_HDR_ROW * r16;
+    const int j = 2 * G + part;
+    R.dd = __ldg(reinterpret_cast<const uint32_t*>(h));
+    R.sc = __ldg(h + layout::k45_sc_off(j));
+    R.mb = __ldg(h + 12 + j);
+    const int q0 = five ? layout::K45_HDR + 512 : layout::K45_HDR;
+    R.q[0] = __ldg(reinterpret_cast<const uint4*>(b + layout::qbyte_off(q0, r16, 32 * G)));
+    R.q[1] = __ldg(reinterpret_cast<const uint4*>(b + layout::qbyte_off(q0, r16, 32 * G + 16)));
+    if (five) {
+        R.hq[0] = __ldg(reinterpret_cast<const uint4*>(b + layout::K45_HDR + 32 * r16));
+        R.hq[1] = __ldg(reinterpret_cast<const uint4*>(b + layout::K45_HDR + 32 * r16 + 16));
     }
-    if (P.fmt == SLAI_FMT_Q4_K || P.fmt == SLAI_FMT_Q5_K) {
-        const bool five = P.fmt == SLAI_FMT_Q5_K;
-        const int r16 = (int)(row & 15), G = (k0 >> 6) & 3;
-        const uint8_t* b = P.w + (row >> 4) * P.tile_bytes + (long long)(k0 >> 8) * layout::step_bytes(P.fmt);
-        const uint8_t* h = b + layout::K45_HDR_ROW * r16;
-        const uint32_t dd = *reinterpret_cast<const uint32_t*>(h);
-        const float d = dev_h2f(dd & 0xFFFFu), mn = dev_h2f(dd >> 16);
-        const int q0 = five ? layout::K45_HDR + 512 : layout::K45_HDR;
-        uint4 qw[2];
-        qw[0] = __ldg(reinterpret_cast<const uint4*>(b + layout::qbyte_off(q0, r16, 32 * G)));
-        qw[1] = __ldg(reinterpret_cast<const uint4*>(b + layout::qbyte_off(q0, r16, 32 * G + 16)));
-        uint4 hq[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
-        if (five) {
-            hq[0] = __ldg(reinterpret_cast<const uint4*>(b + layout::K45_HDR + 32 * r16));
-            hq[1] = __ldg(reinterpret_cast<const uint4*>(b + layout::K45_HDR + 32 * r16 + 16));
-        }
-        const unsigned char* qb = reinterpret_cast<const unsigned char*>(qw);
-        const unsigned char* hb = reinterpret_cast<const unsigned char*>(hq);
+}
+__device__ __forceinline__ void slice_emit(const PrefillGemmParams& P, const SliceRegs& R, int r, int k0, int part, unsigned char* a_hi,
+                                           unsigned char* a_lo) {
+    const bool five = P.fmt == SLAI_FMT_Q5_K;
+    const int G = (k0 >> 6) & 3;
+    const float d1 = __fmul_rn(dev_h2f(R.dd & 0xFFFFu), (float)R.sc), m1 = __fmul_rn(dev_h2f(R.dd >> 16), (float)R.mb);
+    const uint32_t qw[8] = {R.q[0].x, R.q[0].y, R.q[0].z, R.q[0].w, R.q[1].x, R.q[1].y, R.q[1].z, R.q[1].w};
+    const uint32_t hw[8] = {R.hq[0].x, R.hq[0].y, R.hq[0].z, R.hq[0].w, R.hq[1].x, R.hq[1].y, R.hq[1].z, R.hq[1].w};
 #pragma unroll
-        for (int half = 0; half < 2; half++) {
-            const int j = 2 * G + half;
-            const float d1 = __fmul_rn(d, (float)h[layout::k45_sc_off(j)]), m1 = __fmul_rn(mn, (float)h[12 + j]);
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                float v[8];
-#pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const int l = 8 * c + i;
-                    int q = half ? (qb[l] >> 4) : (qb[l] & 0xF);
-                    if (five) q += ((hb[l] >> (2 * G + half)) & 1) ? 16 : 0;
-                    v[i] = __fsub_rn(__fmul_rn(d1, (float)q), m1);
-                }
-                store_split8(a_hi, a_lo, r, 4 * half + c, v);
-            }
-        }
-        return;
-    }
-#pragma unroll 1
-    for (int c = 0; c < 8; c++) {
+    for (int c = 0; c < 4; c++) {
         float v[8];
 #pragma unroll
-        for (int i = 0; i < 8; i++) v[i] = dequant_elem(P.fmt, P.w, P.K, row, k0 + 8 * c + i);
+        for (int i = 0; i < 8; i++) {
+            const int l = 8 * c + i;  // element of the sub-block = byte l of the group
+            int q = (int)((qw[l >> 2] >> (8 * (l & 3) + 4 * part)) & 0xFu);
+            if (five) q += (int)((hw[l >> 2] >> (8 * (l & 3) + 2 * G + part)) & 1u) << 4;
+            v[i] = __fsub_rn(__fmul_rn(d1, (float)q), m1);
+        }
+        store_split8(a_hi, a_lo, r, 4 * part + c, v);
+    }
+}
+__device__ __forceinline__ void slice_generic(const PrefillGemmParams& P, long long row, int r, int k0, int part, unsigned char* a_hi,
+                                              unsigned char* a_lo) {
+#pragma unroll 1
+    for (int c = 4 * part; c < 4 * part + 4; c++) {
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = row < P.M ? dequant_elem(P.fmt, P.w, P.K, row, k0 + 8 * c + i) : 0.f;  // rows beyond the matrix: zeros
         store_split8(a_hi, a_lo, r, c, v);
     }
 }
@@ -208,7 +209,7 @@ prefill_gemm_kernel(const __grid_constant__ PrefillGemmParams P, const __grid_co
 
     if (tid == 0) {
         for (int s = 0; s < PF_STAGES; s++) {
-            mbar_init(full_a + 8 * s, 128);
+            mbar_init(full_a + 8 * s, PF_DQ_THREADS);
             mbar_init(full_b + 8 * s, 1);
             mbar_init(empty + 8 * s, 1);
         }
@@ -262,25 +263,32 @@ prefill_gemm_kernel(const __grid_constant__ PrefillGemmParams P, const __grid_co
             umma_commit(accum);  // arrives when everything issued above has completed (also after a bail-out)
         }
     } else {
-        // ---- weights: one row per thread, dequantised into the A planes ----
-        const int r = tid - 64;
+        // ---- weights: two threads per row, dequantised into the A planes ----
+        const int r = (tid - 64) & (PF_BM - 1), part = (tid - 64) >> 7;
         const long long row = (long long)m0 + r;
+        const bool fast = (P.fmt == SLAI_FMT_Q4_K || P.fmt == SLAI_FMT_Q5_K) && row < P.M;
+        SliceRegs cur = {}, nxt = {};
+        if (fast) slice_fetch(P, row, 0, part, cur);
         bool ok = true;
         for (int s = 0; s < nk && ok; s++) {
             const int st = s % PF_STAGES;
+            if (fast && s + 1 < nk) slice_fetch(P, row, (s + 1) * PF_BK, part, nxt);  // in flight during the wait and the arithmetic
             if (s >= PF_STAGES) ok = mbar_wait(empty + 8 * st, ((s / PF_STAGES) - 1) & 1, P);
             if (!ok) break;
-            dequant_slice(P, row, r, s * PF_BK, a_hi + st * PF_A_BYTES, a_lo + st * PF_A_BYTES);
+            if (fast) slice_emit(P, cur, r, s * PF_BK, part, a_hi + st * PF_A_BYTES, a_lo + st * PF_A_BYTES);
+            else slice_generic(P, row, r, s * PF_BK, part, a_hi + st * PF_A_BYTES, a_lo + st * PF_A_BYTES);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core's reads
             mbar_arrive(full_a + 8 * st);
+            cur = nxt;
         }
         // ---- epilogue: this thread's accumulator row, 16 tokens at a time ----
         if (mbar_wait(accum, 0, P)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int quad = warp & 3;              // a warp reads the 32 TMEM lanes of its quadrant
+            const int colpart = (warp - 2) >> 2;    // the two warps of a quadrant take alternate groups of 16 tokens
             const int orow = m0 + 32 * quad + lane;
             const float bias = (P.bias && orow < P.M) ? P.bias[orow] : 0.f;
-            for (int c0 = 0; c0 < NT; c0 += 16) {
+            for (int c0 = 16 * colpart; c0 < NT; c0 += 32) {
                 uint32_t v[16];
                 tmem_ld16(tmem_d + ((uint32_t)(32 * quad) << 16) + (uint32_t)c0, v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -301,6 +309,163 @@ prefill_gemm_kernel(const __grid_constant__ PrefillGemmParams P, const __grid_co
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(ncols) : "memory");
+}
+
+// ---- causal attention of a block of prompt tokens ---------------------------------------------------------------------
+// The decode step's attention serves one query token and streams that token's whole key / value history; run once per
+// prompt token it reads the caches T / 2 times over.  Here one CTA takes 16 consecutive query tokens of one head and walks
+// the positions they may attend to in tiles of 32: a tile of keys and values is brought into shared memory once (as f32)
+// and serves all 16 queries.  Warp w owns queries 4w .. 4w + 3; for the scores lane = position of the tile (a 128-bit read
+// of its own key row per four dimensions, the queries broadcast), then a streaming softmax per query (running maximum
+// and sum, ops/batched_multiquery_attention.rs:102-156 computes the same softmax over all positions at once), then for the
+// weighted sum of values lane = four output dimensions.  Plain f32 arithmetic, like the decode step's kernel.
+constexpr int PA_QT = 16, PA_KT = 32, PA_THREADS = 128, PA_MAXC = 2;  // head_size <= 128 * PA_MAXC
+
+template <typename T>
+__device__ __forceinline__ void pa_load_rows(const T* __restrict__ g, long long row_stride, int rows, int hs, float* s, int s_stride, int tid) {
+    constexpr int VEC = 16 / (int)sizeof(T);  // elements per 16-byte piece
+    const int ppr = hs / VEC;
+    for (int idx = tid; idx < PA_KT * ppr; idx += PA_THREADS) {
+        const int r = idx / ppr, c = idx - r * ppr;
+        float v[VEC];
+        if (r < rows) {
+            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(g + (long long)r * row_stride) + c);
+            if (sizeof(T) == 2) {
+                const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+                for (int i = 0; i < VEC / 2; i++) {
+                    const float2 f = __half22float2(h2[i]);
+                    v[2 * i] = f.x;
+                    v[2 * i + 1] = f.y;
+                }
+            } else {
+                const float* f = reinterpret_cast<const float*>(&raw);
+#pragma unroll
+                for (int i = 0; i < VEC; i++) v[i] = f[i];
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < VEC; i++) v[i] = 0.f;
+        }
+        float* dst = s + (size_t)r * s_stride + c * VEC;
+#pragma unroll
+        for (int i = 0; i < VEC; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(PA_THREADS)
+prefill_attn_kernel(const float* __restrict__ q, int q_ld, const T* __restrict__ kc, const T* __restrict__ vc, long long head_stride, int hs, int kv_mul,
+                    int pos0, int n_tokens, float* __restrict__ out, int out_ld) {
+    extern __shared__ __align__(16) float pa_sm[];
+    const int ks = hs + 4;              // key rows 4 floats apart modulo 32 banks: the lanes' 128-bit reads do not collide
+    float* q_s = pa_sm;                 // [PA_QT][hs], already divided by sqrt(hs)
+    float* k_s = q_s + PA_QT * hs;      // [PA_KT][hs + 4]
+    float* v_s = k_s + PA_KT * ks;      // [PA_KT][hs]
+    float* p_s = v_s + PA_KT * hs;      // [PA_QT][PA_KT]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int head = blockIdx.x, t0 = blockIdx.y * PA_QT;
+    const int nq = min(PA_QT, n_tokens - t0);
+    const int kvh = head / kv_mul;
+    const T* kbase = kc + (long long)kvh * head_stride;
+    const T* vbase = vc + (long long)kvh * head_stride;
+    const float inv = 1.0f / sqrtf((float)hs);
+    for (int i = tid; i < PA_QT * hs; i += PA_THREADS) {
+        const int tq = i / hs, d = i - tq * hs;
+        q_s[i] = tq < nq ? q[(size_t)(t0 + tq) * q_ld + (size_t)head * hs + d] * inv : 0.f;
+    }
+    float m[4], l[4], acc[4][PA_MAXC][4];
+#pragma unroll
+    for (int qi = 0; qi < 4; qi++) {
+        m[qi] = -INFINITY;
+        l[qi] = 0.f;
+#pragma unroll
+        for (int c = 0; c < PA_MAXC; c++) acc[qi][c][0] = acc[qi][c][1] = acc[qi][c][2] = acc[qi][c][3] = 0.f;
+    }
+    const int last_pos = pos0 + t0 + nq - 1;           // last position any query of this tile attends to
+    const int warp_last = pos0 + t0 + 4 * warp + 3;    // ... any query of this warp
+    for (int kt0 = 0; kt0 <= last_pos; kt0 += PA_KT) {
+        const int cnt = min(PA_KT, last_pos + 1 - kt0);
+        __syncthreads();  // the previous tile has been consumed (and, the first time round, q_s is complete)
+        pa_load_rows<T>(kbase + (long long)kt0 * hs, hs, cnt, hs, k_s, ks, tid);
+        pa_load_rows<T>(vbase + (long long)kt0 * hs, hs, cnt, hs, v_s, hs, tid);
+        __syncthreads();
+        if (kt0 > warp_last || 4 * warp >= nq) continue;  // nothing in this tile for this warp's queries (warp-uniform)
+        float sc[4] = {0.f, 0.f, 0.f, 0.f};
+        const float* kr = k_s + lane * ks;
+        const float* qr = q_s + 4 * warp * hs;
+        for (int d = 0; d < hs; d += 4) {
+            const float4 kv = *reinterpret_cast<const float4*>(kr + d);
+#pragma unroll
+            for (int qi = 0; qi < 4; qi++) {
+                const float4 qv = *reinterpret_cast<const float4*>(qr + qi * hs + d);
+                sc[qi] = fmaf(kv.x, qv.x, fmaf(kv.y, qv.y, fmaf(kv.z, qv.z, fmaf(kv.w, qv.w, sc[qi]))));
+            }
+        }
+#pragma unroll
+        for (int qi = 0; qi < 4; qi++) {
+            const int qpos = pos0 + t0 + 4 * warp + qi;
+            const bool valid = lane < cnt && kt0 + lane <= qpos && 4 * warp + qi < nq;
+            const float sv = valid ? sc[qi] : -INFINITY;
+            float mt = sv;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, o));
+            const float m_new = fmaxf(m[qi], mt);
+            const float pv = valid ? expf(sv - m_new) : 0.f;
+            float ps = pv;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+            const float resc = m[qi] == -INFINITY ? 0.f : expf(m[qi] - m_new);  // nothing accumulated yet: acc and l are zero anyway
+            l[qi] = l[qi] * resc + ps;
+            m[qi] = m_new;
+#pragma unroll
+            for (int c = 0; c < PA_MAXC; c++) {
+                acc[qi][c][0] *= resc; acc[qi][c][1] *= resc; acc[qi][c][2] *= resc; acc[qi][c][3] *= resc;
+            }
+            p_s[(4 * warp + qi) * PA_KT + lane] = pv;
+        }
+        __syncwarp();
+        const float* pr = p_s + 4 * warp * PA_KT;
+        for (int j = 0; j < cnt; j += 4) {
+            float4 pq[4];
+#pragma unroll
+            for (int qi = 0; qi < 4; qi++) pq[qi] = *reinterpret_cast<const float4*>(pr + qi * PA_KT + j);
+#pragma unroll
+            for (int jj = 0; jj < 4; jj++) {
+#pragma unroll
+                for (int c = 0; c < PA_MAXC; c++) {
+                    const int d = 128 * c + 4 * lane;
+                    if (d < hs) {
+                        const float4 vv = *reinterpret_cast<const float4*>(v_s + (size_t)(j + jj) * hs + d);  // rows >= cnt are zero
+#pragma unroll
+                        for (int qi = 0; qi < 4; qi++) {
+                            const float pw = jj == 0 ? pq[qi].x : jj == 1 ? pq[qi].y : jj == 2 ? pq[qi].z : pq[qi].w;
+                            acc[qi][c][0] = fmaf(pw, vv.x, acc[qi][c][0]);
+                            acc[qi][c][1] = fmaf(pw, vv.y, acc[qi][c][1]);
+                            acc[qi][c][2] = fmaf(pw, vv.z, acc[qi][c][2]);
+                            acc[qi][c][3] = fmaf(pw, vv.w, acc[qi][c][3]);
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    }
+#pragma unroll
+    for (int qi = 0; qi < 4; qi++) {
+        const int tq = 4 * warp + qi;
+        if (tq < nq) {
+#pragma unroll
+            for (int c = 0; c < PA_MAXC; c++) {
+                const int d = 128 * c + 4 * lane;
+                if (d < hs) {
+                    const float il = 1.0f / l[qi];  // position 0 is always attended to: l > 0
+                    *reinterpret_cast<float4*>(out + (size_t)(t0 + tq) * out_ld + (size_t)head * hs + d) =
+                        make_float4(acc[qi][c][0] * il, acc[qi][c][1] * il, acc[qi][c][2] * il, acc[qi][c][3] * il);
+                }
+            }
+        }
+    }
 }
 
 // ---- small kernels around the GEMMs ---------------------------------------------------------------------------------
@@ -488,6 +653,32 @@ int prefill_silu_split_launch(slai_ctx* ctx, const float* gate, const float* up,
 int prefill_embed_launch(slai_ctx* ctx, float* x, int dim, const int* d_tokens, int T, const float* table, const slai_qmatrix* qtable) {
     prefill_embed_kernel<<<dim3((dim + 255) / 256, T), 256, 0, ctx->stream>>>(x, dim, d_tokens, table, qtable ? qtable->fmt : 0,
                                                                              qtable ? qtable->data : nullptr);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    return SLAI_OK;
+}
+// Causal attention of prompt tokens pos0 .. pos0 + T - 1 over the caches (which already hold their keys and values).
+// Returns SLAI_ERR_UNSUPPORTED_FORMAT for head sizes the kernel does not take (the caller then uses the decode kernel).
+bool prefill_attention_supported(int head_size, int kv_f16, const void* kc, const void* vc, long long head_stride) {
+    const int esz = kv_f16 ? 2 : 4;
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(vc) | (uintptr_t)(head_stride * esz) | (uintptr_t)(head_size * esz);
+    return head_size % 8 == 0 && head_size <= 128 * PA_MAXC && (bits & 15) == 0;
+}
+int prefill_attention_launch(slai_ctx* ctx, const float* q, int q_ld, const void* kc, const void* vc, int kv_f16, long long head_stride, int head_size,
+                             int n_heads, int kv_mul, int pos0, int T, float* out, int out_ld) {
+    SLAI_REQUIRE(ctx, prefill_attention_supported(head_size, kv_f16, kc, vc, head_stride) && q_ld % 4 == 0 && out_ld % 4 == 0, SLAI_ERR_UNSUPPORTED_FORMAT,
+                 "prefill attention: head size %d / alignment not supported", head_size);
+    const size_t smem = ((size_t)PA_QT * head_size + (size_t)PA_KT * (head_size + 4) + (size_t)PA_KT * head_size + PA_QT * PA_KT) * 4;
+    const dim3 grid((unsigned)n_heads, (unsigned)((T + PA_QT - 1) / PA_QT));
+    static PerDeviceOnce attr;
+    if (attr.need(ctx->device)) {
+        SLAI_CHECK_CUDA(ctx, cudaFuncSetAttribute(prefill_attn_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+        SLAI_CHECK_CUDA(ctx, cudaFuncSetAttribute(prefill_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+        attr.set(ctx->device);
+    }
+    if (kv_f16)
+        prefill_attn_kernel<__half><<<grid, PA_THREADS, smem, ctx->stream>>>(q, q_ld, (const __half*)kc, (const __half*)vc, head_stride, head_size, kv_mul, pos0, T, out, out_ld);
+    else
+        prefill_attn_kernel<float><<<grid, PA_THREADS, smem, ctx->stream>>>(q, q_ld, (const float*)kc, (const float*)vc, head_stride, head_size, kv_mul, pos0, T, out, out_ld);
     SLAI_CHECK_CUDA(ctx, cudaGetLastError());
     return SLAI_OK;
 }
