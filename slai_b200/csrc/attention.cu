@@ -20,6 +20,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnParams P) {
 #ifdef SLAI_TRACE
     unsigned long long tl0 = slai_globaltimer(), tl1 = 0;
 #endif
+    // The grid is sized for the longest context; the blocks of splits the current context does not use leave at once,
+    // while the predecessor still runs, when the position is known not to be written by it.
+    if (P.early && P.batch == 0 && (int)blockIdx.y >= attn_splits(P, __ldcg(P.d_pos) + 1)) return;
     prefetch_plan_issue(P.ahead, (int)(blockIdx.x + gridDim.x * blockIdx.y), (int)(gridDim.x * gridDim.y), (int)threadIdx.x, ATT_THREADS);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the next kernel may start fetching its weights
@@ -166,6 +169,7 @@ static int attention_launch_inner(slai_ctx* ctx, const AttnLaunch& A) {
     }
 
     P.d_pos = A.d_pos;
+    P.early = A.pos_stable ? 1 : 0;
     P.out = A.out;
     P.ahead = A.ahead;
 #ifdef SLAI_TRACE

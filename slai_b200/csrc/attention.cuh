@@ -17,6 +17,7 @@ struct AttnParams {
     int n_heads, kv_mul, hs;  // kv_mul: query heads one work item serves (those of its virtual head)
     int kv_share = 1;         // virtual heads per cache head: virtual head v reads the keys and values of cache head v / kv_share
     const int* d_pos;
+    int early = 0;  // the position scalar is not written by the kernel launched before this one: it may be read before the wait
     int n_splits;   // most splits a KV head is cut into (stride of the partial buffers)
     int tile_pos;   // positions staged in shared memory at a time
     int vec16;      // rows can be copied in 16-byte pieces (alignment of bases, strides and row length)
@@ -293,9 +294,9 @@ __device__ __forceinline__ void attn_item(const AttnParams& P, int kvh, int spli
         P.part_ml[((size_t)head * P.n_splits + split) * 2] = st_s[4 * tid];
         P.part_ml[((size_t)head * P.n_splits + split) * 2 + 1] = st_s[4 * tid + 1];
     }
-    __threadfence();
     att_sync(bar_id);
     if (tid == 0) {
+        __threadfence();  // cumulative: orders the whole block's partials (seen through the barrier) before the ticket
         const unsigned int ticket = atomicAdd(&P.counters[kvh], 1u);
         *is_last_p = (ticket == (unsigned int)ns - 1);
         if (*is_last_p) P.counters[kvh] = 0;  // ready for the next launch

@@ -300,6 +300,7 @@ struct AttnLaunch {
     int pos0 = 0;
     long long q_batch_stride = 0, out_batch_stride = 0;
     unsigned int* batch_counters = nullptr;
+    bool pos_stable = false;  // *d_pos is not written by the kernel launched before this one (it may be read before the dependency wait)
 };
 size_t attention_scratch_bytes(slai_ctx* ctx, int n_heads, int kv_mul, int head_size, int max_pos);
 int attention_launch(slai_ctx* ctx, const AttnLaunch& A);

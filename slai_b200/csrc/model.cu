@@ -319,7 +319,7 @@ static int llama_record(slai_llama* m, int kind) {
             A.q = m->q; A.kcache = kc; A.vcache = vc; A.kv_dtype = c.kv_dtype;
             A.pos_stride = m->head_size; A.head_stride = (int64_t)c.seq_len * m->head_size;
             A.n_heads = m->n_q_local; A.kv_mul = m->kv_mul; A.head_size = m->head_size;
-            A.d_pos = d_pos; A.max_pos = c.seq_len - 1; A.out = m->xb; A.pdl = pdl;
+            A.d_pos = d_pos; A.max_pos = c.seq_len - 1; A.out = m->xb; A.pdl = pdl; A.pos_stable = true;
             A.scratch = m->attn_scratch; A.scratch_bytes = m->attn_scratch_bytes;
             A.ahead = plan_ahead(gu, 2, 0, cap);
             if ((rc = attention_launch(ctx, A))) return rc;
@@ -1000,7 +1000,7 @@ static int gpt2_record(slai_gpt2* m, int kind) {
             A.q = m->q; A.kcache = kc; A.vcache = vc; A.kv_dtype = c.kv_dtype;
             A.pos_stride = m->head_size; A.head_stride = (int64_t)c.n_seq * m->head_size;
             A.n_heads = c.n_head; A.kv_mul = 1; A.head_size = m->head_size; A.d_pos = d_pos; A.max_pos = c.n_seq - 1;
-            A.out = m->xb; A.pdl = pdl; A.scratch = m->attn_scratch; A.scratch_bytes = m->attn_scratch_bytes;
+            A.out = m->xb; A.pdl = pdl; A.pos_stable = true; A.scratch = m->attn_scratch; A.scratch_bytes = m->attn_scratch_bytes;
             if ((rc = attention_launch(ctx, A))) return rc;
             n++;
         }

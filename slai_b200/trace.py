@@ -114,16 +114,37 @@ def main():
     ap.add_argument("--model", default="7b", choices=["7b", "70b", "gpt2xl"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the architecture has (0 = all)")
     ap.add_argument("--json", action="store_true")
+    ap.add_argument("--tp", action="store_true", help="70b only: shard the model over the ranks of a torch.distributed launch "
+                    "(python -m torch.distributed.run --nproc-per-node N -m slai_b200.trace --model 70b --tp); rank 0 prints its timeline")
     a = ap.parse_args()
     if not os.path.exists(TRACE_LIB):
         sys.exit("build the trace library first: python -m slai_b200.build --trace")
     os.environ["SLAI_B200_LIB"] = TRACE_LIB
     from . import synth
     from .ops import Backend
-    backend = Backend(0)
+    rank, world = 0, 1
+    if a.tp:
+        import torch
+        import torch.distributed as dist
+        rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        dist.init_process_group("nccl")
+    backend = Backend(int(os.environ.get("LOCAL_RANK", "0")) if a.tp else 0)
     lib = backend.lib
     lib.slai_debug_timeline.restype = C.c_int
-    if a.model in ("7b", "70b"):
+    if a.tp:
+        import dataclasses
+        from . import tp
+        from .models import LLAMA2_70B
+        cfg = dataclasses.replace(LLAMA2_70B, n_layers=a.layers) if a.layers > 0 else LLAMA2_70B
+        if world > 1:
+            tp.join_group(backend, rank, world, tp.torch_broadcast)
+            tp.enable_peer_exchange(backend, world, tp.torch_all_gather, tp.torch_barrier)
+        m = tp.synthetic_llama_device_tp(backend, cfg, synth.FMT_Q4_K, synth.FMT_Q6_K, rank, world)
+        vocab = cfg.vocab_size
+        backend.synchronize()
+        tp.torch_barrier()
+    elif a.model in ("7b", "70b"):
         import dataclasses
         from .models import LLAMA2_7B, LLAMA2_70B, synthetic_llama_device
         cfg = LLAMA2_7B if a.model == "7b" else LLAMA2_70B
@@ -148,6 +169,12 @@ def main():
     rows = summarise(last)
     t_tok = (last[-1, 14] - last[0, 1]) * 1e-3
     names = [c[0] for c in COLS] + ["kernel", "period", "handover"]
+    if a.tp:  # every rank leaves the group the same way; only rank 0 reports
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+        if rank != 0:
+            return
     if a.json:
         print(json.dumps({"token_us": t_tok, "records_per_token": per_tok,
                           "kernels": [dict(zip(["name", "n"] + names, r)) for r in rows]}))
