@@ -17,7 +17,7 @@ struct AttnParams {
     int n_heads, kv_mul, hs;  // kv_mul: query heads one work item serves (those of its virtual head)
     int kv_share = 1;         // virtual heads per cache head: virtual head v reads the keys and values of cache head v / kv_share
     const int* d_pos;
-    int early = 0;  // the position scalar is not written by the kernel launched before this one: it may be read before the wait
+    int early = 0;  // the position scalar is final before this kernel's blocks can start (AttnLaunch::pos_stable): read it before the wait
     int n_splits;   // most splits a KV head is cut into (stride of the partial buffers)
     int tile_pos;   // positions staged in shared memory at a time
     int vec16;      // rows can be copied in 16-byte pieces (alignment of bases, strides and row length)

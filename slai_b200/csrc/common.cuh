@@ -300,7 +300,10 @@ struct AttnLaunch {
     int pos0 = 0;
     long long q_batch_stride = 0, out_batch_stride = 0;
     unsigned int* batch_counters = nullptr;
-    bool pos_stable = false;  // *d_pos is not written by the kernel launched before this one (it may be read before the dependency wait)
+    // *d_pos was written by a kernel that has completed before any block of this one can start, so it may be read before the
+    // dependency wait.  True inside a decode step: the scalar is written once per token, and the embedding kernel that
+    // follows neither starts before that write is complete nor lets its own dependents start before it has finished.
+    bool pos_stable = false;
 };
 size_t attention_scratch_bytes(slai_ctx* ctx, int n_heads, int kv_mul, int head_size, int max_pos);
 int attention_launch(slai_ctx* ctx, const AttnLaunch& A);

@@ -103,32 +103,6 @@ struct GemvParams {
 __device__ __forceinline__ void mbar_init(uint32_t a, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(a), "r"(count) : "memory");
 }
-__device__ __forceinline__ void mbar_expect_tx(uint32_t a, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(a), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t a, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(a), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait: returns false (and raises the error flag) if the phase does not complete.
-__device__ __noinline__ bool mbar_wait(uint32_t a, uint32_t parity, unsigned int limit, unsigned int* err_flag) {
-    for (unsigned int i = 0; i < limit; i++) {
-        if (mbar_try_wait(a, parity)) return true;
-        if (i > 1024) __nanosleep(64);
-    }
-    atomicExch(err_flag, 1u);
-    return false;
-}
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t mbar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(src), "r"(bytes), "r"(mbar)
-                 : "memory");
-}
 
 // ---- block-wide reductions used by the staging pass -----------------------------------------
 __device__ __forceinline__ float warp_sum(float x) {

@@ -92,11 +92,6 @@ def test_small_llama_logits_and_tokens(backend, fmt, out_fmt, kv_dtype):
     assert n_match > 10
 
 
-def backend_error_flag(backend):
-    """Bounded waits inside the kernels raise a device flag instead of hanging; slai_ctx_sync reports it."""
-    return backend.lib.slai_ctx_sync(backend.h)
-
-
 def test_llama_prefill_generate_equals_stepwise(backend):
     cfg = Llama2Config(dim=256, hidden_dim=512, n_layers=2, n_q_heads=4, n_kv_heads=4, vocab_size=500, seq_len=64)
     w = synthetic_llama_host(cfg, synth.FMT_Q4_K, seed=5, std=0.05, embd_std=1.0)
