@@ -28,6 +28,10 @@ namespace gemvk {
 using namespace frag;
 using namespace gemvfmt;
 
+// Build-time knobs of the measurements behind the shipped shape (SLAI_NVCC_EXTRA="-D..." python -m slai_b200.build):
+// warps per block, and the minimum number of blocks per SM the compiler sizes the registers for (2 = 64 registers per
+// thread at 16 warps, so that the next kernel's blocks are resident while this one runs).  16 warps / 1 block measured
+// fastest; 8 warps and 2 blocks per SM both lose more in the main loop than the early residency gains.
 #ifndef SLAI_GEMV_WARPS
 #define SLAI_GEMV_WARPS 16
 #endif
