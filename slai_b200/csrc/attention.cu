@@ -12,10 +12,14 @@
 
 using namespace attn;
 
+#ifndef SLAI_ATT_MINB
+#define SLAI_ATT_MINB 4
+#endif
+
 namespace {
 
 template <typename T, int MAXQ>
-__global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnParams P) {
+__global__ void __launch_bounds__(ATT_THREADS, SLAI_ATT_MINB) attn_kernel(const AttnParams P) {
     extern __shared__ __align__(16) unsigned char sm[];
 #ifdef SLAI_TRACE
     unsigned long long tl0 = slai_globaltimer(), tl1 = 0;

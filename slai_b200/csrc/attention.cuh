@@ -41,14 +41,14 @@ __device__ __forceinline__ void att_sync(int id) { asm volatile("bar.sync %0, %1
 // Shared memory of one item, in bytes: q | scores | running (max, sum, rescale) | flag | one tile buffer that holds
 // the K rows (padded by 16 bytes: the four threads of a position and the eight positions of a warp then hit 32
 // different banks) and, once the scores are done, the V rows.  The merge of the splits reuses the tile buffer for
-// the (max, sum) pairs of all splits.
+// the (max, sum) pairs of all splits, their weights and the partial sums of the merge's thread groups.
 __host__ __device__ inline size_t attn_k_stride(int hs, int esz) { return (size_t)hs * esz + 16; }
 __host__ __device__ inline size_t attn_head_bytes(int kv_mul, int hs, int tile_pos) {
     return (((size_t)kv_mul * hs + (size_t)kv_mul * tile_pos + 4 * (size_t)kv_mul + 4) * 4 + 15) & ~(size_t)15;
 }
 __host__ __device__ inline size_t attn_item_bytes(int kv_mul, int hs, int esz, int tile_pos, int n_splits) {
     size_t tile = tile_pos * attn_k_stride(hs, esz);
-    const size_t merge = (size_t)kv_mul * n_splits * 4 * 4;  // (max, sum) pairs of all splits, then their weights
+    const size_t merge = (size_t)kv_mul * n_splits * 4 * 4 + 4 * ATT_THREADS * 4;  // (max, sum) pairs of all splits, their weights, the groups' sums of the merge
     if (merge > tile) tile = merge;
     return attn_head_bytes(kv_mul, hs, tile_pos) + ((tile + 15) & ~(size_t)15);
 }
@@ -329,6 +329,49 @@ __device__ __forceinline__ void attn_item(const AttnParams& P, int kvh, int spli
         w_all[2 * i + 1] = w * l;
     }
     att_sync(bar_id);
+    if (ns > 32 && (hs & 3) == 0 && (hs >> 2) <= ATT_THREADS / 2) {
+        // Many splits (measured: pays from three rounds of sixteen loads on; with fewer the plain loop below is quicker).
+        // Threads as (group g, 16-byte chunk c of the head's output): group g adds the splits s = g, g + G, ... of its chunk
+        // (all of a thread's loads are independent: one trip to memory for up to 16 splits per group), the groups' sums
+        // meet in shared memory and are added in group order.  Fixed order throughout.
+        const int chunks = hs >> 2, G = ATT_THREADS / chunks;
+        const int c = tid % chunks, g = tid / chunks;
+        float* gsum = w_all + kv_mul * ns * 2;  // [G][hs]
+#pragma unroll 1
+        for (int h = 0; h < kv_mul; h++) {
+            const int head = kvh * kv_mul + h;
+            const float* wl = w_all + h * ns * 2;
+            float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (g < G) {
+                const float4* po = reinterpret_cast<const float4*>(P.part_o + ((size_t)head * P.n_splits) * hs) + c;
+#pragma unroll 1
+                for (int s0 = g; s0 < ns; s0 += 16 * G) {
+                    float4 o[16];
+#pragma unroll
+                    for (int u = 0; u < 16; u++) o[u] = s0 + u * G < ns ? __ldcg(po + (size_t)(s0 + u * G) * chunks) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int u = 0; u < 16; u++)
+                        if (s0 + u * G < ns) {
+                            const float w = wl[2 * (s0 + u * G)];
+                            if (w > 0.f) {
+                                num.x = fmaf(w, o[u].x, num.x); num.y = fmaf(w, o[u].y, num.y);
+                                num.z = fmaf(w, o[u].z, num.z); num.w = fmaf(w, o[u].w, num.w);
+                            }
+                        }
+                }
+                *reinterpret_cast<float4*>(gsum + g * hs + 4 * c) = num;
+            }
+            att_sync(bar_id);
+            if (tid < hs) {
+                float nsum = 0.f, den = 0.f;
+                for (int gg = 0; gg < G; gg++) nsum += gsum[gg * hs + tid];
+                for (int sp = 0; sp < ns; sp++) den += wl[2 * sp + 1];
+                P.out[(size_t)head * hs + tid] = nsum / den;
+            }
+            att_sync(bar_id);  // gsum is reused by the next head
+        }
+        return;
+    }
 #pragma unroll 1
     for (int i = tid; i < kv_mul * hs; i += ATT_THREADS) {
         const int h = i / hs, d = i - h * hs;
