@@ -165,22 +165,21 @@ __device__ __forceinline__ void attn_item(const AttnParams& P, int kvh, int spli
     Pieces pw;
     pw.init(row_bytes >> 4, tid);
 
+    // K goes to the tile buffer; V is requested in the same trip and waits in registers until K is done with.  The pieces of
+    // the next tile are requested as soon as this tile's V has left the registers, so that their trip to memory runs behind
+    // the softmax and the weighted sum.
+    uint4 kb[4], vb[4];
+    if (P.vec16 && t0 < t1) {
+        const int cnt0 = min(TP, t1 - t0);
+        load_pieces(kb, pw, kbase + (size_t)t0 * row_pitch, row_pitch, cnt0);
+        load_pieces(vb, pw, vbase + (size_t)t0 * row_pitch, row_pitch, cnt0);
+    }
 #pragma unroll 1
     for (int tt = t0; tt < t1; tt += TP) {
         const int cnt = min(TP, t1 - tt);
         if (tt != t0) att_sync(bar_id);  // the previous tile has been consumed
-        // K goes to the tile buffer; V is requested in the same trip and waits in registers until K is done with
-        uint4 vb[4];
-        {
-            if (P.vec16) {
-                uint4 kb[4];
-                load_pieces(kb, pw, kbase + (size_t)tt * row_pitch, row_pitch, cnt);
-                load_pieces(vb, pw, vbase + (size_t)tt * row_pitch, row_pitch, cnt);
-                store_pieces(kb, pw, k_s, k_stride, cnt);
-            } else {
-                copy_rows_u32(kbase + (size_t)tt * row_pitch, row_pitch, row_bytes, cnt, k_s, k_stride, tid);
-            }
-        }
+        if (P.vec16) store_pieces(kb, pw, k_s, k_stride, cnt);
+        else copy_rows_u32(kbase + (size_t)tt * row_pitch, row_pitch, row_bytes, cnt, k_s, k_stride, tid);
         if (tt == t0) {
 #pragma unroll
             for (int u = 0; u < 2 * MAXQ; u++) {
@@ -224,8 +223,16 @@ __device__ __forceinline__ void attn_item(const AttnParams& P, int kvh, int spli
         }
         att_sync(bar_id);
         // the K rows are done with: V takes their place (read by the last step of this tile)
-        if (P.vec16) store_pieces(vb, pw, k_s, row_bytes, cnt);
-        else copy_rows_u32(vbase + (size_t)tt * row_pitch, row_pitch, row_bytes, cnt, k_s, row_bytes, tid);
+        if (P.vec16) {
+            store_pieces(vb, pw, k_s, row_bytes, cnt);
+            if (tt + TP < t1) {
+                const int cn = min(TP, t1 - (tt + TP));
+                load_pieces(kb, pw, kbase + (size_t)(tt + TP) * row_pitch, row_pitch, cn);
+                load_pieces(vb, pw, vbase + (size_t)(tt + TP) * row_pitch, row_pitch, cn);
+            }
+        } else {
+            copy_rows_u32(vbase + (size_t)tt * row_pitch, row_pitch, row_bytes, cnt, k_s, row_bytes, tid);
+        }
         // running softmax per query head
 #pragma unroll 1
         for (int h = warp; h < kv_mul; h += ATT_WARPS) {
