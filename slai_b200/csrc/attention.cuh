@@ -1,5 +1,4 @@
-// Single-query attention over the KV cache, device side (see attention.cu for the operator).  Shared by the
-// stand-alone attention kernel and the persistent decode kernel, which runs four items per block of threads.
+// Single-query attention over the KV cache, device side (see attention.cu for the operator and the launches).
 #pragma once
 #include "common.cuh"
 
@@ -80,8 +79,8 @@ template <> struct Elem<float> {
 
 // Rows of a tile travel as pieces of type V (16 bytes, or 4 when something is not 16-byte aligned); thread `tid`
 // owns pieces tid, tid + 128, ...  A batch is NB pieces per thread: all its loads are issued before anything waits
-// for them, so a tile costs one trip to memory.  L2 loads (ld.global.cg): inside the persistent decode kernel the
-// newest row was written by another SM during the same launch, so L1 must not be trusted.
+// for them, so a tile costs one trip to memory.  L2 loads (ld.global.cg): the newest row was written by the kernel
+// launched just before this one, on other SMs.
 struct Pieces {  // (row, column) of this thread's four 16-byte pieces; the same for every tile of an item
     int r[4], c[4];
     __device__ __forceinline__ void init(int ppr, int tid) {

@@ -125,7 +125,8 @@ struct PerDeviceOnce {
 // Weights that a LATER kernel of the decode step will stream, pulled into L2 by the blocks of the current kernel as
 // soon as they start.  A decode kernel spends microseconds in phases that move no weight bytes (waiting for its
 // predecessor, staging its input vector, the epilogue); with the next kernel's weights requested one kernel ahead
-// the HBM stream runs through those phases and the next kernel's ring fills from L2.
+// the HBM stream runs through those phases and the next kernel's ring fills from L2.  Off unless SLAI_AHEAD_MB is set:
+// the main loop consumes no faster from L2 than from HBM, and the requests lengthen the hand-over (measured).
 // ------------------------------------------------------------------------------------------------
 struct PrefetchPlan {
     const char* ptr[3] = {nullptr, nullptr, nullptr};  // 16-byte aligned

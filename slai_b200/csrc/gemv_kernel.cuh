@@ -199,10 +199,9 @@ __device__ __forceinline__ float4 xchg_local(const GemvParams& P, int i, unsigne
 // Stage the activation vector: optional normalisation, power-of-two scaling so that max|v| lands in
 // [2^25, 2^26), rounding to integers, split into four base-256 digit planes (gemv_frag.cuh), and per-sub-block
 // digit sums (for the `- dmin*m * sum(v)` term of Q4_K / Q5_K and the -32 offset of Q6_K).  Returns 1/scale.
-// The vector is read once (L2 loads: inside the persistent kernel it was written by other SMs during the same
-// launch, so L1 must not be trusted) and kept in registers between the passes when K <= 12288; longer vectors are
-// read again in each pass.  The code is kept small on purpose (the digit pass is one rolled loop that rotates the
-// register copy): it runs once per phase, straight out of a cold instruction cache.
+// The vector is read once (L2 loads: it was written by the kernel launched just before, on other SMs) and kept in
+// registers between the passes when K <= 12288 (the digit pass is unrolled over the register copy, so that its
+// rounds overlap); longer vectors are read again in each pass, four loads in flight per thread.
 // XIN: the vector is the sum over ranks of an incoming tensor-parallel exchange (K <= 24576 so that it stays in
 // registers); block 0 also writes the sum to P.xsum_out.
 template <int SV_GRAN, bool HAS_LN, bool XIN>
@@ -405,8 +404,7 @@ __device__ __forceinline__ int seg_of_tile(const GemvParams& P, int tile) {
     if (P.nseg > 2 && tile >= P.seg[2].tile0) s = 2;
     return s;
 }
-// Segment `s` by value through selects: the parameters may live in registers (persistent decode kernel), where a
-// dynamically indexed array would be spilled to local memory.
+// Segment `s` by value through selects (a dynamically indexed copy of the parameter array would go to local memory).
 __device__ __forceinline__ GemvSeg seg_pick(const GemvParams& P, int s) {
     GemvSeg r = P.seg[0];
     if (P.nseg > 1 && s == 1) r = P.seg[1];

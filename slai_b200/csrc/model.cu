@@ -675,7 +675,7 @@ static int prefill_impl(M* m, RecordFn record, int vocab, int seq_len, const int
 
 // ---- prompt processing as GEMMs -----------------------------------------------------------------------------------------
 // The T prompt tokens go through every layer together (prefill.cu): per layer RmsNorm + fp16-pair split, q / k / v
-// GEMMs, RoPE + KV-cache write, causal attention (the decode kernel with one query token per blockIdx.z), output GEMM
+// GEMMs, RoPE + KV-cache write, causal attention (a tiled kernel of its own, 16 query tokens per CTA), output GEMM
 // with residual, RmsNorm + split, gate and up GEMMs, SiLU + split, down GEMM with residual.  Only the last token's
 // logits are needed: its row of the residual stream goes back into the decode state and the decode step's own final
 // norm + logits GEMV (+ greedy choice) run on it.
