@@ -148,7 +148,7 @@ def build_model(backend, seed=0):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate/up kernel on 2 x 11008 x 4096 Q4_K, from an ncu capture
-# of this benchmark (profiles/): 2 x 688 tiles x 16 steps x 2368-byte blocks = 52 137 984 bytes of weights (the 2.8 % above the
+# of `python -m slai_b200.microbench --fmt q4_k --M 11008 --K 4096 --pair` (summary under profiles/): 2 x 688 tiles x 16 steps x 2368-byte blocks = 52 137 984 bytes of weights (the 2.8 % above the
 # GGUF byte count being the unpacked scales) plus the vectors
 DOMINANT_KERNEL_DRAM_BYTES = 52_230_000
 
@@ -597,7 +597,7 @@ def main():
                                                    "(all 32 layers' pairs in turn, 1.6 GB > L2)",
                          "achieved": algo / per / 1e9, "peak": peak, "unit": "GB/s", "frac": algo / per / 1e9 / peak,
                          "traffic": DOMINANT_KERNEL_DRAM_BYTES, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of this "
-                         "kernel on this shape (one captured launch of this benchmark); algorithmic bytes %d" % algo,
+                         "kernel on this shape (captured launches of slai_b200.microbench --pair); algorithmic bytes %d" % algo,
                          "launches_timed": nl, "us_per_launch": per * 1e6, "peak_source": peak_src},
         }
         if gemv_table is not None:
