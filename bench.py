@@ -56,12 +56,14 @@ def measured_tensor_peak():
     return 1400.0, "fallback (1.4 PFLOP/s sustained, earlier measurement on this pool)"
 
 
-def prefill_record(cfg, n_tokens, seconds, sequential_ms_per_token=None):
+def prefill_record(cfg, n_tokens, seconds, sequential_ms_per_token=None, n_gpus=1):
     """Prompt processing of `n_tokens` through the tensor-core GEMM path: model FLOPs = 2 x layer weights x tokens (the
     logits matrix is applied to the last token only).  Every model product is issued as three fp16 products
     (hi*hi, hi*lo, lo*hi of fp16 operand pairs, f32 accumulation), so the tensor cores execute three times the model
-    FLOPs; both figures are given against the measured dense bf16 peak."""
+    FLOPs; both figures are given against the measured dense bf16 peak (of all `n_gpus` GPUs for a sharded model, whose
+    ranks each run their shard of every GEMM and sum the row-parallel products with an all-reduce)."""
     peak, src = measured_tensor_peak()
+    peak *= n_gpus
     layer_params = sum(r * c for r, c in cfg.matrix_shapes().values())
     flops = 2.0 * cfg.n_layers * layer_params * n_tokens
     rec = {"tokens": n_tokens, "seconds": seconds, "tok_s": n_tokens / seconds, "model_tflops": flops / seconds / 1e12,
@@ -386,9 +388,9 @@ def measure_tp(args, group, n_layers=0, prompt_len=1024, steps=None, warmup=None
     # not whenever each rank has finished building its shard.
     backend.synchronize()
     group.barrier()
-    # warm-up, overwritten by the timed pass: on one GPU the whole prompt, so that the prompt buffers (grown on demand and kept
-    # by the library) have their size before the timed pass, as for every prompt after a server's first
-    m.prefill(prompt[:-1] if world == 1 else prompt[:16], 0)
+    # warm-up, overwritten by the timed pass: the whole prompt, so that the prompt buffers (grown on demand and kept by the
+    # library) have their size before the timed pass, as for every prompt after a server's first
+    m.prefill(prompt[:-1], 0)
     backend.synchronize()
     group.barrier()
     t0 = time.perf_counter()
@@ -418,7 +420,7 @@ def measure_tp(args, group, n_layers=0, prompt_len=1024, steps=None, warmup=None
                           "prompt_len": PL, "decode_positions": [pos, pos + K - 1], "parallelism": f"tp{world}", "exchange": exchange,
                           "logits": "output matrix sharded by rows, logits all-gathered" if world > 1 else "whole output matrix"},
                "prefill_s": prefill_s,
-               "prefill": (prefill_record(cfg, PL - 1, prefill_s, ms / K) if world == 1 else "sequential single-token steps (the GEMM path serves one GPU)"),
+               "prefill": prefill_record(cfg, PL - 1, prefill_s, ms / K, n_gpus=world),
                "clocks": clocks, "launches_per_token": m.launches_per_token(), "gpu_launches": m.launches_per_token() * K,
                "ranks_agree": all(r == ids[0] for r in ids), "nccl_and_peer_exchange_bit_identical": identical,
                "roofline": {"bound": "hbm", "per_gpu_bytes_per_token": per_rank + kv, "achieved": (per_rank + kv) / t / 1e9, "peak": peak,

@@ -297,8 +297,9 @@ int slai_llama_generate_sampled(slai_llama* m, int32_t token, int32_t pos, int32
 /* Prompt processing: tokens[0..n) at positions pos0.. ; fills the KV cache.  If h_last_logits is non-NULL
  * it receives the logits of the last prompt token.  Blocking.  The reference feeds the prompt through its decode step
  * token by token (chat_llama2.rs:109-115); here prompts of 16 tokens or more go through every matrix together as
- * GEMMs on the tensor cores (quantised matrices whose column count is a multiple of 64, one GPU), shorter ones and
- * everything else through the decode step as there.  Same results within 1e-3 relative L2. */
+ * GEMMs on the tensor cores (quantised matrices whose column count is a multiple of 64; a sharded model sums the
+ * partial products of its row-parallel matrices with the group's all-reduce, so every rank must make the call),
+ * shorter ones and everything else through the decode step as there.  Same results within 1e-3 relative L2. */
 int slai_llama_prefill(slai_llama* m, const int32_t* h_tokens, int32_t n, int32_t pos0, float* h_last_logits);
 /* Debug/test access to Llama2State vectors: 0 x, 1 xb, 2 q, 3 hb, 4 logits.  Blocking. */
 int slai_llama_read_state(slai_llama* m, int which, float* h_out, int64_t n);

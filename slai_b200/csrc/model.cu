@@ -132,6 +132,7 @@ struct slai_llama {
     // prompt processing as GEMMs (prefill.cu): buffers for `pf_cap` tokens, grown on demand
     int pf_cap = 0, pf_attn_batch = 0;
     float *pf_x = nullptr, *pf_qkv = nullptr, *pf_q = nullptr, *pf_xb = nullptr, *pf_g = nullptr, *pf_u = nullptr;
+    float* pf_part = nullptr;  // sharded models: this rank's partial of a row-parallel product, [tokens][dim]
     __half *pf_hi = nullptr, *pf_lo = nullptr;
     int* pf_tokens = nullptr;
     void* pf_attn_scratch = nullptr;
@@ -143,7 +144,8 @@ static void llama_drop_prefill(slai_llama* m) {
     if (m->pf_cap) cudaStreamSynchronize(m->ctx->stream);
     cudaFree(m->pf_x); cudaFree(m->pf_qkv); cudaFree(m->pf_q); cudaFree(m->pf_xb); cudaFree(m->pf_g); cudaFree(m->pf_u);
     cudaFree(m->pf_hi); cudaFree(m->pf_lo); cudaFree(m->pf_tokens); cudaFree(m->pf_attn_scratch); cudaFree(m->pf_tickets);
-    m->pf_x = m->pf_qkv = m->pf_q = m->pf_xb = m->pf_g = m->pf_u = nullptr;
+    cudaFree(m->pf_part);
+    m->pf_x = m->pf_qkv = m->pf_q = m->pf_xb = m->pf_g = m->pf_u = m->pf_part = nullptr;
     m->pf_hi = m->pf_lo = nullptr;
     m->pf_tokens = nullptr;
     m->pf_attn_scratch = nullptr;
@@ -678,11 +680,14 @@ static int prefill_impl(M* m, RecordFn record, int vocab, int seq_len, const int
 // GEMMs, RoPE + KV-cache write, causal attention (a tiled kernel of its own, 16 query tokens per CTA), output GEMM
 // with residual, RmsNorm + split, gate and up GEMMs, SiLU + split, down GEMM with residual.  Only the last token's
 // logits are needed: its row of the residual stream goes back into the decode state and the decode step's own final
-// norm + logits GEMV (+ greedy choice) run on it.
+// norm + logits GEMV (+ greedy choice) run on it.  Sharded models run the same sequence on their shards; the two
+// row-parallel products of a layer (output and down projection) leave a partial [tokens][dim] on every rank, summed with
+// one all-reduce each and added to the residual stream, which stays identical on all ranks.
 static bool llama_prefill_eligible(const slai_llama* m, int n) {
     const char* e = getenv("SLAI_PREFILL_SEQUENTIAL");
     if (e && e[0] == '1') return false;
-    if (n < 16 || m->tp != 1 || m->kv_mul > 8) return false;
+    if (n < 16 || m->kv_mul > 8) return false;
+    if (m->tp > 1 && !m->ctx->tp_comm) return false;  // the partial products of a sharded model are summed with the group's all-reduce
     if (!m->out_norm || (!m->token_embd && !m->embd_q)) return false;
     for (auto& w : m->layers) {
         const slai_qmatrix* ms[7] = {w.wq, w.wk, w.wv, w.wo, w.wgate, w.wup, w.wdown};
@@ -703,6 +708,7 @@ static int llama_prefill_reserve(slai_llama* m, int t_pad, int attn_batch, size_
         bool ok = cudaMalloc(&m->pf_x, T * c.dim * 4) == cudaSuccess && cudaMalloc(&m->pf_qkv, T * (m->q_dim + 2 * m->kv_dim) * 4) == cudaSuccess &&
                   cudaMalloc(&m->pf_q, T * m->q_dim * 4) == cudaSuccess && cudaMalloc(&m->pf_xb, T * m->q_dim * 4) == cudaSuccess &&
                   cudaMalloc(&m->pf_g, T * m->hidden * 4) == cudaSuccess && cudaMalloc(&m->pf_u, T * m->hidden * 4) == cudaSuccess &&
+                  (m->tp == 1 || cudaMalloc(&m->pf_part, T * c.dim * 4) == cudaSuccess) &&
                   cudaMalloc(&m->pf_hi, T * kmax * 2) == cudaSuccess && cudaMalloc(&m->pf_lo, T * kmax * 2) == cudaSuccess &&
                   cudaMalloc(&m->pf_tokens, T * 4) == cudaSuccess && cudaMalloc(&m->pf_tickets, (size_t)attn_batch * n_kv * 4) == cudaSuccess &&
                   cudaMemsetAsync(m->pf_tickets, 0, (size_t)attn_batch * n_kv * 4, ctx->stream) == cudaSuccess;
@@ -759,6 +765,14 @@ static int llama_prefill_batched(slai_llama* m, const int32_t* h_tokens, int n, 
         G.out = out; G.ldo = ldo; G.out_off = off; G.resid = resid; G.ldr = ldr; G.bias = bias;
         return prefill_gemm_launch(ctx, G);
     };
+    // x += W * (the activations in pf_hi / pf_lo), W split by columns over the ranks of a sharded model
+    auto row_parallel = [&](const slai_qmatrix* w) -> int {
+        if (m->tp == 1) return gemm(w, c.dim, m->pf_x, c.dim, 0, m->pf_x, c.dim, nullptr);
+        int r = gemm(w, c.dim, m->pf_part, c.dim, 0, nullptr, 0, nullptr);
+        if (!r) r = tp_all_reduce_sum(ctx, m->pf_part, m->pf_part, (int64_t)n * c.dim);
+        if (!r) r = slai_add_assign(ctx, m->pf_x, m->pf_part, (int64_t)n * c.dim);
+        return r;
+    };
     for (int l = 0; l < c.n_layers; l++) {
         const LlamaLayer& w = m->layers[l];
         void* kc = (char*)m->kcache + (size_t)l * m->kv_layer_elems * esz;
@@ -791,13 +805,13 @@ static int llama_prefill_batched(slai_llama* m, const int32_t* h_tokens, int n, 
         }
         // x += Wo xb                                                           transformer.rs:352-355
         if ((rc = prefill_split_launch(ctx, m->pf_xb, m->q_dim, nullptr, 0.f, n, m->q_dim, m->pf_hi, m->pf_lo))) return rc;
-        if ((rc = gemm(w.wo, c.dim, m->pf_x, c.dim, 0, m->pf_x, c.dim, nullptr))) return rc;
+        if ((rc = row_parallel(w.wo))) return rc;
         // FFN                                                                  transformer.rs:356-365
         if ((rc = prefill_split_launch(ctx, m->pf_x, c.dim, w.ffn_norm, c.rms_norm_eps, n, c.dim, m->pf_hi, m->pf_lo))) return rc;
         if ((rc = gemm(w.wgate, m->hidden, m->pf_g, m->hidden, 0, nullptr, 0, nullptr))) return rc;
         if ((rc = gemm(w.wup, m->hidden, m->pf_u, m->hidden, 0, nullptr, 0, nullptr))) return rc;
         if ((rc = prefill_silu_split_launch(ctx, m->pf_g, m->pf_u, n, m->hidden, m->pf_hi, m->pf_lo))) return rc;
-        if ((rc = gemm(w.wdown, c.dim, m->pf_x, c.dim, 0, m->pf_x, c.dim, nullptr))) return rc;
+        if ((rc = row_parallel(w.wdown))) return rc;
     }
     // the last token's state goes back to the decode step's vectors; final norm, logits and the greedy choice as there
     SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(m->x, m->pf_x + (size_t)(n - 1) * c.dim, (size_t)c.dim * 4, cudaMemcpyDeviceToDevice, ctx->stream));
@@ -810,9 +824,12 @@ static int llama_prefill_batched(slai_llama* m, const int32_t* h_tokens, int n, 
         if ((rc = gemv_launch(ctx, L))) return rc;
     } else {
         GemvLaunch L;
-        L.fmt = wout->fmt; L.K = c.dim; L.nseg = 1; L.seg[0] = seg_of(wout, 0, c.vocab_size, nullptr, 0, 0);
-        L.v = m->x; L.out = m->logits; L.pro = PRO_RMS; L.norm_w = m->out_norm; L.eps = c.rms_norm_eps; L.epi = EPI_STORE; L.pdl = false;
+        const int vrows = m->out_sharded ? c.vocab_size / m->tp : c.vocab_size;  // a sharded output matrix: this rank's rows, then gathered
+        L.fmt = wout->fmt; L.K = c.dim; L.nseg = 1; L.seg[0] = seg_of(wout, 0, vrows, nullptr, 0, 0);
+        L.v = m->x; L.out = m->out_sharded ? m->logits_part : m->logits; L.pro = PRO_RMS; L.norm_w = m->out_norm; L.eps = c.rms_norm_eps;
+        L.epi = EPI_STORE; L.pdl = false;
         if ((rc = gemv_launch(ctx, L))) return rc;
+        if (m->out_sharded && (rc = tp_all_gather(ctx, m->logits_part, m->logits, vrows))) return rc;
     }
     if ((rc = launch_argmax(ctx, m->logits, c.vocab_size, m->sc.d + 3, false))) return rc;
     if (h_last_logits) SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(h_last_logits, m->logits, (size_t)c.vocab_size * 4, cudaMemcpyDeviceToHost, ctx->stream));

@@ -191,7 +191,17 @@ def _gpu_rank(rank, world, port, q):
     m = tp.llama_from_host_tp(backend, cfg, weights, synth.FMT_Q4_K, None, rank, world)
     tp.torch_barrier()
     peer = run(m)
-    q.put((rank, s, nccl[0], nccl[1], nccl[2], nccl[3], peer[0], peer[2], peer[3]))
+    # 3. a 20-token prompt through the tensor-core prompt pass on the shards (partial products summed with the group's
+    #    all-reduce), then decoding continues on the peer exchange
+    m3 = tp.llama_from_host_tp(backend, cfg, weights, synth.FMT_Q4_K, None, rank, world)
+    tp.torch_barrier()
+    prompt = np.random.default_rng(9).integers(0, cfg.vocab_size, size=20).astype(np.int32)
+    pf_logits = m3.prefill(prompt, 0, want_logits=True)
+    pf_gen = list(m3.generate(int(np.argmax(pf_logits)), 20, 12))
+    backend.synchronize()
+    dist.barrier()
+    m3.close()
+    q.put((rank, s, nccl[0], nccl[1], nccl[2], nccl[3], peer[0], peer[2], peer[3], pf_logits, pf_gen))
     dist.barrier()
     m.close()
     backend.check(backend.lib.slai_tp_shutdown(backend.h))
@@ -237,3 +247,17 @@ def test_two_gpu_tensor_parallel_llama_matches_oracle():
         assert np.array_equal(got[r][6], got[r][2])
         assert got[r][7] == got[r][4]
         assert got[r][8] == 3 + cfg.n_layers * 5 + 1 + 1 + 1   # + the token tick, + the logits gather
+    # sharded prompt pass: last logits against the oracle fed token by token, same continuation on both ranks
+    ref2 = oracle_llama(cfg, weights, synth.FMT_Q4_K, nthreads=4)
+    prompt = np.random.default_rng(9).integers(0, cfg.vocab_size, size=20).astype(np.int32)
+    for pos, t in enumerate(prompt):
+        want = ref2.forward(int(t), pos)
+    for r in range(2):
+        assert rel_l2(got[r][9], want) < 1e-3, r
+    assert np.array_equal(got[0][9], got[1][9]) and got[0][10] == got[1][10]
+    tok, want_gen = int(np.argmax(want)), []
+    for i in range(12):
+        rl = ref2.forward(tok, 20 + i)
+        tok = O.argmax(rl)
+        want_gen.append(tok)
+    assert sum(1 for a, b in zip(got[0][10], want_gen) if a == b) >= 10, (got[0][10], want_gen)
