@@ -341,6 +341,8 @@ int slai_gpt2_set_matrix(slai_gpt2* m, int weight_id, int layer, const slai_qmat
 int slai_gpt2_set_f32(slai_gpt2* m, int weight_id, int layer, const float* h_data, int64_t n);
 int slai_gpt2_decode(slai_gpt2* m, int32_t token, int32_t pos, float* h_logits, int32_t* next_token);
 int slai_gpt2_generate(slai_gpt2* m, int32_t token, int32_t pos, int32_t n, int32_t* h_tokens);
+/* As slai_llama_prefill: prompts of 16 tokens or more go through every matrix together as tensor-core GEMMs (quantised
+ * matrices whose column count is a multiple of 64, head size a multiple of 8), the rest token by token. */
 int slai_gpt2_prefill(slai_gpt2* m, const int32_t* h_tokens, int32_t n, int32_t pos0, float* h_last_logits);
 
 #ifdef __cplusplus

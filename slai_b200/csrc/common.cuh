@@ -370,6 +370,10 @@ size_t prefill_gemm_smem(int NT);
 int prefill_gemm_launch(slai_ctx* ctx, const PrefillGemm& G);
 int prefill_split_launch(slai_ctx* ctx, const float* x, int ldx, const float* norm_w, float eps, int T, int K, __half* hi, __half* lo);
 int prefill_silu_split_launch(slai_ctx* ctx, const float* gate, const float* up, int T, int H, __half* hi, __half* lo);
+int prefill_split_ln_launch(slai_ctx* ctx, const float* x, int ldx, const float* gamma, const float* beta, float eps, int T, int K, __half* hi,
+                            __half* lo);
+int prefill_gelu_split_launch(slai_ctx* ctx, const float* g, int T, int H, __half* hi, __half* lo);
+int prefill_add_rows_launch(slai_ctx* ctx, float* x, int dim, const float* table, int pos0, int T);
 int prefill_embed_launch(slai_ctx* ctx, float* x, int dim, const int* d_tokens, int T, const float* table, const slai_qmatrix* qtable);
 int rope_kv_store_launch(slai_ctx* ctx, float* q, const float* k, const float* v, int q_dim, int kv_dim, int head_size, const int* d_pos,
                          const float* theta, int neox, void* kcache, void* vcache, int kv_f16, long long kv_head_stride, bool pdl);

@@ -978,7 +978,22 @@ struct slai_gpt2 {
     size_t attn_scratch_bytes = 0;
     GraphSet graphs;
     int launches = 0;
+    // prompt processing as GEMMs (prefill.cu): buffers for `pf_cap` tokens, grown on demand
+    int pf_cap = 0;
+    float *pf_x = nullptr, *pf_qkv = nullptr, *pf_q = nullptr, *pf_xb = nullptr, *pf_ff = nullptr, *pf_theta0 = nullptr;
+    __half *pf_hi = nullptr, *pf_lo = nullptr;
+    int* pf_tokens = nullptr;
 };
+
+static void gpt2_drop_prefill(slai_gpt2* m) {
+    if (m->pf_cap) cudaStreamSynchronize(m->ctx->stream);
+    cudaFree(m->pf_x); cudaFree(m->pf_qkv); cudaFree(m->pf_q); cudaFree(m->pf_xb); cudaFree(m->pf_ff); cudaFree(m->pf_theta0);
+    cudaFree(m->pf_hi); cudaFree(m->pf_lo); cudaFree(m->pf_tokens);
+    m->pf_x = m->pf_qkv = m->pf_q = m->pf_xb = m->pf_ff = m->pf_theta0 = nullptr;
+    m->pf_hi = m->pf_lo = nullptr;
+    m->pf_tokens = nullptr;
+    m->pf_cap = 0;
+}
 
 static int gpt2_record(slai_gpt2* m, int kind) {
     slai_ctx* ctx = m->ctx;
@@ -1118,6 +1133,7 @@ SLAI_API int slai_gpt2_destroy(slai_gpt2* m) {
     cudaFree(m->wpe); cudaFree(m->lnf_g); cudaFree(m->lnf_b);
     cudaFree(m->x); cudaFree(m->xb); cudaFree(m->q); cudaFree(m->ff); cudaFree(m->logits);
     cudaFree(m->kcache); cudaFree(m->vcache); cudaFree(m->sc.d); cudaFree(m->d_history); cudaFree(m->attn_scratch);
+    gpt2_drop_prefill(m);
     delete m;
     return SLAI_OK;
 }
@@ -1190,8 +1206,111 @@ SLAI_API int slai_gpt2_generate(slai_gpt2* m, int32_t token, int32_t pos, int32_
     SLAI_ENTER(m->ctx);
     return generate_impl(m, gpt2_record, m->cfg.n_vocab, m->cfg.n_seq, token, pos, n, h_tokens);
 }
+// ---- prompt processing as GEMMs ---------------------------------------------------------------------------------------
+// The T prompt tokens go through every layer together, as for Llama (prefill.cu): per layer LayerNorm (gamma, beta) +
+// fp16-pair split, the fused q/k/v GEMM with its bias, cache write (the rotation kernel with a table of zero angles: the
+// identity), tiled causal attention, projection GEMM with bias and residual, LayerNorm + split, feed-forward GEMM with
+// bias, GELU + split, second feed-forward GEMM with bias and residual (models/gpt2/cpu.rs:225-383 for one token).
+static bool gpt2_prefill_eligible(const slai_gpt2* m, int n) {
+    const char* e = getenv("SLAI_PREFILL_SEQUENTIAL");
+    if (e && e[0] == '1') return false;
+    if (n < 16 || !m->wte || !m->wpe || !m->lnf_g || !m->lnf_b) return false;
+    const size_t esz = m->cfg.kv_dtype == SLAI_KV_F16 ? 2 : 4;
+    (void)esz;
+    if (!prefill_attention_supported(m->head_size, m->cfg.kv_dtype == SLAI_KV_F16, m->kcache, m->vcache, (long long)m->cfg.n_seq * m->head_size) ||
+        m->cfg.n_embd % 4 != 0)
+        return false;
+    for (auto& w : m->layers) {
+        const slai_qmatrix* ms[4] = {w.w_qkv, w.w_proj, w.w_fc, w.w_fcproj};
+        for (auto* q : ms)
+            if (!q || q->fmt == SLAI_FMT_F32 || q->ncols % 64 != 0) return false;
+        if (!w.ln1_g || !w.ln1_b || !w.ln2_g || !w.ln2_b || !w.b_qkv || !w.b_proj || !w.b_fc || !w.b_fcproj) return false;
+    }
+    return true;
+}
+
+static int gpt2_prefill_batched(slai_gpt2* m, const int32_t* h_tokens, int n, int pos0, float* h_last_logits) {
+    slai_ctx* ctx = m->ctx;
+    const slai_gpt2_config& c = m->cfg;
+    const int E = c.n_embd, F = c.ff_len;
+    const int NT = std::min(256, (n + 15) / 16 * 16);
+    const int t_pad = (n + NT - 1) / NT * NT;
+    const size_t kmax = (size_t)std::max(E, F);
+    if (t_pad > m->pf_cap) gpt2_drop_prefill(m);
+    if (!m->pf_cap) {
+        const size_t T = (size_t)t_pad;
+        bool ok = cudaMalloc(&m->pf_x, T * E * 4) == cudaSuccess && cudaMalloc(&m->pf_qkv, T * 3 * E * 4) == cudaSuccess &&
+                  cudaMalloc(&m->pf_q, T * E * 4) == cudaSuccess && cudaMalloc(&m->pf_xb, T * E * 4) == cudaSuccess &&
+                  cudaMalloc(&m->pf_ff, T * F * 4) == cudaSuccess && cudaMalloc(&m->pf_hi, T * kmax * 2) == cudaSuccess &&
+                  cudaMalloc(&m->pf_lo, T * kmax * 2) == cudaSuccess && cudaMalloc(&m->pf_tokens, T * 4) == cudaSuccess &&
+                  cudaMalloc(&m->pf_theta0, (size_t)m->head_size * 4) == cudaSuccess &&
+                  cudaMemsetAsync(m->pf_theta0, 0, (size_t)m->head_size * 4, ctx->stream) == cudaSuccess;
+        if (!ok) {
+            cudaGetLastError();
+            gpt2_drop_prefill(m);
+            return slai_set_error(ctx, SLAI_ERR_OOM, "prefill: cannot allocate buffers for %d tokens", t_pad);
+        }
+        m->pf_cap = t_pad;
+    }
+    int rc;
+    const size_t esz = c.kv_dtype == SLAI_KV_F16 ? 2 : 4;
+    SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(m->pf_tokens, h_tokens, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream));
+    SLAI_CHECK_CUDA(ctx, cudaMemsetAsync(m->pf_hi, 0, (size_t)m->pf_cap * kmax * 2, ctx->stream));  // rows beyond the prompt stay zero
+    SLAI_CHECK_CUDA(ctx, cudaMemsetAsync(m->pf_lo, 0, (size_t)m->pf_cap * kmax * 2, ctx->stream));
+    // x = wte[:,tok] + wpe[:,pos]                                              gpt2/cpu.rs:227-228
+    if ((rc = prefill_embed_launch(ctx, m->pf_x, E, m->pf_tokens, n, nullptr, m->wte))) return rc;
+    if ((rc = prefill_add_rows_launch(ctx, m->pf_x, E, m->wpe, pos0, n))) return rc;
+    auto gemm = [&](const slai_qmatrix* w, int rows, float* out, int ldo, const float* resid, int ldr, const float* bias) {
+        PrefillGemm G;
+        int nt = NT;
+        const int m_tiles = (rows + 127) / 128;
+        while (nt > 64 && (nt / 2) % 16 == 0 && t_pad % (nt / 2) == 0 && m_tiles * (t_pad / nt) * 2 <= ctx->sm_count) nt /= 2;
+        G.w = w; G.rows = rows; G.x_hi = m->pf_hi; G.x_lo = m->pf_lo; G.T = n; G.t_pad = t_pad; G.NT = nt;
+        G.out = out; G.ldo = ldo; G.out_off = 0; G.resid = resid; G.ldr = ldr; G.bias = bias;
+        return prefill_gemm_launch(ctx, G);
+    };
+    const long long kv_head_stride = (long long)c.n_seq * m->head_size;
+    for (int l = 0; l < c.n_layer; l++) {
+        const Gpt2Layer& w = m->layers[l];
+        void* kc = (char*)m->kcache + (size_t)l * m->kv_layer_elems * esz;
+        void* vc = (char*)m->vcache + (size_t)l * m->kv_layer_elems * esz;
+        if ((rc = prefill_split_ln_launch(ctx, m->pf_x, E, w.ln1_g, w.ln1_b, c.layernorm_eps, n, E, m->pf_hi, m->pf_lo))) return rc;
+        if ((rc = gemm(w.w_qkv, 3 * E, m->pf_qkv, 3 * E, nullptr, 0, w.b_qkv))) return rc;
+        if ((rc = prefill_rope_kv_launch(ctx, m->pf_qkv, 3 * E, E, E, m->head_size, pos0, n, m->pf_theta0, 0, m->pf_q, kc, vc,
+                                         c.kv_dtype == SLAI_KV_F16, kv_head_stride)))
+            return rc;
+        if ((rc = prefill_attention_launch(ctx, m->pf_q, E, kc, vc, c.kv_dtype == SLAI_KV_F16, kv_head_stride, m->head_size, c.n_head, 1, pos0, n,
+                                           m->pf_xb, E)))
+            return rc;
+        if ((rc = prefill_split_launch(ctx, m->pf_xb, E, nullptr, 0.f, n, E, m->pf_hi, m->pf_lo))) return rc;
+        if ((rc = gemm(w.w_proj, E, m->pf_x, E, m->pf_x, E, w.b_proj))) return rc;
+        if ((rc = prefill_split_ln_launch(ctx, m->pf_x, E, w.ln2_g, w.ln2_b, c.layernorm_eps, n, E, m->pf_hi, m->pf_lo))) return rc;
+        if ((rc = gemm(w.w_fc, F, m->pf_ff, F, nullptr, 0, w.b_fc))) return rc;
+        if ((rc = prefill_gelu_split_launch(ctx, m->pf_ff, n, F, m->pf_hi, m->pf_lo))) return rc;
+        if ((rc = gemm(w.w_fcproj, E, m->pf_x, E, m->pf_x, E, w.b_fcproj))) return rc;
+    }
+    // the last token's state goes back to the decode step's vector; final norm, logits and the greedy choice as there
+    SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(m->x, m->pf_x + (size_t)(n - 1) * E, (size_t)E * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    {
+        GemvLaunch L;
+        L.fmt = m->wte->fmt; L.K = E; L.nseg = 1; L.seg[0] = seg_of(m->wte, 0, c.n_vocab, nullptr, 0, 0);
+        L.v = m->x; L.out = m->logits; L.pro = PRO_LN; L.norm_w = m->lnf_g; L.norm_b = m->lnf_b; L.eps = c.layernorm_eps;
+        L.epi = EPI_STORE; L.pdl = false;
+        if ((rc = gemv_launch(ctx, L))) return rc;
+    }
+    if ((rc = launch_argmax(ctx, m->logits, c.n_vocab, m->sc.d + 3, false))) return rc;
+    if (h_last_logits) SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(h_last_logits, m->logits, (size_t)c.n_vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return slai_check_wait_flag(ctx);
+}
+
 SLAI_API int slai_gpt2_prefill(slai_gpt2* m, const int32_t* h_tokens, int32_t n, int32_t pos0, float* h_last_logits) {
     if (!m) return SLAI_ERR_INVALID_ARG;
     SLAI_ENTER(m->ctx);
+    if (h_tokens && n >= 16 && pos0 >= 0 && pos0 + n <= m->cfg.n_seq && gpt2_prefill_eligible(m, n)) {
+        for (int i = 0; i < n; i++)
+            SLAI_REQUIRE(m->ctx, h_tokens[i] >= 0 && h_tokens[i] < m->cfg.n_vocab, SLAI_ERR_INVALID_ARG, "prefill: token %d out of range", h_tokens[i]);
+        return gpt2_prefill_batched(m, h_tokens, n, pos0, h_last_logits);
+    }
     return prefill_impl(m, gpt2_record, m->cfg.n_vocab, m->cfg.n_seq, h_tokens, n, pos0, h_last_logits);
 }

@@ -131,13 +131,23 @@ __device__ __forceinline__ void store_split8(unsigned char* a_hi, unsigned char*
 }
 
 // Half `part` (32 elements = one sub-block of Q4_K / Q5_K) of the slice [k0, k0 + 64) of row `row`.  For Q4_K / Q5_K the
-// packed bytes are fetched into registers (`slice_fetch`) a stage before they are turned into operand rows (`slice_emit`),
-// so that the loads' latency runs behind the previous stage's arithmetic; the other formats go element by element.
+// and one 32-element block of Q8_0 the packed bytes are fetched into registers (`slice_fetch`) a stage before they are
+// turned into operand rows (`slice_emit`), so that the loads' latency runs behind the previous stage's arithmetic; Q6_K
+// goes element by element.
 struct SliceRegs {
     uint4 q[2], hq[2];     // the 32 nibble bytes of the 64-element group, the row's 32 high-bit bytes (Q5_K)
     uint32_t dd, sc, mb;   // f16 d | f16 dmin, scale and minimum of this thread's sub-block
 };
 __device__ __forceinline__ void slice_fetch(const PrefillGemmParams& P, long long row, int k0, int part, SliceRegs& R) {
+    if (P.fmt == SLAI_FMT_Q8_0) {  // a step is four 32-element blocks; this thread's block is 32 consecutive bytes of the lane-ordered region
+        const int r16 = (int)(row & 15), e = (k0 & 127) + 32 * part, b8 = e >> 5;
+        const uint8_t* b = P.w + (row >> 4) * P.tile_bytes + (long long)(k0 >> 7) * 2176;
+        R.dd = __ldg(reinterpret_cast<const unsigned short*>(b + 8 * r16 + 2 * b8));
+        const uint4* q = reinterpret_cast<const uint4*>(b + layout::qbyte_off(128, r16, 32 * b8));
+        R.q[0] = __ldg(q);
+        R.q[1] = __ldg(q + 1);
+        return;
+    }
     const bool five = P.fmt == SLAI_FMT_Q5_K;
     const int r16 = (int)(row & 15), G = (k0 >> 6) & 3;
     const uint8_t* b = P.w + (row >> 4) * P.tile_bytes + (long long)(k0 >> 8) * layout::step_bytes(P.fmt);
@@ -156,6 +166,21 @@ __device__ __forceinline__ void slice_fetch(const PrefillGemmParams& P, long lon
 }
 __device__ __forceinline__ void slice_emit(const PrefillGemmParams& P, const SliceRegs& R, int r, int k0, int part, unsigned char* a_hi,
                                            unsigned char* a_lo) {
+    if (P.fmt == SLAI_FMT_Q8_0) {  // q * scale (quantization.rs:38-41)
+        const float d = dev_h2f(R.dd);
+        const uint32_t qw8[8] = {R.q[0].x, R.q[0].y, R.q[0].z, R.q[0].w, R.q[1].x, R.q[1].y, R.q[1].z, R.q[1].w};
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int l = 8 * c + i;
+                v[i] = __fmul_rn((float)(int)(signed char)((qw8[l >> 2] >> (8 * (l & 3))) & 0xFFu), d);
+            }
+            store_split8(a_hi, a_lo, r, 4 * part + c, v);
+        }
+        return;
+    }
     const bool five = P.fmt == SLAI_FMT_Q5_K;
     const int G = (k0 >> 6) & 3;
     const float d1 = __fmul_rn(dev_h2f(R.dd & 0xFFFFu), (float)R.sc), m1 = __fmul_rn(dev_h2f(R.dd >> 16), (float)R.mb);
@@ -266,7 +291,7 @@ prefill_gemm_kernel(const __grid_constant__ PrefillGemmParams P, const __grid_co
         // ---- weights: two threads per row, dequantised into the A planes ----
         const int r = (tid - 64) & (PF_BM - 1), part = (tid - 64) >> 7;
         const long long row = (long long)m0 + r;
-        const bool fast = (P.fmt == SLAI_FMT_Q4_K || P.fmt == SLAI_FMT_Q5_K) && row < P.M;
+        const bool fast = (P.fmt == SLAI_FMT_Q4_K || P.fmt == SLAI_FMT_Q5_K || P.fmt == SLAI_FMT_Q8_0) && row < P.M;
         SliceRegs cur = {}, nxt = {};
         if (fast) slice_fetch(P, row, 0, part, cur);
         bool ok = true;
@@ -504,6 +529,47 @@ __global__ void prefill_split_kernel(const float* __restrict__ x, int ldx, const
     }
 }
 
+// Row t of X after LayerNorm with gamma / beta (ops/layernorm.rs:104-111 and the caller's scale and shift,
+// models/gpt2/cpu.rs:239-240) as fp16 hi / lo planes [T_pad][K]; same arithmetic as the decode step's fused prologue.
+__global__ void prefill_split_ln_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ gamma, const float* __restrict__ beta, float eps,
+                                        int K, __half* __restrict__ hi, __half* __restrict__ lo) {
+    __shared__ float sh[32];
+    const int t = blockIdx.x;
+    const float* xr = x + (size_t)t * ldx;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < K; i += blockDim.x) s += xr[i];
+    const float mean = block_sum256(s, sh) / (float)K;
+    float v = 0.f;
+    for (int i = threadIdx.x; i < K; i += blockDim.x) {
+        const float d = xr[i] - mean;
+        v += d * d;
+    }
+    v = block_sum256(v, sh);
+    const float mul = 1.0f / sqrtf(v / (float)K + eps);
+    for (int i = threadIdx.x; i < K; i += blockDim.x) {
+        float y = __fmul_rn(__fmul_rn(xr[i] - mean, mul), gamma[i]);
+        if (beta) y += beta[i];
+        store_hi_lo(hi, lo, (size_t)t * K + i, y);
+    }
+}
+
+// gelu (ops/unary.rs:81-85) of [T][H] straight into the hi / lo planes of the next GEMM's input.
+__global__ void prefill_gelu_split_kernel(const float* __restrict__ g, int H, __half* __restrict__ hi, __half* __restrict__ lo) {
+    const int t = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= H) return;
+    const float x = g[(size_t)t * H + i];
+    const float A = 0.044715f, Sq = 0.7978846f;
+    store_hi_lo(hi, lo, (size_t)t * H + i, 0.5f * x * (1.0f + tanhf(Sq * x * (1.0f + A * x * x))));
+}
+
+// x[t] += row (pos0 + t) of a table of position vectors (models/gpt2/cpu.rs:227-228).
+__global__ void prefill_add_rows_kernel(float* __restrict__ x, int dim, const float* __restrict__ table, int pos0) {
+    const int t = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < dim) x[(size_t)t * dim + i] += table[(size_t)(pos0 + t) * dim + i];
+}
+
 // hb = up * gate / (1 + exp(-gate)) (ops/silu.rs:50-58) straight into the hi / lo planes of the down projection's input.
 __global__ void prefill_silu_split_kernel(const float* __restrict__ gate, const float* __restrict__ up, int H, __half* __restrict__ hi,
                                           __half* __restrict__ lo) {
@@ -642,6 +708,22 @@ int prefill_gemm_launch(slai_ctx* ctx, const PrefillGemm& G) {
 
 int prefill_split_launch(slai_ctx* ctx, const float* x, int ldx, const float* norm_w, float eps, int T, int K, __half* hi, __half* lo) {
     prefill_split_kernel<<<T, 256, 0, ctx->stream>>>(x, ldx, norm_w, eps, K, hi, lo);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    return SLAI_OK;
+}
+int prefill_split_ln_launch(slai_ctx* ctx, const float* x, int ldx, const float* gamma, const float* beta, float eps, int T, int K, __half* hi,
+                            __half* lo) {
+    prefill_split_ln_kernel<<<T, 256, 0, ctx->stream>>>(x, ldx, gamma, beta, eps, K, hi, lo);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    return SLAI_OK;
+}
+int prefill_gelu_split_launch(slai_ctx* ctx, const float* g, int T, int H, __half* hi, __half* lo) {
+    prefill_gelu_split_kernel<<<dim3((H + 255) / 256, T), 256, 0, ctx->stream>>>(g, H, hi, lo);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    return SLAI_OK;
+}
+int prefill_add_rows_launch(slai_ctx* ctx, float* x, int dim, const float* table, int pos0, int T) {
+    prefill_add_rows_kernel<<<dim3((dim + 255) / 256, T), 256, 0, ctx->stream>>>(x, dim, table, pos0);
     SLAI_CHECK_CUDA(ctx, cudaGetLastError());
     return SLAI_OK;
 }

@@ -79,3 +79,36 @@ def test_prefill_falls_back_for_short_prompts_and_odd_widths(backend):
     for pos, t in enumerate(prompt):
         lb, _ = b.forward_logits(pos, int(t))
     assert np.array_equal(la, lb)
+
+
+@pytest.mark.parametrize("kv_dtype,n_embd,n_head", [(_lib.KV_F16, 256, 4), (_lib.KV_F32, 192, 3)])
+def test_gpt2_prompt_pass_matches_the_sequential_pass_and_the_oracle(backend, monkeypatch, kv_dtype, n_embd, n_head):
+    """GPT-2's prompt pass as GEMMs (LayerNorm + bias + GELU variants of the Llama pass): last logits against the oracle fed
+    token by token and against the library's own sequential pass, same greedy continuation, continuing from a later
+    position too."""
+    from slai_b200.models import Gpt2Params, gpt2_from_host, synthetic_gpt2_host
+    from helpers import oracle_gpt2
+    p = Gpt2Params(n_vocab=700, n_seq=96, n_embd=n_embd, n_head=n_head, n_layer=2, ff_len=4 * n_embd, kv_dtype=kv_dtype)
+    w = synthetic_gpt2_host(p, seed=6, std=0.08, bias_std=0.05)
+    rng = np.random.default_rng(8)
+    prompt = rng.integers(0, p.n_vocab, size=40).astype(np.int32)
+    batched = gpt2_from_host(backend, p, w)
+    lg_b = batched.prefill(prompt, 0, want_logits=True)
+    ref = oracle_gpt2(p, w, kv_f16=(kv_dtype == _lib.KV_F16))
+    for pos, t in enumerate(prompt):
+        want = ref.forward(int(t), pos)
+    assert rel_l2(lg_b, want) < 1e-3
+    monkeypatch.setenv("SLAI_PREFILL_SEQUENTIAL", "1")
+    seq = gpt2_from_host(backend, p, w)
+    lg_s = seq.prefill(prompt, 0, want_logits=True)
+    monkeypatch.delenv("SLAI_PREFILL_SEQUENTIAL")
+    assert rel_l2(lg_b, lg_s) < 1e-3
+    tok = int(np.argmax(lg_s))
+    assert list(batched.generate(tok, 40, 20)) == list(seq.generate(tok, 40, 20))
+    # a second block of the prompt from position 60 on (attends to everything before it)
+    more = rng.integers(0, p.n_vocab, size=20).astype(np.int32)
+    la = batched.prefill(more, 60, want_logits=True)
+    monkeypatch.setenv("SLAI_PREFILL_SEQUENTIAL", "1")
+    lb = seq.prefill(more, 60, want_logits=True)
+    monkeypatch.delenv("SLAI_PREFILL_SEQUENTIAL")
+    assert rel_l2(la, lb) < 1e-3
