@@ -190,6 +190,18 @@ impl<'a> LlmContext<'a> {
         let mut pass = self.backend.begin_submission();
         self.gemv_quant.launch(self.backend, &mut pass, out, a, b)
     }
+    /// The feed-forward front half of a Llama layer as one kernel: `out = silu(w_gate n(x)) * (w_up n(x))`, `n` = RmsNorm by
+    /// `norm_w` (None: `x` as it is).  Stands for the four dispatches of transformer.rs:356-361.
+    pub fn ffn_gate_up<'b>(&self, out: impl Into<ViewMut<'b, f32>>, w_gate: &GpuQuantMatrix, w_up: &GpuQuantMatrix, x: impl Into<View<'b, f32>>,
+                           norm_w: Option<View<'b, f32>>, eps: f32) -> Result<(), B200Error> {
+        let (out, x) = (out.into(), x.into());
+        let [rows, cols] = w_gate.shape();
+        if w_up.shape() != [rows, cols] || x.len() != cols || out.len() != rows || norm_w.map_or(false, |w| w.len() != cols) {
+            return Err(B200Error::Shape("ffn_gate_up: shapes differ".into()));
+        }
+        let nw = norm_w.map_or(std::ptr::null(), |w| w.ptr);
+        self.backend.check(unsafe { sys::slai_ffn_gate_up(self.backend.h, out.ptr, w_gate.h, w_up.h, x.ptr, nw, eps) })
+    }
     /// `LlmContext::add_assign` (context.rs:428-441).
     pub fn add_assign<'b>(&self, a: impl Into<ViewMut<'b, f32>>, b: impl Into<View<'b, f32>>) -> Result<(), B200Error> {
         let (a, b) = (a.into(), b.into());
