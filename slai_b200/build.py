@@ -10,7 +10,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libslai_b200.so")
-SOURCES = ["gemv.cu", "attention.cu", "ops.cu", "model.cu", "tp.cu", "sampler.cu", "prefill.cu"]
+SOURCES = ["gemv.cu", "gemv_batch.cu", "attention.cu", "ops.cu", "model.cu", "tp.cu", "sampler.cu", "prefill.cu"]
 HEADERS = ["common.cuh", "dequant.cuh", "gemv_frag.cuh", "gemv_formats.cuh", "gemv_kernel.cuh", "attention.cuh", "layout.cuh", os.path.join("..", "..", "include", "slai_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-fvisibility=hidden"]

@@ -257,6 +257,72 @@ struct K45 {
         accB = prim::fma(dB, combine(PB0, PB1, L), accB);
         accB = prim::fma(-mnB, (float)(cq[2] * 128 + cq[3]) * L.wq, accB);
     }
+    // The same step against NV staged vectors at once (vector v's digits `bvs` bytes after vector v-1's for the lanes that
+    // read digits, its sum table `svs` bytes after): the packed weights are loaded and masked once, every vector adds its
+    // own MMAs.  Per vector the arithmetic, and its order, is that of `compute`.
+    template <int NV>
+    SLAI_HD static void compute_batch(uint32_t blk, int step, const LaneCtx& L, const Smem& S, uint32_t bvs, uint32_t svs, float (&accA)[NV],
+                                      float (&accB)[NV]) {
+        const uint32_t hA = blk + 20 * L.g, hB = hA + 160;
+        const uint32_t ddA = prim::lds32(hA), ddB = prim::lds32(hB);
+        const uint32_t scA = prim::lds32(hA + 4 + 4 * (L.t >> 1)), scB = prim::lds32(hB + 4 + 4 * (L.t >> 1));
+        const uint32_t mA = prim::lds32(hA + 12 + 4 * (L.t & 1)), mB = prim::lds32(hB + 12 + 4 * (L.t & 1));
+        uint4 hqA = make_uint4(0u, 0u, 0u, 0u), hqB = hqA;
+        if (FIVE) {
+            hqA = prim::lds16(blk + 320 + 32 * L.g + 16 * (L.t & 1));
+            hqB = prim::lds16(blk + 320 + 32 * (L.g + 8) + 16 * (L.t & 1));
+        }
+        const uint32_t q0 = blk + QOFF + 16 * L.lane;
+        const uint32_t ba = L.bbase + (uint32_t)step * L.bmul;
+        int PA0[NV], PA1[NV], PB0[NV], PB1[NV];
+#pragma unroll
+        for (int v = 0; v < NV; v++) PA0[v] = PA1[v] = PB0[v] = PB1[v] = 0;
+#pragma unroll
+        for (int ci = 0; ci < 2; ci++) {
+            const uint4 qA = prim::lds16(q0 + (ci * 2) * 512), qB = prim::lds16(q0 + (ci * 2 + 1) * 512);
+            const int hsh = 2 * ((L.t >> 1) + 2 * ci);
+            const uint32_t hAx = hqA.x >> hsh, hAy = hqA.y >> hsh, hAz = hqA.z >> hsh, hAw = hqA.w >> hsh;
+            const uint32_t hBx = hqB.x >> hsh, hBy = hqB.y >> hsh, hBz = hqB.z >> hsh, hBw = hqB.w >> hsh;
+#pragma unroll
+            for (int nib = 0; nib < 2; nib++) {
+                uint32_t sA = byte_of(scA, 2 * ci + nib), sB = byte_of(scB, 2 * ci + nib);
+                uint32_t a[8];
+                if (FIVE) {
+                    a[0] = q5_nibs(qA.x, hAx, nib); a[1] = q5_nibs(qB.x, hBx, nib); a[2] = q5_nibs(qA.y, hAy, nib); a[3] = q5_nibs(qB.y, hBy, nib);
+                    a[4] = q5_nibs(qA.z, hAz, nib); a[5] = q5_nibs(qB.z, hBz, nib); a[6] = q5_nibs(qA.w, hAw, nib); a[7] = q5_nibs(qB.w, hBw, nib);
+                } else {
+                    const uint32_t mk = nib ? 0xF0F0F0F0u : 0x0F0F0F0Fu;
+                    a[0] = qA.x & mk; a[1] = qB.x & mk; a[2] = qA.y & mk; a[3] = qB.y & mk;
+                    a[4] = qA.z & mk; a[5] = qB.z & mk; a[6] = qA.w & mk; a[7] = qB.w & mk;
+                    if (nib == 0) {
+                        sA <<= 4;
+                        sB <<= 4;
+                    }
+                }
+#pragma unroll
+                for (int v = 0; v < NV; v++) {
+                    const uint4 bv = prim::lds16(ba + (uint32_t)v * bvs + 128 * ci + 32 * nib);
+                    int c[4];
+                    prim::mma_i8<true, true>(c, a[0], a[1], a[2], a[3], bv.x, bv.y);
+                    prim::mma_i8<true, false>(c, a[4], a[5], a[6], a[7], bv.z, bv.w);
+                    PA0[v] += (int)sA * c[0]; PA1[v] += (int)sA * c[1];
+                    PB0[v] += (int)sB * c[2]; PB1[v] += (int)sB * c[3];
+                }
+            }
+        }
+        const float dA = prim::h2f(ddA & 0xFFFF), mnA = prim::h2f(ddA >> 16);
+        const float dB = prim::h2f(ddB & 0xFFFF), mnB = prim::h2f(ddB >> 16);
+#pragma unroll
+        for (int v = 0; v < NV; v++) {
+            const uint32_t bq = prim::lds32(S.sv + (uint32_t)v * svs + 128 * step + 16 * L.g + 4 * L.t);
+            int cq[4];
+            prim::mma_i8<true, true>(cq, mA, mB, 0u, 0u, bq, 0u);
+            accA[v] = prim::fma(dA, combine(PA0[v], PA1[v], L), accA[v]);
+            accA[v] = prim::fma(-mnA, (float)(cq[0] * 128 + cq[1]) * L.wq, accA[v]);
+            accB[v] = prim::fma(dB, combine(PB0[v], PB1[v], L), accB[v]);
+            accB[v] = prim::fma(-mnB, (float)(cq[2] * 128 + cq[3]) * L.wq, accB[v]);
+        }
+    }
 };
 using Q4K = K45<false>;
 using Q5K = K45<true>;
@@ -302,6 +368,49 @@ struct Q6K {
         accA = prim::fma(dA, combine(PA0, PA1, L), accA);
         accB = prim::fma(dB, combine(PB0, PB1, L), accB);
     }
+    template <int NV>
+    SLAI_HD static void compute_batch(uint32_t blk, int step, const LaneCtx& L, const Smem& S, uint32_t bvs, uint32_t svs, float (&accA)[NV],
+                                      float (&accB)[NV]) {
+        int PA0[NV], PA1[NV], PB0[NV], PB1[NV];
+#pragma unroll
+        for (int v = 0; v < NV; v++) PA0[v] = PA1[v] = PB0[v] = PB1[v] = 0;
+        const uint32_t ba = L.bbase + (uint32_t)step * L.bmul;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const uint2 qhA = prim::lds8(blk + 2048 + (h * 2) * 256 + 8 * L.lane), qhB = prim::lds8(blk + 2048 + (h * 2 + 1) * 256 + 8 * L.lane);
+            const uint2 scwA = prim::lds8(blk + 3072 + 16 * L.g + 8 * h), scwB = prim::lds8(blk + 3072 + 16 * (L.g + 8) + 8 * h);
+#pragma unroll
+            for (int pair = 0; pair < 2; pair++) {
+                const uint2 qlA = prim::lds8(blk + ((h * 2 + pair) * 2) * 256 + 8 * L.lane);
+                const uint2 qlB = prim::lds8(blk + ((h * 2 + pair) * 2 + 1) * 256 + 8 * L.lane);
+#pragma unroll
+                for (int nib = 0; nib < 2; nib++) {
+                    const int sh = 2 * pair + 4 * nib;
+                    const int j8 = 4 * nib + 2 * pair + (L.t >> 1);
+                    const int j = 16 * step + 8 * h + j8;
+                    const uint32_t a0 = q6_nibs(qlA.x, qhA.x >> sh, nib), a1 = q6_nibs(qlB.x, qhB.x >> sh, nib);
+                    const uint32_t a2 = q6_nibs(qlA.y, qhA.y >> sh, nib), a3 = q6_nibs(qlB.y, qhB.y >> sh, nib);
+                    const uint32_t wsA = j8 < 4 ? scwA.x : scwA.y, wsB = j8 < 4 ? scwB.x : scwB.y;
+                    const int scA = (int)(signed char)((wsA >> (8 * (j8 & 3))) & 0xFF), scB = (int)(signed char)((wsB >> (8 * (j8 & 3))) & 0xFF);
+#pragma unroll
+                    for (int v = 0; v < NV; v++) {
+                        const uint2 bv = prim::lds8(ba + (uint32_t)v * bvs + 128 * h + 64 * nib + 32 * pair);
+                        int c[4];
+                        prim::mma_i8<false, true>(c, a0, a1, a2, a3, bv.x, bv.y);
+                        const uint2 sv = prim::lds8(S.sv + (uint32_t)v * svs + 16 * j + 8 * (L.t & 1));
+                        PA0[v] += scA * (c[0] - 32 * (int)sv.x); PA1[v] += scA * (c[1] - 32 * (int)sv.y);
+                        PB0[v] += scB * (c[2] - 32 * (int)sv.x); PB1[v] += scB * (c[3] - 32 * (int)sv.y);
+                    }
+                }
+            }
+        }
+        const float dA = prim::h2f(prim::lds_u16(blk + 3328 + 2 * L.g)), dB = prim::h2f(prim::lds_u16(blk + 3328 + 2 * (L.g + 8)));
+#pragma unroll
+        for (int v = 0; v < NV; v++) {
+            accA[v] = prim::fma(dA, combine(PA0[v], PA1[v], L), accA[v]);
+            accB[v] = prim::fma(dB, combine(PB0[v], PB1[v], L), accB[v]);
+        }
+    }
 };
 
 // ---- Q8_0: a block is 4 GGUF blocks (128 values) ---------------------------------------------
@@ -325,6 +434,27 @@ struct Q80 {
             const float sA = prim::h2f(prim::lds_u16(blk + 8 * L.g + 2 * b)), sB = prim::h2f(prim::lds_u16(blk + 8 * (L.g + 8) + 2 * b));
             accA = prim::fma(sA, combine(c[0], c[1], L), accA);
             accB = prim::fma(sB, combine(c[2], c[3], L), accB);
+        }
+    }
+    template <int NV>
+    SLAI_HD static void compute_batch(uint32_t blk, int step, const LaneCtx& L, const Smem& S, uint32_t bvs, uint32_t svs, float (&accA)[NV],
+                                      float (&accB)[NV]) {
+        (void)S; (void)svs;
+        const uint32_t ba = L.bbase + (uint32_t)step * L.bmul;
+#pragma unroll
+        for (int ci = 0; ci < 2; ci++) {
+            const int b = 2 * ci + (L.t >> 1);
+            const uint4 qA = prim::lds16(blk + 128 + (ci * 2) * 512 + 16 * L.lane), qB = prim::lds16(blk + 128 + (ci * 2 + 1) * 512 + 16 * L.lane);
+            const float sA = prim::h2f(prim::lds_u16(blk + 8 * L.g + 2 * b)), sB = prim::h2f(prim::lds_u16(blk + 8 * (L.g + 8) + 2 * b));
+#pragma unroll
+            for (int v = 0; v < NV; v++) {
+                const uint4 bv = prim::lds16(ba + (uint32_t)v * bvs + 64 * ci);
+                int c[4];
+                prim::mma_i8<false, true>(c, qA.x, qB.x, qA.y, qB.y, bv.x, bv.y);
+                prim::mma_i8<false, false>(c, qA.z, qB.z, qA.w, qB.w, bv.z, bv.w);
+                accA[v] = prim::fma(sA, combine(c[0], c[1], L), accA[v]);
+                accB[v] = prim::fma(sB, combine(c[2], c[3], L), accB[v]);
+            }
         }
     }
 };

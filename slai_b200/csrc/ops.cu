@@ -441,6 +441,8 @@ SLAI_API int slai_gemv_quant(slai_ctx* ctx, float* d_out, const slai_qmatrix* w,
     if (!ctx || !w || !d_out || !d_v) return SLAI_ERR_INVALID_ARG;
     SLAI_ENTER(ctx);
     SLAI_REQUIRE(ctx, n_batch >= 1 && n_batch <= 8, SLAI_ERR_INVALID_ARG, "gemv: n_batch=%d must be in 1..8", n_batch);
+    // A batch streams a quantised matrix once (gemv_batch.cu); dense f32 matrices take the vectors one by one.
+    if (n_batch > 1 && gemv_batch_supported(w)) return gemv_batch_launch(ctx, d_out, w, d_v, n_batch);
     for (int b = 0; b < n_batch; b++) {
         GemvLaunch L;
         L.fmt = w->fmt;
