@@ -338,6 +338,34 @@ def run_gpt2(args):
     emit(line)
 
 
+def measure_batch(m, cfg, n_seq, prompt_len, steps, warmup, bs1_ms_per_token):
+    """`n_seq` sequences decoded together through slai_llama_decode_batch (one KV cache and position per sequence, every
+    weight matrix read once per step for all of them): the prompts advance in lockstep, one token of every sequence per
+    step, then `warmup` + `steps` greedy steps; wall-clock per step of the blocking call (ids read back every step)."""
+    rng = np.random.default_rng(7)
+    prompts = rng.integers(0, cfg.vocab_size, size=(n_seq, prompt_len)).astype(np.int32)
+    m.batch_reserve(n_seq)
+    try:
+        nxt = prompts[:, 0]
+        for p in range(prompt_len):
+            _, nxt = m.decode_batch(prompts[:, p], [p] * n_seq, want_logits=False)
+        pos = prompt_len
+        for _ in range(warmup):
+            _, nxt = m.decode_batch(nxt, [pos] * n_seq, want_logits=False)
+            pos += 1
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            _, nxt = m.decode_batch(nxt, [pos] * n_seq, want_logits=False)
+            pos += 1
+        dt = time.perf_counter() - t0
+    finally:
+        m.batch_reserve(0)
+    return {"n_seq": n_seq, "value": n_seq * steps / dt, "unit": "tok/s (all sequences)", "ms_per_step": dt / steps * 1e3, "steps": steps,
+            "warmup": warmup, "prompt_len": prompt_len, "decode_positions": [pos - steps, pos - 1],
+            "vs_one_sequence_at_a_time": (n_seq * steps / dt) / (1e3 / bs1_ms_per_token),
+            "timing": "wall clock around the blocking per-step call: token ids and positions H2D, greedy ids D2H every step"}
+
+
 def _tp_bit_identity(backend, group, cfg70):
     """Two layers of the 70B shape decoded twice, the half-layer sums once through NCCL all-reduce and once through
     the peer-memory exchange inside the GEMV kernels: same logits bit for bit and same greedy ids."""
@@ -416,6 +444,12 @@ def measure_tp(args, group, n_layers=0, prompt_len=1024, steps=None, warmup=None
     clocks = sampler.stop()
     ids = group.gather_ids(toks)
     ms, prefill_s = group.max_over_ranks([ms, prefill_s])
+    batch = None
+    if world == 1 and not getattr(args, "no_batch", False):
+        try:  # BASELINE configs[4] also names batch 8: eight sequences per step, the weights read once
+            batch = measure_batch(m, cfg, 8, 128, 16, 3, ms / K)
+        except Exception as e:
+            batch = {"error": f"{type(e).__name__}: {e}"}
     rec = None
     if rank == 0:
         per_rank = tp.bytes_per_token_per_rank(cfg, synth.FMT_Q4_K, synth.FMT_Q6_K, world)
@@ -429,7 +463,7 @@ def measure_tp(args, group, n_layers=0, prompt_len=1024, steps=None, warmup=None
                "prefill_s": prefill_s,
                "prefill": prefill_record(cfg, PL - 1, prefill_s, ms / K, n_gpus=world),
                "clocks": clocks, "launches_per_token": m.launches_per_token(), "gpu_launches": m.launches_per_token() * K,
-               "ranks_agree": all(r == ids[0] for r in ids), "nccl_and_peer_exchange_bit_identical": identical,
+               "ranks_agree": all(r == ids[0] for r in ids), "nccl_and_peer_exchange_bit_identical": identical, "batch8": batch,
                "roofline": {"bound": "hbm", "per_gpu_bytes_per_token": per_rank + kv, "achieved": (per_rank + kv) / t / 1e9, "peak": peak,
                             "unit": "GB/s", "frac": (per_rank + kv) / t / 1e9 / peak, "peak_source": peak_src}}
     m.close()
@@ -482,6 +516,7 @@ def main():
     ap.add_argument("--tp", action="store_true", help="Llama-2-70B architecture sharded over all ranks instead of 7B replicas")
     ap.add_argument("--tp-layers", type=int, default=0, help="with --tp: fewer layers than 80 (0 = the full model)")
     ap.add_argument("--tp-nccl", action="store_true", help="with --tp: exchange through NCCL all-reduce instead of peer memory")
+    ap.add_argument("--no-batch", action="store_true", help="skip the eight-sequences-per-step measurement (`batch8`, one GPU only)")
     ap.add_argument("--no-tp", action="store_true", help="skip the sharded 70B measurement that the default run attaches as `tp`")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -559,6 +594,12 @@ def main():
     barrier()
 
     ms, e2e_s = group.max_over_ranks([ms, e2e_s])
+    batch = None
+    if rank == 0 and world == 1 and not args.no_batch:
+        try:
+            batch = measure_batch(m, cfg, 8, PROMPT_LEN, 32, 3, ms / K)
+        except Exception as e:  # the headline line is still reported
+            batch = {"error": f"{type(e).__name__}: {e}"}
     algo, per, nl = time_dominant_kernel(backend, ctx, cfg, mats) if rank == 0 else (0, 1.0, 0)
     launches_per_token = m.launches_per_token()
     backend.lib.slai_free_host(backend.h, pinned)
@@ -613,6 +654,8 @@ def main():
             line["gemv_microbench"] = gemv_table
         if cpu is not None:
             line["cpu_baseline"] = cpu
+        if batch is not None:
+            line["batch8"] = batch
         if tp_rec is not None:
             line["tp"] = tp_rec
         emit(line)

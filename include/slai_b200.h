@@ -301,6 +301,16 @@ int slai_llama_generate_sampled(slai_llama* m, int32_t token, int32_t pos, int32
  * partial products of its row-parallel matrices with the group's all-reduce, so every rank must make the call),
  * shorter ones and everything else through the decode step as there.  Same results within 1e-3 relative L2. */
 int slai_llama_prefill(slai_llama* m, const int32_t* h_tokens, int32_t n, int32_t pos0, float* h_last_logits);
+/* Several sequences decoded together (no counterpart in the reference, whose Llama2State holds one sequence:
+ * models/llama2/transformer.rs:16-44): `slai_llama_batch_reserve` gives the model `n_seq` (1..8; 0 frees them) further KV
+ * caches and activation rows; `slai_llama_decode_batch` takes one token of each of the first `n_seq` sequences, token
+ * h_tokens[b] at position h_pos[b] of sequence b's own cache, and reads every weight matrix once for all of them (the
+ * operator sequence of Llama2::launch, transformer.rs:316-381, on n_seq columns).  A negative position leaves that
+ * sequence out of the step.  h_logits (n_seq x vocab floats) and h_next (the greedy choice per sequence) may be NULL.
+ * Blocking.  Models without q/k/v biases, not sharded.  Per sequence the results equal slai_llama_decode's within 1e-3
+ * relative L2. */
+int slai_llama_batch_reserve(slai_llama* m, int32_t n_seq);
+int slai_llama_decode_batch(slai_llama* m, int32_t n_seq, const int32_t* h_tokens, const int32_t* h_pos, float* h_logits, int32_t* h_next);
 /* Debug/test access to Llama2State vectors: 0 x, 1 xb, 2 q, 3 hb, 4 logits.  Blocking. */
 int slai_llama_read_state(slai_llama* m, int which, float* h_out, int64_t n);
 /* Test access to the KV cache of one layer: positions 0..n_pos as f32, position-major like the reference's cache

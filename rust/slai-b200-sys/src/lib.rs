@@ -106,6 +106,9 @@ extern "C" {
     pub fn slai_llama_read_state(m: *mut slai_llama, which: i32, h_out: *mut f32, n: i64) -> i32;
     pub fn slai_llama_read_kv(m: *mut slai_llama, layer: i32, n_pos: i32, h_keys: *mut f32, h_values: *mut f32) -> i32;
     pub fn slai_llama_stats(m: *mut slai_llama, token: i32, pos: i32, out: *mut slai_llama_stats_t) -> i32;
+    pub fn slai_llama_batch_reserve(m: *mut slai_llama, n_seq: i32) -> i32;
+    pub fn slai_llama_decode_batch(m: *mut slai_llama, n_seq: i32, h_tokens: *const i32, h_pos: *const i32, h_logits: *mut f32,
+                                   h_next: *mut i32) -> i32;
     pub fn slai_llama_launches_per_token(m: *const slai_llama) -> i32;
     pub fn slai_gpt2_create(ctx: *mut slai_ctx, cfg: *const slai_gpt2_config, out: *mut *mut slai_gpt2) -> i32;
     pub fn slai_gpt2_destroy(m: *mut slai_gpt2) -> i32;

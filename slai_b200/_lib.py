@@ -124,6 +124,8 @@ SIGNATURES = {
     "slai_llama_prefill": (C.c_int, [_vp, _vp, _i32, _i32, _vp]),
     "slai_llama_read_kv": (C.c_int, [_vp, C.c_int, C.c_int, _vp, _vp]),
     "slai_llama_stats": (C.c_int, [_vp, C.c_int32, C.c_int32, _vp]),
+    "slai_llama_batch_reserve": (C.c_int, [_vp, _i32]),
+    "slai_llama_decode_batch": (C.c_int, [_vp, _i32, _vp, _vp, _vp, _vp]),
     "slai_llama_read_state": (C.c_int, [_vp, C.c_int, _vp, _i64]),
     "slai_llama_launches_per_token": (C.c_int, [_vp]),
     "slai_gpt2_create": (C.c_int, [_vp, C.POINTER(Gpt2Config), _pp]),

@@ -321,6 +321,7 @@ int launch_embed_f32(slai_ctx* ctx, float* x, const float* table, int dim, const
 int launch_embed_q8(slai_ctx* ctx, float* x, const slai_qmatrix* wte, const int* d_token, const float* wpe,
                     const int* d_pos, bool pdl, const float* rope_theta = nullptr, float* rope_cs = nullptr, int rope_half = 0);
 int launch_argmax(slai_ctx* ctx, const float* v, int64_t n, int32_t* d_out, bool pdl);
+int rms_norm_rows_launch(slai_ctx* ctx, float* d_out, const float* d_x, const float* d_w, int64_t n, int rows, float eps);
 // sampler.cu
 size_t sampler_params_bytes();
 size_t sampler_scratch_bytes(int n);

@@ -138,7 +138,24 @@ struct slai_llama {
     void* pf_attn_scratch = nullptr;
     size_t pf_attn_scratch_bytes = 0;
     unsigned int* pf_tickets = nullptr;
+    // several sequences decoded together (slai_llama_decode_batch): one KV cache per sequence, activations of all of them
+    int bt_n = 0;
+    void *bt_k = nullptr, *bt_v = nullptr;  // [sequence][layer][kv head][position][head_size]
+    size_t bt_cache_bytes = 0;              // per sequence
+    float *bt_x = nullptr, *bt_xn = nullptr, *bt_q = nullptr, *bt_kt = nullptr, *bt_vt = nullptr, *bt_xb = nullptr, *bt_t = nullptr, *bt_g = nullptr,
+          *bt_u = nullptr, *bt_logits = nullptr;
+    int* bt_i = nullptr;  // device ints: [0, 8) tokens, [8, 16) positions, [16, 24) greedy choices
 };
+
+static void llama_drop_batch(slai_llama* m) {
+    if (m->bt_n) cudaStreamSynchronize(m->ctx->stream);
+    cudaFree(m->bt_k); cudaFree(m->bt_v); cudaFree(m->bt_x); cudaFree(m->bt_xn); cudaFree(m->bt_q); cudaFree(m->bt_kt); cudaFree(m->bt_vt);
+    cudaFree(m->bt_xb); cudaFree(m->bt_t); cudaFree(m->bt_g); cudaFree(m->bt_u); cudaFree(m->bt_logits); cudaFree(m->bt_i);
+    m->bt_k = m->bt_v = nullptr;
+    m->bt_x = m->bt_xn = m->bt_q = m->bt_kt = m->bt_vt = m->bt_xb = m->bt_t = m->bt_g = m->bt_u = m->bt_logits = nullptr;
+    m->bt_i = nullptr;
+    m->bt_n = 0;
+}
 
 static void llama_drop_prefill(slai_llama* m) {
     if (m->pf_cap) cudaStreamSynchronize(m->ctx->stream);
@@ -515,12 +532,127 @@ SLAI_API int slai_llama_create(slai_ctx* ctx, const slai_llama_config* cfg, slai
     return SLAI_OK;
 }
 
+// ---- several sequences decoded together ------------------------------------------------------------------------------
+// Every sequence has its own KV cache and position; one step takes one token of each and reads every weight matrix once
+// for all of them (the batched GEMV, gemv_batch.cu).  Per layer: RmsNorm of all rows, q / k / v products, then per sequence
+// RoPE + cache write and the single-query attention kernel on that sequence's cache, output product + residual, RmsNorm,
+// gate / up products, SiLU, down product + residual (the operator sequence of transformer.rs:327-365 on `n_seq` columns).
+SLAI_API int slai_llama_batch_reserve(slai_llama* m, int32_t n_seq) {
+    if (!m) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(m->ctx);
+    slai_ctx* ctx = m->ctx;
+    const slai_llama_config& c = m->cfg;
+    SLAI_REQUIRE(ctx, n_seq >= 0 && n_seq <= 8, SLAI_ERR_INVALID_ARG, "batch: %d sequences (0..8)", n_seq);
+    SLAI_REQUIRE(ctx, m->tp == 1, SLAI_ERR_INVALID_ARG, "batch: sharded models decode one sequence at a time");
+    llama_drop_batch(m);
+    if (n_seq == 0) return SLAI_OK;
+    const size_t esz = c.kv_dtype == SLAI_KV_F16 ? 2 : 4;
+    m->bt_cache_bytes = (size_t)c.n_layers * m->kv_layer_elems * esz;
+    const size_t B = (size_t)n_seq;
+    const size_t wide = (size_t)std::max(c.dim, m->q_dim);
+    bool ok = cudaMalloc(&m->bt_k, B * m->bt_cache_bytes) == cudaSuccess && cudaMalloc(&m->bt_v, B * m->bt_cache_bytes) == cudaSuccess &&
+              cudaMalloc(&m->bt_x, B * c.dim * 4) == cudaSuccess && cudaMalloc(&m->bt_xn, B * wide * 4) == cudaSuccess &&
+              cudaMalloc(&m->bt_q, B * m->q_dim * 4) == cudaSuccess && cudaMalloc(&m->bt_kt, B * m->kv_dim * 4) == cudaSuccess &&
+              cudaMalloc(&m->bt_vt, B * m->kv_dim * 4) == cudaSuccess && cudaMalloc(&m->bt_xb, B * m->q_dim * 4) == cudaSuccess &&
+              cudaMalloc(&m->bt_t, B * c.dim * 4) == cudaSuccess && cudaMalloc(&m->bt_g, B * m->hidden * 4) == cudaSuccess &&
+              cudaMalloc(&m->bt_u, B * m->hidden * 4) == cudaSuccess && cudaMalloc(&m->bt_logits, B * c.vocab_size * 4) == cudaSuccess &&
+              cudaMalloc(&m->bt_i, 24 * sizeof(int)) == cudaSuccess;
+    if (ok)
+        ok = cudaMemsetAsync(m->bt_k, 0, B * m->bt_cache_bytes, ctx->stream) == cudaSuccess &&
+             cudaMemsetAsync(m->bt_v, 0, B * m->bt_cache_bytes, ctx->stream) == cudaSuccess &&
+             cudaMemsetAsync(m->bt_xb, 0, B * m->q_dim * 4, ctx->stream) == cudaSuccess;
+    if (!ok) {
+        cudaGetLastError();
+        m->bt_n = 1;  // so that the buffers obtained so far are released
+        llama_drop_batch(m);
+        return slai_set_error(ctx, SLAI_ERR_OOM, "batch: cannot allocate caches and activations for %d sequences", n_seq);
+    }
+    m->bt_n = n_seq;
+    return SLAI_OK;
+}
+
+// One token of every sequence b < n_seq at position h_pos[b] (a negative position leaves sequence b out of this step: its
+// cache is not touched and its outputs mean nothing).  h_logits: n_seq x vocab floats or null; h_next: the greedy choice
+// per sequence or null.
+SLAI_API int slai_llama_decode_batch(slai_llama* m, int32_t n_seq, const int32_t* h_tokens, const int32_t* h_pos, float* h_logits,
+                                     int32_t* h_next) {
+    if (!m || !h_tokens || !h_pos) return SLAI_ERR_INVALID_ARG;
+    SLAI_ENTER(m->ctx);
+    slai_ctx* ctx = m->ctx;
+    const slai_llama_config& c = m->cfg;
+    SLAI_REQUIRE(ctx, n_seq >= 1 && n_seq <= m->bt_n, SLAI_ERR_INVALID_ARG, "batch: %d sequences, %d reserved (slai_llama_batch_reserve)", n_seq, m->bt_n);
+    SLAI_REQUIRE(ctx, m->out_norm && (m->token_embd || m->embd_q), SLAI_ERR_INVALID_ARG, "llama: embedding / output norm not set");
+    int h[24] = {};
+    for (int b = 0; b < n_seq; b++) {
+        SLAI_REQUIRE(ctx, h_pos[b] < c.seq_len, SLAI_ERR_INVALID_ARG, "batch: position %d of sequence %d exceeds the context", h_pos[b], b);
+        SLAI_REQUIRE(ctx, h_pos[b] < 0 || (h_tokens[b] >= 0 && h_tokens[b] < c.vocab_size), SLAI_ERR_INVALID_ARG, "batch: token %d out of range",
+                     h_tokens[b]);
+        h[b] = h_pos[b] < 0 ? 0 : h_tokens[b];
+        h[8 + b] = h_pos[b] < 0 ? 0 : h_pos[b];
+    }
+    for (auto& w : m->layers) {
+        SLAI_REQUIRE(ctx, w.wq && w.wk && w.wv && w.wo && w.wgate && w.wup && w.wdown && w.attn_norm && w.ffn_norm, SLAI_ERR_INVALID_ARG,
+                     "llama: a layer's weights are not set");
+        SLAI_REQUIRE(ctx, !w.bq && !w.bk && !w.bv, SLAI_ERR_UNSUPPORTED_FORMAT, "batch: q / k / v biases are not supported");
+    }
+    SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(m->bt_i, h, sizeof(h), cudaMemcpyHostToDevice, ctx->stream));
+    const int B = n_seq;
+    int* d_tok = m->bt_i;
+    int* d_pos = m->bt_i + 8;
+    int* d_next = m->bt_i + 16;
+    int rc;
+    if ((rc = prefill_embed_launch(ctx, m->bt_x, c.dim, d_tok, B, m->embd_q ? nullptr : m->token_embd, m->embd_q))) return rc;
+    const size_t esz = c.kv_dtype == SLAI_KV_F16 ? 2 : 4;
+    const long long kv_head_stride = (long long)c.seq_len * m->head_size;
+    for (int l = 0; l < c.n_layers; l++) {
+        const LlamaLayer& w = m->layers[l];
+        if ((rc = rms_norm_rows_launch(ctx, m->bt_xn, m->bt_x, w.attn_norm, c.dim, B, c.rms_norm_eps))) return rc;
+        if ((rc = slai_gemv_quant(ctx, m->bt_q, w.wq, m->bt_xn, B))) return rc;
+        if ((rc = slai_gemv_quant(ctx, m->bt_kt, w.wk, m->bt_xn, B))) return rc;
+        if ((rc = slai_gemv_quant(ctx, m->bt_vt, w.wv, m->bt_xn, B))) return rc;
+        for (int b = 0; b < B; b++) {
+            if (h_pos[b] < 0) continue;
+            void* kc = (char*)m->bt_k + (size_t)b * m->bt_cache_bytes + (size_t)l * m->kv_layer_elems * esz;
+            void* vc = (char*)m->bt_v + (size_t)b * m->bt_cache_bytes + (size_t)l * m->kv_layer_elems * esz;
+            if ((rc = rope_kv_store_launch(ctx, m->bt_q + (size_t)b * m->q_dim, m->bt_kt + (size_t)b * m->kv_dim, m->bt_vt + (size_t)b * m->kv_dim,
+                                           m->q_dim, m->kv_dim, m->head_size, d_pos + b, m->rope_theta, c.rope_variant != 0, kc, vc,
+                                           c.kv_dtype == SLAI_KV_F16, kv_head_stride, false)))
+                return rc;
+            AttnLaunch A = {};
+            A.q = m->bt_q + (size_t)b * m->q_dim; A.kcache = kc; A.vcache = vc; A.kv_dtype = c.kv_dtype;
+            A.pos_stride = m->head_size; A.head_stride = kv_head_stride;
+            A.n_heads = m->n_q_local; A.kv_mul = m->kv_mul; A.head_size = m->head_size;
+            A.d_pos = d_pos + b; A.max_pos = h_pos[b]; A.out = m->bt_xb + (size_t)b * m->q_dim; A.pdl = false;
+            A.scratch = nullptr; A.scratch_bytes = 0;
+            if ((rc = attention_launch(ctx, A))) return rc;
+        }
+        if ((rc = slai_gemv_quant(ctx, m->bt_t, w.wo, m->bt_xb, B))) return rc;
+        if ((rc = slai_add_assign(ctx, m->bt_x, m->bt_t, (int64_t)B * c.dim))) return rc;
+        if ((rc = rms_norm_rows_launch(ctx, m->bt_xn, m->bt_x, w.ffn_norm, c.dim, B, c.rms_norm_eps))) return rc;
+        if ((rc = slai_gemv_quant(ctx, m->bt_g, w.wgate, m->bt_xn, B))) return rc;
+        if ((rc = slai_gemv_quant(ctx, m->bt_u, w.wup, m->bt_xn, B))) return rc;
+        if ((rc = slai_silu_gate(ctx, m->bt_g, m->bt_u, (int64_t)B * m->hidden))) return rc;
+        if ((rc = slai_gemv_quant(ctx, m->bt_t, w.wdown, m->bt_g, B))) return rc;
+        if ((rc = slai_add_assign(ctx, m->bt_x, m->bt_t, (int64_t)B * c.dim))) return rc;
+    }
+    const slai_qmatrix* wout = m->output ? m->output : (m->embd_q ? m->embd_q : &m->embd_as_matrix);
+    if ((rc = rms_norm_rows_launch(ctx, m->bt_xn, m->bt_x, m->out_norm, c.dim, B, c.rms_norm_eps))) return rc;
+    if ((rc = slai_gemv_quant(ctx, m->bt_logits, wout, m->bt_xn, B))) return rc;
+    for (int b = 0; b < B; b++)
+        if ((rc = launch_argmax(ctx, m->bt_logits + (size_t)b * c.vocab_size, c.vocab_size, d_next + b, false))) return rc;
+    if (h_logits) SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(h_logits, m->bt_logits, (size_t)B * c.vocab_size * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (h_next) SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(h_next, d_next, (size_t)B * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return slai_check_wait_flag(ctx);
+}
+
 SLAI_API int slai_llama_destroy(slai_llama* m) {
     if (!m) return SLAI_OK;
     SLAI_ENTER(m->ctx);
     cudaStreamSynchronize(m->ctx->stream);
     destroy_graphs(m->graphs);
     llama_drop_prefill(m);
+    llama_drop_batch(m);
     for (auto& l : m->layers) {
         cudaFree(l.attn_norm); cudaFree(l.ffn_norm); cudaFree(l.bq); cudaFree(l.bk); cudaFree(l.bv);
     }

@@ -516,8 +516,11 @@ __device__ __forceinline__ float blk_max(float x, float* sh) {
     return t;
 }
 
+// One block per row of n elements (a single vector: one block).
 __global__ void rms_norm_kernel(float* out, const float* x, const float* w, long long n, float eps) {
     __shared__ float sh[32];
+    out += (size_t)blockIdx.x * n;
+    x += (size_t)blockIdx.x * n;
     float ss = 0.f;
     for (long long i = threadIdx.x; i < n; i += blockDim.x) ss += x[i] * x[i];
     ss = blk_sum(ss, sh);
@@ -788,6 +791,12 @@ SLAI_API int slai_rms_norm(slai_ctx* ctx, float* d_out, const float* d_x, const 
     if (!ctx || !d_out || !d_x || !d_w || n <= 0) return SLAI_ERR_INVALID_ARG;
     SLAI_ENTER(ctx);
     rms_norm_kernel<<<1, 1024, 0, ctx->stream>>>(d_out, d_x, d_w, n, eps);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    return SLAI_OK;
+}
+// RmsNorm of `rows` vectors of n elements with the same weights.
+int rms_norm_rows_launch(slai_ctx* ctx, float* d_out, const float* d_x, const float* d_w, int64_t n, int rows, float eps) {
+    rms_norm_kernel<<<rows, 1024, 0, ctx->stream>>>(d_out, d_x, d_w, n, eps);
     SLAI_CHECK_CUDA(ctx, cudaGetLastError());
     return SLAI_OK;
 }

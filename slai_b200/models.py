@@ -130,6 +130,24 @@ class Llama2:
                                                                logits.ctypes.data_as(C.c_void_p) if want_logits else None))
         return logits
 
+    def batch_reserve(self, n_seq: int):
+        """KV caches and activation rows for `n_seq` (1..8) sequences decoded together; 0 frees them."""
+        self.backend.check(self.backend.lib.slai_llama_batch_reserve(self.h, n_seq))
+
+    def decode_batch(self, tokens, positions, want_logits: bool = True):
+        """One token of each sequence (tokens[b] at positions[b] of sequence b's own cache; a negative position leaves the
+        sequence out): every weight matrix is read once for all of them.  Returns (logits [n, vocab] or None, greedy ids [n])."""
+        t = np.ascontiguousarray(tokens, dtype=np.int32)
+        p = np.ascontiguousarray(positions, dtype=np.int32)
+        if t.shape != p.shape or t.ndim != 1:
+            raise ValueError("decode_batch: tokens and positions must be vectors of the same length")
+        logits = np.empty((t.size, self.config.vocab_size), dtype=np.float32) if want_logits else None
+        nxt = np.empty(t.size, dtype=np.int32)
+        self.backend.check(self.backend.lib.slai_llama_decode_batch(self.h, t.size, t.ctypes.data_as(C.c_void_p), p.ctypes.data_as(C.c_void_p),
+                                                                    logits.ctypes.data_as(C.c_void_p) if want_logits else None,
+                                                                    nxt.ctypes.data_as(C.c_void_p)))
+        return logits, nxt
+
     def stats(self, token: int, pos: int) -> dict:
         """Device microseconds per kernel class of one (real) decode step run kernel after kernel outside the graph."""
         from ._lib import LlamaStats
