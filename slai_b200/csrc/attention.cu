@@ -41,8 +41,10 @@ __global__ void __launch_bounds__(ATT_THREADS, SLAI_ATT_MINB) attn_kernel(const 
         Q.part_o = P.part_o + (size_t)b * P.po_bs;
         Q.part_ml = P.part_ml + (size_t)b * P.pml_bs;
         Q.counters = P.counters + (size_t)b * gridDim.x;
-        const int n = P.pos0 + b + 1;
-        const int ns = attn_splits(Q, n);
+        Q.kc = reinterpret_cast<const char*>(P.kc) + (size_t)b * P.cache_bs;
+        Q.vc = reinterpret_cast<const char*>(P.vc) + (size_t)b * P.cache_bs;
+        const int n = (P.seq_pos ? __ldcg(P.seq_pos + b) : P.pos0 + b) + 1;
+        const int ns = n > 0 ? attn_splits(Q, n) : 0;  // a sequence left out of the step (negative position): nothing to do
         if ((int)blockIdx.y < ns) attn_item<T, MAXQ>(Q, blockIdx.x, blockIdx.y, ns, n, threadIdx.x, sm, 0);
     } else {
         const int n = __ldcg(P.d_pos) + 1;
@@ -183,6 +185,10 @@ static int attention_launch_inner(slai_ctx* ctx, const AttnLaunch& A) {
     P.part_ml = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + ((po + 255) & ~(size_t)255));
     P.counters = A.batch > 0 ? A.batch_counters : ctx->d_counters + CNT_ATTN_TICKETS;
     P.batch = A.batch; P.pos0 = A.pos0; P.q_bs = A.q_batch_stride; P.out_bs = A.out_batch_stride;
+    SLAI_REQUIRE(ctx, (A.cache_batch_stride == 0 && !A.d_pos_batch) || (A.batch > 0 && A.cache_batch_stride > 0 && A.d_pos_batch &&
+                          A.cache_batch_stride % 4 == 0), SLAI_ERR_INVALID_ARG, "attention: a batch of sequences needs positions and a cache stride");
+    P.cache_bs = A.cache_batch_stride; P.seq_pos = A.d_pos_batch;
+    if (A.cache_batch_stride & 15) P.vec16 = 0;
     P.po_bs = (long long)(per_token / 4); P.pml_bs = (long long)(per_token / 4);  // every token's partials in its own slice of the scratch
     const bool f16 = A.kv_dtype == SLAI_KV_F16;
     if (kv_mul == 1) return f16 ? launch_t<__half, 1>(ctx, P, n_kv, smem, A.pdl) : launch_t<float, 1>(ctx, P, n_kv, smem, A.pdl);

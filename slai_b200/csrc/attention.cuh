@@ -28,6 +28,9 @@ struct AttnParams {
     // batch of query tokens (blockIdx.z): per-token strides of q / out / partials / tickets; position of token b = pos0 + b
     int batch = 0, pos0 = 0;
     long long q_bs = 0, out_bs = 0, po_bs = 0, pml_bs = 0;
+    // a batch of sequences instead: token b has its own caches, cache_bs bytes after token b - 1's, and position seq_pos[b]
+    long long cache_bs = 0;
+    const int* seq_pos = nullptr;
 #ifdef SLAI_TRACE
     unsigned long long* tl = nullptr;  // trace build only: the context's launch timeline
 #endif

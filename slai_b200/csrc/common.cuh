@@ -280,7 +280,7 @@ struct GemvLaunch {
 int gemv_launch(slai_ctx* ctx, const GemvLaunch& L);
 // gemv_batch.cu: out[b][m] = sum_k W[m][k] v[b][k] for a batch of 2..8 vectors in one pass over a quantised matrix
 bool gemv_batch_supported(const slai_qmatrix* w);
-int gemv_batch_launch(slai_ctx* ctx, float* d_out, const slai_qmatrix* w, const float* d_v, int n_batch);
+int gemv_batch_launch(slai_ctx* ctx, float* d_out, const slai_qmatrix* w, const float* d_v, int n_batch, long long ldo = 0);
 
 // attention.cu
 struct AttnLaunch {
@@ -304,6 +304,10 @@ struct AttnLaunch {
     int pos0 = 0;
     long long q_batch_stride = 0, out_batch_stride = 0;
     unsigned int* batch_counters = nullptr;
+    // A batch of sequences instead (one query token of each): token b reads the caches `cache_batch_stride` bytes after token
+    // b - 1's and attends to positions 0..=d_pos_batch[b] (a negative position: nothing is done for b).
+    long long cache_batch_stride = 0;
+    const int* d_pos_batch = nullptr;
     // *d_pos was written by a kernel that has completed before any block of this one can start, so it may be read before the
     // dependency wait.  True inside a decode step: the scalar is written once per token, and the embedding kernel that
     // follows neither starts before that write is complete nor lets its own dependents start before it has finished.
@@ -379,6 +383,11 @@ int prefill_split_ln_launch(slai_ctx* ctx, const float* x, int ldx, const float*
 int prefill_gelu_split_launch(slai_ctx* ctx, const float* g, int T, int H, __half* hi, __half* lo);
 int prefill_add_rows_launch(slai_ctx* ctx, float* x, int dim, const float* table, int pos0, int T);
 int prefill_embed_launch(slai_ctx* ctx, float* x, int dim, const int* d_tokens, int T, const float* table, const slai_qmatrix* qtable);
+// One token of each of `B` sequences: row b of qkv ([B][ld]: q, k, v side by side) at position d_pos[b] (negative: skipped),
+// q rotated into q_out ([B][q_dim]), k and v into the caches of sequence b, `seq_stride` bytes after those of sequence b - 1.
+int rope_kv_store_seqs_launch(slai_ctx* ctx, const float* qkv, int ld, int q_dim, int kv_dim, int head_size, const int* d_pos, int B,
+                              const float* theta, int neox, float* q_out, void* kcache, void* vcache, int kv_f16, long long kv_head_stride,
+                              long long seq_stride);
 int rope_kv_store_launch(slai_ctx* ctx, float* q, const float* k, const float* v, int q_dim, int kv_dim, int head_size, const int* d_pos,
                          const float* theta, int neox, void* kcache, void* vcache, int kv_f16, long long kv_head_stride, bool pdl);
 bool prefill_attention_supported(int head_size, int kv_f16, const void* kc, const void* vc, long long head_stride);

@@ -142,18 +142,22 @@ struct slai_llama {
     int bt_n = 0;
     void *bt_k = nullptr, *bt_v = nullptr;  // [sequence][layer][kv head][position][head_size]
     size_t bt_cache_bytes = 0;              // per sequence
-    float *bt_x = nullptr, *bt_xn = nullptr, *bt_q = nullptr, *bt_kt = nullptr, *bt_vt = nullptr, *bt_xb = nullptr, *bt_t = nullptr, *bt_g = nullptr,
+    float *bt_x = nullptr, *bt_xn = nullptr, *bt_q = nullptr, *bt_qkv = nullptr, *bt_xb = nullptr, *bt_t = nullptr, *bt_g = nullptr,
           *bt_u = nullptr, *bt_logits = nullptr;
     int* bt_i = nullptr;  // device ints: [0, 8) tokens, [8, 16) positions, [16, 24) greedy choices
+    void* bt_attn = nullptr;  // attention partials of all sequences
+    unsigned int* bt_tickets = nullptr;
 };
 
 static void llama_drop_batch(slai_llama* m) {
     if (m->bt_n) cudaStreamSynchronize(m->ctx->stream);
-    cudaFree(m->bt_k); cudaFree(m->bt_v); cudaFree(m->bt_x); cudaFree(m->bt_xn); cudaFree(m->bt_q); cudaFree(m->bt_kt); cudaFree(m->bt_vt);
+    cudaFree(m->bt_k); cudaFree(m->bt_v); cudaFree(m->bt_x); cudaFree(m->bt_xn); cudaFree(m->bt_q); cudaFree(m->bt_qkv);
     cudaFree(m->bt_xb); cudaFree(m->bt_t); cudaFree(m->bt_g); cudaFree(m->bt_u); cudaFree(m->bt_logits); cudaFree(m->bt_i);
-    m->bt_k = m->bt_v = nullptr;
-    m->bt_x = m->bt_xn = m->bt_q = m->bt_kt = m->bt_vt = m->bt_xb = m->bt_t = m->bt_g = m->bt_u = m->bt_logits = nullptr;
+    cudaFree(m->bt_attn); cudaFree(m->bt_tickets);
+    m->bt_k = m->bt_v = m->bt_attn = nullptr;
+    m->bt_x = m->bt_xn = m->bt_q = m->bt_qkv = m->bt_xb = m->bt_t = m->bt_g = m->bt_u = m->bt_logits = nullptr;
     m->bt_i = nullptr;
+    m->bt_tickets = nullptr;
     m->bt_n = 0;
 }
 
@@ -552,15 +556,17 @@ SLAI_API int slai_llama_batch_reserve(slai_llama* m, int32_t n_seq) {
     const size_t wide = (size_t)std::max(c.dim, m->q_dim);
     bool ok = cudaMalloc(&m->bt_k, B * m->bt_cache_bytes) == cudaSuccess && cudaMalloc(&m->bt_v, B * m->bt_cache_bytes) == cudaSuccess &&
               cudaMalloc(&m->bt_x, B * c.dim * 4) == cudaSuccess && cudaMalloc(&m->bt_xn, B * wide * 4) == cudaSuccess &&
-              cudaMalloc(&m->bt_q, B * m->q_dim * 4) == cudaSuccess && cudaMalloc(&m->bt_kt, B * m->kv_dim * 4) == cudaSuccess &&
-              cudaMalloc(&m->bt_vt, B * m->kv_dim * 4) == cudaSuccess && cudaMalloc(&m->bt_xb, B * m->q_dim * 4) == cudaSuccess &&
+              cudaMalloc(&m->bt_q, B * m->q_dim * 4) == cudaSuccess && cudaMalloc(&m->bt_qkv, B * (m->q_dim + 2 * m->kv_dim) * 4) == cudaSuccess &&
+              cudaMalloc(&m->bt_xb, B * m->q_dim * 4) == cudaSuccess &&
               cudaMalloc(&m->bt_t, B * c.dim * 4) == cudaSuccess && cudaMalloc(&m->bt_g, B * m->hidden * 4) == cudaSuccess &&
               cudaMalloc(&m->bt_u, B * m->hidden * 4) == cudaSuccess && cudaMalloc(&m->bt_logits, B * c.vocab_size * 4) == cudaSuccess &&
-              cudaMalloc(&m->bt_i, 24 * sizeof(int)) == cudaSuccess;
+              cudaMalloc(&m->bt_i, 24 * sizeof(int)) == cudaSuccess && cudaMalloc(&m->bt_attn, B * m->attn_scratch_bytes) == cudaSuccess &&
+              cudaMalloc(&m->bt_tickets, B * 1024 * sizeof(unsigned int)) == cudaSuccess;
     if (ok)
         ok = cudaMemsetAsync(m->bt_k, 0, B * m->bt_cache_bytes, ctx->stream) == cudaSuccess &&
              cudaMemsetAsync(m->bt_v, 0, B * m->bt_cache_bytes, ctx->stream) == cudaSuccess &&
-             cudaMemsetAsync(m->bt_xb, 0, B * m->q_dim * 4, ctx->stream) == cudaSuccess;
+             cudaMemsetAsync(m->bt_xb, 0, B * m->q_dim * 4, ctx->stream) == cudaSuccess &&
+             cudaMemsetAsync(m->bt_tickets, 0, B * 1024 * sizeof(unsigned int), ctx->stream) == cudaSuccess;
     if (!ok) {
         cudaGetLastError();
         m->bt_n = 1;  // so that the buffers obtained so far are released
@@ -583,12 +589,14 @@ SLAI_API int slai_llama_decode_batch(slai_llama* m, int32_t n_seq, const int32_t
     SLAI_REQUIRE(ctx, n_seq >= 1 && n_seq <= m->bt_n, SLAI_ERR_INVALID_ARG, "batch: %d sequences, %d reserved (slai_llama_batch_reserve)", n_seq, m->bt_n);
     SLAI_REQUIRE(ctx, m->out_norm && (m->token_embd || m->embd_q), SLAI_ERR_INVALID_ARG, "llama: embedding / output norm not set");
     int h[24] = {};
+    int max_pos = 0;
     for (int b = 0; b < n_seq; b++) {
         SLAI_REQUIRE(ctx, h_pos[b] < c.seq_len, SLAI_ERR_INVALID_ARG, "batch: position %d of sequence %d exceeds the context", h_pos[b], b);
         SLAI_REQUIRE(ctx, h_pos[b] < 0 || (h_tokens[b] >= 0 && h_tokens[b] < c.vocab_size), SLAI_ERR_INVALID_ARG, "batch: token %d out of range",
                      h_tokens[b]);
         h[b] = h_pos[b] < 0 ? 0 : h_tokens[b];
-        h[8 + b] = h_pos[b] < 0 ? 0 : h_pos[b];
+        h[8 + b] = h_pos[b] < 0 ? -1 : h_pos[b];
+        max_pos = std::max(max_pos, (int)h_pos[b]);
     }
     for (auto& w : m->layers) {
         SLAI_REQUIRE(ctx, w.wq && w.wk && w.wv && w.wo && w.wgate && w.wup && w.wdown && w.attn_norm && w.ffn_norm, SLAI_ERR_INVALID_ARG,
@@ -604,40 +612,50 @@ SLAI_API int slai_llama_decode_batch(slai_llama* m, int32_t n_seq, const int32_t
     if ((rc = prefill_embed_launch(ctx, m->bt_x, c.dim, d_tok, B, m->embd_q ? nullptr : m->token_embd, m->embd_q))) return rc;
     const size_t esz = c.kv_dtype == SLAI_KV_F16 ? 2 : 4;
     const long long kv_head_stride = (long long)c.seq_len * m->head_size;
+    const int qkv_ld = m->q_dim + 2 * m->kv_dim;
+    // out[b * ldo + r] = (W in[b])[r]: one pass over a quantised matrix for all sequences, else vector by vector
+    auto product = [&](const slai_qmatrix* wm, const float* in, float* out, long long ldo) -> int {
+        if (B > 1 && gemv_batch_supported(wm)) return gemv_batch_launch(ctx, out, wm, in, B, ldo);
+        for (int b = 0; b < B; b++) {
+            const int r = slai_gemv_quant(ctx, out + (size_t)b * ldo, wm, in + (size_t)b * wm->ncols, 1);
+            if (r) return r;
+        }
+        return SLAI_OK;
+    };
     for (int l = 0; l < c.n_layers; l++) {
         const LlamaLayer& w = m->layers[l];
+        void* kc = (char*)m->bt_k + (size_t)l * m->kv_layer_elems * esz;  // layer l of sequence 0; sequence b is bt_cache_bytes further
+        void* vc = (char*)m->bt_v + (size_t)l * m->kv_layer_elems * esz;
         if ((rc = rms_norm_rows_launch(ctx, m->bt_xn, m->bt_x, w.attn_norm, c.dim, B, c.rms_norm_eps))) return rc;
-        if ((rc = slai_gemv_quant(ctx, m->bt_q, w.wq, m->bt_xn, B))) return rc;
-        if ((rc = slai_gemv_quant(ctx, m->bt_kt, w.wk, m->bt_xn, B))) return rc;
-        if ((rc = slai_gemv_quant(ctx, m->bt_vt, w.wv, m->bt_xn, B))) return rc;
-        for (int b = 0; b < B; b++) {
-            if (h_pos[b] < 0) continue;
-            void* kc = (char*)m->bt_k + (size_t)b * m->bt_cache_bytes + (size_t)l * m->kv_layer_elems * esz;
-            void* vc = (char*)m->bt_v + (size_t)b * m->bt_cache_bytes + (size_t)l * m->kv_layer_elems * esz;
-            if ((rc = rope_kv_store_launch(ctx, m->bt_q + (size_t)b * m->q_dim, m->bt_kt + (size_t)b * m->kv_dim, m->bt_vt + (size_t)b * m->kv_dim,
-                                           m->q_dim, m->kv_dim, m->head_size, d_pos + b, m->rope_theta, c.rope_variant != 0, kc, vc,
-                                           c.kv_dtype == SLAI_KV_F16, kv_head_stride, false)))
-                return rc;
+        if ((rc = product(w.wq, m->bt_xn, m->bt_qkv, qkv_ld))) return rc;
+        if ((rc = product(w.wk, m->bt_xn, m->bt_qkv + m->q_dim, qkv_ld))) return rc;
+        if ((rc = product(w.wv, m->bt_xn, m->bt_qkv + m->q_dim + m->kv_dim, qkv_ld))) return rc;
+        if ((rc = rope_kv_store_seqs_launch(ctx, m->bt_qkv, qkv_ld, m->q_dim, m->kv_dim, m->head_size, d_pos, B, m->rope_theta, c.rope_variant != 0,
+                                            m->bt_q, kc, vc, c.kv_dtype == SLAI_KV_F16, kv_head_stride, (long long)m->bt_cache_bytes)))
+            return rc;
+        {
             AttnLaunch A = {};
-            A.q = m->bt_q + (size_t)b * m->q_dim; A.kcache = kc; A.vcache = vc; A.kv_dtype = c.kv_dtype;
+            A.q = m->bt_q; A.kcache = kc; A.vcache = vc; A.kv_dtype = c.kv_dtype;
             A.pos_stride = m->head_size; A.head_stride = kv_head_stride;
             A.n_heads = m->n_q_local; A.kv_mul = m->kv_mul; A.head_size = m->head_size;
-            A.d_pos = d_pos + b; A.max_pos = h_pos[b]; A.out = m->bt_xb + (size_t)b * m->q_dim; A.pdl = false;
-            A.scratch = nullptr; A.scratch_bytes = 0;
+            A.d_pos = nullptr; A.max_pos = max_pos; A.out = m->bt_xb; A.pdl = false;
+            A.scratch = m->bt_attn; A.scratch_bytes = (size_t)m->bt_n * m->attn_scratch_bytes;
+            A.batch = B; A.pos0 = 0; A.q_batch_stride = m->q_dim; A.out_batch_stride = m->q_dim; A.batch_counters = m->bt_tickets;
+            A.cache_batch_stride = (long long)m->bt_cache_bytes; A.d_pos_batch = d_pos;
             if ((rc = attention_launch(ctx, A))) return rc;
         }
-        if ((rc = slai_gemv_quant(ctx, m->bt_t, w.wo, m->bt_xb, B))) return rc;
+        if ((rc = product(w.wo, m->bt_xb, m->bt_t, c.dim))) return rc;
         if ((rc = slai_add_assign(ctx, m->bt_x, m->bt_t, (int64_t)B * c.dim))) return rc;
         if ((rc = rms_norm_rows_launch(ctx, m->bt_xn, m->bt_x, w.ffn_norm, c.dim, B, c.rms_norm_eps))) return rc;
-        if ((rc = slai_gemv_quant(ctx, m->bt_g, w.wgate, m->bt_xn, B))) return rc;
-        if ((rc = slai_gemv_quant(ctx, m->bt_u, w.wup, m->bt_xn, B))) return rc;
+        if ((rc = product(w.wgate, m->bt_xn, m->bt_g, m->hidden))) return rc;
+        if ((rc = product(w.wup, m->bt_xn, m->bt_u, m->hidden))) return rc;
         if ((rc = slai_silu_gate(ctx, m->bt_g, m->bt_u, (int64_t)B * m->hidden))) return rc;
-        if ((rc = slai_gemv_quant(ctx, m->bt_t, w.wdown, m->bt_g, B))) return rc;
+        if ((rc = product(w.wdown, m->bt_g, m->bt_t, c.dim))) return rc;
         if ((rc = slai_add_assign(ctx, m->bt_x, m->bt_t, (int64_t)B * c.dim))) return rc;
     }
     const slai_qmatrix* wout = m->output ? m->output : (m->embd_q ? m->embd_q : &m->embd_as_matrix);
     if ((rc = rms_norm_rows_launch(ctx, m->bt_xn, m->bt_x, m->out_norm, c.dim, B, c.rms_norm_eps))) return rc;
-    if ((rc = slai_gemv_quant(ctx, m->bt_logits, wout, m->bt_xn, B))) return rc;
+    if ((rc = product(wout, m->bt_xn, m->bt_logits, c.vocab_size))) return rc;
     for (int b = 0; b < B; b++)
         if ((rc = launch_argmax(ctx, m->bt_logits + (size_t)b * c.vocab_size, c.vocab_size, d_next + b, false))) return rc;
     if (h_logits) SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(h_logits, m->bt_logits, (size_t)B * c.vocab_size * 4, cudaMemcpyDeviceToHost, ctx->stream));

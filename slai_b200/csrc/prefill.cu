@@ -597,10 +597,14 @@ __global__ void prefill_embed_kernel(float* __restrict__ x, int dim, const int* 
 __global__ void rope_kv_store_kernel(const float* __restrict__ q_src, const float* __restrict__ k_src, const float* __restrict__ v_src,
                                      int ld, int q_dim, int kv_dim, int head_size, int pos0, const int* __restrict__ d_pos,
                                      const float* __restrict__ theta, int neox, float* __restrict__ q_out, int ldq, void* kcache, void* vcache,
-                                     int kv_f16, long long kv_head_stride) {
+                                     int kv_f16, long long kv_head_stride, long long seq_stride) {
     const int t = blockIdx.y;
     const int p = blockIdx.x * blockDim.x + threadIdx.x;  // pair index over q then k; then plain copies of v
-    const int pos = (d_pos ? *d_pos : pos0) + t;
+    // seq_stride > 0: row t is a sequence of its own, at position d_pos[t] of caches seq_stride bytes after row t - 1's
+    const int pos = seq_stride > 0 ? d_pos[t] : (d_pos ? *d_pos : pos0) + t;
+    if (pos < 0) return;
+    kcache = reinterpret_cast<char*>(kcache) + (size_t)t * seq_stride;
+    vcache = reinterpret_cast<char*>(vcache) + (size_t)t * seq_stride;
     const int nq = q_dim / 2, nk = kv_dim / 2;
     if (p < nq + nk) {
         const bool is_k = p >= nq;
@@ -769,7 +773,7 @@ int prefill_rope_kv_launch(slai_ctx* ctx, const float* qkv, int ld, int q_dim, i
     const int work = q_dim / 2 + kv_dim / 2 + kv_dim;
     rope_kv_store_kernel<<<dim3((work + 255) / 256, T), 256, 0, ctx->stream>>>(qkv, qkv + q_dim, qkv + q_dim + kv_dim, ld, q_dim, kv_dim, head_size,
                                                                               pos0, nullptr, theta, neox, q_out, q_dim, kcache, vcache, kv_f16,
-                                                                              kv_head_stride);
+                                                                              kv_head_stride, 0);
     SLAI_CHECK_CUDA(ctx, cudaGetLastError());
     return SLAI_OK;
 }
@@ -779,7 +783,18 @@ int rope_kv_store_launch(slai_ctx* ctx, float* q, const float* k, const float* v
     const int work = q_dim / 2 + kv_dim / 2 + (v ? kv_dim : 0);
     (void)pdl;
     rope_kv_store_kernel<<<dim3((work + 255) / 256, 1), 256, 0, ctx->stream>>>(q, k, v, 0, q_dim, kv_dim, head_size, 0, d_pos, theta, neox, q, q_dim,
-                                                                              kcache, vcache, kv_f16, kv_head_stride);
+                                                                              kcache, vcache, kv_f16, kv_head_stride, 0);
+    SLAI_CHECK_CUDA(ctx, cudaGetLastError());
+    return SLAI_OK;
+}
+int rope_kv_store_seqs_launch(slai_ctx* ctx, const float* qkv, int ld, int q_dim, int kv_dim, int head_size, const int* d_pos, int B,
+                              const float* theta, int neox, float* q_out, void* kcache, void* vcache, int kv_f16, long long kv_head_stride,
+                              long long seq_stride) {
+    SLAI_REQUIRE(ctx, seq_stride > 0 && d_pos && B >= 1, SLAI_ERR_INVALID_ARG, "rope: a batch of sequences needs positions and a cache stride");
+    const int work = q_dim / 2 + kv_dim / 2 + kv_dim;
+    rope_kv_store_kernel<<<dim3((work + 255) / 256, B), 256, 0, ctx->stream>>>(qkv, qkv + q_dim, qkv + q_dim + kv_dim, ld, q_dim, kv_dim, head_size,
+                                                                              0, d_pos, theta, neox, q_out, q_dim, kcache, vcache, kv_f16,
+                                                                              kv_head_stride, seq_stride);
     SLAI_CHECK_CUDA(ctx, cudaGetLastError());
     return SLAI_OK;
 }

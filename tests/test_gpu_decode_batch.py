@@ -91,6 +91,9 @@ def test_batch_argument_errors(backend):
         m.decode_batch([1, 2], [0, cfg.seq_len])
     lg, nxt = m.decode_batch([1, 2], [0, -1])   # a sequence left out
     assert np.isfinite(lg[0]).all() and nxt[0] == int(np.argmax(lg[0]))
+    lg1, _ = m.decode_batch([1], [0])           # fewer sequences than reserved; one sequence takes the single-vector kernels
+    l0, _ = m.forward_logits(0, 1)
+    assert rel_l2(lg1[0], l0) < 1e-4 and rel_l2(lg[0], l0) < 1e-4
     m.batch_reserve(0)
     with pytest.raises(SlaiError):
         m.decode_batch([1], [0])
