@@ -280,7 +280,9 @@ struct GemvLaunch {
 int gemv_launch(slai_ctx* ctx, const GemvLaunch& L);
 // gemv_batch.cu: out[b][m] = sum_k W[m][k] v[b][k] for a batch of 2..8 vectors in one pass over a quantised matrix
 bool gemv_batch_supported(const slai_qmatrix* w);
-int gemv_batch_launch(slai_ctx* ctx, float* d_out, const slai_qmatrix* w, const float* d_v, int n_batch, long long ldo = 0);
+enum { BATCH_STORE = 0, BATCH_ADD = 1, BATCH_SILU = 2 };
+int gemv_batch_launch(slai_ctx* ctx, float* d_out, const slai_qmatrix* w, const float* d_v, int n_batch, long long ldo = 0, int epi = BATCH_STORE,
+                      const float* d_gate = nullptr);
 
 // attention.cu
 struct AttnLaunch {

@@ -207,13 +207,23 @@ __global__ void __launch_bounds__(BTHREADS, 1) gemv_batch_kernel(const __grid_co
 }
 
 // out[v][m] = sum over the chunks, in order, of the partial sums.
-__global__ void gemv_batch_reduce_kernel(float* out, long long ldo, const float* part, int nch, int nv, int mp, int M, int n_batch) {
+// epi: BATCH_STORE, BATCH_ADD (out += sum: the residual streams of the batch), BATCH_SILU (out = sum * silu(gate), gate laid
+// out like out: ops/silu.rs:50-58 with the sum as h2 and gate as h1).
+__global__ void gemv_batch_reduce_kernel(float* out, long long ldo, const float* part, int nch, int nv, int mp, int M, int n_batch, int epi,
+                                         const float* gate) {
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (long long)n_batch * M) return;
     const int v = (int)(idx / M), m = (int)(idx - (long long)v * M);
     float s = 0.f;
     for (int c = 0; c < nch; c++) s += part[((size_t)c * nv + v) * mp + m];
-    out[(long long)v * ldo + m] = s;
+    const long long o = (long long)v * ldo + m;
+    if (epi == BATCH_ADD) {
+        s = out[o] + s;
+    } else if (epi == BATCH_SILU) {
+        const float g = gate[o];
+        s = s * (g / (1.0f + expf(-g)));
+    }
+    out[o] = s;
 }
 
 template <class F>
@@ -229,7 +239,7 @@ size_t batch_smem(int nv, int ch, uint32_t* plane_out, uint32_t* vstride_out) {
 }
 
 template <class F, int NV>
-int launch_batch_inst(slai_ctx* ctx, BatchParams& P, float* d_out, long long ldo, int M) {
+int launch_batch_inst(slai_ctx* ctx, BatchParams& P, float* d_out, long long ldo, int M, int epi, const float* gate) {
     // Steps per chunk: the fewest rounds of (staging + ch steps) over the SMs; staging a chunk costs about three steps.
     const int G = ctx->sm_count > 0 ? ctx->sm_count : 148;
     int best_ch = 1;
@@ -262,16 +272,16 @@ int launch_batch_inst(slai_ctx* ctx, BatchParams& P, float* d_out, long long ldo
     kern<<<grid, BTHREADS, smem, ctx->stream>>>(P);
     SLAI_CHECK_CUDA(ctx, cudaGetLastError());
     const long long total = (long long)P.n_batch * M;
-    gemv_batch_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(d_out, ldo, P.part, P.nch, NV, P.mp, M, P.n_batch);
+    gemv_batch_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(d_out, ldo, P.part, P.nch, NV, P.mp, M, P.n_batch, epi, gate);
     SLAI_CHECK_CUDA(ctx, cudaGetLastError());
     return SLAI_OK;
 }
 
 template <class F>
-int launch_batch_fmt(slai_ctx* ctx, BatchParams& P, float* d_out, long long ldo, int M) {
-    if (P.n_batch <= 2) return launch_batch_inst<F, 2>(ctx, P, d_out, ldo, M);
-    if (P.n_batch <= 4) return launch_batch_inst<F, 4>(ctx, P, d_out, ldo, M);
-    return launch_batch_inst<F, 8>(ctx, P, d_out, ldo, M);
+int launch_batch_fmt(slai_ctx* ctx, BatchParams& P, float* d_out, long long ldo, int M, int epi, const float* gate) {
+    if (P.n_batch <= 2) return launch_batch_inst<F, 2>(ctx, P, d_out, ldo, M, epi, gate);
+    if (P.n_batch <= 4) return launch_batch_inst<F, 4>(ctx, P, d_out, ldo, M, epi, gate);
+    return launch_batch_inst<F, 8>(ctx, P, d_out, ldo, M, epi, gate);
 }
 
 }  // namespace
@@ -280,8 +290,10 @@ bool gemv_batch_supported(const slai_qmatrix* w) {
     return w->fmt == SLAI_FMT_Q8_0 || w->fmt == SLAI_FMT_Q4_K || w->fmt == SLAI_FMT_Q5_K || w->fmt == SLAI_FMT_Q6_K;
 }
 
-// out[b * ldo + m] = sum_k W[m][k] v[b][k] for b < n_batch (2..8), one pass over W (ldo 0: the rows of `out` are M apart).
-int gemv_batch_launch(slai_ctx* ctx, float* d_out, const slai_qmatrix* w, const float* d_v, int n_batch, long long ldo) {
+// out[b * ldo + m] = sum_k W[m][k] v[b][k] for b < n_batch (2..8), one pass over W (ldo 0: the rows of `out` are M apart);
+// `epi` folds a residual add or the SiLU gate into the store.
+int gemv_batch_launch(slai_ctx* ctx, float* d_out, const slai_qmatrix* w, const float* d_v, int n_batch, long long ldo, int epi,
+                      const float* d_gate) {
     SLAI_REQUIRE(ctx, gemv_batch_supported(w), SLAI_ERR_UNSUPPORTED_FORMAT, "gemv: format %d has no batched kernel", w->fmt);
     SLAI_REQUIRE(ctx, n_batch >= 2 && n_batch <= 8, SLAI_ERR_INVALID_ARG, "gemv: batch of %d", n_batch);
     SLAI_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(d_v) & 15) == 0, SLAI_ERR_INVALID_ARG, "gemv: the input vectors must be 16-byte aligned");
@@ -298,11 +310,12 @@ int gemv_batch_launch(slai_ctx* ctx, float* d_out, const slai_qmatrix* w, const 
     const int M = (int)w->nrows;
     if (ldo <= 0) ldo = M;
     SLAI_REQUIRE(ctx, ldo >= M, SLAI_ERR_SHAPE, "gemv: output rows %lld apart hold fewer than %d values", ldo, M);
+    SLAI_REQUIRE(ctx, epi == BATCH_STORE || epi == BATCH_ADD || (epi == BATCH_SILU && d_gate), SLAI_ERR_INVALID_ARG, "gemv: batch epilogue %d", epi);
     switch (w->fmt) {
-        case SLAI_FMT_Q8_0: return launch_batch_fmt<Q80>(ctx, P, d_out, ldo, M);
-        case SLAI_FMT_Q4_K: return launch_batch_fmt<Q4K>(ctx, P, d_out, ldo, M);
-        case SLAI_FMT_Q5_K: return launch_batch_fmt<Q5K>(ctx, P, d_out, ldo, M);
-        case SLAI_FMT_Q6_K: return launch_batch_fmt<Q6K>(ctx, P, d_out, ldo, M);
+        case SLAI_FMT_Q8_0: return launch_batch_fmt<Q80>(ctx, P, d_out, ldo, M, epi, d_gate);
+        case SLAI_FMT_Q4_K: return launch_batch_fmt<Q4K>(ctx, P, d_out, ldo, M, epi, d_gate);
+        case SLAI_FMT_Q5_K: return launch_batch_fmt<Q5K>(ctx, P, d_out, ldo, M, epi, d_gate);
+        case SLAI_FMT_Q6_K: return launch_batch_fmt<Q6K>(ctx, P, d_out, ldo, M, epi, d_gate);
     }
     return SLAI_ERR_UNSUPPORTED_FORMAT;
 }

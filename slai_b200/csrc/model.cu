@@ -147,10 +147,24 @@ struct slai_llama {
     int* bt_i = nullptr;  // device ints: [0, 8) tokens, [8, 16) positions, [16, 24) greedy choices
     void* bt_attn = nullptr;  // attention partials of all sequences
     unsigned int* bt_tickets = nullptr;
+    // the step of n sequences as a replayed graph (index n), captured for contexts up to bt_cap[n] positions
+    cudaGraphExec_t bt_exec[9] = {};
+    int bt_cap[9] = {};
+    bool bt_warm[9] = {};
 };
+
+static void llama_drop_batch_graphs(slai_llama* m) {
+    for (int i = 0; i < 9; i++) {
+        if (m->bt_exec[i]) cudaGraphExecDestroy(m->bt_exec[i]);
+        m->bt_exec[i] = nullptr;
+        m->bt_cap[i] = 0;
+        m->bt_warm[i] = false;
+    }
+}
 
 static void llama_drop_batch(slai_llama* m) {
     if (m->bt_n) cudaStreamSynchronize(m->ctx->stream);
+    llama_drop_batch_graphs(m);
     cudaFree(m->bt_k); cudaFree(m->bt_v); cudaFree(m->bt_x); cudaFree(m->bt_xn); cudaFree(m->bt_q); cudaFree(m->bt_qkv);
     cudaFree(m->bt_xb); cudaFree(m->bt_t); cudaFree(m->bt_g); cudaFree(m->bt_u); cudaFree(m->bt_logits); cudaFree(m->bt_i);
     cudaFree(m->bt_attn); cudaFree(m->bt_tickets);
@@ -580,6 +594,76 @@ SLAI_API int slai_llama_batch_reserve(slai_llama* m, int32_t n_seq) {
 // One token of every sequence b < n_seq at position h_pos[b] (a negative position leaves sequence b out of this step: its
 // cache is not touched and its outputs mean nothing).  h_logits: n_seq x vocab floats or null; h_next: the greedy choice
 // per sequence or null.
+// The launches of one step of B sequences (tokens and positions are in bt_i); attention is sized for contexts of up to
+// `cap_pos` + 1 positions.
+static int llama_batch_record(slai_llama* m, int B, int cap_pos) {
+    slai_ctx* ctx = m->ctx;
+    const slai_llama_config& c = m->cfg;
+    int* d_tok = m->bt_i;
+    int* d_pos = m->bt_i + 8;
+    int* d_next = m->bt_i + 16;
+    int rc;
+    if ((rc = prefill_embed_launch(ctx, m->bt_x, c.dim, d_tok, B, m->embd_q ? nullptr : m->token_embd, m->embd_q))) return rc;
+    const size_t esz = c.kv_dtype == SLAI_KV_F16 ? 2 : 4;
+    const long long kv_head_stride = (long long)c.seq_len * m->head_size;
+    const int qkv_ld = m->q_dim + 2 * m->kv_dim;
+    // out[b * ldo + r] (=, +=) (W in[b])[r]: one pass over a quantised matrix for all sequences (the residual add or the SiLU
+    // gate folded into its store), else vector by vector and the operators after it
+    auto product = [&](const slai_qmatrix* wm, const float* in, float* out, long long ldo, int epi = BATCH_STORE, float* gate = nullptr) -> int {
+        if (B > 1 && gemv_batch_supported(wm)) return gemv_batch_launch(ctx, out, wm, in, B, ldo, epi, gate);
+        float* dst = epi == BATCH_ADD ? m->bt_t : out;  // (the residual streams are dense: ldo == rows)
+        for (int b = 0; b < B; b++) {
+            const int r = slai_gemv_quant(ctx, dst + (size_t)b * ldo, wm, in + (size_t)b * wm->ncols, 1);
+            if (r) return r;
+        }
+        if (epi == BATCH_ADD) return slai_add_assign(ctx, out, m->bt_t, (int64_t)B * ldo);
+        if (epi == BATCH_SILU) {
+            int r = slai_silu_gate(ctx, gate, out, (int64_t)B * ldo);
+            if (!r) r = slai_copy(ctx, out, gate, (int64_t)B * ldo);
+            return r;
+        }
+        return SLAI_OK;
+    };
+    for (int l = 0; l < c.n_layers; l++) {
+        const LlamaLayer& w = m->layers[l];
+        void* kc = (char*)m->bt_k + (size_t)l * m->kv_layer_elems * esz;  // layer l of sequence 0; sequence b is bt_cache_bytes further
+        void* vc = (char*)m->bt_v + (size_t)l * m->kv_layer_elems * esz;
+        if ((rc = rms_norm_rows_launch(ctx, m->bt_xn, m->bt_x, w.attn_norm, c.dim, B, c.rms_norm_eps))) return rc;
+        if ((rc = product(w.wq, m->bt_xn, m->bt_qkv, qkv_ld))) return rc;
+        if ((rc = product(w.wk, m->bt_xn, m->bt_qkv + m->q_dim, qkv_ld))) return rc;
+        if ((rc = product(w.wv, m->bt_xn, m->bt_qkv + m->q_dim + m->kv_dim, qkv_ld))) return rc;
+        if ((rc = rope_kv_store_seqs_launch(ctx, m->bt_qkv, qkv_ld, m->q_dim, m->kv_dim, m->head_size, d_pos, B, m->rope_theta, c.rope_variant != 0,
+                                            m->bt_q, kc, vc, c.kv_dtype == SLAI_KV_F16, kv_head_stride, (long long)m->bt_cache_bytes)))
+            return rc;
+        {
+            AttnLaunch A = {};
+            A.q = m->bt_q; A.kcache = kc; A.vcache = vc; A.kv_dtype = c.kv_dtype;
+            A.pos_stride = m->head_size; A.head_stride = kv_head_stride;
+            A.n_heads = m->n_q_local; A.kv_mul = m->kv_mul; A.head_size = m->head_size;
+            A.d_pos = nullptr; A.max_pos = cap_pos; A.out = m->bt_xb; A.pdl = false;
+            A.scratch = m->bt_attn; A.scratch_bytes = (size_t)m->bt_n * m->attn_scratch_bytes;
+            A.batch = B; A.pos0 = 0; A.q_batch_stride = m->q_dim; A.out_batch_stride = m->q_dim; A.batch_counters = m->bt_tickets;
+            A.cache_batch_stride = (long long)m->bt_cache_bytes; A.d_pos_batch = d_pos;
+            if ((rc = attention_launch(ctx, A))) return rc;
+        }
+        if ((rc = product(w.wo, m->bt_xb, m->bt_x, c.dim, BATCH_ADD))) return rc;
+        if ((rc = rms_norm_rows_launch(ctx, m->bt_xn, m->bt_x, w.ffn_norm, c.dim, B, c.rms_norm_eps))) return rc;
+        if ((rc = product(w.wgate, m->bt_xn, m->bt_g, m->hidden))) return rc;
+        if ((rc = product(w.wup, m->bt_xn, m->bt_u, m->hidden, BATCH_SILU, m->bt_g))) return rc;
+        if ((rc = product(w.wdown, m->bt_u, m->bt_x, c.dim, BATCH_ADD))) return rc;
+    }
+    const slai_qmatrix* wout = m->output ? m->output : (m->embd_q ? m->embd_q : &m->embd_as_matrix);
+    if ((rc = rms_norm_rows_launch(ctx, m->bt_xn, m->bt_x, m->out_norm, c.dim, B, c.rms_norm_eps))) return rc;
+    if ((rc = product(wout, m->bt_xn, m->bt_logits, c.vocab_size))) return rc;
+    for (int b = 0; b < B; b++)
+        if ((rc = launch_argmax(ctx, m->bt_logits + (size_t)b * c.vocab_size, c.vocab_size, d_next + b, false))) return rc;
+    return SLAI_OK;
+}
+
+// One token of every sequence b < n_seq at position h_pos[b] (a negative position leaves sequence b out of this step: its
+// cache is not touched and its outputs mean nothing).  h_logits: n_seq x vocab floats or null; h_next: the greedy choice
+// per sequence or null.  The first step of a batch size runs launch by launch; later ones replay a graph of the step, captured
+// again whenever the longest context crosses a multiple of 256 positions (the attention launch is sized for the context).
 SLAI_API int slai_llama_decode_batch(slai_llama* m, int32_t n_seq, const int32_t* h_tokens, const int32_t* h_pos, float* h_logits,
                                      int32_t* h_next) {
     if (!m || !h_tokens || !h_pos) return SLAI_ERR_INVALID_ARG;
@@ -605,59 +689,42 @@ SLAI_API int slai_llama_decode_batch(slai_llama* m, int32_t n_seq, const int32_t
     }
     SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(m->bt_i, h, sizeof(h), cudaMemcpyHostToDevice, ctx->stream));
     const int B = n_seq;
-    int* d_tok = m->bt_i;
-    int* d_pos = m->bt_i + 8;
-    int* d_next = m->bt_i + 16;
-    int rc;
-    if ((rc = prefill_embed_launch(ctx, m->bt_x, c.dim, d_tok, B, m->embd_q ? nullptr : m->token_embd, m->embd_q))) return rc;
-    const size_t esz = c.kv_dtype == SLAI_KV_F16 ? 2 : 4;
-    const long long kv_head_stride = (long long)c.seq_len * m->head_size;
-    const int qkv_ld = m->q_dim + 2 * m->kv_dim;
-    // out[b * ldo + r] = (W in[b])[r]: one pass over a quantised matrix for all sequences, else vector by vector
-    auto product = [&](const slai_qmatrix* wm, const float* in, float* out, long long ldo) -> int {
-        if (B > 1 && gemv_batch_supported(wm)) return gemv_batch_launch(ctx, out, wm, in, B, ldo);
-        for (int b = 0; b < B; b++) {
-            const int r = slai_gemv_quant(ctx, out + (size_t)b * ldo, wm, in + (size_t)b * wm->ncols, 1);
-            if (r) return r;
+    const int cap_pos = std::min(c.seq_len - 1, (max_pos / 256 + 1) * 256 - 1);
+    int rc = SLAI_OK;
+    if (!m->graphs.use_graph || !m->bt_warm[B]) {
+        m->bt_warm[B] = true;  // the first step also sets kernel attributes and sizes the scratch: not inside a capture
+        rc = llama_batch_record(m, B, cap_pos);
+    } else {
+        if (m->bt_exec[B] && m->bt_cap[B] != cap_pos) {
+            cudaGraphExecDestroy(m->bt_exec[B]);
+            m->bt_exec[B] = nullptr;
         }
-        return SLAI_OK;
-    };
-    for (int l = 0; l < c.n_layers; l++) {
-        const LlamaLayer& w = m->layers[l];
-        void* kc = (char*)m->bt_k + (size_t)l * m->kv_layer_elems * esz;  // layer l of sequence 0; sequence b is bt_cache_bytes further
-        void* vc = (char*)m->bt_v + (size_t)l * m->kv_layer_elems * esz;
-        if ((rc = rms_norm_rows_launch(ctx, m->bt_xn, m->bt_x, w.attn_norm, c.dim, B, c.rms_norm_eps))) return rc;
-        if ((rc = product(w.wq, m->bt_xn, m->bt_qkv, qkv_ld))) return rc;
-        if ((rc = product(w.wk, m->bt_xn, m->bt_qkv + m->q_dim, qkv_ld))) return rc;
-        if ((rc = product(w.wv, m->bt_xn, m->bt_qkv + m->q_dim + m->kv_dim, qkv_ld))) return rc;
-        if ((rc = rope_kv_store_seqs_launch(ctx, m->bt_qkv, qkv_ld, m->q_dim, m->kv_dim, m->head_size, d_pos, B, m->rope_theta, c.rope_variant != 0,
-                                            m->bt_q, kc, vc, c.kv_dtype == SLAI_KV_F16, kv_head_stride, (long long)m->bt_cache_bytes)))
-            return rc;
-        {
-            AttnLaunch A = {};
-            A.q = m->bt_q; A.kcache = kc; A.vcache = vc; A.kv_dtype = c.kv_dtype;
-            A.pos_stride = m->head_size; A.head_stride = kv_head_stride;
-            A.n_heads = m->n_q_local; A.kv_mul = m->kv_mul; A.head_size = m->head_size;
-            A.d_pos = nullptr; A.max_pos = max_pos; A.out = m->bt_xb; A.pdl = false;
-            A.scratch = m->bt_attn; A.scratch_bytes = (size_t)m->bt_n * m->attn_scratch_bytes;
-            A.batch = B; A.pos0 = 0; A.q_batch_stride = m->q_dim; A.out_batch_stride = m->q_dim; A.batch_counters = m->bt_tickets;
-            A.cache_batch_stride = (long long)m->bt_cache_bytes; A.d_pos_batch = d_pos;
-            if ((rc = attention_launch(ctx, A))) return rc;
+        if (!m->bt_exec[B]) {
+            cudaGraph_t graph = nullptr;
+            SLAI_CHECK_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+            rc = llama_batch_record(m, B, cap_pos);
+            cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+            if (rc == SLAI_OK && e == cudaSuccess) {
+                e = cudaGraphInstantiate(&m->bt_exec[B], graph, 0);
+                if (e != cudaSuccess) m->bt_exec[B] = nullptr;
+            }
+            if (graph) cudaGraphDestroy(graph);
+            if (rc != SLAI_OK || e != cudaSuccess) {
+                cudaGetLastError();
+                m->bt_exec[B] = nullptr;
+                m->graphs.use_graph = false;  // launch by launch from now on
+                rc = llama_batch_record(m, B, cap_pos);
+            } else {
+                m->bt_cap[B] = cap_pos;
+            }
         }
-        if ((rc = product(w.wo, m->bt_xb, m->bt_t, c.dim))) return rc;
-        if ((rc = slai_add_assign(ctx, m->bt_x, m->bt_t, (int64_t)B * c.dim))) return rc;
-        if ((rc = rms_norm_rows_launch(ctx, m->bt_xn, m->bt_x, w.ffn_norm, c.dim, B, c.rms_norm_eps))) return rc;
-        if ((rc = product(w.wgate, m->bt_xn, m->bt_g, m->hidden))) return rc;
-        if ((rc = product(w.wup, m->bt_xn, m->bt_u, m->hidden))) return rc;
-        if ((rc = slai_silu_gate(ctx, m->bt_g, m->bt_u, (int64_t)B * m->hidden))) return rc;
-        if ((rc = product(w.wdown, m->bt_g, m->bt_t, c.dim))) return rc;
-        if ((rc = slai_add_assign(ctx, m->bt_x, m->bt_t, (int64_t)B * c.dim))) return rc;
+        if (m->bt_exec[B]) {
+            SLAI_CHECK_CUDA(ctx, cudaGraphLaunch(m->bt_exec[B], ctx->stream));
+            rc = SLAI_OK;
+        }
     }
-    const slai_qmatrix* wout = m->output ? m->output : (m->embd_q ? m->embd_q : &m->embd_as_matrix);
-    if ((rc = rms_norm_rows_launch(ctx, m->bt_xn, m->bt_x, m->out_norm, c.dim, B, c.rms_norm_eps))) return rc;
-    if ((rc = product(wout, m->bt_xn, m->bt_logits, c.vocab_size))) return rc;
-    for (int b = 0; b < B; b++)
-        if ((rc = launch_argmax(ctx, m->bt_logits + (size_t)b * c.vocab_size, c.vocab_size, d_next + b, false))) return rc;
+    if (rc) return rc;
+    int* d_next = m->bt_i + 16;
     if (h_logits) SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(h_logits, m->bt_logits, (size_t)B * c.vocab_size * 4, cudaMemcpyDeviceToHost, ctx->stream));
     if (h_next) SLAI_CHECK_CUDA(ctx, cudaMemcpyAsync(h_next, d_next, (size_t)B * 4, cudaMemcpyDeviceToHost, ctx->stream));
     SLAI_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -689,6 +756,7 @@ SLAI_API int slai_llama_set_matrix(slai_llama* m, int id, int layer, const slai_
     slai_ctx* ctx = m->ctx;
     const slai_llama_config& c = m->cfg;
     destroy_graphs(m->graphs);
+    llama_drop_batch_graphs(m);
     auto shape_is = [&](int64_t r, int64_t k) { return w->nrows == r && w->ncols == k; };
     if (id == SLAI_W_OUTPUT) {
         // tensor parallel: either the whole matrix on every rank, or this rank's vocab / tp consecutive rows (the
@@ -727,6 +795,7 @@ static int llama_set_f32_impl(slai_llama* m, int id, int layer, const float* dat
     slai_ctx* ctx = m->ctx;
     const slai_llama_config& c = m->cfg;
     destroy_graphs(m->graphs);
+    llama_drop_batch_graphs(m);
     if (id == SLAI_W_TOKEN_EMBD) {
         SLAI_REQUIRE(ctx, n == (int64_t)c.vocab_size * c.dim, SLAI_ERR_SHAPE, "llama: token_embd needs vocab*dim floats");
         int rc = copy_f32(ctx, &m->token_embd, data, n, dev);

@@ -74,6 +74,28 @@ def test_batch_equals_single_sequence_decode(backend):
     assert np.array_equal(l0.view(np.uint32), l1.view(np.uint32))
 
 
+def test_batch_step_across_a_graph_boundary(backend):
+    """The replayed step is captured again when the longest context crosses a multiple of 256 positions: two sequences, one
+    256 positions ahead of... the other never leaving the first bucket, decoded past position 256."""
+    cfg = Llama2Config(dim=256, hidden_dim=512, n_layers=2, n_q_heads=4, n_kv_heads=2, vocab_size=1000, seq_len=320, kv_dtype=_lib.KV_F16)
+    w = synthetic_llama_host(cfg, synth.FMT_Q4_K, synth.FMT_Q6_K, seed=2, std=0.05, embd_std=1.0)
+    mb = llama_from_host(backend, cfg, w, synth.FMT_Q4_K, synth.FMT_Q6_K)
+    mb.batch_reserve(2)
+    singles = [llama_from_host(backend, cfg, w, synth.FMT_Q4_K, synth.FMT_Q6_K) for _ in range(2)]
+    tok = [5, 77]
+    for step in range(266):
+        pos = [step, step // 2]     # sequence 1 advances every other step and stays below 256
+        p = [pos[0], pos[1] if step % 2 == 0 else -1]
+        lg, nxt = mb.decode_batch(tok, p)
+        for b in range(2):
+            if p[b] < 0:
+                continue
+            ls, ns = singles[b].forward_logits(p[b], tok[b])
+            if step < 4 or step > 250:
+                assert rel_l2(lg[b], ls) < 1e-4, (step, b)
+            tok[b] = int(ns)
+
+
 def test_batch_argument_errors(backend):
     cfg = Llama2Config(**{**TINY_LLAMA.__dict__, "kv_dtype": _lib.KV_F32})
     m = llama_from_host(backend, cfg, synthetic_llama_host(cfg, synth.FMT_Q8_0, seed=9), synth.FMT_Q8_0)
