@@ -280,7 +280,10 @@ struct GemvLaunch {
 int gemv_launch(slai_ctx* ctx, const GemvLaunch& L);
 // gemv_batch.cu: out[b][m] = sum_k W[m][k] v[b][k] for a batch of 2..8 vectors in one pass over a quantised matrix
 bool gemv_batch_supported(const slai_qmatrix* w);
-enum { BATCH_STORE = 0, BATCH_ADD = 1, BATCH_SILU = 2 };
+enum { BATCH_STORE = 0, BATCH_ADD = 1, BATCH_SILU = 2, BATCH_PAIR_SILU = 3 };
+// the same for the concatenation by rows of up to three matrices that share the input (see gemv_batch.cu)
+int gemv_batch_launch_multi(slai_ctx* ctx, float* d_out, const slai_qmatrix* const* ws, int nw, const float* d_v, int n_batch, long long ldo,
+                            int epi, const float* d_gate);
 int gemv_batch_launch(slai_ctx* ctx, float* d_out, const slai_qmatrix* w, const float* d_v, int n_batch, long long ldo = 0, int epi = BATCH_STORE,
                       const float* d_gate = nullptr);
 

@@ -26,7 +26,9 @@ constexpr int MAX_CH = 8;
 constexpr int BSMEM_LIMIT = 227 * 1024;
 
 struct BatchParams {
-    const uint8_t* w;
+    const uint8_t* w[3];   // up to three matrices of the same format and K that share the input (q / k / v, gate / up): their
+    int t0[3];             // 16-row tiles form one tile space, matrix i starts at tile t0[i]
+    int nw;
     long long tile_bytes;
     int ntiles, nsteps, K;
     int ch, nch, ngroups;  // steps per chunk, chunks, groups of 16 tiles
@@ -91,7 +93,11 @@ __global__ void __launch_bounds__(BTHREADS, 1) gemv_batch_kernel(const __grid_co
         const int nst = min(P.ch, P.nsteps - s0);
         const int tile = grp * BWARPS + warp;
         const bool active = tile < P.ntiles;
-        const uint8_t* src = P.w + (size_t)(active ? tile : 0) * P.tile_bytes + (size_t)s0 * BatchGeom<F>::STEP;
+        const uint8_t* wbase = P.w[0];
+        int wt0 = 0;
+        if (P.nw > 1 && tile >= P.t0[1]) { wbase = P.w[1]; wt0 = P.t0[1]; }
+        if (P.nw > 2 && tile >= P.t0[2]) { wbase = P.w[2]; wt0 = P.t0[2]; }
+        const uint8_t* src = wbase + (size_t)(active ? tile - wt0 : 0) * P.tile_bytes + (size_t)s0 * BatchGeom<F>::STEP;
         // the first two blocks of this warp's tile are on their way while the vectors are staged
         if (active) stage_request<F>(src, wb, lane);
         stage_commit();
@@ -208,7 +214,8 @@ __global__ void __launch_bounds__(BTHREADS, 1) gemv_batch_kernel(const __grid_co
 
 // out[v][m] = sum over the chunks, in order, of the partial sums.
 // epi: BATCH_STORE, BATCH_ADD (out += sum: the residual streams of the batch), BATCH_SILU (out = sum * silu(gate), gate laid
-// out like out: ops/silu.rs:50-58 with the sum as h2 and gate as h1).
+// out like out: ops/silu.rs:50-58 with the sum as h2 and gate as h1), BATCH_PAIR_SILU (two matrices of M rows each in one
+// launch, gate then up: out = up sum * silu(gate sum)).
 __global__ void gemv_batch_reduce_kernel(float* out, long long ldo, const float* part, int nch, int nv, int mp, int M, int n_batch, int epi,
                                          const float* gate) {
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -222,6 +229,10 @@ __global__ void gemv_batch_reduce_kernel(float* out, long long ldo, const float*
     } else if (epi == BATCH_SILU) {
         const float g = gate[o];
         s = s * (g / (1.0f + expf(-g)));
+    } else if (epi == BATCH_PAIR_SILU) {
+        float u = 0.f;
+        for (int c = 0; c < nch; c++) u += part[((size_t)c * nv + v) * mp + M + m];
+        s = u * (s / (1.0f + expf(-s)));
     }
     out[o] = s;
 }
@@ -291,26 +302,46 @@ bool gemv_batch_supported(const slai_qmatrix* w) {
 }
 
 // out[b * ldo + m] = sum_k W[m][k] v[b][k] for b < n_batch (2..8), one pass over W (ldo 0: the rows of `out` are M apart);
-// `epi` folds a residual add or the SiLU gate into the store.
-int gemv_batch_launch(slai_ctx* ctx, float* d_out, const slai_qmatrix* w, const float* d_v, int n_batch, long long ldo, int epi,
-                      const float* d_gate) {
+// `epi` folds a residual add or the SiLU gate into the store.  W is the concatenation by rows of `nw` (1..3) matrices of the
+// same format and width (all but the last with a multiple of 16 rows); with BATCH_PAIR_SILU the two matrices are gate and up
+// of equal height M and out[b * ldo + m], m < M, receives up * silu(gate).
+int gemv_batch_launch_multi(slai_ctx* ctx, float* d_out, const slai_qmatrix* const* ws, int nw, const float* d_v, int n_batch, long long ldo,
+                            int epi, const float* d_gate) {
+    SLAI_REQUIRE(ctx, nw >= 1 && nw <= 3 && ws && ws[0], SLAI_ERR_INVALID_ARG, "gemv: %d matrices in one batched launch", nw);
+    const slai_qmatrix* w = ws[0];
     SLAI_REQUIRE(ctx, gemv_batch_supported(w), SLAI_ERR_UNSUPPORTED_FORMAT, "gemv: format %d has no batched kernel", w->fmt);
     SLAI_REQUIRE(ctx, n_batch >= 2 && n_batch <= 8, SLAI_ERR_INVALID_ARG, "gemv: batch of %d", n_batch);
     SLAI_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(d_v) & 15) == 0, SLAI_ERR_INVALID_ARG, "gemv: the input vectors must be 16-byte aligned");
     BatchParams P = {};
-    P.w = w->data;
+    int rows_total = 0, tiles = 0;
+    for (int i = 0; i < nw; i++) {
+        SLAI_REQUIRE(ctx, ws[i] && ws[i]->fmt == w->fmt && ws[i]->ncols == w->ncols && ws[i]->tile_bytes == w->tile_bytes, SLAI_ERR_SHAPE,
+                     "gemv: matrices of one batched launch must share format and width");
+        SLAI_REQUIRE(ctx, i == nw - 1 || ws[i]->nrows % 16 == 0, SLAI_ERR_SHAPE, "gemv: %lld rows before another matrix of the launch",
+                     (long long)ws[i]->nrows);
+        P.w[i] = ws[i]->data;
+        P.t0[i] = tiles;
+        tiles += (int)layout::num_tiles(ws[i]->nrows);
+        rows_total += (int)ws[i]->nrows;
+    }
+    P.nw = nw;
     P.tile_bytes = w->tile_bytes;
-    P.ntiles = (int)layout::num_tiles(w->nrows);
+    P.ntiles = tiles;
     P.nsteps = (int)layout::num_steps(w->fmt, w->ncols);
     P.K = (int)w->ncols;
     P.ngroups = (P.ntiles + BWARPS - 1) / BWARPS;
     P.n_batch = n_batch;
     P.v = d_v;
     P.mp = P.ntiles * 16;
-    const int M = (int)w->nrows;
+    int M = rows_total;
+    if (epi == BATCH_PAIR_SILU) {
+        SLAI_REQUIRE(ctx, nw == 2 && ws[0]->nrows == ws[1]->nrows, SLAI_ERR_SHAPE, "gemv: the gate / up epilogue takes two matrices of equal height");
+        M = (int)ws[0]->nrows;
+    }
     if (ldo <= 0) ldo = M;
     SLAI_REQUIRE(ctx, ldo >= M, SLAI_ERR_SHAPE, "gemv: output rows %lld apart hold fewer than %d values", ldo, M);
-    SLAI_REQUIRE(ctx, epi == BATCH_STORE || epi == BATCH_ADD || (epi == BATCH_SILU && d_gate), SLAI_ERR_INVALID_ARG, "gemv: batch epilogue %d", epi);
+    SLAI_REQUIRE(ctx, epi == BATCH_STORE || epi == BATCH_ADD || epi == BATCH_PAIR_SILU || (epi == BATCH_SILU && d_gate), SLAI_ERR_INVALID_ARG,
+                 "gemv: batch epilogue %d", epi);
     switch (w->fmt) {
         case SLAI_FMT_Q8_0: return launch_batch_fmt<Q80>(ctx, P, d_out, ldo, M, epi, d_gate);
         case SLAI_FMT_Q4_K: return launch_batch_fmt<Q4K>(ctx, P, d_out, ldo, M, epi, d_gate);
@@ -318,4 +349,9 @@ int gemv_batch_launch(slai_ctx* ctx, float* d_out, const slai_qmatrix* w, const 
         case SLAI_FMT_Q6_K: return launch_batch_fmt<Q6K>(ctx, P, d_out, ldo, M, epi, d_gate);
     }
     return SLAI_ERR_UNSUPPORTED_FORMAT;
+}
+
+int gemv_batch_launch(slai_ctx* ctx, float* d_out, const slai_qmatrix* w, const float* d_v, int n_batch, long long ldo, int epi,
+                      const float* d_gate) {
+    return gemv_batch_launch_multi(ctx, d_out, &w, 1, d_v, n_batch, ldo, epi, d_gate);
 }

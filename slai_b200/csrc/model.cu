@@ -629,9 +629,17 @@ static int llama_batch_record(slai_llama* m, int B, int cap_pos) {
         void* kc = (char*)m->bt_k + (size_t)l * m->kv_layer_elems * esz;  // layer l of sequence 0; sequence b is bt_cache_bytes further
         void* vc = (char*)m->bt_v + (size_t)l * m->kv_layer_elems * esz;
         if ((rc = rms_norm_rows_launch(ctx, m->bt_xn, m->bt_x, w.attn_norm, c.dim, B, c.rms_norm_eps))) return rc;
-        if ((rc = product(w.wq, m->bt_xn, m->bt_qkv, qkv_ld))) return rc;
-        if ((rc = product(w.wk, m->bt_xn, m->bt_qkv + m->q_dim, qkv_ld))) return rc;
-        if ((rc = product(w.wv, m->bt_xn, m->bt_qkv + m->q_dim + m->kv_dim, qkv_ld))) return rc;
+        // q, k, v in one launch where the three matrices can be walked as one (same format, heights multiples of 16)
+        const bool qkv_one = B > 1 && gemv_batch_supported(w.wq) && w.wk->fmt == w.wq->fmt && w.wv->fmt == w.wq->fmt && m->q_dim % 16 == 0 &&
+                             m->kv_dim % 16 == 0;
+        if (qkv_one) {
+            const slai_qmatrix* ws[3] = {w.wq, w.wk, w.wv};
+            if ((rc = gemv_batch_launch_multi(ctx, m->bt_qkv, ws, 3, m->bt_xn, B, qkv_ld, BATCH_STORE, nullptr))) return rc;
+        } else {
+            if ((rc = product(w.wq, m->bt_xn, m->bt_qkv, qkv_ld))) return rc;
+            if ((rc = product(w.wk, m->bt_xn, m->bt_qkv + m->q_dim, qkv_ld))) return rc;
+            if ((rc = product(w.wv, m->bt_xn, m->bt_qkv + m->q_dim + m->kv_dim, qkv_ld))) return rc;
+        }
         if ((rc = rope_kv_store_seqs_launch(ctx, m->bt_qkv, qkv_ld, m->q_dim, m->kv_dim, m->head_size, d_pos, B, m->rope_theta, c.rope_variant != 0,
                                             m->bt_q, kc, vc, c.kv_dtype == SLAI_KV_F16, kv_head_stride, (long long)m->bt_cache_bytes)))
             return rc;
@@ -648,8 +656,13 @@ static int llama_batch_record(slai_llama* m, int B, int cap_pos) {
         }
         if ((rc = product(w.wo, m->bt_xb, m->bt_x, c.dim, BATCH_ADD))) return rc;
         if ((rc = rms_norm_rows_launch(ctx, m->bt_xn, m->bt_x, w.ffn_norm, c.dim, B, c.rms_norm_eps))) return rc;
-        if ((rc = product(w.wgate, m->bt_xn, m->bt_g, m->hidden))) return rc;
-        if ((rc = product(w.wup, m->bt_xn, m->bt_u, m->hidden, BATCH_SILU, m->bt_g))) return rc;
+        if (B > 1 && gemv_batch_supported(w.wgate) && w.wup->fmt == w.wgate->fmt && m->hidden % 16 == 0) {
+            const slai_qmatrix* ws[2] = {w.wgate, w.wup};  // gate and up in one launch, SiLU in its store
+            if ((rc = gemv_batch_launch_multi(ctx, m->bt_u, ws, 2, m->bt_xn, B, m->hidden, BATCH_PAIR_SILU, nullptr))) return rc;
+        } else {
+            if ((rc = product(w.wgate, m->bt_xn, m->bt_g, m->hidden))) return rc;
+            if ((rc = product(w.wup, m->bt_xn, m->bt_u, m->hidden, BATCH_SILU, m->bt_g))) return rc;
+        }
         if ((rc = product(w.wdown, m->bt_u, m->bt_x, c.dim, BATCH_ADD))) return rc;
     }
     const slai_qmatrix* wout = m->output ? m->output : (m->embd_q ? m->embd_q : &m->embd_as_matrix);
