@@ -60,6 +60,24 @@ impl<'a> Llama2<'a> {
         self.backend.check(unsafe { sys::slai_llama_generate_sampled(self.h, token as i32, pos as i32, n as i32, temperature, topp, seed, out.as_mut_ptr()) })?;
         Ok(out)
     }
+    /// KV caches and activation rows for `n_seq` (1..8) sequences decoded together; 0 frees them.
+    pub fn batch_reserve(&mut self, n_seq: usize) -> Result<(), B200Error> {
+        self.backend.check(unsafe { sys::slai_llama_batch_reserve(self.h, n_seq as i32) })
+    }
+    /// One token of each sequence: `tokens[b]` at `positions[b]` of sequence b's own cache (a negative position leaves the
+    /// sequence out of the step); every weight matrix is read once for all of them.  `logits`, when given, holds
+    /// `tokens.len() * vocab_size` floats.  Returns the greedy token per sequence.
+    pub fn decode_batch(&mut self, tokens: &[i32], positions: &[i32], logits: Option<&mut [f32]>) -> Result<Vec<i32>, B200Error> {
+        if tokens.len() != positions.len() || logits.as_ref().map_or(false, |l| l.len() != tokens.len() * self.vocab) {
+            return Err(B200Error::Shape("decode_batch: one position per token, vocab_size logits per sequence".into()));
+        }
+        let mut next = vec![0i32; tokens.len()];
+        let p = logits.map_or(ptr::null_mut(), |l| l.as_mut_ptr());
+        self.backend.check(unsafe {
+            sys::slai_llama_decode_batch(self.h, tokens.len() as i32, tokens.as_ptr(), positions.as_ptr(), p, next.as_mut_ptr())
+        })?;
+        Ok(next)
+    }
     /// Device time of one decode step per kernel class.
     pub fn stats(&mut self, token: u32, pos: u32) -> Result<Llama2Stats, B200Error> {
         let mut st = Llama2Stats::default();
