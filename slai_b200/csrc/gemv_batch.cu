@@ -11,6 +11,8 @@
 // slice of all vectors once (each vector with its own power-of-two scale for the chunk), then every warp walks its own
 // tile's `ch` blocks, double-buffered with cp.async.  Partial sums per chunk go to a scratch array and a second small
 // kernel adds them in chunk order (deterministic; no atomics).
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "gemv_formats.cuh"
 #include "layout.cuh"
@@ -58,7 +60,9 @@ __device__ __forceinline__ void stage_request(const uint8_t* src, uint32_t dst, 
 }
 __device__ __forceinline__ void stage_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 
-template <class F, int NV>
+// NV vectors are staged; a tile-step block is taken against NC of them at a time (NV / NC passes over the block in shared
+// memory: fewer accumulators live at once).
+template <class F, int NV, int NC = NV>
 __global__ void __launch_bounds__(BTHREADS, 1) gemv_batch_kernel(const __grid_constant__ BatchParams P) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -185,7 +189,19 @@ __global__ void __launch_bounds__(BTHREADS, 1) gemv_batch_kernel(const __grid_co
                 asm volatile("cp.async.wait_group 1;" ::: "memory");  // all but the newest request have landed: block s is here
                 __syncwarp();
                 const uint32_t blk = wb + (uint32_t)(s & 1) * BatchGeom<F>::STRIDE;
-                F::template compute_batch<NV>(blk, s, L, S, bvs, P.vstride, accA, accB);
+                if (NC == NV) {
+                    F::template compute_batch<NV>(blk, s, L, S, bvs, P.vstride, accA, accB);
+                } else {
+#pragma unroll
+                    for (int pass = 0; pass < NV / NC; pass++) {
+                        LaneCtx L2 = L;
+                        L2.bbase += (uint32_t)(pass * NC) * bvs;
+                        Smem S2 = S;
+                        S2.sv += (uint32_t)(pass * NC) * P.vstride;
+                        F::template compute_batch<NC>(blk, s, L2, S2, bvs, P.vstride, reinterpret_cast<float(&)[NC]>(accA[pass * NC]),
+                                                      reinterpret_cast<float(&)[NC]>(accB[pass * NC]));
+                    }
+                }
                 __syncwarp();
                 if (s + 2 < nst) stage_request<F>(src + (size_t)(s + 2) * BatchGeom<F>::STEP, blk, lane);
                 stage_commit();
@@ -249,7 +265,7 @@ size_t batch_smem(int nv, int ch, uint32_t* plane_out, uint32_t* vstride_out) {
     return (size_t)ring_off + (size_t)BWARPS * 2 * BatchGeom<F>::STRIDE;
 }
 
-template <class F, int NV>
+template <class F, int NV, int NC = NV>
 int launch_batch_inst(slai_ctx* ctx, BatchParams& P, float* d_out, long long ldo, int M, int epi, const float* gate) {
     // Steps per chunk: the fewest rounds of (staging + ch steps) over the SMs; staging a chunk costs about three steps.
     const int G = ctx->sm_count > 0 ? ctx->sm_count : 148;
@@ -272,7 +288,7 @@ int launch_batch_inst(slai_ctx* ctx, BatchParams& P, float* d_out, long long ldo
     int rc = ensure_scratch(ctx, part_bytes);
     if (rc) return rc;
     P.part = reinterpret_cast<float*>(ctx->d_scratch);
-    auto kern = gemv_batch_kernel<F, NV>;
+    auto kern = gemv_batch_kernel<F, NV, NC>;
     static PerDeviceOnce attr;  // per instantiation
     if (attr.need(ctx->device)) {
         SLAI_CHECK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BSMEM_LIMIT));
@@ -292,6 +308,11 @@ template <class F>
 int launch_batch_fmt(slai_ctx* ctx, BatchParams& P, float* d_out, long long ldo, int M, int epi, const float* gate) {
     if (P.n_batch <= 2) return launch_batch_inst<F, 2>(ctx, P, d_out, ldo, M, epi, gate);
     if (P.n_batch <= 4) return launch_batch_inst<F, 4>(ctx, P, d_out, ldo, M, epi, gate);
+    // Eight vectors: a block is taken against four of them at a time (two passes over it in shared memory) -- with all
+    // eight at once the accumulators leave the compiler no registers to overlap loads and MMAs (measured 7 % slower on
+    // the 11008-wide shapes).  SLAI_BATCH_PASSES=1 selects the one-pass kernel.
+    static const int passes = [] { const char* e = getenv("SLAI_BATCH_PASSES"); return e ? atoi(e) : 2; }();
+    if (passes != 1) return launch_batch_inst<F, 8, 4>(ctx, P, d_out, ldo, M, epi, gate);
     return launch_batch_inst<F, 8>(ctx, P, d_out, ldo, M, epi, gate);
 }
 
