@@ -340,6 +340,8 @@ int gemv_batch_launch_multi(slai_ctx* ctx, float* d_out, const slai_qmatrix* con
                      "gemv: matrices of one batched launch must share format and width");
         SLAI_REQUIRE(ctx, i == nw - 1 || ws[i]->nrows % 16 == 0, SLAI_ERR_SHAPE, "gemv: %lld rows before another matrix of the launch",
                      (long long)ws[i]->nrows);
+        SLAI_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(ws[i]->data) & 15) == 0 && ws[i]->tile_bytes % 16 == 0, SLAI_ERR_INVALID_ARG,
+                     "gemv: matrix data must be 16-byte aligned");
         P.w[i] = ws[i]->data;
         P.t0[i] = tiles;
         tiles += (int)layout::num_tiles(ws[i]->nrows);
