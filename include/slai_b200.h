@@ -179,7 +179,9 @@ int slai_synth_normal_f32(slai_ctx* ctx, float* d_out, int64_t n, uint64_t seed,
 
 /* ---- GemvQuant::launch (ops/gemv_quant.rs:206-312); LlmContext::matmul_quant_assign (context.rs:355-369)
  * d_out[b*M + i] = sum_k W[i][k] * d_v[b*K + k] for b < n_batch (1 <= n_batch <= 8).  A batch of 2..8 vectors is served
- * by one pass over a quantised matrix (d_v 16-byte aligned); dense f32 matrices take the vectors one by one. */
+ * by one pass over a quantised matrix (d_v 16-byte aligned); dense f32 matrices take the vectors one by one.  The batched
+ * kernel keeps per-chunk partial sums in the context's scratch buffer, grown on demand: inside a recorded pass
+ * (slai_pass_begin) call it only after one eager call of the same matrix shape and batch. */
 int slai_gemv_quant(slai_ctx* ctx, float* d_out, const slai_qmatrix* w, const float* d_v, int n_batch);
 /* The feed-forward front half of a Llama layer as one kernel: out[hidden] = silu(Wgate n(x)) * (Wup n(x)) with
  * n = RmsNorm by `d_norm_w` and `eps` (null weights: x is used as it is).  Replaces the four dispatches RmsNorm::launch,
